@@ -1,0 +1,370 @@
+/*
+ * tensor_ash.h -- C ABI of the B200-native tensor-ash GEMM path.
+ *
+ * PART 1 restates, declaration for declaration, the C interface of the
+ * reference project (its include/tensor_ash.h, lines cited per item as
+ * "ref h:LINE"; the Rust implementation it binds is cited as "ref capi/...").
+ * A program compiled against the reference header links against this library
+ * unchanged: same type names, field order, enum values, function signatures,
+ * status convention (0 / -1, pointer / NULL, message in ta_last_error()).
+ *
+ * PART 2 adds entry points for hot-path functions the reference exposes only
+ * through its Rust API (split-K2, packed / normed-A / fused-store ops,
+ * flash and decode attention, mixed op graphs, position/token cells).  They
+ * are additive: nothing in PART 1 changes shape.
+ *
+ * Every function clears the calling thread's error string on entry.  Handles
+ * are heap objects; destroying NULL is a no-op.  A tensor handed to an
+ * executor must come from the executor's own context.
+ */
+#ifndef TENSOR_ASH_H
+#define TENSOR_ASH_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===================================================================== */
+/* PART 1 -- the reference C ABI                                         */
+/* ===================================================================== */
+
+/* Opaque handles (ref h:11-14; ref capi/src/handles.rs:6-44). */
+typedef struct ta_context ta_context;
+typedef struct ta_executor ta_executor;
+typedef struct ta_tensor ta_tensor;
+typedef struct ta_prepared ta_prepared;
+
+/* Result of one submission (ref h:16-22; ref capi/src/api/matmul.rs:86-102).
+ * gpu_time_ns is device time between two events on the launch stream;
+ * tflops is NaN when has_gpu_time is 0 or the time is 0. */
+typedef struct ta_run_stats {
+  uint32_t has_gpu_time;
+  uint64_t gpu_time_ns;
+  size_t n_calls;
+  uint64_t total_flops;
+  double tflops;
+} ta_run_stats;
+
+/* C = alpha * A @ B (+ C when accumulate != 0)  (ref h:24-30). */
+typedef struct ta_matmul_call {
+  const ta_tensor *a;
+  const ta_tensor *b;
+  const ta_tensor *c;
+  float alpha;
+  uint32_t accumulate;
+} ta_matmul_call;
+
+/* ta_epilogue.activation (ref h:32-38). */
+enum {
+  TA_ACTIVATION_NONE = 0,
+  TA_ACTIVATION_RELU = 1,
+  TA_ACTIVATION_SILU = 2, /* x / (1 + exp(-x)) */
+  TA_ACTIVATION_GELU = 3  /* 0.5 x (1 + tanh(k0 (x + 0.044715 x^3))) */
+};
+
+/* ta_epilogue.binary_kind (ref h:40-45). */
+enum {
+  TA_BINARY_NONE = 0,
+  TA_BINARY_ADD_SCALED = 1, /* out = act + beta * D */
+  TA_BINARY_MUL = 2         /* out = act * D        */
+};
+
+/* Fused epilogue, applied on the accumulator drain in this order:
+ * alpha*acc (+C_old) -> +bias -> activation -> binary with D  (ref h:47-59).
+ * All-zero means none.  bias is [N] or [B, N]; d is non-NULL iff
+ * binary_kind != 0 and has exactly C's shape. */
+typedef struct ta_epilogue {
+  const ta_tensor *bias;
+  uint32_t activation;
+  uint32_t binary_kind;
+  const ta_tensor *d;
+  float beta;
+} ta_epilogue;
+
+/* One GEMM with its epilogue (ref h:61-65). */
+typedef struct ta_matmul_op {
+  ta_matmul_call call;
+  ta_epilogue epilogue;
+} ta_matmul_op;
+
+/* ta_softmax_rows mask_kind (ref h:67-76). */
+enum {
+  TA_SOFTMAX_MASK_FULL = 0,
+  TA_SOFTMAX_MASK_PREFIX = 1, /* columns >= valid_or_prefix store 0 */
+  TA_SOFTMAX_MASK_CAUSAL = 2  /* row i sees valid_or_prefix + (i % rows_per_group) + 1 columns */
+};
+
+/* Rotary geometry (ref h:78-88): rot_dim even, 2 <= rot_dim <= head_dim. */
+typedef struct ta_rope_desc {
+  uint32_t heads;
+  uint32_t head_dim;
+  uint32_t rot_dim;
+  uint32_t pos_base;
+} ta_rope_desc;
+
+/* 3-D strided copy, strides and offsets in elements (ref h:90-98). */
+typedef struct ta_copy_desc {
+  uint32_t extent[3];
+  uint32_t src_offset;
+  uint32_t src_strides[3];
+  uint32_t dst_offset;
+  uint32_t dst_strides[3];
+} ta_copy_desc;
+
+/* Route report (ref h:100-108).  kernel is interned for the process lifetime. */
+typedef struct ta_dispatch_info {
+  const char *kernel;
+  uint32_t tile[3];
+  uint32_t has_split_k2;
+  uint32_t split_k2_splits;
+} ta_dispatch_info;
+
+/* ref h:110-111; ref capi/src/api/lifecycle.rs:11-21.  Version "2.0.0". */
+const char *ta_version(void);
+const char *ta_last_error(void);
+
+/* ref h:113-116.  device_preference: NULL/"auto", or "index:N" for CUDA
+ * device N (the reference's adapter-kind names are accepted and mean auto). */
+ta_context *ta_context_create(uint32_t enable_validation, const char *device_preference);
+void ta_context_destroy(ta_context *ctx);
+
+/* ref h:118-120: 0 for NULL, 1 on every CUDA device this library runs on. */
+uint32_t ta_context_supports_f16(const ta_context *ctx);
+uint32_t ta_context_supports_bda(const ta_context *ctx);
+
+/* ref h:122-135; ref capi/src/api/lifecycle.rs:60-127.  n_slots = concurrent
+ * submissions (one CUDA stream each); kernel_selection NULL/"auto" or any
+ * registry name / alias (ML_KERNEL syntax). */
+ta_executor *ta_executor_create(const ta_context *ctx, size_t n_slots,
+                                uint32_t max_calls_per_submit, const char *kernel_selection);
+ta_executor *ta_executor_create_v2(const ta_context *ctx, size_t n_slots,
+                                   uint32_t max_calls_per_submit, const char *kernel_selection,
+                                   uint32_t tune);
+void ta_executor_destroy(ta_executor *exec);
+
+/* ref h:137-153; ref capi/src/api/tensor.rs.  rank >= 1, every dim > 0;
+ * contents uninitialised.  f16 tensors keep the float host API. */
+ta_tensor *ta_tensor_create(const ta_context *ctx, const uint32_t *shape, size_t rank);
+ta_tensor *ta_tensor_create_on_executor(const ta_executor *exec, const uint32_t *shape,
+                                        size_t rank);
+ta_tensor *ta_tensor_create_f16(const ta_context *ctx, const uint32_t *shape, size_t rank);
+ta_tensor *ta_tensor_create_f16_on_executor(const ta_executor *exec, const uint32_t *shape,
+                                            size_t rank);
+void ta_tensor_destroy(ta_tensor *tensor);
+uint64_t ta_tensor_len(const ta_tensor *tensor);        /* elements; 0 for NULL */
+uint64_t ta_tensor_size_bytes(const ta_tensor *tensor); /* f16 rounded up to 16 B */
+uint32_t ta_tensor_is_f16(const ta_tensor *tensor);
+
+/* ref h:155-158; ref src/executor/transfer.rs:21-84.  Host side is float;
+ * f16 tensors round to nearest-even on upload and widen on download.
+ * len may be below capacity; above it the call fails. */
+int ta_upload(const ta_executor *exec, const ta_tensor *dst, const float *src, size_t len);
+int ta_download(const ta_executor *exec, const ta_tensor *src, float *dst, size_t len);
+
+/* ref h:160-164; ref src/executor/dispatch.rs:31-85. */
+int ta_matmul(const ta_executor *exec, const ta_tensor *a, const ta_tensor *b, const ta_tensor *c,
+              float alpha, uint32_t accumulate, ta_run_stats *stats);
+int ta_matmul_batch(const ta_executor *exec, const ta_matmul_call *calls, size_t n_calls,
+                    ta_run_stats *stats);
+
+/* ref h:166-175; ref src/executor/dispatch.rs:87-188.  ta_run_ops: independent
+ * ops, one submission.  ta_run_op_graph: later ops may read earlier outputs. */
+int ta_run_ops(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops,
+               ta_run_stats *stats);
+int ta_run_op_graph(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops,
+                    ta_run_stats *stats);
+
+/* Model ops (ref h:177-209; ref capi/src/api/elementwise.rs).  Operands f32.
+ * In place is allowed except for ta_copy_strided (src != dst). */
+int ta_softmax_rows(const ta_executor *exec, const ta_tensor *input, const ta_tensor *output,
+                    float scale, uint32_t mask_kind, uint32_t valid_or_prefix,
+                    uint32_t rows_per_group, ta_run_stats *stats);
+int ta_rms_norm(const ta_executor *exec, const ta_tensor *input, const ta_tensor *weight,
+                const ta_tensor *output, float eps, ta_run_stats *stats);
+int ta_layer_norm(const ta_executor *exec, const ta_tensor *input, const ta_tensor *weight,
+                  const ta_tensor *bias, const ta_tensor *output, float eps, ta_run_stats *stats);
+int ta_rope(const ta_executor *exec, const ta_tensor *input, const ta_tensor *table,
+            const ta_tensor *output, const ta_rope_desc *desc, ta_run_stats *stats);
+int ta_copy_strided(const ta_executor *exec, const ta_tensor *src, const ta_tensor *dst,
+                    const ta_copy_desc *desc, ta_run_stats *stats);
+
+/* Prepared replay (ref h:211-233; ref src/executor/prepared.rs:46-353).  The
+ * op batch is validated, routed and captured once (a CUDA graph) and replayed
+ * per call.  The executor and every referenced tensor must outlive the handle;
+ * one submission in flight per handle; destroy waits for in-flight work. */
+ta_prepared *ta_prepared_create(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops,
+                                uint32_t as_graph);
+int ta_prepared_run(ta_prepared *prepared, ta_run_stats *stats);
+int ta_prepared_submit(ta_prepared *prepared);
+int ta_prepared_wait(ta_prepared *prepared, ta_run_stats *stats);
+void ta_prepared_destroy(ta_prepared *prepared);
+
+/* ref h:235-244; ref capi/src/api/diagnostics.rs. */
+int ta_dispatch_info_for(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t n,
+                         uint32_t k, uint32_t b_f16, ta_dispatch_info *out);
+int ta_tune_shape(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
+
+/* ===================================================================== */
+/* PART 2 -- additive entry points for the rest of the hot path          */
+/* ===================================================================== */
+
+/* Deterministic two-stage split-K: partial planes to executor scratch, then a
+ * fixed-order plane sum; no atomics, run-to-run bit-identical.  Replaces
+ * Executor::run_matmuls_split_k2 (ref src/executor/reduction.rs:21-70).
+ * splits == 0 picks the default (ref src/executor/splitk2.rs:94-122); splits
+ * <= 1 after that runs the plain route; accumulate is rejected. */
+int ta_matmul_split_k2(const ta_executor *exec, const ta_matmul_call *calls, size_t n_calls,
+                       uint32_t splits, ta_run_stats *stats);
+
+/* ta_store_desc.kind: fused store of an M == 1 f16-weight GEMV
+ * (ref src/matmul/api.rs:120-250, MatmulStore / MatmulStoreDesc). */
+enum {
+  TA_STORE_NONE = 0,
+  TA_STORE_ROPE = 1,        /* rotate pairs, write to C */
+  TA_STORE_SCATTER = 2,     /* write to dst at pos*pos_scale + head*stride_head + d*stride_dim */
+  TA_STORE_ROPE_SCATTER = 3 /* rotate, then scatter */
+};
+
+typedef struct ta_store_desc {
+  uint32_t kind;
+  uint32_t head_dim;
+  uint32_t pos_base;    /* position when pos_cell is NULL */
+  uint32_t pos_scale;   /* elements per position in dst */
+  uint32_t stride_head; /* elements between heads in dst */
+  uint32_t stride_dim;  /* elements between lanes of a head in dst */
+  const ta_tensor *table; /* rope (cos, sin) table [T_max, head_dim/2, 2]; kinds 1 and 3 */
+  const ta_tensor *dst;   /* scatter destination (f32 or f16); kinds 2 and 3 */
+} ta_store_desc;
+
+/* ta_matmul_op plus the fields the reference keeps Rust-only
+ * (ref capi/src/api/ops.rs:63-68 sets them to "none"):
+ *   packed_b      B is [N/tile][K][tile] f16 (ref src/matmul/api.rs:317-344);
+ *   normed_weight fused RMSNorm of A: a'[k] = a[k] * rsqrt(mean(a^2)+eps) * w[k]
+ *                 (ref src/matmul/resolution.rs:217-247);
+ *   store         fused RoPE / scatter store. */
+typedef struct ta_matmul_op_ex {
+  ta_matmul_op op;
+  uint32_t packed_b;
+  const ta_tensor *normed_weight;
+  float normed_eps;
+  ta_store_desc store;
+} ta_matmul_op_ex;
+
+int ta_run_ops_ex(const ta_executor *exec, const ta_matmul_op_ex *ops, size_t n_ops,
+                  uint32_t as_graph, ta_run_stats *stats);
+
+/* One launch computing silu(x @ Wg) * (x @ Wup) for packed f16 weights that
+ * share x: the decode SwiGLU gate.  The reference issues this as an `up` GEMV
+ * followed by a `gate` GEMV whose Mul epilogue reads `up`
+ * (ref tools/llama-ash/src/model/forward/mod.rs:194-206); arithmetic per
+ * output is the same, x is read once.  x [M, K] f32 (M <= 8), wg/wup packed
+ * f16 [K, N], out [M, N] f32.  normed_weight may be NULL. */
+int ta_swiglu_gemv(const ta_executor *exec, const ta_tensor *x, const ta_tensor *wg,
+                   const ta_tensor *wup, const ta_tensor *out, const ta_tensor *normed_weight,
+                   float normed_eps, ta_run_stats *stats);
+
+/* Packed-weight helpers (ref src/matmul/api.rs:317-344,
+ * ref src/pipeline/routing.rs:10-41).  Host-only; no device is touched. */
+int ta_pack_f16w_row_tiles(const float *src, float *dst, size_t k, size_t n, size_t tile_n);
+uint32_t ta_f16w_row_tile_n(uint32_t k, uint32_t n);
+
+/* Raw binary16 upload into an f16 tensor (ref src/executor/transfer.rs:44-62). */
+int ta_upload_f16(const ta_executor *exec, const ta_tensor *dst, const uint16_t *src, size_t len);
+
+/* A second handle over the same device memory under another shape with the
+ * same element count (ref src/tensor.rs:96-112).  Destroy both handles; the
+ * memory is released with the last one. */
+ta_tensor *ta_tensor_alias_with_shape(const ta_tensor *tensor, const uint32_t *shape, size_t rank);
+
+/* Causal prefill flash attention (ref src/executor/elementwise/flash.rs:26-253,
+ * FlashAttentionDesc ref src/executor/elementwise/mod.rs:162-184).
+ * kt [H_kv, dh, T_max], v [H_kv, T_max, dh] (f32 or f16, same dtype);
+ * q/out [H, T_q, dh], or token-major [T_q, H*dh] when token_major != 0.
+ * Row i attends positions < min(kv_len, pos_base + i + 1). */
+typedef struct ta_flash_desc {
+  uint32_t heads;
+  uint32_t kv_heads;
+  uint32_t head_dim; /* 64 or 128 */
+  uint32_t t_q;
+  uint32_t kv_len;
+  uint32_t pos_base;
+  float scale;
+  uint32_t token_major;
+} ta_flash_desc;
+
+int ta_flash_attention(const ta_executor *exec, const ta_tensor *q, const ta_tensor *kt,
+                       const ta_tensor *v, const ta_tensor *out, const ta_flash_desc *desc,
+                       ta_run_stats *stats);
+
+/* Split-K decode attention, two launches (ref src/executor/elementwise/attn.rs:27-185,
+ * AttnDecodeDesc ref src/executor/elementwise/mod.rs:202-237).  q/out
+ * [H_kv, group, dh] f32; scratch >= kv_heads * chunks * group * (dh + 2) f32.
+ * pos_cell, when non-NULL, overrides kv_len with (*cell + 1) read on the
+ * device at run time and fixes the chunk count at TA_ATTN_DECODE_MAX_CHUNKS. */
+#define TA_ATTN_DECODE_MAX_CHUNKS 32u
+typedef struct ta_pos_cell ta_pos_cell;
+
+typedef struct ta_attn_decode_desc {
+  uint32_t kv_heads;
+  uint32_t group; /* Q heads per KV head, <= 8 */
+  uint32_t head_dim; /* 64 */
+  uint32_t kv_len;
+  float scale;
+  const ta_pos_cell *pos_cell;
+} ta_attn_decode_desc;
+
+uint32_t ta_attn_decode_num_chunks(uint32_t kv_len);
+int ta_attn_decode(const ta_executor *exec, const ta_tensor *q, const ta_tensor *kt,
+                   const ta_tensor *v, const ta_tensor *scratch, const ta_tensor *out,
+                   const ta_attn_decode_desc *desc, ta_run_stats *stats);
+
+/* 4-byte host-visible cells read or written by kernels in replayed graphs
+ * (ref src/executor/cells.rs:51-201: PosBuffer, HostU32Buffer). */
+ta_pos_cell *ta_pos_cell_create(const ta_context *ctx);
+void ta_pos_cell_destroy(ta_pos_cell *cell);
+int ta_pos_cell_set(ta_pos_cell *cell, uint32_t value);
+int ta_pos_cell_get(const ta_pos_cell *cell, uint32_t *value);
+
+/* Registry and routing introspection (ref src/pipeline/catalog.rs:10-41,129-376).
+ * Host-only. */
+size_t ta_kernel_spec_count(void);
+/* Fills name/tile for registry entry `index`; -1 when out of range. */
+int ta_kernel_spec_at(size_t index, ta_dispatch_info *out);
+/* Resolves an ML_KERNEL-style name or alias to a registry index; -2 for
+ * "auto", -1 (with an error message) for an unknown name. */
+int ta_kernel_selection_parse(const char *name);
+
+/* Shape resolution exactly as a matmul call would do it
+ * (ref src/matmul/resolution.rs:16-76,421-441), without touching a device.
+ * Shapes are rank-2/3 arrays.  On success fills out[0..8] =
+ * {m, n, k, batch, stride_a, stride_b, stride_c, flops_lo32, flops_hi32}. */
+int ta_resolve_shapes(const uint32_t *a, size_t a_rank, const uint32_t *b, size_t b_rank,
+                      const uint32_t *c, size_t c_rank, uint32_t out[9]);
+
+/* Split-K heuristics (ref src/executor/splitk2.rs:48-122).  Host-only.
+ * ta_heuristic_splits returns 0 when the shape stays data-parallel. */
+uint32_t ta_default_num_k_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k,
+                                 uint32_t tile_m, uint32_t tile_n);
+uint32_t ta_heuristic_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
+
+/* Bit-exact software conversions (ref src/dtype.rs:42-112).  Host-only. */
+uint16_t ta_f32_to_f16_bits(float value);
+float ta_f16_bits_to_f32(uint16_t bits);
+
+/* Interop for callers that own device memory or streams themselves: the raw
+ * CUDA device pointer of a tensor and the CUDA device ordinal of a context. */
+void *ta_tensor_device_ptr(const ta_tensor *tensor);
+int ta_context_device_index(const ta_context *ctx);
+
+/* Kernels launched by this library on the calling process since load; a
+ * caller can difference it around a region to count launches. */
+uint64_t ta_kernel_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TENSOR_ASH_H */

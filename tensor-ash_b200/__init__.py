@@ -1,0 +1,36 @@
+"""tensor-ash GEMM hot path, B200-native: Python host mirror over the C ABI.
+
+Everything here is a thin ctypes layer over ``lib/libtensor_ash.so`` (the
+``tensor_ash.h`` symbols).  Class and method names follow the reference crate's
+public API (``src/lib.rs:34-58``: ``Executor``, ``Tensor``, ``MatmulCall``,
+``MatmulOp``, ``Epilogue``, ``Activation``, ``PreparedOps``, ``RunStats``,
+``pack_f16w_row_tiles``, ``f16w_row_tile_n`` ...), so parity tests read like the
+reference's own.  There is no CPU path: if the shared library is missing the
+import of :mod:`capi` raises, and every compute call needs a CUDA device.
+"""
+from .api import (  # noqa: F401
+    Activation,
+    Binary,
+    Context,
+    DispatchInfo,
+    Epilogue,
+    Executor,
+    MatmulCall,
+    MatmulOp,
+    PreparedOps,
+    RunStats,
+    Tensor,
+    TensorAshError,
+    default_num_k_splits,
+    f16w_row_tile_n,
+    f32_to_f16_bits,
+    f16_bits_to_f32,
+    heuristic_splits,
+    kernel_launch_count,
+    kernel_selection_parse,
+    kernel_specs,
+    pack_f16w_row_tiles,
+    resolve_shapes,
+    version,
+)
+from .capi import lib, lib_path  # noqa: F401

@@ -1,0 +1,436 @@
+"""Host-side mirror of the reference crate's public API, over the C ABI.
+
+Reference types mirrored (paths in the reference project):
+  Executor / ExecutorConfig      src/executor/mod.rs:85-369
+  Tensor                         src/tensor.rs:20-201
+  MatmulCall / MatmulOp / Epilogue / Activation / EpilogueBinary / RunStats
+                                 src/matmul/api.rs:3-353
+  PreparedOps                    src/executor/prepared.rs:46-353
+  DispatchInfo                   src/executor/mod.rs:61-81
+Errors surface as :class:`TensorAshError` carrying ``ta_last_error()``, the
+analogue of the crate's ``anyhow::Result`` failures.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import capi
+from .capi import lib
+
+
+class TensorAshError(RuntimeError):
+    pass
+
+
+def _err() -> str:
+    return (lib().ta_last_error() or b"").decode("utf-8", "replace")
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise TensorAshError(_err())
+
+
+def version() -> str:
+    return lib().ta_version().decode()
+
+
+class Activation(enum.IntEnum):
+    NONE = 0
+    RELU = 1
+    SILU = 2
+    GELU = 3
+
+
+class Binary(enum.IntEnum):
+    NONE = 0
+    ADD_SCALED = 1
+    MUL = 2
+
+
+@dataclass
+class RunStats:
+    gpu_time_ns: Optional[int]
+    n_calls: int
+    total_flops: int
+
+    def tflops(self) -> Optional[float]:
+        if not self.gpu_time_ns:
+            return None
+        return self.total_flops / self.gpu_time_ns * 1e-3
+
+    @staticmethod
+    def _from(c: capi.RunStatsC) -> "RunStats":
+        return RunStats(int(c.gpu_time_ns) if c.has_gpu_time else None, int(c.n_calls),
+                        int(c.total_flops))
+
+
+@dataclass
+class DispatchInfo:
+    kernel: str
+    tile: tuple
+    split_k2: Optional[int]
+
+
+class Context:
+    """A CUDA device (``VulkanContext`` in the reference)."""
+
+    def __init__(self, validation: bool = False, device: Optional[str] = "auto"):
+        h = lib().ta_context_create(int(validation), device.encode() if device is not None else None)
+        if not h:
+            raise TensorAshError(_err())
+        self._h = h
+
+    @property
+    def supports_f16(self) -> bool:
+        return bool(lib().ta_context_supports_f16(self._h))
+
+    @property
+    def supports_bda(self) -> bool:
+        return bool(lib().ta_context_supports_bda(self._h))
+
+    @property
+    def device_index(self) -> int:
+        return int(lib().ta_context_device_index(self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().ta_context_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _shape_arr(shape: Sequence[int]):
+    return (C.c_uint32 * len(shape))(*[int(d) for d in shape]), len(shape)
+
+
+class Tensor:
+    """Row-major contiguous device tensor, f32 or f16 storage."""
+
+    def __init__(self, handle, ctx: Context, shape, keepalive=None):
+        self._h = handle
+        self.ctx = ctx
+        self.shape = tuple(int(d) for d in shape)
+        self._keepalive = keepalive
+
+    @staticmethod
+    def uninit_device(ctx: Context, shape) -> "Tensor":
+        arr, rank = _shape_arr(shape)
+        h = lib().ta_tensor_create(ctx._h, arr, rank)
+        if not h:
+            raise TensorAshError(_err())
+        return Tensor(h, ctx, shape)
+
+    @staticmethod
+    def uninit_device_f16(ctx: Context, shape) -> "Tensor":
+        arr, rank = _shape_arr(shape)
+        h = lib().ta_tensor_create_f16(ctx._h, arr, rank)
+        if not h:
+            raise TensorAshError(_err())
+        return Tensor(h, ctx, shape)
+
+    def alias_with_shape(self, shape) -> "Tensor":
+        arr, rank = _shape_arr(shape)
+        h = lib().ta_tensor_alias_with_shape(self._h, arr, rank)
+        if not h:
+            raise TensorAshError(_err())
+        return Tensor(h, self.ctx, shape, keepalive=self)
+
+    def len(self) -> int:
+        return int(lib().ta_tensor_len(self._h))
+
+    def size_bytes(self) -> int:
+        return int(lib().ta_tensor_size_bytes(self._h))
+
+    @property
+    def is_f16(self) -> bool:
+        return bool(lib().ta_tensor_is_f16(self._h))
+
+    @property
+    def device_ptr(self) -> int:
+        return int(lib().ta_tensor_device_ptr(self._h) or 0)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().ta_tensor_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+@dataclass
+class MatmulCall:
+    a: Tensor
+    b: Tensor
+    c: Tensor
+    alpha: float = 1.0
+    accumulate: bool = False
+
+    def _c(self) -> capi.MatmulCallC:
+        return capi.MatmulCallC(self.a._h, self.b._h, self.c._h, self.alpha, int(self.accumulate))
+
+
+@dataclass
+class Epilogue:
+    bias: Optional[Tensor] = None
+    activation: Activation = Activation.NONE
+    binary: Binary = Binary.NONE
+    d: Optional[Tensor] = None
+    beta: float = 0.0
+
+    def _c(self) -> capi.EpilogueC:
+        return capi.EpilogueC(self.bias._h if self.bias is not None else None, int(self.activation),
+                              int(self.binary), self.d._h if self.d is not None else None, self.beta)
+
+
+@dataclass
+class MatmulOp:
+    call: MatmulCall
+    epilogue: Epilogue = field(default_factory=Epilogue)
+
+    def _c(self) -> capi.MatmulOpC:
+        return capi.MatmulOpC(self.call._c(), self.epilogue._c())
+
+
+def _ops_array(ops: Sequence[MatmulOp]):
+    arr = (capi.MatmulOpC * max(len(ops), 1))()
+    for i, op in enumerate(ops):
+        arr[i] = op._c()
+    return arr
+
+
+class PreparedOps:
+    """Record-once / replay-many op batch (a captured CUDA graph)."""
+
+    def __init__(self, handle, keepalive):
+        self._h = handle
+        self._keepalive = keepalive
+
+    def run(self) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_prepared_run(self._h, C.byref(st)))
+        return RunStats._from(st)
+
+    def submit(self) -> None:
+        _check(lib().ta_prepared_submit(self._h))
+
+    def wait(self) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_prepared_wait(self._h, C.byref(st)))
+        return RunStats._from(st)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().ta_prepared_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Executor:
+    """Validates, routes and submits ops on one device."""
+
+    def __init__(self, ctx: Context, n_slots: int = 2, max_calls_per_submit: int = 16,
+                 kernel: Optional[str] = "auto", tune: bool = False):
+        sel = kernel.encode() if kernel is not None else None
+        h = lib().ta_executor_create_v2(ctx._h, n_slots, max_calls_per_submit, sel, int(tune))
+        if not h:
+            raise TensorAshError(_err())
+        self._h = h
+        self.ctx = ctx
+
+    # ---- transfers (host side is always f32)
+    def upload(self, src: np.ndarray, dst: Tensor) -> None:
+        src = np.ascontiguousarray(src, dtype=np.float32)
+        _check(lib().ta_upload(self._h, dst._h, src.ctypes.data, src.size))
+
+    def upload_f16(self, src: np.ndarray, dst: Tensor) -> None:
+        src = np.ascontiguousarray(src, dtype=np.uint16)
+        _check(lib().ta_upload_f16(self._h, dst._h, src.ctypes.data, src.size))
+
+    def download(self, src: Tensor, n: Optional[int] = None) -> np.ndarray:
+        n = src.len() if n is None else n
+        out = np.empty(n, dtype=np.float32)
+        _check(lib().ta_download(self._h, src._h, out.ctypes.data, n))
+        return out.reshape(src.shape) if n == src.len() else out
+
+    def download_into(self, src: Tensor, out: np.ndarray) -> None:
+        assert out.dtype == np.float32 and out.flags.c_contiguous
+        _check(lib().ta_download(self._h, src._h, out.ctypes.data, out.size))
+
+    # ---- GEMM
+    def run_matmuls(self, calls: Sequence[MatmulCall]) -> RunStats:
+        arr = (capi.MatmulCallC * max(len(calls), 1))()
+        for i, c in enumerate(calls):
+            arr[i] = c._c()
+        st = capi.RunStatsC()
+        _check(lib().ta_matmul_batch(self._h, arr, len(calls), C.byref(st)))
+        return RunStats._from(st)
+
+    def matmul(self, a: Tensor, b: Tensor, c: Tensor, alpha: float = 1.0,
+               accumulate: bool = False) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_matmul(self._h, a._h, b._h, c._h, alpha, int(accumulate), C.byref(st)))
+        return RunStats._from(st)
+
+    def run_ops(self, ops: Sequence[MatmulOp]) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_run_ops(self._h, _ops_array(ops), len(ops), C.byref(st)))
+        return RunStats._from(st)
+
+    def run_op_graph(self, ops: Sequence[MatmulOp]) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_run_op_graph(self._h, _ops_array(ops), len(ops), C.byref(st)))
+        return RunStats._from(st)
+
+    def run_matmuls_split_k2(self, calls: Sequence[MatmulCall], splits: int = 0) -> RunStats:
+        arr = (capi.MatmulCallC * max(len(calls), 1))()
+        for i, c in enumerate(calls):
+            arr[i] = c._c()
+        st = capi.RunStatsC()
+        _check(lib().ta_matmul_split_k2(self._h, arr, len(calls), splits, C.byref(st)))
+        return RunStats._from(st)
+
+    def prepare_ops(self, ops: Sequence[MatmulOp], as_graph: bool = False) -> PreparedOps:
+        h = lib().ta_prepared_create(self._h, _ops_array(ops), len(ops), int(as_graph))
+        if not h:
+            raise TensorAshError(_err())
+        return PreparedOps(h, (self, list(ops)))
+
+    # ---- routing
+    def dispatch_info_for(self, batch: int, m: int, n: int, k: int, b_f16: bool = False) -> DispatchInfo:
+        out = capi.DispatchInfoC()
+        _check(lib().ta_dispatch_info_for(self._h, batch, m, n, k, int(b_f16), C.byref(out)))
+        return DispatchInfo(out.kernel.decode(), tuple(out.tile),
+                            int(out.split_k2_splits) if out.has_split_k2 else None)
+
+    def tune_shape(self, batch: int, m: int, n: int, k: int) -> None:
+        _check(lib().ta_tune_shape(self._h, batch, m, n, k))
+
+    # ---- model ops
+    def softmax_rows(self, inp: Tensor, out: Tensor, scale: float = 1.0, mask_kind: int = 0,
+                     valid_or_prefix: int = 0, rows_per_group: int = 0) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_softmax_rows(self._h, inp._h, out._h, scale, mask_kind, valid_or_prefix,
+                                     rows_per_group, C.byref(st)))
+        return RunStats._from(st)
+
+    def rms_norm(self, inp: Tensor, weight: Tensor, out: Tensor, eps: float) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_rms_norm(self._h, inp._h, weight._h, out._h, eps, C.byref(st)))
+        return RunStats._from(st)
+
+    def layer_norm(self, inp: Tensor, weight: Tensor, bias: Tensor, out: Tensor, eps: float) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_layer_norm(self._h, inp._h, weight._h, bias._h, out._h, eps, C.byref(st)))
+        return RunStats._from(st)
+
+    def rope(self, inp: Tensor, table: Tensor, out: Tensor, heads: int, head_dim: int, rot_dim: int,
+             pos_base: int = 0) -> RunStats:
+        st = capi.RunStatsC()
+        desc = capi.RopeDescC(heads, head_dim, rot_dim, pos_base)
+        _check(lib().ta_rope(self._h, inp._h, table._h, out._h, C.byref(desc), C.byref(st)))
+        return RunStats._from(st)
+
+    def copy_strided(self, src: Tensor, dst: Tensor, extent, src_offset, src_strides, dst_offset,
+                     dst_strides) -> RunStats:
+        st = capi.RunStatsC()
+        desc = capi.CopyDescC((C.c_uint32 * 3)(*extent), src_offset, (C.c_uint32 * 3)(*src_strides),
+                              dst_offset, (C.c_uint32 * 3)(*dst_strides))
+        _check(lib().ta_copy_strided(self._h, src._h, dst._h, C.byref(desc), C.byref(st)))
+        return RunStats._from(st)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().ta_executor_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------- host-only helpers
+def pack_f16w_row_tiles(src: np.ndarray, k: int, n: int, tile_n: int) -> np.ndarray:
+    src = np.ascontiguousarray(src, dtype=np.float32).reshape(-1)
+    if src.size != k * n:
+        raise TensorAshError("pack_f16w_row_tiles: src len")
+    out = np.empty_like(src)
+    _check(lib().ta_pack_f16w_row_tiles(src.ctypes.data, out.ctypes.data, k, n, tile_n))
+    return out
+
+
+def f16w_row_tile_n(k: int, n: int) -> int:
+    return int(lib().ta_f16w_row_tile_n(k, n))
+
+
+def f32_to_f16_bits(v: float) -> int:
+    return int(lib().ta_f32_to_f16_bits(v))
+
+
+def f16_bits_to_f32(bits: int) -> float:
+    return float(lib().ta_f16_bits_to_f32(bits))
+
+
+def default_num_k_splits(batch, m, n, k, tile_m, tile_n) -> int:
+    return int(lib().ta_default_num_k_splits(batch, m, n, k, tile_m, tile_n))
+
+
+def heuristic_splits(batch, m, n, k) -> Optional[int]:
+    return int(lib().ta_heuristic_splits(batch, m, n, k)) or None
+
+
+def kernel_specs():
+    out = []
+    for i in range(lib().ta_kernel_spec_count()):
+        d = capi.DispatchInfoC()
+        _check(lib().ta_kernel_spec_at(i, C.byref(d)))
+        out.append((d.kernel.decode(), tuple(d.tile)))
+    return out
+
+
+def kernel_selection_parse(name: str):
+    """Registry index for an ML_KERNEL-style name, or None for auto."""
+    rc = lib().ta_kernel_selection_parse(name.encode())
+    if rc == -1:
+        raise TensorAshError(_err())
+    return None if rc == -2 else rc
+
+
+def resolve_shapes(a, b, c) -> dict:
+    aa, ar = _shape_arr(a)
+    ba, br = _shape_arr(b)
+    ca, cr = _shape_arr(c)
+    out = (C.c_uint32 * 9)()
+    _check(lib().ta_resolve_shapes(aa, ar, ba, br, ca, cr, out))
+    return dict(m=out[0], n=out[1], k=out[2], batch=out[3], batch_stride_a=out[4],
+                batch_stride_b=out[5], batch_stride_c=out[6], total_flops=out[7] | (out[8] << 32))
+
+
+def kernel_launch_count() -> int:
+    return int(lib().ta_kernel_launch_count())
+
+
+def is_nan(x: float) -> bool:
+    return math.isnan(x)

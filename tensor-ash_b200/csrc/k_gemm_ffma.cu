@@ -1,0 +1,220 @@
+// SIMT FFMA GEMM tiles: the any-shape, any-alignment FP32 route, its f16-weight
+// sibling, and the stage-1 / reduce kernels of deterministic two-stage split-K.
+//
+// Arithmetic follows the reference's default FP32 shader
+// (shaders/matmul_bda_v4_kernel.glsl:296-323): every output element is one
+// thread's fmaf chain over k ascending, f16 B is widened exactly to f32 while
+// staging (:124-146), and the fused epilogue runs at the store (:377-451).
+// Split-K stage 1 partitions K as shaders/matmul_splitk2_kernel.glsl:138-142
+// and plain-stores alpha*partial into plane (batch*S + split) (:197-215);
+// the reduce sums planes s = 0..S-1 in order
+// (shaders/matmul_f32_splitk2_reduce.comp:54-59), which is what makes the
+// route bit-stable from run to run.
+#include <cuda_fp16.h>
+
+#include "k_epilogue.cuh"
+#include "ta_core.hpp"
+
+namespace ta {
+
+constexpr int FFMA_BK = 16;
+
+template <int BM, int BN, int TM, int TN, bool B_F16, bool SPLITK>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_ffma_kernel(GemmParams p, float *__restrict__ scratch) {
+  constexpr int NT = (BM / TM) * (BN / TN);
+  constexpr int TX = BN / TN;
+  static_assert(TN % 4 == 0 && TM % 4 == 0, "micro tile is built from float4 strips");
+  __shared__ __align__(16) float As[FFMA_BK][BM + 4];
+  __shared__ __align__(16) float Bs[FFMA_BK][BN + 4];
+
+  const int tid = threadIdx.x;
+  const int tx = tid % TX, ty = tid / TX;
+  const uint32_t block_col = blockIdx.x, block_row = blockIdx.y;
+  uint32_t batch = blockIdx.z, split = 0;
+  uint32_t k_lo = 0, k_hi = p.k;
+  if (SPLITK) {
+    split = blockIdx.z % p.splits;
+    batch = blockIdx.z / p.splits;
+    const uint32_t per = p.k / p.splits, rem = p.k % p.splits;
+    k_lo = split * per + min(split, rem);
+    k_hi = k_lo + per + (split < rem ? 1u : 0u);
+  }
+
+  const float *__restrict__ A = (const float *)p.a + (size_t)batch * p.stride_a;
+  const size_t b_off = (size_t)batch * p.stride_b;
+  const float *__restrict__ Bf = (const float *)p.b + b_off;
+  const __half *__restrict__ Bh = (const __half *)p.b + b_off;
+
+  const uint32_t row0 = block_row * BM, col0 = block_col * BN;
+
+  // Column strips of 4: strip s covers cols (s * TX + tx) * 4 .. +3, so a warp's
+  // float4 reads of Bs are contiguous (no bank conflicts).
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+  const bool a_vec = (p.k % 4 == 0) && ((p.stride_a % 4) == 0) && (k_lo % 4 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0);
+  const bool b_vec = !B_F16 && (p.n % 4 == 0) && ((p.stride_b % 4) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.b) & 15) == 0);
+
+  for (uint32_t k0 = k_lo; k0 < k_hi; k0 += FFMA_BK) {
+    // ---- stage A tile (BM x BK), transposed into As[kk][row]
+    for (int idx = tid; idx < BM * (FFMA_BK / 4); idx += NT) {
+      const int r = idx / (FFMA_BK / 4), kq = (idx % (FFMA_BK / 4)) * 4;
+      const uint32_t gr = row0 + r, gk = k0 + kq;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (gr < p.m) {
+        const float *src = A + (size_t)gr * p.k + gk;
+        if (a_vec && gk + 4 <= k_hi) {
+          const float4 t = *reinterpret_cast<const float4 *>(src);
+          v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (gk + q < k_hi) v[q] = src[q];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) As[kq + q][r] = v[q];
+    }
+    // ---- stage B tile (BK x BN)
+    for (int idx = tid; idx < FFMA_BK * (BN / 4); idx += NT) {
+      const int kk = idx / (BN / 4), cq = (idx % (BN / 4)) * 4;
+      const uint32_t gk = k0 + kk, gc = col0 + cq;
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (gk < k_hi) {
+        const size_t off = (size_t)gk * p.n + gc;
+        if (B_F16) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (gc + q < p.n) v[q] = __half2float(Bh[off + q]);
+        } else if (b_vec && gc + 4 <= p.n) {
+          const float4 t = *reinterpret_cast<const float4 *>(Bf + off);
+          v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (gc + q < p.n) v[q] = Bf[off + q];
+        }
+      }
+      *reinterpret_cast<float4 *>(&Bs[kk][cq]) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int kk = 0; kk < FFMA_BK; ++kk) {
+      float a_reg[TM], b_reg[TN];
+#pragma unroll
+      for (int i = 0; i < TM; i += 4) {
+        const float4 t = *reinterpret_cast<const float4 *>(&As[kk][ty * TM + i]);
+        a_reg[i] = t.x; a_reg[i + 1] = t.y; a_reg[i + 2] = t.z; a_reg[i + 3] = t.w;
+      }
+#pragma unroll
+      for (int s = 0; s < TN / 4; ++s) {
+        const float4 t = *reinterpret_cast<const float4 *>(&Bs[kk][(s * TX + tx) * 4]);
+        b_reg[s * 4] = t.x; b_reg[s * 4 + 1] = t.y; b_reg[s * 4 + 2] = t.z; b_reg[s * 4 + 3] = t.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a_reg[i], b_reg[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+  // ---- store
+  const size_t mn = (size_t)p.m * p.n;
+  float *__restrict__ out;
+  if (SPLITK) out = scratch + ((size_t)batch * p.splits + split) * mn;
+  else out = p.c + (size_t)batch * p.stride_c;
+  const float *__restrict__ D = p.d ? p.d + (size_t)batch * p.stride_c : nullptr;
+  const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
+  const bool alpha_is_one = p.alpha == 1.0f;
+
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const uint32_t gr = row0 + ty * TM + i;
+    if (gr >= p.m) continue;
+#pragma unroll
+    for (int s = 0; s < TN / 4; ++s) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t gc = col0 + (s * TX + tx) * 4 + q;
+        if (gc >= p.n) continue;
+        const size_t idx = (size_t)gr * p.n + gc;
+        float v = acc[i][s * 4 + q];
+        if (!alpha_is_one) v = p.alpha * v;
+        if (!SPLITK) {
+          if (p.accumulate) v += out[idx];
+          v = epi_apply(v, bias != nullptr, bias ? bias[gc] : 0.0f, p.act, p.binary,
+                        D ? D[idx] : 0.0f, p.beta);
+        }
+        out[idx] = v;
+      }
+    }
+  }
+}
+
+template <int BM, int BN, int TM, int TN, bool SPLITK>
+static void launch_ffma_t(const GemmParams &p, float *scratch, cudaStream_t stream) {
+  dim3 grid((p.n + BN - 1) / BN, (p.m + BM - 1) / BM, p.batch * (SPLITK ? p.splits : 1u));
+  dim3 block((BM / TM) * (BN / TN));
+  if (grid.y > 65535 || grid.z > 65535) fail("GEMM grid exceeds launch limits (M tiles %u, batch %u)", grid.y, grid.z);
+  if (p.b_f16) gemm_ffma_kernel<BM, BN, TM, TN, true, SPLITK><<<grid, block, 0, stream>>>(p, scratch);
+  else gemm_ffma_kernel<BM, BN, TM, TN, false, SPLITK><<<grid, block, 0, stream>>>(p, scratch);
+  TA_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream) {
+  if (tile >= 128) launch_ffma_t<128, 128, 8, 8, false>(p, nullptr, stream);
+  else launch_ffma_t<64, 64, 4, 4, false>(p, nullptr, stream);
+}
+
+void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream) {
+  if (tile >= 128) launch_ffma_t<128, 128, 8, 8, true>(p, scratch, stream);
+  else launch_ffma_t<64, 64, 4, 4, true>(p, scratch, stream);
+}
+
+// One thread per 4 consecutive outputs; planes added in split order starting
+// from 0.0f (shaders/matmul_f32_splitk2_reduce.comp:44-75).
+__global__ void splitk2_reduce_kernel(const float *__restrict__ scratch, float *__restrict__ c,
+                                      uint64_t total, uint64_t mn, uint32_t splits) {
+  const uint64_t base = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (base >= total) return;
+  if ((mn & 3) == 0 && base + 4 <= total) {
+    const uint64_t b = base / mn, e = base % mn;
+    const float *src = scratch + b * splits * mn + e;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4 *>(src + (uint64_t)s * mn);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4 *>(c + base) = acc;
+  } else {
+    for (uint32_t lane = 0; lane < 4; ++lane) {
+      const uint64_t i = base + lane;
+      if (i >= total) break;
+      const uint64_t b = i / mn, e = i % mn;
+      const float *src = scratch + b * splits * mn + e;
+      float acc = 0.0f;
+      for (uint32_t s = 0; s < splits; ++s) acc += src[(uint64_t)s * mn];
+      c[i] = acc;
+    }
+  }
+}
+
+void launch_splitk2_reduce(const float *scratch, float *c, uint64_t total, uint64_t mn,
+                           uint32_t splits, cudaStream_t stream) {
+  const uint64_t threads = (total + 3) / 4;
+  const uint32_t blocks = (uint32_t)((threads + 255) / 256);
+  splitk2_reduce_kernel<<<blocks, 256, 0, stream>>>(scratch, c, total, mn, splits);
+  TA_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+}  // namespace ta

@@ -1,0 +1,440 @@
+// FP32 GEMM on the 5th-generation tensor cores: TMA-fed, tcgen05.mma kind::tf32
+// with a 3-pass split (3xTF32), f32 accumulators in tensor memory, fused
+// epilogue on the TMEM -> register drain.  Persistent: one CTA per SM walks a
+// static tile schedule.
+//
+// What it computes is the reference's default FP32 GEMM
+// (shaders/matmul_bda_v4_kernel.glsl:225-452 with the epilogue of
+// shaders/matmul_epilogue_common.glsl:14-82):
+//     C[b,i,j] = epi(alpha * sum_k A[b,i,k] * B[b,k,j] (+ C[b,i,j]))
+// A [B,M,K], B [K,N] or [B,K,N], C/D [B,M,N] row-major f32, bias [N] or [B,N].
+//
+// Split: x = hi + lo with hi = rna_tf32(x), lo = rna_tf32(x - hi) (x - hi is
+// exact in f32).  Per K step the tensor core adds  a_lo*b_hi + a_hi*b_lo +
+// a_hi*b_hi  into one f32 accumulator; the dropped a_lo*b_lo term is 2^-22
+// relative.  The split is elementwise, so the converter warps rewrite the TMA
+// tile in place (hi) and into a twin buffer (lo) at identical offsets: the
+// shared-memory swizzle never has to be decoded.
+//
+// Warp roles (320 threads): warps 0-3 drain TMEM and run the epilogue (warp w
+// owns TMEM lanes 32w..32w+31 = tile rows), warp 4 issues TMA, warp 5 owns the
+// TMEM allocation and issues the MMAs, warps 6-9 split tiles into hi/lo.
+// Every mbarrier wait is bounded (about two seconds); on a timeout the CTA
+// raises a flag, all roles leave their loops, and the host reports an error.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "k_epilogue.cuh"
+#include "ta_core.hpp"
+
+namespace ta {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 16;                      // floats per stage along K (64-byte rows of A)
+constexpr int NUM_THREADS = 320;
+constexpr uint32_t WAIT_LIMIT_NS = 2000000000u;
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 4;             // 8 KiB
+  static constexpr int B_BYTES = BK * BN * 4;             // 16 KiB at BN = 256
+  static constexpr int HALF_BYTES = A_BYTES + B_BYTES;    // hi (raw) region, then lo region
+  static constexpr int STAGE_BYTES = 2 * HALF_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
+  static constexpr int TMEM_COLS = 512;                   // two accumulator buffers at BN = 256
+  static constexpr int ACC_STRIDE = (BN == 256) ? 256 : 128;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the wait gave up (flag raised by this or
+// another role); callers then leave their loops.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0) {
+      if (*abort) return false;
+      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
+  uint32_t *r = reinterpret_cast<uint32_t *>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t rna_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+
+// Shared-memory matrix descriptor (64-bit): start address, leading / stride
+// byte offsets (all >> 4), descriptor version 1, swizzle mode in the top bits.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type) {
+  const uint32_t lo = ((addr >> 4) & 0x3fffu) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+  const uint32_t hi = ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (layout_type << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_SW64 = 4;
+
+// ---------------------------------------------------------------- kernel
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
+                   const __grid_constant__ CUtensorMap map_b, uint32_t *__restrict__ status) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  // barrier map (8 bytes each)
+  auto full_raw = [&](int s) { return bar_base + 8u * s; };
+  auto full_cvt = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto empty = [&](int s) { return bar_base + 8u * (2 * C::STAGES + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (3 * C::STAGES + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (3 * C::STAGES + 2 + b); };
+  volatile uint32_t *tmem_slot =
+      reinterpret_cast<volatile uint32_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (3 * C::STAGES + 4));
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_raw(s), 1);
+      mbar_init(full_cvt(s), 128);
+      mbar_init(empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 128);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 5) tmem_alloc(smem_u32((const void *)tmem_slot), C::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
+  const uint32_t tiles_per_batch = tiles_m * tiles_n;
+  const uint32_t num_tiles = tiles_per_batch * p.batch;
+  const uint32_t k_blocks = (p.k + BK - 1) / BK;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      const int m0 = (int)(rem / tiles_n) * BM, n0 = (int)(rem % tiles_n) * BN;
+      const int za = p.stride_a ? (int)batch : 0, zb = p.stride_b ? (int)batch : 0;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+          mbar_arrive_expect_tx(full_raw(stage), C::HALF_BYTES);
+          tma_load_3d(dst, &map_a, full_raw(stage), (int)(kb * BK), m0, za);
+#pragma unroll
+          for (int nb = 0; nb < BN / 32; ++nb)
+            tma_load_3d(dst + C::A_BYTES + nb * (BK * 128), &map_b, full_raw(stage), n0 + nb * 32,
+                        (int)(kb * BK), zb);
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    uint32_t stage = 0, phase = 0, acc_it = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+      ok = mbar_wait(acc_empty(buf), acc_phase ^ 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * C::ACC_STRIDE;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        ok = mbar_wait(full_cvt(stage), phase, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_hi = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t b_hi = a_hi + C::A_BYTES;
+          const uint32_t a_lo = a_hi + C::HALF_BYTES, b_lo = b_hi + C::HALF_BYTES;
+#pragma unroll
+          for (int j = 0; j < BK / 8; ++j) {
+            const uint64_t da_hi = make_desc(a_hi + j * 32, 16, 512, LAYOUT_SW64);
+            const uint64_t da_lo = make_desc(a_lo + j * 32, 16, 512, LAYOUT_SW64);
+            const uint64_t db_hi = make_desc(b_hi + j * 1024, BK * 128, 1024, LAYOUT_SW128);
+            const uint64_t db_lo = make_desc(b_lo + j * 1024, BK * 128, 1024, LAYOUT_SW128);
+            mma_tf32(d_tmem, da_lo, db_hi, idesc, (kb | (uint32_t)j) != 0u);
+            mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+            mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+          }
+          tc_commit(empty(stage));                       // stage reusable once these MMAs retire
+          if (kb + 1 == k_blocks) tc_commit(acc_full(buf));
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ hi/lo converters
+    const int t = threadIdx.x - 6 * 32;  // 0..127
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        ok = mbar_wait(full_raw(stage), phase, abort_flag);
+        if (!ok) break;
+        float4 *hi = reinterpret_cast<float4 *>(smem_gen + stage * C::STAGE_BYTES);
+        float4 *lo = reinterpret_cast<float4 *>(smem_gen + stage * C::STAGE_BYTES + C::HALF_BYTES);
+#pragma unroll 4
+        for (int i = t; i < C::HALF_BYTES / 16; i += 128) {
+          const float4 v = hi[i];
+          uint4 h, l;
+          h.x = rna_tf32(v.x); h.y = rna_tf32(v.y); h.z = rna_tf32(v.z); h.w = rna_tf32(v.w);
+          l.x = rna_tf32(v.x - __uint_as_float(h.x));
+          l.y = rna_tf32(v.y - __uint_as_float(h.y));
+          l.z = rna_tf32(v.z - __uint_as_float(h.z));
+          l.w = rna_tf32(v.w - __uint_as_float(h.w));
+          *reinterpret_cast<uint4 *>(hi + i) = h;
+          *reinterpret_cast<uint4 *>(lo + i) = l;
+        }
+        // generic-proxy writes -> visible to the tensor core's async-proxy reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(full_cvt(stage));
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 0-3)
+    uint32_t acc_it = 0;
+    bool ok = true;
+    const bool alpha_is_one = p.alpha == 1.0f;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      const uint32_t m0 = (rem / tiles_n) * BM, n0 = (rem % tiles_n) * BN;
+      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+      ok = mbar_wait(acc_full(buf), acc_phase, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t row = m0 + warp * 32 + lane;
+      const bool row_ok = row < p.m;
+      const size_t row_off = (size_t)batch * p.stride_c + (size_t)row * p.n;
+      float *__restrict__ crow = p.c + row_off;
+      const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
+      const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
+      const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(taddr + c0, v);
+        const uint32_t col0 = n0 + c0;
+        if (row_ok && col0 < p.n) {
+#pragma unroll
+          for (int q = 0; q < 32; q += 4) {
+            const uint32_t col = col0 + q;
+            if (col < p.n) {  // N % 4 == 0: a float4 is either fully in or fully out
+              float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+              if (p.accumulate) {
+                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+              }
+              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+              o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
+              o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
+              o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
+              o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
+              *reinterpret_cast<float4 *>(crow + col) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty(buf));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give copies and MMAs still in flight a bounded time to land before the
+    // shared and tensor memory they target is released.
+    for (int i = 0; i < 64; ++i) __nanosleep(100000);
+    if (threadIdx.x == 0) atomicOr(status, 1u);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+void encode_map(const Context &ctx, CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1,
+                uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0,
+                uint32_t box1, CUtensorMapSwizzle swz) {
+  auto encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ctx.encode_tiled);
+  if (!encode) fail("cuTensorMapEncodeTiled is unavailable in this CUDA driver");
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  const cuuint32_t box[3] = {box0, box1, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base), dims,
+                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) fail("cuTensorMapEncodeTiled failed with CUresult %d", (int)rc);
+}
+
+template <int BN>
+void launch_t(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx.device & 63]) {
+    TA_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::SMEM_BYTES));
+    attr_set[ctx.device & 63] = true;
+  }
+  CUtensorMap map_a, map_b;
+  const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
+  // A [ba, M, K]: dims innermost first {K, M, ba}; 64-byte rows in shared memory.
+  encode_map(ctx, &map_a, p.a, p.k, p.m, ba, (uint64_t)p.k * 4,
+             p.stride_a ? (uint64_t)p.stride_a * 4 : (uint64_t)p.m * p.k * 4, BK, BM,
+             CU_TENSOR_MAP_SWIZZLE_64B);
+  // B [bb, K, N]: dims {N, K, bb}; boxes of 32 columns (128 bytes) x BK rows.
+  encode_map(ctx, &map_b, p.b, p.n, p.k, bb, (uint64_t)p.n * 4,
+             p.stride_b ? (uint64_t)p.stride_b * 4 : (uint64_t)p.k * p.n * 4, 32, BK,
+             CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
+  const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
+  gemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);
+  TA_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+}  // namespace
+
+// TMA needs 16-byte global strides and bases: K % 4 == 0, N % 4 == 0 (that
+// also makes every batch stride a multiple of 16 bytes), f32 operands.
+bool gemm_tf32x3_eligible(const GemmParams &p) {
+  if (p.b_f16) return false;
+  if (p.k % 4 || p.n % 4) return false;
+  if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.b) |
+       reinterpret_cast<uintptr_t>(p.c)) & 15)
+    return false;
+  if (p.d && (reinterpret_cast<uintptr_t>(p.d) & 15)) return false;
+  if (p.bias && (reinterpret_cast<uintptr_t>(p.bias) & 15)) return false;
+  if ((p.stride_a % 4) || (p.stride_b % 4) || (p.stride_c % 4) || (p.bias_stride % 4)) return false;
+  return true;
+}
+
+void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
+                        cudaStream_t stream) {
+  if (!gemm_tf32x3_eligible(p)) fail("tf32x3 GEMM needs f32 operands with K and N multiples of 4");
+  if (tile_n >= 256) launch_t<256>(ctx, p, status, stream);
+  else launch_t<128>(ctx, p, status, stream);
+}
+
+}  // namespace ta

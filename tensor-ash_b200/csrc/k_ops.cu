@@ -1,0 +1,195 @@
+// Non-GEMM model ops behind ta_softmax_rows / ta_rms_norm / ta_layer_norm /
+// ta_rope / ta_copy_strided.  Semantics follow the reference shaders:
+//   masked row softmax   shaders/op_softmax_f32_row.comp:30-91 (masked columns store exactly 0)
+//   RMS / LayerNorm      shaders/op_rmsnorm_body.glsl:60-168 (one workgroup per row)
+//   interleaved RoPE     shaders/op_rope_body.glsl:100-134 (r0 = fma(x0,c,-x1*s), r1 = fma(x0,s,x1*c))
+//   3-D strided copy     shaders/op_copy_strided_body.glsl:40-98
+// All are bandwidth-trivial next to the GEMMs; one block per row, fixed-order
+// tree reductions so results do not depend on scheduling.
+#include "ta_core.hpp"
+
+namespace ta {
+
+namespace {
+
+constexpr int ROW_THREADS = 256;
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float *sh) {
+  // fixed-order: warp shuffle tree, then the first warp folds the warp results
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, other) : v + other;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float r = (lane < ROW_THREADS / 32) ? sh[lane] : (is_max ? -INFINITY : 0.0f);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, r, o);
+    r = is_max ? fmaxf(r, other) : r + other;
+  }
+  return r;
+}
+
+__global__ void __launch_bounds__(ROW_THREADS)
+softmax_rows_kernel(const float *__restrict__ in, float *__restrict__ out, uint32_t cols,
+                    float scale, uint32_t mask_kind, uint32_t valid_or_prefix,
+                    uint32_t rows_per_group) {
+  __shared__ float sh[32];
+  const uint32_t row = blockIdx.x;
+  uint32_t valid = cols;
+  if (mask_kind == 1) valid = min(valid_or_prefix, cols);
+  else if (mask_kind == 2) {
+    const uint64_t v = (uint64_t)valid_or_prefix + (rows_per_group ? row % rows_per_group : 0u) + 1u;
+    valid = (uint32_t)min((uint64_t)cols, v);
+  }
+  const float *x = in + (size_t)row * cols;
+  float *y = out + (size_t)row * cols;
+  float mx = -INFINITY;
+  for (uint32_t j = threadIdx.x; j < valid; j += ROW_THREADS) mx = fmaxf(mx, x[j] * scale);
+  mx = block_reduce(mx, true, sh);
+  float sum = 0.0f;
+  for (uint32_t j = threadIdx.x; j < valid; j += ROW_THREADS) sum += expf(x[j] * scale - mx);
+  sum = block_reduce(sum, false, sh);
+  const float inv = 1.0f / sum;
+  for (uint32_t j = threadIdx.x; j < cols; j += ROW_THREADS)
+    y[j] = j < valid ? expf(x[j] * scale - mx) * inv : 0.0f;
+}
+
+__global__ void __launch_bounds__(ROW_THREADS)
+norm_rows_kernel(const float *__restrict__ in, const float *__restrict__ w,
+                 const float *__restrict__ b, float *__restrict__ out, uint32_t cols, float eps,
+                 bool layer_norm) {
+  __shared__ float sh[32];
+  const float *x = in + (size_t)blockIdx.x * cols;
+  float *y = out + (size_t)blockIdx.x * cols;
+  float mean = 0.0f;
+  if (layer_norm) {
+    float s = 0.0f;
+    for (uint32_t j = threadIdx.x; j < cols; j += ROW_THREADS) s += x[j];
+    mean = block_reduce(s, false, sh) / (float)cols;
+  }
+  float ss = 0.0f;
+  for (uint32_t j = threadIdx.x; j < cols; j += ROW_THREADS) {
+    const float d = x[j] - mean;
+    ss += d * d;
+  }
+  ss = block_reduce(ss, false, sh);
+  const float inv = rsqrtf(ss / (float)cols + eps);
+  // the row may be normalised in place: every read of x[j] happens before the write of y[j]
+  for (uint32_t j = threadIdx.x; j < cols; j += ROW_THREADS) {
+    const float v = (x[j] - mean) * inv * w[j];
+    y[j] = layer_norm ? v + b[j] : v;
+  }
+}
+
+__global__ void rope_kernel(const float *__restrict__ in, const float *__restrict__ table,
+                            float *__restrict__ out, uint32_t tokens, uint32_t heads,
+                            uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base) {
+  // one thread per pair of lanes (pass-through lanes beyond rot_dim are copied as pairs too)
+  const uint32_t half_dim = head_dim / 2;
+  const uint64_t total = (uint64_t)tokens * heads * half_dim;
+  const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const uint32_t i = (uint32_t)(idx % half_dim);
+  const uint64_t vec = idx / half_dim;
+  const uint32_t t = (uint32_t)(vec / heads);
+  const size_t base = (size_t)vec * head_dim + 2 * i;
+  const float x0 = in[base], x1 = in[base + 1];
+  if (2 * i < rot_dim) {
+    const float *cs = table + ((size_t)(pos_base + t) * (rot_dim / 2) + i) * 2;
+    const float c = cs[0], s = cs[1];
+    out[base] = fmaf(x0, c, -x1 * s);
+    out[base + 1] = fmaf(x0, s, x1 * c);
+  } else {
+    out[base] = x0;
+    out[base + 1] = x1;
+  }
+}
+
+__global__ void rope_tail_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                 uint64_t vecs, uint32_t head_dim) {
+  // odd head_dim: the last lane has no partner and passes through
+  const uint64_t v = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (v < vecs) out[v * head_dim + head_dim - 1] = in[v * head_dim + head_dim - 1];
+}
+
+struct CopyArgs {
+  uint32_t extent[3], src_off, src_strides[3], dst_off, dst_strides[3];
+};
+
+__global__ void copy_strided_kernel(const float *__restrict__ src, float *__restrict__ dst,
+                                    CopyArgs a) {
+  const uint64_t total = (uint64_t)a.extent[0] * a.extent[1] * a.extent[2];
+  const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const uint32_t x = (uint32_t)(idx % a.extent[0]);
+  const uint32_t y = (uint32_t)((idx / a.extent[0]) % a.extent[1]);
+  const uint32_t z = (uint32_t)(idx / ((uint64_t)a.extent[0] * a.extent[1]));
+  const size_t s = (size_t)a.src_off + (size_t)x * a.src_strides[0] + (size_t)y * a.src_strides[1] +
+                   (size_t)z * a.src_strides[2];
+  const size_t d = (size_t)a.dst_off + (size_t)x * a.dst_strides[0] + (size_t)y * a.dst_strides[1] +
+                   (size_t)z * a.dst_strides[2];
+  dst[d] = src[s];
+}
+
+inline void launched() {
+  TA_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+}  // namespace
+
+void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t cols, float scale,
+                         uint32_t mask_kind, uint32_t valid_or_prefix, uint32_t rows_per_group,
+                         cudaStream_t stream) {
+  softmax_rows_kernel<<<rows, ROW_THREADS, 0, stream>>>(in, out, cols, scale, mask_kind,
+                                                        valid_or_prefix, rows_per_group);
+  launched();
+}
+
+void launch_rms_norm(const float *in, const float *w, float *out, uint32_t rows, uint32_t cols,
+                     float eps, cudaStream_t stream) {
+  norm_rows_kernel<<<rows, ROW_THREADS, 0, stream>>>(in, w, nullptr, out, cols, eps, false);
+  launched();
+}
+
+void launch_layer_norm(const float *in, const float *w, const float *b, float *out, uint32_t rows,
+                       uint32_t cols, float eps, cudaStream_t stream) {
+  norm_rows_kernel<<<rows, ROW_THREADS, 0, stream>>>(in, w, b, out, cols, eps, true);
+  launched();
+}
+
+void launch_rope(const float *in, const float *table, float *out, uint32_t tokens, uint32_t heads,
+                 uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base, cudaStream_t stream) {
+  const uint64_t total = (uint64_t)tokens * heads * (head_dim / 2);
+  rope_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, stream>>>(in, table, out, tokens, heads,
+                                                                   head_dim, rot_dim, pos_base);
+  launched();
+  if (head_dim & 1u) {
+    const uint64_t vecs = (uint64_t)tokens * heads;
+    rope_tail_kernel<<<(uint32_t)((vecs + 255) / 256), 256, 0, stream>>>(in, out, vecs, head_dim);
+    launched();
+  }
+}
+
+void launch_copy_strided(const float *src, float *dst, const uint32_t extent[3], uint32_t src_off,
+                         const uint32_t src_strides[3], uint32_t dst_off,
+                         const uint32_t dst_strides[3], cudaStream_t stream) {
+  CopyArgs a;
+  for (int i = 0; i < 3; ++i) {
+    a.extent[i] = extent[i];
+    a.src_strides[i] = src_strides[i];
+    a.dst_strides[i] = dst_strides[i];
+  }
+  a.src_off = src_off;
+  a.dst_off = dst_off;
+  const uint64_t total = (uint64_t)extent[0] * extent[1] * extent[2];
+  copy_strided_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, stream>>>(src, dst, a);
+  launched();
+}
+
+}  // namespace ta

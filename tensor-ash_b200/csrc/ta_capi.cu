@@ -1,0 +1,654 @@
+// extern "C" boundary: the symbols of include/tensor_ash.h.
+//
+// Conventions follow the reference's Rust cdylib (capi/src/error.rs:8-121,
+// capi/src/handles.rs:6-60): the per-thread error string is cleared on entry,
+// status functions return 0 / -1, creators return pointer / NULL, any C++
+// exception is caught here (the analogue of the reference's panic barrier),
+// destroying NULL is a no-op, and a tensor from another context is rejected
+// with "<operation>: <operand> belongs to a different ... context".
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <string>
+
+#pragma GCC visibility push(default)
+#include "../../include/tensor_ash.h"
+#pragma GCC visibility pop
+#include "ta_core.hpp"
+
+using namespace ta;
+
+struct ta_context {
+  std::shared_ptr<Context> ctx;
+};
+struct ta_executor {
+  std::shared_ptr<Context> ctx;
+  std::unique_ptr<Executor> exec;
+};
+struct ta_tensor {
+  Tensor tensor;
+};
+struct ta_prepared {
+  std::unique_ptr<PreparedOps> prepared;
+  std::shared_ptr<Context> ctx;
+};
+struct ta_pos_cell {
+  std::shared_ptr<Context> ctx;
+  uint32_t *host = nullptr;  // pinned, mapped
+};
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int status_call(const std::function<void()> &f) {
+  g_last_error.clear();
+  try {
+    f();
+    return 0;
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+  } catch (...) {
+    g_last_error = "panic crossed tensor-ash C ABI boundary";
+  }
+  return -1;
+}
+
+template <class T>
+T *create_call(const std::function<T *()> &f) {
+  g_last_error.clear();
+  try {
+    return f();
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+  } catch (...) {
+    g_last_error = "panic crossed tensor-ash C ABI boundary";
+  }
+  return nullptr;
+}
+
+template <class T>
+const T &checked_ref(const T *p, const char *msg) {
+  if (!p) fail("%s", msg);
+  return *p;
+}
+
+const Tensor &checked_tensor(const ta_executor &exec, const ta_tensor *t, const char *operation,
+                             const char *operand) {
+  if (!t) fail("%s: %s is null", operation, operand);
+  if (t->tensor.ctx().get() != exec.ctx.get())
+    fail("%s: %s belongs to a different Vulkan context", operation, operand);
+  return t->tensor;
+}
+
+void write_stats(ta_run_stats *out, const RunStats &st) {
+  if (!out) return;
+  out->has_gpu_time = st.gpu_time_ns ? 1u : 0u;
+  out->gpu_time_ns = st.gpu_time_ns.value_or(0);
+  out->n_calls = st.n_calls;
+  out->total_flops = st.total_flops;
+  const auto tf = st.tflops();
+  out->tflops = tf ? *tf : std::nan("");
+}
+
+MatmulCall checked_call(const ta_executor &exec, const ta_matmul_call &raw, const char *operation) {
+  MatmulCall c;
+  c.a = &checked_tensor(exec, raw.a, operation, "a");
+  c.b = &checked_tensor(exec, raw.b, operation, "b");
+  c.c = &checked_tensor(exec, raw.c, operation, "c");
+  c.alpha = raw.alpha;
+  c.accumulate = raw.accumulate != 0;
+  return c;
+}
+
+// (capi/src/api/ops.rs:14-69)
+MatmulOp checked_op(const ta_executor &exec, const ta_matmul_op &raw, const char *operation) {
+  MatmulOp op;
+  op.call = checked_call(exec, raw.call, operation);
+  const ta_epilogue &ep = raw.epilogue;
+  if (ep.bias) op.epilogue.bias = &checked_tensor(exec, ep.bias, operation, "epilogue.bias");
+  if (ep.activation > 3)
+    fail("%s: epilogue.activation %u is invalid (0=none 1=relu 2=silu 3=gelu)", operation,
+         ep.activation);
+  op.epilogue.activation = (Activation)ep.activation;
+  switch (ep.binary_kind) {
+    case 0:
+      if (ep.d) fail("%s: epilogue.d is set but binary_kind is 0 (none)", operation);
+      break;
+    case 1:
+      op.epilogue.binary = BinaryKind::AddScaled;
+      op.epilogue.d = &checked_tensor(exec, ep.d, operation, "epilogue.d");
+      op.epilogue.beta = ep.beta;
+      break;
+    case 2:
+      op.epilogue.binary = BinaryKind::Mul;
+      op.epilogue.d = &checked_tensor(exec, ep.d, operation, "epilogue.d");
+      break;
+    default:
+      fail("%s: epilogue.binary_kind %u is invalid (0=none 1=add_scaled 2=mul)", operation,
+           ep.binary_kind);
+  }
+  return op;
+}
+
+std::vector<MatmulOp> checked_ops(const ta_executor &exec, const ta_matmul_op *ops, size_t n,
+                                  const char *operation) {
+  if (n && !ops) fail("%s: ops is null", operation);
+  std::vector<MatmulOp> out;
+  out.reserve(n);
+  for (size_t i = 0; i < n; ++i)
+    out.push_back(checked_op(exec, ops[i], strf("%s: op %zu", operation, i).c_str()));
+  return out;
+}
+
+ta_executor *executor_create(const ta_context *ctx, size_t n_slots, uint32_t max_calls,
+                             const char *selection, bool tune, const char *operation) {
+  const ta_context &c = checked_ref(ctx, strf("%s: ctx is null", operation).c_str());
+  const int sel = kernel_selection_parse(selection ? selection : "auto");
+  ExecutorConfig cfg;
+  cfg.n_slots = n_slots;
+  cfg.max_calls_per_submit = max_calls;
+  cfg.tune = tune;
+  auto *h = new ta_executor;
+  h->ctx = c.ctx;
+  try {
+    h->exec = std::make_unique<Executor>(c.ctx, sel, cfg);
+  } catch (...) {
+    delete h;
+    throw;
+  }
+  return h;
+}
+
+ta_tensor *tensor_create(const std::shared_ptr<Context> &ctx, const uint32_t *shape, size_t rank,
+                         DType dtype, const char *operation) {
+  if (rank && !shape) fail("%s: shape is null", operation);
+  auto *h = new ta_tensor;
+  try {
+    h->tensor = Tensor::uninit_device(ctx, shape, rank, dtype);
+  } catch (...) {
+    delete h;
+    throw;
+  }
+  return h;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+const char *ta_version(void) { return "2.0.0"; }
+const char *ta_last_error(void) { return g_last_error.c_str(); }
+
+ta_context *ta_context_create(uint32_t enable_validation, const char *device_preference) {
+  return create_call<ta_context>([&]() {
+    std::string pref = device_preference ? device_preference : "";
+    if (!device_preference) {
+      if (const char *env = getenv("ML_DEVICE")) pref = env;  // src/context/mod.rs:95-103
+    }
+    auto *h = new ta_context;
+    try {
+      h->ctx = Context::create(enable_validation != 0, pref);
+    } catch (...) {
+      delete h;
+      throw;
+    }
+    return h;
+  });
+}
+
+void ta_context_destroy(ta_context *ctx) {
+  g_last_error.clear();
+  delete ctx;
+}
+
+uint32_t ta_context_supports_f16(const ta_context *ctx) { return ctx ? 1u : 0u; }
+uint32_t ta_context_supports_bda(const ta_context *ctx) { return ctx ? 1u : 0u; }
+
+ta_executor *ta_executor_create(const ta_context *ctx, size_t n_slots, uint32_t max_calls_per_submit,
+                                const char *kernel_selection) {
+  return create_call<ta_executor>([&]() {
+    const char *sel = kernel_selection;
+    if (!sel) sel = getenv("ML_KERNEL");
+    return executor_create(ctx, n_slots, max_calls_per_submit, sel, false, "ta_executor_create");
+  });
+}
+
+ta_executor *ta_executor_create_v2(const ta_context *ctx, size_t n_slots,
+                                   uint32_t max_calls_per_submit, const char *kernel_selection,
+                                   uint32_t tune) {
+  return create_call<ta_executor>([&]() {
+    const char *sel = kernel_selection;
+    if (!sel) sel = getenv("ML_KERNEL");
+    return executor_create(ctx, n_slots, max_calls_per_submit, sel, tune != 0,
+                           "ta_executor_create_v2");
+  });
+}
+
+void ta_executor_destroy(ta_executor *exec) {
+  g_last_error.clear();
+  delete exec;
+}
+
+ta_tensor *ta_tensor_create(const ta_context *ctx, const uint32_t *shape, size_t rank) {
+  return create_call<ta_tensor>([&]() {
+    const ta_context &c = checked_ref(ctx, "ta_tensor_create: ctx is null");
+    return tensor_create(c.ctx, shape, rank, DType::F32, "ta_tensor_create");
+  });
+}
+ta_tensor *ta_tensor_create_on_executor(const ta_executor *exec, const uint32_t *shape, size_t rank) {
+  return create_call<ta_tensor>([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_tensor_create_on_executor: exec is null");
+    return tensor_create(e.ctx, shape, rank, DType::F32, "ta_tensor_create_on_executor");
+  });
+}
+ta_tensor *ta_tensor_create_f16(const ta_context *ctx, const uint32_t *shape, size_t rank) {
+  return create_call<ta_tensor>([&]() {
+    const ta_context &c = checked_ref(ctx, "ta_tensor_create_f16: ctx is null");
+    return tensor_create(c.ctx, shape, rank, DType::F16, "ta_tensor_create_f16");
+  });
+}
+ta_tensor *ta_tensor_create_f16_on_executor(const ta_executor *exec, const uint32_t *shape,
+                                            size_t rank) {
+  return create_call<ta_tensor>([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_tensor_create_f16_on_executor: exec is null");
+    return tensor_create(e.ctx, shape, rank, DType::F16, "ta_tensor_create_f16_on_executor");
+  });
+}
+void ta_tensor_destroy(ta_tensor *tensor) {
+  g_last_error.clear();
+  delete tensor;
+}
+uint64_t ta_tensor_len(const ta_tensor *tensor) { return tensor ? tensor->tensor.len() : 0; }
+uint64_t ta_tensor_size_bytes(const ta_tensor *tensor) {
+  return tensor ? tensor->tensor.size_bytes() : 0;
+}
+uint32_t ta_tensor_is_f16(const ta_tensor *tensor) {
+  return tensor && tensor->tensor.dtype == DType::F16 ? 1u : 0u;
+}
+
+int ta_upload(const ta_executor *exec, const ta_tensor *dst, const float *src, size_t len) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_upload: exec is null");
+    const Tensor &d = checked_tensor(e, dst, "ta_upload", "dst");
+    if (len && !src) fail("ta_upload: src is null");
+    e.exec->upload(src, len, d);
+  });
+}
+
+int ta_download(const ta_executor *exec, const ta_tensor *src, float *dst, size_t len) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_download: exec is null");
+    const Tensor &s = checked_tensor(e, src, "ta_download", "src");
+    if (len && !dst) fail("ta_download: dst is null");
+    e.exec->download(s, dst, len);
+  });
+}
+
+int ta_matmul(const ta_executor *exec, const ta_tensor *a, const ta_tensor *b, const ta_tensor *c,
+              float alpha, uint32_t accumulate, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_matmul: exec is null");
+    const ta_matmul_call raw{a, b, c, alpha, accumulate};
+    write_stats(stats, e.exec->run_matmuls({checked_call(e, raw, "ta_matmul")}));
+  });
+}
+
+int ta_matmul_batch(const ta_executor *exec, const ta_matmul_call *calls, size_t n_calls,
+                    ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_matmul_batch: exec is null");
+    if (n_calls && !calls) fail("ta_matmul_batch: calls is null");
+    std::vector<MatmulCall> v;
+    for (size_t i = 0; i < n_calls; ++i)
+      v.push_back(checked_call(e, calls[i], strf("ta_matmul_batch: call %zu", i).c_str()));
+    write_stats(stats, e.exec->run_matmuls(v));
+  });
+}
+
+int ta_run_ops(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_run_ops: exec is null");
+    write_stats(stats, e.exec->run_ops(checked_ops(e, ops, n_ops, "ta_run_ops")));
+  });
+}
+
+int ta_run_op_graph(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops,
+                    ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_run_op_graph: exec is null");
+    write_stats(stats, e.exec->run_op_graph(checked_ops(e, ops, n_ops, "ta_run_op_graph")));
+  });
+}
+
+int ta_softmax_rows(const ta_executor *exec, const ta_tensor *input, const ta_tensor *output,
+                    float scale, uint32_t mask_kind, uint32_t valid_or_prefix,
+                    uint32_t rows_per_group, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_softmax_rows: exec is null");
+    const Tensor &in = checked_tensor(e, input, "ta_softmax_rows", "input");
+    const Tensor &out = checked_tensor(e, output, "ta_softmax_rows", "output");
+    if (mask_kind > 2)
+      fail("ta_softmax_rows: mask_kind %u is invalid (0=full 1=prefix 2=causal)", mask_kind);
+    write_stats(stats, e.exec->softmax_rows(in, out, scale, mask_kind, valid_or_prefix, rows_per_group));
+  });
+}
+
+int ta_rms_norm(const ta_executor *exec, const ta_tensor *input, const ta_tensor *weight,
+                const ta_tensor *output, float eps, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_rms_norm: exec is null");
+    const Tensor &in = checked_tensor(e, input, "ta_rms_norm", "input");
+    const Tensor &w = checked_tensor(e, weight, "ta_rms_norm", "weight");
+    const Tensor &out = checked_tensor(e, output, "ta_rms_norm", "output");
+    write_stats(stats, e.exec->rms_norm(in, w, out, eps));
+  });
+}
+
+int ta_layer_norm(const ta_executor *exec, const ta_tensor *input, const ta_tensor *weight,
+                  const ta_tensor *bias, const ta_tensor *output, float eps, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_layer_norm: exec is null");
+    const Tensor &in = checked_tensor(e, input, "ta_layer_norm", "input");
+    const Tensor &w = checked_tensor(e, weight, "ta_layer_norm", "weight");
+    const Tensor &b = checked_tensor(e, bias, "ta_layer_norm", "bias");
+    const Tensor &out = checked_tensor(e, output, "ta_layer_norm", "output");
+    write_stats(stats, e.exec->layer_norm(in, w, b, out, eps));
+  });
+}
+
+int ta_rope(const ta_executor *exec, const ta_tensor *input, const ta_tensor *table,
+            const ta_tensor *output, const ta_rope_desc *desc, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_rope: exec is null");
+    const Tensor &in = checked_tensor(e, input, "ta_rope", "input");
+    const Tensor &tab = checked_tensor(e, table, "ta_rope", "table");
+    const Tensor &out = checked_tensor(e, output, "ta_rope", "output");
+    const ta_rope_desc &d = checked_ref(desc, "ta_rope: desc is null");
+    write_stats(stats, e.exec->rope(in, tab, out, d.heads, d.head_dim, d.rot_dim, d.pos_base));
+  });
+}
+
+int ta_copy_strided(const ta_executor *exec, const ta_tensor *src, const ta_tensor *dst,
+                    const ta_copy_desc *desc, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_copy_strided: exec is null");
+    const Tensor &s = checked_tensor(e, src, "ta_copy_strided", "src");
+    const Tensor &d = checked_tensor(e, dst, "ta_copy_strided", "dst");
+    const ta_copy_desc &cd = checked_ref(desc, "ta_copy_strided: desc is null");
+    write_stats(stats, e.exec->copy_strided(s, d, cd.extent, cd.src_offset, cd.src_strides,
+                                            cd.dst_offset, cd.dst_strides));
+  });
+}
+
+ta_prepared *ta_prepared_create(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops,
+                                uint32_t as_graph) {
+  return create_call<ta_prepared>([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_prepared_create: exec is null");
+    auto v = checked_ops(e, ops, n_ops, "ta_prepared_create");
+    auto *h = new ta_prepared;
+    h->ctx = e.ctx;
+    try {
+      h->prepared = prepare_ops(*e.exec, v, as_graph != 0);
+    } catch (...) {
+      delete h;
+      throw;
+    }
+    return h;
+  });
+}
+
+int ta_prepared_run(ta_prepared *prepared, ta_run_stats *stats) {
+  return status_call([&]() {
+    if (!prepared) fail("ta_prepared_run: prepared is null");
+    write_stats(stats, prepared->prepared->run());
+  });
+}
+int ta_prepared_submit(ta_prepared *prepared) {
+  return status_call([&]() {
+    if (!prepared) fail("ta_prepared_submit: prepared is null");
+    prepared->prepared->submit();
+  });
+}
+int ta_prepared_wait(ta_prepared *prepared, ta_run_stats *stats) {
+  return status_call([&]() {
+    if (!prepared) fail("ta_prepared_wait: prepared is null");
+    write_stats(stats, prepared->prepared->wait());
+  });
+}
+void ta_prepared_destroy(ta_prepared *prepared) {
+  g_last_error.clear();
+  delete prepared;
+}
+
+int ta_dispatch_info_for(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t n, uint32_t k,
+                         uint32_t b_f16, ta_dispatch_info *out) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_dispatch_info_for: exec is null");
+    if (!out) fail("ta_dispatch_info_for: out is null");
+    if (!batch || !m || !n || !k)
+      fail("matmul dimensions must be non-zero, got B=%u rows=%u cols=%u", batch, m, n);
+    const Route r = e.exec->plan_shape(batch, m, n, k, b_f16 != 0, true);
+    const KernelSpec &spec = KERNEL_SPECS[r.kernel];
+    out->kernel = spec.name;
+    out->tile[0] = spec.tile_m;
+    out->tile[1] = spec.tile_n;
+    out->tile[2] = spec.tile_k;
+    out->has_split_k2 = r.splits > 1;
+    out->split_k2_splits = r.splits > 1 ? r.splits : 0;
+  });
+}
+
+int ta_tune_shape(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_tune_shape: exec is null");
+    if (!batch || !m || !n || !k)
+      fail("matmul dimensions must be non-zero, got B=%u rows=%u cols=%u", batch, m, n);
+    e.exec->tune_shape(batch, m, n, k);
+  });
+}
+
+// ===================================================================== PART 2
+
+int ta_matmul_split_k2(const ta_executor *exec, const ta_matmul_call *calls, size_t n_calls,
+                       uint32_t splits, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_matmul_split_k2: exec is null");
+    if (n_calls && !calls) fail("ta_matmul_split_k2: calls is null");
+    std::vector<MatmulCall> v;
+    for (size_t i = 0; i < n_calls; ++i)
+      v.push_back(checked_call(e, calls[i], strf("ta_matmul_split_k2: call %zu", i).c_str()));
+    write_stats(stats, e.exec->run_matmuls_split_k2(v, splits));
+  });
+}
+
+int ta_run_ops_ex(const ta_executor *exec, const ta_matmul_op_ex *ops, size_t n_ops,
+                  uint32_t as_graph, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_run_ops_ex: exec is null");
+    if (n_ops && !ops) fail("ta_run_ops_ex: ops is null");
+    std::vector<MatmulOp> v;
+    for (size_t i = 0; i < n_ops; ++i) {
+      const std::string label = strf("ta_run_ops_ex: op %zu", i);
+      MatmulOp op = checked_op(e, ops[i].op, label.c_str());
+      op.packed_b = ops[i].packed_b != 0;
+      if (ops[i].normed_weight) {
+        op.normed_weight = &checked_tensor(e, ops[i].normed_weight, label.c_str(), "normed_weight");
+        op.normed_eps = ops[i].normed_eps;
+      }
+      const ta_store_desc &s = ops[i].store;
+      if (s.kind > 3) fail("%s: store.kind %u is invalid (0..3)", label.c_str(), s.kind);
+      op.store.kind = (StoreKind)s.kind;
+      op.store.head_dim = s.head_dim;
+      op.store.pos_base = s.pos_base;
+      op.store.pos_scale = s.pos_scale;
+      op.store.stride_head = s.stride_head;
+      op.store.stride_dim = s.stride_dim;
+      if (s.table) op.store.table = &checked_tensor(e, s.table, label.c_str(), "store.table");
+      if (s.dst) op.store.dst = &checked_tensor(e, s.dst, label.c_str(), "store.dst");
+      v.push_back(op);
+    }
+    write_stats(stats, as_graph ? e.exec->run_op_graph(v) : e.exec->run_ops(v));
+  });
+}
+
+int ta_swiglu_gemv(const ta_executor *exec, const ta_tensor *, const ta_tensor *, const ta_tensor *,
+                   const ta_tensor *, const ta_tensor *, float, ta_run_stats *) {
+  return status_call([&]() {
+    checked_ref(exec, "ta_swiglu_gemv: exec is null");
+    fail("ta_swiglu_gemv: the packed f16-weight GEMV kernels are not built yet");
+  });
+}
+
+int ta_pack_f16w_row_tiles(const float *src, float *dst, size_t k, size_t n, size_t tile_n) {
+  return status_call([&]() {
+    if (!src || !dst) fail("ta_pack_f16w_row_tiles: src/dst is null");
+    pack_f16w_row_tiles(src, dst, k, n, tile_n);
+  });
+}
+uint32_t ta_f16w_row_tile_n(uint32_t k, uint32_t n) { return f16w_row_tile_n(k, n); }
+
+int ta_upload_f16(const ta_executor *exec, const ta_tensor *dst, const uint16_t *src, size_t len) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_upload_f16: exec is null");
+    const Tensor &d = checked_tensor(e, dst, "ta_upload_f16", "dst");
+    if (len && !src) fail("ta_upload_f16: src is null");
+    e.exec->upload_f16(src, len, d);
+  });
+}
+
+ta_tensor *ta_tensor_alias_with_shape(const ta_tensor *tensor, const uint32_t *shape, size_t rank) {
+  return create_call<ta_tensor>([&]() {
+    if (!tensor) fail("ta_tensor_alias_with_shape: tensor is null");
+    if (rank && !shape) fail("ta_tensor_alias_with_shape: shape is null");
+    auto *h = new ta_tensor;
+    try {
+      h->tensor = tensor->tensor.alias_with_shape(shape, rank);
+    } catch (...) {
+      delete h;
+      throw;
+    }
+    return h;
+  });
+}
+
+int ta_flash_attention(const ta_executor *exec, const ta_tensor *, const ta_tensor *,
+                       const ta_tensor *, const ta_tensor *, const ta_flash_desc *, ta_run_stats *) {
+  return status_call([&]() {
+    checked_ref(exec, "ta_flash_attention: exec is null");
+    fail("ta_flash_attention: the flash-attention kernel is not built yet");
+  });
+}
+
+uint32_t ta_attn_decode_num_chunks(uint32_t kv_len) {
+  // clamp(ceil(kv_len / 32), 8, 32)  (src/executor/elementwise/mod.rs:235-237)
+  const uint32_t c = (kv_len + 31) / 32;
+  return c < 8 ? 8 : (c > TA_ATTN_DECODE_MAX_CHUNKS ? TA_ATTN_DECODE_MAX_CHUNKS : c);
+}
+
+int ta_attn_decode(const ta_executor *exec, const ta_tensor *, const ta_tensor *, const ta_tensor *,
+                   const ta_tensor *, const ta_tensor *, const ta_attn_decode_desc *,
+                   ta_run_stats *) {
+  return status_call([&]() {
+    checked_ref(exec, "ta_attn_decode: exec is null");
+    fail("ta_attn_decode: the decode-attention kernels are not built yet");
+  });
+}
+
+ta_pos_cell *ta_pos_cell_create(const ta_context *ctx) {
+  return create_call<ta_pos_cell>([&]() {
+    const ta_context &c = checked_ref(ctx, "ta_pos_cell_create: ctx is null");
+    c.ctx->make_current();
+    auto *h = new ta_pos_cell;
+    h->ctx = c.ctx;
+    const cudaError_t e = cudaHostAlloc((void **)&h->host, sizeof(uint32_t), cudaHostAllocMapped);
+    if (e != cudaSuccess) {
+      delete h;
+      fail("ta_pos_cell_create: pinned allocation failed: %s", cudaGetErrorString(e));
+    }
+    *h->host = 0;
+    return h;
+  });
+}
+void ta_pos_cell_destroy(ta_pos_cell *cell) {
+  g_last_error.clear();
+  if (!cell) return;
+  if (cell->host) {
+    cudaSetDevice(cell->ctx->device);
+    cudaFreeHost(cell->host);
+  }
+  delete cell;
+}
+int ta_pos_cell_set(ta_pos_cell *cell, uint32_t value) {
+  return status_call([&]() {
+    if (!cell) fail("ta_pos_cell_set: cell is null");
+    *(volatile uint32_t *)cell->host = value;
+  });
+}
+int ta_pos_cell_get(const ta_pos_cell *cell, uint32_t *value) {
+  return status_call([&]() {
+    if (!cell) fail("ta_pos_cell_get: cell is null");
+    if (!value) fail("ta_pos_cell_get: value is null");
+    *value = *(volatile uint32_t *)cell->host;
+  });
+}
+
+size_t ta_kernel_spec_count(void) { return KERNEL_SPEC_COUNT; }
+
+int ta_kernel_spec_at(size_t index, ta_dispatch_info *out) {
+  return status_call([&]() {
+    if (!out) fail("ta_kernel_spec_at: out is null");
+    if (index >= KERNEL_SPEC_COUNT)
+      fail("ta_kernel_spec_at: index %zu out of range (%zu kernels)", index, KERNEL_SPEC_COUNT);
+    const KernelSpec &s = KERNEL_SPECS[index];
+    out->kernel = s.name;
+    out->tile[0] = s.tile_m;
+    out->tile[1] = s.tile_n;
+    out->tile[2] = s.tile_k;
+    out->has_split_k2 = s.family == Family::SplitK2;
+    out->split_k2_splits = 0;
+  });
+}
+
+int ta_kernel_selection_parse(const char *name) {
+  g_last_error.clear();
+  try {
+    return kernel_selection_parse(name ? name : "");
+  } catch (const std::exception &e) {
+    g_last_error = e.what();
+    return -1;
+  }
+}
+
+int ta_resolve_shapes(const uint32_t *a, size_t a_rank, const uint32_t *b, size_t b_rank,
+                      const uint32_t *c, size_t c_rank, uint32_t out[9]) {
+  return status_call([&]() {
+    if (!a || !b || !c || !out) fail("ta_resolve_shapes: null argument");
+    const ResolvedMatmul r = ResolvedMatmul::from_shapes(MatrixShape::from_shape(a, a_rank),
+                                                         MatrixShape::from_shape(b, b_rank),
+                                                         MatrixShape::from_shape(c, c_rank));
+    out[0] = r.m; out[1] = r.n; out[2] = r.k; out[3] = r.batch;
+    out[4] = r.batch_stride_a; out[5] = r.batch_stride_b; out[6] = r.batch_stride_c;
+    out[7] = (uint32_t)(r.total_flops & 0xffffffffu);
+    out[8] = (uint32_t)(r.total_flops >> 32);
+  });
+}
+
+uint32_t ta_default_num_k_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, uint32_t tile_m,
+                                 uint32_t tile_n) {
+  return default_num_k_splits(batch, m, n, k, tile_m, tile_n);
+}
+uint32_t ta_heuristic_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
+  return heuristic_splits(batch, m, n, k).value_or(0);
+}
+
+uint16_t ta_f32_to_f16_bits(float value) { return f32_to_f16_bits(value); }
+float ta_f16_bits_to_f32(uint16_t bits) { return f16_bits_to_f32(bits); }
+
+void *ta_tensor_device_ptr(const ta_tensor *tensor) { return tensor ? tensor->tensor.ptr() : nullptr; }
+int ta_context_device_index(const ta_context *ctx) { return ctx ? ctx->ctx->device : -1; }
+uint64_t ta_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"
+#pragma GCC visibility pop

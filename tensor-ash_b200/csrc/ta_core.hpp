@@ -1,0 +1,393 @@
+// Host-side core of the B200-native tensor-ash GEMM path.
+//
+// The types mirror the reference crate's public API one for one so that code
+// and tests written against it read the same here:
+//   Context        <- VulkanContext            (src/context/mod.rs)
+//   Tensor         <- Tensor                   (src/tensor.rs:20-201)
+//   MatmulCall/Op, Epilogue, Activation, EpilogueBinary, MatmulStore, RunStats
+//                  <- src/matmul/api.rs:3-353
+//   ResolvedMatmul <- src/matmul/resolution.rs:78-441
+//   Executor       <- src/executor/mod.rs:85-369, dispatch.rs, reduction.rs,
+//                     prepared.rs, transfer.rs, elementwise/*.rs
+//   PreparedOps    <- src/executor/prepared.rs:46-353 (a captured CUDA graph)
+//   KernelSpec / KERNEL_SPECS / KernelSelection <- src/pipeline/catalog.rs
+// What Vulkan did (instance, queues, descriptor sets, pipeline cache, fences)
+// is a CUDA device ordinal, one stream per executor slot and two events.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace ta {
+
+// ------------------------------------------------------------------ errors
+struct Error : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+[[noreturn]] void fail(const char *fmt, ...) __attribute__((format(printf, 1, 2)));
+std::string strf(const char *fmt, ...) __attribute__((format(printf, 1, 2)));
+void cuda_check(cudaError_t e, const char *what);
+#define TA_CUDA(expr) ::ta::cuda_check((expr), #expr)
+
+// Launch counter behind ta_kernel_launch_count().
+extern std::atomic<uint64_t> g_launches;
+
+// ------------------------------------------------------------------ dtype
+enum class DType : uint8_t { F32 = 0, F16 = 1 };
+inline uint64_t dtype_size(DType d) { return d == DType::F32 ? 4 : 2; }
+inline const char *dtype_name(DType d) { return d == DType::F32 ? "f32" : "f16"; }
+
+// Bit-exact RNE conversions (src/dtype.rs:42-112).
+uint16_t f32_to_f16_bits(float v);
+float f16_bits_to_f32(uint16_t h);
+
+// ------------------------------------------------------------------ context
+struct Context {
+  int device = 0;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t smem_optin = 0;
+  std::string name;
+  bool validation = false;
+  // cuTensorMapEncodeTiled, fetched through the runtime so the library has no
+  // link-time dependency on the driver library.
+  void *encode_tiled = nullptr;
+
+  static std::shared_ptr<Context> create(bool validation, const std::string &preference);
+  void make_current() const;
+};
+
+// ------------------------------------------------------------------ tensor
+struct Buffer {
+  std::shared_ptr<Context> ctx;
+  void *ptr = nullptr;
+  uint64_t bytes = 0;
+  ~Buffer();
+};
+
+struct Tensor {
+  std::shared_ptr<Buffer> buf;
+  std::vector<uint32_t> shape;
+  DType dtype = DType::F32;
+
+  static uint64_t numel_checked(const uint32_t *shape, size_t rank);
+  static Tensor uninit_device(const std::shared_ptr<Context> &ctx, const uint32_t *shape,
+                              size_t rank, DType dtype);
+  Tensor alias_with_shape(const uint32_t *shape, size_t rank) const;
+
+  uint64_t len() const {
+    uint64_t n = 1;
+    for (uint32_t d : shape) n *= d;
+    return n;
+  }
+  uint64_t size_bytes() const { return buf->bytes; }
+  void *ptr() const { return buf->ptr; }
+  const std::shared_ptr<Context> &ctx() const { return buf->ctx; }
+  std::string shape_str() const;
+};
+
+// ------------------------------------------------------------------ op description
+enum class Activation : uint32_t { None = 0, Relu = 1, Silu = 2, Gelu = 3 };
+enum class BinaryKind : uint32_t { None = 0, AddScaled = 1, Mul = 2 };
+enum class StoreKind : uint32_t { None = 0, Rope = 1, Scatter = 2, RopeScatter = 3 };
+
+struct MatmulCall {
+  const Tensor *a = nullptr, *b = nullptr, *c = nullptr;
+  float alpha = 1.0f;
+  bool accumulate = false;
+};
+
+struct Epilogue {
+  const Tensor *bias = nullptr;
+  Activation activation = Activation::None;
+  BinaryKind binary = BinaryKind::None;
+  const Tensor *d = nullptr;
+  float beta = 0.0f;
+  bool is_none() const {
+    return !bias && activation == Activation::None && binary == BinaryKind::None;
+  }
+};
+
+struct PosCell;  // 4-byte pinned host cell, device-visible
+
+struct MatmulStore {
+  StoreKind kind = StoreKind::None;
+  uint32_t head_dim = 0, pos_base = 0, pos_scale = 0, stride_head = 0, stride_dim = 0;
+  const Tensor *table = nullptr;
+  const Tensor *dst = nullptr;
+  const PosCell *pos_cell = nullptr;
+  bool is_none() const { return kind == StoreKind::None; }
+};
+
+struct MatmulOp {
+  MatmulCall call;
+  Epilogue epilogue;
+  const Tensor *normed_weight = nullptr;  // normed-A (weight[K], eps)
+  float normed_eps = 0.0f;
+  MatmulStore store;
+  bool packed_b = false;
+};
+
+struct RunStats {
+  std::optional<uint64_t> gpu_time_ns;
+  size_t n_calls = 0;
+  uint64_t total_flops = 0;
+  // flops / ns * 1e-3 (src/matmul/api.rs:346-353); nullopt when no/zero time.
+  std::optional<double> tflops() const {
+    if (!gpu_time_ns || *gpu_time_ns == 0) return std::nullopt;
+    return (double)total_flops / (double)*gpu_time_ns * 1e-3;
+  }
+};
+
+// ------------------------------------------------------------------ resolution
+struct MatrixShape {
+  uint32_t batch, rows, cols;
+  static MatrixShape from_shape(const uint32_t *shape, size_t rank);
+  uint32_t batch_stride(const char *label) const;
+};
+
+struct ResolvedMatmul {
+  uint32_t m = 0, n = 0, k = 0, batch = 0;
+  uint32_t batch_stride_a = 0, batch_stride_b = 0, batch_stride_c = 0;
+  uint64_t total_flops = 0;
+  bool b_f16 = false, a_f16 = false, packed_b = false;
+
+  static ResolvedMatmul from_shapes(MatrixShape a, MatrixShape b, MatrixShape c);
+  static ResolvedMatmul from_call(const MatmulCall &call);
+  static ResolvedMatmul from_op(const MatmulOp &op);
+  void validate_bias_shape(const std::vector<uint32_t> &shape) const;
+};
+
+// ------------------------------------------------------------------ registry
+// One CUDA tile variant.  `family` drives eligibility checks and launch.
+enum class Family : uint8_t {
+  Tf32x3,     // tcgen05 kind::tf32, 3-pass split, TMEM accumulate (FP32 parity)
+  Ffma,       // SIMT FFMA tiles, any shape / alignment, f32 or f16 B
+  F16wUmma,   // tcgen05 kind::f16: A f32->f16 RNE at staging, B f16
+  RowGemv,    // M-row GEMV over f16 (optionally packed) or f32 weights
+  SplitK2     // stage-1 kernels of the two-stage split-K route
+};
+
+struct KernelSpec {
+  const char *name;
+  uint32_t tile_m, tile_n, tile_k;
+  Family family;
+  bool weights_f16;  // reads B as f16 storage
+  const char *const *aliases;  // NULL-terminated; includes the reference names it supersedes
+};
+
+extern const KernelSpec KERNEL_SPECS[];
+extern const size_t KERNEL_SPEC_COUNT;
+
+// Returns -2 for "auto"/"", an index into KERNEL_SPECS, or throws.
+int kernel_selection_parse(const std::string &value);
+int kernel_index_by_name(const char *name);  // -1 when absent
+
+// Row-GEMV routing (src/pipeline/routing.rs:10-41).
+bool f16w_row_uses_k16(uint32_t k, uint32_t n);
+uint32_t f16w_row_tile_n(uint32_t k, uint32_t n);
+
+// Split-K heuristics (src/executor/splitk2.rs:36-122).
+uint32_t default_num_k_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, uint32_t tile_m,
+                              uint32_t tile_n);
+std::optional<uint32_t> heuristic_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
+void splitk2_stage1_tile(uint32_t m, uint32_t n, const char **name, uint32_t tile[3]);
+
+void pack_f16w_row_tiles(const float *src, float *dst, size_t k, size_t n, size_t tile_n);
+
+// Tuned-winner store (src/pipeline/tuning.rs:60-199): text file, one line per
+// shape "B M N K kernel [splitk2=S]", header carries the registry hash.
+struct TunedEntry {
+  int kernel = -1;
+  uint32_t splits = 0;
+};
+struct TuneKey {
+  uint32_t batch, m, n, k;
+  bool b_f16;
+  bool operator==(const TuneKey &o) const {
+    return batch == o.batch && m == o.m && n == o.n && k == o.k && b_f16 == o.b_f16;
+  }
+};
+struct TuneKeyHash {
+  size_t operator()(const TuneKey &t) const {
+    uint64_t h = 1469598103934665603ull;
+    for (uint64_t v : {(uint64_t)t.batch, (uint64_t)t.m, (uint64_t)t.n, (uint64_t)t.k,
+                       (uint64_t)t.b_f16}) {
+      h ^= v;
+      h *= 1099511628211ull;
+    }
+    return (size_t)h;
+  }
+};
+uint64_t registry_hash();
+std::string tune_store_path(const std::string &device_name);
+std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> load_tuned(const std::string &path);
+void save_tuned(const std::string &path,
+                const std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> &map);
+
+// ------------------------------------------------------------------ device parameter blocks
+// Everything a GEMM kernel needs, in elements (not bytes) for strides.
+struct GemmParams {
+  const void *a;
+  const void *b;
+  float *c;
+  const float *bias;
+  const float *d;
+  uint32_t m, n, k, batch;
+  uint32_t stride_a, stride_b, stride_c;  // batch strides, 0 = broadcast
+  uint32_t bias_stride;                    // 0 = [N], n = [B, N]
+  float alpha, beta;
+  uint32_t accumulate, act, binary, b_f16;
+  // split-K stage 1 only: K range partition count; plane = (batch*splits+s)
+  uint32_t splits;
+};
+
+struct Route {
+  int kernel = -1;       // index into KERNEL_SPECS
+  uint32_t splits = 0;   // >1: two-stage split-K route
+};
+
+// ------------------------------------------------------------------ executor
+struct Slot {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+  void *scratch = nullptr;       // grow-only device scratch (split-K planes)
+  size_t scratch_bytes = 0;
+  void *staging = nullptr;       // grow-only pinned host staging
+  size_t staging_bytes = 0;
+  uint32_t *status = nullptr;    // device word: kernels report bounded-wait timeouts here
+  bool busy = false;
+};
+
+struct ExecutorConfig {
+  size_t n_slots = 2;
+  uint32_t max_calls_per_submit = 16;
+  bool tune = false;
+};
+
+struct PreparedOps;
+
+class Executor {
+ public:
+  Executor(std::shared_ptr<Context> ctx, int selection, ExecutorConfig cfg);
+  ~Executor();
+
+  const std::shared_ptr<Context> &context() const { return ctx_; }
+
+  void upload(const float *src, size_t len, const Tensor &dst);
+  void upload_f16(const uint16_t *src, size_t len, const Tensor &dst);
+  void download(const Tensor &src, float *dst, size_t len);
+
+  RunStats run_matmuls(const std::vector<MatmulCall> &calls);
+  RunStats run_ops(const std::vector<MatmulOp> &ops);
+  RunStats run_op_graph(const std::vector<MatmulOp> &ops);
+  RunStats run_matmuls_split_k2(const std::vector<MatmulCall> &calls, uint32_t splits);
+
+  // Route a plain shape: explicit selection > tuned winner > heuristic
+  // (src/pipeline/mod.rs:259-360, src/executor/mod.rs:145-218).
+  Route plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16,
+                   bool allow_split_k2) const;
+  Route plan_op(const MatmulOp &op, const ResolvedMatmul &r, bool allow_split_k2) const;
+  void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
+
+  // Model ops (src/executor/elementwise/ops.rs).
+  RunStats softmax_rows(const Tensor &in, const Tensor &out, float scale, uint32_t mask_kind,
+                        uint32_t valid_or_prefix, uint32_t rows_per_group);
+  RunStats rms_norm(const Tensor &in, const Tensor &w, const Tensor &out, float eps);
+  RunStats layer_norm(const Tensor &in, const Tensor &w, const Tensor &b, const Tensor &out,
+                      float eps);
+  RunStats rope(const Tensor &in, const Tensor &table, const Tensor &out, uint32_t heads,
+                uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base);
+  RunStats copy_strided(const Tensor &src, const Tensor &dst, const uint32_t extent[3],
+                        uint32_t src_off, const uint32_t src_strides[3], uint32_t dst_off,
+                        const uint32_t dst_strides[3]);
+
+  void validate_tensor(const Tensor &t, const char *what) const;
+
+  // Slot checkout (src/executor/submission.rs:37-53): blocks while all busy.
+  Slot &checkout_slot();
+  void release_slot(Slot &s);
+
+  // Enqueue one validated op on a stream (no sync).  Used by run_* and by
+  // graph capture.
+  void enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Route &route, Slot &slot,
+                  cudaStream_t stream);
+  void ensure_scratch(Slot &slot, size_t bytes);
+
+  uint32_t max_calls() const { return cfg_.max_calls_per_submit; }
+  int selection() const { return selection_; }
+
+ private:
+  friend struct PreparedOps;
+  RunStats run_ops_impl(const std::vector<MatmulOp> &ops, bool graph);
+  RunStats timed(Slot &slot, size_t n_calls, uint64_t flops, const std::function<void(cudaStream_t)> &record);
+
+  std::shared_ptr<Context> ctx_;
+  int selection_;  // -2 auto, else registry index
+  ExecutorConfig cfg_;
+  std::vector<Slot> slots_;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  mutable std::mutex tune_mu_;
+  mutable std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> tuned_;
+  std::string tune_path_;
+};
+
+// Record-once / replay-many op batch (src/executor/prepared.rs:46-353).
+struct PreparedOps {
+  Executor *exec = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+  void *scratch = nullptr;
+  size_t n_calls = 0;
+  uint64_t total_flops = 0;
+  bool in_flight = false;
+
+  ~PreparedOps();
+  void submit();
+  RunStats wait();
+  RunStats run();
+};
+std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<MatmulOp> &ops,
+                                         bool as_graph);
+
+// ------------------------------------------------------------------ kernel launchers
+// Implemented beside each kernel.  All are asynchronous on `stream`.
+void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream);
+bool gemm_tf32x3_eligible(const GemmParams &p);
+void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
+                        cudaStream_t stream);
+void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream);
+void launch_splitk2_reduce(const float *scratch, float *c, uint64_t total, uint64_t mn,
+                           uint32_t splits, cudaStream_t stream);
+
+void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t cols, float scale,
+                         uint32_t mask_kind, uint32_t valid_or_prefix, uint32_t rows_per_group,
+                         cudaStream_t stream);
+void launch_rms_norm(const float *in, const float *w, float *out, uint32_t rows, uint32_t cols,
+                     float eps, cudaStream_t stream);
+void launch_layer_norm(const float *in, const float *w, const float *b, float *out, uint32_t rows,
+                       uint32_t cols, float eps, cudaStream_t stream);
+void launch_rope(const float *in, const float *table, float *out, uint32_t tokens, uint32_t heads,
+                 uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base, cudaStream_t stream);
+void launch_copy_strided(const float *src, float *dst, const uint32_t extent[3], uint32_t src_off,
+                         const uint32_t src_strides[3], uint32_t dst_off,
+                         const uint32_t dst_strides[3], cudaStream_t stream);
+
+}  // namespace ta

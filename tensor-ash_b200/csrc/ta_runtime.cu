@@ -1,0 +1,859 @@
+// CUDA runtime layer: context (device ordinal), tensors (cudaMalloc), the
+// executor (one stream + two events + grow-only scratch per slot), transfers,
+// routing, submission and prepared replay (CUDA graphs).
+//
+// Reference call stack mirrored here (src/executor/dispatch.rs:87-188):
+//   validate -> resolve shapes -> plan/route -> enqueue -> wait -> RunStats.
+// There is no CPU path: when no CUDA device is present context creation fails.
+#include <algorithm>
+#include <cstring>
+#include <functional>
+
+#include "ta_core.hpp"
+
+namespace ta {
+
+void cuda_check(cudaError_t e, const char *what) {
+  if (e != cudaSuccess) fail("CUDA error %s (%d) at %s", cudaGetErrorString(e), (int)e, what);
+}
+
+// ------------------------------------------------------------------ context
+// DevicePreference strings (src/context/mod.rs:60-103): "auto", "discrete",
+// "integrated", "virtual", "cpu", "index:N".  Only "index:N" selects among
+// CUDA devices; the adapter-kind names all mean "the current CUDA device".
+std::shared_ptr<Context> Context::create(bool validation, const std::string &preference) {
+  std::string pref;
+  for (char ch : preference) pref += (char)tolower((unsigned char)ch);
+  int device = -1;
+  if (pref.rfind("index:", 0) == 0) {
+    char *end = nullptr;
+    const long v = strtol(pref.c_str() + 6, &end, 10);
+    if (end == pref.c_str() + 6 || *end || v < 0) fail("invalid ML_DEVICE '%s'", preference.c_str());
+    device = (int)v;
+  } else if (pref.empty() || pref == "auto" || pref == "discrete" || pref == "integrated" ||
+             pref == "virtual" || pref == "cpu" || pref == "other") {
+    device = -1;
+  } else {
+    fail("invalid ML_DEVICE '%s', expected auto, discrete, integrated, virtual, cpu, or index:N",
+         preference.c_str());
+  }
+  int count = 0;
+  const cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    fail("no CUDA device available (%s); this library has no CPU fallback",
+         e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+  if (device < 0) {
+    if (cudaGetDevice(&device) != cudaSuccess) device = 0;
+  }
+  if (device >= count) fail("ML_DEVICE index %d out of range (%d CUDA devices)", device, count);
+  TA_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  TA_CUDA(cudaGetDeviceProperties(&prop, device));
+  auto ctx = std::make_shared<Context>();
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->cc_major = prop.major;
+  ctx->cc_minor = prop.minor;
+  ctx->smem_optin = prop.sharedMemPerBlockOptin;
+  ctx->name = prop.name;
+  ctx->validation = validation;
+  if (prop.major != 10)
+    fail("device %d (%s, sm_%d%d) is not a Blackwell sm_100 part; kernels are built for sm_100a only",
+         device, prop.name, prop.major, prop.minor);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+      qres == cudaDriverEntryPointSuccess)
+    ctx->encode_tiled = fn;
+  return ctx;
+}
+
+void Context::make_current() const { TA_CUDA(cudaSetDevice(device)); }
+
+// ------------------------------------------------------------------ tensor
+Buffer::~Buffer() {
+  if (ptr) {
+    cudaSetDevice(ctx->device);
+    cudaFree(ptr);
+  }
+}
+
+Tensor Tensor::uninit_device(const std::shared_ptr<Context> &ctx, const uint32_t *shape,
+                             size_t rank, DType dtype) {
+  const uint64_t n = numel_checked(shape, rank);
+  uint64_t bytes;
+  if (__builtin_mul_overflow(n, dtype_size(dtype), &bytes)) fail("tensor byte size overflows u64");
+  // Round up to 16 bytes so 128-bit readers never leave the allocation
+  // (src/tensor.rs:78-84).
+  if (bytes > UINT64_MAX - 15) fail("tensor byte size overflows u64");
+  bytes = (bytes + 15) & ~15ull;
+  ctx->make_current();
+  auto buf = std::make_shared<Buffer>();
+  buf->ctx = ctx;
+  buf->bytes = bytes;
+  const cudaError_t e = cudaMalloc(&buf->ptr, bytes);
+  if (e != cudaSuccess) {
+    buf->ptr = nullptr;
+    cudaGetLastError();
+    fail("device allocation of %llu bytes failed: %s", (unsigned long long)bytes,
+         cudaGetErrorString(e));
+  }
+  Tensor t;
+  t.buf = std::move(buf);
+  t.shape.assign(shape, shape + rank);
+  t.dtype = dtype;
+  return t;
+}
+
+Tensor Tensor::alias_with_shape(const uint32_t *new_shape, size_t rank) const {
+  const uint64_t n = numel_checked(new_shape, rank);
+  if (n != len()) {
+    std::vector<uint32_t> s(new_shape, new_shape + rank);
+    Tensor tmp;
+    tmp.shape = s;
+    fail("alias_with_shape: %llu elements for shape %s != %llu in %s", (unsigned long long)n,
+         tmp.shape_str().c_str(), (unsigned long long)len(), shape_str().c_str());
+  }
+  Tensor t;
+  t.buf = buf;
+  t.shape.assign(new_shape, new_shape + rank);
+  t.dtype = dtype;
+  return t;
+}
+
+// ------------------------------------------------------------------ executor
+Executor::Executor(std::shared_ptr<Context> ctx, int selection, ExecutorConfig cfg)
+    : ctx_(std::move(ctx)), selection_(selection), cfg_(cfg) {
+  if (cfg_.n_slots == 0) fail("Executor needs at least one slot");
+  if (cfg_.max_calls_per_submit == 0) fail("Executor max_calls_per_submit must be > 0");
+  ctx_->make_current();
+  slots_.resize(cfg_.n_slots);
+  for (Slot &s : slots_) {
+    TA_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+    TA_CUDA(cudaEventCreate(&s.ev_begin));
+    TA_CUDA(cudaEventCreate(&s.ev_end));
+    TA_CUDA(cudaMalloc(&s.status, sizeof(uint32_t)));
+    TA_CUDA(cudaMemset(s.status, 0, sizeof(uint32_t)));
+  }
+  tune_path_ = tune_store_path(ctx_->name);
+  tuned_ = load_tuned(tune_path_);
+  if (!cfg_.tune) {
+    if (const char *t = getenv("ML_TUNE"); t && (!strcmp(t, "1") || !strcasecmp(t, "true")))
+      cfg_.tune = true;
+  }
+}
+
+Executor::~Executor() {
+  cudaSetDevice(ctx_->device);
+  for (Slot &s : slots_) {
+    if (s.stream) cudaStreamSynchronize(s.stream);
+    if (s.scratch) cudaFree(s.scratch);
+    if (s.staging) cudaFreeHost(s.staging);
+    if (s.status) cudaFree(s.status);
+    if (s.ev_begin) cudaEventDestroy(s.ev_begin);
+    if (s.ev_end) cudaEventDestroy(s.ev_end);
+    if (s.stream) cudaStreamDestroy(s.stream);
+  }
+}
+
+Slot &Executor::checkout_slot() {
+  std::unique_lock<std::mutex> lk(mu_);
+  for (;;) {
+    for (Slot &s : slots_)
+      if (!s.busy) {
+        s.busy = true;
+        return s;
+      }
+    cv_.wait(lk);
+  }
+}
+
+void Executor::release_slot(Slot &s) {
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    s.busy = false;
+  }
+  cv_.notify_one();
+}
+
+namespace {
+struct SlotGuard {
+  Executor &e;
+  Slot &s;
+  SlotGuard(Executor &e_, Slot &s_) : e(e_), s(s_) {}
+  ~SlotGuard() { e.release_slot(s); }
+};
+
+void ensure_staging(Slot &slot, size_t bytes) {
+  if (slot.staging_bytes >= bytes) return;
+  if (slot.staging) cudaFreeHost(slot.staging);
+  slot.staging = nullptr;
+  slot.staging_bytes = 0;
+  TA_CUDA(cudaMallocHost(&slot.staging, bytes));
+  slot.staging_bytes = bytes;
+}
+constexpr size_t STAGING_CHUNK = 32ull << 20;  // f16 conversion is pipelined in 32 MiB pieces
+}  // namespace
+
+void Executor::ensure_scratch(Slot &slot, size_t bytes) {
+  if (slot.scratch_bytes >= bytes) return;
+  TA_CUDA(cudaStreamSynchronize(slot.stream));
+  if (slot.scratch) cudaFree(slot.scratch);
+  slot.scratch = nullptr;
+  slot.scratch_bytes = 0;
+  TA_CUDA(cudaMalloc(&slot.scratch, bytes));
+  slot.scratch_bytes = bytes;
+}
+
+void Executor::validate_tensor(const Tensor &t, const char *what) const {
+  if (t.ctx().get() != ctx_.get()) fail("%s belongs to a different context", what);
+}
+
+// ------------------------------------------------------------------ transfers
+// (src/executor/transfer.rs:21-84, 184-197)
+void Executor::upload(const float *src, size_t len, const Tensor &dst) {
+  validate_tensor(dst, "upload destination");
+  if (len == 0) return;
+  const uint64_t bytes = (uint64_t)len * dtype_size(dst.dtype);
+  if (bytes > dst.size_bytes())
+    fail("upload: %llu bytes > tensor capacity %llu", (unsigned long long)bytes,
+         (unsigned long long)dst.size_bytes());
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  if (dst.dtype == DType::F32) {
+    TA_CUDA(cudaMemcpyAsync(dst.ptr(), src, bytes, cudaMemcpyHostToDevice, slot.stream));
+    TA_CUDA(cudaStreamSynchronize(slot.stream));
+    return;
+  }
+  // f16: software RNE on the host into pinned staging, chunk by chunk.
+  const size_t chunk_elems = STAGING_CHUNK / 2;
+  ensure_staging(slot, std::min(len, chunk_elems) * 2);
+  uint16_t *stage = static_cast<uint16_t *>(slot.staging);
+  for (size_t off = 0; off < len; off += chunk_elems) {
+    const size_t n = std::min(chunk_elems, len - off);
+    for (size_t i = 0; i < n; ++i) stage[i] = f32_to_f16_bits(src[off + i]);
+    TA_CUDA(cudaMemcpyAsync(static_cast<uint16_t *>(dst.ptr()) + off, stage, n * 2,
+                            cudaMemcpyHostToDevice, slot.stream));
+    TA_CUDA(cudaStreamSynchronize(slot.stream));
+  }
+}
+
+void Executor::upload_f16(const uint16_t *src, size_t len, const Tensor &dst) {
+  validate_tensor(dst, "upload destination");
+  if (len == 0) return;
+  if (dst.dtype != DType::F16)
+    fail("upload_f16 requires an f16 destination tensor, got %s", dtype_name(dst.dtype));
+  const uint64_t bytes = (uint64_t)len * 2;
+  if (bytes > dst.size_bytes())
+    fail("upload: %llu bytes > tensor capacity %llu", (unsigned long long)bytes,
+         (unsigned long long)dst.size_bytes());
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  TA_CUDA(cudaMemcpyAsync(dst.ptr(), src, bytes, cudaMemcpyHostToDevice, slot.stream));
+  TA_CUDA(cudaStreamSynchronize(slot.stream));
+}
+
+void Executor::download(const Tensor &src, float *dst, size_t len) {
+  validate_tensor(src, "download source");
+  if (len == 0) return;
+  const uint64_t bytes = (uint64_t)len * dtype_size(src.dtype);
+  if (bytes > src.size_bytes())
+    fail("download: %llu bytes > tensor capacity %llu", (unsigned long long)bytes,
+         (unsigned long long)src.size_bytes());
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  if (src.dtype == DType::F32) {
+    TA_CUDA(cudaMemcpyAsync(dst, src.ptr(), bytes, cudaMemcpyDeviceToHost, slot.stream));
+    TA_CUDA(cudaStreamSynchronize(slot.stream));
+    return;
+  }
+  const size_t chunk_elems = STAGING_CHUNK / 2;
+  ensure_staging(slot, std::min(len, chunk_elems) * 2);
+  uint16_t *stage = static_cast<uint16_t *>(slot.staging);
+  for (size_t off = 0; off < len; off += chunk_elems) {
+    const size_t n = std::min(chunk_elems, len - off);
+    TA_CUDA(cudaMemcpyAsync(stage, static_cast<const uint16_t *>(src.ptr()) + off, n * 2,
+                            cudaMemcpyDeviceToHost, slot.stream));
+    TA_CUDA(cudaStreamSynchronize(slot.stream));
+    for (size_t i = 0; i < n; ++i) dst[off + i] = f16_bits_to_f32(stage[i]);
+  }
+}
+
+// ------------------------------------------------------------------ routing
+namespace {
+
+int idx_of(const char *name) {
+  const int i = kernel_index_by_name(name);
+  if (i < 0) fail("internal: kernel '%s' missing from registry", name);
+  return i;
+}
+
+// Static shape heuristic for B200.  The tensor-core route wins whenever the
+// problem fills at least a few 128-row tiles; tiny and very skinny problems stay
+// on the SIMT tiles, which launch faster and waste no tile area.
+int heuristic_kernel(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16, int sm_count) {
+  if (b_f16) {
+    return idx_of((m >= 128 && n >= 128) ? "f16w_ffma_m128n128" : "f16w_ffma_m64n64");
+  }
+  const bool tma_ok = (k % 4 == 0) && (n % 4 == 0);
+  if (tma_ok && m >= 64 && n >= 64 && k >= 64) {
+    const uint64_t tiles256 = (uint64_t)batch * ((m + 127) / 128) * ((n + 255) / 256);
+    const uint64_t tiles128 = (uint64_t)batch * ((m + 127) / 128) * ((n + 127) / 128);
+    // Narrow problems fill the machine better with the 128-wide tile.
+    if (n <= 128 || (tiles256 < (uint64_t)sm_count && tiles128 >= tiles256 * 2 && n % 256 != 0))
+      return idx_of("tf32x3_m128n128");
+    return idx_of("tf32x3_m128n256");
+  }
+  return idx_of((m >= 128 && n >= 128) ? "ffma_m128n128" : "ffma_m64n64");
+}
+
+bool family_matches_dtype(const KernelSpec &spec, bool b_f16) { return spec.weights_f16 == b_f16; }
+
+}  // namespace
+
+Route Executor::plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16,
+                           bool allow_split_k2) const {
+  Route r;
+  // explicit selection wins when it can run this dtype
+  if (selection_ >= 0 && family_matches_dtype(KERNEL_SPECS[selection_], b_f16) &&
+      KERNEL_SPECS[selection_].family != Family::SplitK2 &&
+      KERNEL_SPECS[selection_].family != Family::RowGemv) {
+    const KernelSpec &spec = KERNEL_SPECS[selection_];
+    const bool tma_ok = (k % 4 == 0) && (n % 4 == 0);
+    if (spec.family == Family::Ffma || (spec.family == Family::Tf32x3 && tma_ok)) {
+      r.kernel = selection_;
+      return r;
+    }
+  }
+  {
+    std::lock_guard<std::mutex> lk(tune_mu_);
+    auto it = tuned_.find(TuneKey{batch, m, n, k, b_f16});
+    if (it != tuned_.end()) {
+      r.kernel = it->second.kernel;
+      r.splits = allow_split_k2 ? it->second.splits : 0;
+      if (KERNEL_SPECS[r.kernel].family != Family::SplitK2 || r.splits > 1) return r;
+    }
+  }
+  if (allow_split_k2 && !b_f16) {
+    if (auto s = heuristic_splits(batch, m, n, k)) {
+      const uint64_t scratch = (uint64_t)batch * *s * m * n * 4;
+      if (scratch <= (256ull << 20)) {  // src/executor/splitk2.rs:142
+        r.kernel = idx_of((m >= 128 && n >= 128) ? "split_k2_m128n128" : "split_k2_m64n64");
+        r.splits = *s;
+        return r;
+      }
+    }
+  }
+  r.kernel = heuristic_kernel(batch, m, n, k, b_f16, ctx_->sm_count);
+  return r;
+}
+
+// Capability demotion (src/executor/mod.rs:268-315): every CUDA family fuses
+// the full epilogue, so only alignment can force a fallback to the SIMT tiles.
+Route Executor::plan_op(const MatmulOp &op, const ResolvedMatmul &r, bool allow_split_k2) const {
+  const bool plain = op.epilogue.is_none() && !op.call.accumulate && !op.normed_weight &&
+                     op.store.is_none() && !op.packed_b;
+  Route route = plan_shape(r.batch, r.m, r.n, r.k, r.b_f16, allow_split_k2 && plain);
+  return route;
+}
+
+// ------------------------------------------------------------------ enqueue
+namespace {
+GemmParams make_params(const MatmulOp &op, const ResolvedMatmul &r) {
+  GemmParams p{};
+  p.a = op.call.a->ptr();
+  p.b = op.call.b->ptr();
+  p.c = static_cast<float *>(op.call.c->ptr());
+  p.bias = op.epilogue.bias ? static_cast<const float *>(op.epilogue.bias->ptr()) : nullptr;
+  p.d = op.epilogue.d ? static_cast<const float *>(op.epilogue.d->ptr()) : nullptr;
+  p.m = r.m; p.n = r.n; p.k = r.k; p.batch = r.batch;
+  p.stride_a = r.batch_stride_a; p.stride_b = r.batch_stride_b; p.stride_c = r.batch_stride_c;
+  p.bias_stride = (op.epilogue.bias && op.epilogue.bias->shape.size() == 2) ? r.n : 0;
+  p.alpha = op.call.alpha;
+  p.beta = op.epilogue.beta;
+  p.accumulate = op.call.accumulate ? 1 : 0;
+  p.act = (uint32_t)op.epilogue.activation;
+  p.binary = (uint32_t)op.epilogue.binary;
+  p.b_f16 = r.b_f16 ? 1 : 0;
+  p.splits = 1;
+  return p;
+}
+}  // namespace
+
+void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Route &route,
+                          Slot &slot, cudaStream_t stream) {
+  if (r.a_f16) fail("f16 A storage (a16 route) is not built in this library yet");
+  if (op.packed_b || op.normed_weight || !op.store.is_none())
+    fail("packed-B / normed-A / fused-store ops route to the row-GEMV kernels, which are not built yet");
+  GemmParams p = make_params(op, r);
+  const KernelSpec &spec = KERNEL_SPECS[route.kernel];
+  if (route.splits > 1) {
+    p.splits = route.splits;
+    float *scratch = static_cast<float *>(slot.scratch);
+    launch_splitk2_stage1(p, spec.tile_m, scratch, stream);
+    launch_splitk2_reduce(scratch, p.c, (uint64_t)r.batch * r.m * r.n, (uint64_t)r.m * r.n,
+                          route.splits, stream);
+    return;
+  }
+  switch (spec.family) {
+    case Family::Tf32x3:
+      if (gemm_tf32x3_eligible(p)) {
+        launch_gemm_tf32x3(*ctx_, p, spec.tile_n, slot.status, stream);
+        return;
+      }
+      launch_gemm_ffma(p, 128, stream);  // alignment demotion
+      return;
+    case Family::Ffma:
+      launch_gemm_ffma(p, spec.tile_m, stream);
+      return;
+    default:
+      launch_gemm_ffma(p, (r.m >= 128 && r.n >= 128) ? 128 : 64, stream);
+      return;
+  }
+}
+
+RunStats Executor::timed(Slot &slot, size_t n_calls, uint64_t flops,
+                         const std::function<void(cudaStream_t)> &record) {
+  TA_CUDA(cudaEventRecord(slot.ev_begin, slot.stream));
+  record(slot.stream);
+  TA_CUDA(cudaEventRecord(slot.ev_end, slot.stream));
+  TA_CUDA(cudaStreamSynchronize(slot.stream));
+  uint32_t status = 0;
+  TA_CUDA(cudaMemcpy(&status, slot.status, sizeof(status), cudaMemcpyDeviceToHost));
+  if (status) {
+    cudaMemset(slot.status, 0, sizeof(uint32_t));
+    fail("a kernel gave up on a bounded device-side wait (status 0x%x); results are invalid", status);
+  }
+  float ms = 0.0f;
+  TA_CUDA(cudaEventElapsedTime(&ms, slot.ev_begin, slot.ev_end));
+  RunStats st;
+  st.gpu_time_ns = (uint64_t)((double)ms * 1e6 + 0.5);
+  st.n_calls = n_calls;
+  st.total_flops = flops;
+  return st;
+}
+
+// C must not alias A or B (src/executor/validation.rs:18-52).
+static void validate_op_tensors(const Executor &e, const MatmulOp &op) {
+  e.validate_tensor(*op.call.a, "matmul A");
+  e.validate_tensor(*op.call.b, "matmul B");
+  e.validate_tensor(*op.call.c, "matmul C");
+  if (op.call.c->ptr() == op.call.a->ptr() || op.call.c->ptr() == op.call.b->ptr())
+    fail("matmul output C must not alias an input (A or B)");
+  if (op.epilogue.bias) e.validate_tensor(*op.epilogue.bias, "epilogue bias");
+  if (op.epilogue.d) e.validate_tensor(*op.epilogue.d, "epilogue D");
+}
+
+RunStats Executor::run_ops_impl(const std::vector<MatmulOp> &ops, bool graph) {
+  (void)graph;  // one in-order stream: later ops already see earlier outputs
+  if (ops.empty()) return RunStats{std::nullopt, 0, 0};
+  if (ops.size() > cfg_.max_calls_per_submit)
+    fail("batch of %zu calls exceeds max_calls_per_submit = %u", ops.size(),
+         cfg_.max_calls_per_submit);
+  std::vector<ResolvedMatmul> resolved;
+  resolved.reserve(ops.size());
+  uint64_t flops = 0;
+  for (const MatmulOp &op : ops) {
+    validate_op_tensors(*this, op);
+    resolved.push_back(ResolvedMatmul::from_op(op));
+    if (__builtin_add_overflow(flops, resolved.back().total_flops, &flops))
+      fail("total FLOP count overflows u64");
+  }
+  ctx_->make_current();
+  // First sight of a plain single op under ML_TUNE: measure candidates once
+  // (src/executor/dispatch.rs:121-149).
+  if (cfg_.tune && ops.size() == 1) {
+    const ResolvedMatmul &r = resolved[0];
+    const bool plain = ops[0].epilogue.is_none() && !ops[0].call.accumulate;
+    bool known;
+    {
+      std::lock_guard<std::mutex> lk(tune_mu_);
+      known = tuned_.count(TuneKey{r.batch, r.m, r.n, r.k, r.b_f16}) != 0;
+    }
+    if (plain && !known && !r.b_f16 && selection_ == -2) tune_shape(r.batch, r.m, r.n, r.k);
+  }
+  std::vector<Route> routes;
+  routes.reserve(ops.size());
+  size_t scratch_bytes = 0;
+  for (size_t i = 0; i < ops.size(); ++i) {
+    // split-K2 auto route only for a lone plain op (dispatch.rs:171-176)
+    routes.push_back(plan_op(ops[i], resolved[i], ops.size() == 1));
+    if (routes.back().splits > 1)
+      scratch_bytes = std::max(scratch_bytes, (size_t)resolved[i].batch * routes.back().splits *
+                                                  resolved[i].m * resolved[i].n * 4);
+  }
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
+  return timed(slot, ops.size(), flops, [&](cudaStream_t st) {
+    for (size_t i = 0; i < ops.size(); ++i) enqueue_op(ops[i], resolved[i], routes[i], slot, st);
+  });
+}
+
+RunStats Executor::run_ops(const std::vector<MatmulOp> &ops) { return run_ops_impl(ops, false); }
+RunStats Executor::run_op_graph(const std::vector<MatmulOp> &ops) { return run_ops_impl(ops, true); }
+
+RunStats Executor::run_matmuls(const std::vector<MatmulCall> &calls) {
+  std::vector<MatmulOp> ops(calls.size());
+  for (size_t i = 0; i < calls.size(); ++i) ops[i].call = calls[i];
+  return run_ops_impl(ops, false);
+}
+
+// (src/executor/reduction.rs:21-70, splitk2.rs:213-271)
+RunStats Executor::run_matmuls_split_k2(const std::vector<MatmulCall> &calls, uint32_t splits_in) {
+  if (calls.empty()) return RunStats{std::nullopt, 0, 0};
+  if (calls.size() > cfg_.max_calls_per_submit)
+    fail("batch of %zu calls exceeds max_calls_per_submit = %u", calls.size(),
+         cfg_.max_calls_per_submit);
+  std::vector<MatmulOp> ops(calls.size());
+  std::vector<ResolvedMatmul> resolved;
+  std::vector<Route> routes;
+  uint64_t flops = 0;
+  size_t scratch_bytes = 0;
+  bool any_split = false;
+  for (size_t i = 0; i < calls.size(); ++i) {
+    ops[i].call = calls[i];
+    validate_op_tensors(*this, ops[i]);
+    if (calls[i].accumulate)
+      fail("run_matmuls_split_k2 does not support accumulate (the reduce stage overwrites C)");
+    ResolvedMatmul r = ResolvedMatmul::from_op(ops[i]);
+    if (r.b_f16 || r.a_f16) fail("run_matmuls_split_k2 requires f32 operands");
+    const char *name;
+    uint32_t tile[3];
+    splitk2_stage1_tile(r.m, r.n, &name, tile);
+    uint32_t s = splits_in ? splits_in : default_num_k_splits(r.batch, r.m, r.n, r.k, tile[0], tile[1]);
+    if (s > r.k) fail("num_k_splits %u exceeds K=%u", s, r.k);
+    if (s > 65535) fail("num_k_splits %u exceeds the 65535 limit", s);
+    if ((uint64_t)r.batch * s > 65535)
+      fail("split-K2 grid z = batch %u * splits %u exceeds 65535", r.batch, s);
+    Route route;
+    if (s <= 1) route = plan_op(ops[i], r, false);
+    else {
+      route.kernel = kernel_index_by_name(name);
+      route.splits = s;
+      any_split = true;
+      const uint64_t bytes = (uint64_t)r.batch * s * r.m * r.n * 4;
+      if (bytes > (4ull << 30)) fail("split-K2 scratch of %llu bytes exceeds the 4 GiB cap", (unsigned long long)bytes);
+      scratch_bytes = std::max(scratch_bytes, (size_t)bytes);
+    }
+    flops += r.total_flops;
+    resolved.push_back(r);
+    routes.push_back(route);
+  }
+  (void)any_split;
+  if (calls.size() > 1 && scratch_bytes) {
+    // ops in one submission share the slot scratch: give each its own region
+    size_t total = 0;
+    for (size_t i = 0; i < calls.size(); ++i)
+      if (routes[i].splits > 1)
+        total += (size_t)resolved[i].batch * routes[i].splits * resolved[i].m * resolved[i].n * 4;
+    scratch_bytes = total;
+  }
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
+  return timed(slot, calls.size(), flops, [&](cudaStream_t st) {
+    // In-order stream: a later op's stage 1 cannot start before the previous
+    // reduce finished, so one scratch region is reused safely.
+    for (size_t i = 0; i < calls.size(); ++i) enqueue_op(ops[i], resolved[i], routes[i], slot, st);
+  });
+}
+
+// ------------------------------------------------------------------ measured tuner
+// (src/executor/tuning.rs:18-313): one warm launch, round 0 discarded, then
+// interleaved measured rounds in alternating order, median per candidate; a
+// challenger must beat the heuristic pick by more than 2 %.
+void Executor::tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
+  {
+    std::lock_guard<std::mutex> lk(tune_mu_);
+    if (tuned_.count(TuneKey{batch, m, n, k, false})) return;
+  }
+  ctx_->make_current();
+  const uint32_t sa[3] = {batch, m, k}, sb[2] = {k, n}, sc[3] = {batch, m, n};
+  Tensor a = Tensor::uninit_device(ctx_, sa, 3, DType::F32);
+  Tensor b = Tensor::uninit_device(ctx_, sb, 2, DType::F32);
+  Tensor c = Tensor::uninit_device(ctx_, sc, 3, DType::F32);
+  TA_CUDA(cudaMemset(a.ptr(), 0, a.size_bytes()));
+  TA_CUDA(cudaMemset(b.ptr(), 0, b.size_bytes()));
+  MatmulOp op;
+  op.call = MatmulCall{&a, &b, &c, 1.0f, false};
+  const ResolvedMatmul r = ResolvedMatmul::from_op(op);
+
+  std::vector<Route> cands;
+  const int heuristic = heuristic_kernel(batch, m, n, k, false, ctx_->sm_count);
+  cands.push_back(Route{heuristic, 0});
+  for (const char *name : {"tf32x3_m128n256", "tf32x3_m128n128", "ffma_m128n128", "ffma_m64n64"}) {
+    const int idx = idx_of(name);
+    if (idx == heuristic) continue;
+    if (KERNEL_SPECS[idx].family == Family::Tf32x3 && (k % 4 || n % 4)) continue;
+    cands.push_back(Route{idx, 0});
+  }
+  const char *sk_name;
+  uint32_t sk_tile[3];
+  splitk2_stage1_tile(m, n, &sk_name, sk_tile);
+  for (uint32_t s : {4u, 8u, 16u, 32u, 64u})
+    if (k / s >= 128 && (uint64_t)batch * s <= 65535 && (uint64_t)batch * s * m * n * 4 <= (256ull << 20))
+      cands.push_back(Route{idx_of(sk_name), s});
+
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  size_t scratch = 0;
+  for (const Route &rt : cands)
+    if (rt.splits > 1) scratch = std::max(scratch, (size_t)batch * rt.splits * m * n * 4);
+  if (scratch) ensure_scratch(slot, scratch);
+
+  const int rounds = 5;  // round 0 discarded
+  std::vector<std::vector<double>> times(cands.size());
+  for (int round = 0; round < rounds; ++round) {
+    for (size_t ci = 0; ci < cands.size(); ++ci) {
+      const size_t i = (round & 1) ? cands.size() - 1 - ci : ci;
+      RunStats st = timed(slot, 1, r.total_flops,
+                          [&](cudaStream_t s) { enqueue_op(op, r, cands[i], slot, s); });
+      if (round > 0) times[i].push_back((double)*st.gpu_time_ns);
+    }
+  }
+  auto median = [](std::vector<double> v) {
+    std::sort(v.begin(), v.end());
+    return v.size() % 2 ? v[v.size() / 2] : 0.5 * (v[v.size() / 2 - 1] + v[v.size() / 2]);
+  };
+  size_t best = 0;
+  const double base = median(times[0]);
+  double best_t = base;
+  for (size_t i = 1; i < cands.size(); ++i) {
+    const double t = median(times[i]);
+    if (t < best_t && t < base * 0.98) {
+      best_t = t;
+      best = i;
+    }
+  }
+  {
+    std::lock_guard<std::mutex> lk(tune_mu_);
+    tuned_[TuneKey{batch, m, n, k, false}] = TunedEntry{cands[best].kernel, cands[best].splits};
+    save_tuned(tune_path_, tuned_);
+  }
+}
+
+// ------------------------------------------------------------------ model ops
+namespace {
+void ensure_f32(const Executor &e, const Tensor &t, const char *op, const char *operand) {
+  e.validate_tensor(t, operand);
+  if (t.dtype != DType::F32) fail("%s: %s must be f32 storage", op, operand);
+}
+void ensure_same_shape(const char *op, const Tensor &a, const Tensor &b) {
+  if (a.shape != b.shape)
+    fail("%s: input shape %s != output shape %s", op, a.shape_str().c_str(), b.shape_str().c_str());
+}
+void rows_cols(const Tensor &t, const char *label, uint32_t *rows, uint32_t *cols) {
+  *cols = t.shape.back();
+  const uint64_t r = t.len() / *cols;
+  if (r > 0xffffffffull) fail("%s: row count %llu exceeds u32", label, (unsigned long long)r);
+  *rows = (uint32_t)r;
+}
+}  // namespace
+
+RunStats Executor::softmax_rows(const Tensor &in, const Tensor &out, float scale, uint32_t mask_kind,
+                                uint32_t valid_or_prefix, uint32_t rows_per_group) {
+  ensure_f32(*this, in, "run_softmax_rows", "input");
+  ensure_f32(*this, out, "run_softmax_rows", "output");
+  ensure_same_shape("run_softmax_rows", in, out);
+  uint32_t rows, cols;
+  rows_cols(in, "run_softmax_rows", &rows, &cols);
+  if (mask_kind == 2 && (rows_per_group == 0 || rows % rows_per_group))
+    fail("run_softmax_rows: rows_per_group %u must divide rows %u", rows_per_group, rows);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, 1, 0, [&](cudaStream_t s) {
+    launch_softmax_rows((const float *)in.ptr(), (float *)out.ptr(), rows, cols, scale, mask_kind,
+                        valid_or_prefix, rows_per_group, s);
+  });
+}
+
+RunStats Executor::rms_norm(const Tensor &in, const Tensor &w, const Tensor &out, float eps) {
+  ensure_f32(*this, in, "run_rms_norm", "input");
+  ensure_f32(*this, w, "run_rms_norm", "weight");
+  ensure_f32(*this, out, "run_rms_norm", "output");
+  ensure_same_shape("run_rms_norm", in, out);
+  uint32_t rows, cols;
+  rows_cols(in, "run_rms_norm", &rows, &cols);
+  if (w.len() != cols)
+    fail("run_rms_norm: weight length %llu != row length %u", (unsigned long long)w.len(), cols);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, 1, 0, [&](cudaStream_t s) {
+    launch_rms_norm((const float *)in.ptr(), (const float *)w.ptr(), (float *)out.ptr(), rows, cols,
+                    eps, s);
+  });
+}
+
+RunStats Executor::layer_norm(const Tensor &in, const Tensor &w, const Tensor &b, const Tensor &out,
+                              float eps) {
+  ensure_f32(*this, in, "run_layer_norm", "input");
+  ensure_f32(*this, w, "run_layer_norm", "weight");
+  ensure_f32(*this, b, "run_layer_norm", "bias");
+  ensure_f32(*this, out, "run_layer_norm", "output");
+  ensure_same_shape("run_layer_norm", in, out);
+  uint32_t rows, cols;
+  rows_cols(in, "run_layer_norm", &rows, &cols);
+  if (w.len() != cols)
+    fail("run_layer_norm: weight length %llu != row length %u", (unsigned long long)w.len(), cols);
+  if (b.len() != cols)
+    fail("run_layer_norm: bias length %llu != row length %u", (unsigned long long)b.len(), cols);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, 1, 0, [&](cudaStream_t s) {
+    launch_layer_norm((const float *)in.ptr(), (const float *)w.ptr(), (const float *)b.ptr(),
+                      (float *)out.ptr(), rows, cols, eps, s);
+  });
+}
+
+RunStats Executor::rope(const Tensor &in, const Tensor &table, const Tensor &out, uint32_t heads,
+                        uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base) {
+  ensure_f32(*this, in, "run_rope", "input");
+  ensure_f32(*this, out, "run_rope", "output");
+  ensure_f32(*this, table, "run_rope", "table");
+  ensure_same_shape("run_rope", in, out);
+  if (rot_dim < 2 || rot_dim % 2 || rot_dim > head_dim)
+    fail("run_rope: rot_dim %u must be even, >= 2, and <= head_dim %u", rot_dim, head_dim);
+  const uint64_t vec = (uint64_t)heads * head_dim;
+  if (vec == 0 || in.len() % vec)
+    fail("run_rope: input length %llu is not a multiple of heads*head_dim %llu",
+         (unsigned long long)in.len(), (unsigned long long)vec);
+  const uint64_t tokens64 = in.len() / vec;
+  if (tokens64 > 0xffffffffull) fail("run_rope: token count exceeds u32");
+  const uint32_t tokens = (uint32_t)tokens64;
+  const uint64_t needed = ((uint64_t)pos_base + tokens) * rot_dim;
+  if (table.len() < needed)
+    fail("run_rope: table length %llu < required %llu (pos_base %u + %u tokens, rot_dim %u)",
+         (unsigned long long)table.len(), (unsigned long long)needed, pos_base, tokens, rot_dim);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, 1, 0, [&](cudaStream_t s) {
+    launch_rope((const float *)in.ptr(), (const float *)table.ptr(), (float *)out.ptr(), tokens,
+                heads, head_dim, rot_dim, pos_base, s);
+  });
+}
+
+RunStats Executor::copy_strided(const Tensor &src, const Tensor &dst, const uint32_t extent[3],
+                                uint32_t src_off, const uint32_t src_strides[3], uint32_t dst_off,
+                                const uint32_t dst_strides[3]) {
+  validate_tensor(src, "src");
+  validate_tensor(dst, "dst");
+  if (src.ptr() == dst.ptr()) fail("run_copy_strided: src and dst must be different tensors");
+  if (src.dtype != DType::F32 || dst.dtype != DType::F32)
+    fail("run_copy_strided: f16 pairings are not built in this library yet");
+  if (!extent[0] || !extent[1] || !extent[2])
+    fail("run_copy_strided: extent [%u, %u, %u] has a zero axis", extent[0], extent[1], extent[2]);
+  auto max_index = [&](uint32_t off, const uint32_t st[3]) {
+    uint64_t v = off;
+    for (int i = 0; i < 3; ++i) v += (uint64_t)(extent[i] - 1) * st[i];
+    return v;
+  };
+  if (max_index(src_off, src_strides) >= src.len())
+    fail("run_copy_strided: source access reaches element %llu but src has %llu",
+         (unsigned long long)max_index(src_off, src_strides), (unsigned long long)src.len());
+  if (max_index(dst_off, dst_strides) >= dst.len())
+    fail("run_copy_strided: destination access reaches element %llu but dst has %llu",
+         (unsigned long long)max_index(dst_off, dst_strides), (unsigned long long)dst.len());
+  if ((uint64_t)extent[0] * extent[1] * extent[2] > 0xffffffffull)
+    fail("run_copy_strided: extent product exceeds u32");
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, 1, 0, [&](cudaStream_t s) {
+    launch_copy_strided((const float *)src.ptr(), (float *)dst.ptr(), extent, src_off, src_strides,
+                        dst_off, dst_strides, s);
+  });
+}
+
+// ------------------------------------------------------------------ prepared replay
+// (src/executor/prepared.rs:78-155): data-parallel routes only; recorded once
+// into a CUDA graph on a private stream; one submission in flight per handle.
+std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<MatmulOp> &ops,
+                                         bool as_graph) {
+  (void)as_graph;
+  if (ops.empty()) fail("prepare_ops: empty op list");
+  if (ops.size() > exec.max_calls())
+    fail("batch of %zu calls exceeds max_calls_per_submit = %u", ops.size(), exec.max_calls());
+  exec.context()->make_current();
+  auto prep = std::make_unique<PreparedOps>();
+  prep->exec = &exec;
+  std::vector<ResolvedMatmul> resolved;
+  std::vector<Route> routes;
+  for (const MatmulOp &op : ops) {
+    validate_op_tensors(exec, op);
+    resolved.push_back(ResolvedMatmul::from_op(op));
+    routes.push_back(exec.plan_op(op, resolved.back(), false));
+    prep->total_flops += resolved.back().total_flops;
+  }
+  prep->n_calls = ops.size();
+  TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
+  TA_CUDA(cudaEventCreate(&prep->ev_begin));
+  TA_CUDA(cudaEventCreate(&prep->ev_end));
+  // Tensor maps and attribute setup happen on first launch of each kernel: run
+  // the batch once eagerly so capture sees only launches.
+  Slot &slot = exec.checkout_slot();
+  {
+    SlotGuard g(exec, slot);
+    TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
+    try {
+      for (size_t i = 0; i < ops.size(); ++i)
+        exec.enqueue_op(ops[i], resolved[i], routes[i], slot, prep->stream);
+    } catch (...) {
+      cudaGraph_t dead = nullptr;
+      cudaStreamEndCapture(prep->stream, &dead);
+      if (dead) cudaGraphDestroy(dead);
+      throw;
+    }
+    TA_CUDA(cudaStreamEndCapture(prep->stream, &prep->graph));
+  }
+  TA_CUDA(cudaGraphInstantiate(&prep->graph_exec, prep->graph, 0));
+  return prep;
+}
+
+PreparedOps::~PreparedOps() {
+  if (exec) cudaSetDevice(exec->context()->device);
+  if (stream) cudaStreamSynchronize(stream);  // wait for in-flight work
+  if (graph_exec) cudaGraphExecDestroy(graph_exec);
+  if (graph) cudaGraphDestroy(graph);
+  if (ev_begin) cudaEventDestroy(ev_begin);
+  if (ev_end) cudaEventDestroy(ev_end);
+  if (stream) cudaStreamDestroy(stream);
+}
+
+void PreparedOps::submit() {
+  if (in_flight) fail("PreparedOps::submit: a submission is already in flight; call wait() first");
+  exec->context()->make_current();
+  TA_CUDA(cudaEventRecord(ev_begin, stream));
+  TA_CUDA(cudaGraphLaunch(graph_exec, stream));
+  TA_CUDA(cudaEventRecord(ev_end, stream));
+  in_flight = true;
+}
+
+RunStats PreparedOps::wait() {
+  if (!in_flight) fail("PreparedOps::wait: nothing in flight; call submit() first");
+  exec->context()->make_current();
+  TA_CUDA(cudaStreamSynchronize(stream));
+  in_flight = false;
+  float ms = 0.0f;
+  TA_CUDA(cudaEventElapsedTime(&ms, ev_begin, ev_end));
+  RunStats st;
+  st.gpu_time_ns = (uint64_t)((double)ms * 1e6 + 0.5);
+  st.n_calls = n_calls;
+  st.total_flops = total_flops;
+  return st;
+}
+
+RunStats PreparedOps::run() {
+  submit();
+  return wait();
+}
+
+}  // namespace ta
