@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path on B200.
+
+Workload (one "step" = one pass of the hot path over one batch of synthetic
+input): the batched FP32 GEMM with broadcast B and fused epilogue,
+    C[b] = silu(A[b] @ B + bias[b]) + 1.0 * R[b],
+    A, R, C [32, 2048, 2048], B [2048, 2048], bias [32, 2048], all f32,
+drawn N(0, 1/sqrt(K)) from a fixed seed.  It runs through the library's public
+API (`Executor.run_ops`, i.e. `ta_run_ops` of the C ABI) as one fused launch of
+the tcgen05 3xTF32 kernel.
+
+Multi-GPU: independent batch planes partition with no collective.  Every rank
+owns one GPU and runs the full 32-plane workload on its own data (weak
+scaling); `value` is the flops all ranks completed divided by the slowest
+rank's device time.
+
+  python bench.py --gpus N --steps K --warmup W          this library
+  python bench.py --impl reference ...                   the reference's CPU GEMM
+                                                          (oracle port) on host cores
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+BATCH, M, N, K = 32, 2048, 2048, 2048
+METRIC = "fp32_batched_gemm_fused_epilogue_tflops"
+UNIT = "TFLOP/s"
+FLOPS_PER_STEP = 2 * BATCH * M * N * K
+WORKLOAD = "configs[1]: batched FP32 GEMM 32x2048x2048x2048, shared B, per-batch bias, silu, +R"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(source="measured", hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"],
+                    bf16_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]))
+    return dict(source="fallback", hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU during the timed region."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(seed: int):
+    """Seeded synthetic inputs of the configuration's shapes and distribution, in
+    pinned host memory (the end-to-end leg copies from here every step)."""
+    import torch
+    rng = np.random.default_rng(seed)
+    sig = 1.0 / np.sqrt(K)
+
+    def pinned(shape):
+        t = torch.empty(shape, dtype=torch.float32).pin_memory()
+        arr = t.numpy()
+        arr[...] = rng.standard_normal(shape, dtype=np.float32) * np.float32(sig)
+        return t, arr
+
+    return {name: pinned(shape) for name, shape in
+            (("a", (BATCH, M, K)), ("b", (K, N)), ("bias", (BATCH, N)), ("r", (BATCH, M, N)))}
+
+
+def spot_check(ta_out: np.ndarray, host, samples: int = 64) -> float:
+    """Bench-time validation in the reference's style (8 well-spaced outputs in
+    tools/ml-bench/src/bench/commands.rs:225-273; 64 here): recompute sampled
+    outputs in float64 with numpy and return the worst relative error."""
+    a, b, bias, r = (host[k][1] for k in ("a", "b", "bias", "r"))
+    total = BATCH * M * N
+    worst = 0.0
+    for s in range(samples):
+        idx = (s * 2654435761 + 12345) % total
+        bi, rem = divmod(idx, M * N)
+        i, j = divmod(rem, N)
+        acc = float(np.dot(a[bi, i].astype(np.float64), b[:, j].astype(np.float64)))
+        x = float(np.float32(acc)) + float(bias[bi, j])
+        x = x / (1.0 + np.exp(-x)) + float(r[bi, i, j])
+        worst = max(worst, abs(float(ta_out[bi, i, j]) - x) / max(1.0, abs(x)))
+    return worst
+
+
+def cpu_baseline(budget_s: float = 12.0) -> dict:
+    """The reference's test-suite CPU GEMM (f64-accumulating cpu_bmm, restated in
+    oracle/ta_oracle.c) plus its epilogue, timed on this host's cores over a
+    bounded sample of the same workload: `rows` rows of one batch plane."""
+    orc = entry.load_oracle()
+    threads = orc.num_threads()
+    rng = np.random.default_rng(1)
+    sig = np.float32(1.0 / np.sqrt(K))
+    b = rng.standard_normal((K, N), dtype=np.float32) * sig
+
+    def run(planes, rows):
+        a = rng.standard_normal((planes, rows, K), dtype=np.float32) * sig
+        bias = rng.standard_normal((planes, N), dtype=np.float32) * sig
+        r = rng.standard_normal((planes, rows, N), dtype=np.float32) * sig
+        t0 = time.perf_counter()
+        c = orc.cpu_bmm(a, b, planes, rows, N, K, threads=0)
+        orc.cpu_epilogue(c, planes, rows, N, bias=bias, act="silu", binary="add_scaled", d=r, beta=1.0)
+        return time.perf_counter() - t0
+
+    probe_rows = min(M, 8 * threads)
+    t_probe = run(1, probe_rows)
+    t_plane = t_probe * M / probe_rows
+    if t_plane >= budget_s:
+        planes, rows = 1, max(probe_rows, int(M * budget_s / t_plane) // threads * threads)
+    else:
+        planes, rows = int(min(BATCH, max(1, budget_s // t_plane))), M
+    t = run(planes, rows)
+    tflops = 2.0 * planes * rows * N * K / t / 1e12
+    return {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{planes} plane(s) x {rows} rows of the {BATCH} x {M} output rows (N={N}, K={K}), "
+                      f"f64-accumulating cpu_bmm + epilogue on {threads} threads, {t:.2f} s"}
+
+
+def run_reference_arm(args, rank: int) -> None:
+    if rank != 0:
+        return
+    per_step = max(2.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_baseline(per_step)
+    vals, t0 = [], time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        last = cpu_baseline(per_step)
+        vals.append(last["value"])
+    wall = time.perf_counter() - t0
+    value = statistics.median(vals)
+    last["value"] = value
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / max(1, args.steps) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "note": "bounded CPU sample per step"},
+        "cpu_baseline": last,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel", default="auto", help="ML_KERNEL-style selection for experiments")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    distributed = world > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    ta = entry.load_package()
+    ctx = ta.Context(False, f"index:{local_rank}")
+    ex = ta.Executor(ctx, 2, 8, args.kernel)
+    host = make_inputs(1234 + rank)
+    dev = {k: ta.Tensor.uninit_device(ctx, v[1].shape) for k, v in host.items()}
+    dev["c"] = ta.Tensor.uninit_device(ctx, (BATCH, M, N))
+    for k, v in host.items():
+        ex.upload(v[1], dev[k])
+    op = ta.MatmulOp(ta.MatmulCall(dev["a"], dev["b"], dev["c"]),
+                     ta.Epilogue(dev["bias"], ta.Activation.SILU, ta.Binary.ADD_SCALED, dev["r"], 1.0))
+    route = ex.dispatch_info_for(BATCH, M, N, K)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if distributed:
+            dist.barrier()
+
+    # ---- device-resident leg: inputs already in HBM when the timed region starts.
+    # The 1.6 GB of operands per launch exceed the 126 MB L2, so no flush is needed.
+    for _ in range(max(args.warmup, 3)):
+        ex.run_ops([op])
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = ta.kernel_launch_count()
+    dev_ns = []
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        dev_ns.append(ex.run_ops([op]).gpu_time_ns)    # CUDA events on the launch stream
+    barrier()
+    wall_s = time.perf_counter() - t0
+    launches = ta.kernel_launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    total_ms = sum(dev_ns) / 1e6
+    if distributed:
+        t = torch.tensor([total_ms, wall_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, wall_s = float(t[0]), float(t[1])
+    ms_per_step = total_ms / args.steps
+    value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
+
+    out_host_t = torch.empty((BATCH, M, N), dtype=torch.float32).pin_memory()
+    out_host = out_host_t.numpy()
+    ex.download_into(dev["c"], out_host)
+    worst_rel = spot_check(out_host, host)
+
+    # ---- end-to-end leg: pinned host buffers in, host buffer out, every step.
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = min(args.steps, 10)
+        h2d = sum(v[1].nbytes for v in host.values())
+        d2h = out_host.nbytes
+
+        def e2e_step():
+            for k, v in host.items():
+                ex.upload(v[1], dev[k])
+            ex.run_ops([op])
+            ex.download_into(dev["c"], out_host)
+
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        if distributed:
+            t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t[0])
+        e2e = {"value": FLOPS_PER_STEP * world * e2e_steps / e2e_s / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "ms_per_step": e2e_s / e2e_steps * 1e3}
+
+    if rank == 0:
+        peaks = measured_peaks()
+        long_run = total_ms > 1000.0
+        bf16 = peaks["bf16_sustained"] if long_run else peaks["bf16"]
+        # tf32 issues at half the bf16 rate and 3xTF32 spends three MMAs per logical product
+        peak = bf16 / 2.0 / 3.0
+        achieved = FLOPS_PER_STEP / (statistics.mean(dev_ns) * 1e-9) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core split, f32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "m": M, "n": N, "k": K,
+                       "kernel": route.kernel, "tile": list(route.tile), "parallelism": f"batch-replicated x{world}",
+                       "l2": "operands per launch (1.63 GB) exceed the 126 MB L2; no flush needed"},
+            "wall_ms_per_step": wall_s / args.steps * 1e3,
+            "median_ms": statistics.median(dev_ns) / 1e6, "min_ms": min(dev_ns) / 1e6,
+            "spot_check_max_rel_err": worst_rel,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "peak_basis": f"{peaks['source']} bf16 {'sustained' if long_run else 'burst'} "
+                                       f"{bf16:.1f} TFLOP/s / 2 (tf32 rate) / 3 (MMA passes per product)",
+                         "executed_tensor_tflops": achieved * 3.0},
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline()
+        assert worst_rel <= 1e-5, f"bench-time validation failed: rel err {worst_rel:.3e}"
+        print(json.dumps(line))
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
