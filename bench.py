@@ -193,10 +193,14 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel", default="auto", help="ML_KERNEL-style selection for experiments")
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="planes per GPU; below 32 is a reduced case for profiler captures, not a bench value")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
 
+    globals()["BATCH"] = args.batch
+    globals()["FLOPS_PER_STEP"] = 2 * args.batch * M * N * K
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -298,7 +302,8 @@ def main() -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core split, f32 accumulate)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "m": M, "n": N, "k": K,
+            "config": {"workload": WORKLOAD if BATCH == 32 else f"REDUCED profiling case, {BATCH} planes (not a bench value)",
+                       "batch_per_gpu": BATCH, "m": M, "n": N, "k": K,
                        "kernel": route.kernel, "tile": list(route.tile), "parallelism": f"batch-replicated x{world}",
                        "l2": "operands per launch (1.63 GB) exceed the 126 MB L2; no flush needed"},
             "wall_ms_per_step": wall_s / args.steps * 1e3,

@@ -141,7 +141,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"  // same asm block: nothing may read the registers earlier
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
         "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
@@ -149,7 +150,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ uint32_t rna_tf32(float x) {
   uint32_t r;
@@ -165,7 +165,13 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes,
   const uint32_t hi = ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (layout_type << 29);
   return ((uint64_t)hi << 32) | lo;
 }
-constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_SW64 = 4;
+// B is N-contiguous ("MN-major").  For 32-bit operands the tensor core reads an
+// MN-major tile only in the 128B-swizzle-with-32-byte-atoms layout (type 1):
+// rows of 32 floats (128 B) per k, 32-byte chunks XOR-ed with (k & 3), groups of
+// 4 k-rows 512 B apart (SBO), 32-column blocks BK*128 B apart (LBO).  TMA
+// produces exactly that image with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.  The
+// plain 128B swizzle (type 2) makes the tensor core read zeros for this case.
+constexpr uint32_t LAYOUT_SW128_BASE32B = 1, LAYOUT_SW64 = 4;
 
 // ---------------------------------------------------------------- kernel
 template <int BN>
@@ -262,8 +268,8 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
           for (int j = 0; j < BK / 8; ++j) {
             const uint64_t da_hi = make_desc(a_hi + j * 32, 16, 512, LAYOUT_SW64);
             const uint64_t da_lo = make_desc(a_lo + j * 32, 16, 512, LAYOUT_SW64);
-            const uint64_t db_hi = make_desc(b_hi + j * 1024, BK * 128, 1024, LAYOUT_SW128);
-            const uint64_t db_lo = make_desc(b_lo + j * 1024, BK * 128, 1024, LAYOUT_SW128);
+            const uint64_t db_hi = make_desc(b_hi + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
+            const uint64_t db_lo = make_desc(b_lo + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
             mma_tf32(d_tmem, da_lo, db_hi, idesc, (kb | (uint32_t)j) != 0u);
             mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
             mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
@@ -406,7 +412,7 @@ void launch_t(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStr
   // B [bb, K, N]: dims {N, K, bb}; boxes of 32 columns (128 bytes) x BK rows.
   encode_map(ctx, &map_b, p.b, p.n, p.k, bb, (uint64_t)p.n * 4,
              p.stride_b ? (uint64_t)p.stride_b * 4 : (uint64_t)p.k * p.n * 4, 32, BK,
-             CU_TENSOR_MAP_SWIZZLE_128B);
+             CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
   gemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);
