@@ -9,11 +9,12 @@
 //     C[b,i,j] = epi(alpha * sum_k A[b,i,k] * B[b,k,j] (+ C[b,i,j]))
 // A [B,M,K], B [K,N] or [B,K,N], C/D [B,M,N] row-major f32, bias [N] or [B,N].
 //
-// Split: x = hi + lo with hi = rna_tf32(x), lo = rna_tf32(x - hi) (x - hi is
-// exact in f32).  Per K step the tensor core adds  a_lo*b_hi + a_hi*b_lo +
-// a_hi*b_hi  into one f32 accumulator; the dropped a_lo*b_lo term is 2^-22
-// relative.  The split is elementwise, so the converter warps rewrite the TMA
-// tile in place (hi) and into a twin buffer (lo) at identical offsets: the
+// Split: x = hi + lo with hi = trunc_tf32(x) (what the tensor core sees when it
+// reads the raw f32 word) and lo = rn_tf32(x - hi) (x - hi is exact in f32).
+// Per K step the tensor core adds  a_lo*b_hi + a_hi*b_lo + a_hi*b_hi  into one
+// f32 accumulator; the dropped a_lo*b_lo term is below 2^-20 relative.  The
+// split is elementwise, so the converter warps leave the TMA tile untouched (it
+// is the hi operand) and write lo into a twin buffer at identical offsets: the
 // shared-memory swizzle never has to be decoded.
 //
 // Warp roles (320 threads): warps 0-3 drain TMEM and run the epilogue (warp w
@@ -81,11 +82,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 // Bounded wait.  Returns false when the wait gave up (flag raised by this or
 // another role); callers then leave their loops.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort) {
+// sleep_ns > 0 backs off between polls: for the long waits (a whole tile's main
+// loop) so that idle warps do not burn issue slots and shared-memory bandwidth.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort,
+                                          uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((++spins & 63u) == 0) {
       if (*abort) return false;
       if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
@@ -151,10 +156,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ uint32_t rna_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
+// The tensor core reads an f32 word as tf32 by ignoring the low 13 mantissa bits
+// (truncation toward zero, measured on B200).  So the raw tile IS the hi operand,
+// hi = trunc_tf32(x), and only lo = x - hi has to be produced: exact in f32, then
+// rounded to nearest tf32 with integer ops (add half an ulp, mask) so the tensor
+// core's own truncation of lo loses nothing.  Four full-rate ALU ops per element.
+__device__ __forceinline__ uint32_t split_lo(float x) {
+  const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+  return (__float_as_uint(x - hi) + 0x1000u) & 0xffffe000u;
 }
 
 // Shared-memory matrix descriptor (64-bit): start address, leading / stride
@@ -295,13 +304,8 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
 #pragma unroll 4
         for (int i = t; i < C::HALF_BYTES / 16; i += 128) {
           const float4 v = hi[i];
-          uint4 h, l;
-          h.x = rna_tf32(v.x); h.y = rna_tf32(v.y); h.z = rna_tf32(v.z); h.w = rna_tf32(v.w);
-          l.x = rna_tf32(v.x - __uint_as_float(h.x));
-          l.y = rna_tf32(v.y - __uint_as_float(h.y));
-          l.z = rna_tf32(v.z - __uint_as_float(h.z));
-          l.w = rna_tf32(v.w - __uint_as_float(h.w));
-          *reinterpret_cast<uint4 *>(hi + i) = h;
+          uint4 l;
+          l.x = split_lo(v.x); l.y = split_lo(v.y); l.z = split_lo(v.z); l.w = split_lo(v.w);
           *reinterpret_cast<uint4 *>(lo + i) = l;
         }
         // generic-proxy writes -> visible to the tensor core's async-proxy reads
@@ -319,7 +323,7 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
       const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
       const uint32_t m0 = (rem / tiles_n) * BM, n0 = (rem % tiles_n) * BN;
       const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
-      ok = mbar_wait(acc_full(buf), acc_phase, abort_flag);
+      ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
       if (!ok) break;
       tc_fence_after();
       const uint32_t row = m0 + warp * 32 + lane;
