@@ -219,6 +219,35 @@ int ta_tune_shape(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t 
 int ta_matmul_split_k2(const ta_executor *exec, const ta_matmul_call *calls, size_t n_calls,
                        uint32_t splits, ta_run_stats *stats);
 
+/* Split-K2 for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Some callers cannot call cudaMalloc when they need a GEMM: code running
+ * inside a memory-pool or framework allocator callback, a real-time or
+ * fault-handling path where the allocator's device-wide synchronisation is not
+ * allowed, or a process whose device memory was budgeted completely at start-up.
+ * ta_matmul_split_k2 grows its executor's scratch with cudaMalloc on first use;
+ * this entry point instead keeps the partial planes in a fixed 4 MiB array
+ * inside the library's device image (present on every GPU that loads the
+ * library, until the process exits) and calls no cudaMalloc, cudaFree or any
+ * other allocating routine.
+ *
+ * C[M,N] = alpha * A[M,K] @ B[K,N], row-major f32, one matrix per call, same
+ * two kernels and therefore bit-identical results to ta_matmul_split_k2.
+ * a, b, c are device pointers on the CURRENT CUDA device; the caller owns them.
+ * Limits: splits >= 2, splits <= K, splits * M * N <=
+ * TA_SPLIT_K2_NOALLOC_MAX_FLOATS; anything larger is rejected with -1 and a
+ * message.  The call enqueues on `stream` (NULL = default stream) and returns
+ * after that stream has finished the two kernels.
+ *
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture.
+ * Every call uses the same array and leaves its partials there: nothing needs
+ * clearing between calls (each plane element is stored before it is read), but
+ * two calls that overlap on the GPU, from any thread or stream, race. */
+#define TA_SPLIT_K2_NOALLOC_MAX_FLOATS (1u << 20)
+int ta_split_k2_noalloc(const float *a, const float *b, float *c, uint32_t m, uint32_t n,
+                        uint32_t k, uint32_t splits, float alpha, void *stream);
+
 /* ta_store_desc.kind: fused store of an M == 1 f16-weight GEMV
  * (ref src/matmul/api.rs:120-250, MatmulStore / MatmulStoreDesc). */
 enum {

@@ -116,6 +116,7 @@ SIGNATURES = {
     "ta_tune_shape": (C.c_int, [_P, _U32, _U32, _U32, _U32]),
     # ---- additive entry points
     "ta_matmul_split_k2": (C.c_int, [_P, C.POINTER(MatmulCallC), _SZ, _U32, _STATS]),
+    "ta_split_k2_noalloc": (C.c_int, [_P, _P, _P, _U32, _U32, _U32, _U32, C.c_float, _P]),
     "ta_run_ops_ex": (C.c_int, [_P, C.POINTER(MatmulOpExC), _SZ, _U32, _STATS]),
     "ta_swiglu_gemv": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_float, _STATS]),
     "ta_pack_f16w_row_tiles": (C.c_int, [_P, _P, _SZ, _SZ, _SZ]),

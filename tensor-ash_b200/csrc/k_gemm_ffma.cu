@@ -15,6 +15,8 @@
 #include "k_epilogue.cuh"
 #include "ta_core.hpp"
 
+#include <mutex>
+
 namespace ta {
 
 constexpr int FFMA_BK = 16;
@@ -215,6 +217,54 @@ void launch_splitk2_reduce(const float *scratch, float *c, uint64_t total, uint6
   splitk2_reduce_kernel<<<blocks, 256, 0, stream>>>(scratch, c, total, mn, splits);
   TA_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// ---------------------------------------------------------------------------
+// Split-K2 without any allocation: the partial planes live in a fixed array
+// that is part of the loaded module (4 MiB per GPU that loads the library, held
+// until the process exits).
+//
+// `g_splitk2_static` is a device symbol.  On the host its name is only a
+// stand-in, never a device address, so the address kernels receive is fetched
+// with cudaGetSymbolAddress: once per device, with that device current, on the
+// first call made for it.  Stage 1 plain-stores every element of every plane
+// it uses before the reduce reads them, so nothing has to start at zero; what a
+// previous call left behind is simply overwritten.  All calls share the one
+// array: two calls whose kernels overlap on the GPU race on it.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) float g_splitk2_static[SPLITK2_STATIC_MAX_FLOATS];
+
+namespace {
+std::mutex g_static_mu;
+float *g_static_ptr[64] = {};  // per device ordinal, filled on first use
+}  // namespace
+
+void launch_splitk2_static(const GemmParams &p, cudaStream_t stream) {
+  const uint64_t need = (uint64_t)p.splits * p.m * p.n;
+  if (p.batch != 1) fail("split-K2 on the static scratch handles one matrix per call (batch %u)", p.batch);
+  if (need > SPLITK2_STATIC_MAX_FLOATS)
+    fail("split-K2 on the static scratch needs splits*M*N = %llu floats, more than the fixed %llu "
+         "(4 MiB); use ta_matmul_split_k2, which sizes its own scratch",
+         (unsigned long long)need, (unsigned long long)SPLITK2_STATIC_MAX_FLOATS);
+  int dev = -1;
+  TA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) fail("unsupported CUDA device ordinal %d", dev);
+  float *scratch;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+      void *sym = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&sym, g_splitk2_static);
+      if (e != cudaSuccess || !sym)
+        fail("cudaGetSymbolAddress for the static split-K2 scratch failed on device %d: %s", dev,
+             cudaGetErrorString(e));
+      g_static_ptr[dev] = static_cast<float *>(sym);
+    }
+    scratch = g_static_ptr[dev];
+  }
+  const uint32_t tile = (p.m >= 128 && p.n >= 128) ? 128 : 64;  // same stage-1 tile rule as the executor
+  launch_splitk2_stage1(p, tile, scratch, stream);
+  launch_splitk2_reduce(scratch, p.c, (uint64_t)p.m * p.n, (uint64_t)p.m * p.n, p.splits, stream);
 }
 
 }  // namespace ta

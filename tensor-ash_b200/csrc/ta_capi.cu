@@ -463,6 +463,28 @@ int ta_matmul_split_k2(const ta_executor *exec, const ta_matmul_call *calls, siz
   });
 }
 
+int ta_split_k2_noalloc(const float *a, const float *b, float *c, uint32_t m, uint32_t n, uint32_t k,
+                        uint32_t splits, float alpha, void *stream) {
+  return status_call([&]() {
+    if (!a || !b || !c) fail("ta_split_k2_noalloc: a, b and c must be device pointers (got null)");
+    if (!m || !n || !k) fail("ta_split_k2_noalloc: M, N, K must be non-zero (got %u, %u, %u)", m, n, k);
+    if (c == a || c == b) fail("ta_split_k2_noalloc: C must not alias an input");
+    if (splits < 2) fail("ta_split_k2_noalloc: splits must be at least 2 (got %u)", splits);
+    if (splits > k) fail("ta_split_k2_noalloc: num_k_splits %u exceeds K=%u", splits, k);
+    if (splits > 65535) fail("ta_split_k2_noalloc: num_k_splits %u exceeds the 65535 limit", splits);
+    if ((uint64_t)m * k > (1ull << 32) || (uint64_t)k * n > (1ull << 32))
+      fail("ta_split_k2_noalloc: operand exceeds 2^32 elements");
+    GemmParams p{};
+    p.a = a; p.b = b; p.c = c;
+    p.m = m; p.n = n; p.k = k; p.batch = 1;
+    p.alpha = alpha;
+    p.splits = splits;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    launch_splitk2_static(p, st);
+    TA_CUDA(cudaStreamSynchronize(st));
+  });
+}
+
 int ta_run_ops_ex(const ta_executor *exec, const ta_matmul_op_ex *ops, size_t n_ops,
                   uint32_t as_graph, ta_run_stats *stats) {
   return status_call([&]() {

@@ -376,6 +376,9 @@ void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n
 void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream);
 void launch_splitk2_reduce(const float *scratch, float *c, uint64_t total, uint64_t mn,
                            uint32_t splits, cudaStream_t stream);
+// Split-K2 on the module's fixed scratch array: no allocation of any kind.
+constexpr uint64_t SPLITK2_STATIC_MAX_FLOATS = 1ull << 20;  // 4 MiB
+void launch_splitk2_static(const GemmParams &p, cudaStream_t stream);
 
 void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t cols, float scale,
                          uint32_t mask_kind, uint32_t valid_or_prefix, uint32_t rows_per_group,
