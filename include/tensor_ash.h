@@ -257,6 +257,8 @@ enum {
   TA_STORE_ROPE_SCATTER = 3 /* rotate, then scatter */
 };
 
+typedef struct ta_pos_cell ta_pos_cell; /* 4-byte host-visible cell, see ta_pos_cell_create */
+
 typedef struct ta_store_desc {
   uint32_t kind;
   uint32_t head_dim;
@@ -266,6 +268,7 @@ typedef struct ta_store_desc {
   uint32_t stride_dim;  /* elements between lanes of a head in dst */
   const ta_tensor *table; /* rope (cos, sin) table [T_max, head_dim/2, 2]; kinds 1 and 3 */
   const ta_tensor *dst;   /* scatter destination (f32 or f16); kinds 2 and 3 */
+  const ta_pos_cell *pos_cell; /* optional: position = pos_base + *cell, read on the device at run time */
 } ta_store_desc;
 
 /* ta_matmul_op plus the fields the reference keeps Rust-only
@@ -334,7 +337,6 @@ int ta_flash_attention(const ta_executor *exec, const ta_tensor *q, const ta_ten
  * pos_cell, when non-NULL, overrides kv_len with (*cell + 1) read on the
  * device at run time and fixes the chunk count at TA_ATTN_DECODE_MAX_CHUNKS. */
 #define TA_ATTN_DECODE_MAX_CHUNKS 32u
-typedef struct ta_pos_cell ta_pos_cell;
 
 typedef struct ta_attn_decode_desc {
   uint32_t kv_heads;

@@ -17,6 +17,10 @@ from .api import (  # noqa: F401
     Executor,
     MatmulCall,
     MatmulOp,
+    MatmulOpEx,
+    MatmulStore,
+    PosCell,
+    StoreKind,
     PreparedOps,
     RunStats,
     Tensor,

@@ -207,6 +207,79 @@ class MatmulOp:
         return capi.MatmulOpC(self.call._c(), self.epilogue._c())
 
 
+class StoreKind(enum.IntEnum):
+    NONE = 0
+    ROPE = 1
+    SCATTER = 2
+    ROPE_SCATTER = 3
+
+
+class PosCell:
+    """4-byte host-visible cell read by kernels at run time (PosBuffer in the reference)."""
+
+    def __init__(self, ctx: Context):
+        h = lib().ta_pos_cell_create(ctx._h)
+        if not h:
+            raise TensorAshError(_err())
+        self._h = h
+        self.ctx = ctx
+
+    def set(self, value: int) -> None:
+        _check(lib().ta_pos_cell_set(self._h, value))
+
+    def get(self) -> int:
+        v = C.c_uint32(0)
+        _check(lib().ta_pos_cell_get(self._h, C.byref(v)))
+        return int(v.value)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().ta_pos_cell_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+@dataclass
+class MatmulStore:
+    """Fused store of an M == 1 f16-weight GEMV (MatmulStore / MatmulStoreDesc in the reference)."""
+    kind: StoreKind = StoreKind.NONE
+    head_dim: int = 0
+    pos_base: int = 0
+    pos_scale: int = 0
+    stride_head: int = 0
+    stride_dim: int = 0
+    table: Optional[Tensor] = None
+    dst: Optional[Tensor] = None
+    pos_cell: Optional[PosCell] = None
+
+    def _c(self) -> capi.StoreDescC:
+        return capi.StoreDescC(int(self.kind), self.head_dim, self.pos_base, self.pos_scale, self.stride_head,
+                               self.stride_dim, self.table._h if self.table is not None else None,
+                               self.dst._h if self.dst is not None else None,
+                               self.pos_cell._h if self.pos_cell is not None else None)
+
+
+@dataclass
+class MatmulOpEx:
+    """MatmulOp plus packed-B, normed-A and fused-store fields (with_packed_b /
+    with_normed_a / with_store_* in the reference, src/matmul/api.rs:120-306)."""
+    call: MatmulCall
+    epilogue: Epilogue = field(default_factory=Epilogue)
+    packed_b: bool = False
+    normed_a: Optional[tuple] = None      # (weight tensor, eps)
+    store: MatmulStore = field(default_factory=MatmulStore)
+
+    def _c(self) -> capi.MatmulOpExC:
+        w, eps = self.normed_a if self.normed_a is not None else (None, 0.0)
+        return capi.MatmulOpExC(capi.MatmulOpC(self.call._c(), self.epilogue._c()), int(self.packed_b),
+                                w._h if w is not None else None, eps, self.store._c())
+
+
 def _ops_array(ops: Sequence[MatmulOp]):
     arr = (capi.MatmulOpC * max(len(ops), 1))()
     for i, op in enumerate(ops):
@@ -300,6 +373,21 @@ class Executor:
     def run_op_graph(self, ops: Sequence[MatmulOp]) -> RunStats:
         st = capi.RunStatsC()
         _check(lib().ta_run_op_graph(self._h, _ops_array(ops), len(ops), C.byref(st)))
+        return RunStats._from(st)
+
+    def run_ops_ex(self, ops: Sequence["MatmulOpEx"], as_graph: bool = False) -> RunStats:
+        arr = (capi.MatmulOpExC * max(len(ops), 1))()
+        for i, op in enumerate(ops):
+            arr[i] = op._c()
+        st = capi.RunStatsC()
+        _check(lib().ta_run_ops_ex(self._h, arr, len(ops), int(as_graph), C.byref(st)))
+        return RunStats._from(st)
+
+    def swiglu_gemv(self, x: Tensor, wg: Tensor, wup: Tensor, out: Tensor, normed_weight: Optional[Tensor] = None,
+                    eps: float = 0.0) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_swiglu_gemv(self._h, x._h, wg._h, wup._h, out._h,
+                                    normed_weight._h if normed_weight is not None else None, eps, C.byref(st)))
         return RunStats._from(st)
 
     def run_matmuls_split_k2(self, calls: Sequence[MatmulCall], splits: int = 0) -> RunStats:

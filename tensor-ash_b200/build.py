@@ -25,6 +25,7 @@ SOURCES = [
     "ta_capi.cu",
     "k_gemm_ffma.cu",
     "k_gemm_tf32x3.cu",
+    "k_gemv.cu",
     "k_ops.cu",
 ]
 

@@ -53,7 +53,7 @@ class DispatchInfoC(C.Structure):
 class StoreDescC(C.Structure):
     _fields_ = [("kind", C.c_uint32), ("head_dim", C.c_uint32), ("pos_base", C.c_uint32),
                 ("pos_scale", C.c_uint32), ("stride_head", C.c_uint32), ("stride_dim", C.c_uint32),
-                ("table", C.c_void_p), ("dst", C.c_void_p)]
+                ("table", C.c_void_p), ("dst", C.c_void_p), ("pos_cell", C.c_void_p)]
 
 
 class MatmulOpExC(C.Structure):

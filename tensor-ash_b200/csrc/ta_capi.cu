@@ -33,8 +33,7 @@ struct ta_prepared {
   std::shared_ptr<Context> ctx;
 };
 struct ta_pos_cell {
-  std::shared_ptr<Context> ctx;
-  uint32_t *host = nullptr;  // pinned, mapped
+  PosCell cell;
 };
 
 namespace {
@@ -509,17 +508,28 @@ int ta_run_ops_ex(const ta_executor *exec, const ta_matmul_op_ex *ops, size_t n_
       op.store.stride_dim = s.stride_dim;
       if (s.table) op.store.table = &checked_tensor(e, s.table, label.c_str(), "store.table");
       if (s.dst) op.store.dst = &checked_tensor(e, s.dst, label.c_str(), "store.dst");
+      if (s.pos_cell) {
+        if (s.pos_cell->cell.ctx.get() != e.ctx.get())
+          fail("%s: store.pos_cell belongs to a different Vulkan context", label.c_str());
+        op.store.pos_cell = &s.pos_cell->cell;
+      }
       v.push_back(op);
     }
     write_stats(stats, as_graph ? e.exec->run_op_graph(v) : e.exec->run_ops(v));
   });
 }
 
-int ta_swiglu_gemv(const ta_executor *exec, const ta_tensor *, const ta_tensor *, const ta_tensor *,
-                   const ta_tensor *, const ta_tensor *, float, ta_run_stats *) {
+int ta_swiglu_gemv(const ta_executor *exec, const ta_tensor *x, const ta_tensor *wg, const ta_tensor *wup,
+                   const ta_tensor *out, const ta_tensor *normed_weight, float normed_eps,
+                   ta_run_stats *stats) {
   return status_call([&]() {
-    checked_ref(exec, "ta_swiglu_gemv: exec is null");
-    fail("ta_swiglu_gemv: the packed f16-weight GEMV kernels are not built yet");
+    const ta_executor &e = checked_ref(exec, "ta_swiglu_gemv: exec is null");
+    const Tensor &tx = checked_tensor(e, x, "ta_swiglu_gemv", "x");
+    const Tensor &tg = checked_tensor(e, wg, "ta_swiglu_gemv", "wg");
+    const Tensor &tu = checked_tensor(e, wup, "ta_swiglu_gemv", "wup");
+    const Tensor &to = checked_tensor(e, out, "ta_swiglu_gemv", "out");
+    const Tensor *tn = normed_weight ? &checked_tensor(e, normed_weight, "ta_swiglu_gemv", "normed_weight") : nullptr;
+    write_stats(stats, e.exec->swiglu_gemv(tx, tg, tu, to, tn, normed_eps));
   });
 }
 
@@ -583,36 +593,38 @@ ta_pos_cell *ta_pos_cell_create(const ta_context *ctx) {
     const ta_context &c = checked_ref(ctx, "ta_pos_cell_create: ctx is null");
     c.ctx->make_current();
     auto *h = new ta_pos_cell;
-    h->ctx = c.ctx;
-    const cudaError_t e = cudaHostAlloc((void **)&h->host, sizeof(uint32_t), cudaHostAllocMapped);
+    h->cell.ctx = c.ctx;
+    cudaError_t e = cudaHostAlloc((void **)&h->cell.host, sizeof(uint32_t), cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaHostGetDevicePointer((void **)&h->cell.device, h->cell.host, 0);
     if (e != cudaSuccess) {
+      if (h->cell.host) cudaFreeHost(h->cell.host);
       delete h;
       fail("ta_pos_cell_create: pinned allocation failed: %s", cudaGetErrorString(e));
     }
-    *h->host = 0;
+    *h->cell.host = 0;
     return h;
   });
 }
 void ta_pos_cell_destroy(ta_pos_cell *cell) {
   g_last_error.clear();
   if (!cell) return;
-  if (cell->host) {
-    cudaSetDevice(cell->ctx->device);
-    cudaFreeHost(cell->host);
+  if (cell->cell.host) {
+    cudaSetDevice(cell->cell.ctx->device);
+    cudaFreeHost(cell->cell.host);
   }
   delete cell;
 }
 int ta_pos_cell_set(ta_pos_cell *cell, uint32_t value) {
   return status_call([&]() {
     if (!cell) fail("ta_pos_cell_set: cell is null");
-    *(volatile uint32_t *)cell->host = value;
+    *(volatile uint32_t *)cell->cell.host = value;
   });
 }
 int ta_pos_cell_get(const ta_pos_cell *cell, uint32_t *value) {
   return status_call([&]() {
     if (!cell) fail("ta_pos_cell_get: cell is null");
     if (!value) fail("ta_pos_cell_get: value is null");
-    *value = *(volatile uint32_t *)cell->host;
+    *value = *(volatile uint32_t *)cell->cell.host;
   });
 }
 

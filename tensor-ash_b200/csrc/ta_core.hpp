@@ -122,7 +122,14 @@ struct Epilogue {
   }
 };
 
-struct PosCell;  // 4-byte pinned host cell, device-visible
+// 4-byte pinned, device-mapped host cell (PosBuffer / HostU32Buffer of
+// src/executor/cells.rs:51-201): kernels in replayed graphs read the token
+// position from it or write a result word into it.
+struct PosCell {
+  std::shared_ptr<Context> ctx;
+  uint32_t *host = nullptr;        // pinned host word
+  uint32_t *device = nullptr;      // the same word as seen from the device
+};
 
 struct MatmulStore {
   StoreKind kind = StoreKind::None;
@@ -256,6 +263,27 @@ struct GemmParams {
   uint32_t splits;
 };
 
+// Parameters of the f16-weight GEMV kernel (M <= 8 activation rows).
+struct GemvParams {
+  const float *x;          // [M, K] f32
+  const void *w;           // f16 weights, [K, N] or packed [N/tile][K][tile]
+  const void *w2;          // optional second matrix sharing x: out = silu(x@w) * (x@w2)
+  float *c;                // [M, N]
+  const float *bias, *d;   // epilogue operands (bias [N]; D [M, N])
+  const float *norm_w;     // fused RMSNorm weight [K] (nullptr = off)
+  float norm_eps;
+  uint32_t m, n, k;
+  float alpha, beta;
+  uint32_t accumulate, act, binary;
+  uint32_t packed, tile_n;
+  uint32_t ksplit, k_cta_max;   // filled by the launcher
+  // fused store (StoreKind): rope table, scatter destination, position cell
+  uint32_t store_kind, head_dim, pos_base, pos_scale, stride_head, stride_dim, dst_f16;
+  const float *table;
+  void *dst;
+  const uint32_t *pos_ptr;
+};
+
 struct Route {
   int kernel = -1;       // index into KERNEL_SPECS
   uint32_t splits = 0;   // >1: two-stage split-K route
@@ -302,6 +330,8 @@ class Executor {
   Route plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16,
                    bool allow_split_k2) const;
   Route plan_op(const MatmulOp &op, const ResolvedMatmul &r, bool allow_split_k2) const;
+  RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
+                       const Tensor *norm_w, float eps);
   void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
 
   // Model ops (src/executor/elementwise/ops.rs).
@@ -379,6 +409,9 @@ void launch_splitk2_reduce(const float *scratch, float *c, uint64_t total, uint6
 // Split-K2 on the module's fixed scratch array: no allocation of any kind.
 constexpr uint64_t SPLITK2_STATIC_MAX_FLOATS = 1ull << 20;  // 4 MiB
 void launch_splitk2_static(const GemmParams &p, cudaStream_t stream);
+
+bool gemv_f16w_supported(uint32_t m, uint32_t n, uint32_t k, bool packed, uint32_t tile_n);
+void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream);
 
 void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t cols, float scale,
                          uint32_t mask_kind, uint32_t valid_or_prefix, uint32_t rows_per_group,

@@ -296,6 +296,9 @@ int idx_of(const char *name) {
 // on the SIMT tiles, which launch faster and waste no tile area.
 int heuristic_kernel(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16, int sm_count) {
   if (b_f16) {
+    // decode shapes: the bandwidth GEMV (src/pipeline/mod.rs:330-347, routing.rs:27-33)
+    if (batch == 1 && m <= 8 && gemv_f16w_supported(m, n, k, false, 0))
+      return idx_of(f16w_row_uses_k16(k, n) ? "f16w_row_bda_k16" : "f16w_row_bda_k16_v2");
     return idx_of((m >= 128 && n >= 128) ? "f16w_ffma_m128n128" : "f16w_ffma_m64n64");
   }
   const bool tma_ok = (k % 4 == 0) && (n % 4 == 0);
@@ -356,7 +359,21 @@ Route Executor::plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, b
 Route Executor::plan_op(const MatmulOp &op, const ResolvedMatmul &r, bool allow_split_k2) const {
   const bool plain = op.epilogue.is_none() && !op.call.accumulate && !op.normed_weight &&
                      op.store.is_none() && !op.packed_b;
+  if (op.packed_b) {   // src/pipeline/routing.rs:35-41
+    Route route;
+    route.kernel = idx_of(f16w_row_tile_n(r.k, r.n) == 32 ? "f16w_row_bda_k16_packed"
+                                                           : "f16w_row_bda_k16_v2_packed");
+    return route;
+  }
   Route route = plan_shape(r.batch, r.m, r.n, r.k, r.b_f16, allow_split_k2 && plain);
+  if ((op.normed_weight || !op.store.is_none()) && KERNEL_SPECS[route.kernel].family != Family::RowGemv) {
+    // only the row kernels implement normed-A and the fused stores (src/executor/mod.rs:268-315)
+    if (!(r.b_f16 && r.batch == 1 && r.m <= 8 && gemv_f16w_supported(r.m, r.n, r.k, false, 0)))
+      fail("normed-A / fused-store ops need the f16-weight row-GEMV route (f16 B, M <= 8, N %% 8 == 0); "
+           "got M=%u N=%u f16_b=%d", r.m, r.n, (int)r.b_f16);
+    route.kernel = idx_of(f16w_row_uses_k16(r.k, r.n) ? "f16w_row_bda_k16" : "f16w_row_bda_k16_v2");
+    route.splits = 0;
+  }
   return route;
 }
 
@@ -386,10 +403,40 @@ GemmParams make_params(const MatmulOp &op, const ResolvedMatmul &r) {
 void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Route &route,
                           Slot &slot, cudaStream_t stream) {
   if (r.a_f16) fail("f16 A storage (a16 route) is not built in this library yet");
-  if (op.packed_b || op.normed_weight || !op.store.is_none())
-    fail("packed-B / normed-A / fused-store ops route to the row-GEMV kernels, which are not built yet");
-  GemmParams p = make_params(op, r);
   const KernelSpec &spec = KERNEL_SPECS[route.kernel];
+  if (spec.family == Family::RowGemv && r.b_f16) {
+    const uint32_t tile_n = op.packed_b ? f16w_row_tile_n(r.k, r.n) : 32;
+    if (!gemv_f16w_supported(r.m, r.n, r.k, op.packed_b, tile_n) || r.batch != 1)
+      fail("row-GEMV route cannot run M=%u N=%u K=%u batch=%u packed=%d", r.m, r.n, r.k, r.batch,
+           (int)op.packed_b);
+    if (op.epilogue.bias && op.epilogue.bias->shape.size() == 2 && r.batch == 1) { /* [1, N] is [N] */ }
+    GemvParams g{};
+    g.x = static_cast<const float *>(op.call.a->ptr());
+    g.w = op.call.b->ptr();
+    g.w2 = nullptr;
+    g.c = static_cast<float *>(op.call.c->ptr());
+    g.bias = op.epilogue.bias ? static_cast<const float *>(op.epilogue.bias->ptr()) : nullptr;
+    g.d = op.epilogue.d ? static_cast<const float *>(op.epilogue.d->ptr()) : nullptr;
+    g.norm_w = op.normed_weight ? static_cast<const float *>(op.normed_weight->ptr()) : nullptr;
+    g.norm_eps = op.normed_eps;
+    g.m = r.m; g.n = r.n; g.k = r.k;
+    g.alpha = op.call.alpha; g.beta = op.epilogue.beta;
+    g.accumulate = op.call.accumulate; g.act = (uint32_t)op.epilogue.activation;
+    g.binary = (uint32_t)op.epilogue.binary;
+    g.packed = op.packed_b; g.tile_n = tile_n;
+    g.store_kind = (uint32_t)op.store.kind;
+    g.head_dim = op.store.head_dim; g.pos_base = op.store.pos_base; g.pos_scale = op.store.pos_scale;
+    g.stride_head = op.store.stride_head; g.stride_dim = op.store.stride_dim;
+    g.table = op.store.table ? static_cast<const float *>(op.store.table->ptr()) : nullptr;
+    g.dst = op.store.dst ? op.store.dst->ptr() : nullptr;
+    g.dst_f16 = op.store.dst && op.store.dst->dtype == DType::F16;
+    g.pos_ptr = op.store.pos_cell ? op.store.pos_cell->device : nullptr;
+    launch_gemv_f16w(g, ctx_->sm_count, stream);
+    return;
+  }
+  if (op.packed_b || op.normed_weight || !op.store.is_none())
+    fail("packed-B / normed-A / fused-store ops need the f16-weight row-GEMV route");
+  GemmParams p = make_params(op, r);
   if (route.splits > 1) {
     p.splits = route.splits;
     float *scratch = static_cast<float *>(slot.scratch);
@@ -561,6 +608,41 @@ RunStats Executor::run_matmuls_split_k2(const std::vector<MatmulCall> &calls, ui
     // reduce finished, so one scratch region is reused safely.
     for (size_t i = 0; i < calls.size(); ++i) enqueue_op(ops[i], resolved[i], routes[i], slot, st);
   });
+}
+
+// Decode SwiGLU gate in one launch: out = silu(x' @ Wg) * (x' @ Wup), packed f16
+// weights sharing x (the reference's up GEMV + gate GEMV with a Mul epilogue,
+// tools/llama-ash/src/model/forward/mod.rs:194-206).
+RunStats Executor::swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
+                               const Tensor *norm_w, float eps) {
+  for (const Tensor *t : {&x, &wg, &wup, &out}) validate_tensor(*t, "swiglu_gemv operand");
+  if (x.dtype != DType::F32 || out.dtype != DType::F32) fail("swiglu_gemv: x and out must be f32 storage");
+  if (wg.dtype != DType::F16 || wup.dtype != DType::F16) fail("swiglu_gemv requires f16 weights");
+  if (wg.shape != wup.shape) fail("swiglu_gemv: gate shape %s != up shape %s", wg.shape_str().c_str(),
+                                  wup.shape_str().c_str());
+  MatmulCall call{&x, &wg, &out, 1.0f, false};
+  const ResolvedMatmul r = ResolvedMatmul::from_call(call);
+  if (r.batch != 1 || r.m > 8) fail("swiglu_gemv requires batch == 1 and M <= 8 (got M=%u, batch=%u)", r.m, r.batch);
+  if (r.n % 32) fail("packed-B GEMV requires N to be a multiple of 32 (got %u)", r.n);
+  if (norm_w) {
+    validate_tensor(*norm_w, "swiglu_gemv normed weight");
+    if (norm_w->dtype != DType::F32) fail("normed-A weight must be f32 storage");
+    if (norm_w->len() != r.k) fail("normed-A weight length %llu must equal K = %u", (unsigned long long)norm_w->len(), r.k);
+  }
+  GemvParams g{};
+  g.x = static_cast<const float *>(x.ptr());
+  g.w = wg.ptr();
+  g.w2 = wup.ptr();
+  g.c = static_cast<float *>(out.ptr());
+  g.norm_w = norm_w ? static_cast<const float *>(norm_w->ptr()) : nullptr;
+  g.norm_eps = eps;
+  g.m = r.m; g.n = r.n; g.k = r.k;
+  g.alpha = 1.0f;
+  g.packed = 1; g.tile_n = f16w_row_tile_n(r.k, r.n);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard guard(*this, slot);
+  return timed(slot, 1, 2 * r.total_flops, [&](cudaStream_t s) { launch_gemv_f16w(g, ctx_->sm_count, s); });
 }
 
 // ------------------------------------------------------------------ measured tuner
