@@ -313,18 +313,17 @@ ta_tensor *ta_tensor_alias_with_shape(const ta_tensor *tensor, const uint32_t *s
 
 /* Causal prefill flash attention (ref src/executor/elementwise/flash.rs:26-253,
  * FlashAttentionDesc ref src/executor/elementwise/mod.rs:162-184).
- * kt [H_kv, dh, T_max], v [H_kv, T_max, dh] (f32 or f16, same dtype);
- * q/out [H, T_q, dh], or token-major [T_q, H*dh] when token_major != 0.
- * Row i attends positions < min(kv_len, pos_base + i + 1). */
+ * kt [H_kv, dh, T_max], v [H_kv, T_max, dh] (f32 or f16, same dtype), dh 64 or
+ * 128; q/out f32, head-major [H, T_q, dh] or token-major [T_q, H*dh]; heads, T_q
+ * and dh come from the tensor shapes, H must be a multiple of H_kv.
+ * Row i attends positions < min(kv_len, pos_base + i + 1); a row that sees no
+ * position is left untouched. */
 typedef struct ta_flash_desc {
-  uint32_t heads;
-  uint32_t kv_heads;
-  uint32_t head_dim; /* 64 or 128 */
-  uint32_t t_q;
-  uint32_t kv_len;
-  uint32_t pos_base;
-  float scale;
-  uint32_t token_major;
+  uint32_t kv_len;               /* valid K/V positions in the caches, <= T_max */
+  uint32_t pos_base;             /* absolute position of query row 0 */
+  float scale;                   /* 1/sqrt(dh) for standard attention */
+  uint32_t token_major_heads;    /* 0: q is [H, T_q, dh]; H > 0: q is token-major [T_q, H*dh] */
+  uint32_t out_token_major_heads;/* 0: out follows q; H > 0: out is [T_q, H*dh] whatever q is */
 } ta_flash_desc;
 
 int ta_flash_attention(const ta_executor *exec, const ta_tensor *q, const ta_tensor *kt,
@@ -333,18 +332,16 @@ int ta_flash_attention(const ta_executor *exec, const ta_tensor *q, const ta_ten
 
 /* Split-K decode attention, two launches (ref src/executor/elementwise/attn.rs:27-185,
  * AttnDecodeDesc ref src/executor/elementwise/mod.rs:202-237).  q/out
- * [H_kv, group, dh] f32; scratch >= kv_heads * chunks * group * (dh + 2) f32.
- * pos_cell, when non-NULL, overrides kv_len with (*cell + 1) read on the
- * device at run time and fixes the chunk count at TA_ATTN_DECODE_MAX_CHUNKS. */
+ * [H_kv, group, dh] f32 (dh = 64, group <= 8, both from the shapes); kt/v as for
+ * ta_flash_attention; scratch f32 with at least kv_heads * chunks * group *
+ * (dh + 2) elements, chunks = ta_attn_decode_num_chunks(kv_len), or
+ * TA_ATTN_DECODE_MAX_CHUNKS with a pos_cell. */
 #define TA_ATTN_DECODE_MAX_CHUNKS 32u
 
 typedef struct ta_attn_decode_desc {
-  uint32_t kv_heads;
-  uint32_t group; /* Q heads per KV head, <= 8 */
-  uint32_t head_dim; /* 64 */
-  uint32_t kv_len;
+  uint32_t kv_len;  /* valid positions, 1..T_max; with pos_cell: kv_len + *cell (record kv_len = 1) */
   float scale;
-  const ta_pos_cell *pos_cell;
+  const ta_pos_cell *pos_cell; /* optional; fixes the chunk grid at TA_ATTN_DECODE_MAX_CHUNKS */
 } ta_attn_decode_desc;
 
 uint32_t ta_attn_decode_num_chunks(uint32_t kv_len);

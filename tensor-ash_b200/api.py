@@ -390,6 +390,20 @@ class Executor:
                                     normed_weight._h if normed_weight is not None else None, eps, C.byref(st)))
         return RunStats._from(st)
 
+    def run_flash_attention(self, q: Tensor, kt: Tensor, v: Tensor, out: Tensor, kv_len: int, pos_base: int,
+                            scale: float, token_major_heads: int = 0, out_token_major_heads: int = 0) -> RunStats:
+        st = capi.RunStatsC()
+        desc = capi.FlashDescC(kv_len, pos_base, scale, token_major_heads, out_token_major_heads)
+        _check(lib().ta_flash_attention(self._h, q._h, kt._h, v._h, out._h, C.byref(desc), C.byref(st)))
+        return RunStats._from(st)
+
+    def run_attn_decode(self, q: Tensor, kt: Tensor, v: Tensor, scratch: Tensor, out: Tensor, kv_len: int,
+                        scale: float, pos_cell: Optional["PosCell"] = None) -> RunStats:
+        st = capi.RunStatsC()
+        desc = capi.AttnDecodeDescC(kv_len, scale, pos_cell._h if pos_cell is not None else None)
+        _check(lib().ta_attn_decode(self._h, q._h, kt._h, v._h, scratch._h, out._h, C.byref(desc), C.byref(st)))
+        return RunStats._from(st)
+
     def run_matmuls_split_k2(self, calls: Sequence[MatmulCall], splits: int = 0) -> RunStats:
         arr = (capi.MatmulCallC * max(len(calls), 1))()
         for i, c in enumerate(calls):

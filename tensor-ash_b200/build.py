@@ -26,6 +26,7 @@ SOURCES = [
     "k_gemm_ffma.cu",
     "k_gemm_tf32x3.cu",
     "k_gemv.cu",
+    "k_attention.cu",
     "k_ops.cu",
 ]
 

@@ -62,14 +62,12 @@ class MatmulOpExC(C.Structure):
 
 
 class FlashDescC(C.Structure):
-    _fields_ = [("heads", C.c_uint32), ("kv_heads", C.c_uint32), ("head_dim", C.c_uint32),
-                ("t_q", C.c_uint32), ("kv_len", C.c_uint32), ("pos_base", C.c_uint32),
-                ("scale", C.c_float), ("token_major", C.c_uint32)]
+    _fields_ = [("kv_len", C.c_uint32), ("pos_base", C.c_uint32), ("scale", C.c_float),
+                ("token_major_heads", C.c_uint32), ("out_token_major_heads", C.c_uint32)]
 
 
 class AttnDecodeDescC(C.Structure):
-    _fields_ = [("kv_heads", C.c_uint32), ("group", C.c_uint32), ("head_dim", C.c_uint32),
-                ("kv_len", C.c_uint32), ("scale", C.c_float), ("pos_cell", C.c_void_p)]
+    _fields_ = [("kv_len", C.c_uint32), ("scale", C.c_float), ("pos_cell", C.c_void_p)]
 
 
 _P = C.c_void_p

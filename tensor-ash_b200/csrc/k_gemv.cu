@@ -33,11 +33,13 @@ namespace {
 
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int GEMV_UNROLL = 4;   // 16-byte loads in flight per lane
 
 template <int MROWS, int TN>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_f16w_kernel(const GemvParams p) {
+  // 16-byte loads in flight per lane: deep for few rows (pure latency hiding),
+  // shallower where the accumulators need the registers
+  constexpr int GEMV_UNROLL = MROWS <= 2 ? 8 : 4;
   constexpr int LPR = TN / 8;          // lanes per weight row (8 f16 per lane)
   constexpr int RPL = 32 / LPR;        // weight rows per warp-wide load
   extern __shared__ __align__(16) uint8_t gemv_smem[];
@@ -127,9 +129,22 @@ gemv_f16w_kernel(const GemvParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) w[j] = __half22float2(h[j]);
         const float *xr = xs + (size_t)(k - k_lo) * MROWS;
+        float xm[MROWS];
+        if constexpr (MROWS >= 4) {
+#pragma unroll
+          for (int m4 = 0; m4 < MROWS / 4; ++m4) {
+            const float4 t = reinterpret_cast<const float4 *>(xr)[m4];
+            xm[4 * m4] = t.x; xm[4 * m4 + 1] = t.y; xm[4 * m4 + 2] = t.z; xm[4 * m4 + 3] = t.w;
+          }
+        } else if constexpr (MROWS == 2) {
+          const float2 t = *reinterpret_cast<const float2 *>(xr);
+          xm[0] = t.x; xm[1] = t.y;
+        } else {
+          xm[0] = xr[0];
+        }
 #pragma unroll
         for (int m = 0; m < MROWS; ++m) {
-          const float xv = xr[m];
+          const float xv = xm[m];
           const float2 x2 = make_float2(xv, xv);
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[m][j] = __ffma2_rn(x2, w[j], acc[m][j]);
@@ -259,9 +274,10 @@ void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream) {
   const uint32_t tn = p.packed ? p.tile_n : 32;
   const uint32_t tiles = (p.n + tn - 1) / tn;
   const int mrows = p.m <= 1 ? 1 : p.m <= 2 ? 2 : p.m <= 4 ? 4 : 8;
-  // K split over a cluster: fill the machine (two CTAs per SM fit), keep every
+  // K split over a cluster: fill the machine, keep every
   // CTA's x slice inside shared memory, never split below 256 rows.
-  const uint64_t slots = 2ull * (uint64_t)sm_count;
+  const uint64_t per_sm = mrows == 1 ? 5 : mrows == 2 ? 4 : mrows == 4 ? 3 : 2;   // resident CTAs (registers)
+  const uint64_t slots = per_sm * (uint64_t)sm_count;
   uint32_t best_s = 0;
   double best_eff = -1.0;
   for (uint32_t s : {1u, 2u, 4u, 8u}) {

@@ -565,26 +565,39 @@ ta_tensor *ta_tensor_alias_with_shape(const ta_tensor *tensor, const uint32_t *s
   });
 }
 
-int ta_flash_attention(const ta_executor *exec, const ta_tensor *, const ta_tensor *,
-                       const ta_tensor *, const ta_tensor *, const ta_flash_desc *, ta_run_stats *) {
+int ta_flash_attention(const ta_executor *exec, const ta_tensor *q, const ta_tensor *kt, const ta_tensor *v,
+                       const ta_tensor *out, const ta_flash_desc *desc, ta_run_stats *stats) {
   return status_call([&]() {
-    checked_ref(exec, "ta_flash_attention: exec is null");
-    fail("ta_flash_attention: the flash-attention kernel is not built yet");
+    const ta_executor &e = checked_ref(exec, "ta_flash_attention: exec is null");
+    const Tensor &tq = checked_tensor(e, q, "ta_flash_attention", "q");
+    const Tensor &tk = checked_tensor(e, kt, "ta_flash_attention", "kt");
+    const Tensor &tv = checked_tensor(e, v, "ta_flash_attention", "v");
+    const Tensor &to = checked_tensor(e, out, "ta_flash_attention", "out");
+    const ta_flash_desc &d = checked_ref(desc, "ta_flash_attention: desc is null");
+    FlashAttentionDesc fd;
+    fd.kv_len = d.kv_len; fd.pos_base = d.pos_base; fd.scale = d.scale;
+    fd.token_major_heads = d.token_major_heads; fd.out_token_major_heads = d.out_token_major_heads;
+    write_stats(stats, e.exec->flash_attention(tq, tk, tv, to, fd));
   });
 }
 
-uint32_t ta_attn_decode_num_chunks(uint32_t kv_len) {
-  // clamp(ceil(kv_len / 32), 8, 32)  (src/executor/elementwise/mod.rs:235-237)
-  const uint32_t c = (kv_len + 31) / 32;
-  return c < 8 ? 8 : (c > TA_ATTN_DECODE_MAX_CHUNKS ? TA_ATTN_DECODE_MAX_CHUNKS : c);
-}
+uint32_t ta_attn_decode_num_chunks(uint32_t kv_len) { return attn_decode_num_chunks(kv_len); }
 
-int ta_attn_decode(const ta_executor *exec, const ta_tensor *, const ta_tensor *, const ta_tensor *,
-                   const ta_tensor *, const ta_tensor *, const ta_attn_decode_desc *,
-                   ta_run_stats *) {
+int ta_attn_decode(const ta_executor *exec, const ta_tensor *q, const ta_tensor *kt, const ta_tensor *v,
+                   const ta_tensor *scratch, const ta_tensor *out, const ta_attn_decode_desc *desc,
+                   ta_run_stats *stats) {
   return status_call([&]() {
-    checked_ref(exec, "ta_attn_decode: exec is null");
-    fail("ta_attn_decode: the decode-attention kernels are not built yet");
+    const ta_executor &e = checked_ref(exec, "ta_attn_decode: exec is null");
+    const Tensor &tq = checked_tensor(e, q, "ta_attn_decode", "q");
+    const Tensor &tk = checked_tensor(e, kt, "ta_attn_decode", "kt");
+    const Tensor &tv = checked_tensor(e, v, "ta_attn_decode", "v");
+    const Tensor &ts = checked_tensor(e, scratch, "ta_attn_decode", "scratch");
+    const Tensor &to = checked_tensor(e, out, "ta_attn_decode", "out");
+    const ta_attn_decode_desc &d = checked_ref(desc, "ta_attn_decode: desc is null");
+    AttnDecodeDesc ad;
+    ad.kv_len = d.kv_len; ad.scale = d.scale;
+    ad.pos_cell = d.pos_cell ? &d.pos_cell->cell : nullptr;
+    write_stats(stats, e.exec->attn_decode(tq, tk, tv, ts, to, ad));
   });
 }
 

@@ -284,6 +284,44 @@ struct GemvParams {
   const uint32_t *pos_ptr;
 };
 
+struct FlashParams {
+  const float *q;
+  const void *kt, *v;
+  float *out;
+  uint32_t heads, group, dh, t_q, t_max, kv_len, pos_base;
+  float scale;
+  uint32_t q_head_stride, q_row_stride, o_head_stride, o_row_stride;
+  uint32_t kv_f16;
+};
+
+struct AttnDecodeParams {
+  const float *q;
+  const void *kt, *v;
+  float *scratch, *out;
+  uint32_t kv_heads, group, t_max, kv_len, num_chunks;
+  float scale;
+  uint32_t kv_f16;
+  const uint32_t *pos_ptr;
+};
+
+struct FlashAttentionDesc {
+  uint32_t kv_len = 0, pos_base = 0;
+  float scale = 1.0f;
+  uint32_t token_major_heads = 0, out_token_major_heads = 0;
+};
+
+struct AttnDecodeDesc {
+  uint32_t kv_len = 0;
+  float scale = 1.0f;
+  const PosCell *pos_cell = nullptr;
+};
+
+constexpr uint32_t ATTN_DECODE_MAX_CHUNKS = 32;
+inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
+  const uint32_t c = (kv_len + 31) / 32;
+  return c < 8 ? 8 : (c > ATTN_DECODE_MAX_CHUNKS ? ATTN_DECODE_MAX_CHUNKS : c);
+}
+
 struct Route {
   int kernel = -1;       // index into KERNEL_SPECS
   uint32_t splits = 0;   // >1: two-stage split-K route
@@ -330,6 +368,15 @@ class Executor {
   Route plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16,
                    bool allow_split_k2) const;
   Route plan_op(const MatmulOp &op, const ResolvedMatmul &r, bool allow_split_k2) const;
+  // Fused attention (src/executor/elementwise/flash.rs:26-253, attn.rs:27-185).
+  FlashParams plan_flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &out,
+                                   const FlashAttentionDesc &desc) const;
+  RunStats flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &out,
+                           const FlashAttentionDesc &desc);
+  AttnDecodeParams plan_attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v,
+                                    const Tensor &scratch, const Tensor &out, const AttnDecodeDesc &desc) const;
+  RunStats attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &scratch,
+                       const Tensor &out, const AttnDecodeDesc &desc);
   RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
                        const Tensor *norm_w, float eps);
   void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
@@ -412,6 +459,9 @@ void launch_splitk2_static(const GemmParams &p, cudaStream_t stream);
 
 bool gemv_f16w_supported(uint32_t m, uint32_t n, uint32_t k, bool packed, uint32_t tile_n);
 void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream);
+
+void launch_flash_prefill(const FlashParams &p, cudaStream_t stream);
+void launch_attn_decode(const AttnDecodeParams &p, cudaStream_t stream);
 
 void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t cols, float scale,
                          uint32_t mask_kind, uint32_t valid_or_prefix, uint32_t rows_per_group,

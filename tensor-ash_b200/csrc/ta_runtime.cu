@@ -855,6 +855,136 @@ RunStats Executor::copy_strided(const Tensor &src, const Tensor &dst, const uint
   });
 }
 
+// ------------------------------------------------------------------ fused attention
+FlashParams Executor::plan_flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v,
+                                           const Tensor &out, const FlashAttentionDesc &desc) const {
+  ensure_f32(*this, q, "run_flash_attention", "q");
+  ensure_f32(*this, out, "run_flash_attention", "out");
+  validate_tensor(kt, "kt");
+  validate_tensor(v, "v");
+  if (kt.dtype != v.dtype)
+    fail("run_flash_attention: kt (%s) and v (%s) must share a storage type", dtype_name(kt.dtype),
+         dtype_name(v.dtype));
+  if (kt.shape.size() != 3) fail("run_flash_attention: kt must be [H_kv, dh, T_max], got %s", kt.shape_str().c_str());
+  if (v.shape.size() != 3) fail("run_flash_attention: v must be [H_kv, T_max, dh], got %s", v.shape_str().c_str());
+  const uint32_t kv_heads = kt.shape[0], dh = kt.shape[1], t_max = kt.shape[2];
+  if (v.shape[1] != t_max || v.shape[0] != kv_heads || v.shape[2] != dh)
+    fail("run_flash_attention: inconsistent cache shapes kt %s, v %s", kt.shape_str().c_str(), v.shape_str().c_str());
+  FlashParams p{};
+  uint32_t heads, t_q;
+  if (desc.token_major_heads) {
+    heads = desc.token_major_heads;
+    t_q = q.shape[0];
+    if (q.len() != (uint64_t)t_q * heads * dh)
+      fail("run_flash_attention: token-major q %s does not hold [T=%u, H=%u, dh=%u]", q.shape_str().c_str(), t_q, heads, dh);
+    p.q_head_stride = dh;
+    p.q_row_stride = heads * dh;
+  } else {
+    if (q.shape.size() != 3) fail("run_flash_attention: q must be [H, T_q, dh], got %s", q.shape_str().c_str());
+    heads = q.shape[0];
+    t_q = q.shape[1];
+    if (q.shape[2] != dh)
+      fail("run_flash_attention: q dh %u != cache dh %u (q %s, kt %s)", q.shape[2], dh, q.shape_str().c_str(),
+           kt.shape_str().c_str());
+    p.q_head_stride = t_q * dh;
+    p.q_row_stride = dh;
+  }
+  if (desc.out_token_major_heads) {
+    if (desc.out_token_major_heads != heads)
+      fail("run_flash_attention: out_token_major_heads %u != q heads %u", desc.out_token_major_heads, heads);
+    if (out.len() != (uint64_t)t_q * heads * dh)
+      fail("run_flash_attention: token-major out %s does not hold [T=%u, H=%u, dh=%u]", out.shape_str().c_str(), t_q, heads, dh);
+    p.o_head_stride = dh;
+    p.o_row_stride = heads * dh;
+  } else if (desc.token_major_heads) {
+    if (out.len() != q.len())
+      fail("run_flash_attention: out shape %s must match token-major q %s", out.shape_str().c_str(), q.shape_str().c_str());
+    p.o_head_stride = p.q_head_stride;
+    p.o_row_stride = p.q_row_stride;
+  } else {
+    if (out.shape != q.shape)
+      fail("run_flash_attention: out shape %s must equal q shape %s", out.shape_str().c_str(), q.shape_str().c_str());
+    p.o_head_stride = p.q_head_stride;
+    p.o_row_stride = p.q_row_stride;
+  }
+  if (kv_heads == 0 || heads % kv_heads) fail("run_flash_attention: H=%u must be a multiple of H_kv=%u", heads, kv_heads);
+  if (desc.kv_len > t_max) fail("run_flash_attention: kv_len %u exceeds cache T_max %u", desc.kv_len, t_max);
+  if (dh != 64 && dh != 128) fail("run_flash_attention: head dimension %u unsupported (64 or 128)", dh);
+  if (q.ptr() == out.ptr()) fail("run_flash_attention: q and out must be different tensors");
+  p.q = static_cast<const float *>(q.ptr());
+  p.kt = kt.ptr();
+  p.v = v.ptr();
+  p.out = static_cast<float *>(out.ptr());
+  p.heads = heads; p.group = heads / kv_heads; p.dh = dh; p.t_q = t_q; p.t_max = t_max;
+  p.kv_len = desc.kv_len; p.pos_base = desc.pos_base; p.scale = desc.scale;
+  p.kv_f16 = kt.dtype == DType::F16;
+  return p;
+}
+
+RunStats Executor::flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &out,
+                                   const FlashAttentionDesc &desc) {
+  const FlashParams p = plan_flash_attention(q, kt, v, out, desc);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, 1, 0, [&](cudaStream_t s) { launch_flash_prefill(p, s); });
+}
+
+AttnDecodeParams Executor::plan_attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v,
+                                            const Tensor &scratch, const Tensor &out,
+                                            const AttnDecodeDesc &desc) const {
+  ensure_f32(*this, q, "run_attn_decode", "q");
+  validate_tensor(kt, "kt");
+  validate_tensor(v, "v");
+  ensure_f32(*this, scratch, "run_attn_decode", "scratch");
+  ensure_f32(*this, out, "run_attn_decode", "out");
+  if (kt.dtype != v.dtype)
+    fail("run_attn_decode: kt (%s) and v (%s) must share a storage type", dtype_name(kt.dtype), dtype_name(v.dtype));
+  if (kt.shape.size() != 3) fail("run_attn_decode: kt must be [H_kv, dh, T_max], got %s", kt.shape_str().c_str());
+  if (v.shape.size() != 3) fail("run_attn_decode: v must be [H_kv, T_max, dh], got %s", v.shape_str().c_str());
+  const uint32_t kv_heads = kt.shape[0], dh = kt.shape[1], t_max = kt.shape[2];
+  if (v.shape[2] != dh || v.shape[1] != t_max || v.shape[0] != kv_heads)
+    fail("run_attn_decode: inconsistent caches kt %s, v %s", kt.shape_str().c_str(), v.shape_str().c_str());
+  if (dh != 64) fail("run_attn_decode: head dimension %u unsupported (compiled variant: 64)", dh);
+  const uint64_t heads_elems = (uint64_t)kv_heads * dh;
+  if (q.len() % heads_elems)
+    fail("run_attn_decode: q length %llu must be kv_heads*group*dh (kv_heads %u, dh %u)",
+         (unsigned long long)q.len(), kv_heads, dh);
+  const uint64_t group = q.len() / heads_elems;
+  if (group == 0 || group > 8) fail("run_attn_decode: GQA group %llu unsupported (1..=8)", (unsigned long long)group);
+  if (out.len() != q.len())
+    fail("run_attn_decode: out length %llu must equal q length %llu", (unsigned long long)out.len(),
+         (unsigned long long)q.len());
+  if (desc.kv_len == 0 || desc.kv_len > t_max) fail("run_attn_decode: kv_len %u out of range 1..=%u", desc.kv_len, t_max);
+  if (desc.pos_cell && desc.pos_cell->ctx.get() != ctx_.get())
+    fail("run_attn_decode: pos cell belongs to a different context");
+  const uint32_t num_chunks = desc.pos_cell ? ATTN_DECODE_MAX_CHUNKS : attn_decode_num_chunks(desc.kv_len);
+  const uint64_t needed = (uint64_t)kv_heads * num_chunks * group * (dh + 2);
+  if (scratch.len() < needed)
+    fail("run_attn_decode: scratch length %llu < required %llu (kv_heads %u * chunks %u * group %llu * (dh+2))",
+         (unsigned long long)scratch.len(), (unsigned long long)needed, kv_heads, num_chunks,
+         (unsigned long long)group);
+  AttnDecodeParams p{};
+  p.q = static_cast<const float *>(q.ptr());
+  p.kt = kt.ptr();
+  p.v = v.ptr();
+  p.scratch = static_cast<float *>(scratch.ptr());
+  p.out = static_cast<float *>(out.ptr());
+  p.kv_heads = kv_heads; p.group = (uint32_t)group; p.t_max = t_max; p.kv_len = desc.kv_len;
+  p.num_chunks = num_chunks; p.scale = desc.scale; p.kv_f16 = kt.dtype == DType::F16;
+  p.pos_ptr = desc.pos_cell ? desc.pos_cell->device : nullptr;
+  return p;
+}
+
+RunStats Executor::attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &scratch,
+                               const Tensor &out, const AttnDecodeDesc &desc) {
+  const AttnDecodeParams p = plan_attn_decode(q, kt, v, scratch, out, desc);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, 2, 0, [&](cudaStream_t s) { launch_attn_decode(p, s); });
+}
+
 // ------------------------------------------------------------------ prepared replay
 // (src/executor/prepared.rs:78-155): data-parallel routes only; recorded once
 // into a CUDA graph on a private stream; one submission in flight per handle.
