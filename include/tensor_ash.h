@@ -356,6 +356,58 @@ void ta_pos_cell_destroy(ta_pos_cell *cell);
 int ta_pos_cell_set(ta_pos_cell *cell, uint32_t value);
 int ta_pos_cell_get(const ta_pos_cell *cell, uint32_t *value);
 
+/* Token-id list in host-visible memory, read by gather kernels on the device
+ * (ref src/executor/cells.rs:140-201, TokenIdBuffer). */
+typedef struct ta_token_ids ta_token_ids;
+ta_token_ids *ta_token_ids_create(const ta_context *ctx, uint32_t capacity);
+void ta_token_ids_destroy(ta_token_ids *ids);
+int ta_token_ids_set(ta_token_ids *ids, const uint32_t *tokens, uint32_t n); /* n <= capacity */
+
+/* Mixed op graphs: matmuls and model ops in one submission or one prepared
+ * replay (ref src/executor/graph_ops.rs:27-161 ExecOp, :249-353 run_exec_ops /
+ * prepare_exec_ops).  Later ops may read what earlier ops wrote.  Operand slots
+ * by kind (unused slots stay zero):
+ *   MATMUL            mm
+ *   RMS_NORM          in0 input, in1 weight, out; f0 = eps
+ *   LAYER_NORM        in0 input, in1 weight, in2 bias, out; f0 = eps
+ *   SOFTMAX_ROWS      in0 input, out; f0 = scale; u0 mask kind, u1 valid/prefix, u2 rows per group
+ *   ROPE              in0 input, in1 table, out; rope
+ *   ROPE_SCATTER      in0 input, in1 table, out = dst (f32/f16); rope; dst_offset, dst_strides
+ *                     per (token, head, dim), pos_scale; cell = position added to
+ *                     rope.pos_base and (times pos_scale) to dst_offset
+ *   COPY_STRIDED      in0 src, out dst (any f32/f16 pairing); copy
+ *   BINARY            in0 a, in1 b, out; u0 = 0: a + f0*b, 1: silu(a)*b
+ *   ATTN_DECODE       in0 q, in1 kt, in2 v, in3 scratch, out; attn
+ *   FLASH_ATTN        in0 q, in1 kt, in2 v, out; flash
+ *   ARGMAX            in0 input; cell receives the index (ties keep the largest index)
+ *   EMBED_GATHER      cell = token id word; in0 table [vocab, embd] (f32/f16), out [embd]
+ *   EMBED_GATHER_ROWS tokens; in0 table, out [n, embd] */
+enum {
+  TA_EXEC_MATMUL = 0, TA_EXEC_RMS_NORM, TA_EXEC_LAYER_NORM, TA_EXEC_SOFTMAX_ROWS, TA_EXEC_ROPE,
+  TA_EXEC_ROPE_SCATTER, TA_EXEC_COPY_STRIDED, TA_EXEC_BINARY, TA_EXEC_ATTN_DECODE, TA_EXEC_FLASH_ATTN,
+  TA_EXEC_ARGMAX, TA_EXEC_EMBED_GATHER, TA_EXEC_EMBED_GATHER_ROWS
+};
+
+typedef struct ta_exec_op {
+  uint32_t kind;
+  ta_matmul_op_ex mm;
+  const ta_tensor *in0, *in1, *in2, *in3, *out;
+  float f0;
+  uint32_t u0, u1, u2;
+  ta_rope_desc rope;
+  ta_copy_desc copy;
+  uint32_t dst_offset, dst_strides[3], pos_scale;
+  ta_flash_desc flash;
+  ta_attn_decode_desc attn;
+  const ta_pos_cell *cell;
+  const ta_token_ids *tokens;
+} ta_exec_op;
+
+int ta_run_exec_ops(const ta_executor *exec, const ta_exec_op *ops, size_t n_ops, ta_run_stats *stats);
+/* Prepared replay of a mixed graph; the handle works with ta_prepared_run /
+ * _submit / _wait / _destroy and carries the same lifetime contract. */
+ta_prepared *ta_prepared_create_exec(const ta_executor *exec, const ta_exec_op *ops, size_t n_ops);
+
 /* Registry and routing introspection (ref src/pipeline/catalog.rs:10-41,129-376).
  * Host-only. */
 size_t ta_kernel_spec_count(void);

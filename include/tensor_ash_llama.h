@@ -1,0 +1,74 @@
+/*
+ * tensor_ash_llama.h -- llama-architecture runner built only on library ops.
+ *
+ * Counterpart of the reference's tools/llama-ash (model/mod.rs:59-190,
+ * model/forward/{mod,prefill,decode}.rs): the same op graphs -- prefill through
+ * one mixed graph with fused causal attention, greedy decode through one
+ * prepared (record-once, replay-many) graph whose position comes from a 4-byte
+ * cell and whose next token is chosen and embedded on the device.  The GGUF
+ * loader is not part of this build; weights are random-initialised from a seed
+ * (the benchmark configuration is random-init).
+ */
+#ifndef TENSOR_ASH_LLAMA_H
+#define TENSOR_ASH_LLAMA_H
+
+#include "tensor_ash.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ta_llama ta_llama;
+
+typedef struct ta_llama_config {
+  uint32_t layers;    /* 22 */
+  uint32_t embd;      /* 2048 */
+  uint32_t heads;     /* 32 */
+  uint32_t kv_heads;  /* 4 */
+  uint32_t head_dim;  /* 64 (heads * head_dim == embd) */
+  uint32_t ffn;       /* 5632 */
+  uint32_t vocab;     /* 32000 */
+  uint32_t t_max;     /* KV-cache capacity in positions */
+  float rms_eps;      /* 1e-5 */
+  float rope_theta;   /* 1e4 */
+  float weight_sigma; /* weights ~ N(0, sigma), rounded to f16; 0.02 */
+  float norm_jitter;  /* norm weights = 1 + jitter * u, u uniform [-1,1); 0 gives all ones */
+  uint64_t seed;
+} ta_llama_config;
+
+/* Weight tensors are generated on the host in chunks of 2^20 elements; chunk c
+ * of tensor id t uses the documented LCG + Box-Muller stream with seed
+ * (seed * 1000003 + t) * 4096 + c, so a checker can rebuild any tensor.
+ * Tensor ids: 0 token embedding [vocab, embd]; 1 output norm; 2 lm_head
+ * [embd, vocab]; per layer L (base = 16 + 16*L): +0 attn_norm, +1 wq, +2 wk,
+ * +3 wv, +4 wo, +5 ffn_norm, +6 w_gate, +7 w_up, +8 w_down (all [n_in, n_out]). */
+ta_llama *ta_llama_create_random(const ta_executor *exec, const ta_llama_config *cfg);
+void ta_llama_destroy(ta_llama *model);
+
+/* Forget the KV cache: the next prefill starts at position 0. */
+int ta_llama_reset(ta_llama *model);
+
+/* Prefill n prompt tokens at the current position (one graph submission);
+ * *next_token receives the greedy next token. */
+int ta_llama_prefill(ta_llama *model, const uint32_t *tokens, uint32_t n, uint32_t *next_token,
+                     ta_run_stats *stats);
+
+/* Greedy decode of n tokens starting from `first_token` (normally the token the
+ * prefill returned): each step is one replay of the prepared decode graph, one
+ * 4-byte position write and one 4-byte token read.  out_tokens[i] is the token
+ * chosen after consuming step i's input.  stats sums the device time. */
+int ta_llama_decode(ta_llama *model, uint32_t first_token, uint32_t n, uint32_t *out_tokens,
+                    ta_run_stats *stats);
+
+/* Logits of the most recent step ([vocab] floats), for margin checks. */
+int ta_llama_logits(ta_llama *model, float *out, size_t len);
+
+/* Current position (tokens in the KV cache) and weight bytes read per decoded token. */
+uint32_t ta_llama_position(const ta_llama *model);
+uint64_t ta_llama_weight_bytes_per_token(const ta_llama *model);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TENSOR_ASH_LLAMA_H */

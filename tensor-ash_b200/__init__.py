@@ -14,7 +14,10 @@ from .api import (  # noqa: F401
     Context,
     DispatchInfo,
     Epilogue,
+    ExecKind,
+    ExecOp,
     Executor,
+    TokenIdBuffer,
     MatmulCall,
     MatmulOp,
     MatmulOpEx,
@@ -38,3 +41,4 @@ from .api import (  # noqa: F401
     version,
 )
 from .capi import lib, lib_path  # noqa: F401
+from .llama import Llama, LlamaConfig  # noqa: F401

@@ -280,6 +280,154 @@ class MatmulOpEx:
                                 w._h if w is not None else None, eps, self.store._c())
 
 
+class TokenIdBuffer:
+    """Token-id list in host-visible memory (TokenIdBuffer in the reference)."""
+
+    def __init__(self, ctx: Context, capacity: int):
+        h = lib().ta_token_ids_create(ctx._h, capacity)
+        if not h:
+            raise TensorAshError(_err())
+        self._h = h
+        self.ctx = ctx
+
+    def set(self, tokens) -> None:
+        arr = np.ascontiguousarray(tokens, dtype=np.uint32)
+        _check(lib().ta_token_ids_set(self._h, arr.ctypes.data, arr.size))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().ta_token_ids_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ExecKind(enum.IntEnum):
+    MATMUL = 0
+    RMS_NORM = 1
+    LAYER_NORM = 2
+    SOFTMAX_ROWS = 3
+    ROPE = 4
+    ROPE_SCATTER = 5
+    COPY_STRIDED = 6
+    BINARY = 7
+    ATTN_DECODE = 8
+    FLASH_ATTN = 9
+    ARGMAX = 10
+    EMBED_GATHER = 11
+    EMBED_GATHER_ROWS = 12
+
+
+class ExecOp:
+    """One op of a mixed graph (ExecOp in the reference, src/executor/graph_ops.rs:27-161).
+    Build with the class methods; keeps its operands alive."""
+
+    def __init__(self, kind: ExecKind, **kw):
+        self.c = capi.ExecOpC()
+        self.c.kind = int(kind)
+        self._keep = []
+        for name in ("in0", "in1", "in2", "in3", "out"):
+            t = kw.get(name)
+            if t is not None:
+                setattr(self.c, name, t._h)
+                self._keep.append(t)
+        self.c.f0 = kw.get("f0", 0.0)
+        for name in ("u0", "u1", "u2", "dst_offset", "pos_scale"):
+            setattr(self.c, name, int(kw.get(name, 0)))
+        if "dst_strides" in kw:
+            self.c.dst_strides = (C.c_uint32 * 3)(*kw["dst_strides"])
+        if "rope" in kw:
+            self.c.rope = capi.RopeDescC(*kw["rope"])
+        if "copy" in kw:
+            ext, so, ss, do, ds = kw["copy"]
+            self.c.copy = capi.CopyDescC((C.c_uint32 * 3)(*ext), so, (C.c_uint32 * 3)(*ss), do, (C.c_uint32 * 3)(*ds))
+        if "flash" in kw:
+            self.c.flash = capi.FlashDescC(*kw["flash"])
+        if "attn" in kw:
+            kv_len, scale, cell = kw["attn"]
+            self.c.attn = capi.AttnDecodeDescC(kv_len, scale, cell._h if cell is not None else None)
+            self._keep.append(cell)
+        for name in ("cell", "tokens"):
+            obj = kw.get(name)
+            if obj is not None:
+                setattr(self.c, name, obj._h)
+                self._keep.append(obj)
+        if "mm" in kw:
+            op = kw["mm"]
+            self.c.mm = op._c() if isinstance(op, MatmulOpEx) else MatmulOpEx(op.call, op.epilogue)._c()
+            self._keep.append(op)
+
+    @classmethod
+    def matmul(cls, op):
+        return cls(ExecKind.MATMUL, mm=op)
+
+    @classmethod
+    def rms_norm(cls, inp, weight, out, eps):
+        return cls(ExecKind.RMS_NORM, in0=inp, in1=weight, out=out, f0=eps)
+
+    @classmethod
+    def layer_norm(cls, inp, weight, bias, out, eps):
+        return cls(ExecKind.LAYER_NORM, in0=inp, in1=weight, in2=bias, out=out, f0=eps)
+
+    @classmethod
+    def softmax_rows(cls, inp, out, scale=1.0, mask_kind=0, valid_or_prefix=0, rows_per_group=0):
+        return cls(ExecKind.SOFTMAX_ROWS, in0=inp, out=out, f0=scale, u0=mask_kind, u1=valid_or_prefix, u2=rows_per_group)
+
+    @classmethod
+    def rope(cls, inp, table, out, heads, head_dim, rot_dim, pos_base=0):
+        return cls(ExecKind.ROPE, in0=inp, in1=table, out=out, rope=(heads, head_dim, rot_dim, pos_base))
+
+    @classmethod
+    def rope_scatter(cls, inp, table, dst, heads, head_dim, rot_dim, pos_base, dst_offset, dst_strides,
+                     pos_scale=0, cell=None):
+        return cls(ExecKind.ROPE_SCATTER, in0=inp, in1=table, out=dst, rope=(heads, head_dim, rot_dim, pos_base),
+                   dst_offset=dst_offset, dst_strides=dst_strides, pos_scale=pos_scale, cell=cell)
+
+    @classmethod
+    def copy_strided(cls, src, dst, extent, src_offset, src_strides, dst_offset, dst_strides):
+        return cls(ExecKind.COPY_STRIDED, in0=src, out=dst, copy=(extent, src_offset, src_strides, dst_offset, dst_strides))
+
+    @classmethod
+    def binary_add_scaled(cls, a, b, out, beta):
+        return cls(ExecKind.BINARY, in0=a, in1=b, out=out, u0=0, f0=beta)
+
+    @classmethod
+    def binary_silu_mul(cls, a, b, out):
+        return cls(ExecKind.BINARY, in0=a, in1=b, out=out, u0=1)
+
+    @classmethod
+    def attn_decode(cls, q, kt, v, scratch, out, kv_len, scale, pos_cell=None):
+        return cls(ExecKind.ATTN_DECODE, in0=q, in1=kt, in2=v, in3=scratch, out=out, attn=(kv_len, scale, pos_cell))
+
+    @classmethod
+    def flash_attn(cls, q, kt, v, out, kv_len, pos_base, scale, token_major_heads=0, out_token_major_heads=0):
+        return cls(ExecKind.FLASH_ATTN, in0=q, in1=kt, in2=v, out=out,
+                   flash=(kv_len, pos_base, scale, token_major_heads, out_token_major_heads))
+
+    @classmethod
+    def argmax(cls, inp, result_cell):
+        return cls(ExecKind.ARGMAX, in0=inp, cell=result_cell)
+
+    @classmethod
+    def embed_gather(cls, token_cell, table, out):
+        return cls(ExecKind.EMBED_GATHER, cell=token_cell, in0=table, out=out)
+
+    @classmethod
+    def embed_gather_rows(cls, tokens, table, out):
+        return cls(ExecKind.EMBED_GATHER_ROWS, tokens=tokens, in0=table, out=out)
+
+
+def _exec_array(ops):
+    arr = (capi.ExecOpC * max(len(ops), 1))()
+    for i, op in enumerate(ops):
+        arr[i] = op.c
+    return arr
+
+
 def _ops_array(ops: Sequence[MatmulOp]):
     arr = (capi.MatmulOpC * max(len(ops), 1))()
     for i, op in enumerate(ops):
@@ -389,6 +537,17 @@ class Executor:
         _check(lib().ta_swiglu_gemv(self._h, x._h, wg._h, wup._h, out._h,
                                     normed_weight._h if normed_weight is not None else None, eps, C.byref(st)))
         return RunStats._from(st)
+
+    def run_exec_ops(self, ops) -> RunStats:
+        st = capi.RunStatsC()
+        _check(lib().ta_run_exec_ops(self._h, _exec_array(ops), len(ops), C.byref(st)))
+        return RunStats._from(st)
+
+    def prepare_exec_ops(self, ops) -> PreparedOps:
+        h = lib().ta_prepared_create_exec(self._h, _exec_array(ops), len(ops))
+        if not h:
+            raise TensorAshError(_err())
+        return PreparedOps(h, (self, list(ops)))
 
     def run_flash_attention(self, q: Tensor, kt: Tensor, v: Tensor, out: Tensor, kv_len: int, pos_base: int,
                             scale: float, token_major_heads: int = 0, out_token_major_heads: int = 0) -> RunStats:

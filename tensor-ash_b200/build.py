@@ -22,7 +22,9 @@ LIB = os.path.join(LIB_DIR, "libtensor_ash.so")
 SOURCES = [
     "ta_host.cpp",
     "ta_runtime.cu",
+    "ta_graph.cu",
     "ta_capi.cu",
+    "llama_ash.cu",
     "k_gemm_ffma.cu",
     "k_gemm_tf32x3.cu",
     "k_gemv.cu",

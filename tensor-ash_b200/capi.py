@@ -70,6 +70,22 @@ class AttnDecodeDescC(C.Structure):
     _fields_ = [("kv_len", C.c_uint32), ("scale", C.c_float), ("pos_cell", C.c_void_p)]
 
 
+class ExecOpC(C.Structure):
+    _fields_ = [("kind", C.c_uint32), ("mm", MatmulOpExC),
+                ("in0", C.c_void_p), ("in1", C.c_void_p), ("in2", C.c_void_p), ("in3", C.c_void_p),
+                ("out", C.c_void_p), ("f0", C.c_float), ("u0", C.c_uint32), ("u1", C.c_uint32),
+                ("u2", C.c_uint32), ("rope", RopeDescC), ("copy", CopyDescC), ("dst_offset", C.c_uint32),
+                ("dst_strides", C.c_uint32 * 3), ("pos_scale", C.c_uint32), ("flash", FlashDescC),
+                ("attn", AttnDecodeDescC), ("cell", C.c_void_p), ("tokens", C.c_void_p)]
+
+
+class LlamaConfigC(C.Structure):
+    _fields_ = [("layers", C.c_uint32), ("embd", C.c_uint32), ("heads", C.c_uint32), ("kv_heads", C.c_uint32),
+                ("head_dim", C.c_uint32), ("ffn", C.c_uint32), ("vocab", C.c_uint32), ("t_max", C.c_uint32),
+                ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("weight_sigma", C.c_float),
+                ("norm_jitter", C.c_float), ("seed", C.c_uint64)]
+
+
 _P = C.c_void_p
 _U32 = C.c_uint32
 _SZ = C.c_size_t
@@ -128,6 +144,11 @@ SIGNATURES = {
     "ta_pos_cell_destroy": (None, [_P]),
     "ta_pos_cell_set": (C.c_int, [_P, _U32]),
     "ta_pos_cell_get": (C.c_int, [_P, C.POINTER(_U32)]),
+    "ta_token_ids_create": (_P, [_P, _U32]),
+    "ta_token_ids_destroy": (None, [_P]),
+    "ta_token_ids_set": (C.c_int, [_P, _P, _U32]),
+    "ta_run_exec_ops": (C.c_int, [_P, C.POINTER(ExecOpC), _SZ, _STATS]),
+    "ta_prepared_create_exec": (_P, [_P, C.POINTER(ExecOpC), _SZ]),
     "ta_kernel_spec_count": (_SZ, []),
     "ta_kernel_spec_at": (C.c_int, [_SZ, C.POINTER(DispatchInfoC)]),
     "ta_kernel_selection_parse": (C.c_int, [C.c_char_p]),
@@ -140,6 +161,15 @@ SIGNATURES = {
     "ta_tensor_device_ptr": (_P, [_P]),
     "ta_context_device_index": (C.c_int, [_P]),
     "ta_kernel_launch_count": (C.c_uint64, []),
+    # ---- tensor_ash_llama.h
+    "ta_llama_create_random": (_P, [_P, C.POINTER(LlamaConfigC)]),
+    "ta_llama_destroy": (None, [_P]),
+    "ta_llama_reset": (C.c_int, [_P]),
+    "ta_llama_prefill": (C.c_int, [_P, C.POINTER(_U32), _U32, C.POINTER(_U32), _STATS]),
+    "ta_llama_decode": (C.c_int, [_P, _U32, _U32, C.POINTER(_U32), _STATS]),
+    "ta_llama_logits": (C.c_int, [_P, _P, _SZ]),
+    "ta_llama_position": (_U32, [_P]),
+    "ta_llama_weight_bytes_per_token": (C.c_uint64, [_P]),
 }
 
 _lib = None

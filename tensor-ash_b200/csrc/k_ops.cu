@@ -6,6 +6,8 @@
 //   3-D strided copy     shaders/op_copy_strided_body.glsl:40-98
 // All are bandwidth-trivial next to the GEMMs; one block per row, fixed-order
 // tree reductions so results do not depend on scheduling.
+#include <cuda_fp16.h>
+
 #include "ta_core.hpp"
 
 namespace ta {
@@ -117,12 +119,18 @@ __global__ void rope_tail_kernel(const float *__restrict__ in, float *__restrict
   if (v < vecs) out[v * head_dim + head_dim - 1] = in[v * head_dim + head_dim - 1];
 }
 
+__device__ __forceinline__ float cvt_load(float v) { return v; }
+__device__ __forceinline__ float cvt_load(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T cvt_store(float v);
+template <> __device__ __forceinline__ float cvt_store<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half cvt_store<__half>(float v) { return __float2half_rn(v); }
+
 struct CopyArgs {
   uint32_t extent[3], src_off, src_strides[3], dst_off, dst_strides[3];
 };
 
-__global__ void copy_strided_kernel(const float *__restrict__ src, float *__restrict__ dst,
-                                    CopyArgs a) {
+template <typename TS, typename TD>
+__global__ void copy_strided_kernel(const TS *__restrict__ src, TD *__restrict__ dst, CopyArgs a) {
   const uint64_t total = (uint64_t)a.extent[0] * a.extent[1] * a.extent[2];
   const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -133,7 +141,90 @@ __global__ void copy_strided_kernel(const float *__restrict__ src, float *__rest
                    (size_t)z * a.src_strides[2];
   const size_t d = (size_t)a.dst_off + (size_t)x * a.dst_strides[0] + (size_t)y * a.dst_strides[1] +
                    (size_t)z * a.dst_strides[2];
-  dst[d] = src[s];
+  dst[d] = cvt_store<TD>(cvt_load(src[s]));
+}
+
+// out = a + beta*b (mode 0) or silu(a)*b (mode 1); out may alias either input
+// (shaders/op_binary_body.glsl:60-100).
+__global__ void binary_kernel(const float *a, const float *b, float *out, uint32_t n, uint32_t mode,
+                              float beta) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float x = a[i], y = b[i];
+  out[i] = mode == 0 ? fmaf(beta, y, x) : (x / (1.0f + expf(-x))) * y;
+}
+
+// One block; ties keep the LARGEST index (shaders/op_argmax_f32.comp:44-75).
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float *__restrict__ in, uint32_t n, uint32_t *result) {
+  __shared__ float sval[256];
+  __shared__ uint32_t sidx[256];
+  const uint32_t tid = threadIdx.x;
+  float best = -INFINITY;
+  uint32_t best_idx = 0;
+  for (uint32_t i = tid; i < n; i += 256) {
+    const float v = in[i];
+    if (v >= best) {
+      best = v;
+      best_idx = i;
+    }
+  }
+  sval[tid] = best;
+  sidx[tid] = best_idx;
+  __syncthreads();
+  for (uint32_t stride = 128; stride > 0; stride >>= 1) {
+    if (tid < stride) {
+      const float o = sval[tid + stride];
+      const uint32_t oi = sidx[tid + stride];
+      if (o > sval[tid] || (o == sval[tid] && oi > sidx[tid])) {
+        sval[tid] = o;
+        sidx[tid] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (tid == 0) *result = sidx[0];
+}
+
+// Row gather by token id read on the device, id clamped to vocab-1
+// (shaders/op_embed_gather.comp:60-90).  grid (ceil(embd/256), n_tokens).
+template <typename TT>
+__global__ void embed_gather_kernel(const uint32_t *__restrict__ tokens, const TT *__restrict__ table,
+                                    float *__restrict__ out, uint32_t embd, uint32_t vocab) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+  if (i >= embd) return;
+  const uint32_t token = min(tokens[t], vocab - 1u);
+  out[(size_t)t * embd + i] = cvt_load(table[(size_t)token * embd + i]);
+}
+
+// RoPE + strided scatter of [T, H, dh] activations (shaders/op_rope_body.glsl
+// scatter variant): every element, rotated or pass-through, is written to
+// dst_off + pos*pos_scale + t*s0 + h*s1 + d*s2.
+template <typename TD>
+__global__ void rope_scatter_kernel(const float *__restrict__ in, const float *__restrict__ table,
+                                    TD *__restrict__ dst, uint32_t tokens, uint32_t heads, uint32_t head_dim,
+                                    uint32_t rot_dim, uint32_t pos_base, uint32_t dst_off, uint32_t s0,
+                                    uint32_t s1, uint32_t s2, uint32_t pos_scale,
+                                    const uint32_t *__restrict__ pos_ptr) {
+  const uint32_t half_dim = head_dim / 2;
+  const uint64_t total = (uint64_t)tokens * heads * half_dim;
+  const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const uint32_t i = (uint32_t)(idx % half_dim);
+  const uint64_t vec = idx / half_dim;
+  const uint32_t t = (uint32_t)(vec / heads), h = (uint32_t)(vec % heads);
+  const uint32_t p = pos_ptr ? *pos_ptr : 0u;
+  const size_t base = (size_t)vec * head_dim + 2 * i;
+  float r0 = in[base], r1 = in[base + 1];
+  if (2 * i < rot_dim) {
+    const float *cs = table + ((size_t)(pos_base + p + t) * (rot_dim / 2) + i) * 2;
+    const float x0 = r0, x1 = r1;
+    r0 = fmaf(x0, cs[0], -x1 * cs[1]);
+    r1 = fmaf(x0, cs[1], x1 * cs[0]);
+  }
+  const size_t d = (size_t)dst_off + (size_t)p * pos_scale + (size_t)t * s0 + (size_t)h * s1 + (size_t)(2 * i) * s2;
+  dst[d] = cvt_store<TD>(r0);
+  dst[d + s2] = cvt_store<TD>(r1);
 }
 
 inline void launched() {
@@ -176,8 +267,8 @@ void launch_rope(const float *in, const float *table, float *out, uint32_t token
   }
 }
 
-void launch_copy_strided(const float *src, float *dst, const uint32_t extent[3], uint32_t src_off,
-                         const uint32_t src_strides[3], uint32_t dst_off,
+void launch_copy_strided(const void *src, bool src_f16, void *dst, bool dst_f16, const uint32_t extent[3],
+                         uint32_t src_off, const uint32_t src_strides[3], uint32_t dst_off,
                          const uint32_t dst_strides[3], cudaStream_t stream) {
   CopyArgs a;
   for (int i = 0; i < 3; ++i) {
@@ -188,7 +279,51 @@ void launch_copy_strided(const float *src, float *dst, const uint32_t extent[3],
   a.src_off = src_off;
   a.dst_off = dst_off;
   const uint64_t total = (uint64_t)extent[0] * extent[1] * extent[2];
-  copy_strided_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, stream>>>(src, dst, a);
+  const uint32_t blocks = (uint32_t)((total + 255) / 256);
+  if (!src_f16 && !dst_f16)
+    copy_strided_kernel<<<blocks, 256, 0, stream>>>((const float *)src, (float *)dst, a);
+  else if (!src_f16 && dst_f16)
+    copy_strided_kernel<<<blocks, 256, 0, stream>>>((const float *)src, (__half *)dst, a);
+  else if (src_f16 && dst_f16)
+    copy_strided_kernel<<<blocks, 256, 0, stream>>>((const __half *)src, (__half *)dst, a);
+  else
+    copy_strided_kernel<<<blocks, 256, 0, stream>>>((const __half *)src, (float *)dst, a);
+  launched();
+}
+
+void launch_binary(const float *a, const float *b, float *out, uint32_t n, uint32_t mode, float beta,
+                   cudaStream_t stream) {
+  binary_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a, b, out, n, mode, beta);
+  launched();
+}
+
+void launch_argmax(const float *in, uint32_t n, uint32_t *result, cudaStream_t stream) {
+  argmax_kernel<<<1, 256, 0, stream>>>(in, n, result);
+  launched();
+}
+
+void launch_embed_gather(const uint32_t *tokens, uint32_t n_tokens, const void *table, bool table_f16,
+                         float *out, uint32_t embd, uint32_t vocab, cudaStream_t stream) {
+  dim3 grid((embd + 255) / 256, n_tokens);
+  if (table_f16) embed_gather_kernel<<<grid, 256, 0, stream>>>(tokens, (const __half *)table, out, embd, vocab);
+  else embed_gather_kernel<<<grid, 256, 0, stream>>>(tokens, (const float *)table, out, embd, vocab);
+  launched();
+}
+
+void launch_rope_scatter(const float *in, const float *table, void *dst, bool dst_f16, uint32_t tokens,
+                         uint32_t heads, uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base,
+                         uint32_t dst_off, const uint32_t strides[3], uint32_t pos_scale,
+                         const uint32_t *pos_ptr, cudaStream_t stream) {
+  const uint64_t total = (uint64_t)tokens * heads * (head_dim / 2);
+  const uint32_t blocks = (uint32_t)((total + 255) / 256);
+  if (dst_f16)
+    rope_scatter_kernel<<<blocks, 256, 0, stream>>>(in, table, (__half *)dst, tokens, heads, head_dim, rot_dim,
+                                                    pos_base, dst_off, strides[0], strides[1], strides[2],
+                                                    pos_scale, pos_ptr);
+  else
+    rope_scatter_kernel<<<blocks, 256, 0, stream>>>(in, table, (float *)dst, tokens, heads, head_dim, rot_dim,
+                                                    pos_base, dst_off, strides[0], strides[1], strides[2],
+                                                    pos_scale, pos_ptr);
   launched();
 }
 

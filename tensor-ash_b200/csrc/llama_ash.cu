@@ -1,0 +1,556 @@
+// llama-architecture runner on library ops only: the prefill and decode op graphs
+// of the reference's tools/llama-ash (model/forward/prefill.rs:89-291,
+// forward/decode.rs:52-98,172-246, forward/mod.rs:50-87,134-328, model/load.rs:144-255).
+//
+// Weights live as f16 [n_in, n_out]; decode uses packed row tiles for q/k/v, gate,
+// up and lm_head, row-major for o and down, exactly the reference's split.  KV
+// caches are f16: Kt [H_kv, dh, T_max] and V [H_kv, T_max, dh] per layer.
+//
+// Decode is ONE prepared graph per model: per layer three packed GEMVs with the
+// attention RMSNorm fused into A and RoPE / KV-append fused into the store, the
+// split-K decode attention, o-projection + residual, up, gate (SiLU * up), down
+// + residual; then lm_head with the final norm fused, argmax into a host-visible
+// word, and the next token's embedding row gathered on the device.  A step is
+// one position write, one graph launch and one token read.
+#include <cmath>
+#include <cstring>
+#include <array>
+#include <thread>
+
+#pragma GCC visibility push(default)
+#include "../../include/tensor_ash_llama.h"
+#pragma GCC visibility pop
+#include "ta_handles.hpp"
+
+namespace {
+
+// ---- deterministic weight streams: the LCG of the reference's test fixtures
+// (tools/test-support/src/lib.rs:9-18) with Box-Muller on top, per 2^20-element chunk.
+inline uint64_t lcg_seed(uint64_t seed) { return (seed * 0x9E3779B97F4A7C15ull) | 1ull; }
+inline uint64_t lcg_step(uint64_t s) { return s * 6364136223846793005ull + 1442695040888963407ull; }
+
+void fill_normal_chunk(float *out, size_t n, uint64_t seed, double sigma) {
+  uint64_t s = lcg_seed(seed);
+  const double two_pi = 6.283185307179586476925286766559;
+  for (size_t i = 0; i < n; i += 2) {
+    s = lcg_step(s);
+    const double u1 = ((double)(uint32_t)(s >> 40) + 1.0) / 16777216.0;
+    s = lcg_step(s);
+    const double u2 = (double)(uint32_t)(s >> 40) / 16777216.0;
+    const double r = std::sqrt(-2.0 * std::log(u1));
+    out[i] = (float)(sigma * r * std::cos(two_pi * u2));
+    if (i + 1 < n) out[i + 1] = (float)(sigma * r * std::sin(two_pi * u2));
+  }
+}
+
+void fill_uniform_chunk(float *out, size_t n, uint64_t seed) {
+  uint64_t s = lcg_seed(seed);
+  for (size_t i = 0; i < n; ++i) {
+    s = lcg_step(s);
+    out[i] = (float)(uint32_t)(s >> 40) / (float)(1u << 24) * 2.0f - 1.0f;
+  }
+}
+
+constexpr size_t CHUNK = 1u << 20;
+
+uint64_t chunk_seed(uint64_t seed, uint32_t tensor_id, size_t chunk) {
+  return (seed * 1000003ull + tensor_id) * 4096ull + chunk;
+}
+
+// Generates tensor `id` (n elements) as f16 bits, in parallel over chunks.
+std::vector<uint16_t> gen_weight_f16(uint64_t seed, uint32_t id, size_t n, double sigma) {
+  std::vector<uint16_t> bits(n);
+  const size_t chunks = (n + CHUNK - 1) / CHUNK;
+  const unsigned nt = std::max(1u, std::min(32u, std::thread::hardware_concurrency()));
+  std::vector<std::thread> pool;
+  for (unsigned t = 0; t < nt; ++t)
+    pool.emplace_back([&, t]() {
+      std::vector<float> tmp(CHUNK);
+      for (size_t c = t; c < chunks; c += nt) {
+        const size_t off = c * CHUNK, len = std::min(CHUNK, n - off);
+        fill_normal_chunk(tmp.data(), len, chunk_seed(seed, id, c), sigma);
+        for (size_t i = 0; i < len; ++i) bits[off + i] = f32_to_f16_bits(tmp[i]);
+      }
+    });
+  for (auto &th : pool) th.join();
+  return bits;
+}
+
+// [K, N] -> packed [N/tile][K][tile] on raw f16 bits (src/matmul/api.rs:317-344)
+std::vector<uint16_t> pack_bits(const std::vector<uint16_t> &src, size_t k, size_t n, size_t tile) {
+  std::vector<uint16_t> out(src.size());
+  const size_t tiles = n / tile;
+  for (size_t t = 0; t < tiles; ++t)
+    for (size_t kk = 0; kk < k; ++kk)
+      memcpy(&out[(t * k + kk) * tile], &src[kk * n + t * tile], tile * 2);
+  return out;
+}
+
+struct Layer {
+  Tensor attn_norm, ffn_norm;
+  Tensor wq_p, wk_p, wv_p, w_qkv, wo, w_gate, w_up, w_gate_p, w_up_p, w_down;
+  Tensor kt_cache, v_cache;
+};
+
+}  // namespace
+
+struct ta_llama {
+  std::shared_ptr<Context> ctx;
+  Executor *exec = nullptr;
+  ta_llama_config cfg{};
+  std::vector<Layer> layers;
+  Tensor embd, output_norm, lm_head, lm_head_p, rope_table;
+  // decode scratch (t = 1)
+  Tensor x_a, x_b, q, k, v, attn, o, up, gate, logits, attn_partials;
+  PosCell pos_cell, token_cell;
+  TokenIds token_ids;
+  std::unique_ptr<PreparedOps> decode_graph;
+  uint32_t pos = 0;
+  ~ta_llama();
+};
+
+namespace {
+
+Tensor make(const std::shared_ptr<Context> &ctx, std::initializer_list<uint32_t> shape, DType dt) {
+  std::vector<uint32_t> s(shape);
+  return Tensor::uninit_device(ctx, s.data(), s.size(), dt);
+}
+
+Tensor upload_bits(ta_llama &m, const std::vector<uint16_t> &bits, uint32_t rows, uint32_t cols) {
+  Tensor t = make(m.ctx, {rows, cols}, DType::F16);
+  m.exec->upload_f16(bits.data(), bits.size(), t);
+  return t;
+}
+
+Tensor norm_weight(ta_llama &m, uint32_t id) {
+  std::vector<float> w(m.cfg.embd, 1.0f);
+  if (m.cfg.norm_jitter != 0.0f) {
+    std::vector<float> u(m.cfg.embd);
+    fill_uniform_chunk(u.data(), u.size(), chunk_seed(m.cfg.seed, id, 0));
+    for (size_t i = 0; i < w.size(); ++i) w[i] = 1.0f + m.cfg.norm_jitter * u[i];
+  }
+  Tensor t = make(m.ctx, {m.cfg.embd}, DType::F32);
+  m.exec->upload(w.data(), w.size(), t);
+  return t;
+}
+
+void make_pinned_cell(const std::shared_ptr<Context> &ctx, PosCell &c) {
+  c.ctx = ctx;
+  TA_CUDA(cudaHostAlloc((void **)&c.host, sizeof(uint32_t), cudaHostAllocMapped));
+  TA_CUDA(cudaHostGetDevicePointer((void **)&c.device, c.host, 0));
+  *c.host = 0;
+}
+
+}  // namespace
+
+ta_llama::~ta_llama() {
+  decode_graph.reset();   // waits for in-flight work before the tensors go away
+  if (ctx) cudaSetDevice(ctx->device);
+  if (pos_cell.host) cudaFreeHost(pos_cell.host);
+  if (token_cell.host) cudaFreeHost(token_cell.host);
+  if (token_ids.host) cudaFreeHost(token_ids.host);
+}
+
+// ------------------------------------------------------------------ construction
+namespace {
+
+void build_model(ta_llama &m) {
+  const ta_llama_config &c = m.cfg;
+  if (!c.layers || !c.embd || !c.heads || !c.kv_heads || !c.head_dim || !c.ffn || !c.vocab || !c.t_max)
+    fail("ta_llama_create_random: every config dimension must be non-zero");
+  if (c.heads * c.head_dim != c.embd) fail("ta_llama_create_random: heads * head_dim must equal embd");
+  if (c.heads % c.kv_heads || c.heads / c.kv_heads > 8) fail("ta_llama_create_random: GQA group must be 1..8");
+  if (c.head_dim != 64) fail("ta_llama_create_random: head_dim must be 64 (decode attention variant)");
+  const uint32_t kv_dim = c.kv_heads * c.head_dim, n_qkv = c.embd + 2 * kv_dim;
+  for (uint32_t n : {c.embd, kv_dim, c.ffn, c.vocab})
+    if (n % 32) fail("ta_llama_create_random: projection widths must be multiples of 32 (got %u)", n);
+  const double sigma = c.weight_sigma;
+  const uint64_t seed = c.seed;
+  auto tile = [](uint32_t k, uint32_t n) { return f16w_row_tile_n(k, n); };
+
+  {  // token embedding [vocab, embd], final norm, lm_head [embd, vocab]
+    auto e = gen_weight_f16(seed, 0, (size_t)c.vocab * c.embd, sigma);
+    m.embd = upload_bits(m, e, c.vocab, c.embd);
+    m.output_norm = norm_weight(m, 1);
+    auto h = gen_weight_f16(seed, 2, (size_t)c.embd * c.vocab, sigma);
+    m.lm_head = upload_bits(m, h, c.embd, c.vocab);
+    m.lm_head_p = upload_bits(m, pack_bits(h, c.embd, c.vocab, tile(c.embd, c.vocab)), c.embd, c.vocab);
+  }
+  m.layers.resize(c.layers);
+  for (uint32_t li = 0; li < c.layers; ++li) {
+    Layer &L = m.layers[li];
+    const uint32_t base = 16 + 16 * li;
+    L.attn_norm = norm_weight(m, base + 0);
+    L.ffn_norm = norm_weight(m, base + 5);
+    auto wq = gen_weight_f16(seed, base + 1, (size_t)c.embd * c.embd, sigma);
+    auto wk = gen_weight_f16(seed, base + 2, (size_t)c.embd * kv_dim, sigma);
+    auto wv = gen_weight_f16(seed, base + 3, (size_t)c.embd * kv_dim, sigma);
+    L.wq_p = upload_bits(m, pack_bits(wq, c.embd, c.embd, tile(c.embd, c.embd)), c.embd, c.embd);
+    L.wk_p = upload_bits(m, pack_bits(wk, c.embd, kv_dim, tile(c.embd, kv_dim)), c.embd, kv_dim);
+    L.wv_p = upload_bits(m, pack_bits(wv, c.embd, kv_dim, tile(c.embd, kv_dim)), c.embd, kv_dim);
+    {  // concatenated [embd, embd + 2 kv_dim] for the prefill GEMM
+      std::vector<uint16_t> cat((size_t)c.embd * n_qkv);
+      for (uint32_t r = 0; r < c.embd; ++r) {
+        memcpy(&cat[(size_t)r * n_qkv], &wq[(size_t)r * c.embd], (size_t)c.embd * 2);
+        memcpy(&cat[(size_t)r * n_qkv + c.embd], &wk[(size_t)r * kv_dim], (size_t)kv_dim * 2);
+        memcpy(&cat[(size_t)r * n_qkv + c.embd + kv_dim], &wv[(size_t)r * kv_dim], (size_t)kv_dim * 2);
+      }
+      L.w_qkv = upload_bits(m, cat, c.embd, n_qkv);
+    }
+    L.wo = upload_bits(m, gen_weight_f16(seed, base + 4, (size_t)c.embd * c.embd, sigma), c.embd, c.embd);
+    auto wg = gen_weight_f16(seed, base + 6, (size_t)c.embd * c.ffn, sigma);
+    auto wu = gen_weight_f16(seed, base + 7, (size_t)c.embd * c.ffn, sigma);
+    L.w_gate = upload_bits(m, wg, c.embd, c.ffn);
+    L.w_up = upload_bits(m, wu, c.embd, c.ffn);
+    L.w_gate_p = upload_bits(m, pack_bits(wg, c.embd, c.ffn, tile(c.embd, c.ffn)), c.embd, c.ffn);
+    L.w_up_p = upload_bits(m, pack_bits(wu, c.embd, c.ffn, tile(c.embd, c.ffn)), c.embd, c.ffn);
+    L.w_down = upload_bits(m, gen_weight_f16(seed, base + 8, (size_t)c.ffn * c.embd, sigma), c.ffn, c.embd);
+    L.kt_cache = make(m.ctx, {c.kv_heads, c.head_dim, c.t_max}, DType::F16);
+    L.v_cache = make(m.ctx, {c.kv_heads, c.t_max, c.head_dim}, DType::F16);
+    TA_CUDA(cudaMemset(L.kt_cache.ptr(), 0, L.kt_cache.size_bytes()));
+    TA_CUDA(cudaMemset(L.v_cache.ptr(), 0, L.v_cache.size_bytes()));
+  }
+  {  // rope table [t_max, dh/2, 2], angles in f64 (model/load.rs:243-253)
+    const uint32_t half = c.head_dim / 2;
+    std::vector<float> table((size_t)c.t_max * half * 2);
+    for (uint32_t p = 0; p < c.t_max; ++p)
+      for (uint32_t i = 0; i < half; ++i) {
+        const double theta = (double)p / std::pow((double)c.rope_theta, 2.0 * i / (double)c.head_dim);
+        table[((size_t)p * half + i) * 2] = (float)std::cos(theta);
+        table[((size_t)p * half + i) * 2 + 1] = (float)std::sin(theta);
+      }
+    m.rope_table = make(m.ctx, {c.t_max, half, 2}, DType::F32);
+    m.exec->upload(table.data(), table.size(), m.rope_table);
+  }
+  // decode scratch
+  m.x_a = make(m.ctx, {1, c.embd}, DType::F32);
+  m.x_b = make(m.ctx, {1, c.embd}, DType::F32);
+  m.q = make(m.ctx, {1, c.embd}, DType::F32);
+  m.k = make(m.ctx, {1, kv_dim}, DType::F32);
+  m.v = make(m.ctx, {1, kv_dim}, DType::F32);
+  m.attn = make(m.ctx, {1, c.embd}, DType::F32);
+  m.o = make(m.ctx, {1, c.embd}, DType::F32);
+  m.up = make(m.ctx, {1, c.ffn}, DType::F32);
+  m.gate = make(m.ctx, {1, c.ffn}, DType::F32);
+  m.logits = make(m.ctx, {1, c.vocab}, DType::F32);
+  m.attn_partials = make(m.ctx, {c.kv_heads * ATTN_DECODE_MAX_CHUNKS * (c.heads / c.kv_heads) * (c.head_dim + 2)}, DType::F32);
+  make_pinned_cell(m.ctx, m.pos_cell);
+  make_pinned_cell(m.ctx, m.token_cell);
+  m.token_ids.ctx = m.ctx;
+  m.token_ids.capacity = c.t_max;
+  TA_CUDA(cudaHostAlloc((void **)&m.token_ids.host, (size_t)c.t_max * 4, cudaHostAllocMapped));
+  TA_CUDA(cudaHostGetDevicePointer((void **)&m.token_ids.device, m.token_ids.host, 0));
+}
+
+ExecOp mm_op(const Tensor &a, const Tensor &b, const Tensor &c) {
+  ExecOp o;
+  o.kind = ExecKind::Matmul;
+  o.mm.call = MatmulCall{&a, &b, &c, 1.0f, false};
+  return o;
+}
+
+// forward/mod.rs:134-227 push_mlp_ops; residual adds and the SiLU gate ride the
+// GEMM epilogues at every width (every kernel family here fuses them).
+void push_mlp_ops(ta_llama &m, std::vector<ExecOp> &ops, Layer &L, bool decode, const Tensor &attn_flat,
+                  const Tensor &o, const Tensor &on, const Tensor &up, const Tensor &gate, const Tensor &x_in,
+                  const Tensor &x_out) {
+  const float eps = m.cfg.rms_eps;
+  ExecOp op = mm_op(attn_flat, L.wo, o);
+  op.mm.epilogue.binary = BinaryKind::AddScaled;
+  op.mm.epilogue.d = &x_in;
+  op.mm.epilogue.beta = 1.0f;
+  ops.push_back(op);
+  if (decode) {
+    ExecOp u = mm_op(o, L.w_up_p, up);
+    u.mm.packed_b = true; u.mm.normed_weight = &L.ffn_norm; u.mm.normed_eps = eps;
+    ops.push_back(u);
+    ExecOp g = mm_op(o, L.w_gate_p, gate);
+    g.mm.packed_b = true; g.mm.normed_weight = &L.ffn_norm; g.mm.normed_eps = eps;
+    g.mm.epilogue.activation = Activation::Silu;
+    g.mm.epilogue.binary = BinaryKind::Mul;
+    g.mm.epilogue.d = &up;
+    ops.push_back(g);
+  } else {
+    ExecOp n;
+    n.kind = ExecKind::RmsNorm;
+    n.in0 = &o; n.in1 = &L.ffn_norm; n.out = &on; n.f0 = eps;
+    ops.push_back(n);
+    ops.push_back(mm_op(on, L.w_up, up));
+    ExecOp g = mm_op(on, L.w_gate, gate);
+    g.mm.epilogue.activation = Activation::Silu;
+    g.mm.epilogue.binary = BinaryKind::Mul;
+    g.mm.epilogue.d = &up;
+    ops.push_back(g);
+  }
+  ExecOp d = mm_op(gate, L.w_down, x_out);
+  d.mm.epilogue.binary = BinaryKind::AddScaled;
+  d.mm.epilogue.d = &o;
+  d.mm.epilogue.beta = 1.0f;
+  ops.push_back(d);
+}
+
+// forward/decode.rs:172-246 decode_ops + forward/mod.rs:316-328 decode_close_ops,
+// position-relative (pos_base 0 + *pos_cell).
+std::vector<ExecOp> decode_ops(ta_llama &m) {
+  const ta_llama_config &c = m.cfg;
+  const float eps = c.rms_eps;
+  const uint32_t dh = c.head_dim, t_max = c.t_max;
+  std::vector<ExecOp> ops;
+  const Tensor *x_in = &m.x_a, *x_out = &m.x_b;
+  for (Layer &L : m.layers) {
+    auto gemv = [&](const Tensor &w, const Tensor &out) {
+      ExecOp o = mm_op(*x_in, w, out);
+      o.mm.packed_b = true; o.mm.normed_weight = &L.attn_norm; o.mm.normed_eps = eps;
+      o.mm.store.head_dim = dh; o.mm.store.pos_cell = &m.pos_cell;
+      return o;
+    };
+    ExecOp q = gemv(L.wq_p, m.q);
+    q.mm.store.kind = StoreKind::Rope; q.mm.store.table = &m.rope_table;
+    ops.push_back(q);
+    ExecOp k = gemv(L.wk_p, m.k);
+    k.mm.store.kind = StoreKind::RopeScatter; k.mm.store.table = &m.rope_table; k.mm.store.dst = &L.kt_cache;
+    k.mm.store.pos_scale = 1; k.mm.store.stride_head = dh * t_max; k.mm.store.stride_dim = t_max;
+    ops.push_back(k);
+    ExecOp v = gemv(L.wv_p, m.v);
+    v.mm.store.kind = StoreKind::Scatter; v.mm.store.dst = &L.v_cache;
+    v.mm.store.pos_scale = dh; v.mm.store.stride_head = t_max * dh; v.mm.store.stride_dim = 1;
+    ops.push_back(v);
+    ExecOp a;
+    a.kind = ExecKind::AttnDecode;
+    a.in0 = &m.q; a.in1 = &L.kt_cache; a.in2 = &L.v_cache; a.in3 = &m.attn_partials; a.out = &m.attn;
+    a.attn.kv_len = 1; a.attn.scale = 1.0f / std::sqrt((float)dh); a.attn.pos_cell = &m.pos_cell;
+    ops.push_back(a);
+    push_mlp_ops(m, ops, L, true, m.attn, m.o, m.o, m.up, m.gate, *x_in, *x_out);
+    std::swap(x_in, x_out);
+  }
+  ExecOp head = mm_op(*x_in, m.lm_head_p, m.logits);
+  head.mm.packed_b = true; head.mm.normed_weight = &m.output_norm; head.mm.normed_eps = eps;
+  ops.push_back(head);
+  ExecOp am;
+  am.kind = ExecKind::Argmax;
+  am.in0 = &m.logits; am.cell = &m.token_cell;
+  ops.push_back(am);
+  ExecOp eg;
+  eg.kind = ExecKind::EmbedGather;
+  eg.cell = &m.token_cell; eg.in0 = &m.embd; eg.out = &m.x_a;
+  ops.push_back(eg);
+  return ops;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ prefill
+namespace {
+
+struct PrefillScratch {
+  Tensor x_a, x_b, xn, qkv, q, k, v, attn_flat, o, on, up, gate, last, last_n;
+};
+
+ExecOp copy_op(const Tensor &src, const Tensor &dst, std::array<uint32_t, 3> extent, uint32_t src_off,
+               std::array<uint32_t, 3> ss, uint32_t dst_off, std::array<uint32_t, 3> ds) {
+  ExecOp o;
+  o.kind = ExecKind::CopyStrided;
+  o.in0 = &src; o.out = &dst; o.src_offset = src_off; o.dst_offset = dst_off;
+  for (int i = 0; i < 3; ++i) {
+    o.extent[i] = extent[i];
+    o.src_strides[i] = ss[i];
+    o.strides[i] = ds[i];
+  }
+  return o;
+}
+
+// forward/prefill.rs:89-291 (f32 activations, composed QKV split, fused flash).
+std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint32_t pos_base) {
+  const ta_llama_config &c = m.cfg;
+  const uint32_t heads = c.heads, kv = c.kv_heads, dh = c.head_dim, t_max = c.t_max, embd = c.embd;
+  const uint32_t kv_dim = kv * dh, n_qkv = embd + 2 * kv_dim;
+  std::vector<ExecOp> ops;
+  {
+    ExecOp g;
+    g.kind = ExecKind::EmbedGatherRows;
+    g.tokens = &m.token_ids; g.in0 = &m.embd; g.out = &s.x_a;
+    ops.push_back(g);
+  }
+  const Tensor *x_in = &s.x_a, *x_out = &s.x_b;
+  for (Layer &L : m.layers) {
+    ExecOp n;
+    n.kind = ExecKind::RmsNorm;
+    n.in0 = x_in; n.in1 = &L.attn_norm; n.out = &s.xn; n.f0 = c.rms_eps;
+    ops.push_back(n);
+    ops.push_back(mm_op(s.xn, L.w_qkv, s.qkv));
+    ops.push_back(copy_op(s.qkv, s.q, {embd, t, 1}, 0, {1, n_qkv, 0}, 0, {1, embd, 0}));
+    ops.push_back(copy_op(s.qkv, s.k, {kv_dim, t, 1}, embd, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
+    ops.push_back(copy_op(s.qkv, s.v, {kv_dim, t, 1}, embd + kv_dim, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
+    for (int which = 0; which < 2; ++which) {
+      ExecOp r;
+      r.kind = ExecKind::Rope;
+      r.in0 = which ? &s.k : &s.q; r.in1 = &m.rope_table; r.out = r.in0;
+      r.heads = which ? kv : heads; r.head_dim = dh; r.rot_dim = dh; r.pos_base = pos_base;
+      ops.push_back(r);
+    }
+    ops.push_back(copy_op(s.k, L.kt_cache, {dh, kv, t}, 0, {1, dh, kv * dh}, pos_base, {t_max, dh * t_max, 1}));
+    ops.push_back(copy_op(s.v, L.v_cache, {dh, kv, t}, 0, {1, dh, kv * dh}, pos_base * dh, {1, t_max * dh, dh}));
+    ExecOp f;
+    f.kind = ExecKind::FlashAttn;
+    f.in0 = &s.q; f.in1 = &L.kt_cache; f.in2 = &L.v_cache; f.out = &s.attn_flat;
+    f.flash.kv_len = pos_base + t; f.flash.pos_base = pos_base; f.flash.scale = 1.0f / std::sqrt((float)dh);
+    f.flash.token_major_heads = heads;
+    ops.push_back(f);
+    push_mlp_ops(m, ops, L, false, s.attn_flat, s.o, s.on, s.up, s.gate, *x_in, *x_out);
+    std::swap(x_in, x_out);
+  }
+  // final norm + lm_head on the last row (forward/mod.rs:231-270), then argmax
+  ops.push_back(copy_op(*x_in, s.last, {embd, 1, 1}, (t - 1) * embd, {1, 0, 0}, 0, {1, 0, 0}));
+  ExecOp n;
+  n.kind = ExecKind::RmsNorm;
+  n.in0 = &s.last; n.in1 = &m.output_norm; n.out = &s.last_n; n.f0 = c.rms_eps;
+  ops.push_back(n);
+  ops.push_back(mm_op(s.last_n, m.lm_head, m.logits));
+  ExecOp am;
+  am.kind = ExecKind::Argmax;
+  am.in0 = &m.logits; am.cell = &m.token_cell;
+  ops.push_back(am);
+  return ops;
+}
+
+int guarded(const std::function<void()> &f) {
+  ta_set_last_error("");
+  try {
+    f();
+    return 0;
+  } catch (const std::exception &e) {
+    ta_set_last_error(e.what());
+  } catch (...) {
+    ta_set_last_error("panic crossed tensor-ash C ABI boundary");
+  }
+  return -1;
+}
+
+void write_stats(ta_run_stats *out, const RunStats &st) {
+  if (!out) return;
+  out->has_gpu_time = st.gpu_time_ns ? 1u : 0u;
+  out->gpu_time_ns = st.gpu_time_ns.value_or(0);
+  out->n_calls = st.n_calls;
+  out->total_flops = st.total_flops;
+  const auto tf = st.tflops();
+  out->tflops = tf ? *tf : std::nan("");
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+ta_llama *ta_llama_create_random(const ta_executor *exec, const ta_llama_config *cfg) {
+  ta_llama *m = nullptr;
+  const int rc = guarded([&]() {
+    if (!exec) fail("ta_llama_create_random: exec is null");
+    if (!cfg) fail("ta_llama_create_random: cfg is null");
+    m = new ta_llama;
+    m->ctx = exec->ctx;
+    m->exec = exec->exec.get();
+    m->cfg = *cfg;
+    m->ctx->make_current();
+    build_model(*m);
+  });
+  if (rc != 0) {
+    delete m;
+    return nullptr;
+  }
+  return m;
+}
+
+void ta_llama_destroy(ta_llama *model) {
+  ta_set_last_error("");
+  delete model;
+}
+
+int ta_llama_reset(ta_llama *model) {
+  return guarded([&]() {
+    if (!model) fail("ta_llama_reset: model is null");
+    model->pos = 0;
+  });
+}
+
+int ta_llama_prefill(ta_llama *model, const uint32_t *tokens, uint32_t n, uint32_t *next_token,
+                     ta_run_stats *stats) {
+  return guarded([&]() {
+    if (!model) fail("ta_llama_prefill: model is null");
+    if (!tokens || n == 0) fail("ta_llama_prefill: prefill needs at least one token");
+    ta_llama &m = *model;
+    const ta_llama_config &c = m.cfg;
+    if (m.pos + n > c.t_max) fail("ta_llama_prefill: KV cache overflow (%u + %u > %u)", m.pos, n, c.t_max);
+    m.ctx->make_current();
+    const uint32_t kv_dim = c.kv_heads * c.head_dim;
+    PrefillScratch s;
+    auto f32 = [&](uint32_t r, uint32_t cols) { return make(m.ctx, {r, cols}, DType::F32); };
+    s.x_a = f32(n, c.embd); s.x_b = f32(n, c.embd); s.xn = f32(n, c.embd);
+    s.qkv = f32(n, c.embd + 2 * kv_dim);
+    s.q = f32(n, c.embd); s.k = f32(n, kv_dim); s.v = f32(n, kv_dim);
+    s.attn_flat = f32(n, c.embd); s.o = f32(n, c.embd); s.on = f32(n, c.embd);
+    s.up = f32(n, c.ffn); s.gate = f32(n, c.ffn);
+    s.last = f32(1, c.embd); s.last_n = f32(1, c.embd);
+    memcpy(m.token_ids.host, tokens, (size_t)n * 4);
+    m.token_ids.len = n;
+    const RunStats st = m.exec->run_exec_ops(prefill_ops(m, s, n, m.pos));
+    m.pos += n;
+    if (next_token) *next_token = *(volatile uint32_t *)m.token_cell.host;
+    write_stats(stats, st);
+  });
+}
+
+int ta_llama_decode(ta_llama *model, uint32_t first_token, uint32_t n, uint32_t *out_tokens,
+                    ta_run_stats *stats) {
+  return guarded([&]() {
+    if (!model) fail("ta_llama_decode: model is null");
+    ta_llama &m = *model;
+    if (n && !out_tokens) fail("ta_llama_decode: out_tokens is null");
+    if (m.pos + n > m.cfg.t_max) fail("ta_llama_decode: KV cache overflow (%u + %u > %u)", m.pos, n, m.cfg.t_max);
+    m.ctx->make_current();
+    RunStats total;
+    total.gpu_time_ns = 0;
+    if (n == 0) { write_stats(stats, total); return; }
+    // first input embedding: gather on the device from the token word
+    *(volatile uint32_t *)m.token_cell.host = first_token;
+    m.exec->embed_gather(m.token_cell, m.embd, m.x_a);
+    if (!m.decode_graph) {
+      *(volatile uint32_t *)m.pos_cell.host = m.pos;   // the eager pass inside prepare writes this slot
+      m.decode_graph = prepare_exec_ops(*m.exec, decode_ops(m));
+      // the eager pass and capture consumed x_a and rewrote it with the argmax token: restore the input
+      *(volatile uint32_t *)m.token_cell.host = first_token;
+      m.exec->embed_gather(m.token_cell, m.embd, m.x_a);
+    }
+    for (uint32_t i = 0; i < n; ++i) {
+      *(volatile uint32_t *)m.pos_cell.host = m.pos;
+      const RunStats st = m.decode_graph->run();
+      out_tokens[i] = *(volatile uint32_t *)m.token_cell.host;
+      m.pos += 1;
+      *total.gpu_time_ns += st.gpu_time_ns.value_or(0);
+      total.n_calls += st.n_calls;
+      total.total_flops += st.total_flops;
+    }
+    write_stats(stats, total);
+  });
+}
+
+int ta_llama_logits(ta_llama *model, float *out, size_t len) {
+  return guarded([&]() {
+    if (!model) fail("ta_llama_logits: model is null");
+    if (!out) fail("ta_llama_logits: out is null");
+    model->exec->download(model->logits, out, std::min(len, (size_t)model->cfg.vocab));
+  });
+}
+
+uint32_t ta_llama_position(const ta_llama *model) { return model ? model->pos : 0; }
+
+// benchmarks/THESES.md:46-50 formula: f16 bytes of every matrix read per token
+uint64_t ta_llama_weight_bytes_per_token(const ta_llama *model) {
+  if (!model) return 0;
+  const ta_llama_config &c = model->cfg;
+  const uint64_t kv_dim = (uint64_t)c.kv_heads * c.head_dim;
+  const uint64_t per_layer = 2ull * c.embd * c.embd + 2ull * c.embd * kv_dim + 3ull * c.embd * c.ffn;
+  return 2ull * (c.layers * per_layer + (uint64_t)c.embd * c.vocab);
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

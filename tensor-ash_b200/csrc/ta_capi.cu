@@ -18,27 +18,17 @@
 
 using namespace ta;
 
-struct ta_context {
-  std::shared_ptr<Context> ctx;
-};
-struct ta_executor {
-  std::shared_ptr<Context> ctx;
-  std::unique_ptr<Executor> exec;
-};
-struct ta_tensor {
-  Tensor tensor;
-};
-struct ta_prepared {
-  std::unique_ptr<PreparedOps> prepared;
-  std::shared_ptr<Context> ctx;
-};
-struct ta_pos_cell {
-  PosCell cell;
-};
+#include "ta_handles.hpp"
 
 namespace {
 
 thread_local std::string g_last_error;
+}  // namespace
+
+// shared with the other translation units that export C symbols
+void ta_set_last_error(const char *msg) { g_last_error = msg ? msg : ""; }
+
+namespace {
 
 int status_call(const std::function<void()> &f) {
   g_last_error.clear();
@@ -484,21 +474,14 @@ int ta_split_k2_noalloc(const float *a, const float *b, float *c, uint32_t m, ui
   });
 }
 
-int ta_run_ops_ex(const ta_executor *exec, const ta_matmul_op_ex *ops, size_t n_ops,
-                  uint32_t as_graph, ta_run_stats *stats) {
-  return status_call([&]() {
-    const ta_executor &e = checked_ref(exec, "ta_run_ops_ex: exec is null");
-    if (n_ops && !ops) fail("ta_run_ops_ex: ops is null");
-    std::vector<MatmulOp> v;
-    for (size_t i = 0; i < n_ops; ++i) {
-      const std::string label = strf("ta_run_ops_ex: op %zu", i);
-      MatmulOp op = checked_op(e, ops[i].op, label.c_str());
-      op.packed_b = ops[i].packed_b != 0;
-      if (ops[i].normed_weight) {
-        op.normed_weight = &checked_tensor(e, ops[i].normed_weight, label.c_str(), "normed_weight");
-        op.normed_eps = ops[i].normed_eps;
+static MatmulOp checked_op_ex(const ta_executor &e, const ta_matmul_op_ex &raw, const std::string &label) {
+      MatmulOp op = checked_op(e, raw.op, label.c_str());
+      op.packed_b = raw.packed_b != 0;
+      if (raw.normed_weight) {
+        op.normed_weight = &checked_tensor(e, raw.normed_weight, label.c_str(), "normed_weight");
+        op.normed_eps = raw.normed_eps;
       }
-      const ta_store_desc &s = ops[i].store;
+      const ta_store_desc &s = raw.store;
       if (s.kind > 3) fail("%s: store.kind %u is invalid (0..3)", label.c_str(), s.kind);
       op.store.kind = (StoreKind)s.kind;
       op.store.head_dim = s.head_dim;
@@ -513,9 +496,117 @@ int ta_run_ops_ex(const ta_executor *exec, const ta_matmul_op_ex *ops, size_t n_
           fail("%s: store.pos_cell belongs to a different Vulkan context", label.c_str());
         op.store.pos_cell = &s.pos_cell->cell;
       }
-      v.push_back(op);
-    }
+      return op;
+}
+
+int ta_run_ops_ex(const ta_executor *exec, const ta_matmul_op_ex *ops, size_t n_ops,
+                  uint32_t as_graph, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_run_ops_ex: exec is null");
+    if (n_ops && !ops) fail("ta_run_ops_ex: ops is null");
+    std::vector<MatmulOp> v;
+    for (size_t i = 0; i < n_ops; ++i) v.push_back(checked_op_ex(e, ops[i], strf("ta_run_ops_ex: op %zu", i)));
     write_stats(stats, as_graph ? e.exec->run_op_graph(v) : e.exec->run_ops(v));
+  });
+}
+
+static std::vector<ExecOp> checked_exec_ops(const ta_executor &e, const ta_exec_op *ops, size_t n, const char *operation) {
+  if (n && !ops) fail("%s: ops is null", operation);
+  std::vector<ExecOp> v(n);
+  for (size_t i = 0; i < n; ++i) {
+    const ta_exec_op &r = ops[i];
+    const std::string label = strf("%s: op %zu", operation, i);
+    ExecOp &o = v[i];
+    if (r.kind > TA_EXEC_EMBED_GATHER_ROWS) fail("%s: kind %u is invalid", label.c_str(), r.kind);
+    o.kind = (ExecKind)r.kind;
+    if (r.kind == TA_EXEC_MATMUL) o.mm = checked_op_ex(e, r.mm, label);
+    auto opt = [&](const ta_tensor *t, const char *name) -> const Tensor * {
+      return t ? &checked_tensor(e, t, label.c_str(), name) : nullptr;
+    };
+    o.in0 = opt(r.in0, "in0"); o.in1 = opt(r.in1, "in1"); o.in2 = opt(r.in2, "in2"); o.in3 = opt(r.in3, "in3");
+    o.out = opt(r.out, "out");
+    o.f0 = r.f0; o.u0 = r.u0; o.u1 = r.u1; o.u2 = r.u2;
+    o.heads = r.rope.heads; o.head_dim = r.rope.head_dim; o.rot_dim = r.rope.rot_dim; o.pos_base = r.rope.pos_base;
+    if (r.kind == TA_EXEC_COPY_STRIDED) {
+      o.src_offset = r.copy.src_offset; o.dst_offset = r.copy.dst_offset;
+      for (int d = 0; d < 3; ++d) {
+        o.extent[d] = r.copy.extent[d];
+        o.src_strides[d] = r.copy.src_strides[d];
+        o.strides[d] = r.copy.dst_strides[d];
+      }
+    } else {
+      o.dst_offset = r.dst_offset;
+      for (int d = 0; d < 3; ++d) o.strides[d] = r.dst_strides[d];
+    }
+    o.pos_scale = r.pos_scale;
+    o.flash.kv_len = r.flash.kv_len; o.flash.pos_base = r.flash.pos_base; o.flash.scale = r.flash.scale;
+    o.flash.token_major_heads = r.flash.token_major_heads;
+    o.flash.out_token_major_heads = r.flash.out_token_major_heads;
+    o.attn.kv_len = r.attn.kv_len; o.attn.scale = r.attn.scale;
+    o.attn.pos_cell = r.attn.pos_cell ? &r.attn.pos_cell->cell : nullptr;
+    o.cell = r.cell ? &r.cell->cell : nullptr;
+    o.tokens = r.tokens ? &r.tokens->ids : nullptr;
+  }
+  return v;
+}
+
+int ta_run_exec_ops(const ta_executor *exec, const ta_exec_op *ops, size_t n_ops, ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_run_exec_ops: exec is null");
+    write_stats(stats, e.exec->run_exec_ops(checked_exec_ops(e, ops, n_ops, "ta_run_exec_ops")));
+  });
+}
+
+ta_prepared *ta_prepared_create_exec(const ta_executor *exec, const ta_exec_op *ops, size_t n_ops) {
+  return create_call<ta_prepared>([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_prepared_create_exec: exec is null");
+    auto v = checked_exec_ops(e, ops, n_ops, "ta_prepared_create_exec");
+    auto *h = new ta_prepared;
+    h->ctx = e.ctx;
+    try {
+      h->prepared = prepare_exec_ops(*e.exec, v);
+    } catch (...) {
+      delete h;
+      throw;
+    }
+    return h;
+  });
+}
+
+ta_token_ids *ta_token_ids_create(const ta_context *ctx, uint32_t capacity) {
+  return create_call<ta_token_ids>([&]() {
+    const ta_context &c = checked_ref(ctx, "ta_token_ids_create: ctx is null");
+    if (capacity == 0) fail("ta_token_ids_create: capacity must be non-zero");
+    c.ctx->make_current();
+    auto *h = new ta_token_ids;
+    h->ids.ctx = c.ctx;
+    h->ids.capacity = capacity;
+    cudaError_t err = cudaHostAlloc((void **)&h->ids.host, (size_t)capacity * 4, cudaHostAllocMapped);
+    if (err == cudaSuccess) err = cudaHostGetDevicePointer((void **)&h->ids.device, h->ids.host, 0);
+    if (err != cudaSuccess) {
+      if (h->ids.host) cudaFreeHost(h->ids.host);
+      delete h;
+      fail("ta_token_ids_create: pinned allocation failed: %s", cudaGetErrorString(err));
+    }
+    return h;
+  });
+}
+void ta_token_ids_destroy(ta_token_ids *ids) {
+  g_last_error.clear();
+  if (!ids) return;
+  if (ids->ids.host) {
+    cudaSetDevice(ids->ids.ctx->device);
+    cudaFreeHost(ids->ids.host);
+  }
+  delete ids;
+}
+int ta_token_ids_set(ta_token_ids *ids, const uint32_t *tokens, uint32_t n) {
+  return status_call([&]() {
+    if (!ids) fail("ta_token_ids_set: ids is null");
+    if (n && !tokens) fail("ta_token_ids_set: tokens is null");
+    if (n > ids->ids.capacity) fail("ta_token_ids_set: %u tokens exceed capacity %u", n, ids->ids.capacity);
+    memcpy(ids->ids.host, tokens, (size_t)n * 4);
+    ids->ids.len = n;
   });
 }
 

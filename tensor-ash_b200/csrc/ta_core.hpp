@@ -316,6 +316,54 @@ struct AttnDecodeDesc {
   const PosCell *pos_cell = nullptr;
 };
 
+// Token-id list in pinned, device-mapped host memory (TokenIdBuffer of
+// src/executor/cells.rs:140-201): prefill writes the prompt ids here and a
+// gather kernel reads them on the device.
+struct TokenIds {
+  std::shared_ptr<Context> ctx;
+  uint32_t *host = nullptr, *device = nullptr;
+  uint32_t capacity = 0, len = 0;
+};
+
+// One op of a mixed graph (ExecOp of src/executor/graph_ops.rs:27-161).
+// Operand slots by kind:
+//   Matmul           mm
+//   RmsNorm          in0 input, in1 weight, out; f0 eps
+//   LayerNorm        in0 input, in1 weight, in2 bias, out; f0 eps
+//   SoftmaxRows      in0 input, out; f0 scale; u0 mask kind, u1 valid/prefix, u2 rows per group
+//   Rope             in0 input, in1 table, out; heads/head_dim/rot_dim/pos_base; cell = position (optional)
+//   RopeScatter      in0 input, in1 table, out = dst; rope fields; dst_offset, strides[3], pos_scale; cell
+//   CopyStrided      in0 src, out dst; extent, src_offset, src_strides, dst_offset, strides
+//   Binary           in0 a, in1 b, out; u0 mode (0 a+beta*b, 1 silu(a)*b); f0 beta
+//   AttnDecode       in0 q, in1 kt, in2 v, in3 scratch, out; attn
+//   FlashAttn        in0 q, in1 kt, in2 v, out; flash
+//   Argmax           in0 input; cell = result word
+//   EmbedGather      cell = token word; in0 table, out
+//   EmbedGatherRows  tokens; in0 table, out [n, embd]
+enum class ExecKind : uint32_t {
+  Matmul = 0, RmsNorm, LayerNorm, SoftmaxRows, Rope, RopeScatter, CopyStrided, Binary, AttnDecode,
+  FlashAttn, Argmax, EmbedGather, EmbedGatherRows
+};
+
+struct ExecOp {
+  ExecKind kind = ExecKind::Matmul;
+  MatmulOp mm;
+  const Tensor *in0 = nullptr, *in1 = nullptr, *in2 = nullptr, *in3 = nullptr, *out = nullptr;
+  float f0 = 0.0f;
+  uint32_t u0 = 0, u1 = 0, u2 = 0;
+  uint32_t heads = 0, head_dim = 0, rot_dim = 0, pos_base = 0;
+  uint32_t extent[3] = {0, 0, 0}, src_offset = 0, src_strides[3] = {0, 0, 0};
+  uint32_t dst_offset = 0, strides[3] = {0, 0, 0}, pos_scale = 0;
+  FlashAttentionDesc flash;
+  AttnDecodeDesc attn;
+  const PosCell *cell = nullptr;
+  const TokenIds *tokens = nullptr;
+};
+
+struct Slot;
+// A planned op: only launches.
+using Launch = std::function<void(Slot &, cudaStream_t)>;
+
 constexpr uint32_t ATTN_DECODE_MAX_CHUNKS = 32;
 inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
   const uint32_t c = (kv_len + 31) / 32;
@@ -377,6 +425,19 @@ class Executor {
                                     const Tensor &scratch, const Tensor &out, const AttnDecodeDesc &desc) const;
   RunStats attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &scratch,
                        const Tensor &out, const AttnDecodeDesc &desc);
+  // Mixed graphs (src/executor/graph_ops.rs:249-353).  n_launches returns how
+  // many kernels the op enqueues.
+  Launch plan_exec_op(const ExecOp &op, uint64_t *flops, size_t *n_calls) const;
+  Launch plan_exec_op_tail(const ExecOp &op, size_t *n_calls) const;
+  RunStats run_exec_ops(const std::vector<ExecOp> &ops);
+  RunStats run_single(const ExecOp &op);
+  RunStats binary(const Tensor &a, const Tensor &b, const Tensor &out, uint32_t mode, float beta);
+  RunStats rope_scatter(const Tensor &in, const Tensor &table, const Tensor &dst, uint32_t heads,
+                        uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base, uint32_t dst_offset,
+                        const uint32_t strides[3], uint32_t pos_scale, const PosCell *cell);
+  RunStats argmax(const Tensor &in, const PosCell &result);
+  RunStats embed_gather(const PosCell &token, const Tensor &table, const Tensor &out);
+  RunStats embed_gather_rows(const TokenIds &tokens, const Tensor &table, const Tensor &out);
   RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
                        const Tensor *norm_w, float eps);
   void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
@@ -412,6 +473,7 @@ class Executor {
   friend struct PreparedOps;
   RunStats run_ops_impl(const std::vector<MatmulOp> &ops, bool graph);
   RunStats timed(Slot &slot, size_t n_calls, uint64_t flops, const std::function<void(cudaStream_t)> &record);
+  friend std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<ExecOp> &ops);
 
   std::shared_ptr<Context> ctx_;
   int selection_;  // -2 auto, else registry index
@@ -423,6 +485,14 @@ class Executor {
   mutable std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> tuned_;
   std::string tune_path_;
 };
+
+struct SlotGuard {
+  Executor &e;
+  Slot &s;
+  SlotGuard(Executor &e_, Slot &s_) : e(e_), s(s_) {}
+  ~SlotGuard() { e.release_slot(s); }
+};
+void validate_op_tensors(const Executor &e, const MatmulOp &op);
 
 // Record-once / replay-many op batch (src/executor/prepared.rs:46-353).
 struct PreparedOps {
@@ -443,6 +513,7 @@ struct PreparedOps {
 };
 std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<MatmulOp> &ops,
                                          bool as_graph);
+std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<ExecOp> &ops);
 
 // ------------------------------------------------------------------ kernel launchers
 // Implemented beside each kernel.  All are asynchronous on `stream`.
@@ -472,8 +543,17 @@ void launch_layer_norm(const float *in, const float *w, const float *b, float *o
                        uint32_t cols, float eps, cudaStream_t stream);
 void launch_rope(const float *in, const float *table, float *out, uint32_t tokens, uint32_t heads,
                  uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base, cudaStream_t stream);
-void launch_copy_strided(const float *src, float *dst, const uint32_t extent[3], uint32_t src_off,
-                         const uint32_t src_strides[3], uint32_t dst_off,
+void launch_copy_strided(const void *src, bool src_f16, void *dst, bool dst_f16, const uint32_t extent[3],
+                         uint32_t src_off, const uint32_t src_strides[3], uint32_t dst_off,
                          const uint32_t dst_strides[3], cudaStream_t stream);
+void launch_binary(const float *a, const float *b, float *out, uint32_t n, uint32_t mode, float beta,
+                   cudaStream_t stream);
+void launch_argmax(const float *in, uint32_t n, uint32_t *result, cudaStream_t stream);
+void launch_embed_gather(const uint32_t *tokens, uint32_t n_tokens, const void *table, bool table_f16,
+                         float *out, uint32_t embd, uint32_t vocab, cudaStream_t stream);
+void launch_rope_scatter(const float *in, const float *table, void *dst, bool dst_f16, uint32_t tokens,
+                         uint32_t heads, uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base,
+                         uint32_t dst_off, const uint32_t strides[3], uint32_t pos_scale,
+                         const uint32_t *pos_ptr, cudaStream_t stream);
 
 }  // namespace ta

@@ -1,0 +1,520 @@
+// Mixed op graphs: matmuls and model ops in one submission or one captured
+// replay (ExecOp, run_exec_ops, prepare_exec_ops of the reference,
+// src/executor/graph_ops.rs:27-161, 249-353), and the single-op entry points
+// built on the same planners.
+//
+// Every op is validated and planned before anything is enqueued (the
+// reference's "validated and planned before anything is recorded",
+// graph_ops.rs:246-248): planning returns a closure that only launches.  All
+// closures of one submission run on one in-order CUDA stream, which is what
+// resolves RAW / WAW / WAR hazards between ops here; the reference's explicit
+// barrier bookkeeping (HazardCursor) has no CUDA counterpart to build.
+#include <algorithm>
+#include <functional>
+
+#include "ta_core.hpp"
+
+namespace ta {
+
+namespace {
+void ensure_f32(const Executor &e, const Tensor &t, const char *op, const char *operand) {
+  e.validate_tensor(t, operand);
+  if (t.dtype != DType::F32) fail("%s: %s must be f32 storage", op, operand);
+}
+void ensure_same_shape(const char *op, const Tensor &a, const Tensor &b) {
+  if (a.shape != b.shape)
+    fail("%s: input shape %s != output shape %s", op, a.shape_str().c_str(), b.shape_str().c_str());
+}
+void rows_cols(const Tensor &t, const char *label, uint32_t *rows, uint32_t *cols) {
+  *cols = t.shape.back();
+  const uint64_t r = t.len() / *cols;
+  if (r > 0xffffffffull) fail("%s: row count %llu exceeds u32", label, (unsigned long long)r);
+  *rows = (uint32_t)r;
+}
+}  // namespace
+
+FlashParams Executor::plan_flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v,
+                                           const Tensor &out, const FlashAttentionDesc &desc) const {
+  ensure_f32(*this, q, "run_flash_attention", "q");
+  ensure_f32(*this, out, "run_flash_attention", "out");
+  validate_tensor(kt, "kt");
+  validate_tensor(v, "v");
+  if (kt.dtype != v.dtype)
+    fail("run_flash_attention: kt (%s) and v (%s) must share a storage type", dtype_name(kt.dtype),
+         dtype_name(v.dtype));
+  if (kt.shape.size() != 3) fail("run_flash_attention: kt must be [H_kv, dh, T_max], got %s", kt.shape_str().c_str());
+  if (v.shape.size() != 3) fail("run_flash_attention: v must be [H_kv, T_max, dh], got %s", v.shape_str().c_str());
+  const uint32_t kv_heads = kt.shape[0], dh = kt.shape[1], t_max = kt.shape[2];
+  if (v.shape[1] != t_max || v.shape[0] != kv_heads || v.shape[2] != dh)
+    fail("run_flash_attention: inconsistent cache shapes kt %s, v %s", kt.shape_str().c_str(), v.shape_str().c_str());
+  FlashParams p{};
+  uint32_t heads, t_q;
+  if (desc.token_major_heads) {
+    heads = desc.token_major_heads;
+    t_q = q.shape[0];
+    if (q.len() != (uint64_t)t_q * heads * dh)
+      fail("run_flash_attention: token-major q %s does not hold [T=%u, H=%u, dh=%u]", q.shape_str().c_str(), t_q, heads, dh);
+    p.q_head_stride = dh;
+    p.q_row_stride = heads * dh;
+  } else {
+    if (q.shape.size() != 3) fail("run_flash_attention: q must be [H, T_q, dh], got %s", q.shape_str().c_str());
+    heads = q.shape[0];
+    t_q = q.shape[1];
+    if (q.shape[2] != dh)
+      fail("run_flash_attention: q dh %u != cache dh %u (q %s, kt %s)", q.shape[2], dh, q.shape_str().c_str(),
+           kt.shape_str().c_str());
+    p.q_head_stride = t_q * dh;
+    p.q_row_stride = dh;
+  }
+  if (desc.out_token_major_heads) {
+    if (desc.out_token_major_heads != heads)
+      fail("run_flash_attention: out_token_major_heads %u != q heads %u", desc.out_token_major_heads, heads);
+    if (out.len() != (uint64_t)t_q * heads * dh)
+      fail("run_flash_attention: token-major out %s does not hold [T=%u, H=%u, dh=%u]", out.shape_str().c_str(), t_q, heads, dh);
+    p.o_head_stride = dh;
+    p.o_row_stride = heads * dh;
+  } else if (desc.token_major_heads) {
+    if (out.len() != q.len())
+      fail("run_flash_attention: out shape %s must match token-major q %s", out.shape_str().c_str(), q.shape_str().c_str());
+    p.o_head_stride = p.q_head_stride;
+    p.o_row_stride = p.q_row_stride;
+  } else {
+    if (out.shape != q.shape)
+      fail("run_flash_attention: out shape %s must equal q shape %s", out.shape_str().c_str(), q.shape_str().c_str());
+    p.o_head_stride = p.q_head_stride;
+    p.o_row_stride = p.q_row_stride;
+  }
+  if (kv_heads == 0 || heads % kv_heads) fail("run_flash_attention: H=%u must be a multiple of H_kv=%u", heads, kv_heads);
+  if (desc.kv_len > t_max) fail("run_flash_attention: kv_len %u exceeds cache T_max %u", desc.kv_len, t_max);
+  if (dh != 64 && dh != 128) fail("run_flash_attention: head dimension %u unsupported (64 or 128)", dh);
+  if (q.ptr() == out.ptr()) fail("run_flash_attention: q and out must be different tensors");
+  p.q = static_cast<const float *>(q.ptr());
+  p.kt = kt.ptr();
+  p.v = v.ptr();
+  p.out = static_cast<float *>(out.ptr());
+  p.heads = heads; p.group = heads / kv_heads; p.dh = dh; p.t_q = t_q; p.t_max = t_max;
+  p.kv_len = desc.kv_len; p.pos_base = desc.pos_base; p.scale = desc.scale;
+  p.kv_f16 = kt.dtype == DType::F16;
+  return p;
+}
+
+AttnDecodeParams Executor::plan_attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v,
+                                            const Tensor &scratch, const Tensor &out,
+                                            const AttnDecodeDesc &desc) const {
+  ensure_f32(*this, q, "run_attn_decode", "q");
+  validate_tensor(kt, "kt");
+  validate_tensor(v, "v");
+  ensure_f32(*this, scratch, "run_attn_decode", "scratch");
+  ensure_f32(*this, out, "run_attn_decode", "out");
+  if (kt.dtype != v.dtype)
+    fail("run_attn_decode: kt (%s) and v (%s) must share a storage type", dtype_name(kt.dtype), dtype_name(v.dtype));
+  if (kt.shape.size() != 3) fail("run_attn_decode: kt must be [H_kv, dh, T_max], got %s", kt.shape_str().c_str());
+  if (v.shape.size() != 3) fail("run_attn_decode: v must be [H_kv, T_max, dh], got %s", v.shape_str().c_str());
+  const uint32_t kv_heads = kt.shape[0], dh = kt.shape[1], t_max = kt.shape[2];
+  if (v.shape[2] != dh || v.shape[1] != t_max || v.shape[0] != kv_heads)
+    fail("run_attn_decode: inconsistent caches kt %s, v %s", kt.shape_str().c_str(), v.shape_str().c_str());
+  if (dh != 64) fail("run_attn_decode: head dimension %u unsupported (compiled variant: 64)", dh);
+  const uint64_t heads_elems = (uint64_t)kv_heads * dh;
+  if (q.len() % heads_elems)
+    fail("run_attn_decode: q length %llu must be kv_heads*group*dh (kv_heads %u, dh %u)",
+         (unsigned long long)q.len(), kv_heads, dh);
+  const uint64_t group = q.len() / heads_elems;
+  if (group == 0 || group > 8) fail("run_attn_decode: GQA group %llu unsupported (1..=8)", (unsigned long long)group);
+  if (out.len() != q.len())
+    fail("run_attn_decode: out length %llu must equal q length %llu", (unsigned long long)out.len(),
+         (unsigned long long)q.len());
+  if (desc.kv_len == 0 || desc.kv_len > t_max) fail("run_attn_decode: kv_len %u out of range 1..=%u", desc.kv_len, t_max);
+  if (desc.pos_cell && desc.pos_cell->ctx.get() != ctx_.get())
+    fail("run_attn_decode: pos cell belongs to a different context");
+  const uint32_t num_chunks = desc.pos_cell ? ATTN_DECODE_MAX_CHUNKS : attn_decode_num_chunks(desc.kv_len);
+  const uint64_t needed = (uint64_t)kv_heads * num_chunks * group * (dh + 2);
+  if (scratch.len() < needed)
+    fail("run_attn_decode: scratch length %llu < required %llu (kv_heads %u * chunks %u * group %llu * (dh+2))",
+         (unsigned long long)scratch.len(), (unsigned long long)needed, kv_heads, num_chunks,
+         (unsigned long long)group);
+  AttnDecodeParams p{};
+  p.q = static_cast<const float *>(q.ptr());
+  p.kt = kt.ptr();
+  p.v = v.ptr();
+  p.scratch = static_cast<float *>(scratch.ptr());
+  p.out = static_cast<float *>(out.ptr());
+  p.kv_heads = kv_heads; p.group = (uint32_t)group; p.t_max = t_max; p.kv_len = desc.kv_len;
+  p.num_chunks = num_chunks; p.scale = desc.scale; p.kv_f16 = kt.dtype == DType::F16;
+  p.pos_ptr = desc.pos_cell ? desc.pos_cell->device : nullptr;
+  return p;
+}
+
+// ------------------------------------------------------------------ planning
+namespace {
+const Tensor &need(const Tensor *t, const char *op, const char *operand) {
+  if (!t) fail("%s: %s is null", op, operand);
+  return *t;
+}
+const uint32_t *cell_ptr(const Executor &e, const PosCell *cell, const char *op) {
+  if (!cell) return nullptr;
+  if (cell->ctx.get() != e.context().get()) fail("%s: position/result cell belongs to a different context", op);
+  return cell->device;
+}
+// Shared rope-geometry validation (src/executor/elementwise/ops.rs:176-207).
+uint32_t rope_tokens(const char *op, const Tensor &in, const Tensor &table, const ExecOp &o) {
+  if (o.rot_dim < 2 || o.rot_dim % 2 || o.rot_dim > o.head_dim)
+    fail("%s: rot_dim %u must be even, >= 2, and <= head_dim %u", op, o.rot_dim, o.head_dim);
+  const uint64_t vec = (uint64_t)o.heads * o.head_dim;
+  if (vec == 0 || in.len() % vec)
+    fail("%s: input length %llu is not a multiple of heads*head_dim %llu", op, (unsigned long long)in.len(),
+         (unsigned long long)vec);
+  const uint64_t tokens64 = in.len() / vec;
+  if (tokens64 > 0xffffffffull) fail("%s: token count exceeds u32", op);
+  const uint64_t needed = ((uint64_t)o.pos_base + tokens64) * o.rot_dim;
+  if (table.len() < needed)
+    fail("%s: table length %llu < required %llu (pos_base %u + %llu tokens, rot_dim %u)", op,
+         (unsigned long long)table.len(), (unsigned long long)needed, o.pos_base,
+         (unsigned long long)tokens64, o.rot_dim);
+  return (uint32_t)tokens64;
+}
+}  // namespace
+
+Launch Executor::plan_exec_op(const ExecOp &o, uint64_t *flops, size_t *n_calls) const {
+  if (n_calls) *n_calls += 1;
+  switch (o.kind) {
+    case ExecKind::Matmul: {
+      validate_op_tensors(*this, o.mm);
+      const ResolvedMatmul r = ResolvedMatmul::from_op(o.mm);
+      const Route route = plan_op(o.mm, r, false);   // data-parallel routes only inside graphs
+      if (flops) *flops += r.total_flops;
+      const MatmulOp mm = o.mm;
+      Executor *self = const_cast<Executor *>(this);
+      return [self, mm, r, route](Slot &slot, cudaStream_t st) { self->enqueue_op(mm, r, route, slot, st); };
+    }
+    case ExecKind::RmsNorm:
+    case ExecKind::LayerNorm: {
+      const bool ln = o.kind == ExecKind::LayerNorm;
+      const char *name = ln ? "run_layer_norm" : "run_rms_norm";
+      const Tensor &in = need(o.in0, name, "input"), &w = need(o.in1, name, "weight"), &out = need(o.out, name, "output");
+      ensure_f32(*this, in, name, "input");
+      ensure_f32(*this, w, name, "weight");
+      ensure_f32(*this, out, name, "output");
+      ensure_same_shape(name, in, out);
+      uint32_t rows, cols;
+      rows_cols(in, name, &rows, &cols);
+      if (w.len() != cols) fail("%s: weight length %llu != row length %u", name, (unsigned long long)w.len(), cols);
+      const float *bp = nullptr;
+      if (ln) {
+        const Tensor &b = need(o.in2, name, "bias");
+        ensure_f32(*this, b, name, "bias");
+        if (b.len() != cols) fail("%s: bias length %llu != row length %u", name, (unsigned long long)b.len(), cols);
+        bp = (const float *)b.ptr();
+      }
+      const float *ip = (const float *)in.ptr(), *wp = (const float *)w.ptr();
+      float *op = (float *)out.ptr();
+      const float eps = o.f0;
+      if (ln) return [=](Slot &, cudaStream_t st) { launch_layer_norm(ip, wp, bp, op, rows, cols, eps, st); };
+      return [=](Slot &, cudaStream_t st) { launch_rms_norm(ip, wp, op, rows, cols, eps, st); };
+    }
+    case ExecKind::SoftmaxRows: {
+      const Tensor &in = need(o.in0, "run_softmax_rows", "input"), &out = need(o.out, "run_softmax_rows", "output");
+      ensure_f32(*this, in, "run_softmax_rows", "input");
+      ensure_f32(*this, out, "run_softmax_rows", "output");
+      ensure_same_shape("run_softmax_rows", in, out);
+      uint32_t rows, cols;
+      rows_cols(in, "run_softmax_rows", &rows, &cols);
+      if (o.u0 > 2) fail("run_softmax_rows: mask kind %u is invalid (0=full 1=prefix 2=causal)", o.u0);
+      if (o.u0 == 2 && (o.u2 == 0 || rows % o.u2))
+        fail("run_softmax_rows: rows_per_group %u must divide rows %u", o.u2, rows);
+      const float *ip = (const float *)in.ptr();
+      float *op = (float *)out.ptr();
+      const float scale = o.f0;
+      const uint32_t mk = o.u0, vp = o.u1, rpg = o.u2;
+      return [=](Slot &, cudaStream_t st) { launch_softmax_rows(ip, op, rows, cols, scale, mk, vp, rpg, st); };
+    }
+    case ExecKind::Rope: {
+      const Tensor &in = need(o.in0, "run_rope", "input"), &tab = need(o.in1, "run_rope", "table"),
+                   &out = need(o.out, "run_rope", "output");
+      ensure_f32(*this, in, "run_rope", "input");
+      ensure_f32(*this, out, "run_rope", "output");
+      ensure_f32(*this, tab, "run_rope", "table");
+      ensure_same_shape("run_rope", in, out);
+      const uint32_t tokens = rope_tokens("run_rope", in, tab, o);
+      const float *ip = (const float *)in.ptr(), *tp = (const float *)tab.ptr();
+      float *op = (float *)out.ptr();
+      const uint32_t heads = o.heads, hd = o.head_dim, rd = o.rot_dim, pb = o.pos_base;
+      return [=](Slot &, cudaStream_t st) { launch_rope(ip, tp, op, tokens, heads, hd, rd, pb, st); };
+    }
+    case ExecKind::RopeScatter: {
+      const Tensor &in = need(o.in0, "run_rope_scatter", "input"), &tab = need(o.in1, "run_rope_scatter", "table"),
+                   &dst = need(o.out, "run_rope_scatter", "dst");
+      ensure_f32(*this, in, "run_rope_scatter", "input");
+      ensure_f32(*this, tab, "run_rope_scatter", "table");
+      validate_tensor(dst, "dst");
+      if (in.ptr() == dst.ptr()) fail("run_rope_scatter: input and dst must be different tensors");
+      const uint32_t tokens = rope_tokens("run_rope_scatter", in, tab, o);
+      const uint64_t max_index = (uint64_t)o.dst_offset + (uint64_t)(tokens - 1) * o.strides[0] +
+                                 (uint64_t)(o.heads - 1) * o.strides[1] + (uint64_t)(o.head_dim - 1) * o.strides[2];
+      if (max_index >= dst.len())
+        fail("run_rope_scatter: destination access reaches element %llu but dst has %llu",
+             (unsigned long long)max_index, (unsigned long long)dst.len());
+      if (o.head_dim % 2) fail("run_rope_scatter: head_dim %u must be even", o.head_dim);
+      const float *ip = (const float *)in.ptr(), *tp = (const float *)tab.ptr();
+      void *dp = dst.ptr();
+      const bool f16 = dst.dtype == DType::F16;
+      const uint32_t *pp = cell_ptr(*this, o.cell, "run_rope_scatter");
+      const ExecOp oc = o;
+      return [=](Slot &, cudaStream_t st) {
+        launch_rope_scatter(ip, tp, dp, f16, tokens, oc.heads, oc.head_dim, oc.rot_dim, oc.pos_base, oc.dst_offset,
+                            oc.strides, oc.pos_scale, pp, st);
+      };
+    }
+    case ExecKind::CopyStrided: {
+      const Tensor &src = need(o.in0, "run_copy_strided", "src"), &dst = need(o.out, "run_copy_strided", "dst");
+      validate_tensor(src, "src");
+      validate_tensor(dst, "dst");
+      if (src.ptr() == dst.ptr()) fail("run_copy_strided: src and dst must be different tensors");
+      if (!o.extent[0] || !o.extent[1] || !o.extent[2])
+        fail("run_copy_strided: extent [%u, %u, %u] has a zero axis", o.extent[0], o.extent[1], o.extent[2]);
+      auto max_index = [&](uint32_t off, const uint32_t st[3]) {
+        uint64_t v = off;
+        for (int i = 0; i < 3; ++i) v += (uint64_t)(o.extent[i] - 1) * st[i];
+        return v;
+      };
+      if (max_index(o.src_offset, o.src_strides) >= src.len())
+        fail("run_copy_strided: source access reaches element %llu but src has %llu",
+             (unsigned long long)max_index(o.src_offset, o.src_strides), (unsigned long long)src.len());
+      if (max_index(o.dst_offset, o.strides) >= dst.len())
+        fail("run_copy_strided: destination access reaches element %llu but dst has %llu",
+             (unsigned long long)max_index(o.dst_offset, o.strides), (unsigned long long)dst.len());
+      if ((uint64_t)o.extent[0] * o.extent[1] * o.extent[2] > 0xffffffffull)
+        fail("run_copy_strided: extent product exceeds u32");
+      const void *sp = src.ptr();
+      void *dp = dst.ptr();
+      const bool sf = src.dtype == DType::F16, df = dst.dtype == DType::F16;
+      const ExecOp oc = o;
+      return [=](Slot &, cudaStream_t st) {
+        launch_copy_strided(sp, sf, dp, df, oc.extent, oc.src_offset, oc.src_strides, oc.dst_offset, oc.strides, st);
+      };
+    }
+    case ExecKind::Binary: {
+      const Tensor &a = need(o.in0, "run_binary", "a"), &b = need(o.in1, "run_binary", "b"), &out = need(o.out, "run_binary", "out");
+      ensure_f32(*this, a, "run_binary", "a");
+      ensure_f32(*this, out, "run_binary", "out");
+      validate_tensor(b, "b");
+      if (b.dtype != a.dtype) fail("run_binary: b (%s) must match a (%s) storage", dtype_name(b.dtype), dtype_name(a.dtype));
+      if (a.len() != b.len() || a.len() != out.len())
+        fail("run_binary: element counts differ (a %llu, b %llu, out %llu)", (unsigned long long)a.len(),
+             (unsigned long long)b.len(), (unsigned long long)out.len());
+      if (a.len() > 0xffffffffull) fail("run_binary: too large");
+      if (o.u0 > 1) fail("run_binary: mode %u is invalid (0=add_scaled 1=silu_mul)", o.u0);
+      const float *ap = (const float *)a.ptr(), *bp = (const float *)b.ptr();
+      float *op = (float *)out.ptr();
+      const uint32_t n = (uint32_t)a.len(), mode = o.u0;
+      const float beta = o.f0;
+      return [=](Slot &, cudaStream_t st) { launch_binary(ap, bp, op, n, mode, beta, st); };
+    }
+    default:
+      break;
+  }
+  return plan_exec_op_tail(o, n_calls);
+}
+
+Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
+  switch (o.kind) {
+    case ExecKind::AttnDecode: {
+      const AttnDecodeParams p = plan_attn_decode(need(o.in0, "run_attn_decode", "q"), need(o.in1, "run_attn_decode", "kt"),
+                                                  need(o.in2, "run_attn_decode", "v"), need(o.in3, "run_attn_decode", "scratch"),
+                                                  need(o.out, "run_attn_decode", "out"), o.attn);
+      if (n_calls) *n_calls += 1;   // two dispatches
+      return [p](Slot &, cudaStream_t st) { launch_attn_decode(p, st); };
+    }
+    case ExecKind::FlashAttn: {
+      const FlashParams p = plan_flash_attention(need(o.in0, "run_flash_attention", "q"), need(o.in1, "run_flash_attention", "kt"),
+                                                 need(o.in2, "run_flash_attention", "v"), need(o.out, "run_flash_attention", "out"),
+                                                 o.flash);
+      return [p](Slot &, cudaStream_t st) { launch_flash_prefill(p, st); };
+    }
+    case ExecKind::Argmax: {
+      const Tensor &in = need(o.in0, "run_argmax", "input");
+      ensure_f32(*this, in, "run_argmax", "input");
+      if (!o.cell) fail("run_argmax: result cell is null");
+      if (o.cell->ctx.get() != ctx_.get()) fail("run_argmax: result buffer belongs to a different context");
+      if (in.len() > 0xffffffffull) fail("run_argmax: input too large");
+      const float *ip = (const float *)in.ptr();
+      const uint32_t n = (uint32_t)in.len();
+      uint32_t *rp = o.cell->device;
+      return [=](Slot &, cudaStream_t st) { launch_argmax(ip, n, rp, st); };
+    }
+    case ExecKind::EmbedGather:
+    case ExecKind::EmbedGatherRows: {
+      const bool rows = o.kind == ExecKind::EmbedGatherRows;
+      const Tensor &table = need(o.in0, "run_embed_gather", "table"), &out = need(o.out, "run_embed_gather", "out");
+      validate_tensor(table, "table");
+      ensure_f32(*this, out, "run_embed_gather", "out");
+      if (table.shape.size() != 2)
+        fail("run_embed_gather: table must be [vocab, embd], got %s", table.shape_str().c_str());
+      const uint32_t vocab = table.shape[0], embd = table.shape[1];
+      uint32_t n_tokens = 1;
+      const uint32_t *tp;
+      if (rows) {
+        if (!o.tokens) fail("run_embed_gather: token buffer is null");
+        if (o.tokens->ctx.get() != ctx_.get()) fail("run_embed_gather: token buffer belongs to a different context");
+        n_tokens = o.tokens->len;
+        if (n_tokens == 0) fail("run_embed_gather: token buffer is empty");
+        tp = o.tokens->device;
+      } else {
+        if (!o.cell) fail("run_embed_gather: token cell is null");
+        if (o.cell->ctx.get() != ctx_.get()) fail("run_embed_gather: token buffer belongs to a different context");
+        tp = o.cell->device;
+      }
+      if (out.len() != (uint64_t)n_tokens * embd)
+        fail("run_embed_gather: out length %llu != n_tokens %u * embd %u", (unsigned long long)out.len(), n_tokens, embd);
+      const void *tab = table.ptr();
+      const bool tf16 = table.dtype == DType::F16;
+      float *op = (float *)out.ptr();
+      return [=](Slot &, cudaStream_t st) { launch_embed_gather(tp, n_tokens, tab, tf16, op, embd, vocab, st); };
+    }
+    default:
+      fail("exec op kind %u is not recognised", (unsigned)o.kind);
+  }
+}
+
+// ------------------------------------------------------------------ submission
+RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
+  if (ops.empty()) return RunStats{std::nullopt, 0, 0};
+  uint64_t flops = 0;
+  size_t n_calls = 0;
+  std::vector<Launch> plan;
+  plan.reserve(ops.size());
+  for (const ExecOp &op : ops) plan.push_back(plan_exec_op(op, &flops, &n_calls));
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  return timed(slot, n_calls, flops, [&](cudaStream_t st) {
+    for (const Launch &l : plan) l(slot, st);
+  });
+}
+
+RunStats Executor::run_single(const ExecOp &op) { return run_exec_ops({op}); }
+
+std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<ExecOp> &ops) {
+  if (ops.empty()) fail("prepare_exec_ops: empty op list");
+  exec.context()->make_current();
+  auto prep = std::make_unique<PreparedOps>();
+  prep->exec = &exec;
+  std::vector<Launch> plan;
+  plan.reserve(ops.size());
+  for (const ExecOp &op : ops) plan.push_back(exec.plan_exec_op(op, &prep->total_flops, &prep->n_calls));
+  TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
+  TA_CUDA(cudaEventCreate(&prep->ev_begin));
+  TA_CUDA(cudaEventCreate(&prep->ev_end));
+  Slot &slot = exec.checkout_slot();
+  {
+    SlotGuard g(exec, slot);
+    // Run once eagerly: first-use set-up (function attributes, tensor maps) must
+    // not happen inside the capture, and it proves the batch launches at all.
+    for (const Launch &l : plan) l(slot, prep->stream);
+    TA_CUDA(cudaStreamSynchronize(prep->stream));
+    TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
+    try {
+      for (const Launch &l : plan) l(slot, prep->stream);
+    } catch (...) {
+      cudaGraph_t dead = nullptr;
+      cudaStreamEndCapture(prep->stream, &dead);
+      if (dead) cudaGraphDestroy(dead);
+      throw;
+    }
+    TA_CUDA(cudaStreamEndCapture(prep->stream, &prep->graph));
+  }
+  TA_CUDA(cudaGraphInstantiate(&prep->graph_exec, prep->graph, 0));
+  return prep;
+}
+
+// ------------------------------------------------------------------ single-op entry points
+RunStats Executor::softmax_rows(const Tensor &in, const Tensor &out, float scale, uint32_t mask_kind,
+                                uint32_t valid_or_prefix, uint32_t rows_per_group) {
+  ExecOp o;
+  o.kind = ExecKind::SoftmaxRows;
+  o.in0 = &in; o.out = &out; o.f0 = scale; o.u0 = mask_kind; o.u1 = valid_or_prefix; o.u2 = rows_per_group;
+  return run_single(o);
+}
+RunStats Executor::rms_norm(const Tensor &in, const Tensor &w, const Tensor &out, float eps) {
+  ExecOp o;
+  o.kind = ExecKind::RmsNorm;
+  o.in0 = &in; o.in1 = &w; o.out = &out; o.f0 = eps;
+  return run_single(o);
+}
+RunStats Executor::layer_norm(const Tensor &in, const Tensor &w, const Tensor &b, const Tensor &out, float eps) {
+  ExecOp o;
+  o.kind = ExecKind::LayerNorm;
+  o.in0 = &in; o.in1 = &w; o.in2 = &b; o.out = &out; o.f0 = eps;
+  return run_single(o);
+}
+RunStats Executor::rope(const Tensor &in, const Tensor &table, const Tensor &out, uint32_t heads,
+                        uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base) {
+  ExecOp o;
+  o.kind = ExecKind::Rope;
+  o.in0 = &in; o.in1 = &table; o.out = &out;
+  o.heads = heads; o.head_dim = head_dim; o.rot_dim = rot_dim; o.pos_base = pos_base;
+  return run_single(o);
+}
+RunStats Executor::rope_scatter(const Tensor &in, const Tensor &table, const Tensor &dst, uint32_t heads,
+                                uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base, uint32_t dst_offset,
+                                const uint32_t strides[3], uint32_t pos_scale, const PosCell *cell) {
+  ExecOp o;
+  o.kind = ExecKind::RopeScatter;
+  o.in0 = &in; o.in1 = &table; o.out = &dst;
+  o.heads = heads; o.head_dim = head_dim; o.rot_dim = rot_dim; o.pos_base = pos_base;
+  o.dst_offset = dst_offset; o.pos_scale = pos_scale; o.cell = cell;
+  for (int i = 0; i < 3; ++i) o.strides[i] = strides[i];
+  return run_single(o);
+}
+RunStats Executor::copy_strided(const Tensor &src, const Tensor &dst, const uint32_t extent[3],
+                                uint32_t src_off, const uint32_t src_strides[3], uint32_t dst_off,
+                                const uint32_t dst_strides[3]) {
+  ExecOp o;
+  o.kind = ExecKind::CopyStrided;
+  o.in0 = &src; o.out = &dst; o.src_offset = src_off; o.dst_offset = dst_off;
+  for (int i = 0; i < 3; ++i) {
+    o.extent[i] = extent[i];
+    o.src_strides[i] = src_strides[i];
+    o.strides[i] = dst_strides[i];
+  }
+  return run_single(o);
+}
+RunStats Executor::binary(const Tensor &a, const Tensor &b, const Tensor &out, uint32_t mode, float beta) {
+  ExecOp o;
+  o.kind = ExecKind::Binary;
+  o.in0 = &a; o.in1 = &b; o.out = &out; o.u0 = mode; o.f0 = beta;
+  return run_single(o);
+}
+RunStats Executor::argmax(const Tensor &in, const PosCell &result) {
+  ExecOp o;
+  o.kind = ExecKind::Argmax;
+  o.in0 = &in; o.cell = &result;
+  return run_single(o);
+}
+RunStats Executor::embed_gather(const PosCell &token, const Tensor &table, const Tensor &out) {
+  ExecOp o;
+  o.kind = ExecKind::EmbedGather;
+  o.cell = &token; o.in0 = &table; o.out = &out;
+  return run_single(o);
+}
+RunStats Executor::embed_gather_rows(const TokenIds &tokens, const Tensor &table, const Tensor &out) {
+  ExecOp o;
+  o.kind = ExecKind::EmbedGatherRows;
+  o.tokens = &tokens; o.in0 = &table; o.out = &out;
+  return run_single(o);
+}
+RunStats Executor::flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &out,
+                                   const FlashAttentionDesc &desc) {
+  ExecOp o;
+  o.kind = ExecKind::FlashAttn;
+  o.in0 = &q; o.in1 = &kt; o.in2 = &v; o.out = &out; o.flash = desc;
+  return run_single(o);
+}
+RunStats Executor::attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &scratch,
+                               const Tensor &out, const AttnDecodeDesc &desc) {
+  ExecOp o;
+  o.kind = ExecKind::AttnDecode;
+  o.in0 = &q; o.in1 = &kt; o.in2 = &v; o.in3 = &scratch; o.out = &out; o.attn = desc;
+  return run_single(o);
+}
+
+}  // namespace ta

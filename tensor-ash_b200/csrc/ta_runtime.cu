@@ -177,12 +177,6 @@ void Executor::release_slot(Slot &s) {
 }
 
 namespace {
-struct SlotGuard {
-  Executor &e;
-  Slot &s;
-  SlotGuard(Executor &e_, Slot &s_) : e(e_), s(s_) {}
-  ~SlotGuard() { e.release_slot(s); }
-};
 
 void ensure_staging(Slot &slot, size_t bytes) {
   if (slot.staging_bytes >= bytes) return;
@@ -484,7 +478,7 @@ RunStats Executor::timed(Slot &slot, size_t n_calls, uint64_t flops,
 }
 
 // C must not alias A or B (src/executor/validation.rs:18-52).
-static void validate_op_tensors(const Executor &e, const MatmulOp &op) {
+void validate_op_tensors(const Executor &e, const MatmulOp &op) {
   e.validate_tensor(*op.call.a, "matmul A");
   e.validate_tensor(*op.call.b, "matmul B");
   e.validate_tensor(*op.call.c, "matmul C");
@@ -717,272 +711,6 @@ void Executor::tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
     tuned_[TuneKey{batch, m, n, k, false}] = TunedEntry{cands[best].kernel, cands[best].splits};
     save_tuned(tune_path_, tuned_);
   }
-}
-
-// ------------------------------------------------------------------ model ops
-namespace {
-void ensure_f32(const Executor &e, const Tensor &t, const char *op, const char *operand) {
-  e.validate_tensor(t, operand);
-  if (t.dtype != DType::F32) fail("%s: %s must be f32 storage", op, operand);
-}
-void ensure_same_shape(const char *op, const Tensor &a, const Tensor &b) {
-  if (a.shape != b.shape)
-    fail("%s: input shape %s != output shape %s", op, a.shape_str().c_str(), b.shape_str().c_str());
-}
-void rows_cols(const Tensor &t, const char *label, uint32_t *rows, uint32_t *cols) {
-  *cols = t.shape.back();
-  const uint64_t r = t.len() / *cols;
-  if (r > 0xffffffffull) fail("%s: row count %llu exceeds u32", label, (unsigned long long)r);
-  *rows = (uint32_t)r;
-}
-}  // namespace
-
-RunStats Executor::softmax_rows(const Tensor &in, const Tensor &out, float scale, uint32_t mask_kind,
-                                uint32_t valid_or_prefix, uint32_t rows_per_group) {
-  ensure_f32(*this, in, "run_softmax_rows", "input");
-  ensure_f32(*this, out, "run_softmax_rows", "output");
-  ensure_same_shape("run_softmax_rows", in, out);
-  uint32_t rows, cols;
-  rows_cols(in, "run_softmax_rows", &rows, &cols);
-  if (mask_kind == 2 && (rows_per_group == 0 || rows % rows_per_group))
-    fail("run_softmax_rows: rows_per_group %u must divide rows %u", rows_per_group, rows);
-  ctx_->make_current();
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  return timed(slot, 1, 0, [&](cudaStream_t s) {
-    launch_softmax_rows((const float *)in.ptr(), (float *)out.ptr(), rows, cols, scale, mask_kind,
-                        valid_or_prefix, rows_per_group, s);
-  });
-}
-
-RunStats Executor::rms_norm(const Tensor &in, const Tensor &w, const Tensor &out, float eps) {
-  ensure_f32(*this, in, "run_rms_norm", "input");
-  ensure_f32(*this, w, "run_rms_norm", "weight");
-  ensure_f32(*this, out, "run_rms_norm", "output");
-  ensure_same_shape("run_rms_norm", in, out);
-  uint32_t rows, cols;
-  rows_cols(in, "run_rms_norm", &rows, &cols);
-  if (w.len() != cols)
-    fail("run_rms_norm: weight length %llu != row length %u", (unsigned long long)w.len(), cols);
-  ctx_->make_current();
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  return timed(slot, 1, 0, [&](cudaStream_t s) {
-    launch_rms_norm((const float *)in.ptr(), (const float *)w.ptr(), (float *)out.ptr(), rows, cols,
-                    eps, s);
-  });
-}
-
-RunStats Executor::layer_norm(const Tensor &in, const Tensor &w, const Tensor &b, const Tensor &out,
-                              float eps) {
-  ensure_f32(*this, in, "run_layer_norm", "input");
-  ensure_f32(*this, w, "run_layer_norm", "weight");
-  ensure_f32(*this, b, "run_layer_norm", "bias");
-  ensure_f32(*this, out, "run_layer_norm", "output");
-  ensure_same_shape("run_layer_norm", in, out);
-  uint32_t rows, cols;
-  rows_cols(in, "run_layer_norm", &rows, &cols);
-  if (w.len() != cols)
-    fail("run_layer_norm: weight length %llu != row length %u", (unsigned long long)w.len(), cols);
-  if (b.len() != cols)
-    fail("run_layer_norm: bias length %llu != row length %u", (unsigned long long)b.len(), cols);
-  ctx_->make_current();
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  return timed(slot, 1, 0, [&](cudaStream_t s) {
-    launch_layer_norm((const float *)in.ptr(), (const float *)w.ptr(), (const float *)b.ptr(),
-                      (float *)out.ptr(), rows, cols, eps, s);
-  });
-}
-
-RunStats Executor::rope(const Tensor &in, const Tensor &table, const Tensor &out, uint32_t heads,
-                        uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base) {
-  ensure_f32(*this, in, "run_rope", "input");
-  ensure_f32(*this, out, "run_rope", "output");
-  ensure_f32(*this, table, "run_rope", "table");
-  ensure_same_shape("run_rope", in, out);
-  if (rot_dim < 2 || rot_dim % 2 || rot_dim > head_dim)
-    fail("run_rope: rot_dim %u must be even, >= 2, and <= head_dim %u", rot_dim, head_dim);
-  const uint64_t vec = (uint64_t)heads * head_dim;
-  if (vec == 0 || in.len() % vec)
-    fail("run_rope: input length %llu is not a multiple of heads*head_dim %llu",
-         (unsigned long long)in.len(), (unsigned long long)vec);
-  const uint64_t tokens64 = in.len() / vec;
-  if (tokens64 > 0xffffffffull) fail("run_rope: token count exceeds u32");
-  const uint32_t tokens = (uint32_t)tokens64;
-  const uint64_t needed = ((uint64_t)pos_base + tokens) * rot_dim;
-  if (table.len() < needed)
-    fail("run_rope: table length %llu < required %llu (pos_base %u + %u tokens, rot_dim %u)",
-         (unsigned long long)table.len(), (unsigned long long)needed, pos_base, tokens, rot_dim);
-  ctx_->make_current();
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  return timed(slot, 1, 0, [&](cudaStream_t s) {
-    launch_rope((const float *)in.ptr(), (const float *)table.ptr(), (float *)out.ptr(), tokens,
-                heads, head_dim, rot_dim, pos_base, s);
-  });
-}
-
-RunStats Executor::copy_strided(const Tensor &src, const Tensor &dst, const uint32_t extent[3],
-                                uint32_t src_off, const uint32_t src_strides[3], uint32_t dst_off,
-                                const uint32_t dst_strides[3]) {
-  validate_tensor(src, "src");
-  validate_tensor(dst, "dst");
-  if (src.ptr() == dst.ptr()) fail("run_copy_strided: src and dst must be different tensors");
-  if (src.dtype != DType::F32 || dst.dtype != DType::F32)
-    fail("run_copy_strided: f16 pairings are not built in this library yet");
-  if (!extent[0] || !extent[1] || !extent[2])
-    fail("run_copy_strided: extent [%u, %u, %u] has a zero axis", extent[0], extent[1], extent[2]);
-  auto max_index = [&](uint32_t off, const uint32_t st[3]) {
-    uint64_t v = off;
-    for (int i = 0; i < 3; ++i) v += (uint64_t)(extent[i] - 1) * st[i];
-    return v;
-  };
-  if (max_index(src_off, src_strides) >= src.len())
-    fail("run_copy_strided: source access reaches element %llu but src has %llu",
-         (unsigned long long)max_index(src_off, src_strides), (unsigned long long)src.len());
-  if (max_index(dst_off, dst_strides) >= dst.len())
-    fail("run_copy_strided: destination access reaches element %llu but dst has %llu",
-         (unsigned long long)max_index(dst_off, dst_strides), (unsigned long long)dst.len());
-  if ((uint64_t)extent[0] * extent[1] * extent[2] > 0xffffffffull)
-    fail("run_copy_strided: extent product exceeds u32");
-  ctx_->make_current();
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  return timed(slot, 1, 0, [&](cudaStream_t s) {
-    launch_copy_strided((const float *)src.ptr(), (float *)dst.ptr(), extent, src_off, src_strides,
-                        dst_off, dst_strides, s);
-  });
-}
-
-// ------------------------------------------------------------------ fused attention
-FlashParams Executor::plan_flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v,
-                                           const Tensor &out, const FlashAttentionDesc &desc) const {
-  ensure_f32(*this, q, "run_flash_attention", "q");
-  ensure_f32(*this, out, "run_flash_attention", "out");
-  validate_tensor(kt, "kt");
-  validate_tensor(v, "v");
-  if (kt.dtype != v.dtype)
-    fail("run_flash_attention: kt (%s) and v (%s) must share a storage type", dtype_name(kt.dtype),
-         dtype_name(v.dtype));
-  if (kt.shape.size() != 3) fail("run_flash_attention: kt must be [H_kv, dh, T_max], got %s", kt.shape_str().c_str());
-  if (v.shape.size() != 3) fail("run_flash_attention: v must be [H_kv, T_max, dh], got %s", v.shape_str().c_str());
-  const uint32_t kv_heads = kt.shape[0], dh = kt.shape[1], t_max = kt.shape[2];
-  if (v.shape[1] != t_max || v.shape[0] != kv_heads || v.shape[2] != dh)
-    fail("run_flash_attention: inconsistent cache shapes kt %s, v %s", kt.shape_str().c_str(), v.shape_str().c_str());
-  FlashParams p{};
-  uint32_t heads, t_q;
-  if (desc.token_major_heads) {
-    heads = desc.token_major_heads;
-    t_q = q.shape[0];
-    if (q.len() != (uint64_t)t_q * heads * dh)
-      fail("run_flash_attention: token-major q %s does not hold [T=%u, H=%u, dh=%u]", q.shape_str().c_str(), t_q, heads, dh);
-    p.q_head_stride = dh;
-    p.q_row_stride = heads * dh;
-  } else {
-    if (q.shape.size() != 3) fail("run_flash_attention: q must be [H, T_q, dh], got %s", q.shape_str().c_str());
-    heads = q.shape[0];
-    t_q = q.shape[1];
-    if (q.shape[2] != dh)
-      fail("run_flash_attention: q dh %u != cache dh %u (q %s, kt %s)", q.shape[2], dh, q.shape_str().c_str(),
-           kt.shape_str().c_str());
-    p.q_head_stride = t_q * dh;
-    p.q_row_stride = dh;
-  }
-  if (desc.out_token_major_heads) {
-    if (desc.out_token_major_heads != heads)
-      fail("run_flash_attention: out_token_major_heads %u != q heads %u", desc.out_token_major_heads, heads);
-    if (out.len() != (uint64_t)t_q * heads * dh)
-      fail("run_flash_attention: token-major out %s does not hold [T=%u, H=%u, dh=%u]", out.shape_str().c_str(), t_q, heads, dh);
-    p.o_head_stride = dh;
-    p.o_row_stride = heads * dh;
-  } else if (desc.token_major_heads) {
-    if (out.len() != q.len())
-      fail("run_flash_attention: out shape %s must match token-major q %s", out.shape_str().c_str(), q.shape_str().c_str());
-    p.o_head_stride = p.q_head_stride;
-    p.o_row_stride = p.q_row_stride;
-  } else {
-    if (out.shape != q.shape)
-      fail("run_flash_attention: out shape %s must equal q shape %s", out.shape_str().c_str(), q.shape_str().c_str());
-    p.o_head_stride = p.q_head_stride;
-    p.o_row_stride = p.q_row_stride;
-  }
-  if (kv_heads == 0 || heads % kv_heads) fail("run_flash_attention: H=%u must be a multiple of H_kv=%u", heads, kv_heads);
-  if (desc.kv_len > t_max) fail("run_flash_attention: kv_len %u exceeds cache T_max %u", desc.kv_len, t_max);
-  if (dh != 64 && dh != 128) fail("run_flash_attention: head dimension %u unsupported (64 or 128)", dh);
-  if (q.ptr() == out.ptr()) fail("run_flash_attention: q and out must be different tensors");
-  p.q = static_cast<const float *>(q.ptr());
-  p.kt = kt.ptr();
-  p.v = v.ptr();
-  p.out = static_cast<float *>(out.ptr());
-  p.heads = heads; p.group = heads / kv_heads; p.dh = dh; p.t_q = t_q; p.t_max = t_max;
-  p.kv_len = desc.kv_len; p.pos_base = desc.pos_base; p.scale = desc.scale;
-  p.kv_f16 = kt.dtype == DType::F16;
-  return p;
-}
-
-RunStats Executor::flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &out,
-                                   const FlashAttentionDesc &desc) {
-  const FlashParams p = plan_flash_attention(q, kt, v, out, desc);
-  ctx_->make_current();
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  return timed(slot, 1, 0, [&](cudaStream_t s) { launch_flash_prefill(p, s); });
-}
-
-AttnDecodeParams Executor::plan_attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v,
-                                            const Tensor &scratch, const Tensor &out,
-                                            const AttnDecodeDesc &desc) const {
-  ensure_f32(*this, q, "run_attn_decode", "q");
-  validate_tensor(kt, "kt");
-  validate_tensor(v, "v");
-  ensure_f32(*this, scratch, "run_attn_decode", "scratch");
-  ensure_f32(*this, out, "run_attn_decode", "out");
-  if (kt.dtype != v.dtype)
-    fail("run_attn_decode: kt (%s) and v (%s) must share a storage type", dtype_name(kt.dtype), dtype_name(v.dtype));
-  if (kt.shape.size() != 3) fail("run_attn_decode: kt must be [H_kv, dh, T_max], got %s", kt.shape_str().c_str());
-  if (v.shape.size() != 3) fail("run_attn_decode: v must be [H_kv, T_max, dh], got %s", v.shape_str().c_str());
-  const uint32_t kv_heads = kt.shape[0], dh = kt.shape[1], t_max = kt.shape[2];
-  if (v.shape[2] != dh || v.shape[1] != t_max || v.shape[0] != kv_heads)
-    fail("run_attn_decode: inconsistent caches kt %s, v %s", kt.shape_str().c_str(), v.shape_str().c_str());
-  if (dh != 64) fail("run_attn_decode: head dimension %u unsupported (compiled variant: 64)", dh);
-  const uint64_t heads_elems = (uint64_t)kv_heads * dh;
-  if (q.len() % heads_elems)
-    fail("run_attn_decode: q length %llu must be kv_heads*group*dh (kv_heads %u, dh %u)",
-         (unsigned long long)q.len(), kv_heads, dh);
-  const uint64_t group = q.len() / heads_elems;
-  if (group == 0 || group > 8) fail("run_attn_decode: GQA group %llu unsupported (1..=8)", (unsigned long long)group);
-  if (out.len() != q.len())
-    fail("run_attn_decode: out length %llu must equal q length %llu", (unsigned long long)out.len(),
-         (unsigned long long)q.len());
-  if (desc.kv_len == 0 || desc.kv_len > t_max) fail("run_attn_decode: kv_len %u out of range 1..=%u", desc.kv_len, t_max);
-  if (desc.pos_cell && desc.pos_cell->ctx.get() != ctx_.get())
-    fail("run_attn_decode: pos cell belongs to a different context");
-  const uint32_t num_chunks = desc.pos_cell ? ATTN_DECODE_MAX_CHUNKS : attn_decode_num_chunks(desc.kv_len);
-  const uint64_t needed = (uint64_t)kv_heads * num_chunks * group * (dh + 2);
-  if (scratch.len() < needed)
-    fail("run_attn_decode: scratch length %llu < required %llu (kv_heads %u * chunks %u * group %llu * (dh+2))",
-         (unsigned long long)scratch.len(), (unsigned long long)needed, kv_heads, num_chunks,
-         (unsigned long long)group);
-  AttnDecodeParams p{};
-  p.q = static_cast<const float *>(q.ptr());
-  p.kt = kt.ptr();
-  p.v = v.ptr();
-  p.scratch = static_cast<float *>(scratch.ptr());
-  p.out = static_cast<float *>(out.ptr());
-  p.kv_heads = kv_heads; p.group = (uint32_t)group; p.t_max = t_max; p.kv_len = desc.kv_len;
-  p.num_chunks = num_chunks; p.scale = desc.scale; p.kv_f16 = kt.dtype == DType::F16;
-  p.pos_ptr = desc.pos_cell ? desc.pos_cell->device : nullptr;
-  return p;
-}
-
-RunStats Executor::attn_decode(const Tensor &q, const Tensor &kt, const Tensor &v, const Tensor &scratch,
-                               const Tensor &out, const AttnDecodeDesc &desc) {
-  const AttnDecodeParams p = plan_attn_decode(q, kt, v, scratch, out, desc);
-  ctx_->make_current();
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  return timed(slot, 2, 0, [&](cudaStream_t s) { launch_attn_decode(p, s); });
 }
 
 // ------------------------------------------------------------------ prepared replay

@@ -1,0 +1,174 @@
+"""Mixed graphs: the ops the llama graphs use beside matmuls (binary, argmax,
+embedding gathers, RoPE + scatter, f32 -> f16 strided copies) one by one against
+numpy, then a prepared mixed graph replayed with a moving position cell.
+Mirrors the reference's tests/attn_decode.rs + tools/llama-ash graph tests in
+structure: each op alone, then the composed graph against the composed host model.
+"""
+import numpy as np
+import pytest
+
+
+def up(ta, ctx, ex, arr):
+    t = ta.Tensor.uninit_device(ctx, list(arr.shape))
+    ex.upload(np.ascontiguousarray(arr, dtype=np.float32).ravel(), t)
+    return t
+
+
+def rope_table(t_max, half, theta=1e4):
+    p = np.arange(t_max, dtype=np.float64)[:, None]
+    i = np.arange(half, dtype=np.float64)[None, :]
+    ang = p / np.power(theta, 2.0 * i / (2 * half))
+    return np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
+def rope_host(x, table, heads, dh, pos0):
+    t = x.shape[0]
+    xh = x.reshape(t, heads, dh // 2, 2).astype(np.float64)
+    cs = table[pos0:pos0 + t].astype(np.float64)[:, None]
+    a, b = xh[..., 0], xh[..., 1]
+    return np.stack([a * cs[..., 0] - b * cs[..., 1], a * cs[..., 1] + b * cs[..., 0]], -1).reshape(t, heads * dh)
+
+
+@pytest.mark.gpu
+def test_binary_ops(gpu, orc):
+    ta, ctx, ex = gpu
+    a = orc.fill_det(5 * 333, 1).reshape(5, 333)
+    b = orc.fill_det(5 * 333, 2).reshape(5, 333)
+    ta_, tb = up(ta, ctx, ex, a), up(ta, ctx, ex, b)
+    out = ta.Tensor.uninit_device(ctx, [5, 333])
+    ex.run_exec_ops([ta.ExecOp.binary_add_scaled(ta_, tb, out, 0.5)])
+    want = (a.astype(np.float32) + np.float32(0.5) * b.astype(np.float32))
+    np.testing.assert_allclose(ex.download(out).reshape(5, 333), want, rtol=1e-6, atol=1e-7)
+    ex.run_exec_ops([ta.ExecOp.binary_silu_mul(ta_, tb, out)])
+    a64 = a.astype(np.float64)
+    want = a64 / (1 + np.exp(-a64)) * b
+    np.testing.assert_allclose(ex.download(out).reshape(5, 333), want, rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 7, 1000, 32000, 151936])
+def test_argmax_first_maximum(gpu, orc, n):
+    ta, ctx, ex = gpu
+    x = orc.fill_det(n, 40 + n % 7).copy()
+    if n > 10:
+        # duplicate maximum: the lower index wins
+        x[n // 3] = 5.0
+        x[n - 2] = 5.0
+    t = up(ta, ctx, ex, x.reshape(1, n))
+    cell = ta.PosCell(ctx)
+    cell.set(0xFFFFFFFF)
+    ex.run_exec_ops([ta.ExecOp.argmax(t, cell)])
+    assert cell.get() == int(np.argmax(x))
+
+
+@pytest.mark.gpu
+def test_embed_gather_f16_and_f32_tables(gpu, orc):
+    ta, ctx, ex = gpu
+    vocab, embd = 97, 160
+    tab = orc.fill_det(vocab * embd, 9).reshape(vocab, embd)
+    t32 = up(ta, ctx, ex, tab)
+    t16 = ta.Tensor.uninit_device_f16(ctx, [vocab, embd])
+    ex.upload(tab.ravel(), t16)
+    tab16 = tab.astype(np.float16).astype(np.float32)
+    cell = ta.PosCell(ctx)
+    out = ta.Tensor.uninit_device(ctx, [1, embd])
+    for tok in (0, 42, vocab - 1):
+        cell.set(tok)
+        ex.run_exec_ops([ta.ExecOp.embed_gather(cell, t32, out)])
+        np.testing.assert_array_equal(ex.download(out), tab[tok])
+        ex.run_exec_ops([ta.ExecOp.embed_gather(cell, t16, out)])
+        np.testing.assert_array_equal(ex.download(out), tab16[tok])
+    ids = ta.TokenIdBuffer(ctx, 16)
+    toks = [3, 96, 0, 3, 50]
+    ids.set(toks)
+    rows = ta.Tensor.uninit_device(ctx, [len(toks), embd])
+    ex.run_exec_ops([ta.ExecOp.embed_gather_rows(ids, t16, rows)])
+    np.testing.assert_array_equal(ex.download(rows).reshape(len(toks), embd), tab16[toks])
+    # an id beyond the table is clamped to the last row, so a bad id can never read out of bounds
+    ids.set([1, vocab + 5])
+    rows2 = ta.Tensor.uninit_device(ctx, [2, embd])
+    ex.run_exec_ops([ta.ExecOp.embed_gather_rows(ids, t16, rows2)])
+    np.testing.assert_array_equal(ex.download(rows2).reshape(2, embd), tab16[[1, vocab - 1]])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dst_f16", [False, True])
+def test_rope_scatter_into_transposed_cache(gpu, orc, dst_f16):
+    ta, ctx, ex = gpu
+    heads, dh, t_max, t, pos0 = 2, 64, 24, 5, 7
+    x = orc.fill_det(t * heads * dh, 3).reshape(t, heads * dh)
+    table = rope_table(t_max, dh // 2)
+    tx, tt = up(ta, ctx, ex, x), up(ta, ctx, ex, table)
+    mk = ta.Tensor.uninit_device_f16 if dst_f16 else ta.Tensor.uninit_device
+    kt = mk(ctx, [heads, dh, t_max])
+    zero = np.zeros(heads * dh * t_max, dtype=np.float32)
+    ex.upload(zero, kt)
+    # Kt[h, d, p]: token stride 1, head stride dh*t_max, dim stride t_max
+    ex.run_exec_ops([ta.ExecOp.rope_scatter(tx, tt, kt, heads, dh, dh, pos0, pos0, [1, dh * t_max, t_max])])
+    got = ex.download(kt).reshape(heads, dh, t_max)
+    want = np.zeros((heads, dh, t_max))
+    want[:, :, pos0:pos0 + t] = rope_host(x, table, heads, dh, pos0).reshape(t, heads, dh).transpose(1, 2, 0)
+    if dst_f16:
+        np.testing.assert_allclose(got, want, rtol=1e-3, atol=1e-6)
+        assert np.array_equal(got[:, :, :pos0], np.zeros((heads, dh, pos0)))
+    else:
+        np.testing.assert_allclose(got, want, rtol=2e-6, atol=2e-7)
+
+
+@pytest.mark.gpu
+def test_copy_strided_f32_to_f16_rounds_to_nearest_even(gpu, orc):
+    ta, ctx, ex = gpu
+    t, kv, dh, t_max = 6, 2, 64, 16
+    v = orc.fill_det(t * kv * dh, 5).reshape(t, kv * dh)
+    tv = up(ta, ctx, ex, v)
+    cache = ta.Tensor.uninit_device_f16(ctx, [kv, t_max, dh])
+    ex.upload(np.zeros(kv * t_max * dh, dtype=np.float32), cache)
+    pos0 = 3
+    ex.run_exec_ops([ta.ExecOp.copy_strided(tv, cache, [dh, kv, t], 0, [1, dh, kv * dh], pos0 * dh,
+                                            [1, t_max * dh, dh])])
+    got = ex.download(cache).reshape(kv, t_max, dh)
+    want = np.zeros((kv, t_max, dh), dtype=np.float32)
+    want[:, pos0:pos0 + t] = v.astype(np.float16).astype(np.float32).reshape(t, kv, dh).transpose(1, 0, 2)
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.gpu
+def test_prepared_mixed_graph_replays_with_position_cell(gpu, orc):
+    """norm -> matmul(+rope scatter store through the cell) -> argmax -> gather, replayed at
+    three positions from one recording."""
+    ta, ctx, ex = gpu
+    embd, heads, dh, t_max, vocab = 128, 2, 64, 12, 64
+    x = orc.fill_det(embd, 21).reshape(1, embd)
+    w = orc.fill_det(embd * heads * dh, 22).reshape(embd, heads * dh)
+    nw = 1.0 + 0.1 * orc.fill_det(embd, 23)
+    table = rope_table(t_max, dh // 2)
+    emb = orc.fill_det(vocab * embd, 24).reshape(vocab, embd)
+    tx, tw, tnw, tt, temb = (up(ta, ctx, ex, a) for a in (x, w, nw.reshape(embd), table, emb))
+    xn = ta.Tensor.uninit_device(ctx, [1, embd])
+    y = ta.Tensor.uninit_device(ctx, [1, heads * dh])
+    kt = ta.Tensor.uninit_device(ctx, [heads, dh, t_max])
+    ex.upload(np.zeros(heads * dh * t_max, dtype=np.float32), kt)
+    nxt = ta.Tensor.uninit_device(ctx, [1, embd])
+    pos, tok = ta.PosCell(ctx), ta.PosCell(ctx)
+    ops = [
+        ta.ExecOp.rms_norm(tx, tnw, xn, 1e-5),
+        ta.ExecOp.matmul(ta.MatmulOp(ta.MatmulCall(xn, tw, y))),
+        ta.ExecOp.rope_scatter(y, tt, kt, heads, dh, dh, 0, 0, [1, dh * t_max, t_max], pos_scale=1, cell=pos),
+        ta.ExecOp.argmax(y, tok),
+        ta.ExecOp.embed_gather(tok, temb, nxt),
+    ]
+    pos.set(0)
+    prepared = ex.prepare_exec_ops(ops)
+    x64 = x.astype(np.float64)
+    xn_h = x64 / np.sqrt((x64 * x64).mean() + 1e-5) * nw
+    y_h = xn_h @ w.astype(np.float64)
+    want = np.zeros((heads, dh, t_max))
+    for p in (0, 4, 11):
+        pos.set(p)
+        st = prepared.run()
+        assert st.n_calls >= 1
+        want[:, :, p] = rope_host(y_h, table, heads, dh, p).reshape(heads, dh)
+        assert tok.get() == int(np.argmax(y_h))
+        np.testing.assert_array_equal(ex.download(nxt), emb[tok.get()])
+    got = ex.download(kt).reshape(heads, dh, t_max)
+    np.testing.assert_allclose(got, want, rtol=3e-5, atol=3e-5)

@@ -1,0 +1,129 @@
+"""Llama runner: prefill graph and prepared decode graph against the numpy forward.
+
+Token parity follows the reference's own criterion for greedy decoding
+(tools/llama-ash/tests: tokens must agree wherever the top-2 logit margin is
+larger than the accumulated rounding error); logits are compared with a
+relative-to-max tolerance of 2e-4 (f32 accumulation on the device against f64
+on the host, through `layers` blocks with f16 KV rounding on both sides).
+"""
+import numpy as np
+import pytest
+
+from llama_ref import RefLlama
+
+LOGIT_TOL = 2e-4
+
+
+def small_cfg(ta, **kw):
+    base = dict(layers=2, embd=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1024, t_max=96,
+                weight_sigma=0.05, norm_jitter=0.25, seed=7)
+    base.update(kw)
+    return ta.LlamaConfig(**base)
+
+
+def check_logits(got, want):
+    denom = np.abs(want).max()
+    err = np.abs(got.astype(np.float64) - want).max() / denom
+    assert err <= LOGIT_TOL, f"logits rel err {err:.3e}"
+
+
+def margin(logits):
+    top = np.sort(logits)[-2:]
+    return top[1] - top[0]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prompt_len", [1, 5, 33])
+def test_prefill_matches_host_forward(ta, orc, gpu, prompt_len):
+    cfg = small_cfg(ta)
+    ctx = ta.Context()
+    ex = ta.Executor(ctx, max_calls_per_submit=256)
+    model = ta.Llama(ex, cfg)
+    ref = RefLlama(orc, cfg)
+    prompt = [(17 * i + 3) % cfg.vocab for i in range(prompt_len)]
+    nxt, st = model.prefill(prompt)
+    want = ref.forward(prompt)
+    check_logits(model.logits(), want)
+    if margin(want) > 1e-3 * np.abs(want).max():
+        assert nxt == int(np.argmax(want))
+    assert model.position == prompt_len
+    assert st.gpu_time_ns is not None and st.gpu_time_ns > 0
+
+
+@pytest.mark.gpu
+def test_decode_graph_matches_host_forward(ta, orc, gpu):
+    cfg = small_cfg(ta)
+    ctx = ta.Context()
+    ex = ta.Executor(ctx, max_calls_per_submit=256)
+    model = ta.Llama(ex, cfg)
+    ref = RefLlama(orc, cfg)
+    prompt = [5, 900, 31, 64, 512, 77, 1]
+    nxt, _ = model.prefill(prompt)
+    want = ref.forward(prompt)
+    tok = int(np.argmax(want))
+    assert nxt == tok
+    n = 24
+    got, st = model.decode(nxt, n)
+    assert st.n_calls > 0
+    # teacher-forced on the device's own choices, so one near-tie cannot derail the rest
+    fed = nxt
+    for i in range(n):
+        want = ref.forward([fed])
+        if margin(want) > 1e-3 * np.abs(want).max():
+            assert got[i] == int(np.argmax(want)), f"step {i}"
+        fed = got[i]
+    check_logits(model.logits(), want)
+    assert model.position == len(prompt) + n
+
+
+@pytest.mark.gpu
+def test_decode_continues_across_calls_and_reset(ta, orc, gpu):
+    cfg = small_cfg(ta, seed=11)
+    ctx = ta.Context()
+    ex = ta.Executor(ctx, max_calls_per_submit=256)
+    model = ta.Llama(ex, cfg)
+    prompt = [9, 8, 7, 6]
+    nxt, _ = model.prefill(prompt)
+    a, _ = model.decode(nxt, 10)
+    model.reset()
+    nxt2, _ = model.prefill(prompt)
+    assert nxt2 == nxt
+    b1, _ = model.decode(nxt2, 4)
+    b2, _ = model.decode(b1[-1], 6)
+    assert a == b1 + b2
+
+
+@pytest.mark.gpu
+def test_chunked_prefill_matches_single_prefill(ta, orc, gpu):
+    cfg = small_cfg(ta, seed=3)
+    ctx = ta.Context()
+    ex = ta.Executor(ctx, max_calls_per_submit=256)
+    model = ta.Llama(ex, cfg)
+    prompt = [(29 * i + 11) % cfg.vocab for i in range(40)]
+    model.prefill(prompt)
+    whole = model.logits()
+    model.reset()
+    model.prefill(prompt[:24])
+    model.prefill(prompt[24:])
+    parts = model.logits()
+    assert np.abs(whole - parts).max() <= 2e-5 * np.abs(whole).max()
+
+
+@pytest.mark.gpu
+def test_kv_overflow_and_bad_config_are_errors(ta, gpu):
+    ctx = ta.Context()
+    ex = ta.Executor(ctx, max_calls_per_submit=256)
+    with pytest.raises(ta.TensorAshError, match="heads \\* head_dim"):
+        ta.Llama(ex, small_cfg(ta, heads=3))
+    model = ta.Llama(ex, small_cfg(ta, t_max=8))
+    with pytest.raises(ta.TensorAshError, match="KV cache overflow"):
+        model.prefill(list(range(9)))
+    nxt, _ = model.prefill(list(range(6)))
+    with pytest.raises(ta.TensorAshError, match="KV cache overflow"):
+        model.decode(nxt, 3)
+
+
+def test_weight_bytes_formula_matches_config_5():
+    # 22 layers, embd 2048, kv_dim 256, ffn 5632, vocab 32000: f16 bytes per decoded token
+    per_layer = 2 * 2048 * 2048 + 2 * 2048 * 256 + 3 * 2048 * 5632
+    assert 2 * (22 * per_layer + 2048 * 32000) == 2_068_840_448
