@@ -154,36 +154,63 @@ __global__ void binary_kernel(const float *a, const float *b, float *out, uint32
   out[i] = mode == 0 ? fmaf(beta, y, x) : (x / (1.0f + expf(-x))) * y;
 }
 
-// One block; ties keep the LARGEST index (shaders/op_argmax_f32.comp:44-75).
-__global__ void __launch_bounds__(256)
+// Greedy pick over one row: the maximum, ties resolved to the LARGEST index
+// (the rule of shaders/op_argmax_f32.comp:44-75).  One block of 1024 threads;
+// 16-byte loads when the row is aligned, (value, index) pairs folded through
+// warp shuffles and one shared-memory hop.  NaNs never win (comparisons are false).
+struct ArgBest {
+  float v;
+  uint32_t i;
+};
+__device__ __forceinline__ void arg_fold(ArgBest &b, float v, uint32_t i) {
+  if (v > b.v || (v == b.v && i > b.i)) {
+    b.v = v;
+    b.i = i;
+  }
+}
+constexpr int ARGMAX_THREADS = 1024;
+__global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_kernel(const float *__restrict__ in, uint32_t n, uint32_t *result) {
-  __shared__ float sval[256];
-  __shared__ uint32_t sidx[256];
+  __shared__ float sval[ARGMAX_THREADS / 32];
+  __shared__ uint32_t sidx[ARGMAX_THREADS / 32];
   const uint32_t tid = threadIdx.x;
-  float best = -INFINITY;
-  uint32_t best_idx = 0;
-  for (uint32_t i = tid; i < n; i += 256) {
-    const float v = in[i];
-    if (v >= best) {
-      best = v;
-      best_idx = i;
+  ArgBest best{-INFINITY, 0u};
+  uint32_t done = 0;
+  if ((reinterpret_cast<uintptr_t>(in) & 15u) == 0) {
+    const uint32_t n4 = n / 4;
+    const float4 *in4 = reinterpret_cast<const float4 *>(in);
+    for (uint32_t q = tid; q < n4; q += ARGMAX_THREADS) {
+      const float4 v = in4[q];
+      arg_fold(best, v.x, 4 * q);
+      arg_fold(best, v.y, 4 * q + 1);
+      arg_fold(best, v.z, 4 * q + 2);
+      arg_fold(best, v.w, 4 * q + 3);
     }
+    done = n4 * 4;
   }
-  sval[tid] = best;
-  sidx[tid] = best_idx;
+  for (uint32_t i = done + tid; i < n; i += ARGMAX_THREADS) arg_fold(best, in[i], i);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best.v, off);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, best.i, off);
+    arg_fold(best, ov, oi);
+  }
+  if ((tid & 31u) == 0) {
+    sval[tid >> 5] = best.v;
+    sidx[tid >> 5] = best.i;
+  }
   __syncthreads();
-  for (uint32_t stride = 128; stride > 0; stride >>= 1) {
-    if (tid < stride) {
-      const float o = sval[tid + stride];
-      const uint32_t oi = sidx[tid + stride];
-      if (o > sval[tid] || (o == sval[tid] && oi > sidx[tid])) {
-        sval[tid] = o;
-        sidx[tid] = oi;
-      }
+  if (tid < 32) {
+    best.v = sval[tid];
+    best.i = sidx[tid];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best.v, off);
+      const uint32_t oi = __shfl_xor_sync(0xffffffffu, best.i, off);
+      arg_fold(best, ov, oi);
     }
-    __syncthreads();
+    if (tid == 0) *result = best.i;
   }
-  if (tid == 0) *result = sidx[0];
 }
 
 // Row gather by token id read on the device, id clamped to vocab-1
@@ -298,7 +325,7 @@ void launch_binary(const float *a, const float *b, float *out, uint32_t n, uint3
 }
 
 void launch_argmax(const float *in, uint32_t n, uint32_t *result, cudaStream_t stream) {
-  argmax_kernel<<<1, 256, 0, stream>>>(in, n, result);
+  argmax_kernel<<<1, ARGMAX_THREADS, 0, stream>>>(in, n, result);
   launched();
 }
 

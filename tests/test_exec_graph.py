@@ -47,18 +47,19 @@ def test_binary_ops(gpu, orc):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("n", [1, 7, 1000, 32000, 151936])
-def test_argmax_first_maximum(gpu, orc, n):
+def test_argmax_ties_keep_the_largest_index(gpu, orc, n):
     ta, ctx, ex = gpu
     x = orc.fill_det(n, 40 + n % 7).copy()
     if n > 10:
-        # duplicate maximum: the lower index wins
+        # duplicate maximum: the larger index wins (shaders/op_argmax_f32.comp:44-75)
         x[n // 3] = 5.0
         x[n - 2] = 5.0
     t = up(ta, ctx, ex, x.reshape(1, n))
     cell = ta.PosCell(ctx)
     cell.set(0xFFFFFFFF)
     ex.run_exec_ops([ta.ExecOp.argmax(t, cell)])
-    assert cell.get() == int(np.argmax(x))
+    want = int(np.flatnonzero(x == x.max())[-1])
+    assert cell.get() == want
 
 
 @pytest.mark.gpu
@@ -75,9 +76,9 @@ def test_embed_gather_f16_and_f32_tables(gpu, orc):
     for tok in (0, 42, vocab - 1):
         cell.set(tok)
         ex.run_exec_ops([ta.ExecOp.embed_gather(cell, t32, out)])
-        np.testing.assert_array_equal(ex.download(out), tab[tok])
+        np.testing.assert_array_equal(ex.download(out).ravel(), tab[tok])
         ex.run_exec_ops([ta.ExecOp.embed_gather(cell, t16, out)])
-        np.testing.assert_array_equal(ex.download(out), tab16[tok])
+        np.testing.assert_array_equal(ex.download(out).ravel(), tab16[tok])
     ids = ta.TokenIdBuffer(ctx, 16)
     toks = [3, 96, 0, 3, 50]
     ids.set(toks)
@@ -137,7 +138,7 @@ def test_prepared_mixed_graph_replays_with_position_cell(gpu, orc):
     """norm -> matmul(+rope scatter store through the cell) -> argmax -> gather, replayed at
     three positions from one recording."""
     ta, ctx, ex = gpu
-    embd, heads, dh, t_max, vocab = 128, 2, 64, 12, 64
+    embd, heads, dh, t_max, vocab = 128, 2, 64, 12, 128
     x = orc.fill_det(embd, 21).reshape(1, embd)
     w = orc.fill_det(embd * heads * dh, 22).reshape(embd, heads * dh)
     nw = 1.0 + 0.1 * orc.fill_det(embd, 23)
@@ -169,6 +170,6 @@ def test_prepared_mixed_graph_replays_with_position_cell(gpu, orc):
         assert st.n_calls >= 1
         want[:, :, p] = rope_host(y_h, table, heads, dh, p).reshape(heads, dh)
         assert tok.get() == int(np.argmax(y_h))
-        np.testing.assert_array_equal(ex.download(nxt), emb[tok.get()])
+        np.testing.assert_array_equal(ex.download(nxt).ravel(), emb[tok.get()])
     got = ex.download(kt).reshape(heads, dh, t_max)
     np.testing.assert_allclose(got, want, rtol=3e-5, atol=3e-5)
