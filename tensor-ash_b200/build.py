@@ -27,6 +27,7 @@ SOURCES = [
     "llama_ash.cu",
     "k_gemm_ffma.cu",
     "k_gemm_tf32x3.cu",
+    "k_gemm_f16w.cu",
     "k_gemv.cu",
     "k_attention.cu",
     "k_ops.cu",

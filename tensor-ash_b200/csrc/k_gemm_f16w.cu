@@ -1,0 +1,332 @@
+// f16-weight GEMM on the tensor cores: C = epi(alpha * f16(A) @ B (+ C)) with
+// A [B,M,K] f32, B [K,N] or [B,K,N] f16 (row-major, as uploaded), C/D f32.
+// tcgen05.mma kind::f16 with f32 accumulation in tensor memory; the fused
+// epilogue runs on the TMEM -> register drain.
+//
+// This is the tensor-core form of the reference's f16-weight tile kernels
+// (shaders/matmul_bda_v4_kernel.glsl with B_IS_F16: f16 weights widened, f32
+// accumulate; epilogue shaders/matmul_epilogue_common.glsl:14-82).  The one
+// numeric difference: A is rounded to f16 (nearest-even) on its way into shared
+// memory, because the tensor core multiplies f16 x f16.  Products are exact in
+// f32 and accumulation is f32, so the error against the f64 oracle stays inside
+// the f16-weight tolerance (2e-3 relative) -- a product's relative error grows
+// from 2^-24 to at most 2^-11 and averages down over K.  |A| above 65504 would
+// overflow f16; such inputs belong on the FFMA tiles (explicit kernel selection).
+//
+// Pipeline per K block of 32: TMA brings the raw f32 A tile (128 x 32, plain
+// rows) and the f16 B tile (32 x BN, 128-byte swizzle, N-contiguous) into one
+// stage; four converter warps turn the A tile into f16 in the 64-byte-swizzled
+// K-major layout the tensor core reads; one thread issues two K=16 MMAs.
+// Warps 0-3 drain TMEM (double-buffered accumulators), warp 4 is the TMA
+// producer, warp 5 owns TMEM and issues MMAs, warps 6-13 convert (two groups of
+// four warps taking alternate K blocks, so one block's load-convert-store-fence
+// chain overlaps the next).  All waits are
+// bounded; a timeout raises the abort flag and the host reports an error.
+#include <cuda_fp16.h>
+
+#include "k_epilogue.cuh"
+#include "k_umma.cuh"
+#include "ta_core.hpp"
+
+namespace ta {
+
+namespace {
+
+using namespace umma;
+
+constexpr int BM = 128;
+constexpr int BK = 32;                     // K elements per stage
+constexpr int CVT_GROUPS = 2;               // converter groups of 4 warps, alternating K blocks
+constexpr int NUM_THREADS = 192 + CVT_GROUPS * 128;
+
+template <int BN>
+struct Cfg {
+  static constexpr int RAW_BYTES = BM * BK * 4;           // 16 KiB f32 A tile
+  static constexpr int A16_BYTES = BM * BK * 2;           // 8 KiB f16 A tile
+  static constexpr int B_BYTES = BK * BN * 2;             // 16 KiB at BN = 256
+  static constexpr int STAGE_BYTES = RAW_BYTES + A16_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 5 : (BN == 128 ? 6 : 7);
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * BN;                // 128, 256 or 512: powers of two
+};
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_f16w_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
+                 const __grid_constant__ CUtensorMap map_b, uint32_t *__restrict__ status) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  auto full_raw = [&](int s) { return bar_base + 8u * s; };
+  auto full_cvt = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto empty = [&](int s) { return bar_base + 8u * (2 * C::STAGES + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (3 * C::STAGES + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (3 * C::STAGES + 2 + b); };
+  volatile uint32_t *tmem_slot =
+      reinterpret_cast<volatile uint32_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (3 * C::STAGES + 4));
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_raw(s), 1);
+      mbar_init(full_cvt(s), 128);
+      mbar_init(empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 128);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 5) tmem_alloc(smem_u32((const void *)tmem_slot), C::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
+  const uint32_t tiles_per_batch = tiles_m * tiles_n;
+  const uint32_t num_tiles = tiles_per_batch * p.batch;
+  const uint32_t k_blocks = (p.k + BK - 1) / BK;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      // M fastest: consecutive CTAs share one B column block (weights stream once through L2)
+      const int m0 = (int)(rem % tiles_m) * BM, n0 = (int)(rem / tiles_m) * BN;
+      const int za = p.stride_a ? (int)batch : 0, zb = p.stride_b ? (int)batch : 0;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+          mbar_arrive_expect_tx(full_raw(stage), C::RAW_BYTES + C::B_BYTES);
+          tma_load_3d(dst, &map_a, full_raw(stage), (int)(kb * BK), m0, za);
+#pragma unroll
+          for (int nb = 0; nb < BN / 64; ++nb)
+            tma_load_3d(dst + C::RAW_BYTES + C::A16_BYTES + nb * (BK * 128), &map_b, full_raw(stage),
+                        n0 + nb * 64, (int)(kb * BK), zb);
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    // c f32 | a,b f16 | a K-major, b N-major | N >> 3 | M >> 4
+    const uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    uint32_t stage = 0, phase = 0, acc_it = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+      ok = mbar_wait(acc_empty(buf), acc_phase ^ 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        ok = mbar_wait(full_cvt(stage), phase, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a16 = smem_base + stage * C::STAGE_BYTES + C::RAW_BYTES;
+          const uint32_t b16 = a16 + C::A16_BYTES;
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j) {
+            // A: 64-byte rows, 8-row groups 512 B apart; B: 128-byte rows per k, 8-k groups 1 KiB
+            // apart, 64-column blocks BK*128 B apart
+            const uint64_t da = make_desc(a16 + j * 32, 16, 512, LAYOUT_SW64);
+            const uint64_t db = make_desc(b16 + j * 2048, BK * 128, 1024, LAYOUT_SW128);
+            mma_f16(d_tmem, da, db, idesc, (kb | (uint32_t)j) != 0u);
+          }
+          tc_commit(empty(stage));
+          if (kb + 1 == k_blocks) tc_commit(acc_full(buf));
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ f32 -> f16 converters
+    // The raw tile is 1024 float4 (row r = f / 8, float4 c4 = f % 8); consecutive
+    // threads take consecutive float4 (conflict-free reads) and each writes the 8
+    // bytes of f16 it produced into 16-byte chunk (c4 / 2) ^ ((r >> 1) & 3) of
+    // the row: the 64-byte swizzle the descriptor names.
+    const int t = (threadIdx.x - 6 * 32) & 127, group = (threadIdx.x - 6 * 32) >> 7;
+    uint32_t stage = 0, phase = 0, it_all = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it_all) {
+        if ((int)(it_all % CVT_GROUPS) == group) {
+          ok = mbar_wait(full_raw(stage), phase, abort_flag);
+          if (!ok) break;
+          const float4 *raw = reinterpret_cast<const float4 *>(smem_gen + stage * C::STAGE_BYTES);
+          uint8_t *a16 = smem_gen + stage * C::STAGE_BYTES + C::RAW_BYTES;
+          float4 v[(BM * BK / 4) / 128];
+#pragma unroll
+          for (int it = 0; it < (BM * BK / 4) / 128; ++it) v[it] = raw[t + it * 128];
+#pragma unroll
+          for (int it = 0; it < (BM * BK / 4) / 128; ++it) {
+            const int f = t + it * 128;
+            const int r = f >> 3, c4 = f & 7;
+            const int chunk = (c4 >> 1) ^ ((r >> 1) & 3);
+            uint2 h;
+            h.x = pack_half2(v[it].x, v[it].y);
+            h.y = pack_half2(v[it].z, v[it].w);
+            *reinterpret_cast<uint2 *>(a16 + r * 64 + chunk * 16 + (c4 & 1) * 8) = h;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(full_cvt(stage));
+        }
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 0-3)
+    uint32_t acc_it = 0;
+    bool ok = true;
+    const bool alpha_is_one = p.alpha == 1.0f;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      const uint32_t m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
+      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+      ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t row = m0 + warp * 32 + lane;
+      const bool row_ok = row < p.m;
+      const size_t row_off = (size_t)batch * p.stride_c + (size_t)row * p.n;
+      float *__restrict__ crow = p.c + row_off;
+      const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
+      const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(taddr + c0, v);
+        const uint32_t col0 = n0 + c0;
+        if (row_ok && col0 < p.n) {
+#pragma unroll
+          for (int q = 0; q < 32; q += 4) {
+            const uint32_t col = col0 + q;
+            if (col < p.n) {  // N % 8 == 0: a float4 is either fully in or fully out
+              float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+              if (p.accumulate) {
+                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+              }
+              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+              o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
+              o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
+              o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
+              o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
+              *reinterpret_cast<float4 *>(crow + col) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty(buf));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(100000);   // let copies / MMAs in flight land
+    if (threadIdx.x == 0) atomicOr(status, 1u);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <int BN>
+void launch_t(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx.device & 63]) {
+    TA_CUDA(cudaFuncSetAttribute(gemm_f16w_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::SMEM_BYTES));
+    attr_set[ctx.device & 63] = true;
+  }
+  CUtensorMap map_a, map_b;
+  const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
+  // A [ba, M, K] f32: plain 128-byte rows of 32 floats
+  encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.a, p.k, p.m, ba, (uint64_t)p.k * 4,
+              p.stride_a ? (uint64_t)p.stride_a * 4 : (uint64_t)p.m * p.k * 4, BK, BM,
+              CU_TENSOR_MAP_SWIZZLE_NONE);
+  // B [bb, K, N] f16: boxes of 64 columns (128 bytes) x BK rows, 128-byte swizzle
+  encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, p.n, p.k, bb, (uint64_t)p.n * 2,
+              p.stride_b ? (uint64_t)p.stride_b * 2 : (uint64_t)p.k * p.n * 2, 64, BK,
+              CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
+  const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
+  gemm_f16w_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);
+  TA_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+}  // namespace
+
+// TMA needs 16-byte strides and bases: K % 4 == 0 for the f32 A rows, N % 8 == 0
+// for the f16 B rows; float4 epilogue accesses need N % 4 == 0 and aligned C/D/bias.
+bool gemm_f16w_umma_eligible(const GemmParams &p) {
+  if (!p.b_f16) return false;
+  if (p.k % 4 || p.n % 8) return false;
+  if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.b) |
+       reinterpret_cast<uintptr_t>(p.c)) & 15)
+    return false;
+  if (p.d && (reinterpret_cast<uintptr_t>(p.d) & 15)) return false;
+  if (p.bias && (reinterpret_cast<uintptr_t>(p.bias) & 15)) return false;
+  if ((p.stride_a % 4) || (p.stride_b % 8) || (p.stride_c % 4) || (p.bias_stride % 4)) return false;
+  return true;
+}
+
+// Column-tile width: fewest waves of (tile width + fixed per-tile cost); the fixed
+// part stands for the A staging and conversion every tile repeats.
+uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_count) {
+  uint32_t best = 256;
+  uint64_t best_cost = ~0ull;
+  for (uint32_t bn : {256u, 128u, 64u}) {
+    const uint64_t tiles = (uint64_t)batch * ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
+    const uint64_t waves = (tiles + sm_count - 1) / sm_count;
+    const uint64_t cost = waves * (bn + 96);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
+                           cudaStream_t stream) {
+  if (!gemm_f16w_umma_eligible(p))
+    fail("f16w tensor-core GEMM needs f32 A, f16 B, K %% 4 == 0 and N %% 8 == 0");
+  if (tile_n >= 256) launch_t<256>(ctx, p, status, stream);
+  else if (tile_n >= 128) launch_t<128>(ctx, p, status, stream);
+  else launch_t<64>(ctx, p, status, stream);
+}
+
+}  // namespace ta

@@ -92,6 +92,10 @@ struct Layer {
   Tensor kt_cache, v_cache;
 };
 
+struct PrefillScratch {
+  Tensor x_a, x_b, xn, qkv, q, k, v, attn_flat, o, on, up, gate, last, last_n;
+};
+
 }  // namespace
 
 struct ta_llama {
@@ -105,6 +109,7 @@ struct ta_llama {
   PosCell pos_cell, token_cell;
   TokenIds token_ids;
   std::unique_ptr<PreparedOps> decode_graph;
+  std::unique_ptr<PrefillScratch> prefill_full;
   uint32_t pos = 0;
   ~ta_llama();
 };
@@ -342,9 +347,10 @@ std::vector<ExecOp> decode_ops(ta_llama &m) {
 // ------------------------------------------------------------------ prefill
 namespace {
 
-struct PrefillScratch {
-  Tensor x_a, x_b, xn, qkv, q, k, v, attn_flat, o, on, up, gate, last, last_n;
-};
+
+// Prefill activations are allocated once for t_max rows; a call works on
+// free reshapes of their first n rows (Tensor::alias_with_shape).
+PrefillScratch prefill_view(ta_llama &m, uint32_t n);
 
 ExecOp copy_op(const Tensor &src, const Tensor &dst, std::array<uint32_t, 3> extent, uint32_t src_off,
                std::array<uint32_t, 3> ss, uint32_t dst_off, std::array<uint32_t, 3> ds) {
@@ -413,6 +419,34 @@ std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint
   return ops;
 }
 
+PrefillScratch prefill_view(ta_llama &m, uint32_t n) {
+  const ta_llama_config &c = m.cfg;
+  const uint32_t kv_dim = c.kv_heads * c.head_dim;
+  PrefillScratch &full = *m.prefill_full;
+  if (full.x_a.len() == 0) {
+    auto f32 = [&](uint32_t cols) { return make(m.ctx, {c.t_max, cols}, DType::F32); };
+    full.x_a = f32(c.embd); full.x_b = f32(c.embd); full.xn = f32(c.embd);
+    full.qkv = f32(c.embd + 2 * kv_dim);
+    full.q = f32(c.embd); full.k = f32(kv_dim); full.v = f32(kv_dim);
+    full.attn_flat = f32(c.embd); full.o = f32(c.embd); full.on = f32(c.embd);
+    full.up = f32(c.ffn); full.gate = f32(c.ffn);
+    full.last = make(m.ctx, {1, c.embd}, DType::F32);
+    full.last_n = make(m.ctx, {1, c.embd}, DType::F32);
+  }
+  auto rows = [&](const Tensor &t, uint32_t cols) {
+    const uint32_t shape[2] = {n, cols};
+    return t.alias_with_shape(shape, 2);
+  };
+  PrefillScratch s;
+  s.x_a = rows(full.x_a, c.embd); s.x_b = rows(full.x_b, c.embd); s.xn = rows(full.xn, c.embd);
+  s.qkv = rows(full.qkv, c.embd + 2 * kv_dim);
+  s.q = rows(full.q, c.embd); s.k = rows(full.k, kv_dim); s.v = rows(full.v, kv_dim);
+  s.attn_flat = rows(full.attn_flat, c.embd); s.o = rows(full.o, c.embd); s.on = rows(full.on, c.embd);
+  s.up = rows(full.up, c.ffn); s.gate = rows(full.gate, c.ffn);
+  s.last = full.last; s.last_n = full.last_n;
+  return s;
+}
+
 int guarded(const std::function<void()> &f) {
   ta_set_last_error("");
   try {
@@ -447,6 +481,7 @@ ta_llama *ta_llama_create_random(const ta_executor *exec, const ta_llama_config 
     if (!exec) fail("ta_llama_create_random: exec is null");
     if (!cfg) fail("ta_llama_create_random: cfg is null");
     m = new ta_llama;
+    m->prefill_full.reset(new PrefillScratch);
     m->ctx = exec->ctx;
     m->exec = exec->exec.get();
     m->cfg = *cfg;
@@ -481,15 +516,7 @@ int ta_llama_prefill(ta_llama *model, const uint32_t *tokens, uint32_t n, uint32
     const ta_llama_config &c = m.cfg;
     if (m.pos + n > c.t_max) fail("ta_llama_prefill: KV cache overflow (%u + %u > %u)", m.pos, n, c.t_max);
     m.ctx->make_current();
-    const uint32_t kv_dim = c.kv_heads * c.head_dim;
-    PrefillScratch s;
-    auto f32 = [&](uint32_t r, uint32_t cols) { return make(m.ctx, {r, cols}, DType::F32); };
-    s.x_a = f32(n, c.embd); s.x_b = f32(n, c.embd); s.xn = f32(n, c.embd);
-    s.qkv = f32(n, c.embd + 2 * kv_dim);
-    s.q = f32(n, c.embd); s.k = f32(n, kv_dim); s.v = f32(n, kv_dim);
-    s.attn_flat = f32(n, c.embd); s.o = f32(n, c.embd); s.on = f32(n, c.embd);
-    s.up = f32(n, c.ffn); s.gate = f32(n, c.ffn);
-    s.last = f32(1, c.embd); s.last_n = f32(1, c.embd);
+    PrefillScratch s = prefill_view(m, n);
     memcpy(m.token_ids.host, tokens, (size_t)n * 4);
     m.token_ids.len = n;
     const RunStats st = m.exec->run_exec_ops(prefill_ops(m, s, n, m.pos));

@@ -309,8 +309,12 @@ static const char *const A_F16W_FFMA_64[] = {
     "f16w_ffma_m64n64", "f16w_small_bda_v4", "f16w_small", "f16w_k64_bda_v4", "f16w_k64", nullptr};
 static const char *const A_F16W_UMMA[] = {
     "f16w_umma_m128n256", "f16w_umma", "f16w_coopmat_aligned", "f16w_coopmat", "coopmat",
-    "f16w_coopmat_m64n64", "coopmat_m64", "f16w_coopmat_m64n128", "coopmat_m64n128",
-    "f16w_coopmat_m128n64", "coopmat_m128n64", "f16w_cm2", "cm2", "cm2_gemm", nullptr};
+    "f16w_cm2", "cm2", "cm2_gemm", nullptr};
+static const char *const A_F16W_UMMA_128[] = {
+    "f16w_umma_m128n128", "f16w_coopmat_m64n128", "coopmat_m64n128", nullptr};
+static const char *const A_F16W_UMMA_64[] = {
+    "f16w_umma_m128n64", "f16w_coopmat_m64n64", "coopmat_m64", "f16w_coopmat_m128n64",
+    "coopmat_m128n64", nullptr};
 static const char *const A_ROW[] = {"row_bda", "row", "gemv_bda", nullptr};
 static const char *const A_F16W_ROW[] = {"f16w_row_bda", "f16w_row", nullptr};
 static const char *const A_F16W_ROW_K16[] = {"f16w_row_bda_k16", "f16w_row_k16", nullptr};
@@ -329,7 +333,9 @@ const KernelSpec KERNEL_SPECS[] = {
     {"ffma_m64n64", 64, 64, 16, Family::Ffma, false, A_FFMA_64},
     {"f16w_ffma_m128n128", 128, 128, 16, Family::Ffma, true, A_F16W_FFMA_128},
     {"f16w_ffma_m64n64", 64, 64, 16, Family::Ffma, true, A_F16W_FFMA_64},
-    {"f16w_umma_m128n256", 128, 256, 64, Family::F16wUmma, true, A_F16W_UMMA},
+    {"f16w_umma_m128n256", 128, 256, 32, Family::F16wUmma, true, A_F16W_UMMA},
+    {"f16w_umma_m128n128", 128, 128, 32, Family::F16wUmma, true, A_F16W_UMMA_128},
+    {"f16w_umma_m128n64", 128, 64, 32, Family::F16wUmma, true, A_F16W_UMMA_64},
     {"row_bda", 1, 32, 1, Family::RowGemv, false, A_ROW},
     {"f16w_row_bda", 1, 32, 1, Family::RowGemv, true, A_F16W_ROW},
     {"f16w_row_bda_k16", 1, 32, 1, Family::RowGemv, true, A_F16W_ROW_K16},

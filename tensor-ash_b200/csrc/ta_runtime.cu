@@ -293,6 +293,11 @@ int heuristic_kernel(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_
     // decode shapes: the bandwidth GEMV (src/pipeline/mod.rs:330-347, routing.rs:27-33)
     if (batch == 1 && m <= 8 && gemv_f16w_supported(m, n, k, false, 0))
       return idx_of(f16w_row_uses_k16(k, n) ? "f16w_row_bda_k16" : "f16w_row_bda_k16_v2");
+    // prefill / training shapes: the tensor cores once a 128-row tile is at least a quarter full
+    if (k % 4 == 0 && n % 8 == 0 && m >= 32 && n >= 64 && k >= 64) {
+      const uint32_t bn = gemm_f16w_umma_tile_n(batch, m, n, sm_count);
+      return idx_of(bn == 256 ? "f16w_umma_m128n256" : bn == 128 ? "f16w_umma_m128n128" : "f16w_umma_m128n64");
+    }
     return idx_of((m >= 128 && n >= 128) ? "f16w_ffma_m128n128" : "f16w_ffma_m64n64");
   }
   const bool tma_ok = (k % 4 == 0) && (n % 4 == 0);
@@ -320,7 +325,9 @@ Route Executor::plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, b
       KERNEL_SPECS[selection_].family != Family::RowGemv) {
     const KernelSpec &spec = KERNEL_SPECS[selection_];
     const bool tma_ok = (k % 4 == 0) && (n % 4 == 0);
-    if (spec.family == Family::Ffma || (spec.family == Family::Tf32x3 && tma_ok)) {
+    const bool umma_ok = (k % 4 == 0) && (n % 8 == 0);
+    if (spec.family == Family::Ffma || (spec.family == Family::Tf32x3 && tma_ok) ||
+        (spec.family == Family::F16wUmma && umma_ok)) {
       r.kernel = selection_;
       return r;
     }
@@ -446,6 +453,13 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
         return;
       }
       launch_gemm_ffma(p, 128, stream);  // alignment demotion
+      return;
+    case Family::F16wUmma:
+      if (gemm_f16w_umma_eligible(p)) {
+        launch_gemm_f16w_umma(*ctx_, p, spec.tile_n, slot.status, stream);
+        return;
+      }
+      launch_gemm_ffma(p, (r.m >= 128 && r.n >= 128) ? 128 : 64, stream);  // alignment demotion
       return;
     case Family::Ffma:
       launch_gemm_ffma(p, spec.tile_m, stream);

@@ -254,7 +254,11 @@ def test_f16_weight_storage(setup, orc):
         c = ta.Tensor.uninit_device(ctx, (m, n))
         ex.run_matmuls([ta.MatmulCall(a, b16, c)])
         ref = orc.cpu_bmm(ha, orc.round_via_f16(hb), 1, m, n, k)
-        check(orc, ex.download(c), ref, orc.tolerance(k), f"f16w {m}x{n}x{k}")
+        if ex.dispatch_info_for(1, m, n, k, b_f16=True).kernel.startswith("f16w_umma"):
+            # tensor-core route: A is rounded to f16 on the way in, the f16-weight tolerance applies
+            assert rel_err(ex.download(c), ref) <= 2e-3, f"f16w {m}x{n}x{k}"
+        else:
+            check(orc, ex.download(c), ref, orc.tolerance(k), f"f16w {m}x{n}x{k}")
 
 
 def test_stats_and_dispatch_info(setup, orc):

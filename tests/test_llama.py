@@ -4,7 +4,9 @@ Token parity follows the reference's own criterion for greedy decoding
 (tools/llama-ash/tests: tokens must agree wherever the top-2 logit margin is
 larger than the accumulated rounding error); logits are compared with a
 relative-to-max tolerance of 2e-4 (f32 accumulation on the device against f64
-on the host, through `layers` blocks with f16 KV rounding on both sides).
+on the host, through `layers` blocks with f16 KV rounding on both sides).  Prompts
+of 32 tokens and more run their projections on the f16 tensor-core GEMM, which
+rounds activations to f16 on the way in: there the f16-weight bound 2e-3 applies.
 """
 import numpy as np
 import pytest
@@ -21,10 +23,10 @@ def small_cfg(ta, **kw):
     return ta.LlamaConfig(**base)
 
 
-def check_logits(got, want):
+def check_logits(got, want, tol=LOGIT_TOL):
     denom = np.abs(want).max()
     err = np.abs(got.astype(np.float64) - want).max() / denom
-    assert err <= LOGIT_TOL, f"logits rel err {err:.3e}"
+    assert err <= tol, f"logits rel err {err:.3e}"
 
 
 def margin(logits):
@@ -43,8 +45,9 @@ def test_prefill_matches_host_forward(ta, orc, gpu, prompt_len):
     prompt = [(17 * i + 3) % cfg.vocab for i in range(prompt_len)]
     nxt, st = model.prefill(prompt)
     want = ref.forward(prompt)
-    check_logits(model.logits(), want)
-    if margin(want) > 1e-3 * np.abs(want).max():
+    tol = 2e-3 if prompt_len >= 32 else LOGIT_TOL
+    check_logits(model.logits(), want, tol)
+    if margin(want) > 4 * tol * np.abs(want).max():
         assert nxt == int(np.argmax(want))
     assert model.position == prompt_len
     assert st.gpu_time_ns is not None and st.gpu_time_ns > 0
@@ -106,7 +109,8 @@ def test_chunked_prefill_matches_single_prefill(ta, orc, gpu):
     model.prefill(prompt[:24])
     model.prefill(prompt[24:])
     parts = model.logits()
-    assert np.abs(whole - parts).max() <= 2e-5 * np.abs(whole).max()
+    # 40 and 24 rows take the tensor-core GEMM, 16 rows the f32-activation tiles
+    assert np.abs(whole - parts).max() <= 2e-3 * np.abs(whole).max()
 
 
 @pytest.mark.gpu
