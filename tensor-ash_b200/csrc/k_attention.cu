@@ -12,15 +12,10 @@
 // state lives in registers; K/V tiles of 32 positions are staged in shared
 // memory; tiles past the CTA's causal frontier are skipped.
 //
-// attn_decode_stage1_kernel / attn_decode_combine_kernel: split-K decode
-// attention (shaders/attention_decode_kernel.glsl:89-170 and
-// shaders/op_attn_decode_combine.comp:42-74): one CTA per (chunk, kv head), 8 q
-// rows x 16 lanes, lanes stride the chunk's positions with private online
-// softmax state, a xor-shuffle butterfly merges the 16 lane states exactly, and
-// partials [kv_heads, chunks, group, dh + 2] go to caller scratch.  The combine
-// rescales every chunk to the global max and sums in chunk order.  The valid
-// length may come from a host-visible cell (kv_len + *pos), read on the device,
-// so a captured graph serves every position.
+// attn_decode_kernel: split-K decode attention (shaders/attention_decode_kernel.glsl:89-170
+// and shaders/op_attn_decode_combine.comp:42-74 in one launch), described at the kernel.
+// The valid length may come from a host-visible cell (kv_len + *pos), read on the
+// device, so a captured graph serves every position.
 #include <cuda_fp16.h>
 
 #include "ta_core.hpp"
@@ -130,119 +125,177 @@ flash_prefill_kernel(const FlashParams p) {
   }
 }
 
-// ------------------------------------------------------------------ decode, stage 1
-constexpr int DEC_DH = 64, DEC_LANES = 16, DEC_THREADS = 128;
+// ------------------------------------------------------------------ decode
+// One CTA per (chunk, kv head), 128 threads = 8 query rows x 16 lanes.  A chunk
+// is walked in tiles of 64 positions: the K tile [d][j] and the V tile [j][d]
+// are staged in shared memory with 16-byte loads issued up front (one round trip
+// of latency per tile), thread (r, c) computes the four scores j = 4c..4c+3 of
+// row r, the tile's max / sum meet through xor-shuffles inside the 16-lane
+// group, probabilities go through shared memory, and thread (r, c) accumulates
+// the four output dims d = 4c..4c+3.  Partials [kv_heads, chunks, group, dh+2]
+// (acc, m, l) go to caller scratch.  The last CTA of a kv head to finish (a
+// ticket counter, reset for the next launch) rescales every chunk to the global
+// max and sums in chunk order, so the result does not depend on which CTA that is.
+constexpr int DEC_DH = 64, DEC_LANES = 16, DEC_THREADS = 128, DEC_BP = 64;
 
 __global__ void __launch_bounds__(DEC_THREADS)
-attn_decode_stage1_kernel(const AttnDecodeParams p) {
-  __shared__ float Qsh[8 * DEC_DH];
+attn_decode_kernel(const AttnDecodeParams p) {
+  __shared__ __align__(16) float Ksh[DEC_DH * DEC_BP];   // [d][j]
+  __shared__ __align__(16) float Vsh[DEC_BP * DEC_DH];   // [j][d]
+  __shared__ __align__(16) float Qsh[8 * DEC_DH];
+  __shared__ float Psh[8 * DEC_BP];
+  __shared__ uint32_t last_flag;
   const uint32_t chunk = blockIdx.x, kv_head = blockIdx.y, tid = threadIdx.x;
   const uint32_t row = tid / DEC_LANES, lane = tid % DEC_LANES;
   const bool live = row < p.group;
-  for (uint32_t i = tid; i < p.group * DEC_DH; i += DEC_THREADS) Qsh[i] = p.q[(size_t)kv_head * p.group * DEC_DH + i];
-  __syncthreads();
 
+  // the position cell is host-written before the launch: read it ahead of the dependency wait
   const uint32_t kv_len = p.kv_len + (p.pos_ptr ? *p.pos_ptr : 0u);
-  const uint32_t chunk_size = (kv_len + p.num_chunks - 1) / p.num_chunks;
+  if (p.pdl) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+  for (uint32_t i = tid; i < p.group * DEC_DH; i += DEC_THREADS) Qsh[i] = p.q[(size_t)kv_head * p.group * DEC_DH + i];
+
+  // positions per chunk, a multiple of 8 so that f16 K rows start on 16 bytes
+  const uint32_t chunk_size = (((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u;
   const uint32_t p0 = min(kv_len, chunk * chunk_size), p1 = min(p0 + chunk_size, kv_len);
   const size_t kt_base = (size_t)kv_head * DEC_DH * p.t_max, v_base = (size_t)kv_head * p.t_max * DEC_DH;
+  const bool vec16 = p.kv_f16 && (p.t_max % 8u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(p.kt) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.v) & 15u) == 0;
 
-  float m = NEG_BIG, l = 0.0f, acc[DEC_DH];
+  float m_run = NEG_BIG, l_run = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+
+  for (uint32_t t0 = p0; t0 < p1; t0 += DEC_BP) {
+    const uint32_t n = min((uint32_t)DEC_BP, p1 - t0);
+    if (vec16) {
+      // K: 64 d-rows x 8 groups of 8 positions; V: 64 position rows x 8 groups of 8 dims
+      uint4 kraw[4], vraw[4];
 #pragma unroll
-  for (int d = 0; d < DEC_DH; ++d) acc[d] = 0.0f;
-
-  if (live) {
-    const float *qr = &Qsh[row * DEC_DH];
-    for (uint32_t pos = p0 + lane; pos < p1; pos += DEC_LANES) {
-      float s = 0.0f;
-      if (p.kv_f16) {
-        const __half *kt = static_cast<const __half *>(p.kt) + kt_base + pos;
-#pragma unroll 16
-        for (int d = 0; d < DEC_DH; ++d) s = fmaf(qr[d], __half2float(kt[(size_t)d * p.t_max]), s);
-      } else {
-        const float *kt = static_cast<const float *>(p.kt) + kt_base + pos;
-#pragma unroll 16
-        for (int d = 0; d < DEC_DH; ++d) s = fmaf(qr[d], kt[(size_t)d * p.t_max], s);
+      for (int it = 0; it < 4; ++it) {
+        const uint32_t i = tid + it * DEC_THREADS, d = i >> 3, jg = (i & 7u) * 8u;
+        kraw[it] = make_uint4(0u, 0u, 0u, 0u);
+        vraw[it] = make_uint4(0u, 0u, 0u, 0u);
+        if (jg < n)   // a group may run past kv_len inside t_max: masked below
+          kraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.kt) + kt_base + (size_t)d * p.t_max + t0 + jg);
+        const uint32_t j = i >> 3, dg = (i & 7u) * 8u;
+        if (j < n)
+          vraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)(t0 + j) * DEC_DH + dg);
       }
-      s *= p.scale;
-      const float m_new = fmaxf(m, s);
-      const float corr = expf(m - m_new), pe = expf(s - m_new);
-      l = l * corr + pe;
-      if (p.kv_f16) {
-        const uint4 *vv = reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)pos * DEC_DH);
 #pragma unroll
-        for (int d8 = 0; d8 < DEC_DH / 8; ++d8) {
-          const uint4 raw = vv[d8];
-          const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 f = __half22float2(h[q]);
-            acc[d8 * 8 + 2 * q] = fmaf(pe, f.x, acc[d8 * 8 + 2 * q] * corr);
-            acc[d8 * 8 + 2 * q + 1] = fmaf(pe, f.y, acc[d8 * 8 + 2 * q + 1] * corr);
-          }
-        }
-      } else {
-        const float4 *vv = reinterpret_cast<const float4 *>(static_cast<const float *>(p.v) + v_base + (size_t)pos * DEC_DH);
-#pragma unroll
-        for (int d4 = 0; d4 < DEC_DH / 4; ++d4) {
-          const float4 f = vv[d4];
-          acc[4 * d4] = fmaf(pe, f.x, acc[4 * d4] * corr);
-          acc[4 * d4 + 1] = fmaf(pe, f.y, acc[4 * d4 + 1] * corr);
-          acc[4 * d4 + 2] = fmaf(pe, f.z, acc[4 * d4 + 2] * corr);
-          acc[4 * d4 + 3] = fmaf(pe, f.w, acc[4 * d4 + 3] * corr);
-        }
+      for (int it = 0; it < 4; ++it) {
+        const uint32_t i = tid + it * DEC_THREADS, r8 = i >> 3, g8 = (i & 7u) * 8u;
+        const __half2 *hk = reinterpret_cast<const __half2 *>(&kraw[it]);
+        const __half2 *hv = reinterpret_cast<const __half2 *>(&vraw[it]);
+        float4 *kd = reinterpret_cast<float4 *>(&Ksh[r8 * DEC_BP + g8]);
+        float4 *vd = reinterpret_cast<float4 *>(&Vsh[r8 * DEC_DH + g8]);
+        const float2 k0 = __half22float2(hk[0]), k1 = __half22float2(hk[1]), k2 = __half22float2(hk[2]), k3 = __half22float2(hk[3]);
+        const float2 v0 = __half22float2(hv[0]), v1 = __half22float2(hv[1]), v2 = __half22float2(hv[2]), v3 = __half22float2(hv[3]);
+        kd[0] = make_float4(k0.x, k0.y, k1.x, k1.y);
+        kd[1] = make_float4(k2.x, k2.y, k3.x, k3.y);
+        vd[0] = make_float4(v0.x, v0.y, v1.x, v1.y);
+        vd[1] = make_float4(v2.x, v2.y, v3.x, v3.y);
       }
-      m = m_new;
+    } else {
+      for (uint32_t i = tid; i < DEC_DH * DEC_BP; i += DEC_THREADS) {
+        const uint32_t d = i / DEC_BP, j = i % DEC_BP;
+        Ksh[i] = j < n ? kv_load(p.kt, kt_base + (size_t)d * p.t_max + t0 + j, p.kv_f16) : 0.0f;
+      }
+      for (uint32_t i = tid; i < DEC_BP * DEC_DH; i += DEC_THREADS) {
+        const uint32_t j = i / DEC_DH, d = i % DEC_DH;
+        Vsh[i] = j < n ? kv_load(p.v, v_base + (size_t)(t0 + j) * DEC_DH + d, p.kv_f16) : 0.0f;
+      }
     }
-  }
-  // exact butterfly merge of the 16 lane states of each row (xor 8, 4, 2, 1 stays inside the group)
-#pragma unroll
-  for (int off = DEC_LANES / 2; off >= 1; off >>= 1) {
-    const float m_o = __shfl_xor_sync(0xffffffffu, m, off);
-    const float l_o = __shfl_xor_sync(0xffffffffu, l, off);
-    const float m_new = fmaxf(m, m_o);
-    const float c_self = expf(m - m_new), c_other = expf(m_o - m_new);
-    l = l * c_self + l_o * c_other;
-#pragma unroll
-    for (int d = 0; d < DEC_DH; ++d) {
-      const float a_o = __shfl_xor_sync(0xffffffffu, acc[d], off);
-      acc[d] = acc[d] * c_self + a_o * c_other;
-    }
-    m = m_new;
-  }
-  if (live) {
-    float *dst = p.scratch + (((size_t)kv_head * p.num_chunks + chunk) * p.group + row) * (DEC_DH + 2);
-#pragma unroll
-    for (int d = 0; d < DEC_DH; ++d)
-      if ((d % DEC_LANES) == (int)lane) dst[d] = acc[d];
-    if (lane == 0) {
-      dst[DEC_DH] = m;
-      dst[DEC_DH + 1] = l;
-    }
-  }
-}
+    __syncthreads();
 
-// ------------------------------------------------------------------ decode, combine
-__global__ void __launch_bounds__(64)
-attn_decode_combine_kernel(const AttnDecodeParams p) {
-  const uint32_t row_id = blockIdx.x, tid = threadIdx.x;
-  const uint32_t kv_head = row_id / p.group, row = row_id % p.group;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+      const float *qr = &Qsh[row * DEC_DH];
+#pragma unroll 16
+      for (int d = 0; d < DEC_DH; ++d) {
+        const float qd = qr[d];
+        const float4 kk = *reinterpret_cast<const float4 *>(&Ksh[d * DEC_BP + lane * 4]);
+        s[0] = fmaf(qd, kk.x, s[0]); s[1] = fmaf(qd, kk.y, s[1]);
+        s[2] = fmaf(qd, kk.z, s[2]); s[3] = fmaf(qd, kk.w, s[3]);
+      }
+    }
+    float tmax = NEG_BIG;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      s[q] = (lane * 4 + q) < n ? s[q] * p.scale : NEG_BIG;
+      tmax = fmaxf(tmax, s[q]);
+    }
+#pragma unroll
+    for (int off = DEC_LANES / 2; off >= 1; off >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+    const float m_new = fmaxf(m_run, tmax);
+    const float corr = expf(m_run - m_new);
+    float lsum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float pe = (lane * 4 + q) < n ? expf(s[q] - m_new) : 0.0f;
+      lsum += pe;
+      Psh[row * DEC_BP + lane * 4 + q] = pe;
+    }
+#pragma unroll
+    for (int off = DEC_LANES / 2; off >= 1; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+    l_run = l_run * corr + lsum;
+    m_run = m_new;
+    __syncthreads();
+    if (live) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[q] *= corr;
+      const float *pr = &Psh[row * DEC_BP];
+      for (uint32_t j = 0; j < n; ++j) {
+        const float pj = pr[j];
+        const float4 vv = *reinterpret_cast<const float4 *>(&Vsh[j * DEC_DH + lane * 4]);
+        acc[0] = fmaf(pj, vv.x, acc[0]); acc[1] = fmaf(pj, vv.y, acc[1]);
+        acc[2] = fmaf(pj, vv.z, acc[2]); acc[3] = fmaf(pj, vv.w, acc[3]);
+      }
+    }
+    __syncthreads();
+  }
+
   const uint32_t stride = DEC_DH + 2;
+  if (live) {
+    float *dst = p.scratch + (((size_t)kv_head * p.num_chunks + chunk) * p.group + row) * stride;
+    dst[lane * 4] = acc[0]; dst[lane * 4 + 1] = acc[1]; dst[lane * 4 + 2] = acc[2]; dst[lane * 4 + 3] = acc[3];
+    if (lane == 0) {
+      dst[DEC_DH] = m_run;
+      dst[DEC_DH + 1] = l_run;
+    }
+  }
+  // ---- the last CTA of this kv head combines (shaders/op_attn_decode_combine.comp:42-74)
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t ticket = atomicAdd(&p.counters[kv_head], 1u);
+    last_flag = ticket == p.num_chunks - 1 ? 1u : 0u;
+    if (last_flag) p.counters[kv_head] = 0u;   // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (!last_flag || !live) return;
+  __threadfence();
   const float *base = p.scratch + ((size_t)kv_head * p.num_chunks * p.group + row) * stride;
   const size_t chunk_step = (size_t)p.group * stride;
+  // chunks past the valid length hold nothing; partials come from other CTAs: L2 loads
+  const uint32_t live_chunks = chunk_size ? min(p.num_chunks, (kv_len + chunk_size - 1) / chunk_size) : 0u;
   float m_star = NEG_BIG;
-  for (uint32_t i = 0; i < p.num_chunks; ++i) m_star = fmaxf(m_star, base[i * chunk_step + DEC_DH]);
-  float w[32], l_total = 0.0f;
-  for (uint32_t i = 0; i < p.num_chunks; ++i) {
-    w[i] = expf(base[i * chunk_step + DEC_DH] - m_star);
-    l_total = fmaf(base[i * chunk_step + DEC_DH + 1], w[i], l_total);
+#pragma unroll 8
+  for (uint32_t i = 0; i < live_chunks; ++i) m_star = fmaxf(m_star, __ldcg(&base[i * chunk_step + DEC_DH]));
+  float l_total = 0.0f, num[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (uint32_t i = 0; i < live_chunks; ++i) {
+    const float w = expf(__ldcg(&base[i * chunk_step + DEC_DH]) - m_star);
+    l_total = fmaf(__ldcg(&base[i * chunk_step + DEC_DH + 1]), w, l_total);
+    // rows are dh + 2 floats long: 8-byte aligned, not 16
+    const float2 a = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4]));
+    const float2 b = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4 + 2]));
+    num[0] = fmaf(a.x, w, num[0]); num[1] = fmaf(a.y, w, num[1]);
+    num[2] = fmaf(b.x, w, num[2]); num[3] = fmaf(b.y, w, num[3]);
   }
   const float inv = l_total > 0.0f ? 1.0f / l_total : 0.0f;
-  for (uint32_t d = tid; d < DEC_DH; d += 64) {
-    float num = 0.0f;
-    for (uint32_t i = 0; i < p.num_chunks; ++i) num = fmaf(base[i * chunk_step + d], w[i], num);
-    p.out[(size_t)row_id * DEC_DH + d] = num * inv;
-  }
+  float *o = p.out + ((size_t)kv_head * p.group + row) * DEC_DH + lane * 4;
+  *reinterpret_cast<float4 *>(o) = make_float4(num[0] * inv, num[1] * inv, num[2] * inv, num[3] * inv);
 }
 
 inline void launched() {
@@ -261,9 +314,19 @@ void launch_flash_prefill(const FlashParams &p, cudaStream_t stream) {
 }
 
 void launch_attn_decode(const AttnDecodeParams &p, cudaStream_t stream) {
-  attn_decode_stage1_kernel<<<dim3(p.num_chunks, p.kv_heads), DEC_THREADS, 0, stream>>>(p);
-  launched();
-  attn_decode_combine_kernel<<<p.kv_heads * p.group, 64, 0, stream>>>(p);
+  if (!p.counters) fail("run_attn_decode: internal: no ticket counters");
+  if (p.kv_heads > ATTN_DECODE_MAX_KV_HEADS)
+    fail("run_attn_decode: %u kv heads exceed the %u ticket counters", p.kv_heads, ATTN_DECODE_MAX_KV_HEADS);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.num_chunks, p.kv_heads, 1);
+  cfg.blockDim = dim3(DEC_THREADS, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel, p));
   launched();
 }
 

@@ -17,9 +17,11 @@
 // is the hi operand) and write lo into a twin buffer at identical offsets: the
 // shared-memory swizzle never has to be decoded.
 //
-// Warp roles (320 threads): warps 0-3 drain TMEM and run the epilogue (warp w
+// Warp roles (448 threads): warps 0-3 drain TMEM and run the epilogue (warp w
 // owns TMEM lanes 32w..32w+31 = tile rows), warp 4 issues TMA, warp 5 owns the
-// TMEM allocation and issues the MMAs, warps 6-9 split tiles into hi/lo.
+// TMEM allocation and issues the MMAs, warps 6-13 split tiles into hi/lo in two
+// groups of four that take alternate K blocks (one block's load-split-store-fence
+// chain overlaps the next block's).
 // Every mbarrier wait is bounded (about two seconds); on a timeout the CTA
 // raises a flag, all roles leave their loops, and the host reports an error.
 #include <cuda.h>
@@ -35,7 +37,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;                      // floats per stage along K (64-byte rows of A)
-constexpr int NUM_THREADS = 320;
+constexpr int CVT_GROUPS = 2;               // converter groups of 4 warps, alternating K blocks
+constexpr int NUM_THREADS = 192 + CVT_GROUPS * 128;
 
 template <int BN>
 struct Cfg {
@@ -172,25 +175,27 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------ hi/lo converters
-    const int t = threadIdx.x - 6 * 32;  // 0..127
-    uint32_t stage = 0, phase = 0;
+    const int t = (threadIdx.x - 6 * 32) & 127, group = (threadIdx.x - 6 * 32) >> 7;
+    uint32_t stage = 0, phase = 0, it_all = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-        ok = mbar_wait(full_raw(stage), phase, abort_flag);
-        if (!ok) break;
-        float4 *hi = reinterpret_cast<float4 *>(smem_gen + stage * C::STAGE_BYTES);
-        float4 *lo = reinterpret_cast<float4 *>(smem_gen + stage * C::STAGE_BYTES + C::HALF_BYTES);
+      for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it_all) {
+        if ((int)(it_all % CVT_GROUPS) == group) {
+          ok = mbar_wait(full_raw(stage), phase, abort_flag);
+          if (!ok) break;
+          float4 *hi = reinterpret_cast<float4 *>(smem_gen + stage * C::STAGE_BYTES);
+          float4 *lo = reinterpret_cast<float4 *>(smem_gen + stage * C::STAGE_BYTES + C::HALF_BYTES);
 #pragma unroll 4
-        for (int i = t; i < C::HALF_BYTES / 16; i += 128) {
-          const float4 v = hi[i];
-          uint4 l;
-          l.x = split_lo(v.x); l.y = split_lo(v.y); l.z = split_lo(v.z); l.w = split_lo(v.w);
-          *reinterpret_cast<uint4 *>(lo + i) = l;
+          for (int i = t; i < C::HALF_BYTES / 16; i += 128) {
+            const float4 v = hi[i];
+            uint4 l;
+            l.x = split_lo(v.x); l.y = split_lo(v.y); l.z = split_lo(v.z); l.w = split_lo(v.w);
+            *reinterpret_cast<uint4 *>(lo + i) = l;
+          }
+          // generic-proxy writes -> visible to the tensor core's async-proxy reads
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(full_cvt(stage));
         }
-        // generic-proxy writes -> visible to the tensor core's async-proxy reads
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(full_cvt(stage));
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
       }
     }

@@ -1,11 +1,13 @@
 // Decode GEMV / skinny GEMM over f16 weights: out[m, :] = epi(alpha * x'[m, :] @ W),
 // M <= 8 activation rows per weight pass, W f16 either row-major [K, N] or packed
 // [N/tile][K][tile] (tile 32 or 64), x f32.  HBM-bound: every weight byte is read
-// exactly once with 128-bit loads and the weights are never staged.
+// exactly once with 128-bit streaming loads and never staged.
 //
 // Semantics follow the reference's row kernel (shaders/matmul_row_bda_kernel.glsl):
 //   * f16 weights widened exactly to f32, f32 fma accumulation (:252-259, :334-341);
-//   * fused RMSNorm of A: x'[k] = x[k] * rsqrt(mean(x^2) + eps) * w[k] (:212-234);
+//   * fused RMSNorm of A: x'[k] = x[k] * rsqrt(mean(x^2) + eps) * w[k] (:212-234); the
+//     per-row factor rsqrt(...) is applied to the finished dot products instead of to
+//     every element (same value up to f32 rounding order);
 //   * epilogue alpha -> (+C) -> bias -> act -> binary(D) (:272-276);
 //   * fused store: interleaved-pair RoPE with the partner column, then C or a
 //     strided scatter destination (f32 or f16), position from pos_base + *pos_ptr
@@ -16,11 +18,28 @@
 // tree -> warp index -> cluster rank), so results are run-to-run bit-identical.
 // The f64 oracle with f16-rounded weights is the parity reference (rel 2e-3).
 //
+// Latency structure (a decode step is a chain of ~100 such launches over a few MB
+// each, so the chain latency matters as much as the bandwidth):
+//   * weights first: a CTA issues the 16-byte loads of its first pass before
+//     anything else, and only then waits for the previous kernel in the stream
+//     (programmatic dependent launch, `griddepcontrol.wait`).  Weights never
+//     depend on earlier kernels, so their HBM latency hides behind the tail of the
+//     producer of x.  Everything that reads x or writes memory comes after the wait;
+//   * passes are double-buffered in registers: the loads of pass i+1 are in flight
+//     while pass i is multiplied;
+//   * cluster ranks push their partial tile straight into rank 0's shared memory
+//     (distributed shared memory stores) and leave; rank 0 alone waits, sums in
+//     rank order and runs the epilogue;
+//   * up to three GEMVs that share x (q, k, v projections) ride in one launch as
+//     segments of the tile range, each with its own epilogue and store.
+//
 // A second weight matrix sharing x can ride along (`w2`): half of the warps take
-// each matrix and the epilogue stores silu(x@W) * (x@W2), the decode SwiGLU gate,
-// in one launch with x read once.
+// each matrix and the epilogue stores silu(x@W) * (x@W2), the decode SwiGLU gate
+// (and x@W2 itself when `c2` is set), in one launch with x read once.
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
+
+#include <cstdlib>
 
 #include "k_epilogue.cuh"
 #include "ta_core.hpp"
@@ -34,65 +53,45 @@ namespace {
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 
+template <int MROWS>
+struct GemvCfg {
+  static constexpr int U = MROWS <= 2 ? 4 : 2;   // 16-byte loads per lane per pass
+};
+
 template <int MROWS, int TN>
 __global__ void __launch_bounds__(GEMV_THREADS)
-gemv_f16w_kernel(const GemvParams p) {
-  // 16-byte loads in flight per lane: deep for few rows (pure latency hiding),
-  // shallower where the accumulators need the registers
-  constexpr int GEMV_UNROLL = MROWS <= 2 ? 8 : 4;
+gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
+  constexpr int U = GemvCfg<MROWS>::U;
   constexpr int LPR = TN / 8;          // lanes per weight row (8 f16 per lane)
   constexpr int RPL = 32 / LPR;        // weight rows per warp-wide load
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   cg::cluster_group cluster = cg::this_cluster();
-  const uint32_t S = p.ksplit;
+  const uint32_t S = g.ksplit;
   const uint32_t rank = S > 1 ? cluster.block_rank() : 0;
-  const uint32_t tile = blockIdx.x / S;
+  const uint32_t tile_all = blockIdx.x / S;
+  int si = 0;
+  while (si + 1 < (int)g.nseg && tile_all >= g.tile_end[si]) ++si;
+  const GemvParams &p = g.seg[si];
+  const uint32_t tile = tile_all - (si ? g.tile_end[si - 1] : 0u);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool dual = p.w2 != nullptr;
   const int nw = dual ? GEMV_WARPS / 2 : GEMV_WARPS;   // warps per matrix
   const int wi = warp % nw, mat = warp / nw;
 
-  // K range of this CTA, in whole warp-load blocks
-  const uint32_t blocks = (p.k + RPL - 1) / RPL;
-  const uint32_t blocks_per = (blocks + S - 1) / S;
-  const uint32_t k_lo = min(p.k, rank * blocks_per * RPL);
-  const uint32_t k_hi = min(p.k, (rank + 1) * blocks_per * RPL);
-  const uint32_t k_cta = k_hi - k_lo;
+  // K range of this CTA
+  const uint32_t k_lo = min(p.k, rank * g.k_cta), k_hi = min(p.k, k_lo + g.k_cta);
+  const uint32_t k_len = k_hi - k_lo;
+  const uint32_t rows_per_pass = (uint32_t)nw * RPL * U;
+  const uint32_t passes = (k_len + rows_per_pass - 1) / rows_per_pass;
 
-  // shared: xs[k_cta][MROWS] | wpart[2][nw][MROWS][TN] | cpart[2][MROWS][TN] | scale[MROWS]
+  // shared: xs[k_cta][MROWS] | wpart[WARPS][MROWS][TN] | cpart[S][2][MROWS][TN] | red[WARPS][MROWS] | scale[MROWS]
   float *xs = reinterpret_cast<float *>(gemv_smem);
-  float *wpart = xs + (size_t)p.k_cta_max * MROWS;
-  float *cpart = wpart + 2 * GEMV_WARPS * MROWS * TN;
-  float *scale = cpart + 2 * MROWS * TN;
+  float *wpart = xs + (size_t)g.k_cta * MROWS;
+  float *cpart = wpart + GEMV_WARPS * MROWS * TN;
+  float *red = cpart + (size_t)S * 2 * MROWS * TN;
+  float *scale = red + GEMV_WARPS * MROWS;
 
-  // ---- fused RMSNorm scale per activation row (whole K, every CTA computes it)
-  if (p.norm_w) {
-    for (int m = warp; m < MROWS; m += GEMV_WARPS) {
-      float ss = 0.0f;
-      if ((uint32_t)m < p.m)
-        for (uint32_t k = lane; k < p.k; k += 32) {
-          const float a = p.x[(size_t)m * p.k + k];
-          ss = fmaf(a, a, ss);
-        }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) scale[m] = rsqrtf(ss / (float)p.k + p.norm_eps);
-    }
-    __syncthreads();
-  }
-  // ---- stage this CTA's slice of x' as xs[k][m]
-  for (uint32_t idx = threadIdx.x; idx < k_cta * MROWS; idx += GEMV_THREADS) {
-    const uint32_t kk = idx / MROWS, m = idx % MROWS;
-    float v = 0.0f;
-    if (m < p.m) {
-      v = p.x[(size_t)m * p.k + k_lo + kk];
-      if (p.norm_w) v = v * scale[m] * p.norm_w[k_lo + kk];
-    }
-    xs[idx] = v;
-  }
-  __syncthreads();
-
-  // ---- stream the weights
+  // ---- weight addressing
   const __half *__restrict__ W = static_cast<const __half *>(mat == 0 ? p.w : p.w2);
   const uint32_t col0 = tile * TN;
   const int lrow = lane / LPR, lcg = (lane % LPR) * 8;
@@ -105,30 +104,92 @@ gemv_f16w_kernel(const GemvParams p) {
     base = (size_t)col0 + lcg;
     row_stride = p.n;
   }
+  auto load_pass = [&](uint4 (&wv)[U], uint32_t pass) {
+    const uint32_t k0 = k_lo + pass * rows_per_pass + (uint32_t)wi * RPL + lrow;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t k = k0 + u * nw * RPL;
+      wv[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (k < k_hi && col_ok) wv[u] = __ldcs(reinterpret_cast<const uint4 *>(W + base + (size_t)k * row_stride));
+    }
+  };
+
+  uint4 wa[U], wb[U];
+  if (passes > 0) load_pass(wa, 0);
+  if (passes > 1) load_pass(wb, 1);
+  // the position cell is written by the host before the launch, never by a kernel:
+  // fetch it now (it may live in host memory) so its latency hides behind the weights
+  uint32_t pos = p.pos_base;
+  if (p.pos_ptr && rank == 0 && p.store_kind != 0) pos += *p.pos_ptr;
+
+  // ---- everything below may depend on the previous kernel in the stream
+  if (g.pdl) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+
+  // ---- fused RMSNorm: sum of squares per activation row (whole K, fixed order).
+  // x'[k] = x[k] * s * w[k] with one scalar s per row, so s factors out of the dot
+  // product: the slice is staged as x[k] * w[k] and rank 0 multiplies the finished
+  // sums by s.  Only rank 0 needs s, and nothing waits for it before the epilogue.
+  if (p.norm_w && rank == 0) {
+    float ss[MROWS];
+#pragma unroll
+    for (int m = 0; m < MROWS; ++m) {
+      ss[m] = 0.0f;
+      if ((uint32_t)m < p.m) {
+        const float *xr = p.x + (size_t)m * p.k;
+        if ((p.k & 3u) == 0 && (reinterpret_cast<uintptr_t>(xr) & 15u) == 0) {
+          for (uint32_t k = threadIdx.x * 4; k < p.k; k += GEMV_THREADS * 4) {
+            const float4 a = *reinterpret_cast<const float4 *>(xr + k);
+            ss[m] = fmaf(a.x, a.x, ss[m]); ss[m] = fmaf(a.y, a.y, ss[m]);
+            ss[m] = fmaf(a.z, a.z, ss[m]); ss[m] = fmaf(a.w, a.w, ss[m]);
+          }
+        } else {
+          for (uint32_t k = threadIdx.x; k < p.k; k += GEMV_THREADS) ss[m] = fmaf(xr[k], xr[k], ss[m]);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss[m] += __shfl_xor_sync(0xffffffffu, ss[m], o);
+      if (lane == 0) red[warp * MROWS + m] = ss[m];
+    }
+  }
+  // ---- stage this CTA's slice of x (times the norm weight) as xs[k][m]
+  for (uint32_t idx = threadIdx.x; idx < k_len * MROWS; idx += GEMV_THREADS) {
+    const uint32_t kk = idx / MROWS, m = idx % MROWS;
+    float v = 0.0f;
+    if (m < p.m) {
+      v = p.x[(size_t)m * p.k + k_lo + kk];
+      if (p.norm_w) v *= p.norm_w[k_lo + kk];
+    }
+    xs[idx] = v;
+  }
+  __syncthreads();
+  if (p.norm_w && rank == 0 && threadIdx.x < MROWS) {
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < GEMV_WARPS; ++w) s += red[w * MROWS + threadIdx.x];
+    scale[threadIdx.x] = rsqrtf(s / (float)p.k + p.norm_eps);   // read after the reduction barriers below
+  }
+
+  // ---- stream the weights: pass i multiplies while pass i+1 is in flight
   float2 acc[MROWS][4];
 #pragma unroll
   for (int m = 0; m < MROWS; ++m)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[m][j] = make_float2(0.f, 0.f);
 
-  const uint32_t step = (uint32_t)nw * RPL;
-  for (uint32_t kb = k_lo + (uint32_t)wi * RPL; kb < k_hi; kb += step * GEMV_UNROLL) {
-    uint4 wv[GEMV_UNROLL];
+  auto mul_pass = [&](const uint4 (&wv)[U], uint32_t pass) {
+    const uint32_t kk0 = pass * rows_per_pass + (uint32_t)wi * RPL + lrow;
 #pragma unroll
-    for (int u = 0; u < GEMV_UNROLL; ++u) {
-      const uint32_t k = kb + u * step + lrow;
-      wv[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (k < k_hi && col_ok) wv[u] = __ldcs(reinterpret_cast<const uint4 *>(W + base + (size_t)k * row_stride));
-    }
-#pragma unroll
-    for (int u = 0; u < GEMV_UNROLL; ++u) {
-      const uint32_t k = kb + u * step + lrow;
-      if (k < k_hi) {
+    for (int u = 0; u < U; ++u) {
+      const uint32_t kk = kk0 + u * nw * RPL;
+      if (kk < k_len) {
         const __half2 *h = reinterpret_cast<const __half2 *>(&wv[u]);
         float2 w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) w[j] = __half22float2(h[j]);
-        const float *xr = xs + (size_t)(k - k_lo) * MROWS;
+        const float *xr = xs + (size_t)kk * MROWS;
         float xm[MROWS];
         if constexpr (MROWS >= 4) {
 #pragma unroll
@@ -144,12 +205,19 @@ gemv_f16w_kernel(const GemvParams p) {
         }
 #pragma unroll
         for (int m = 0; m < MROWS; ++m) {
-          const float xv = xm[m];
-          const float2 x2 = make_float2(xv, xv);
+          const float2 x2 = make_float2(xm[m], xm[m]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[m][j] = __ffma2_rn(x2, w[j], acc[m][j]);
         }
       }
+    }
+  };
+  for (uint32_t pass = 0; pass < passes; pass += 2) {
+    mul_pass(wa, pass);
+    if (pass + 2 < passes) load_pass(wa, pass + 2);
+    if (pass + 1 < passes) {
+      mul_pass(wb, pass + 1);
+      if (pass + 3 < passes) load_pass(wb, pass + 3);
     }
   }
 
@@ -165,78 +233,98 @@ gemv_f16w_kernel(const GemvParams p) {
       }
   if (lane < LPR) {
 #pragma unroll
-    for (int m = 0; m < MROWS; ++m)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float *dst = wpart + (((size_t)mat * GEMV_WARPS + wi) * MROWS + m) * TN + lcg + 2 * j;
-        dst[0] = acc[m][j].x;
-        dst[1] = acc[m][j].y;
-      }
+    for (int m = 0; m < MROWS; ++m) {
+      float *dst = wpart + ((size_t)warp * MROWS + m) * TN + lcg;
+      reinterpret_cast<float4 *>(dst)[0] = make_float4(acc[m][0].x, acc[m][0].y, acc[m][1].x, acc[m][1].y);
+      reinterpret_cast<float4 *>(dst)[1] = make_float4(acc[m][2].x, acc[m][2].y, acc[m][3].x, acc[m][3].y);
+    }
   }
   __syncthreads();
   const int nmat = dual ? 2 : 1;
+  float *cdst = S > 1 ? cluster.map_shared_rank(cpart, 0) : cpart;   // rank 0's buffer
   for (int idx = threadIdx.x; idx < nmat * MROWS * TN; idx += GEMV_THREADS) {
     const int mt = idx / (MROWS * TN), rem = idx % (MROWS * TN);
     float s = 0.0f;
-    for (int w = 0; w < nw; ++w) s += wpart[((size_t)mt * GEMV_WARPS + w) * MROWS * TN + rem];
-    cpart[idx] = s;
+    for (int w = 0; w < nw; ++w) s += wpart[((size_t)(mt * nw + w)) * MROWS * TN + rem];
+    cdst[(size_t)rank * 2 * MROWS * TN + idx] = s;
   }
-  if (S > 1) cluster.sync(); else __syncthreads();
-
-  if (rank == 0) {
-    float *fin = wpart;   // reuse: final pre-store values [MROWS][TN]
-    for (int idx = threadIdx.x; idx < MROWS * TN; idx += GEMV_THREADS) {
-      float g = 0.0f, u = 0.0f;
-      for (uint32_t r = 0; r < S; ++r) {
-        const float *rp = S > 1 ? cluster.map_shared_rank(cpart, r) : cpart;
-        g += rp[idx];
-        if (dual) u += rp[MROWS * TN + idx];
-      }
-      float v = p.alpha == 1.0f ? g : p.alpha * g;
-      if (dual) v = epi_activate(v, 2) * u;
-      fin[idx] = v;
-    }
+  if (S > 1) {
+    cluster.barrier_arrive();          // release: the pushed partials are visible to rank 0 after its wait
+    if (rank != 0) return;
+    cluster.barrier_wait();
+  } else {
     __syncthreads();
-    const uint32_t pos = p.pos_base + (p.pos_ptr ? *p.pos_ptr : 0u);
-    for (int idx = threadIdx.x; idx < MROWS * TN; idx += GEMV_THREADS) {
-      const uint32_t m = idx / TN, c = col0 + idx % TN;
-      if (m >= p.m || c >= p.n) continue;
-      const size_t ci = (size_t)m * p.n + c;
-      float v = fin[idx];
-      if (p.store_kind == 0) {
-        if (p.accumulate) v += p.c[ci];
-        v = epi_apply(v, p.bias != nullptr, p.bias ? p.bias[c] : 0.0f, p.act, p.binary,
-                      p.d ? p.d[ci] : 0.0f, p.beta);
+  }
+
+  // ---- rank 0: sum ranks in order, epilogue, store
+  float *fin = wpart;   // reuse: final pre-store values [MROWS][TN]
+  float *fin2 = wpart + MROWS * TN;
+  for (int idx = threadIdx.x; idx < MROWS * TN; idx += GEMV_THREADS) {
+    float gsum = 0.0f, usum = 0.0f;
+    for (uint32_t r = 0; r < S; ++r) {
+      const float *rp = cpart + (size_t)r * 2 * MROWS * TN;
+      gsum += rp[idx];
+      if (dual) usum += rp[MROWS * TN + idx];
+    }
+    if (p.norm_w) {
+      const float sc = scale[idx / TN];
+      gsum *= sc;
+      usum *= sc;
+    }
+    float v = p.alpha == 1.0f ? gsum : p.alpha * gsum;
+    if (dual) {
+      v = epi_activate(v, 2) * usum;
+      fin2[idx] = usum;
+    }
+    fin[idx] = v;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < MROWS * TN; idx += GEMV_THREADS) {
+    const uint32_t m = idx / TN, c = col0 + idx % TN;
+    if (m >= p.m || c >= p.n) continue;
+    const size_t ci = (size_t)m * p.n + c;
+    float v = fin[idx];
+    if (dual && p.c2) p.c2[ci] = fin2[idx];
+    if (p.store_kind == 0) {
+      if (p.accumulate) v += p.c[ci];
+      v = epi_apply(v, p.bias != nullptr, p.bias ? p.bias[c] : 0.0f, p.act, p.binary,
+                    p.d ? p.d[ci] : 0.0f, p.beta);
+      p.c[ci] = v;
+    } else {
+      if (p.store_kind != 2) {   // rope with the partner column (c ^ 1)
+        const float partner = fin[idx ^ 1];
+        const uint32_t dim = c % p.head_dim;
+        const float *cs = p.table + ((size_t)pos * (p.head_dim / 2) + dim / 2) * 2;
+        v = (dim & 1u) == 0u ? fmaf(v, cs[0], -partner * cs[1]) : fmaf(partner, cs[1], v * cs[0]);
+      }
+      if (p.store_kind == 1) {
         p.c[ci] = v;
       } else {
-        if (p.store_kind != 2) {   // rope with the partner column (c ^ 1)
-          const float partner = fin[idx ^ 1];
-          const uint32_t dim = c % p.head_dim;
-          const float *cs = p.table + ((size_t)pos * (p.head_dim / 2) + dim / 2) * 2;
-          v = (dim & 1u) == 0u ? fmaf(v, cs[0], -partner * cs[1]) : fmaf(partner, cs[1], v * cs[0]);
-        }
-        if (p.store_kind == 1) {
-          p.c[ci] = v;
-        } else {
-          const size_t di = (size_t)pos * p.pos_scale + (size_t)(c / p.head_dim) * p.stride_head +
-                            (size_t)(c % p.head_dim) * p.stride_dim;
-          if (p.dst_f16) reinterpret_cast<__half *>(p.dst)[di] = __float2half_rn(v);
-          else reinterpret_cast<float *>(p.dst)[di] = v;
-        }
+        const size_t di = (size_t)pos * p.pos_scale + (size_t)(c / p.head_dim) * p.stride_head +
+                          (size_t)(c % p.head_dim) * p.stride_dim;
+        if (p.dst_f16) reinterpret_cast<__half *>(p.dst)[di] = __float2half_rn(v);
+        else reinterpret_cast<float *>(p.dst)[di] = v;
       }
     }
   }
-  if (S > 1) cluster.sync();   // remote partials stay mapped until rank 0 has read them
 }
 
-size_t gemv_smem_bytes(uint32_t k_cta_max, int mrows, int tn) {
-  return ((size_t)k_cta_max * mrows + 2 * (size_t)GEMV_WARPS * mrows * tn + 2 * (size_t)mrows * tn + mrows) *
-             sizeof(float) + 16;
+size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s) {
+  return ((size_t)k_cta * mrows + (size_t)GEMV_WARPS * mrows * tn + (size_t)s * 2 * mrows * tn +
+          (size_t)GEMV_WARPS * mrows + mrows) * sizeof(float) + 16;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("TA_NO_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
 }
 
 template <int MROWS, int TN>
-void launch_t(GemvParams p, uint32_t tiles, cudaStream_t stream) {
-  const size_t smem = gemv_smem_bytes(p.k_cta_max, MROWS, TN);
+void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
+  const size_t smem = gemv_smem_bytes(g.k_cta, MROWS, TN, g.ksplit);
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -246,18 +334,25 @@ void launch_t(GemvParams p, uint32_t tiles, cudaStream_t stream) {
     attr_done[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles * p.ksplit, 1, 1);
+  cfg.gridDim = dim3(tiles * g.ksplit, 1, 1);
   cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = p.ksplit;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = g.ksplit;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = 1;
+  ++na;
+  if (g.pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN>, p));
+  cfg.numAttrs = na;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN>, g));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -270,38 +365,50 @@ bool gemv_f16w_supported(uint32_t m, uint32_t n, uint32_t k, bool packed, uint32
   return n % 8 == 0;   // 16-byte loads of row-major rows
 }
 
-void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream) {
-  const uint32_t tn = p.packed ? p.tile_n : 32;
-  const uint32_t tiles = (p.n + tn - 1) / tn;
-  const int mrows = p.m <= 1 ? 1 : p.m <= 2 ? 2 : p.m <= 4 ? 4 : 8;
-  // K split over a cluster: fill the machine, keep every
-  // CTA's x slice inside shared memory, never split below 256 rows.
-  const uint64_t per_sm = mrows == 1 ? 5 : mrows == 2 ? 4 : mrows == 4 ? 3 : 2;   // resident CTAs (registers)
-  const uint64_t slots = per_sm * (uint64_t)sm_count;
-  uint32_t best_s = 0;
-  double best_eff = -1.0;
+// Segments must agree on everything the CTA geometry depends on.
+bool gemv_f16w_groupable(const GemvParams &a, const GemvParams &b) {
+  const uint32_t ta = a.packed ? a.tile_n : 32, tb = b.packed ? b.tile_n : 32;
+  return a.x == b.x && a.m == b.m && a.k == b.k && a.norm_w == b.norm_w && a.norm_eps == b.norm_eps &&
+         ta == tb && !a.w2 == !b.w2;
+}
+
+void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, cudaStream_t stream) {
+  if (nseg < 1 || nseg > GEMV_MAX_SEGS) fail("GEMV group of %d segments (1..%d)", nseg, GEMV_MAX_SEGS);
+  GemvGroup g{};
+  const GemvParams &p0 = segs[0];
+  const uint32_t tn = p0.packed ? p0.tile_n : 32;
+  uint32_t tiles = 0;
+  for (int i = 0; i < nseg; ++i) {
+    if (i && !gemv_f16w_groupable(p0, segs[i])) fail("GEMV group: segment %d does not share x / K / tile with segment 0", i);
+    g.seg[i] = segs[i];
+    tiles += (segs[i].n + tn - 1) / tn;
+    g.tile_end[i] = tiles;
+  }
+  g.nseg = (uint32_t)nseg;
+  g.pdl = (pdl && pdl_enabled()) ? 1u : 0u;
+  const int mrows = p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8;
+  const uint32_t u = mrows <= 2 ? 4 : 2;
+  const uint32_t rpl = 32 / (tn / 8);
+  const uint32_t nw = p0.w2 ? GEMV_WARPS / 2 : GEMV_WARPS;
+  const uint32_t rows_per_pass = nw * rpl * u;
+  // K split over a cluster: aim at two CTAs and more per SM so that most of a small
+  // matrix is in flight at once; never split below one pass of rows.
+  uint32_t best_s = 1;
   for (uint32_t s : {1u, 2u, 4u, 8u}) {
-    if (s > 1 && p.k / s < 256) break;
-    const uint32_t rpl = 32 / (tn / 8);
-    const uint32_t k_cta = (((p.k + rpl - 1) / rpl + s - 1) / s) * rpl;
-    if (gemv_smem_bytes(k_cta, mrows, (int)tn) > 196 * 1024) continue;
-    const double waves = (double)tiles * s / (double)slots;
-    const double eff = waves / (double)(uint64_t)(waves + 0.999999);
-    if (eff > best_eff + 0.02) {
-      best_eff = eff;
-      best_s = s;
-    }
+    if (s > 1 && p0.k / s < rows_per_pass) break;
+    const uint32_t k_cta = (p0.k + s - 1) / s;
+    if (gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 160 * 1024) continue;
+    best_s = s;
+    if ((uint64_t)tiles * s >= 2ull * (uint64_t)sm_count) break;
   }
-  if (!best_s) fail("GEMV: K = %u with %u rows does not fit shared memory at any cluster split", p.k, p.m);
-  p.ksplit = best_s;
-  {
-    const uint32_t rpl = 32 / (tn / 8);
-    p.k_cta_max = (((p.k + rpl - 1) / rpl + best_s - 1) / best_s) * rpl;
-  }
+  g.ksplit = best_s;
+  g.k_cta = (p0.k + best_s - 1) / best_s;
+  if (gemv_smem_bytes(g.k_cta, mrows, (int)tn, best_s) > 196 * 1024)
+    fail("GEMV: K = %u with %u rows does not fit shared memory at any cluster split", p0.k, p0.m);
 #define TA_GEMV_CASE(MR)                                             \
   if (mrows == MR) {                                                 \
-    if (tn == 64) launch_t<MR, 64>(p, tiles, stream);                \
-    else launch_t<MR, 32>(p, tiles, stream);                         \
+    if (tn == 64) launch_t<MR, 64>(g, tiles, stream);                \
+    else launch_t<MR, 32>(g, tiles, stream);                         \
     return;                                                          \
   }
   TA_GEMV_CASE(1)
@@ -309,6 +416,10 @@ void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream) {
   TA_GEMV_CASE(4)
   TA_GEMV_CASE(8)
 #undef TA_GEMV_CASE
+}
+
+void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream) {
+  launch_gemv_f16w_group(&p, 1, sm_count, true, stream);
 }
 
 }  // namespace ta

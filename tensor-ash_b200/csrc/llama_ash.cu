@@ -349,7 +349,7 @@ namespace {
 
 
 // Prefill activations are allocated once for t_max rows; a call works on
-// free reshapes of their first n rows (Tensor::alias_with_shape).
+// views of their first n rows (same buffer, shorter shape).
 PrefillScratch prefill_view(ta_llama &m, uint32_t n);
 
 ExecOp copy_op(const Tensor &src, const Tensor &dst, std::array<uint32_t, 3> extent, uint32_t src_off,
@@ -423,7 +423,7 @@ PrefillScratch prefill_view(ta_llama &m, uint32_t n) {
   const ta_llama_config &c = m.cfg;
   const uint32_t kv_dim = c.kv_heads * c.head_dim;
   PrefillScratch &full = *m.prefill_full;
-  if (full.x_a.len() == 0) {
+  if (full.x_a.shape.empty()) {
     auto f32 = [&](uint32_t cols) { return make(m.ctx, {c.t_max, cols}, DType::F32); };
     full.x_a = f32(c.embd); full.x_b = f32(c.embd); full.xn = f32(c.embd);
     full.qkv = f32(c.embd + 2 * kv_dim);
@@ -433,9 +433,12 @@ PrefillScratch prefill_view(ta_llama &m, uint32_t n) {
     full.last = make(m.ctx, {1, c.embd}, DType::F32);
     full.last_n = make(m.ctx, {1, c.embd}, DType::F32);
   }
-  auto rows = [&](const Tensor &t, uint32_t cols) {
-    const uint32_t shape[2] = {n, cols};
-    return t.alias_with_shape(shape, 2);
+  auto rows = [&](const Tensor &t, uint32_t cols) {   // the first n rows of a [t_max, cols] buffer
+    Tensor v;
+    v.buf = t.buf;
+    v.shape = {n, cols};
+    v.dtype = t.dtype;
+    return v;
   };
   PrefillScratch s;
   s.x_a = rows(full.x_a, c.embd); s.x_b = rows(full.x_b, c.embd); s.xn = rows(full.xn, c.embd);

@@ -269,6 +269,7 @@ struct GemvParams {
   const void *w;           // f16 weights, [K, N] or packed [N/tile][K][tile]
   const void *w2;          // optional second matrix sharing x: out = silu(x@w) * (x@w2)
   float *c;                // [M, N]
+  float *c2;               // with w2: optional [M, N] destination of x@w2 itself
   const float *bias, *d;   // epilogue operands (bias [N]; D [M, N])
   const float *norm_w;     // fused RMSNorm weight [K] (nullptr = off)
   float norm_eps;
@@ -276,12 +277,21 @@ struct GemvParams {
   float alpha, beta;
   uint32_t accumulate, act, binary;
   uint32_t packed, tile_n;
-  uint32_t ksplit, k_cta_max;   // filled by the launcher
   // fused store (StoreKind): rope table, scatter destination, position cell
   uint32_t store_kind, head_dim, pos_base, pos_scale, stride_head, stride_dim, dst_f16;
   const float *table;
   void *dst;
   const uint32_t *pos_ptr;
+};
+
+// Up to three GEMVs sharing x, M, K, norm and tile width in one launch.
+constexpr int GEMV_MAX_SEGS = 3;
+struct GemvGroup {
+  GemvParams seg[GEMV_MAX_SEGS];
+  uint32_t tile_end[GEMV_MAX_SEGS];   // running tile count after each segment
+  uint32_t nseg;
+  uint32_t ksplit, k_cta;             // cluster size along K and rows per rank
+  uint32_t pdl;                       // 1: launched with programmatic stream serialization
 };
 
 struct FlashParams {
@@ -302,6 +312,8 @@ struct AttnDecodeParams {
   float scale;
   uint32_t kv_f16;
   const uint32_t *pos_ptr;
+  uint32_t *counters;   // per-kv-head tickets (zero between launches), owned by the submitting slot
+  uint32_t pdl;
 };
 
 struct FlashAttentionDesc {
@@ -365,6 +377,7 @@ struct Slot;
 using Launch = std::function<void(Slot &, cudaStream_t)>;
 
 constexpr uint32_t ATTN_DECODE_MAX_CHUNKS = 32;
+constexpr uint32_t ATTN_DECODE_MAX_KV_HEADS = 256;
 inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
   const uint32_t c = (kv_len + 31) / 32;
   return c < 8 ? 8 : (c > ATTN_DECODE_MAX_CHUNKS ? ATTN_DECODE_MAX_CHUNKS : c);
@@ -384,6 +397,7 @@ struct Slot {
   void *staging = nullptr;       // grow-only pinned host staging
   size_t staging_bytes = 0;
   uint32_t *status = nullptr;    // device word: kernels report bounded-wait timeouts here
+  uint32_t *counters = nullptr;  // ATTN_DECODE_MAX_KV_HEADS zeroed device words (decode attention tickets)
   bool busy = false;
 };
 
@@ -438,6 +452,8 @@ class Executor {
   RunStats argmax(const Tensor &in, const PosCell &result);
   RunStats embed_gather(const PosCell &token, const Tensor &table, const Tensor &out);
   RunStats embed_gather_rows(const TokenIds &tokens, const Tensor &table, const Tensor &out);
+  bool gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route, GemvParams *out) const;
+  std::vector<Launch> plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops, size_t *n_calls) const;
   RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
                        const Tensor *norm_w, float eps);
   void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
@@ -502,6 +518,7 @@ struct PreparedOps {
   cudaStream_t stream = nullptr;
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   void *scratch = nullptr;
+  uint32_t *counters = nullptr;   // this object's own decode-attention tickets
   size_t n_calls = 0;
   uint64_t total_flops = 0;
   bool in_flight = false;
@@ -534,6 +551,8 @@ void launch_splitk2_static(const GemmParams &p, cudaStream_t stream);
 
 bool gemv_f16w_supported(uint32_t m, uint32_t n, uint32_t k, bool packed, uint32_t tile_n);
 void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream);
+bool gemv_f16w_groupable(const GemvParams &a, const GemvParams &b);
+void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, cudaStream_t stream);
 
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream);
 void launch_attn_decode(const AttnDecodeParams &p, cudaStream_t stream);

@@ -322,7 +322,12 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
                                                   need(o.in2, "run_attn_decode", "v"), need(o.in3, "run_attn_decode", "scratch"),
                                                   need(o.out, "run_attn_decode", "out"), o.attn);
       if (n_calls) *n_calls += 1;   // two dispatches
-      return [p](Slot &, cudaStream_t st) { launch_attn_decode(p, st); };
+      return [p](Slot &slot, cudaStream_t st) {
+        AttnDecodeParams q = p;
+        q.counters = slot.counters;
+        q.pdl = 1;
+        launch_attn_decode(q, st);
+      };
     }
     case ExecKind::FlashAttn: {
       const FlashParams p = plan_flash_attention(need(o.in0, "run_flash_attention", "q"), need(o.in1, "run_flash_attention", "kt"),
@@ -376,13 +381,104 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
 }
 
 // ------------------------------------------------------------------ submission
+// Plans a whole op list.  Besides planning op by op it fuses launches where the
+// result is the same as running the ops one after another:
+//   * consecutive row-GEMVs that read the same x (same fused norm, M, K, tile
+//     width) and neither read nor overwrite one another's outputs become
+//     segments of one launch (the q / k / v projections of a decode layer);
+//   * `up = x@Wup` directly followed by `gate = silu(x@Wg) * up` becomes the
+//     dual-matrix launch, which still writes `up`.
+// The reference gets the same effect from eliding barriers between independent
+// dispatches (HazardCursor, src/executor/graph_ops.rs:587-624); here a launch
+// boundary is the barrier, so independent ops share a launch instead.
+std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops,
+                                            size_t *n_calls) const {
+  struct Cand {
+    bool gemv = false;
+    GemvParams g{};
+    uint64_t flops = 0;
+  };
+  auto candidate = [&](const ExecOp &o) {
+    Cand c;
+    if (o.kind != ExecKind::Matmul) return c;
+    validate_op_tensors(*this, o.mm);
+    const ResolvedMatmul r = ResolvedMatmul::from_op(o.mm);
+    const Route route = plan_op(o.mm, r, false);
+    c.gemv = gemv_params_for(o.mm, r, route, &c.g);
+    c.flops = r.total_flops;
+    return c;
+  };
+  auto writes = [](const GemvParams &g) -> const void * { return g.store_kind >= 2 ? g.dst : (const void *)g.c; };
+  auto reads_ptr = [](const GemvParams &g, const void *ptr) {
+    return ptr == g.x || ptr == g.d || ptr == g.bias || ptr == g.norm_w || ptr == g.table ||
+           (g.accumulate && ptr == g.c);
+  };
+  const int sms = ctx_->sm_count;
+  std::vector<Launch> plan;
+  plan.reserve(ops.size());
+  size_t i = 0;
+  while (i < ops.size()) {
+    Cand c0 = candidate(ops[i]);
+    if (!c0.gemv) {
+      plan.push_back(plan_exec_op(ops[i], flops, n_calls));
+      ++i;
+      continue;
+    }
+    // SwiGLU pair
+    if (i + 1 < ops.size()) {
+      Cand c1 = candidate(ops[i + 1]);
+      const GemvParams &u = c0.g, &gt = c1.g;
+      const bool up_plain = u.alpha == 1.0f && !u.accumulate && !u.bias && u.act == 0 && u.binary == 0 &&
+                            u.store_kind == 0;
+      if (c1.gemv && up_plain && gemv_f16w_groupable(u, gt) && u.n == gt.n && gt.alpha == 1.0f &&
+          !gt.accumulate && !gt.bias && gt.act == (uint32_t)Activation::Silu &&
+          gt.binary == (uint32_t)BinaryKind::Mul && gt.d == u.c && gt.store_kind == 0 && gt.c != u.c &&
+          gt.x != u.c) {
+        GemvParams f = gt;
+        f.w2 = u.w;
+        f.c2 = u.c;
+        f.act = 0; f.binary = 0; f.d = nullptr;
+        if (flops) *flops += c0.flops + c1.flops;
+        if (n_calls) *n_calls += 2;
+        plan.push_back([f, sms](Slot &, cudaStream_t st) { launch_gemv_f16w_group(&f, 1, sms, true, st); });
+        i += 2;
+        continue;
+      }
+    }
+    // group of independent GEMVs on the same x
+    std::vector<GemvParams> segs{c0.g};
+    uint64_t fl = c0.flops;
+    size_t j = i + 1;
+    while (j < ops.size() && segs.size() < (size_t)GEMV_MAX_SEGS) {
+      Cand cj = candidate(ops[j]);
+      if (!cj.gemv || cj.g.w2 || !gemv_f16w_groupable(segs[0], cj.g)) break;
+      bool independent = true;
+      for (const GemvParams &e : segs) {
+        if (reads_ptr(cj.g, writes(e)) || reads_ptr(e, writes(cj.g)) || writes(e) == writes(cj.g))
+          independent = false;
+        // a scatter segment may also leave its plain C untouched; keep C buffers apart as well
+        if (e.c == cj.g.c && (e.store_kind < 2 || cj.g.store_kind < 2)) independent = false;
+      }
+      if (!independent) break;
+      segs.push_back(cj.g);
+      fl += cj.flops;
+      ++j;
+    }
+    if (flops) *flops += fl;
+    if (n_calls) *n_calls += segs.size();
+    plan.push_back([segs, sms](Slot &, cudaStream_t st) {
+      launch_gemv_f16w_group(segs.data(), (int)segs.size(), sms, true, st);
+    });
+    i = j;
+  }
+  return plan;
+}
+
 RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
   if (ops.empty()) return RunStats{std::nullopt, 0, 0};
   uint64_t flops = 0;
   size_t n_calls = 0;
-  std::vector<Launch> plan;
-  plan.reserve(ops.size());
-  for (const ExecOp &op : ops) plan.push_back(plan_exec_op(op, &flops, &n_calls));
+  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls);
   ctx_->make_current();
   Slot &slot = checkout_slot();
   SlotGuard g(*this, slot);
@@ -398,15 +494,18 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
   exec.context()->make_current();
   auto prep = std::make_unique<PreparedOps>();
   prep->exec = &exec;
-  std::vector<Launch> plan;
-  plan.reserve(ops.size());
-  for (const ExecOp &op : ops) plan.push_back(exec.plan_exec_op(op, &prep->total_flops, &prep->n_calls));
+  std::vector<Launch> plan = exec.plan_exec_ops(ops, &prep->total_flops, &prep->n_calls);
   TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
   TA_CUDA(cudaEventCreate(&prep->ev_begin));
   TA_CUDA(cudaEventCreate(&prep->ev_end));
-  Slot &slot = exec.checkout_slot();
+  TA_CUDA(cudaMalloc((void **)&prep->counters, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
+  TA_CUDA(cudaMemset(prep->counters, 0, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
+  Slot &real_slot = exec.checkout_slot();
   {
-    SlotGuard g(exec, slot);
+    SlotGuard g(exec, real_slot);
+    // the captured launches must not point at state another submission may use later
+    Slot slot = real_slot;
+    slot.counters = prep->counters;
     // Run once eagerly: first-use set-up (function attributes, tensor maps) must
     // not happen inside the capture, and it proves the batch launches at all.
     for (const Launch &l : plan) l(slot, prep->stream);

@@ -134,6 +134,8 @@ Executor::Executor(std::shared_ptr<Context> ctx, int selection, ExecutorConfig c
     TA_CUDA(cudaEventCreate(&s.ev_end));
     TA_CUDA(cudaMalloc(&s.status, sizeof(uint32_t)));
     TA_CUDA(cudaMemset(s.status, 0, sizeof(uint32_t)));
+    TA_CUDA(cudaMalloc((void **)&s.counters, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
+    TA_CUDA(cudaMemset(s.counters, 0, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
   }
   tune_path_ = tune_store_path(ctx_->name);
   tuned_ = load_tuned(tune_path_);
@@ -150,6 +152,7 @@ Executor::~Executor() {
     if (s.scratch) cudaFree(s.scratch);
     if (s.staging) cudaFreeHost(s.staging);
     if (s.status) cudaFree(s.status);
+    if (s.counters) cudaFree(s.counters);
     if (s.ev_begin) cudaEventDestroy(s.ev_begin);
     if (s.ev_end) cudaEventDestroy(s.ev_end);
     if (s.stream) cudaStreamDestroy(s.stream);
@@ -401,39 +404,52 @@ GemmParams make_params(const MatmulOp &op, const ResolvedMatmul &r) {
 }
 }  // namespace
 
+// GEMV launch description of an op on the row-GEMV route; false when the route is another family.
+bool Executor::gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route,
+                               GemvParams *out) const {
+  const KernelSpec &spec = KERNEL_SPECS[route.kernel];
+  if (!(spec.family == Family::RowGemv && r.b_f16)) return false;
+  if (r.a_f16) fail("f16 A storage (a16 route) is not built in this library yet");
+  const uint32_t tile_n = op.packed_b ? f16w_row_tile_n(r.k, r.n) : 32;
+  if (!gemv_f16w_supported(r.m, r.n, r.k, op.packed_b, tile_n) || r.batch != 1)
+    fail("row-GEMV route cannot run M=%u N=%u K=%u batch=%u packed=%d", r.m, r.n, r.k, r.batch,
+         (int)op.packed_b);
+  GemvParams g{};
+  g.x = static_cast<const float *>(op.call.a->ptr());
+  g.w = op.call.b->ptr();
+  g.w2 = nullptr;
+  g.c = static_cast<float *>(op.call.c->ptr());
+  g.c2 = nullptr;
+  g.bias = op.epilogue.bias ? static_cast<const float *>(op.epilogue.bias->ptr()) : nullptr;
+  g.d = op.epilogue.d ? static_cast<const float *>(op.epilogue.d->ptr()) : nullptr;
+  g.norm_w = op.normed_weight ? static_cast<const float *>(op.normed_weight->ptr()) : nullptr;
+  g.norm_eps = op.normed_eps;
+  g.m = r.m; g.n = r.n; g.k = r.k;
+  g.alpha = op.call.alpha; g.beta = op.epilogue.beta;
+  g.accumulate = op.call.accumulate; g.act = (uint32_t)op.epilogue.activation;
+  g.binary = (uint32_t)op.epilogue.binary;
+  g.packed = op.packed_b; g.tile_n = tile_n;
+  g.store_kind = (uint32_t)op.store.kind;
+  g.head_dim = op.store.head_dim; g.pos_base = op.store.pos_base; g.pos_scale = op.store.pos_scale;
+  g.stride_head = op.store.stride_head; g.stride_dim = op.store.stride_dim;
+  g.table = op.store.table ? static_cast<const float *>(op.store.table->ptr()) : nullptr;
+  g.dst = op.store.dst ? op.store.dst->ptr() : nullptr;
+  g.dst_f16 = op.store.dst && op.store.dst->dtype == DType::F16;
+  g.pos_ptr = op.store.pos_cell ? op.store.pos_cell->device : nullptr;
+  *out = g;
+  return true;
+}
+
 void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Route &route,
                           Slot &slot, cudaStream_t stream) {
   if (r.a_f16) fail("f16 A storage (a16 route) is not built in this library yet");
   const KernelSpec &spec = KERNEL_SPECS[route.kernel];
-  if (spec.family == Family::RowGemv && r.b_f16) {
-    const uint32_t tile_n = op.packed_b ? f16w_row_tile_n(r.k, r.n) : 32;
-    if (!gemv_f16w_supported(r.m, r.n, r.k, op.packed_b, tile_n) || r.batch != 1)
-      fail("row-GEMV route cannot run M=%u N=%u K=%u batch=%u packed=%d", r.m, r.n, r.k, r.batch,
-           (int)op.packed_b);
-    if (op.epilogue.bias && op.epilogue.bias->shape.size() == 2 && r.batch == 1) { /* [1, N] is [N] */ }
-    GemvParams g{};
-    g.x = static_cast<const float *>(op.call.a->ptr());
-    g.w = op.call.b->ptr();
-    g.w2 = nullptr;
-    g.c = static_cast<float *>(op.call.c->ptr());
-    g.bias = op.epilogue.bias ? static_cast<const float *>(op.epilogue.bias->ptr()) : nullptr;
-    g.d = op.epilogue.d ? static_cast<const float *>(op.epilogue.d->ptr()) : nullptr;
-    g.norm_w = op.normed_weight ? static_cast<const float *>(op.normed_weight->ptr()) : nullptr;
-    g.norm_eps = op.normed_eps;
-    g.m = r.m; g.n = r.n; g.k = r.k;
-    g.alpha = op.call.alpha; g.beta = op.epilogue.beta;
-    g.accumulate = op.call.accumulate; g.act = (uint32_t)op.epilogue.activation;
-    g.binary = (uint32_t)op.epilogue.binary;
-    g.packed = op.packed_b; g.tile_n = tile_n;
-    g.store_kind = (uint32_t)op.store.kind;
-    g.head_dim = op.store.head_dim; g.pos_base = op.store.pos_base; g.pos_scale = op.store.pos_scale;
-    g.stride_head = op.store.stride_head; g.stride_dim = op.store.stride_dim;
-    g.table = op.store.table ? static_cast<const float *>(op.store.table->ptr()) : nullptr;
-    g.dst = op.store.dst ? op.store.dst->ptr() : nullptr;
-    g.dst_f16 = op.store.dst && op.store.dst->dtype == DType::F16;
-    g.pos_ptr = op.store.pos_cell ? op.store.pos_cell->device : nullptr;
-    launch_gemv_f16w(g, ctx_->sm_count, stream);
-    return;
+  {
+    GemvParams g;
+    if (gemv_params_for(op, r, route, &g)) {
+      launch_gemv_f16w(g, ctx_->sm_count, stream);
+      return;
+    }
   }
   if (op.packed_b || op.normed_weight || !op.store.is_none())
     fail("packed-B / normed-A / fused-store ops need the f16-weight row-GEMV route");
@@ -780,6 +796,7 @@ PreparedOps::~PreparedOps() {
   if (ev_begin) cudaEventDestroy(ev_begin);
   if (ev_end) cudaEventDestroy(ev_end);
   if (stream) cudaStreamDestroy(stream);
+  if (counters) cudaFree(counters);
 }
 
 void PreparedOps::submit() {
