@@ -18,6 +18,7 @@
 // device, so a captured graph serves every position.
 #include <cuda_fp16.h>
 
+#include "k_trace.cuh"
 #include "ta_core.hpp"
 
 namespace ta {
@@ -135,7 +136,7 @@ flash_prefill_kernel(const FlashParams p) {
 // the four output dims d = 4c..4c+3.  Partials [kv_heads, chunks, group, dh+2]
 // (acc, m, l) go to caller scratch.  The last CTA of a kv head to finish (a
 // ticket counter, reset for the next launch) rescales every chunk to the global
-// max and sums in chunk order, so the result does not depend on which CTA that is.
+// max while summing in chunk order, so the result does not depend on which CTA that is.
 constexpr int DEC_DH = 64, DEC_LANES = 16, DEC_THREADS = 128, DEC_BP = 64;
 
 __global__ void __launch_bounds__(DEC_THREADS)
@@ -149,14 +150,11 @@ attn_decode_kernel(const AttnDecodeParams p) {
   const uint32_t row = tid / DEC_LANES, lane = tid % DEC_LANES;
   const bool live = row < p.group;
 
+  TA_TRACE_BEGIN_IF(blockIdx.y == 0)
+  TA_TRACE(0)
   // the position cell is host-written before the launch: read it ahead of the dependency wait
   const uint32_t kv_len = p.kv_len + (p.pos_ptr ? *p.pos_ptr : 0u);
-  if (p.pdl) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  }
-  for (uint32_t i = tid; i < p.group * DEC_DH; i += DEC_THREADS) Qsh[i] = p.q[(size_t)kv_head * p.group * DEC_DH + i];
-
+  TA_TRACE(1)
   // positions per chunk, a multiple of 8 so that f16 K rows start on 16 bytes
   const uint32_t chunk_size = (((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u;
   const uint32_t p0 = min(kv_len, chunk * chunk_size), p1 = min(p0 + chunk_size, kv_len);
@@ -164,24 +162,52 @@ attn_decode_kernel(const AttnDecodeParams p) {
   const bool vec16 = p.kv_f16 && (p.t_max % 8u) == 0 &&
                      (reinterpret_cast<uintptr_t>(p.kt) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.v) & 15u) == 0;
 
+  // K: 64 d-rows x 8 groups of 8 positions; V: 64 position rows x 8 groups of 8 dims
+  uint4 kraw[4], vraw[4];
+  auto load_tile = [&](uint32_t t0, uint32_t n) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const uint32_t i = tid + it * DEC_THREADS, d = i >> 3, jg = (i & 7u) * 8u;
+      kraw[it] = make_uint4(0u, 0u, 0u, 0u);
+      vraw[it] = make_uint4(0u, 0u, 0u, 0u);
+      if (jg < n)   // a group may run past kv_len inside t_max: masked at the scores
+        kraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.kt) + kt_base + (size_t)d * p.t_max + t0 + jg);
+      const uint32_t j = i >> 3, dg = (i & 7u) * 8u;
+      if (j < n)
+        vraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)(t0 + j) * DEC_DH + dg);
+    }
+  };
+  // The launch before this one may only have appended position kv_len - 1 (the planner
+  // sets prefetch_kv when that holds): every other position is read before the wait.
+  const uint32_t n_first = min((uint32_t)DEC_BP, p1 - p0);
+  const bool newest_here = kv_len > 0 && kv_len - 1 >= p0 && kv_len - 1 < p0 + n_first;
+  const bool early = vec16 && n_first > 0 && p.prefetch_kv && !newest_here;
+  if (early) load_tile(p0, n_first);
+
+  if (p.pdl) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+  TA_TRACE(2)
+  // q: group x 64 floats, one float4 per thread (requested before the late tile loads)
+  float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool q_vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
+  if (q_vec) {
+    if (tid * 4 < p.group * DEC_DH) qv = *reinterpret_cast<const float4 *>(p.q + (size_t)kv_head * p.group * DEC_DH + tid * 4);
+  }
+  if (vec16 && n_first > 0 && !early) load_tile(p0, n_first);
+  if (q_vec) {
+    if (tid * 4 < p.group * DEC_DH) *reinterpret_cast<float4 *>(&Qsh[tid * 4]) = qv;
+  } else {
+    for (uint32_t i = tid; i < p.group * DEC_DH; i += DEC_THREADS) Qsh[i] = p.q[(size_t)kv_head * p.group * DEC_DH + i];
+  }
+
   float m_run = NEG_BIG, l_run = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
 
   for (uint32_t t0 = p0; t0 < p1; t0 += DEC_BP) {
     const uint32_t n = min((uint32_t)DEC_BP, p1 - t0);
     if (vec16) {
-      // K: 64 d-rows x 8 groups of 8 positions; V: 64 position rows x 8 groups of 8 dims
-      uint4 kraw[4], vraw[4];
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const uint32_t i = tid + it * DEC_THREADS, d = i >> 3, jg = (i & 7u) * 8u;
-        kraw[it] = make_uint4(0u, 0u, 0u, 0u);
-        vraw[it] = make_uint4(0u, 0u, 0u, 0u);
-        if (jg < n)   // a group may run past kv_len inside t_max: masked below
-          kraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.kt) + kt_base + (size_t)d * p.t_max + t0 + jg);
-        const uint32_t j = i >> 3, dg = (i & 7u) * 8u;
-        if (j < n)
-          vraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)(t0 + j) * DEC_DH + dg);
-      }
+      if (t0 != p0) load_tile(t0, n);
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const uint32_t i = tid + it * DEC_THREADS, r8 = i >> 3, g8 = (i & 7u) * 8u;
@@ -255,6 +281,7 @@ attn_decode_kernel(const AttnDecodeParams p) {
     __syncthreads();
   }
 
+  TA_TRACE(3)
   const uint32_t stride = DEC_DH + 2;
   if (live) {
     float *dst = p.scratch + (((size_t)kv_head * p.num_chunks + chunk) * p.group + row) * stride;
@@ -273,30 +300,37 @@ attn_decode_kernel(const AttnDecodeParams p) {
     if (last_flag) p.counters[kv_head] = 0u;   // ready for the next launch on this stream
   }
   __syncthreads();
+  TA_TRACE(4)
+  if (last_flag) { TA_TRACE(6) }
   if (!last_flag || !live) return;
   __threadfence();
   const float *base = p.scratch + ((size_t)kv_head * p.num_chunks * p.group + row) * stride;
   const size_t chunk_step = (size_t)p.group * stride;
   // chunks past the valid length hold nothing; partials come from other CTAs: L2 loads
   const uint32_t live_chunks = chunk_size ? min(p.num_chunks, (kv_len + chunk_size - 1) / chunk_size) : 0u;
-  float m_star = NEG_BIG;
+  // one pass in chunk order with a running maximum (the rescale of an online softmax):
+  // no load depends on a computed value, so eight chunks' partials are in flight at once
+  float m_star = NEG_BIG, l_total = 0.0f, num[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 8
-  for (uint32_t i = 0; i < live_chunks; ++i) m_star = fmaxf(m_star, __ldcg(&base[i * chunk_step + DEC_DH]));
-  float l_total = 0.0f, num[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
   for (uint32_t i = 0; i < live_chunks; ++i) {
-    const float w = expf(__ldcg(&base[i * chunk_step + DEC_DH]) - m_star);
-    l_total = fmaf(__ldcg(&base[i * chunk_step + DEC_DH + 1]), w, l_total);
+    const float m_i = __ldcg(&base[i * chunk_step + DEC_DH]);
+    const float l_i = __ldcg(&base[i * chunk_step + DEC_DH + 1]);
     // rows are dh + 2 floats long: 8-byte aligned, not 16
     const float2 a = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4]));
     const float2 b = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4 + 2]));
-    num[0] = fmaf(a.x, w, num[0]); num[1] = fmaf(a.y, w, num[1]);
-    num[2] = fmaf(b.x, w, num[2]); num[3] = fmaf(b.y, w, num[3]);
+    const float m_new = fmaxf(m_star, m_i);
+    const float c_old = expf(m_star - m_new), w = expf(m_i - m_new);
+    l_total = fmaf(l_i, w, l_total * c_old);
+    num[0] = fmaf(a.x, w, num[0] * c_old); num[1] = fmaf(a.y, w, num[1] * c_old);
+    num[2] = fmaf(b.x, w, num[2] * c_old); num[3] = fmaf(b.y, w, num[3] * c_old);
+    m_star = m_new;
   }
   const float inv = l_total > 0.0f ? 1.0f / l_total : 0.0f;
   float *o = p.out + ((size_t)kv_head * p.group + row) * DEC_DH + lane * 4;
   *reinterpret_cast<float4 *>(o) = make_float4(num[0] * inv, num[1] * inv, num[2] * inv, num[3] * inv);
+  TA_TRACE(5)
 }
+
 
 inline void launched() {
   TA_CUDA(cudaGetLastError());
@@ -304,6 +338,8 @@ inline void launched() {
 }
 
 }  // namespace
+
+TA_TRACE_EXPORT(ta_debug_attn_trace)
 
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream) {
   dim3 grid((p.t_q + 63) / 64, p.heads);

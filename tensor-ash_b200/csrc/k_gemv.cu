@@ -39,9 +39,11 @@
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "k_epilogue.cuh"
+#include "k_trace.cuh"
 #include "ta_core.hpp"
 
 namespace cg = cooperative_groups;
@@ -53,13 +55,15 @@ namespace {
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 
+constexpr int XS_PRE = 6;   // slice elements per thread fetched in the single activation round trip
+
 template <int MROWS>
 struct GemvCfg {
   static constexpr int U = MROWS <= 2 ? 4 : 2;   // 16-byte loads per lane per pass
 };
 
 template <int MROWS, int TN>
-__global__ void __launch_bounds__(GEMV_THREADS)
+__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? 4 : 2)
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   constexpr int U = GemvCfg<MROWS>::U;
   constexpr int LPR = TN / 8;          // lanes per weight row (8 f16 per lane)
@@ -114,24 +118,57 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   };
 
+  TA_TRACE_BEGIN()
+  TA_TRACE(0)
   uint4 wa[U], wb[U];
   if (passes > 0) load_pass(wa, 0);
   if (passes > 1) load_pass(wb, 1);
+  TA_TRACE(1)
   // the position cell is written by the host before the launch, never by a kernel:
   // fetch it now (it may live in host memory) so its latency hides behind the weights
   uint32_t pos = p.pos_base;
   if (p.pos_ptr && rank == 0 && p.store_kind != 0) pos += *p.pos_ptr;
+  // also independent of earlier kernels: the norm weights of the first slice elements
+  // and this thread's rope table entry; epilogue operands (D, bias, old C) follow the wait
+  float nwv[XS_PRE];
+#pragma unroll
+  for (int it = 0; it < XS_PRE; ++it) {
+    const uint32_t idx = threadIdx.x + it * GEMV_THREADS, kk = idx / MROWS;
+    nwv[it] = (p.norm_w && kk < k_len) ? p.norm_w[k_lo + kk] : 1.0f;
+  }
+  const uint32_t e_m = threadIdx.x / TN, e_c = col0 + threadIdx.x % TN;
+  const bool e_valid = rank == 0 && threadIdx.x < MROWS * TN && e_m < p.m && e_c < p.n;
+  const size_t e_ci = (size_t)e_m * p.n + e_c;
+  float pre_d = 0.0f, pre_bias = 0.0f, pre_c = 0.0f;
+  float2 pre_cs = make_float2(1.0f, 0.0f);
+  if (e_valid && (p.store_kind == 1 || p.store_kind == 3))
+    pre_cs = *reinterpret_cast<const float2 *>(p.table + ((size_t)pos * (p.head_dim / 2) + (e_c % p.head_dim) / 2) * 2);
 
   // ---- everything below may depend on the previous kernel in the stream
   if (g.pdl) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
+  TA_TRACE(2)
 
-  // ---- fused RMSNorm: sum of squares per activation row (whole K, fixed order).
+  // ---- activations: one L2 round trip.  The first slice elements of every thread
+  // and (rank 0) the whole rows for the RMSNorm sum of squares are requested back
+  // to back; nothing consumes a value before every request is out.
   // x'[k] = x[k] * s * w[k] with one scalar s per row, so s factors out of the dot
   // product: the slice is staged as x[k] * w[k] and rank 0 multiplies the finished
   // sums by s.  Only rank 0 needs s, and nothing waits for it before the epilogue.
+  const uint32_t stage_n = k_len * MROWS;
+  float xv[XS_PRE];
+#pragma unroll
+  for (int it = 0; it < XS_PRE; ++it) {
+    const uint32_t idx = threadIdx.x + it * GEMV_THREADS, kk = idx / MROWS, m = idx % MROWS;
+    xv[it] = (idx < stage_n && m < p.m) ? p.x[(size_t)m * p.k + k_lo + kk] : 0.0f;
+  }
+  if (e_valid && p.store_kind == 0) {
+    if (p.d) pre_d = p.d[e_ci];
+    if (p.bias) pre_bias = p.bias[e_c];
+    if (p.accumulate) pre_c = p.c[e_ci];
+  }
   if (p.norm_w && rank == 0) {
     float ss[MROWS];
 #pragma unroll
@@ -155,7 +192,12 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   }
   // ---- stage this CTA's slice of x (times the norm weight) as xs[k][m]
-  for (uint32_t idx = threadIdx.x; idx < k_len * MROWS; idx += GEMV_THREADS) {
+#pragma unroll
+  for (int it = 0; it < XS_PRE; ++it) {
+    const uint32_t idx = threadIdx.x + it * GEMV_THREADS;
+    if (idx < stage_n) xs[idx] = xv[it] * nwv[it];
+  }
+  for (uint32_t idx = threadIdx.x + XS_PRE * GEMV_THREADS; idx < stage_n; idx += GEMV_THREADS) {
     const uint32_t kk = idx / MROWS, m = idx % MROWS;
     float v = 0.0f;
     if (m < p.m) {
@@ -165,6 +207,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     xs[idx] = v;
   }
   __syncthreads();
+  TA_TRACE(3)
   if (p.norm_w && rank == 0 && threadIdx.x < MROWS) {
     float s = 0.0f;
 #pragma unroll
@@ -221,6 +264,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   }
 
+  TA_TRACE(4)
   // ---- fixed-order reduction: lanes sharing a column group, then warps, then cluster ranks
 #pragma unroll
   for (int m = 0; m < MROWS; ++m)
@@ -248,6 +292,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     for (int w = 0; w < nw; ++w) s += wpart[((size_t)(mt * nw + w)) * MROWS * TN + rem];
     cdst[(size_t)rank * 2 * MROWS * TN + idx] = s;
   }
+  TA_TRACE(5)
   if (S > 1) {
     cluster.barrier_arrive();          // release: the pushed partials are visible to rank 0 after its wait
     if (rank != 0) return;
@@ -255,6 +300,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   } else {
     __syncthreads();
   }
+  TA_TRACE(6)
 
   // ---- rank 0: sum ranks in order, epilogue, store
   float *fin = wpart;   // reuse: final pre-store values [MROWS][TN]
@@ -282,20 +328,23 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   for (int idx = threadIdx.x; idx < MROWS * TN; idx += GEMV_THREADS) {
     const uint32_t m = idx / TN, c = col0 + idx % TN;
     if (m >= p.m || c >= p.n) continue;
+    const bool first = idx == (int)threadIdx.x && idx < GEMV_THREADS;   // operands prefetched above
     const size_t ci = (size_t)m * p.n + c;
     float v = fin[idx];
     if (dual && p.c2) p.c2[ci] = fin2[idx];
     if (p.store_kind == 0) {
-      if (p.accumulate) v += p.c[ci];
-      v = epi_apply(v, p.bias != nullptr, p.bias ? p.bias[c] : 0.0f, p.act, p.binary,
-                    p.d ? p.d[ci] : 0.0f, p.beta);
+      if (p.accumulate) v += first ? pre_c : p.c[ci];
+      const float bv = p.bias ? (first ? pre_bias : p.bias[c]) : 0.0f;
+      const float dv = p.d ? (first ? pre_d : p.d[ci]) : 0.0f;
+      v = epi_apply(v, p.bias != nullptr, bv, p.act, p.binary, dv, p.beta);
       p.c[ci] = v;
     } else {
       if (p.store_kind != 2) {   // rope with the partner column (c ^ 1)
         const float partner = fin[idx ^ 1];
         const uint32_t dim = c % p.head_dim;
-        const float *cs = p.table + ((size_t)pos * (p.head_dim / 2) + dim / 2) * 2;
-        v = (dim & 1u) == 0u ? fmaf(v, cs[0], -partner * cs[1]) : fmaf(partner, cs[1], v * cs[0]);
+        float2 cs = pre_cs;
+        if (!first) cs = *reinterpret_cast<const float2 *>(p.table + ((size_t)pos * (p.head_dim / 2) + dim / 2) * 2);
+        v = (dim & 1u) == 0u ? fmaf(v, cs.x, -partner * cs.y) : fmaf(partner, cs.y, v * cs.x);
       }
       if (p.store_kind == 1) {
         p.c[ci] = v;
@@ -307,6 +356,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       }
     }
   }
+  TA_TRACE(7)
 }
 
 size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s) {
@@ -391,15 +441,23 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   const uint32_t rpl = 32 / (tn / 8);
   const uint32_t nw = p0.w2 ? GEMV_WARPS / 2 : GEMV_WARPS;
   const uint32_t rows_per_pass = nw * rpl * u;
-  // K split over a cluster: aim at two CTAs and more per SM so that most of a small
-  // matrix is in flight at once; never split below one pass of rows.
+  // K split over a cluster: about one and a half CTAs per SM.  With four resident
+  // per SM that is one wave for this launch and leaves room for the early CTAs of
+  // the next launch, which prefetch their weights while this one finishes.  Never
+  // split below one pass of rows.
+  uint64_t weight_bytes = 0;
+  for (int i = 0; i < nseg; ++i) weight_bytes += (uint64_t)segs[i].k * segs[i].n * 2 * (segs[i].w2 ? 2 : 1);
   uint32_t best_s = 1;
   for (uint32_t s : {1u, 2u, 4u, 8u}) {
     if (s > 1 && p0.k / s < rows_per_pass) break;
     const uint32_t k_cta = (p0.k + s - 1) / s;
     if (gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 160 * 1024) continue;
     best_s = s;
-    if ((uint64_t)tiles * s >= 2ull * (uint64_t)sm_count) break;
+    // small matrices: 1.5 CTAs per SM; from 16 MB up the stream itself matters and more
+    // CTAs keep more of it in flight (up to 3.5 per SM, still one wave)
+    const uint64_t want2 = weight_bytes >= (16ull << 20) ? 7ull : 3ull;   // CTAs per SM, doubled
+    if ((uint64_t)tiles * s * 2 >= want2 * (uint64_t)sm_count) break;
+    if (s < 8 && (uint64_t)tiles * s * 2 * 2 > 8ull * (uint64_t)sm_count) break;   // the next split would not fit one wave
   }
   g.ksplit = best_s;
   g.k_cta = (p0.k + best_s - 1) / best_s;
@@ -417,6 +475,8 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   TA_GEMV_CASE(8)
 #undef TA_GEMV_CASE
 }
+
+TA_TRACE_EXPORT(ta_debug_gemv_trace)
 
 void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream) {
   launch_gemv_f16w_group(&p, 1, sm_count, true, stream);

@@ -526,6 +526,7 @@ static std::vector<ExecOp> checked_exec_ops(const ta_executor &e, const ta_exec_
     o.in0 = opt(r.in0, "in0"); o.in1 = opt(r.in1, "in1"); o.in2 = opt(r.in2, "in2"); o.in3 = opt(r.in3, "in3");
     o.out = opt(r.out, "out");
     o.f0 = r.f0; o.u0 = r.u0; o.u1 = r.u1; o.u2 = r.u2;
+    if (r.kind == TA_EXEC_ATTN_DECODE) o.u0 = 0;   // planner-internal hint, not caller input
     o.heads = r.rope.heads; o.head_dim = r.rope.head_dim; o.rot_dim = r.rope.rot_dim; o.pos_base = r.rope.pos_base;
     if (r.kind == TA_EXEC_COPY_STRIDED) {
       o.src_offset = r.copy.src_offset; o.dst_offset = r.copy.dst_offset;

@@ -314,6 +314,7 @@ struct AttnDecodeParams {
   const uint32_t *pos_ptr;
   uint32_t *counters;   // per-kv-head tickets (zero between launches), owned by the submitting slot
   uint32_t pdl;
+  uint32_t prefetch_kv; // 1: the launch before this one wrote at most position kv_len - 1 of the cache
 };
 
 struct FlashAttentionDesc {

@@ -322,10 +322,12 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
                                                   need(o.in2, "run_attn_decode", "v"), need(o.in3, "run_attn_decode", "scratch"),
                                                   need(o.out, "run_attn_decode", "out"), o.attn);
       if (n_calls) *n_calls += 1;   // two dispatches
-      return [p](Slot &slot, cudaStream_t st) {
+      const uint32_t prefetch = o.u0;   // internal hint from plan_exec_ops (the C ABI clears it)
+      return [p, prefetch](Slot &slot, cudaStream_t st) {
         AttnDecodeParams q = p;
         q.counters = slot.counters;
         q.pdl = 1;
+        q.prefetch_kv = prefetch;
         launch_attn_decode(q, st);
       };
     }
@@ -416,11 +418,31 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
   const int sms = ctx_->sm_count;
   std::vector<Launch> plan;
   plan.reserve(ops.size());
+  std::vector<GemvParams> prev_gemv;   // segments of the launch planned last, when it was a GEMV
   size_t i = 0;
   while (i < ops.size()) {
     Cand c0 = candidate(ops[i]);
     if (!c0.gemv) {
-      plan.push_back(plan_exec_op(ops[i], flops, n_calls));
+      ExecOp op = ops[i];
+      if (op.kind == ExecKind::AttnDecode) {
+        // Decode attention may read the cache ahead of its dependency wait when the launch
+        // before it (the only one that can still be running then) appends nothing but
+        // position kv_len - 1: a GEMV whose scatter stores use the same position cell.
+        bool ok = !prev_gemv.empty() && op.in1 && op.in2;
+        for (const GemvParams &e : prev_gemv) {
+          const void *kt = op.in1 ? op.in1->ptr() : nullptr, *v = op.in2 ? op.in2->ptr() : nullptr;
+          if (e.store_kind >= 2) {
+            const uint32_t *cell = op.attn.pos_cell ? op.attn.pos_cell->device : nullptr;
+            if (e.pos_ptr != cell || e.pos_base + 1 != op.attn.kv_len) ok = false;
+          } else if ((const void *)e.c == kt || (const void *)e.c == v) {
+            ok = false;
+          }
+          if ((const void *)e.c2 == kt || (const void *)e.c2 == v) ok = false;
+        }
+        op.u0 = ok ? 1u : 0u;
+      }
+      plan.push_back(plan_exec_op(op, flops, n_calls));
+      prev_gemv.clear();
       ++i;
       continue;
     }
@@ -441,6 +463,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         if (flops) *flops += c0.flops + c1.flops;
         if (n_calls) *n_calls += 2;
         plan.push_back([f, sms](Slot &, cudaStream_t st) { launch_gemv_f16w_group(&f, 1, sms, true, st); });
+        prev_gemv.assign(1, f);
         i += 2;
         continue;
       }
@@ -469,6 +492,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     plan.push_back([segs, sms](Slot &, cudaStream_t st) {
       launch_gemv_f16w_group(segs.data(), (int)segs.size(), sms, true, st);
     });
+    prev_gemv = segs;
     i = j;
   }
   return plan;
