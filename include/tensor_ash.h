@@ -381,12 +381,28 @@ int ta_token_ids_set(ta_token_ids *ids, const uint32_t *tokens, uint32_t n); /* 
  *   FLASH_ATTN        in0 q, in1 kt, in2 v, out; flash
  *   ARGMAX            in0 input; cell receives the index (ties keep the largest index)
  *   EMBED_GATHER      cell = token id word; in0 table [vocab, embd] (f32/f16), out [embd]
- *   EMBED_GATHER_ROWS tokens; in0 table, out [n, embd] */
+ *   EMBED_GATHER_ROWS tokens; in0 table, out [n, embd]
+ *   ALL_REDUCE        out = f32 tensor summed in place over the ranks of comm
+ *   ALL_GATHER        in0 [n] f32 of every rank -> out [world * n] in rank order; comm */
 enum {
   TA_EXEC_MATMUL = 0, TA_EXEC_RMS_NORM, TA_EXEC_LAYER_NORM, TA_EXEC_SOFTMAX_ROWS, TA_EXEC_ROPE,
   TA_EXEC_ROPE_SCATTER, TA_EXEC_COPY_STRIDED, TA_EXEC_BINARY, TA_EXEC_ATTN_DECODE, TA_EXEC_FLASH_ATTN,
-  TA_EXEC_ARGMAX, TA_EXEC_EMBED_GATHER, TA_EXEC_EMBED_GATHER_ROWS
+  TA_EXEC_ARGMAX, TA_EXEC_EMBED_GATHER, TA_EXEC_EMBED_GATHER_ROWS, TA_EXEC_ALL_REDUCE, TA_EXEC_ALL_GATHER
 };
+
+/* Communicator for tensor-parallel graphs: one rank per process and GPU, NCCL over
+ * NVLink underneath (bound at run time; creating a communicator fails with a
+ * message where NCCL is absent).  No counterpart in the reference, which is
+ * single-device.  Rank 0 makes an id with ta_comm_unique_id, every rank receives
+ * the same 128 bytes out of band (e.g. a torch.distributed broadcast) and calls
+ * ta_comm_create collectively.  world == 1 needs no id (NULL) and no NCCL. */
+typedef struct ta_comm ta_comm;
+#define TA_COMM_ID_BYTES 128
+int ta_comm_unique_id(uint8_t out[TA_COMM_ID_BYTES]);
+ta_comm *ta_comm_create(const ta_context *ctx, uint32_t rank, uint32_t world, const uint8_t *id);
+void ta_comm_destroy(ta_comm *comm);
+uint32_t ta_comm_rank(const ta_comm *comm);
+uint32_t ta_comm_world(const ta_comm *comm);
 
 typedef struct ta_exec_op {
   uint32_t kind;
@@ -401,6 +417,7 @@ typedef struct ta_exec_op {
   ta_attn_decode_desc attn;
   const ta_pos_cell *cell;
   const ta_token_ids *tokens;
+  const struct ta_comm *comm;      /* TA_EXEC_ALL_REDUCE (in place on `out`), TA_EXEC_ALL_GATHER (in0 -> out) */
 } ta_exec_op;
 
 int ta_run_exec_ops(const ta_executor *exec, const ta_exec_op *ops, size_t n_ops, ta_run_stats *stats);

@@ -43,6 +43,15 @@ typedef struct ta_llama_config {
  * [embd, vocab]; per layer L (base = 16 + 16*L): +0 attn_norm, +1 wq, +2 wk,
  * +3 wv, +4 wo, +5 ffn_norm, +6 w_gate, +7 w_up, +8 w_down (all [n_in, n_out]). */
 ta_llama *ta_llama_create_random(const ta_executor *exec, const ta_llama_config *cfg);
+
+/* Tensor-parallel shard of the same model on the rank of `comm` (NULL or world 1: the whole
+ * model).  Column-parallel wq / wk / wv (by head; a kv head is shared by neighbouring ranks
+ * when there are more ranks than kv heads), w_gate, w_up (by MLP column) and lm_head (by
+ * vocabulary column); row-parallel wo and w_down, whose partial sums are all-reduced (sum,
+ * f32) -- the one exchange step per projection.  Rank 0 folds the residual into its partial
+ * sum.  Every rank ends a step with the same logits and the same greedy token.  `comm`
+ * must outlive the model; all ranks must call prefill / decode in step. */
+ta_llama *ta_llama_create_random_tp(const ta_executor *exec, const ta_llama_config *cfg, const ta_comm *comm);
 void ta_llama_destroy(ta_llama *model);
 
 /* Forget the KV cache: the next prefill starts at position 0. */
@@ -63,7 +72,7 @@ int ta_llama_decode(ta_llama *model, uint32_t first_token, uint32_t n, uint32_t 
 /* Logits of the most recent step ([vocab] floats), for margin checks. */
 int ta_llama_logits(ta_llama *model, float *out, size_t len);
 
-/* Current position (tokens in the KV cache) and weight bytes read per decoded token. */
+/* Current position (tokens in the KV cache) and weight bytes this rank reads per decoded token. */
 uint32_t ta_llama_position(const ta_llama *model);
 uint64_t ta_llama_weight_bytes_per_token(const ta_llama *model);
 

@@ -11,6 +11,7 @@ import of :mod:`capi` raises, and every compute call needs a CUDA device.
 from .api import (  # noqa: F401
     Activation,
     Binary,
+    Comm,
     Context,
     DispatchInfo,
     Epilogue,
@@ -41,4 +42,4 @@ from .api import (  # noqa: F401
     version,
 )
 from .capi import lib, lib_path  # noqa: F401
-from .llama import Llama, LlamaConfig  # noqa: F401
+from .llama import Llama, LlamaConfig, shard_plan  # noqa: F401

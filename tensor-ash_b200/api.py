@@ -306,6 +306,61 @@ class TokenIdBuffer:
             pass
 
 
+class Comm:
+    """Communicator of a tensor-parallel group: one rank per process and GPU, NCCL underneath.
+
+    ``Comm.unique_id()`` on rank 0 makes the 128-byte id; every rank receives it out of band
+    (``from_torch_distributed`` broadcasts it over an initialised ``torch.distributed``
+    group) and constructs its ``Comm`` collectively.  ``world == 1`` needs neither id nor NCCL.
+    """
+
+    ID_BYTES = 128
+
+    def __init__(self, ctx: Context, rank: int, world: int, unique_id: Optional[bytes] = None):
+        buf = None
+        if world > 1:
+            if unique_id is None or len(unique_id) != self.ID_BYTES:
+                raise TensorAshError("Comm: a 128-byte unique id is required when world > 1")
+            buf = (C.c_uint8 * self.ID_BYTES).from_buffer_copy(unique_id)
+        h = lib().ta_comm_create(ctx._h, rank, world, buf)
+        if not h:
+            raise TensorAshError(_err())
+        self._h, self.ctx, self.rank, self.world = h, ctx, rank, world
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = (C.c_uint8 * Comm.ID_BYTES)()
+        _check(lib().ta_comm_unique_id(buf))
+        return bytes(buf)
+
+    @classmethod
+    def from_torch_distributed(cls, ctx: Context) -> "Comm":
+        """Collective over the default torch.distributed group (any backend)."""
+        import torch
+        import torch.distributed as dist
+
+        rank, world = dist.get_rank(), dist.get_world_size()
+        if world == 1:
+            return cls(ctx, 0, 1)
+        on_gpu = dist.get_backend() == "nccl"
+        t = torch.zeros(cls.ID_BYTES, dtype=torch.uint8, device="cuda" if on_gpu else "cpu")
+        if rank == 0:
+            t.copy_(torch.frombuffer(bytearray(cls.unique_id()), dtype=torch.uint8))
+        dist.broadcast(t, src=0)
+        return cls(ctx, rank, world, bytes(t.cpu().numpy().tobytes()))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().ta_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class ExecKind(enum.IntEnum):
     MATMUL = 0
     RMS_NORM = 1
@@ -320,6 +375,8 @@ class ExecKind(enum.IntEnum):
     ARGMAX = 10
     EMBED_GATHER = 11
     EMBED_GATHER_ROWS = 12
+    ALL_REDUCE = 13
+    ALL_GATHER = 14
 
 
 class ExecOp:
@@ -351,7 +408,7 @@ class ExecOp:
             kv_len, scale, cell = kw["attn"]
             self.c.attn = capi.AttnDecodeDescC(kv_len, scale, cell._h if cell is not None else None)
             self._keep.append(cell)
-        for name in ("cell", "tokens"):
+        for name in ("cell", "tokens", "comm"):
             obj = kw.get(name)
             if obj is not None:
                 setattr(self.c, name, obj._h)
@@ -419,6 +476,16 @@ class ExecOp:
     @classmethod
     def embed_gather_rows(cls, tokens, table, out):
         return cls(ExecKind.EMBED_GATHER_ROWS, tokens=tokens, in0=table, out=out)
+
+    @classmethod
+    def all_reduce(cls, tensor, comm):
+        """Sum `tensor` (f32) in place over the ranks of `comm`."""
+        return cls(ExecKind.ALL_REDUCE, out=tensor, comm=comm)
+
+    @classmethod
+    def all_gather(cls, src, dst, comm):
+        """dst [world * n] = every rank's src [n], in rank order."""
+        return cls(ExecKind.ALL_GATHER, in0=src, out=dst, comm=comm)
 
 
 def _exec_array(ops):

@@ -24,6 +24,7 @@ SOURCES = [
     "ta_runtime.cu",
     "ta_graph.cu",
     "ta_capi.cu",
+    "ta_comm.cu",
     "llama_ash.cu",
     "k_gemm_ffma.cu",
     "k_gemm_tf32x3.cu",
@@ -85,7 +86,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
         objs = list(pool.map(lambda s: _compile(s, verbose), SOURCES))
     if not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
         cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs,
-               "-Xlinker", "--exclude-libs,ALL"]
+               "-Xlinker", "--exclude-libs,ALL", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

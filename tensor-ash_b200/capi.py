@@ -76,7 +76,7 @@ class ExecOpC(C.Structure):
                 ("out", C.c_void_p), ("f0", C.c_float), ("u0", C.c_uint32), ("u1", C.c_uint32),
                 ("u2", C.c_uint32), ("rope", RopeDescC), ("copy", CopyDescC), ("dst_offset", C.c_uint32),
                 ("dst_strides", C.c_uint32 * 3), ("pos_scale", C.c_uint32), ("flash", FlashDescC),
-                ("attn", AttnDecodeDescC), ("cell", C.c_void_p), ("tokens", C.c_void_p)]
+                ("attn", AttnDecodeDescC), ("cell", C.c_void_p), ("tokens", C.c_void_p), ("comm", C.c_void_p)]
 
 
 class LlamaConfigC(C.Structure):
@@ -161,8 +161,14 @@ SIGNATURES = {
     "ta_tensor_device_ptr": (_P, [_P]),
     "ta_context_device_index": (C.c_int, [_P]),
     "ta_kernel_launch_count": (C.c_uint64, []),
+    "ta_comm_unique_id": (C.c_int, [_P]),
+    "ta_comm_create": (_P, [_P, _U32, _U32, _P]),
+    "ta_comm_destroy": (None, [_P]),
+    "ta_comm_rank": (_U32, [_P]),
+    "ta_comm_world": (_U32, [_P]),
     # ---- tensor_ash_llama.h
     "ta_llama_create_random": (_P, [_P, C.POINTER(LlamaConfigC)]),
+    "ta_llama_create_random_tp": (_P, [_P, C.POINTER(LlamaConfigC), _P]),
     "ta_llama_destroy": (None, [_P]),
     "ta_llama_reset": (C.c_int, [_P]),
     "ta_llama_prefill": (C.c_int, [_P, C.POINTER(_U32), _U32, C.POINTER(_U32), _STATS]),

@@ -86,6 +86,17 @@ std::vector<uint16_t> pack_bits(const std::vector<uint16_t> &src, size_t k, size
   return out;
 }
 
+// columns [c0, c0 + w) of a row-major [rows, cols] matrix
+std::vector<uint16_t> slice_cols(const std::vector<uint16_t> &src, size_t rows, size_t cols, size_t c0, size_t w) {
+  std::vector<uint16_t> out(rows * w);
+  for (size_t r = 0; r < rows; ++r) memcpy(&out[r * w], &src[r * cols + c0], w * 2);
+  return out;
+}
+// rows [r0, r0 + h) of a row-major [rows, cols] matrix
+std::vector<uint16_t> slice_rows(const std::vector<uint16_t> &src, size_t cols, size_t r0, size_t h) {
+  return std::vector<uint16_t>(src.begin() + r0 * cols, src.begin() + (r0 + h) * cols);
+}
+
 struct Layer {
   Tensor attn_norm, ffn_norm;
   Tensor wq_p, wk_p, wv_p, w_qkv, wo, w_gate, w_up, w_gate_p, w_up_p, w_down;
@@ -102,10 +113,14 @@ struct ta_llama {
   std::shared_ptr<Context> ctx;
   Executor *exec = nullptr;
   ta_llama_config cfg{};
+  // tensor-parallel shard of this rank (world 1: the whole model)
+  const Comm *comm = nullptr;
+  uint32_t rank = 0, world = 1;
+  uint32_t heads_l = 0, kv_l = 0, kv_first = 0, q_w = 0, kv_w = 0, ffn_l = 0, vocab_l = 0;
   std::vector<Layer> layers;
   Tensor embd, output_norm, lm_head, lm_head_p, rope_table;
   // decode scratch (t = 1)
-  Tensor x_a, x_b, q, k, v, attn, o, up, gate, logits, attn_partials;
+  Tensor x_a, x_b, q, k, v, attn, o, up, gate, logits, logits_l, attn_partials;
   PosCell pos_cell, token_cell;
   TokenIds token_ids;
   std::unique_ptr<PreparedOps> decode_graph;
@@ -166,20 +181,39 @@ void build_model(ta_llama &m) {
   if (c.heads * c.head_dim != c.embd) fail("ta_llama_create_random: heads * head_dim must equal embd");
   if (c.heads % c.kv_heads || c.heads / c.kv_heads > 8) fail("ta_llama_create_random: GQA group must be 1..8");
   if (c.head_dim != 64) fail("ta_llama_create_random: head_dim must be 64 (decode attention variant)");
-  const uint32_t kv_dim = c.kv_heads * c.head_dim, n_qkv = c.embd + 2 * kv_dim;
-  for (uint32_t n : {c.embd, kv_dim, c.ffn, c.vocab})
+  const uint32_t kv_dim = c.kv_heads * c.head_dim;
+  // Tensor-parallel shard (world 1 keeps everything): query heads and the MLP width split
+  // evenly; kv heads split, or are shared by W / kv_heads neighbouring ranks when there are
+  // more ranks than kv heads; the lm_head splits by vocabulary columns.  Column-parallel:
+  // wq, wk, wv, w_gate, w_up, lm_head.  Row-parallel (partial sums, all-reduced): wo, w_down.
+  const uint32_t W = m.world, R = m.rank;
+  if (c.heads % W) fail("ta_llama_create: %u heads do not split over %u ranks", c.heads, W);
+  if (c.kv_heads % W && W % c.kv_heads) fail("ta_llama_create: %u kv heads do not map onto %u ranks", c.kv_heads, W);
+  if (c.ffn % W || c.vocab % W) fail("ta_llama_create: ffn %u / vocab %u do not split over %u ranks", c.ffn, c.vocab, W);
+  m.heads_l = c.heads / W;
+  m.kv_l = c.kv_heads >= W ? c.kv_heads / W : 1;
+  m.kv_first = (uint32_t)(((uint64_t)R * c.kv_heads) / W);
+  m.q_w = m.heads_l * c.head_dim;
+  m.kv_w = m.kv_l * c.head_dim;
+  m.ffn_l = c.ffn / W;
+  m.vocab_l = c.vocab / W;
+  if (m.heads_l % m.kv_l || m.heads_l / m.kv_l > 8) fail("ta_llama_create: local GQA group must be 1..8");
+  const uint32_t n_qkv = m.q_w + 2 * m.kv_w;
+  for (uint32_t n : {c.embd, kv_dim, c.ffn, c.vocab, m.q_w, m.kv_w, m.ffn_l, m.vocab_l})
     if (n % 32) fail("ta_llama_create_random: projection widths must be multiples of 32 (got %u)", n);
   const double sigma = c.weight_sigma;
   const uint64_t seed = c.seed;
   auto tile = [](uint32_t k, uint32_t n) { return f16w_row_tile_n(k, n); };
+  const size_t q0 = (size_t)R * m.q_w, kv0 = (size_t)m.kv_first * c.head_dim, f0 = (size_t)R * m.ffn_l,
+               v0 = (size_t)R * m.vocab_l;
 
-  {  // token embedding [vocab, embd], final norm, lm_head [embd, vocab]
+  {  // token embedding [vocab, embd] (replicated), final norm, lm_head columns [embd, vocab_l]
     auto e = gen_weight_f16(seed, 0, (size_t)c.vocab * c.embd, sigma);
     m.embd = upload_bits(m, e, c.vocab, c.embd);
     m.output_norm = norm_weight(m, 1);
-    auto h = gen_weight_f16(seed, 2, (size_t)c.embd * c.vocab, sigma);
-    m.lm_head = upload_bits(m, h, c.embd, c.vocab);
-    m.lm_head_p = upload_bits(m, pack_bits(h, c.embd, c.vocab, tile(c.embd, c.vocab)), c.embd, c.vocab);
+    auto h = slice_cols(gen_weight_f16(seed, 2, (size_t)c.embd * c.vocab, sigma), c.embd, c.vocab, v0, m.vocab_l);
+    m.lm_head = upload_bits(m, h, c.embd, m.vocab_l);
+    m.lm_head_p = upload_bits(m, pack_bits(h, c.embd, m.vocab_l, tile(c.embd, m.vocab_l)), c.embd, m.vocab_l);
   }
   m.layers.resize(c.layers);
   for (uint32_t li = 0; li < c.layers; ++li) {
@@ -187,31 +221,33 @@ void build_model(ta_llama &m) {
     const uint32_t base = 16 + 16 * li;
     L.attn_norm = norm_weight(m, base + 0);
     L.ffn_norm = norm_weight(m, base + 5);
-    auto wq = gen_weight_f16(seed, base + 1, (size_t)c.embd * c.embd, sigma);
-    auto wk = gen_weight_f16(seed, base + 2, (size_t)c.embd * kv_dim, sigma);
-    auto wv = gen_weight_f16(seed, base + 3, (size_t)c.embd * kv_dim, sigma);
-    L.wq_p = upload_bits(m, pack_bits(wq, c.embd, c.embd, tile(c.embd, c.embd)), c.embd, c.embd);
-    L.wk_p = upload_bits(m, pack_bits(wk, c.embd, kv_dim, tile(c.embd, kv_dim)), c.embd, kv_dim);
-    L.wv_p = upload_bits(m, pack_bits(wv, c.embd, kv_dim, tile(c.embd, kv_dim)), c.embd, kv_dim);
-    {  // concatenated [embd, embd + 2 kv_dim] for the prefill GEMM
+    auto wq = slice_cols(gen_weight_f16(seed, base + 1, (size_t)c.embd * c.embd, sigma), c.embd, c.embd, q0, m.q_w);
+    auto wk = slice_cols(gen_weight_f16(seed, base + 2, (size_t)c.embd * kv_dim, sigma), c.embd, kv_dim, kv0, m.kv_w);
+    auto wv = slice_cols(gen_weight_f16(seed, base + 3, (size_t)c.embd * kv_dim, sigma), c.embd, kv_dim, kv0, m.kv_w);
+    L.wq_p = upload_bits(m, pack_bits(wq, c.embd, m.q_w, tile(c.embd, m.q_w)), c.embd, m.q_w);
+    L.wk_p = upload_bits(m, pack_bits(wk, c.embd, m.kv_w, tile(c.embd, m.kv_w)), c.embd, m.kv_w);
+    L.wv_p = upload_bits(m, pack_bits(wv, c.embd, m.kv_w, tile(c.embd, m.kv_w)), c.embd, m.kv_w);
+    {  // concatenated [embd, q_w + 2 kv_w] for the prefill GEMM
       std::vector<uint16_t> cat((size_t)c.embd * n_qkv);
       for (uint32_t r = 0; r < c.embd; ++r) {
-        memcpy(&cat[(size_t)r * n_qkv], &wq[(size_t)r * c.embd], (size_t)c.embd * 2);
-        memcpy(&cat[(size_t)r * n_qkv + c.embd], &wk[(size_t)r * kv_dim], (size_t)kv_dim * 2);
-        memcpy(&cat[(size_t)r * n_qkv + c.embd + kv_dim], &wv[(size_t)r * kv_dim], (size_t)kv_dim * 2);
+        memcpy(&cat[(size_t)r * n_qkv], &wq[(size_t)r * m.q_w], (size_t)m.q_w * 2);
+        memcpy(&cat[(size_t)r * n_qkv + m.q_w], &wk[(size_t)r * m.kv_w], (size_t)m.kv_w * 2);
+        memcpy(&cat[(size_t)r * n_qkv + m.q_w + m.kv_w], &wv[(size_t)r * m.kv_w], (size_t)m.kv_w * 2);
       }
       L.w_qkv = upload_bits(m, cat, c.embd, n_qkv);
     }
-    L.wo = upload_bits(m, gen_weight_f16(seed, base + 4, (size_t)c.embd * c.embd, sigma), c.embd, c.embd);
-    auto wg = gen_weight_f16(seed, base + 6, (size_t)c.embd * c.ffn, sigma);
-    auto wu = gen_weight_f16(seed, base + 7, (size_t)c.embd * c.ffn, sigma);
-    L.w_gate = upload_bits(m, wg, c.embd, c.ffn);
-    L.w_up = upload_bits(m, wu, c.embd, c.ffn);
-    L.w_gate_p = upload_bits(m, pack_bits(wg, c.embd, c.ffn, tile(c.embd, c.ffn)), c.embd, c.ffn);
-    L.w_up_p = upload_bits(m, pack_bits(wu, c.embd, c.ffn, tile(c.embd, c.ffn)), c.embd, c.ffn);
-    L.w_down = upload_bits(m, gen_weight_f16(seed, base + 8, (size_t)c.ffn * c.embd, sigma), c.ffn, c.embd);
-    L.kt_cache = make(m.ctx, {c.kv_heads, c.head_dim, c.t_max}, DType::F16);
-    L.v_cache = make(m.ctx, {c.kv_heads, c.t_max, c.head_dim}, DType::F16);
+    L.wo = upload_bits(m, slice_rows(gen_weight_f16(seed, base + 4, (size_t)c.embd * c.embd, sigma), c.embd, q0, m.q_w),
+                       m.q_w, c.embd);
+    auto wg = slice_cols(gen_weight_f16(seed, base + 6, (size_t)c.embd * c.ffn, sigma), c.embd, c.ffn, f0, m.ffn_l);
+    auto wu = slice_cols(gen_weight_f16(seed, base + 7, (size_t)c.embd * c.ffn, sigma), c.embd, c.ffn, f0, m.ffn_l);
+    L.w_gate = upload_bits(m, wg, c.embd, m.ffn_l);
+    L.w_up = upload_bits(m, wu, c.embd, m.ffn_l);
+    L.w_gate_p = upload_bits(m, pack_bits(wg, c.embd, m.ffn_l, tile(c.embd, m.ffn_l)), c.embd, m.ffn_l);
+    L.w_up_p = upload_bits(m, pack_bits(wu, c.embd, m.ffn_l, tile(c.embd, m.ffn_l)), c.embd, m.ffn_l);
+    L.w_down = upload_bits(m, slice_rows(gen_weight_f16(seed, base + 8, (size_t)c.ffn * c.embd, sigma), c.embd, f0, m.ffn_l),
+                           m.ffn_l, c.embd);
+    L.kt_cache = make(m.ctx, {m.kv_l, c.head_dim, c.t_max}, DType::F16);
+    L.v_cache = make(m.ctx, {m.kv_l, c.t_max, c.head_dim}, DType::F16);
     TA_CUDA(cudaMemset(L.kt_cache.ptr(), 0, L.kt_cache.size_bytes()));
     TA_CUDA(cudaMemset(L.v_cache.ptr(), 0, L.v_cache.size_bytes()));
   }
@@ -230,15 +266,16 @@ void build_model(ta_llama &m) {
   // decode scratch
   m.x_a = make(m.ctx, {1, c.embd}, DType::F32);
   m.x_b = make(m.ctx, {1, c.embd}, DType::F32);
-  m.q = make(m.ctx, {1, c.embd}, DType::F32);
-  m.k = make(m.ctx, {1, kv_dim}, DType::F32);
-  m.v = make(m.ctx, {1, kv_dim}, DType::F32);
-  m.attn = make(m.ctx, {1, c.embd}, DType::F32);
+  m.q = make(m.ctx, {1, m.q_w}, DType::F32);
+  m.k = make(m.ctx, {1, m.kv_w}, DType::F32);
+  m.v = make(m.ctx, {1, m.kv_w}, DType::F32);
+  m.attn = make(m.ctx, {1, m.q_w}, DType::F32);
   m.o = make(m.ctx, {1, c.embd}, DType::F32);
-  m.up = make(m.ctx, {1, c.ffn}, DType::F32);
-  m.gate = make(m.ctx, {1, c.ffn}, DType::F32);
+  m.up = make(m.ctx, {1, m.ffn_l}, DType::F32);
+  m.gate = make(m.ctx, {1, m.ffn_l}, DType::F32);
   m.logits = make(m.ctx, {1, c.vocab}, DType::F32);
-  m.attn_partials = make(m.ctx, {c.kv_heads * ATTN_DECODE_MAX_CHUNKS * (c.heads / c.kv_heads) * (c.head_dim + 2)}, DType::F32);
+  m.logits_l = make(m.ctx, {1, m.vocab_l}, DType::F32);
+  m.attn_partials = make(m.ctx, {m.kv_l * ATTN_DECODE_MAX_CHUNKS * (m.heads_l / m.kv_l) * (c.head_dim + 2)}, DType::F32);
   make_pinned_cell(m.ctx, m.pos_cell);
   make_pinned_cell(m.ctx, m.token_cell);
   m.token_ids.ctx = m.ctx;
@@ -256,15 +293,30 @@ ExecOp mm_op(const Tensor &a, const Tensor &b, const Tensor &c) {
 
 // forward/mod.rs:134-227 push_mlp_ops; residual adds and the SiLU gate ride the
 // GEMM epilogues at every width (every kernel family here fuses them).
+ExecOp all_reduce_op(ta_llama &m, const Tensor &t) {
+  ExecOp o;
+  o.kind = ExecKind::AllReduce;
+  o.out = &t;
+  o.comm = m.comm;
+  return o;
+}
+
 void push_mlp_ops(ta_llama &m, std::vector<ExecOp> &ops, Layer &L, bool decode, const Tensor &attn_flat,
                   const Tensor &o, const Tensor &on, const Tensor &up, const Tensor &gate, const Tensor &x_in,
                   const Tensor &x_out) {
   const float eps = m.cfg.rms_eps;
+  const bool tp = m.world > 1;
+  // Row-parallel projections produce partial sums: rank 0 alone folds the residual in,
+  // so the all-reduced sum holds it exactly once.
+  const bool add_residual = m.rank == 0;
   ExecOp op = mm_op(attn_flat, L.wo, o);
-  op.mm.epilogue.binary = BinaryKind::AddScaled;
-  op.mm.epilogue.d = &x_in;
-  op.mm.epilogue.beta = 1.0f;
+  if (add_residual) {
+    op.mm.epilogue.binary = BinaryKind::AddScaled;
+    op.mm.epilogue.d = &x_in;
+    op.mm.epilogue.beta = 1.0f;
+  }
   ops.push_back(op);
+  if (tp) ops.push_back(all_reduce_op(m, o));
   if (decode) {
     ExecOp u = mm_op(o, L.w_up_p, up);
     u.mm.packed_b = true; u.mm.normed_weight = &L.ffn_norm; u.mm.normed_eps = eps;
@@ -288,10 +340,33 @@ void push_mlp_ops(ta_llama &m, std::vector<ExecOp> &ops, Layer &L, bool decode, 
     ops.push_back(g);
   }
   ExecOp d = mm_op(gate, L.w_down, x_out);
-  d.mm.epilogue.binary = BinaryKind::AddScaled;
-  d.mm.epilogue.d = &o;
-  d.mm.epilogue.beta = 1.0f;
+  if (add_residual) {
+    d.mm.epilogue.binary = BinaryKind::AddScaled;
+    d.mm.epilogue.d = &o;
+    d.mm.epilogue.beta = 1.0f;
+  }
   ops.push_back(d);
+  if (tp) ops.push_back(all_reduce_op(m, x_out));
+}
+
+// lm_head on one normed row; sharded ranks gather their logit slices (rank order =
+// vocabulary order) so that every rank takes the same argmax over the whole vocabulary.
+void push_head_ops(ta_llama &m, std::vector<ExecOp> &ops, ExecOp head) {
+  if (m.world == 1) {
+    head.mm.call.c = &m.logits;
+    ops.push_back(head);
+  } else {
+    head.mm.call.c = &m.logits_l;
+    ops.push_back(head);
+    ExecOp ag;
+    ag.kind = ExecKind::AllGather;
+    ag.in0 = &m.logits_l; ag.out = &m.logits; ag.comm = m.comm;
+    ops.push_back(ag);
+  }
+  ExecOp am;
+  am.kind = ExecKind::Argmax;
+  am.in0 = &m.logits; am.cell = &m.token_cell;
+  ops.push_back(am);
 }
 
 // forward/decode.rs:172-246 decode_ops + forward/mod.rs:316-328 decode_close_ops,
@@ -330,11 +405,7 @@ std::vector<ExecOp> decode_ops(ta_llama &m) {
   }
   ExecOp head = mm_op(*x_in, m.lm_head_p, m.logits);
   head.mm.packed_b = true; head.mm.normed_weight = &m.output_norm; head.mm.normed_eps = eps;
-  ops.push_back(head);
-  ExecOp am;
-  am.kind = ExecKind::Argmax;
-  am.in0 = &m.logits; am.cell = &m.token_cell;
-  ops.push_back(am);
+  push_head_ops(m, ops, head);
   ExecOp eg;
   eg.kind = ExecKind::EmbedGather;
   eg.cell = &m.token_cell; eg.in0 = &m.embd; eg.out = &m.x_a;
@@ -368,8 +439,8 @@ ExecOp copy_op(const Tensor &src, const Tensor &dst, std::array<uint32_t, 3> ext
 // forward/prefill.rs:89-291 (f32 activations, composed QKV split, fused flash).
 std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint32_t pos_base) {
   const ta_llama_config &c = m.cfg;
-  const uint32_t heads = c.heads, kv = c.kv_heads, dh = c.head_dim, t_max = c.t_max, embd = c.embd;
-  const uint32_t kv_dim = kv * dh, n_qkv = embd + 2 * kv_dim;
+  const uint32_t heads = m.heads_l, kv = m.kv_l, dh = c.head_dim, t_max = c.t_max, embd = c.embd;
+  const uint32_t q_w = m.q_w, kv_dim = kv * dh, n_qkv = q_w + 2 * kv_dim;
   std::vector<ExecOp> ops;
   {
     ExecOp g;
@@ -384,9 +455,9 @@ std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint
     n.in0 = x_in; n.in1 = &L.attn_norm; n.out = &s.xn; n.f0 = c.rms_eps;
     ops.push_back(n);
     ops.push_back(mm_op(s.xn, L.w_qkv, s.qkv));
-    ops.push_back(copy_op(s.qkv, s.q, {embd, t, 1}, 0, {1, n_qkv, 0}, 0, {1, embd, 0}));
-    ops.push_back(copy_op(s.qkv, s.k, {kv_dim, t, 1}, embd, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
-    ops.push_back(copy_op(s.qkv, s.v, {kv_dim, t, 1}, embd + kv_dim, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
+    ops.push_back(copy_op(s.qkv, s.q, {q_w, t, 1}, 0, {1, n_qkv, 0}, 0, {1, q_w, 0}));
+    ops.push_back(copy_op(s.qkv, s.k, {kv_dim, t, 1}, q_w, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
+    ops.push_back(copy_op(s.qkv, s.v, {kv_dim, t, 1}, q_w + kv_dim, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
     for (int which = 0; which < 2; ++which) {
       ExecOp r;
       r.kind = ExecKind::Rope;
@@ -411,25 +482,21 @@ std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint
   n.kind = ExecKind::RmsNorm;
   n.in0 = &s.last; n.in1 = &m.output_norm; n.out = &s.last_n; n.f0 = c.rms_eps;
   ops.push_back(n);
-  ops.push_back(mm_op(s.last_n, m.lm_head, m.logits));
-  ExecOp am;
-  am.kind = ExecKind::Argmax;
-  am.in0 = &m.logits; am.cell = &m.token_cell;
-  ops.push_back(am);
+  push_head_ops(m, ops, mm_op(s.last_n, m.lm_head, m.logits));
   return ops;
 }
 
 PrefillScratch prefill_view(ta_llama &m, uint32_t n) {
   const ta_llama_config &c = m.cfg;
-  const uint32_t kv_dim = c.kv_heads * c.head_dim;
+  const uint32_t kv_dim = m.kv_w;
   PrefillScratch &full = *m.prefill_full;
   if (full.x_a.shape.empty()) {
     auto f32 = [&](uint32_t cols) { return make(m.ctx, {c.t_max, cols}, DType::F32); };
     full.x_a = f32(c.embd); full.x_b = f32(c.embd); full.xn = f32(c.embd);
-    full.qkv = f32(c.embd + 2 * kv_dim);
-    full.q = f32(c.embd); full.k = f32(kv_dim); full.v = f32(kv_dim);
-    full.attn_flat = f32(c.embd); full.o = f32(c.embd); full.on = f32(c.embd);
-    full.up = f32(c.ffn); full.gate = f32(c.ffn);
+    full.qkv = f32(m.q_w + 2 * kv_dim);
+    full.q = f32(m.q_w); full.k = f32(kv_dim); full.v = f32(kv_dim);
+    full.attn_flat = f32(m.q_w); full.o = f32(c.embd); full.on = f32(c.embd);
+    full.up = f32(m.ffn_l); full.gate = f32(m.ffn_l);
     full.last = make(m.ctx, {1, c.embd}, DType::F32);
     full.last_n = make(m.ctx, {1, c.embd}, DType::F32);
   }
@@ -442,10 +509,10 @@ PrefillScratch prefill_view(ta_llama &m, uint32_t n) {
   };
   PrefillScratch s;
   s.x_a = rows(full.x_a, c.embd); s.x_b = rows(full.x_b, c.embd); s.xn = rows(full.xn, c.embd);
-  s.qkv = rows(full.qkv, c.embd + 2 * kv_dim);
-  s.q = rows(full.q, c.embd); s.k = rows(full.k, kv_dim); s.v = rows(full.v, kv_dim);
-  s.attn_flat = rows(full.attn_flat, c.embd); s.o = rows(full.o, c.embd); s.on = rows(full.on, c.embd);
-  s.up = rows(full.up, c.ffn); s.gate = rows(full.gate, c.ffn);
+  s.qkv = rows(full.qkv, m.q_w + 2 * kv_dim);
+  s.q = rows(full.q, m.q_w); s.k = rows(full.k, kv_dim); s.v = rows(full.v, kv_dim);
+  s.attn_flat = rows(full.attn_flat, m.q_w); s.o = rows(full.o, c.embd); s.on = rows(full.on, c.embd);
+  s.up = rows(full.up, m.ffn_l); s.gate = rows(full.gate, m.ffn_l);
   s.last = full.last; s.last_n = full.last_n;
   return s;
 }
@@ -479,12 +546,22 @@ void write_stats(ta_run_stats *out, const RunStats &st) {
 extern "C" {
 
 ta_llama *ta_llama_create_random(const ta_executor *exec, const ta_llama_config *cfg) {
+  return ta_llama_create_random_tp(exec, cfg, nullptr);
+}
+
+ta_llama *ta_llama_create_random_tp(const ta_executor *exec, const ta_llama_config *cfg, const ta_comm *comm) {
   ta_llama *m = nullptr;
   const int rc = guarded([&]() {
     if (!exec) fail("ta_llama_create_random: exec is null");
     if (!cfg) fail("ta_llama_create_random: cfg is null");
     m = new ta_llama;
     m->prefill_full.reset(new PrefillScratch);
+    if (comm) {
+      if (comm->comm->ctx.get() != exec->ctx.get()) fail("ta_llama_create_random_tp: comm belongs to a different context");
+      m->comm = comm->comm.get();
+      m->rank = comm->comm->rank;
+      m->world = comm->comm->world;
+    }
     m->ctx = exec->ctx;
     m->exec = exec->exec.get();
     m->cfg = *cfg;
@@ -577,9 +654,8 @@ uint32_t ta_llama_position(const ta_llama *model) { return model ? model->pos : 
 uint64_t ta_llama_weight_bytes_per_token(const ta_llama *model) {
   if (!model) return 0;
   const ta_llama_config &c = model->cfg;
-  const uint64_t kv_dim = (uint64_t)c.kv_heads * c.head_dim;
-  const uint64_t per_layer = 2ull * c.embd * c.embd + 2ull * c.embd * kv_dim + 3ull * c.embd * c.ffn;
-  return 2ull * (c.layers * per_layer + (uint64_t)c.embd * c.vocab);
+  const uint64_t per_layer = 2ull * c.embd * model->q_w + 2ull * c.embd * model->kv_w + 3ull * c.embd * model->ffn_l;
+  return 2ull * (c.layers * per_layer + (uint64_t)c.embd * model->vocab_l);
 }
 
 }  // extern "C"

@@ -517,7 +517,7 @@ static std::vector<ExecOp> checked_exec_ops(const ta_executor &e, const ta_exec_
     const ta_exec_op &r = ops[i];
     const std::string label = strf("%s: op %zu", operation, i);
     ExecOp &o = v[i];
-    if (r.kind > TA_EXEC_EMBED_GATHER_ROWS) fail("%s: kind %u is invalid", label.c_str(), r.kind);
+    if (r.kind > TA_EXEC_ALL_GATHER) fail("%s: kind %u is invalid", label.c_str(), r.kind);
     o.kind = (ExecKind)r.kind;
     if (r.kind == TA_EXEC_MATMUL) o.mm = checked_op_ex(e, r.mm, label);
     auto opt = [&](const ta_tensor *t, const char *name) -> const Tensor * {
@@ -547,6 +547,7 @@ static std::vector<ExecOp> checked_exec_ops(const ta_executor &e, const ta_exec_
     o.attn.pos_cell = r.attn.pos_cell ? &r.attn.pos_cell->cell : nullptr;
     o.cell = r.cell ? &r.cell->cell : nullptr;
     o.tokens = r.tokens ? &r.tokens->ids : nullptr;
+    o.comm = r.comm ? r.comm->comm.get() : nullptr;
   }
   return v;
 }
@@ -573,6 +574,34 @@ ta_prepared *ta_prepared_create_exec(const ta_executor *exec, const ta_exec_op *
     return h;
   });
 }
+
+int ta_comm_unique_id(uint8_t out[TA_COMM_ID_BYTES]) {
+  return status_call([&]() {
+    if (!out) fail("ta_comm_unique_id: out is null");
+    comm_unique_id(out);
+  });
+}
+ta_comm *ta_comm_create(const ta_context *ctx, uint32_t rank, uint32_t world, const uint8_t *id) {
+  return create_call<ta_comm>([&]() {
+    const ta_context &c = checked_ref(ctx, "ta_comm_create: ctx is null");
+    if (world > 1 && !id) fail("ta_comm_create: id is null");
+    uint8_t zero[TA_COMM_ID_BYTES] = {0};
+    auto *h = new ta_comm;
+    try {
+      h->comm = Comm::create(c.ctx, rank, world, id ? id : zero);
+    } catch (...) {
+      delete h;
+      throw;
+    }
+    return h;
+  });
+}
+void ta_comm_destroy(ta_comm *comm) {
+  g_last_error.clear();
+  delete comm;
+}
+uint32_t ta_comm_rank(const ta_comm *comm) { return comm ? comm->comm->rank : 0; }
+uint32_t ta_comm_world(const ta_comm *comm) { return comm ? comm->comm->world : 0; }
 
 ta_token_ids *ta_token_ids_create(const ta_context *ctx, uint32_t capacity) {
   return create_call<ta_token_ids>([&]() {

@@ -355,7 +355,21 @@ struct TokenIds {
 //   EmbedGatherRows  tokens; in0 table, out [n, embd]
 enum class ExecKind : uint32_t {
   Matmul = 0, RmsNorm, LayerNorm, SoftmaxRows, Rope, RopeScatter, CopyStrided, Binary, AttnDecode,
-  FlashAttn, Argmax, EmbedGather, EmbedGatherRows
+  FlashAttn, Argmax, EmbedGather, EmbedGatherRows, AllReduce, AllGather
+};
+
+// ------------------------------------------------------------------ communicator (tensor parallel)
+constexpr size_t COMM_ID_BYTES = 128;
+void comm_unique_id(uint8_t out[COMM_ID_BYTES]);
+struct Comm {
+  std::shared_ptr<Context> ctx;
+  uint32_t rank = 0, world = 1;
+  void *handle = nullptr;   // ncclComm_t; null when world == 1
+  static std::unique_ptr<Comm> create(const std::shared_ptr<Context> &ctx, uint32_t rank, uint32_t world,
+                                      const uint8_t id[COMM_ID_BYTES]);
+  ~Comm();
+  void all_reduce_sum(float *data, size_t count, cudaStream_t stream) const;   // in place
+  void all_gather(const float *src, float *dst, size_t count_per_rank, cudaStream_t stream) const;
 };
 
 struct ExecOp {
@@ -371,6 +385,7 @@ struct ExecOp {
   AttnDecodeDesc attn;
   const PosCell *cell = nullptr;
   const TokenIds *tokens = nullptr;
+  const Comm *comm = nullptr;   // AllReduce (in place on `out`) / AllGather (in0 -> out)
 };
 
 struct Slot;

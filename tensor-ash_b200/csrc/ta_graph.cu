@@ -321,7 +321,6 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       const AttnDecodeParams p = plan_attn_decode(need(o.in0, "run_attn_decode", "q"), need(o.in1, "run_attn_decode", "kt"),
                                                   need(o.in2, "run_attn_decode", "v"), need(o.in3, "run_attn_decode", "scratch"),
                                                   need(o.out, "run_attn_decode", "out"), o.attn);
-      if (n_calls) *n_calls += 1;   // two dispatches
       const uint32_t prefetch = o.u0;   // internal hint from plan_exec_ops (the C ABI clears it)
       return [p, prefetch](Slot &slot, cudaStream_t st) {
         AttnDecodeParams q = p;
@@ -376,6 +375,31 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       const bool tf16 = table.dtype == DType::F16;
       float *op = (float *)out.ptr();
       return [=](Slot &, cudaStream_t st) { launch_embed_gather(tp, n_tokens, tab, tf16, op, embd, vocab, st); };
+    }
+    case ExecKind::AllReduce: {
+      const Tensor &t = need(o.out, "run_all_reduce", "tensor");
+      ensure_f32(*this, t, "run_all_reduce", "tensor");
+      if (!o.comm) fail("run_all_reduce: communicator is null");
+      if (o.comm->ctx.get() != ctx_.get()) fail("run_all_reduce: communicator belongs to a different context");
+      const Comm *comm = o.comm;
+      float *ptr = (float *)t.ptr();
+      const size_t count = (size_t)t.len();
+      return [=](Slot &, cudaStream_t st) { comm->all_reduce_sum(ptr, count, st); };
+    }
+    case ExecKind::AllGather: {
+      const Tensor &src = need(o.in0, "run_all_gather", "src"), &dst = need(o.out, "run_all_gather", "dst");
+      ensure_f32(*this, src, "run_all_gather", "src");
+      ensure_f32(*this, dst, "run_all_gather", "dst");
+      if (!o.comm) fail("run_all_gather: communicator is null");
+      if (o.comm->ctx.get() != ctx_.get()) fail("run_all_gather: communicator belongs to a different context");
+      if (dst.len() != src.len() * o.comm->world)
+        fail("run_all_gather: dst length %llu != src length %llu * world %u", (unsigned long long)dst.len(),
+             (unsigned long long)src.len(), o.comm->world);
+      const Comm *comm = o.comm;
+      const float *sp = (const float *)src.ptr();
+      float *dp = (float *)dst.ptr();
+      const size_t count = (size_t)src.len();
+      return [=](Slot &, cudaStream_t st) { comm->all_gather(sp, dp, count, st); };
     }
     default:
       fail("exec op kind %u is not recognised", (unsigned)o.kind);

@@ -25,6 +25,9 @@ struct ta_pos_cell {
 struct ta_token_ids {
   TokenIds ids;
 };
+struct ta_comm {
+  std::unique_ptr<Comm> comm;
+};
 
 
 // Thread-local error string of the C ABI (capi/src/error.rs:8-32).

@@ -54,13 +54,32 @@ def chunk_seed(seed: int, tensor_id: int, chunk: int) -> int:
     return ((seed * 1000003 + tensor_id) * 4096 + chunk) & 0xFFFFFFFFFFFFFFFF
 
 
+def shard_plan(cfg: LlamaConfig, rank: int, world: int) -> dict:
+    """The tensor-parallel shard of `rank` (the rule ``ta_llama_create_random_tp`` applies):
+    query heads and MLP columns split evenly, kv heads split or shared by neighbouring ranks,
+    lm_head split by vocabulary column.  Offsets are in elements of the unsharded axis."""
+    if cfg.heads % world or cfg.ffn % world or cfg.vocab % world:
+        raise ValueError("heads, ffn and vocab must divide by the world size")
+    if cfg.kv_heads % world and world % cfg.kv_heads:
+        raise ValueError("kv heads must divide by, or divide, the world size")
+    heads_l = cfg.heads // world
+    kv_l = cfg.kv_heads // world if cfg.kv_heads >= world else 1
+    kv_first = rank * cfg.kv_heads // world
+    return dict(heads_l=heads_l, kv_l=kv_l, kv_first=kv_first, group_l=heads_l // kv_l,
+                q0=rank * heads_l * cfg.head_dim, q_w=heads_l * cfg.head_dim,
+                kv0=kv_first * cfg.head_dim, kv_w=kv_l * cfg.head_dim,
+                f0=rank * (cfg.ffn // world), ffn_l=cfg.ffn // world,
+                v0=rank * (cfg.vocab // world), vocab_l=cfg.vocab // world,
+                adds_residual=rank == 0)
+
+
 class Llama:
-    def __init__(self, exec_: Executor, cfg: LlamaConfig):
+    def __init__(self, exec_: Executor, cfg: LlamaConfig, comm=None):
         c = cfg._c()
-        h = capi.lib().ta_llama_create_random(exec_._h, C.byref(c))
+        h = capi.lib().ta_llama_create_random_tp(exec_._h, C.byref(c), comm._h if comm is not None else None)
         if not h:
             raise TensorAshError(_err())
-        self._h, self._exec, self.cfg = h, exec_, cfg
+        self._h, self._exec, self.cfg, self._comm = h, exec_, cfg, comm
 
     def reset(self) -> None:
         _check(capi.lib().ta_llama_reset(self._h))

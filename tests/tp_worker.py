@@ -1,0 +1,147 @@
+"""One rank of the tensor-parallel tests (started by tests/test_tp.py with RANK / WORLD_SIZE /
+MASTER_* in the environment).  `cpu`: numpy shards + gloo collectives against the unsharded
+host forward.  `gpu`: the sharded device runner against the single-GPU runner and the host."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+import __graft_entry__ as entry  # noqa: E402
+from llama_ref import RefLlama  # noqa: E402
+
+
+def small_cfg(ta, **kw):
+    base = dict(layers=2, embd=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1024, t_max=96,
+                weight_sigma=0.05, norm_jitter=0.25, seed=7)
+    base.update(kw)
+    return ta.LlamaConfig(**base)
+
+
+class ShardedRef:
+    """The host forward of one rank's shard; collectives where the device graph has them."""
+
+    def __init__(self, ref: RefLlama, plan: dict, dist, torch):
+        self.ref, self.p, self.dist, self.torch = ref, plan, dist, torch
+        self.k = [np.zeros((0, plan["kv_l"], ref.cfg.head_dim)) for _ in ref.layers]
+        self.v = [np.zeros((0, plan["kv_l"], ref.cfg.head_dim)) for _ in ref.layers]
+        self.pos = 0
+
+    def all_reduce(self, x):
+        t = self.torch.from_numpy(np.ascontiguousarray(x))
+        self.dist.all_reduce(t)
+        return t.numpy()
+
+    def forward(self, tokens):
+        ref, p, c = self.ref, self.p, self.ref.cfg
+        t, pos0 = len(tokens), self.pos
+        x = ref.embd[np.asarray(tokens, dtype=np.int64)]
+        scale = float(np.float32(1.0) / np.sqrt(np.float32(c.head_dim)))
+        f16 = lambda a: a.astype(np.float32).astype(np.float16).astype(np.float64)  # noqa: E731
+        q0, qw, kv0, kvw, f0, fl = p["q0"], p["q_w"], p["kv0"], p["kv_w"], p["f0"], p["ffn_l"]
+        for li, L in enumerate(ref.layers):
+            xn = ref._rms(x, L["attn_norm"])
+            q = ref._rope(xn @ L["wq"][:, q0:q0 + qw], p["heads_l"], pos0).reshape(t, p["heads_l"], c.head_dim)
+            k = f16(ref._rope(xn @ L["wk"][:, kv0:kv0 + kvw], p["kv_l"], pos0)).reshape(t, p["kv_l"], c.head_dim)
+            v = f16(xn @ L["wv"][:, kv0:kv0 + kvw]).reshape(t, p["kv_l"], c.head_dim)
+            self.k[li] = np.concatenate([self.k[li], k])
+            self.v[li] = np.concatenate([self.v[li], v])
+            K, V = self.k[li], self.v[li]
+            out = np.empty((t, p["heads_l"], c.head_dim))
+            for h in range(p["heads_l"]):
+                g = h // p["group_l"]
+                s = (q[:, h, :] @ K[:, g, :].T) * scale
+                kpos = np.arange(K.shape[0])[None, :]
+                qpos = (pos0 + np.arange(t))[:, None]
+                s = np.where(kpos <= qpos, s, -np.inf)
+                s = s - s.max(axis=1, keepdims=True)
+                pr = np.exp(s)
+                out[:, h, :] = (pr @ V[:, g, :]) / pr.sum(axis=1, keepdims=True)
+            o = out.reshape(t, qw) @ L["wo"][q0:q0 + qw, :]
+            if p["adds_residual"]:
+                o = o + x
+            o = self.all_reduce(o)
+            on = ref._rms(o, L["ffn_norm"])
+            up = on @ L["w_up"][:, f0:f0 + fl]
+            gate = on @ L["w_gate"][:, f0:f0 + fl]
+            act = gate / (1.0 + np.exp(-gate)) * up
+            xo = act @ L["w_down"][f0:f0 + fl, :]
+            if p["adds_residual"]:
+                xo = xo + o
+            x = self.all_reduce(xo)
+        self.pos += t
+        last = ref._rms(x[-1:], ref.output_norm)
+        local = (last @ ref.lm_head[:, p["v0"]:p["v0"] + p["vocab_l"]])[0]
+        parts = [self.torch.zeros(p["vocab_l"], dtype=self.torch.float64) for _ in range(self.dist.get_world_size())]
+        self.dist.all_gather(parts, self.torch.from_numpy(np.ascontiguousarray(local)))
+        return np.concatenate([q.numpy() for q in parts])
+
+
+def main_cpu():
+    import torch
+    import torch.distributed as dist
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ta = entry.load_package()
+    orc = entry.load_oracle()
+    cfg = small_cfg(ta)
+    ref_full, ref_shard = RefLlama(orc, cfg), RefLlama(orc, cfg)
+    sh = ShardedRef(ref_shard, ta.shard_plan(cfg, rank, world), dist, torch)
+    prompt = [5, 900, 31, 64, 512, 77, 1]
+    for step_tokens in (prompt, [3], [1000]):
+        want = ref_full.forward(step_tokens)
+        got = sh.forward(step_tokens)
+        err = np.abs(got - want).max() / np.abs(want).max()
+        assert err < 1e-12, f"rank {rank}: sharded host forward differs, rel {err:.3e}"
+    dist.barrier()
+    dist.destroy_process_group()
+    print("TP-CPU-OK", rank)
+
+
+def main_gpu():
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    world = dist.get_world_size()
+    ta = entry.load_package()
+    orc = entry.load_oracle()
+    cfg = small_cfg(ta)
+    ctx = ta.Context(False, f"index:{rank}")
+    ex = ta.Executor(ctx, 2, 256)
+    comm = ta.Comm.from_torch_distributed(ctx)
+    assert comm.world == world and comm.rank == rank
+    model = ta.Llama(ex, cfg, comm)
+    ref = RefLlama(orc, cfg)
+    prompt = [5, 900, 31, 64, 512, 77, 1]
+    nxt, _ = model.prefill(prompt)
+    want = ref.forward(prompt)
+    got = model.logits().astype(np.float64)
+    err = np.abs(got - want).max() / np.abs(want).max()
+    assert err <= 2e-4, f"rank {rank}: prefill logits rel err {err:.3e}"
+    assert nxt == int(np.argmax(want))
+    toks, _ = model.decode(nxt, 16)
+    fed = nxt
+    for i in range(16):
+        want = ref.forward([fed])
+        top = np.sort(want)[-2:]
+        if top[1] - top[0] > 1e-3 * np.abs(want).max():
+            assert toks[i] == int(np.argmax(want)), f"rank {rank} step {i}"
+        fed = toks[i]
+    # every rank must hold the same token stream
+    t = torch.tensor(toks, dtype=torch.int64, device="cuda")
+    ref_t = t.clone()
+    dist.broadcast(ref_t, src=0)
+    assert torch.equal(t, ref_t), f"rank {rank}: token stream differs from rank 0"
+    dist.barrier()
+    model.close()
+    comm.close()
+    dist.destroy_process_group()
+    print("TP-GPU-OK", rank)
+
+
+if __name__ == "__main__":
+    (main_cpu if sys.argv[1] == "cpu" else main_gpu)()
