@@ -59,11 +59,11 @@ constexpr int XS_PRE = 6;   // slice elements per thread fetched in the single a
 
 template <int MROWS>
 struct GemvCfg {
-  static constexpr int U = MROWS <= 2 ? 4 : 2;   // 16-byte loads per lane per pass
+  static constexpr int U = 4;   // 16-byte loads per lane per pass (two passes in flight)
 };
 
 template <int MROWS, int TN>
-__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? 4 : 2)
+__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? 4 : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   constexpr int U = GemvCfg<MROWS>::U;
   constexpr int LPR = TN / 8;          // lanes per weight row (8 f16 per lane)
@@ -437,7 +437,7 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   g.nseg = (uint32_t)nseg;
   g.pdl = (pdl && pdl_enabled()) ? 1u : 0u;
   const int mrows = p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8;
-  const uint32_t u = mrows <= 2 ? 4 : 2;
+  const uint32_t u = 4;
   const uint32_t rpl = 32 / (tn / 8);
   const uint32_t nw = p0.w2 ? GEMV_WARPS / 2 : GEMV_WARPS;
   const uint32_t rows_per_pass = nw * rpl * u;
@@ -453,6 +453,8 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
     const uint32_t k_cta = (p0.k + s - 1) / s;
     if (gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 160 * 1024) continue;
     best_s = s;
+    // the staged x slice (k_cta x rows floats) must leave room for several CTAs per SM
+    if (s < 8 && gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 40 * 1024 && p0.k / (2 * s) >= rows_per_pass) continue;
     // small matrices: 1.5 CTAs per SM; from 16 MB up the stream itself matters and more
     // CTAs keep more of it in flight (up to 3.5 per SM, still one wave)
     const uint64_t want2 = weight_bytes >= (16ull << 20) ? 7ull : 3ull;   // CTAs per SM, doubled
