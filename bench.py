@@ -209,7 +209,32 @@ def bench_llama(ta, ctx, comm, world: int, peaks: dict) -> dict:
     return out
 
 
-def bench_gemv(ta, ctx, peaks: dict) -> dict:
+def bench_f16w_gemm(ta, ctx, peaks: dict, reps: int = 20) -> dict:
+    """f16-weight GEMM (tcgen05 kind::f16) on the prefill shapes of configs[4] and two large squares."""
+    ex = ta.Executor(ctx, 2, 16)
+    rng = np.random.default_rng(5)
+    res = {}
+    for m, n, k in ((512, 2048, 2048), (512, 2560, 2048), (512, 5632, 2048), (512, 2048, 5632),
+                    (4096, 4096, 4096), (8192, 8192, 8192)):
+        a = ta.Tensor.uninit_device(ctx, (m, k))
+        b = ta.Tensor.uninit_device_f16(ctx, (k, n))
+        c = ta.Tensor.uninit_device(ctx, (m, n))
+        ex.upload(rng.standard_normal(m * k, dtype=np.float32), a)
+        ex.upload_f16(rng.standard_normal(k * n, dtype=np.float32).astype(np.float16).view(np.uint16), b)
+        calls = [ta.MatmulCall(a, b, c)]
+        for _ in range(3):
+            ex.run_matmuls(calls)
+        med = statistics.median(ex.run_matmuls(calls).gpu_time_ns for _ in range(reps))
+        tf = 2.0 * m * n * k / med / 1e3
+        res[f"{m}x{n}x{k}"] = {"kernel": ex.dispatch_info_for(1, m, n, k, b_f16=True).kernel, "us": med / 1e3,
+                               "tflops": tf, "frac_of_bf16_sustained": tf / peaks["bf16_sustained"]}
+        for t in (a, b, c):
+            t.close()
+    ex.close()
+    return res
+
+
+def bench_gemv(ta, ctx, peaks: dict, reps: int = 30) -> dict:
     """Configuration 3: decode MLP at 4096 x 11008, packed f16 weights (tile 32), M in {1, 4, 8}:
     fused silu(x@Wg) * (x@Wup) and the down projection, timed as a replayed graph over two
     rotating weight sets (each pass streams 540 MB, far beyond the 126 MB L2)."""
@@ -243,7 +268,7 @@ def bench_gemv(ta, ctx, peaks: dict) -> dict:
         prep = ex.prepare_exec_ops(ops)
         for _ in range(3):
             prep.run()
-        ts = [prep.run().gpu_time_ns for _ in range(30)]
+        ts = [prep.run().gpu_time_ns for _ in range(reps)]
         med = statistics.median(ts) * 1e-9 / len(sets)     # one gate+up+down pass
         bytes_pass = 2 * 2 * k * n + 2 * n * k + 4 * m * (k + n) + 4 * m * (n + k) + 4 * m * n
         res[f"M={m}"] = {"us_per_mlp_pass": med * 1e6, "gbs": bytes_pass / med / 1e9,
@@ -289,7 +314,10 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
-                    help="skip the GEMV (configs[2]) and llama (configs[4]) figures added under extra_metrics")
+                    help="skip the GEMV (configs[2]), llama (configs[4]) and f16w GEMM figures under extra_metrics")
+    ap.add_argument("--extras-only", default=None, choices=["gemv", "llama", "f16w_gemm"],
+                    help="run only this extra workload and print its figures (small cases for profiler captures; "
+                         "--steps sets its timed repetitions)")
     args = ap.parse_args()
 
     globals()["BATCH"] = args.batch
@@ -312,6 +340,21 @@ def main() -> None:
 
     ta = entry.load_package()
     ctx = ta.Context(False, f"index:{local_rank}")
+    if args.extras_only:
+        peaks = measured_peaks()
+        if args.extras_only == "gemv":
+            out = bench_gemv(ta, ctx, peaks, reps=max(1, args.steps))
+        elif args.extras_only == "f16w_gemm":
+            out = bench_f16w_gemm(ta, ctx, peaks, reps=max(1, args.steps))
+        else:
+            comm = ta.Comm.from_torch_distributed(ctx) if distributed else None
+            out = bench_llama(ta, ctx, comm, world, peaks)
+        if rank == 0:
+            print(json.dumps({"extras_only": args.extras_only, "not_a_bench_line": True, **out}))
+        if distributed:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     ex = ta.Executor(ctx, 2, 8, args.kernel)
     host = make_inputs(1234 + rank)
     dev = {k: ta.Tensor.uninit_device(ctx, v[1].shape) for k, v in host.items()}
@@ -399,6 +442,7 @@ def main() -> None:
             extras["llama"] = bench_llama(ta, ctx, comm, world, peaks)
             if world == 1:
                 extras["gemv_f16w"] = bench_gemv(ta, ctx, peaks)
+                extras["f16w_gemm"] = bench_f16w_gemm(ta, ctx, peaks)
         except Exception as exc:  # the headline line must still be printed
             extras["error"] = f"{type(exc).__name__}: {exc}"
 

@@ -44,6 +44,7 @@
 
 #include "k_epilogue.cuh"
 #include "k_trace.cuh"
+#include "k_umma.cuh"
 #include "ta_core.hpp"
 
 namespace cg = cooperative_groups;
@@ -62,8 +63,16 @@ struct GemvCfg {
   static constexpr int U = 4;   // 16-byte loads per lane per pass (two passes in flight)
 };
 
-template <int MROWS, int TN>
-__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? 4 : (MROWS == 4 ? 3 : 2))
+constexpr int RING_STAGES = 4;             // bulk-copy ring: stages of one pass (16 KiB) each
+constexpr int RING_STAGE_BYTES = 16384;
+
+// BULK: packed weights only.  One thread streams the CTA's contiguous tile slice into a
+// shared-memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier transaction
+// counts), four passes ahead and starting before the dependency wait; the warps read their
+// 16-byte pieces from the ring instead of from global memory.  In-flight bytes per SM then
+// depend on shared memory (64 KiB per CTA), not on registers.
+template <int MROWS, int TN, bool BULK>
+__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (BULK ? 3 : 4) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   constexpr int U = GemvCfg<MROWS>::U;
   constexpr int LPR = TN / 8;          // lanes per weight row (8 f16 per lane)
@@ -89,7 +98,9 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   const uint32_t passes = (k_len + rows_per_pass - 1) / rows_per_pass;
 
   // shared: xs[k_cta][MROWS] | wpart[WARPS][MROWS][TN] | cpart[S][2][MROWS][TN] | red[WARPS][MROWS] | scale[MROWS]
-  float *xs = reinterpret_cast<float *>(gemv_smem);
+  // BULK prepends: ring[RING_STAGES][16 KiB] | full barriers | abort flag (128 bytes reserved)
+  constexpr size_t RING_BYTES = BULK ? (size_t)RING_STAGES * RING_STAGE_BYTES + 128 : 0;
+  float *xs = reinterpret_cast<float *>(gemv_smem + RING_BYTES);
   float *wpart = xs + (size_t)g.k_cta * MROWS;
   float *cpart = wpart + GEMV_WARPS * MROWS * TN;
   float *red = cpart + (size_t)S * 2 * MROWS * TN;
@@ -117,12 +128,52 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       if (k < k_hi && col_ok) wv[u] = __ldcs(reinterpret_cast<const uint4 *>(W + base + (size_t)k * row_stride));
     }
   };
+  // ---- BULK: ring bookkeeping.  Stage s holds pass p (p % RING_STAGES == s): rows_per_pass rows
+  // of matrix 0, then (dual) the same rows of matrix 1, each row TN halves, rows contiguous.
+  const uint32_t ring_base = umma::smem_u32(gemv_smem);
+  const uint32_t bar_base = ring_base + RING_STAGES * RING_STAGE_BYTES;
+  volatile uint32_t *ring_abort = reinterpret_cast<volatile uint32_t *>(gemv_smem + RING_STAGES * RING_STAGE_BYTES + 64);
+  auto issue_pass = [&](uint32_t pass) {   // one thread
+    const uint32_t stage = pass % RING_STAGES;
+    const uint32_t row0 = k_lo + pass * rows_per_pass;
+    const uint32_t rows = min(rows_per_pass, k_hi - row0);
+    const uint32_t bytes = rows * TN * 2;
+    const uint32_t bar = bar_base + 8u * stage;
+    umma::mbar_arrive_expect_tx(bar, bytes * (dual ? 2u : 1u));
+    for (int mt = 0; mt < (dual ? 2 : 1); ++mt) {
+      const __half *src = static_cast<const __half *>(mt == 0 ? p.w : p.w2) + ((size_t)tile * p.k + row0) * TN;
+      const uint32_t dst = ring_base + stage * RING_STAGE_BYTES + mt * (rows_per_pass * TN * 2);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+    }
+  };
+  auto ring_pass = [&](uint4 (&wv)[U], uint32_t pass) {   // every thread, after the stage's barrier
+    const uint32_t stage = pass % RING_STAGES;
+    const uint8_t *sp = gemv_smem + stage * RING_STAGE_BYTES + mat * (rows_per_pass * TN * 2);
+    const uint32_t r0 = (uint32_t)wi * RPL + lrow, kk0 = pass * rows_per_pass + r0;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t r = r0 + u * nw * RPL;
+      wv[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (kk0 + u * nw * RPL < k_len) wv[u] = *reinterpret_cast<const uint4 *>(sp + ((size_t)r * TN + lcg) * 2);
+    }
+  };
 
   TA_TRACE_BEGIN()
   TA_TRACE(0)
   uint4 wa[U], wb[U];
-  if (passes > 0) load_pass(wa, 0);
-  if (passes > 1) load_pass(wb, 1);
+  if constexpr (BULK) {
+    if (threadIdx.x == 0) {
+      for (int st = 0; st < RING_STAGES; ++st) umma::mbar_init(bar_base + 8u * st, 1);
+      *ring_abort = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      for (uint32_t ps = 0; ps < passes && ps < (uint32_t)RING_STAGES; ++ps) issue_pass(ps);
+    }
+  } else {
+    if (passes > 0) load_pass(wa, 0);
+    if (passes > 1) load_pass(wb, 1);
+  }
   TA_TRACE(1)
   // the position cell is written by the host before the launch, never by a kernel:
   // fetch it now (it may live in host memory) so its latency hides behind the weights
@@ -255,12 +306,28 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       }
     }
   };
-  for (uint32_t pass = 0; pass < passes; pass += 2) {
-    mul_pass(wa, pass);
-    if (pass + 2 < passes) load_pass(wa, pass + 2);
-    if (pass + 1 < passes) {
-      mul_pass(wb, pass + 1);
-      if (pass + 3 < passes) load_pass(wb, pass + 3);
+  if constexpr (BULK) {
+    bool ring_ok = true;
+    for (uint32_t pass = 0; pass < passes; ++pass) {
+      if (ring_ok) ring_ok = umma::mbar_wait(bar_base + 8u * (pass % RING_STAGES), (pass / RING_STAGES) & 1u, ring_abort);
+      if (ring_ok) {
+        ring_pass(wa, pass);
+        mul_pass(wa, pass);
+      }
+      if (pass + RING_STAGES < passes) {
+        __syncthreads();   // every warp is done with the stage before it is refilled
+        if (threadIdx.x == 0 && ring_ok) issue_pass(pass + RING_STAGES);
+      }
+    }
+    if (!ring_ok && threadIdx.x == 0 && g.status) atomicOr(g.status, 2u);   // the host call fails
+  } else {
+    for (uint32_t pass = 0; pass < passes; pass += 2) {
+      mul_pass(wa, pass);
+      if (pass + 2 < passes) load_pass(wa, pass + 2);
+      if (pass + 1 < passes) {
+        mul_pass(wb, pass + 1);
+        if (pass + 3 < passes) load_pass(wb, pass + 3);
+      }
     }
   }
 
@@ -359,9 +426,10 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   TA_TRACE(7)
 }
 
-size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s) {
+size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s, bool bulk = false) {
   return ((size_t)k_cta * mrows + (size_t)GEMV_WARPS * mrows * tn + (size_t)s * 2 * mrows * tn +
-          (size_t)GEMV_WARPS * mrows + mrows) * sizeof(float) + 16;
+          (size_t)GEMV_WARPS * mrows + mrows) * sizeof(float) + 16 +
+         (bulk ? (size_t)RING_STAGES * RING_STAGE_BYTES + 128 : 0);
 }
 
 bool pdl_enabled() {
@@ -372,14 +440,14 @@ bool pdl_enabled() {
   return on;
 }
 
-template <int MROWS, int TN>
+template <int MROWS, int TN, bool BULK>
 void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
-  const size_t smem = gemv_smem_bytes(g.k_cta, MROWS, TN, g.ksplit);
+  const size_t smem = gemv_smem_bytes(g.k_cta, MROWS, TN, g.ksplit, BULK);
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  200 * 1024));
     attr_done[dev & 63] = true;
   }
@@ -402,7 +470,7 @@ void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN>, g));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK>, g));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -422,7 +490,16 @@ bool gemv_f16w_groupable(const GemvParams &a, const GemvParams &b) {
          ta == tb && !a.w2 == !b.w2;
 }
 
-void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, cudaStream_t stream) {
+static bool bulk_possible(const GemvParams *segs, int nseg) {
+  for (int i = 0; i < nseg; ++i)
+    if (!segs[i].packed || (reinterpret_cast<uintptr_t>(segs[i].w) & 15u) ||
+        (segs[i].w2 && (reinterpret_cast<uintptr_t>(segs[i].w2) & 15u)))
+      return false;
+  return true;
+}
+
+void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, uint32_t *status,
+                            cudaStream_t stream) {
   if (nseg < 1 || nseg > GEMV_MAX_SEGS) fail("GEMV group of %d segments (1..%d)", nseg, GEMV_MAX_SEGS);
   GemvGroup g{};
   const GemvParams &p0 = segs[0];
@@ -436,6 +513,7 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   }
   g.nseg = (uint32_t)nseg;
   g.pdl = (pdl && pdl_enabled()) ? 1u : 0u;
+  g.status = status;
   const int mrows = p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8;
   const uint32_t u = 4;
   const uint32_t rpl = 32 / (tn / 8);
@@ -445,31 +523,55 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   // per SM that is one wave for this launch and leaves room for the early CTAs of
   // the next launch, which prefetch their weights while this one finishes.  Never
   // split below one pass of rows.
+  bool bulk = bulk_possible(segs, nseg);   // bulk-copy ring: packed tiles (contiguous per CTA), 16-byte aligned bases
   uint64_t weight_bytes = 0;
   for (int i = 0; i < nseg; ++i) weight_bytes += (uint64_t)segs[i].k * segs[i].n * 2 * (segs[i].w2 ? 2 : 1);
+  if (p0.m > 2) bulk = false;   // more rows: the staged x slice and the accumulators need the space
+  // measured: the ring wins on long streams (4096 x 11008: 3.8 -> 4.8 TB/s) and is neutral to
+  // slightly slower on the few-MB matrices of a decode step, which are latency-bound
+  if (weight_bytes < (64ull << 20)) bulk = false;
+  if (const char *e = std::getenv("TA_GEMV_BULK")) bulk = e[0] != '0' && p0.m <= 2 && bulk_possible(segs, nseg);
   uint32_t best_s = 1;
-  for (uint32_t s : {1u, 2u, 4u, 8u}) {
-    if (s > 1 && p0.k / s < rows_per_pass) break;
-    const uint32_t k_cta = (p0.k + s - 1) / s;
-    if (gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 160 * 1024) continue;
-    best_s = s;
-    // the staged x slice (k_cta x rows floats) must leave room for several CTAs per SM
-    if (s < 8 && gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 40 * 1024 && p0.k / (2 * s) >= rows_per_pass) continue;
-    // small matrices: 1.5 CTAs per SM; from 16 MB up the stream itself matters and more
-    // CTAs keep more of it in flight (up to 3.5 per SM, still one wave)
-    const uint64_t want2 = weight_bytes >= (16ull << 20) ? 7ull : 3ull;   // CTAs per SM, doubled
-    if ((uint64_t)tiles * s * 2 >= want2 * (uint64_t)sm_count) break;
-    if (s < 8 && (uint64_t)tiles * s * 2 * 2 > 8ull * (uint64_t)sm_count) break;   // the next split would not fit one wave
+  if (weight_bytes >= (64ull << 20) && mrows <= 2) {
+    // Large matrices stream: about eight passes per CTA amortise its prologue and epilogue
+    // while several CTAs per SM overlap them (measured best on 4096 x 11008 and the llama MLP).
+    const uint32_t want_k = 8 * rows_per_pass;
+    for (uint32_t s : {1u, 2u, 4u, 8u}) {
+      best_s = s;
+      if (p0.k / s <= want_k + want_k / 2) break;
+    }
+  } else {
+    for (uint32_t s : {1u, 2u, 4u, 8u}) {
+      if (s > 1 && p0.k / s < rows_per_pass) break;
+      const uint32_t k_cta = (p0.k + s - 1) / s;
+      if (gemv_smem_bytes(k_cta, mrows, (int)tn, s, bulk) > 160 * 1024) continue;
+      best_s = s;
+      // the staged x slice (k_cta x rows floats) must leave room for several CTAs per SM
+      if (s < 8 && gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 40 * 1024 && p0.k / (2 * s) >= rows_per_pass) continue;
+      // small matrices: 1.5 CTAs per SM; from 16 MB up more CTAs keep more of the stream in flight
+      const uint64_t want2 = weight_bytes >= (16ull << 20) ? 7ull : 3ull;   // CTAs per SM, doubled
+      if ((uint64_t)tiles * s * 2 >= want2 * (uint64_t)sm_count) break;
+      if (s < 8 && (uint64_t)tiles * s * 2 * 2 > 8ull * (uint64_t)sm_count) break;   // the next split would not fit one wave
+    }
+  }
+  if (const char *e = std::getenv("TA_GEMV_KSPLIT")) {   // experiments: force the cluster split
+    const uint32_t v = (uint32_t)atoi(e);
+    if ((v == 1 || v == 2 || v == 4 || v == 8) && p0.k / v >= rows_per_pass) best_s = v;
   }
   g.ksplit = best_s;
   g.k_cta = (p0.k + best_s - 1) / best_s;
-  if (gemv_smem_bytes(g.k_cta, mrows, (int)tn, best_s) > 196 * 1024)
+  if (gemv_smem_bytes(g.k_cta, mrows, (int)tn, best_s, bulk) > 196 * 1024)
     fail("GEMV: K = %u with %u rows does not fit shared memory at any cluster split", p0.k, p0.m);
-#define TA_GEMV_CASE(MR)                                             \
-  if (mrows == MR) {                                                 \
-    if (tn == 64) launch_t<MR, 64>(g, tiles, stream);                \
-    else launch_t<MR, 32>(g, tiles, stream);                         \
-    return;                                                          \
+#define TA_GEMV_CASE(MR)                                                          \
+  if (mrows == MR) {                                                              \
+    if (bulk) {                                                                   \
+      if (tn == 64) launch_t<MR, 64, true>(g, tiles, stream);                     \
+      else launch_t<MR, 32, true>(g, tiles, stream);                              \
+    } else {                                                                      \
+      if (tn == 64) launch_t<MR, 64, false>(g, tiles, stream);                    \
+      else launch_t<MR, 32, false>(g, tiles, stream);                             \
+    }                                                                             \
+    return;                                                                       \
   }
   TA_GEMV_CASE(1)
   TA_GEMV_CASE(2)
@@ -480,8 +582,8 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
 
 TA_TRACE_EXPORT(ta_debug_gemv_trace)
 
-void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream) {
-  launch_gemv_f16w_group(&p, 1, sm_count, true, stream);
+void launch_gemv_f16w(GemvParams p, int sm_count, uint32_t *status, cudaStream_t stream) {
+  launch_gemv_f16w_group(&p, 1, sm_count, true, status, stream);
 }
 
 }  // namespace ta

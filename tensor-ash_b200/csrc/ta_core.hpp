@@ -292,6 +292,7 @@ struct GemvGroup {
   uint32_t nseg;
   uint32_t ksplit, k_cta;             // cluster size along K and rows per rank
   uint32_t pdl;                       // 1: launched with programmatic stream serialization
+  uint32_t *status;                   // device word for bounded-wait timeouts (may be null)
 };
 
 struct FlashParams {
@@ -566,9 +567,10 @@ constexpr uint64_t SPLITK2_STATIC_MAX_FLOATS = 1ull << 20;  // 4 MiB
 void launch_splitk2_static(const GemmParams &p, cudaStream_t stream);
 
 bool gemv_f16w_supported(uint32_t m, uint32_t n, uint32_t k, bool packed, uint32_t tile_n);
-void launch_gemv_f16w(GemvParams p, int sm_count, cudaStream_t stream);
+void launch_gemv_f16w(GemvParams p, int sm_count, uint32_t *status, cudaStream_t stream);
 bool gemv_f16w_groupable(const GemvParams &a, const GemvParams &b);
-void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, cudaStream_t stream);
+void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, uint32_t *status,
+                            cudaStream_t stream);
 
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream);
 void launch_attn_decode(const AttnDecodeParams &p, cudaStream_t stream);

@@ -486,7 +486,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         f.act = 0; f.binary = 0; f.d = nullptr;
         if (flops) *flops += c0.flops + c1.flops;
         if (n_calls) *n_calls += 2;
-        plan.push_back([f, sms](Slot &, cudaStream_t st) { launch_gemv_f16w_group(&f, 1, sms, true, st); });
+        plan.push_back([f, sms](Slot &slot, cudaStream_t st) { launch_gemv_f16w_group(&f, 1, sms, true, slot.status, st); });
         prev_gemv.assign(1, f);
         i += 2;
         continue;
@@ -513,8 +513,8 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     }
     if (flops) *flops += fl;
     if (n_calls) *n_calls += segs.size();
-    plan.push_back([segs, sms](Slot &, cudaStream_t st) {
-      launch_gemv_f16w_group(segs.data(), (int)segs.size(), sms, true, st);
+    plan.push_back([segs, sms](Slot &slot, cudaStream_t st) {
+      launch_gemv_f16w_group(segs.data(), (int)segs.size(), sms, true, slot.status, st);
     });
     prev_gemv = segs;
     i = j;

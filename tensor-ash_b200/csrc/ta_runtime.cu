@@ -447,7 +447,7 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
   {
     GemvParams g;
     if (gemv_params_for(op, r, route, &g)) {
-      launch_gemv_f16w(g, ctx_->sm_count, stream);
+      launch_gemv_f16w(g, ctx_->sm_count, slot.status, stream);
       return;
     }
   }
@@ -666,7 +666,7 @@ RunStats Executor::swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &
   ctx_->make_current();
   Slot &slot = checkout_slot();
   SlotGuard guard(*this, slot);
-  return timed(slot, 1, 2 * r.total_flops, [&](cudaStream_t s) { launch_gemv_f16w(g, ctx_->sm_count, s); });
+  return timed(slot, 1, 2 * r.total_flops, [&](cudaStream_t s) { launch_gemv_f16w(g, ctx_->sm_count, slot.status, s); });
 }
 
 // ------------------------------------------------------------------ measured tuner
