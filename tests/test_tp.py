@@ -62,19 +62,22 @@ def test_shard_plan_covers_every_column_once(ta):
         ta.shard_plan(cfg, 0, 3)
 
 
-def test_sharded_forward_over_gloo_matches_unsharded(ta, orc):
-    outs = run_workers("cpu", 2, 29611)
+@pytest.mark.parametrize("world,port", [(2, 29611), (4, 29613)])
+def test_sharded_forward_over_gloo_matches_unsharded(ta, orc, world, port):
+    """world 4 on 2 kv heads exercises kv heads shared by neighbouring ranks."""
+    outs = run_workers("cpu", world, port)
     for rc, out in outs:
         assert rc == 0, out
         assert "TP-CPU-OK" in out, out
 
 
 @pytest.mark.gpu
-def test_two_rank_llama_matches_single_gpu(ta, orc):
+@pytest.mark.parametrize("world,port", [(2, 29612), (4, 29614)])
+def test_sharded_llama_on_devices_matches_host_forward(ta, orc, world, port):
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    outs = run_workers("gpu", 2, 29612)
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    outs = run_workers("gpu", world, port)
     for rc, out in outs:
         assert rc == 0, out
         assert "TP-GPU-OK" in out, out

@@ -86,7 +86,7 @@ def main_cpu():
     rank, world = dist.get_rank(), dist.get_world_size()
     ta = entry.load_package()
     orc = entry.load_oracle()
-    cfg = small_cfg(ta)
+    cfg = small_cfg(ta, heads=4 if world <= 2 else 8, embd=256 if world <= 2 else 512)
     ref_full, ref_shard = RefLlama(orc, cfg), RefLlama(orc, cfg)
     sh = ShardedRef(ref_shard, ta.shard_plan(cfg, rank, world), dist, torch)
     prompt = [5, 900, 31, 64, 512, 77, 1]
@@ -109,7 +109,7 @@ def main_gpu():
     world = dist.get_world_size()
     ta = entry.load_package()
     orc = entry.load_oracle()
-    cfg = small_cfg(ta)
+    cfg = small_cfg(ta, heads=4 if world <= 2 else 8, embd=256 if world <= 2 else 512)
     ctx = ta.Context(False, f"index:{rank}")
     ex = ta.Executor(ctx, 2, 256)
     comm = ta.Comm.from_torch_distributed(ctx)
