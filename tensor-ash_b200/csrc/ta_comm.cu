@@ -10,8 +10,15 @@
 // imported torch the loader hands back the NCCL torch ships, so both use one copy.
 // Collectives are enqueued on the caller's stream and can be captured into CUDA
 // graphs like any other node.
+// Small all-reduces (a decode step's [1, embd] partial sums, 8 KB) do not go through
+// NCCL: every rank owns an exchange buffer that all peers map (CUDA IPC over NVLink peer
+// access), and one kernel per rank pushes its vector into every peer's buffer, raises a
+// flag there, waits (bounded) for the peers' flags in its own buffer and adds the vectors
+// in rank order.  One launch, one NVLink store latency; every rank computes the same sum
+// in the same order, so the result is bit-identical across ranks.
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -76,6 +83,89 @@ NcclApi &nccl_required() {
 
 }  // namespace
 
+// ------------------------------------------------------------------ peer-write all-reduce
+// Exchange buffer of one rank: data[2 parities][world][PEER_MAX_FLOATS] then
+// flags[2][world][PEER_MAX_CTAS] then epoch[PEER_MAX_CTAS] (this rank's call counters).
+constexpr uint32_t PEER_MAX_FLOATS = 8192, PEER_MAX_CTAS = 8, PEER_MAX_WORLD = 8, PEER_THREADS = 256;
+constexpr size_t PEER_DATA_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_FLOATS * sizeof(float);
+constexpr size_t PEER_FLAG_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_CTAS * sizeof(uint32_t);
+constexpr size_t PEER_BUF_BYTES = PEER_DATA_BYTES + PEER_FLAG_BYTES + PEER_MAX_CTAS * sizeof(uint32_t);
+
+struct PeerTable {
+  uint8_t *buf[PEER_MAX_WORLD];   // every rank's exchange buffer as mapped in this process
+  uint32_t rank, world;
+};
+
+__device__ __forceinline__ float *peer_data(uint8_t *buf, uint32_t parity, uint32_t src) {
+  return reinterpret_cast<float *>(buf) + ((size_t)parity * PEER_MAX_WORLD + src) * PEER_MAX_FLOATS;
+}
+__device__ __forceinline__ uint32_t *peer_flag(uint8_t *buf, uint32_t parity, uint32_t src, uint32_t cta) {
+  return reinterpret_cast<uint32_t *>(buf + PEER_DATA_BYTES) + ((size_t)parity * PEER_MAX_WORLD + src) * PEER_MAX_CTAS + cta;
+}
+
+// CTA c of every rank handles floats [c * 1024, (c + 1) * 1024) and synchronises only with CTA c
+// of the peers.  Call e of a CTA uses parity e & 1: a rank can be at most one call ahead of a
+// peer (it needs the peer's flag of call e to finish call e), so the slot a peer still reads
+// is never the one being written.
+__global__ void __launch_bounds__(PEER_THREADS)
+peer_all_reduce_kernel(float *data, uint32_t count, PeerTable t, uint32_t *status, uint32_t pdl) {
+  if (pdl) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+  const uint32_t cta = blockIdx.x, me = t.rank;
+  uint8_t *mine = t.buf[me];
+  uint32_t *epoch_p = reinterpret_cast<uint32_t *>(mine + PEER_DATA_BYTES + PEER_FLAG_BYTES) + cta;
+  const uint32_t e = *epoch_p, parity = e & 1u, ticket = e + 1u;
+  const uint32_t idx = (cta * PEER_THREADS + threadIdx.x) * 4;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool live = idx < count;   // count % 4 == 0
+  if (live) {
+    v = *reinterpret_cast<const float4 *>(data + idx);
+    for (uint32_t r = 0; r < t.world; ++r)
+      if (r != me) *reinterpret_cast<float4 *>(peer_data(t.buf[r], parity, me) + idx) = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ uint32_t ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1u;
+  __syncthreads();
+  if (threadIdx.x < t.world && threadIdx.x != me) {
+    const uint32_t r = threadIdx.x;
+    // raise my flag in peer r's buffer, then wait for peer r's flag in mine
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag(t.buf[r], parity, me, cta)), "r"(ticket) : "memory");
+    const uint32_t *f = peer_flag(mine, parity, r, cta);
+    uint64_t t0, now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    uint32_t seen = 0, spins = 0;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+      if (seen == ticket) break;
+      if ((++spins & 255u) == 0) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (now - t0 > 1000000000ull) {   // one second: give up, report, carry on with what is there
+          ok_flag = 0u;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (live) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t r = 0; r < t.world; ++r) {   // rank order: the same sum on every rank
+      float4 x = v;
+      if (r != me) x = __ldcg(reinterpret_cast<const float4 *>(peer_data(mine, parity, r) + idx));
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    *reinterpret_cast<float4 *>(data + idx) = acc;
+  }
+  if (threadIdx.x == 0) {
+    *epoch_p = ticket;
+    if (!ok_flag && status) atomicOr(status, 4u);
+  }
+}
+
 void comm_unique_id(uint8_t out[COMM_ID_BYTES]) {
   static_assert(COMM_ID_BYTES == sizeof(NcclUniqueId), "id size");
   NcclUniqueId id;
@@ -96,14 +186,97 @@ std::unique_ptr<Comm> Comm::create(const std::shared_ptr<Context> &ctx, uint32_t
   NcclUniqueId id;
   memcpy(&id, id_bytes, sizeof(id));
   nccl_check(api.CommInitRank(&c->handle, (int)world, id, (int)rank), "ncclCommInitRank");
+  c->setup_peer_exchange();
   return c;
 }
 
-Comm::~Comm() {
-  if (handle) {
-    if (ctx) cudaSetDevice(ctx->device);
-    nccl().CommDestroy(handle);
+// Maps every rank's exchange buffer into this process: IPC handles travel through an
+// NCCL all-gather.  Any failure (no peer access, IPC unavailable) leaves the communicator
+// on NCCL for all sizes.
+void Comm::setup_peer_exchange() {
+  const char *env = std::getenv("TA_PEER_ALLREDUCE");
+  if (env && env[0] == '0') return;
+  if (world > PEER_MAX_WORLD) return;
+  NcclApi &api = nccl();
+  void *buf = nullptr;
+  if (cudaMalloc(&buf, PEER_BUF_BYTES) != cudaSuccess) { cudaGetLastError(); return; }
+  cudaMemset(buf, 0, PEER_BUF_BYTES);
+  cudaIpcMemHandle_t mine;
+  if (cudaIpcGetMemHandle(&mine, buf) != cudaSuccess) { cudaGetLastError(); cudaFree(buf); return; }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "ipc handle size");
+  uint8_t *dev_handles = nullptr;   // [world + 1][64]: slot world holds this rank's handle and an ok byte
+  TA_CUDA(cudaMalloc((void **)&dev_handles, (size_t)(world + 1) * 64));
+  TA_CUDA(cudaMemcpy(dev_handles + (size_t)world * 64, &mine, 64, cudaMemcpyHostToDevice));
+  cudaStream_t st;
+  TA_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  nccl_check(api.AllGather(dev_handles + (size_t)world * 64, dev_handles, 16, NCCL_FLOAT32, handle, st),
+             "ncclAllGather (ipc handles)");
+  TA_CUDA(cudaStreamSynchronize(st));
+  std::vector<cudaIpcMemHandle_t> all(world);
+  TA_CUDA(cudaMemcpy(all.data(), dev_handles, (size_t)world * 64, cudaMemcpyDeviceToHost));
+  cudaFree(dev_handles);
+  std::vector<void *> mapped(world, nullptr);
+  bool ok = true;
+  for (uint32_t r = 0; r < world && ok; ++r) {
+    if (r == rank) { mapped[r] = buf; continue; }
+    if (cudaIpcOpenMemHandle(&mapped[r], all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      cudaGetLastError();
+      ok = false;
+    }
   }
+  // all ranks must agree: sum of failures over the group
+  float *flag_dev = nullptr;
+  TA_CUDA(cudaMalloc((void **)&flag_dev, sizeof(float)));
+  const float bad = ok ? 0.0f : 1.0f;
+  TA_CUDA(cudaMemcpy(flag_dev, &bad, sizeof(float), cudaMemcpyHostToDevice));
+  nccl_check(api.AllReduce(flag_dev, flag_dev, 1, NCCL_FLOAT32, NCCL_SUM, handle, st), "ncclAllReduce (peer setup)");
+  TA_CUDA(cudaStreamSynchronize(st));
+  float total_bad = 0.0f;
+  TA_CUDA(cudaMemcpy(&total_bad, flag_dev, sizeof(float), cudaMemcpyDeviceToHost));
+  cudaFree(flag_dev);
+  cudaStreamDestroy(st);
+  if (total_bad != 0.0f) {
+    for (uint32_t r = 0; r < world; ++r)
+      if (r != rank && mapped[r]) cudaIpcCloseMemHandle(mapped[r]);
+    cudaFree(buf);
+    return;
+  }
+  peer_own = buf;
+  peer_bufs = mapped;
+}
+
+bool Comm::peer_all_reduce_sum(float *data, size_t count, uint32_t *status, bool pdl, cudaStream_t stream) const {
+  if (!peer_own || count == 0 || count > PEER_MAX_FLOATS || (count & 3u) ||
+      (reinterpret_cast<uintptr_t>(data) & 15u))
+    return false;
+  PeerTable t{};
+  for (uint32_t r = 0; r < world; ++r) t.buf[r] = static_cast<uint8_t *>(peer_bufs[r]);
+  t.rank = rank;
+  t.world = world;
+  const uint32_t ctas = (uint32_t)((count / 4 + PEER_THREADS - 1) / PEER_THREADS);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas, 1, 1);
+  cfg.blockDim = dim3(PEER_THREADS, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, peer_all_reduce_kernel, data, (uint32_t)count, t, status, pdl ? 1u : 0u));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return true;
+}
+
+Comm::~Comm() {
+  if (ctx) cudaSetDevice(ctx->device);
+  if (peer_own) {
+    cudaDeviceSynchronize();
+    for (uint32_t r = 0; r < world; ++r)
+      if (r != rank && r < peer_bufs.size() && peer_bufs[r]) cudaIpcCloseMemHandle(peer_bufs[r]);
+    cudaFree(peer_own);
+  }
+  if (handle) nccl().CommDestroy(handle);
 }
 
 void Comm::all_reduce_sum(float *data, size_t count, cudaStream_t stream) const {

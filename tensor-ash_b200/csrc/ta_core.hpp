@@ -366,6 +366,11 @@ struct Comm {
   std::shared_ptr<Context> ctx;
   uint32_t rank = 0, world = 1;
   void *handle = nullptr;   // ncclComm_t; null when world == 1
+  void *peer_own = nullptr;            // this rank's exchange buffer (small all-reduces), null = NCCL only
+  std::vector<void *> peer_bufs;       // every rank's buffer as mapped here (index = rank)
+  void setup_peer_exchange();
+  // one-launch peer-write all-reduce; false when the request does not fit it (caller uses NCCL)
+  bool peer_all_reduce_sum(float *data, size_t count, uint32_t *status, bool pdl, cudaStream_t stream) const;
   static std::unique_ptr<Comm> create(const std::shared_ptr<Context> &ctx, uint32_t rank, uint32_t world,
                                       const uint8_t id[COMM_ID_BYTES]);
   ~Comm();

@@ -384,7 +384,9 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       const Comm *comm = o.comm;
       float *ptr = (float *)t.ptr();
       const size_t count = (size_t)t.len();
-      return [=](Slot &, cudaStream_t st) { comm->all_reduce_sum(ptr, count, st); };
+      return [=](Slot &slot, cudaStream_t st) {
+        if (!comm->peer_all_reduce_sum(ptr, count, slot.status, true, st)) comm->all_reduce_sum(ptr, count, st);
+      };
     }
     case ExecKind::AllGather: {
       const Tensor &src = need(o.in0, "run_all_gather", "src"), &dst = need(o.out, "run_all_gather", "dst");
