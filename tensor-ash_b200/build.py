@@ -28,6 +28,7 @@ SOURCES = [
     "llama_ash.cu",
     "k_gemm_ffma.cu",
     "k_gemm_tf32x3.cu",
+    "k_gemm_tf32x3_2cta.cu",
     "k_gemm_f16w.cu",
     "k_gemv.cu",
     "k_attention.cu",

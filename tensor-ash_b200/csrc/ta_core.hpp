@@ -558,6 +558,8 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
 // Implemented beside each kernel.  All are asynchronous on `stream`.
 void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream);
 bool gemm_tf32x3_eligible(const GemmParams &p);
+bool gemm_tf32x3_pair_supported(const GemmParams &p, int sm_count);
+void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStream_t stream);
 bool gemm_f16w_umma_eligible(const GemmParams &p);
 uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_count);
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,

@@ -297,6 +297,7 @@ static const char *const A_FFMA_128[] = {
     "m128n64k64_bda_v4", "m128n64k64_bda_v4_tm8_tn8", "m128n64k64_bda_v4_tm16_tn4",
     "m128n64k64_bda_v4_aligned", "m64n128", "64x128", "wide", "m64n128_bda", "m64n128_bda_v4",
     "m64n128k64", "64x128k64", nullptr};
+static const char *const A_TF32_PAIR[] = {"tf32x3_m256n256", "tf32x3_pair", "tf32x3_2cta", nullptr};
 static const char *const A_FFMA_64[] = {
     "ffma_m64n64", "small", "small_64", "64", "small_bda", "64_bda", "small_bda_v4", "k64",
     "small_k64", "64k", "k64_bda", "k64_bda_v4", "k64_bda_v4_tm8_tn4", "k64_bda_v4_tm4_tn8",
@@ -327,6 +328,7 @@ static const char *const A_SK_128[] = {"split_k2_m128n128", nullptr};
 static const char *const A_SK_64[] = {"split_k2_m64n64", nullptr};
 
 const KernelSpec KERNEL_SPECS[] = {
+    {"tf32x3_m256n256", 256, 256, 16, Family::Tf32x3, false, A_TF32_PAIR},
     {"tf32x3_m128n256", 128, 256, 16, Family::Tf32x3, false, A_TF32_256},
     {"tf32x3_m128n128", 128, 128, 16, Family::Tf32x3, false, A_TF32_128},
     {"ffma_m128n128", 128, 128, 16, Family::Ffma, false, A_FFMA_128},

@@ -465,7 +465,8 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
   switch (spec.family) {
     case Family::Tf32x3:
       if (gemm_tf32x3_eligible(p)) {
-        launch_gemm_tf32x3(*ctx_, p, spec.tile_n, slot.status, stream);
+        if (spec.tile_m == 256) launch_gemm_tf32x3_pair(*ctx_, p, slot.status, stream);
+        else launch_gemm_tf32x3(*ctx_, p, spec.tile_n, slot.status, stream);
         return;
       }
       launch_gemm_ffma(p, 128, stream);  // alignment demotion

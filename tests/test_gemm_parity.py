@@ -33,7 +33,7 @@ def check(orc, got, ref, abs_tol, label):
     assert r <= REL_TOL, f"{label}: rel err {r:.3e} > {REL_TOL}"
 
 
-@pytest.fixture(scope="module", params=["auto", "ffma", "tf32x3", "tf32x3_m128n128", "small"])
+@pytest.fixture(scope="module", params=["auto", "ffma", "tf32x3", "tf32x3_m128n128", "tf32x3_m256n256", "small"])
 def setup(request, ta):
     ctx = ta.Context(False, "index:0")
     ex = ta.Executor(ctx, 2, 16, request.param, tune=False)
