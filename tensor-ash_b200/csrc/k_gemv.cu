@@ -41,6 +41,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "k_epilogue.cuh"
 #include "k_trace.cuh"
@@ -71,12 +72,20 @@ constexpr int RING_STAGE_BYTES = 16384;
 // counts), four passes ahead and starting before the dependency wait; the warps read their
 // 16-byte pieces from the ring instead of from global memory.  In-flight bytes per SM then
 // depend on shared memory (64 KiB per CTA), not on registers.
-template <int MROWS, int TN, bool BULK>
+// MMA (3 to 8 activation rows): the dot products run on the tensor cores instead of the FMA
+// pipe, which at M = 8 has no headroom left beside a full-rate weight stream.
+// mma.sync m16n8k8 tf32 with x as the A operand (rows = activation rows, padded to 16) split
+// into hi + lo tf32 parts (two MMAs; f16 weights are exact in tf32, so the products carry ~21
+// bits of x) and the weights as the B operand: lane (g, t) = (lane / 4, lane % 4) loads the
+// TN/8 consecutive columns TN/8*g.. of rows k0 + t and k0 + t + 4, which is exactly the B
+// fragment (k = t, t + 4; n = g) of TN/8 MMAs whose column j stands for n = TN/8 * j + q.
+template <int MROWS, int TN, bool BULK, bool MMA>
 __global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (BULK ? 3 : 4) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
+  static_assert(!MMA || (MROWS == 8 && !BULK), "the tensor-core variant handles up to 8 rows, register path");
   constexpr int U = GemvCfg<MROWS>::U;
-  constexpr int LPR = TN / 8;          // lanes per weight row (8 f16 per lane)
-  constexpr int RPL = 32 / LPR;        // weight rows per warp-wide load
+  constexpr int LPR = TN / 8;                    // lanes per weight row (8 f16 per lane)
+  constexpr int RPL = MMA ? 8 : 32 / LPR;        // weight rows per warp-wide load
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t S = g.ksplit;
@@ -170,7 +179,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       for (uint32_t ps = 0; ps < passes && ps < (uint32_t)RING_STAGES; ++ps) issue_pass(ps);
     }
-  } else {
+  } else if constexpr (!MMA) {
     if (passes > 0) load_pass(wa, 0);
     if (passes > 1) load_pass(wb, 1);
   }
@@ -248,14 +257,29 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     const uint32_t idx = threadIdx.x + it * GEMV_THREADS;
     if (idx < stage_n) xs[idx] = xv[it] * nwv[it];
   }
-  for (uint32_t idx = threadIdx.x + XS_PRE * GEMV_THREADS; idx < stage_n; idx += GEMV_THREADS) {
-    const uint32_t kk = idx / MROWS, m = idx % MROWS;
-    float v = 0.0f;
-    if (m < p.m) {
-      v = p.x[(size_t)m * p.k + k_lo + kk];
-      if (p.norm_w) v *= p.norm_w[k_lo + kk];
+  if constexpr (MROWS >= 4) {
+    // many rows: walk k within a row so that global reads are contiguous (the first
+    // XS_PRE * 256 / MROWS k of every row are staged above)
+    const uint32_t kk_done = (XS_PRE * GEMV_THREADS) / MROWS;
+#pragma unroll
+    for (int m = 0; m < MROWS; ++m) {
+      const bool row = (uint32_t)m < p.m;
+      for (uint32_t kk = kk_done + threadIdx.x; kk < k_len; kk += GEMV_THREADS) {
+        float v = row ? p.x[(size_t)m * p.k + k_lo + kk] : 0.0f;
+        if (row && p.norm_w) v *= p.norm_w[k_lo + kk];
+        xs[(size_t)kk * MROWS + m] = v;
+      }
     }
-    xs[idx] = v;
+  } else {
+    for (uint32_t idx = threadIdx.x + XS_PRE * GEMV_THREADS; idx < stage_n; idx += GEMV_THREADS) {
+      const uint32_t kk = idx / MROWS, m = idx % MROWS;
+      float v = 0.0f;
+      if (m < p.m) {
+        v = p.x[(size_t)m * p.k + k_lo + kk];
+        if (p.norm_w) v *= p.norm_w[k_lo + kk];
+      }
+      xs[idx] = v;
+    }
   }
   __syncthreads();
   TA_TRACE(3)
@@ -266,89 +290,168 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     scale[threadIdx.x] = rsqrtf(s / (float)p.k + p.norm_eps);   // read after the reduction barriers below
   }
 
-  // ---- stream the weights: pass i multiplies while pass i+1 is in flight
-  float2 acc[MROWS][4];
-#pragma unroll
-  for (int m = 0; m < MROWS; ++m)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[m][j] = make_float2(0.f, 0.f);
-
-  auto mul_pass = [&](const uint4 (&wv)[U], uint32_t pass) {
-    const uint32_t kk0 = pass * rows_per_pass + (uint32_t)wi * RPL + lrow;
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const uint32_t kk = kk0 + u * nw * RPL;
-      if (kk < k_len) {
-        const __half2 *h = reinterpret_cast<const __half2 *>(&wv[u]);
-        float2 w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) w[j] = __half22float2(h[j]);
-        const float *xr = xs + (size_t)kk * MROWS;
-        float xm[MROWS];
-        if constexpr (MROWS >= 4) {
-#pragma unroll
-          for (int m4 = 0; m4 < MROWS / 4; ++m4) {
-            const float4 t = reinterpret_cast<const float4 *>(xr)[m4];
-            xm[4 * m4] = t.x; xm[4 * m4 + 1] = t.y; xm[4 * m4 + 2] = t.z; xm[4 * m4 + 3] = t.w;
-          }
-        } else if constexpr (MROWS == 2) {
-          const float2 t = *reinterpret_cast<const float2 *>(xr);
-          xm[0] = t.x; xm[1] = t.y;
-        } else {
-          xm[0] = xr[0];
-        }
-#pragma unroll
-        for (int m = 0; m < MROWS; ++m) {
-          const float2 x2 = make_float2(xm[m], xm[m]);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc[m][j] = __ffma2_rn(x2, w[j], acc[m][j]);
-        }
-      }
+  if constexpr (MMA) {
+    // ---- tensor-core stream: NQ columns per lane and k row, two k rows per k8 block
+    constexpr int NQ = TN / 8;
+    using WVec = typename std::conditional<NQ == 4, uint2, uint4>::type;
+    const int gq = lane >> 2, tq = lane & 3;
+    const bool mcol_ok = col0 + NQ * gq < p.n;
+    size_t mbase, mstride;   // in halfs
+    if (p.packed) {
+      mbase = ((size_t)tile * p.k) * TN + NQ * gq;
+      mstride = TN;
+    } else {
+      mbase = (size_t)col0 + NQ * gq;
+      mstride = p.n;
     }
-  };
-  if constexpr (BULK) {
-    bool ring_ok = true;
-    for (uint32_t pass = 0; pass < passes; ++pass) {
-      if (ring_ok) ring_ok = umma::mbar_wait(bar_base + 8u * (pass % RING_STAGES), (pass / RING_STAGES) & 1u, ring_abort);
-      if (ring_ok) {
-        ring_pass(wa, pass);
-        mul_pass(wa, pass);
+    auto load_blocks = [&](WVec (&wv)[U][2], uint32_t pass) {
+      const uint32_t k0 = k_lo + pass * rows_per_pass + (uint32_t)wi * 8;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t k = k0 + u * nw * 8 + tq + 4 * h;
+          wv[u][h] = WVec{};
+          if (k < k_hi && mcol_ok) wv[u][h] = __ldcs(reinterpret_cast<const WVec *>(W + mbase + (size_t)k * mstride));
+        }
+    };
+    float dacc[NQ][4];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dacc[q][i] = 0.0f;
+    auto mma_blocks = [&](const WVec (&wv)[U][2], uint32_t pass) {
+      const uint32_t kk0 = pass * rows_per_pass + (uint32_t)wi * 8;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t kk = kk0 + u * nw * 8 + tq;
+        const float x0 = kk < k_len ? xs[(size_t)kk * MROWS + gq] : 0.0f;
+        const float x1 = kk + 4 < k_len ? xs[(size_t)(kk + 4) * MROWS + gq] : 0.0f;
+        const uint32_t x0h = __float_as_uint(x0) & 0xffffe000u, x1h = __float_as_uint(x1) & 0xffffe000u;
+        const uint32_t x0l = __float_as_uint(x0 - __uint_as_float(x0h)), x1l = __float_as_uint(x1 - __uint_as_float(x1h));
+        const __half *h0 = reinterpret_cast<const __half *>(&wv[u][0]);
+        const __half *h1 = reinterpret_cast<const __half *>(&wv[u][1]);
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+          const uint32_t b0 = __float_as_uint(__half2float(h0[q])), b1 = __float_as_uint(__half2float(h1[q]));
+          asm volatile(
+              "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              : "+f"(dacc[q][0]), "+f"(dacc[q][1]), "+f"(dacc[q][2]), "+f"(dacc[q][3])
+              : "r"(x0h), "r"(0u), "r"(x1h), "r"(0u), "r"(b0), "r"(b1));
+#ifndef TA_EXP_NOLO
+          asm volatile(
+              "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              : "+f"(dacc[q][0]), "+f"(dacc[q][1]), "+f"(dacc[q][2]), "+f"(dacc[q][3])
+              : "r"(x0l), "r"(0u), "r"(x1l), "r"(0u), "r"(b0), "r"(b1));
+#endif
+        }
       }
-      if (pass + RING_STAGES < passes) {
-        __syncthreads();   // every warp is done with the stage before it is refilled
-        if (threadIdx.x == 0 && ring_ok) issue_pass(pass + RING_STAGES);
-      }
-    }
-    if (!ring_ok && threadIdx.x == 0 && g.status) atomicOr(g.status, 2u);   // the host call fails
-  } else {
+    };
+    WVec ma[U][2], mb[U][2];
+    if (passes > 0) load_blocks(ma, 0);
+    if (passes > 1) load_blocks(mb, 1);
     for (uint32_t pass = 0; pass < passes; pass += 2) {
-      mul_pass(wa, pass);
-      if (pass + 2 < passes) load_pass(wa, pass + 2);
+      mma_blocks(ma, pass);
+      if (pass + 2 < passes) load_blocks(ma, pass + 2);
       if (pass + 1 < passes) {
-        mul_pass(wb, pass + 1);
-        if (pass + 3 < passes) load_pass(wb, pass + 3);
+        mma_blocks(mb, pass + 1);
+        if (pass + 3 < passes) load_blocks(mb, pass + 3);
       }
     }
-  }
+    TA_TRACE(4)
+    // lane (g, t) holds row g, columns [2 NQ t, 2 NQ (t + 1)): d0 -> column NQ*2t + q, d1 -> NQ*(2t+1) + q
+    float *dst = wpart + ((size_t)warp * MROWS + gq) * TN + 2 * NQ * tq;
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+      dst[q] = dacc[q][0];
+      dst[NQ + q] = dacc[q][1];
+    }
+  } else {
+    // ---- stream the weights: pass i multiplies while pass i+1 is in flight
+    float2 acc[MROWS][4];
+  #pragma unroll
+    for (int m = 0; m < MROWS; ++m)
+  #pragma unroll
+      for (int j = 0; j < 4; ++j) acc[m][j] = make_float2(0.f, 0.f);
 
-  TA_TRACE(4)
-  // ---- fixed-order reduction: lanes sharing a column group, then warps, then cluster ranks
-#pragma unroll
-  for (int m = 0; m < MROWS; ++m)
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int o = 16; o >= LPR; o >>= 1) {
-        acc[m][j].x += __shfl_xor_sync(0xffffffffu, acc[m][j].x, o);
-        acc[m][j].y += __shfl_xor_sync(0xffffffffu, acc[m][j].y, o);
+    auto mul_pass = [&](const uint4 (&wv)[U], uint32_t pass) {
+      const uint32_t kk0 = pass * rows_per_pass + (uint32_t)wi * RPL + lrow;
+  #pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t kk = kk0 + u * nw * RPL;
+        if (kk < k_len) {
+          const __half2 *h = reinterpret_cast<const __half2 *>(&wv[u]);
+          float2 w[4];
+  #pragma unroll
+          for (int j = 0; j < 4; ++j) w[j] = __half22float2(h[j]);
+          const float *xr = xs + (size_t)kk * MROWS;
+          float xm[MROWS];
+          if constexpr (MROWS >= 4) {
+  #pragma unroll
+            for (int m4 = 0; m4 < MROWS / 4; ++m4) {
+              const float4 t = reinterpret_cast<const float4 *>(xr)[m4];
+              xm[4 * m4] = t.x; xm[4 * m4 + 1] = t.y; xm[4 * m4 + 2] = t.z; xm[4 * m4 + 3] = t.w;
+            }
+          } else if constexpr (MROWS == 2) {
+            const float2 t = *reinterpret_cast<const float2 *>(xr);
+            xm[0] = t.x; xm[1] = t.y;
+          } else {
+            xm[0] = xr[0];
+          }
+  #pragma unroll
+          for (int m = 0; m < MROWS; ++m) {
+            const float2 x2 = make_float2(xm[m], xm[m]);
+  #pragma unroll
+            for (int j = 0; j < 4; ++j) acc[m][j] = __ffma2_rn(x2, w[j], acc[m][j]);
+          }
+        }
       }
-  if (lane < LPR) {
-#pragma unroll
-    for (int m = 0; m < MROWS; ++m) {
-      float *dst = wpart + ((size_t)warp * MROWS + m) * TN + lcg;
-      reinterpret_cast<float4 *>(dst)[0] = make_float4(acc[m][0].x, acc[m][0].y, acc[m][1].x, acc[m][1].y);
-      reinterpret_cast<float4 *>(dst)[1] = make_float4(acc[m][2].x, acc[m][2].y, acc[m][3].x, acc[m][3].y);
+    };
+    if constexpr (BULK) {
+      bool ring_ok = true;
+      for (uint32_t pass = 0; pass < passes; ++pass) {
+        if (ring_ok) ring_ok = umma::mbar_wait(bar_base + 8u * (pass % RING_STAGES), (pass / RING_STAGES) & 1u, ring_abort);
+        if (ring_ok) {
+          ring_pass(wa, pass);
+          mul_pass(wa, pass);
+        }
+        if (pass + RING_STAGES < passes) {
+          __syncthreads();   // every warp is done with the stage before it is refilled
+          if (threadIdx.x == 0 && ring_ok) issue_pass(pass + RING_STAGES);
+        }
+      }
+      if (!ring_ok && threadIdx.x == 0 && g.status) atomicOr(g.status, 2u);   // the host call fails
+    } else {
+      for (uint32_t pass = 0; pass < passes; pass += 2) {
+        mul_pass(wa, pass);
+        if (pass + 2 < passes) load_pass(wa, pass + 2);
+        if (pass + 1 < passes) {
+          mul_pass(wb, pass + 1);
+          if (pass + 3 < passes) load_pass(wb, pass + 3);
+        }
+      }
     }
+
+    TA_TRACE(4)
+    // ---- fixed-order reduction: lanes sharing a column group, then warps, then cluster ranks
+  #pragma unroll
+    for (int m = 0; m < MROWS; ++m)
+  #pragma unroll
+      for (int j = 0; j < 4; ++j)
+  #pragma unroll
+        for (int o = 16; o >= LPR; o >>= 1) {
+          acc[m][j].x += __shfl_xor_sync(0xffffffffu, acc[m][j].x, o);
+          acc[m][j].y += __shfl_xor_sync(0xffffffffu, acc[m][j].y, o);
+        }
+    if (lane < LPR) {
+  #pragma unroll
+      for (int m = 0; m < MROWS; ++m) {
+        float *dst = wpart + ((size_t)warp * MROWS + m) * TN + lcg;
+        reinterpret_cast<float4 *>(dst)[0] = make_float4(acc[m][0].x, acc[m][0].y, acc[m][1].x, acc[m][1].y);
+        reinterpret_cast<float4 *>(dst)[1] = make_float4(acc[m][2].x, acc[m][2].y, acc[m][3].x, acc[m][3].y);
+      }
+    }
+
   }
   __syncthreads();
   const int nmat = dual ? 2 : 1;
@@ -440,14 +543,14 @@ bool pdl_enabled() {
   return on;
 }
 
-template <int MROWS, int TN, bool BULK>
+template <int MROWS, int TN, bool BULK, bool MMA = false>
 void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   const size_t smem = gemv_smem_bytes(g.k_cta, MROWS, TN, g.ksplit, BULK);
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  200 * 1024));
     attr_done[dev & 63] = true;
   }
@@ -470,7 +573,7 @@ void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK>, g));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK, MMA>, g));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -514,9 +617,13 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   g.nseg = (uint32_t)nseg;
   g.pdl = (pdl && pdl_enabled()) ? 1u : 0u;
   g.status = status;
-  const int mrows = p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8;
+  // five rows and more: tensor-core variant (8-row kernel).  Measured on 4096 x 11008: at M = 8 it
+  // is ahead of the FMA path (196 vs 214 us per MLP pass), at M = 4 behind it (160 vs 99 us).
+  bool mma = p0.m >= 5;
+  if (const char *e = std::getenv("TA_GEMV_MMA")) mma = mma && e[0] != '0';
+  const int mrows = mma ? 8 : (p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8);
   const uint32_t u = 4;
-  const uint32_t rpl = 32 / (tn / 8);
+  const uint32_t rpl = mma ? 8 : 32 / (tn / 8);
   const uint32_t nw = p0.w2 ? GEMV_WARPS / 2 : GEMV_WARPS;
   const uint32_t rows_per_pass = nw * rpl * u;
   // K split over a cluster: about one and a half CTAs per SM.  With four resident
@@ -572,6 +679,11 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
       else launch_t<MR, 32, false>(g, tiles, stream);                             \
     }                                                                             \
     return;                                                                       \
+  }
+  if (mma) {
+    if (tn == 64) launch_t<8, 64, false, true>(g, tiles, stream);
+    else launch_t<8, 32, false, true>(g, tiles, stream);
+    return;
   }
   TA_GEMV_CASE(1)
   TA_GEMV_CASE(2)
