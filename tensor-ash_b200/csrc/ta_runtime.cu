@@ -693,7 +693,7 @@ void Executor::tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
   std::vector<Route> cands;
   const int heuristic = heuristic_kernel(batch, m, n, k, false, ctx_->sm_count);
   cands.push_back(Route{heuristic, 0});
-  for (const char *name : {"tf32x3_m128n256", "tf32x3_m128n128", "ffma_m128n128", "ffma_m64n64"}) {
+  for (const char *name : {"tf32x3_m128n256", "tf32x3_m128n128", "tf32x3_m256n256", "ffma_m128n128", "ffma_m64n64"}) {
     const int idx = idx_of(name);
     if (idx == heuristic) continue;
     if (KERNEL_SPECS[idx].family == Family::Tf32x3 && (k % 4 || n % 4)) continue;
