@@ -17,15 +17,28 @@
 // is the hi operand) and write lo into a twin buffer at identical offsets: the
 // shared-memory swizzle never has to be decoded.
 //
-// Warp roles (448 threads): warps 0-3 drain TMEM and run the epilogue (warp w
-// owns TMEM lanes 32w..32w+31 = tile rows), warp 4 issues TMA, warp 5 owns the
-// TMEM allocation and issues the MMAs, warps 6-13 split tiles into hi/lo in two
-// groups of four that take alternate K blocks (one block's load-split-store-fence
-// chain overlaps the next block's).
+// Warp roles (640 threads, five warpgroups): warps 0-7 drain TMEM and run the epilogue
+// (warp w owns TMEM lanes 32 (w % 4).. = tile rows and the column half w / 4), warp 8 issues
+// TMA, warp 9 owns the TMEM allocation and issues the MMAs, warps 12-19 split tiles into
+// hi/lo in two groups of four that take alternate K blocks (one block's load-split-store-
+// fence chain overlaps the next block's).  setmaxnreg moves registers from the worker
+// warpgroups (48 each) to the epilogue warpgroups (168 each).
+//
+// Accuracy: the tensor-memory accumulator truncates after every MMA, an error that grows
+// linearly with the number of MMAs it absorbs (measured: 9e-6 relative at K = 1024, 1.6e-5 at
+// K = 2048 when a whole K runs in one accumulator).  K is therefore cut into chunks: a chunk
+// accumulates in one of the two tensor-memory buffers, the epilogue warps drain it into
+// per-thread running sums (round-to-nearest f32 adds) while the next chunk runs in the other
+// buffer; a tile's epilogue runs on the running sums.  Draining tensor memory takes bandwidth
+// from the MMAs writing it (measured on 32 x 2048^3: 197 TFLOP/s with one drain per tile, 190
+// with chunks of 1024, 172 with chunks of 512), so the default chunk is 1024 (at most ~1e-5
+// relative at any K); TA_TF32X3_CHUNK_KB=32 selects chunks of 512 (4.2e-6 at any K).
 // Every mbarrier wait is bounded (about two seconds); on a timeout the CTA
 // raises a flag, all roles leave their loops, and the host reports an error.
 #include <cuda.h>
 #include <cudaTypedefs.h>
+
+#include <cstdlib>
 
 #include "k_epilogue.cuh"
 #include "k_umma.cuh"
@@ -38,7 +51,18 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 16;                      // floats per stage along K (64-byte rows of A)
 constexpr int CVT_GROUPS = 2;               // converter groups of 4 warps, alternating K blocks
-constexpr int NUM_THREADS = 192 + CVT_GROUPS * 128;
+// warpgroups (4 warps each): 0-1 epilogue (left / right half of the tile's columns), 2 = TMA
+// warp + MMA warp + two idle warps, 3-4 converters
+constexpr int EPI_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, CVT_WARP0 = 12;
+constexpr int NUM_THREADS = (CVT_WARP0 + 4 * CVT_GROUPS) * 32;   // 640
+constexpr uint32_t CHUNK_KB = 64;           // K blocks (1024 k) per tensor-memory accumulation
+// setmaxnreg only redistributes the registers the CTA was launched with (threads x the
+// per-thread count the compiler reports, 96 for 640 threads), and `inc` blocks until they are
+// there: the split must fit that pool or the kernel never starts.
+constexpr int LAUNCH_REGS = 96, EPI_REGS = 168, WORKER_REGS = 48;
+static_assert(EPI_WARPS * 32 * EPI_REGS + (NUM_THREADS - EPI_WARPS * 32) * WORKER_REGS <= NUM_THREADS * LAUNCH_REGS,
+              "setmaxnreg split exceeds the CTA's launch-time register allocation");
+static_assert(NUM_THREADS * (LAUNCH_REGS + 8) > 65536, "LAUNCH_REGS must be what __launch_bounds__ yields");
 
 template <int BN>
 struct Cfg {
@@ -95,13 +119,13 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 128);
+      mbar_init(acc_empty(b), EPI_WARPS * 32);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 5) tmem_alloc(smem_u32((const void *)tmem_slot), C::TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(smem_u32((const void *)tmem_slot), C::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -112,7 +136,13 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
   const uint32_t num_tiles = tiles_per_batch * p.batch;
   const uint32_t k_blocks = (p.k + BK - 1) / BK;
 
-  if (warp == 4) {
+  // Register budget by warpgroup (setmaxnreg is a warpgroup-wide instruction, so the split is on
+  // warp / 4 first): the epilogue warpgroups keep a whole tile's running sums in registers,
+  // everyone else needs few.
+  const int wgroup = warp >> 2;
+  if (wgroup == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WORKER_REGS));
+  if (warp == TMA_WARP) {
     // ------------------------------------------------------------ TMA producer
     uint32_t stage = 0, phase = 0;
     bool ok = true;
@@ -136,46 +166,52 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------ MMA issuer
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) |
                            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     uint32_t stage = 0, phase = 0, acc_it = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
-      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
-      ok = mbar_wait(acc_empty(buf), acc_phase ^ 1u, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * C::ACC_STRIDE;
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-        ok = mbar_wait(full_cvt(stage), phase, abort_flag);
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (uint32_t kb0 = 0; ok && kb0 < k_blocks; kb0 += p.chunk_kb, ++acc_it) {
+        // one K chunk per tensor-memory buffer: the epilogue warps drain chunk c while chunk c+1 runs
+        const uint32_t kb1 = min(k_blocks, kb0 + p.chunk_kb);
+        const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+        ok = mbar_wait(acc_empty(buf), acc_phase ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_hi = smem_base + stage * C::STAGE_BYTES;
-          const uint32_t b_hi = a_hi + C::A_BYTES;
-          const uint32_t a_lo = a_hi + C::HALF_BYTES, b_lo = b_hi + C::HALF_BYTES;
+        const uint32_t d_tmem = tmem_base + buf * C::ACC_STRIDE;
+        for (uint32_t kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(full_cvt(stage), phase, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_hi = smem_base + stage * C::STAGE_BYTES;
+            const uint32_t b_hi = a_hi + C::A_BYTES;
+            const uint32_t a_lo = a_hi + C::HALF_BYTES, b_lo = b_hi + C::HALF_BYTES;
 #pragma unroll
-          for (int j = 0; j < BK / 8; ++j) {
-            const uint64_t da_hi = make_desc(a_hi + j * 32, 16, 512, LAYOUT_SW64);
-            const uint64_t da_lo = make_desc(a_lo + j * 32, 16, 512, LAYOUT_SW64);
-            const uint64_t db_hi = make_desc(b_hi + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
-            const uint64_t db_lo = make_desc(b_lo + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
-            mma_tf32(d_tmem, da_lo, db_hi, idesc, (kb | (uint32_t)j) != 0u);
-            mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
-            mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            for (int j = 0; j < BK / 8; ++j) {
+              const uint64_t da_hi = make_desc(a_hi + j * 32, 16, 512, LAYOUT_SW64);
+              const uint64_t da_lo = make_desc(a_lo + j * 32, 16, 512, LAYOUT_SW64);
+              const uint64_t db_hi = make_desc(b_hi + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
+              const uint64_t db_lo = make_desc(b_lo + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
+              mma_tf32(d_tmem, da_lo, db_hi, idesc, ((kb - kb0) | (uint32_t)j) != 0u);
+              mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+              mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            }
+            tc_commit(empty(stage));                       // stage reusable once these MMAs retire
+            if (kb + 1 == kb1) tc_commit(acc_full(buf));
           }
-          tc_commit(empty(stage));                       // stage reusable once these MMAs retire
-          if (kb + 1 == k_blocks) tc_commit(acc_full(buf));
+          __syncwarp();
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
-        __syncwarp();
-        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp >= 6) {
+  }
+  } else if (wgroup >= 3) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WORKER_REGS));
     // ------------------------------------------------------------ hi/lo converters
-    const int t = (threadIdx.x - 6 * 32) & 127, group = (threadIdx.x - 6 * 32) >> 7;
+    const int t = (threadIdx.x - CVT_WARP0 * 32) & 127, group = (threadIdx.x - CVT_WARP0 * 32) >> 7;
     uint32_t stage = 0, phase = 0, it_all = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
@@ -200,54 +236,67 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 0-3)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EPI_REGS));
+    // ------------------------------------------------------------ epilogue (warps 0-7)
+    // Warp w drains TMEM lanes 32 (w % 4) .. +31 (tile rows) and the column half w / 4.  The
+    // chunks of a tile are summed in registers (ordinary round-to-nearest f32 adds), so the
+    // truncating tensor-memory accumulator never absorbs more than one chunk of MMAs.
+    constexpr int HALF_N = BN / 2;
+    const int lane_grp = warp & 3, col_half = warp >> 2;
     uint32_t acc_it = 0;
     bool ok = true;
     const bool alpha_is_one = p.alpha == 1.0f;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-      const uint32_t m0 = (rem / tiles_n) * BM, n0 = (rem % tiles_n) * BN;
-      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
-      ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
+      const uint32_t m0 = (rem / tiles_n) * BM, n0 = (rem % tiles_n) * BN + col_half * HALF_N;
+      float sum[HALF_N];
+#pragma unroll
+      for (int i = 0; i < HALF_N; ++i) sum[i] = 0.0f;
+      for (uint32_t kb0 = 0; ok && kb0 < k_blocks; kb0 += p.chunk_kb, ++acc_it) {
+        const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+        ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + col_half * HALF_N + ((uint32_t)(lane_grp * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < HALF_N; c0 += 16) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) sum[c0 + i] += v[i];
+        }
+        tc_fence_before();
+        mbar_arrive(acc_empty(buf));
+      }
       if (!ok) break;
-      tc_fence_after();
-      const uint32_t row = m0 + warp * 32 + lane;
+      const uint32_t row = m0 + lane_grp * 32 + lane;
       const bool row_ok = row < p.m;
       const size_t row_off = (size_t)batch * p.stride_c + (size_t)row * p.n;
       float *__restrict__ crow = p.c + row_off;
       const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
-      const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(warp * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        tmem_ld32(taddr + c0, v);
-        const uint32_t col0 = n0 + c0;
-        if (row_ok && col0 < p.n) {
+      if (row_ok) {
 #pragma unroll
-          for (int q = 0; q < 32; q += 4) {
-            const uint32_t col = col0 + q;
-            if (col < p.n) {  // N % 4 == 0: a float4 is either fully in or fully out
-              float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-              if (p.accumulate) {
-                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
-                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
-              }
-              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
-              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
-              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
-              o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
-              o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
-              o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
-              o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
-              *reinterpret_cast<float4 *>(crow + col) = o;
+        for (int q = 0; q < HALF_N; q += 4) {
+          const uint32_t col = n0 + q;
+          if (col < p.n) {  // N % 4 == 0: a float4 is either fully in or fully out
+            float4 o = make_float4(sum[q], sum[q + 1], sum[q + 2], sum[q + 3]);
+            if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+            if (p.accumulate) {
+              const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+              o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
             }
+            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+            if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+            if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+            o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
+            o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
+            o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
+            o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
+            *reinterpret_cast<float4 *>(crow + col) = o;
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(acc_empty(buf));
     }
   }
 
@@ -261,7 +310,7 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
     if (threadIdx.x == 0) atomicOr(status, 1u);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
@@ -284,8 +333,14 @@ void encode_map(const Context &ctx, CUtensorMap *map, const void *base, uint64_t
 }
 
 template <int BN>
-void launch_t(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStream_t stream) {
+void launch_t(const Context &ctx, const GemmParams &p_in, uint32_t *status, cudaStream_t stream) {
   using C = Cfg<BN>;
+  GemmParams p = p_in;
+  p.chunk_kb = CHUNK_KB;
+  if (const char *e = std::getenv("TA_TF32X3_CHUNK_KB")) {   // experiments: K blocks per accumulation
+    const int v = atoi(e);
+    if (v > 0) p.chunk_kb = (uint32_t)v;
+  }
   static bool attr_set[64] = {};
   if (!attr_set[ctx.device & 63]) {
     TA_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -261,6 +261,8 @@ struct GemmParams {
   uint32_t accumulate, act, binary, b_f16;
   // split-K stage 1 only: K range partition count; plane = (batch*splits+s)
   uint32_t splits;
+  // tf32x3 tensor-core kernel: K blocks of 16 accumulated in tensor memory between drains (set by its launcher)
+  uint32_t chunk_kb;
 };
 
 // Parameters of the f16-weight GEMV kernel (M <= 8 activation rows).
