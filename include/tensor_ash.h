@@ -324,6 +324,9 @@ typedef struct ta_flash_desc {
   float scale;                   /* 1/sqrt(dh) for standard attention */
   uint32_t token_major_heads;    /* 0: q is [H, T_q, dh]; H > 0: q is token-major [T_q, H*dh] */
   uint32_t out_token_major_heads;/* 0: out follows q; H > 0: out is [T_q, H*dh] whatever q is */
+  uint32_t simt;                 /* 1: pin the f32-operand kernel (run_flash_attention_simt in the reference);
+                                  * 0: f16 caches with head dim 64 and >= 32 query rows take the tensor-core
+                                  * kernel, which rounds Q*scale and the softmax weights through f16 */
 } ta_flash_desc;
 
 int ta_flash_attention(const ta_executor *exec, const ta_tensor *q, const ta_tensor *kt,

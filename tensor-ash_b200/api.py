@@ -461,9 +461,10 @@ class ExecOp:
         return cls(ExecKind.ATTN_DECODE, in0=q, in1=kt, in2=v, in3=scratch, out=out, attn=(kv_len, scale, pos_cell))
 
     @classmethod
-    def flash_attn(cls, q, kt, v, out, kv_len, pos_base, scale, token_major_heads=0, out_token_major_heads=0):
+    def flash_attn(cls, q, kt, v, out, kv_len, pos_base, scale, token_major_heads=0, out_token_major_heads=0,
+                   simt=False):
         return cls(ExecKind.FLASH_ATTN, in0=q, in1=kt, in2=v, out=out,
-                   flash=(kv_len, pos_base, scale, token_major_heads, out_token_major_heads))
+                   flash=(kv_len, pos_base, scale, token_major_heads, out_token_major_heads, int(simt)))
 
     @classmethod
     def argmax(cls, inp, result_cell):
@@ -617,9 +618,10 @@ class Executor:
         return PreparedOps(h, (self, list(ops)))
 
     def run_flash_attention(self, q: Tensor, kt: Tensor, v: Tensor, out: Tensor, kv_len: int, pos_base: int,
-                            scale: float, token_major_heads: int = 0, out_token_major_heads: int = 0) -> RunStats:
+                            scale: float, token_major_heads: int = 0, out_token_major_heads: int = 0,
+                            simt: bool = False) -> RunStats:
         st = capi.RunStatsC()
-        desc = capi.FlashDescC(kv_len, pos_base, scale, token_major_heads, out_token_major_heads)
+        desc = capi.FlashDescC(kv_len, pos_base, scale, token_major_heads, out_token_major_heads, int(simt))
         _check(lib().ta_flash_attention(self._h, q._h, kt._h, v._h, out._h, C.byref(desc), C.byref(st)))
         return RunStats._from(st)
 

@@ -63,7 +63,7 @@ class MatmulOpExC(C.Structure):
 
 class FlashDescC(C.Structure):
     _fields_ = [("kv_len", C.c_uint32), ("pos_base", C.c_uint32), ("scale", C.c_float),
-                ("token_major_heads", C.c_uint32), ("out_token_major_heads", C.c_uint32)]
+                ("token_major_heads", C.c_uint32), ("out_token_major_heads", C.c_uint32), ("simt", C.c_uint32)]
 
 
 class AttnDecodeDescC(C.Structure):

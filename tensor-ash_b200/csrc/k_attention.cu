@@ -126,6 +126,199 @@ flash_prefill_kernel(const FlashParams p) {
   }
 }
 
+// ------------------------------------------------------------------ prefill, tensor cores
+// The f16-operand route of the reference (its coopmat2 flash kernels round Q*scale, K, V and
+// the softmax weights through f16 and accumulate in f32, tests/correctness/flash.rs:481-485):
+// mma.sync m16n8k16 for S = (Q*scale) K^T and O = P V, online softmax in registers.
+// CTA = 4 warps x 16 query rows; K/V tiles of 64 positions arrive through cp.async into a
+// double-buffered shared-memory pair (Kt rows [d][pos], V rows [pos][d], 16-byte padded) and
+// reach the B fragments with ldmatrix.trans.  f16 caches with dh = 64 only.
+constexpr int FM_BQ = 64, FM_BKV = 64, FM_DH = 64, FM_PAD = 8, FM_LD = FM_BKV + FM_PAD;
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *smem_row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
+__global__ void __launch_bounds__(128)
+flash_prefill_mma_kernel(const FlashParams p) {
+  __shared__ __align__(16) __half Ksh[2][FM_DH * FM_LD];    // [d][pos]
+  __shared__ __align__(16) __half Vsh[2][FM_BKV * FM_LD];   // [pos][d]
+  const uint32_t head = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t g = lane >> 2, t = lane & 3;
+  const uint32_t q0 = blockIdx.x * FM_BQ;
+  const uint32_t kv_head = head / p.group;
+  const __half *kt = static_cast<const __half *>(p.kt) + (size_t)kv_head * FM_DH * p.t_max;
+  const __half *vv = static_cast<const __half *>(p.v) + (size_t)kv_head * p.t_max * FM_DH;
+
+  const uint32_t row_a = q0 + warp * 16 + g, row_b = row_a + 8;   // this thread's two query rows
+  const uint32_t valid_a = row_a < p.t_q ? (uint32_t)min((uint64_t)p.kv_len, (uint64_t)p.pos_base + row_a + 1u) : 0u;
+  const uint32_t valid_b = row_b < p.t_q ? (uint32_t)min((uint64_t)p.kv_len, (uint64_t)p.pos_base + row_b + 1u) : 0u;
+  const uint32_t last_row = min(q0 + FM_BQ, p.t_q) - 1u;
+  const uint32_t valid_max = (uint32_t)min((uint64_t)p.kv_len, (uint64_t)p.pos_base + last_row + 1u);
+  const uint32_t num_tiles = (valid_max + FM_BKV - 1) / FM_BKV;
+
+  auto load_tile = [&](uint32_t tile, int buf) {
+    const uint32_t k0 = tile * FM_BKV;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const uint32_t i = tid + it * 128, r = i >> 3, c8 = (i & 7u) * 8u;
+      // K: row r = head dim d, 8 positions k0 + c8..; V: row r = position k0 + r, 8 dims c8..
+      __half *kd = &Ksh[buf][r * FM_LD + c8];
+      __half *vd = &Vsh[buf][r * FM_LD + c8];
+      if (k0 + c8 + 8 <= p.t_max) cp_async16(kd, kt + (size_t)r * p.t_max + k0 + c8);
+      else *reinterpret_cast<uint4 *>(kd) = make_uint4(0u, 0u, 0u, 0u);
+      if (k0 + r < p.t_max) cp_async16(vd, vv + (size_t)(k0 + r) * FM_DH + c8);
+      else *reinterpret_cast<uint4 *>(vd) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (num_tiles > 0) load_tile(0, 0);
+
+  // Q * scale as f16 A fragments: 4 steps of 16 head dims
+  uint32_t qf[4][4];
+  {
+    const float *qa = p.q + (size_t)head * p.q_head_stride + (size_t)min(row_a, p.t_q - 1) * p.q_row_stride;
+    const float *qb = p.q + (size_t)head * p.q_head_stride + (size_t)min(row_b, p.t_q - 1) * p.q_row_stride;
+    const bool la = row_a < p.t_q, lb = row_b < p.t_q;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int d0 = 16 * s + 2 * t;
+      const float2 a0 = la ? *reinterpret_cast<const float2 *>(qa + d0) : make_float2(0.f, 0.f);
+      const float2 b0 = lb ? *reinterpret_cast<const float2 *>(qb + d0) : make_float2(0.f, 0.f);
+      const float2 a1 = la ? *reinterpret_cast<const float2 *>(qa + d0 + 8) : make_float2(0.f, 0.f);
+      const float2 b1 = lb ? *reinterpret_cast<const float2 *>(qb + d0 + 8) : make_float2(0.f, 0.f);
+      qf[s][0] = pack_h2(a0.x * p.scale, a0.y * p.scale);
+      qf[s][1] = pack_h2(b0.x * p.scale, b0.y * p.scale);
+      qf[s][2] = pack_h2(a1.x * p.scale, a1.y * p.scale);
+      qf[s][3] = pack_h2(b1.x * p.scale, b1.y * p.scale);
+    }
+  }
+
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
+  float m_a = NEG_BIG, m_b = NEG_BIG, l_a = 0.0f, l_b = 0.0f;   // l: this thread's share of the row sum
+
+  // ldmatrix row addressing: lane -> matrix lane / 8, row lane % 8
+  const uint32_t lm = lane >> 3, lr = lane & 7;
+
+  for (uint32_t tile = 0; tile < num_tiles; ++tile) {
+    const int buf = (int)(tile & 1u);
+    if (tile + 1 < num_tiles) {
+      load_tile(tile + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t k0 = tile * FM_BKV;
+
+    // ---- S = (Q*scale) K^T : 8 blocks of 8 positions
+    float sc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[j][i] = 0.0f;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {   // position blocks 2jp, 2jp+1
+        uint32_t b[4];
+        // matrices: (d 16s..+7, blk 2jp), (d 16s+8.., blk 2jp), (d 16s.., blk 2jp+1), (d 16s+8.., blk 2jp+1)
+        ldmatrix_x4_trans(b, &Ksh[buf][(16 * s + (lm & 1u) * 8 + lr) * FM_LD + (2 * jp + (lm >> 1)) * 8]);
+        mma_f16_16816(sc[2 * jp], qf[s], b[0], b[1]);
+        mma_f16_16816(sc[2 * jp + 1], qf[s], b[2], b[3]);
+      }
+    }
+    // ---- mask, running max, probabilities
+    float mx_a = NEG_BIG, mx_b = NEG_BIG;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t pos = k0 + 8 * j + 2 * t;
+      sc[j][0] = pos < valid_a ? sc[j][0] : NEG_BIG;
+      sc[j][1] = pos + 1 < valid_a ? sc[j][1] : NEG_BIG;
+      sc[j][2] = pos < valid_b ? sc[j][2] : NEG_BIG;
+      sc[j][3] = pos + 1 < valid_b ? sc[j][3] : NEG_BIG;
+      mx_a = fmaxf(mx_a, fmaxf(sc[j][0], sc[j][1]));
+      mx_b = fmaxf(mx_b, fmaxf(sc[j][2], sc[j][3]));
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    const float corr_a = expf(m_a - mn_a), corr_b = expf(m_b - mn_b);   // 1 while nothing is visible yet
+    m_a = mn_a;
+    m_b = mn_b;
+    l_a *= corr_a;
+    l_b *= corr_b;
+    uint32_t pf[4][4];   // P as A fragments: 4 steps of 16 positions
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p0 = sc[j][0] > -3.0e38f ? expf(sc[j][0] - mn_a) : 0.0f;
+      const float p1 = sc[j][1] > -3.0e38f ? expf(sc[j][1] - mn_a) : 0.0f;
+      const float p2 = sc[j][2] > -3.0e38f ? expf(sc[j][2] - mn_b) : 0.0f;
+      const float p3 = sc[j][3] > -3.0e38f ? expf(sc[j][3] - mn_b) : 0.0f;
+      l_a += p0 + p1;
+      l_b += p2 + p3;
+      pf[j >> 1][(j & 1) * 2] = pack_h2(p0, p1);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_h2(p2, p3);
+      o[j][0] *= corr_a; o[j][1] *= corr_a;
+      o[j][2] *= corr_b; o[j][3] *= corr_b;
+    }
+    // ---- O += P V : 4 steps of 16 positions x 8 blocks of 8 head dims
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {   // head-dim blocks 2jp, 2jp+1
+        uint32_t b[4];
+        // matrices: (pos 16ks..+7, dblk 2jp), (pos 16ks+8.., dblk 2jp), (pos 16ks.., dblk 2jp+1), (pos 16ks+8.., 2jp+1)
+        ldmatrix_x4_trans(b, &Vsh[buf][(16 * ks + (lm & 1u) * 8 + lr) * FM_LD + (2 * jp + (lm >> 1)) * 8]);
+        mma_f16_16816(o[2 * jp], pf[ks], b[0], b[1]);
+        mma_f16_16816(o[2 * jp + 1], pf[ks], b[2], b[3]);
+      }
+    }
+    __syncthreads();   // the buffer is refilled by the load issued in the next iteration
+  }
+
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+  if (valid_a > 0) {
+    float *oa = p.out + (size_t)head * p.o_head_stride + (size_t)row_a * p.o_row_stride;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float2 *>(oa + 8 * j + 2 * t) = make_float2(o[j][0] * inv_a, o[j][1] * inv_a);
+  }
+  if (valid_b > 0) {
+    float *ob = p.out + (size_t)head * p.o_head_stride + (size_t)row_b * p.o_row_stride;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float2 *>(ob + 8 * j + 2 * t) = make_float2(o[j][2] * inv_b, o[j][3] * inv_b);
+  }
+}
+
 // ------------------------------------------------------------------ decode
 // One CTA per (chunk, kv head), 128 threads = 8 query rows x 16 lanes.  A chunk
 // is walked in tiles of 64 positions: the K tile [d][j] and the V tile [j][d]
@@ -341,8 +534,23 @@ inline void launched() {
 
 TA_TRACE_EXPORT(ta_debug_attn_trace)
 
+// The tensor-core route: f16 caches, head dim 64, 16-byte-aligned rows, at least 32 query rows
+// (short prefills keep f32 operands), and not pinned to the f32 kernel by the caller.
+bool flash_prefill_mma_eligible(const FlashParams &p) {
+  return !p.simt && p.kv_f16 && p.dh == 64 && p.t_q >= 32 && (p.t_max % 8u) == 0 &&
+         (reinterpret_cast<uintptr_t>(p.kt) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.v) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(p.q) & 7u) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0 &&
+         (p.q_row_stride % 2u) == 0 && (p.q_head_stride % 2u) == 0 && (p.o_row_stride % 2u) == 0 &&
+         (p.o_head_stride % 2u) == 0;
+}
+
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream) {
   dim3 grid((p.t_q + 63) / 64, p.heads);
+  if (flash_prefill_mma_eligible(p)) {
+    flash_prefill_mma_kernel<<<grid, 128, 0, stream>>>(p);
+    launched();
+    return;
+  }
   if (p.dh == 64) flash_prefill_kernel<64><<<grid, 128, 0, stream>>>(p);
   else if (p.dh == 128) flash_prefill_kernel<128><<<grid, 128, 0, stream>>>(p);
   else fail("run_flash_attention: head dim %u is not supported (64 or 128)", p.dh);

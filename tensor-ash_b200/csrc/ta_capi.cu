@@ -543,6 +543,7 @@ static std::vector<ExecOp> checked_exec_ops(const ta_executor &e, const ta_exec_
     o.flash.kv_len = r.flash.kv_len; o.flash.pos_base = r.flash.pos_base; o.flash.scale = r.flash.scale;
     o.flash.token_major_heads = r.flash.token_major_heads;
     o.flash.out_token_major_heads = r.flash.out_token_major_heads;
+    o.flash.simt = r.flash.simt;
     o.attn.kv_len = r.attn.kv_len; o.attn.scale = r.attn.scale;
     o.attn.pos_cell = r.attn.pos_cell ? &r.attn.pos_cell->cell : nullptr;
     o.cell = r.cell ? &r.cell->cell : nullptr;
@@ -698,6 +699,7 @@ int ta_flash_attention(const ta_executor *exec, const ta_tensor *q, const ta_ten
     FlashAttentionDesc fd;
     fd.kv_len = d.kv_len; fd.pos_base = d.pos_base; fd.scale = d.scale;
     fd.token_major_heads = d.token_major_heads; fd.out_token_major_heads = d.out_token_major_heads;
+    fd.simt = d.simt;
     write_stats(stats, e.exec->flash_attention(tq, tk, tv, to, fd));
   });
 }

@@ -305,6 +305,7 @@ struct FlashParams {
   float scale;
   uint32_t q_head_stride, q_row_stride, o_head_stride, o_row_stride;
   uint32_t kv_f16;
+  uint32_t simt;   // 1: pin the f32-operand kernel (run_flash_attention_simt of the reference)
 };
 
 struct AttnDecodeParams {
@@ -324,6 +325,7 @@ struct FlashAttentionDesc {
   uint32_t kv_len = 0, pos_base = 0;
   float scale = 1.0f;
   uint32_t token_major_heads = 0, out_token_major_heads = 0;
+  uint32_t simt = 0;
 };
 
 struct AttnDecodeDesc {

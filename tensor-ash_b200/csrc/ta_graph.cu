@@ -95,6 +95,7 @@ FlashParams Executor::plan_flash_attention(const Tensor &q, const Tensor &kt, co
   p.heads = heads; p.group = heads / kv_heads; p.dh = dh; p.t_q = t_q; p.t_max = t_max;
   p.kv_len = desc.kv_len; p.pos_base = desc.pos_base; p.scale = desc.scale;
   p.kv_f16 = kt.dtype == DType::F16;
+  p.simt = desc.simt;
   return p;
 }
 
