@@ -24,6 +24,8 @@
 // bounded; a timeout raises the abort flag and the host reports an error.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "k_epilogue.cuh"
 #include "k_umma.cuh"
 #include "ta_core.hpp"
@@ -261,6 +263,233 @@ gemm_f16w_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
   }
 }
 
+// ------------------------------------------------------------------ pre-converted A
+// When the caller's slot has scratch for it, A is rounded to f16 once per launch by a small
+// elementwise kernel (rows padded to a multiple of 8 halves) and the GEMM becomes a plain
+// TMA -> tcgen05 pipeline: no converter warps, no raw f32 tile in shared memory, K blocks of 64.
+// Both operands take the 128-byte swizzle (A K-major: SBO 1024; B N-major: LBO 64*128, SBO 1024).
+constexpr int PK = 64;                       // K elements per stage
+constexpr int PRE_THREADS = 192;             // warps 0-3 epilogue, 4 TMA, 5 MMA + TMEM
+
+template <int BN>
+struct PreCfg {
+  static constexpr int A_BYTES = BM * PK * 2;             // 16 KiB
+  static constexpr int B_BYTES = PK * BN * 2;             // 32 KiB at BN = 256
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+__global__ void __launch_bounds__(256)
+convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint32_t k, uint32_t kp, uint64_t rows) {
+  // one thread per 8 output halves (16 bytes); the pad columns k..kp-1 are zeros
+  const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t per_row = kp / 8;
+  if (idx >= rows * per_row) return;
+  const uint64_t r = idx / per_row;
+  const uint32_t c = (uint32_t)(idx % per_row) * 8;
+  const float *src = a + r * k + c;
+  float v[8];
+  if (c + 8 <= k && (k & 3u) == 0) {
+    const float4 x = *reinterpret_cast<const float4 *>(src), y = *reinterpret_cast<const float4 *>(src + 4);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = c + i < k ? src[i] : 0.0f;
+  }
+  uint4 o;
+  o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]);
+  o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+  *reinterpret_cast<uint4 *>(out + r * kp + c) = o;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(PRE_THREADS, 1)
+gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b, uint32_t *__restrict__ status) {
+  using C = PreCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  auto full = [&](int s) { return bar_base + 8u * s; };
+  auto empty = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto acc_full = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+  auto acc_empty = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
+  volatile uint32_t *tmem_slot =
+      reinterpret_cast<volatile uint32_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 128);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 5) tmem_alloc(smem_u32((const void *)tmem_slot), C::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
+  const uint32_t tiles_per_batch = tiles_m * tiles_n;
+  const uint32_t num_tiles = tiles_per_batch * p.batch;
+  const uint32_t k_blocks = (p.k + PK - 1) / PK;
+
+  if (warp == 4) {
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      const int m0 = (int)(rem % tiles_m) * BM, n0 = (int)(rem / tiles_m) * BN;
+      const int za = p.stride_a ? (int)batch : 0, zb = p.stride_b ? (int)batch : 0;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+          mbar_arrive_expect_tx(full(stage), C::STAGE_BYTES);
+          tma_load_3d(dst, &map_a, full(stage), (int)(kb * PK), m0, za);
+#pragma unroll
+          for (int nb = 0; nb < BN / 64; ++nb)
+            tma_load_3d(dst + C::A_BYTES + nb * (PK * 128), &map_b, full(stage), n0 + nb * 64, (int)(kb * PK), zb);
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 5) {
+    const uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    uint32_t stage = 0, phase = 0, acc_it = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+      ok = mbar_wait(acc_empty(buf), acc_phase ^ 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        ok = mbar_wait(full(stage), phase, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a16 = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t b16 = a16 + C::A_BYTES;
+#pragma unroll
+          for (int j = 0; j < PK / 16; ++j) {
+            const uint64_t da = make_desc(a16 + j * 32, 16, 1024, LAYOUT_SW128);
+            const uint64_t db = make_desc(b16 + j * 2048, PK * 128, 1024, LAYOUT_SW128);
+            mma_f16(d_tmem, da, db, idesc, (kb | (uint32_t)j) != 0u);
+          }
+          tc_commit(empty(stage));
+          if (kb + 1 == k_blocks) tc_commit(acc_full(buf));
+        }
+        __syncwarp();
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else {
+    uint32_t acc_it = 0;
+    bool ok = true;
+    const bool alpha_is_one = p.alpha == 1.0f;
+    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      const uint32_t m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
+      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+      ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t row = m0 + warp * 32 + lane;
+      const bool row_ok = row < p.m;
+      const size_t row_off = (size_t)batch * p.stride_c + (size_t)row * p.n;
+      float *__restrict__ crow = p.c + row_off;
+      const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
+      const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(taddr + c0, v);
+        const uint32_t col0 = n0 + c0;
+        if (row_ok && col0 < p.n) {
+#pragma unroll
+          for (int q = 0; q < 32; q += 4) {
+            const uint32_t col = col0 + q;
+            if (col < p.n) {
+              float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+              if (p.accumulate) {
+                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+              }
+              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+              o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
+              o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
+              o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
+              o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
+              *reinterpret_cast<float4 *>(crow + col) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty(buf));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(100000);
+    if (threadIdx.x == 0) atomicOr(status, 1u);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <int BN>
+void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t kp, uint32_t *status,
+                  cudaStream_t stream) {
+  using C = PreCfg<BN>;
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx.device & 63]) {
+    TA_CUDA(cudaFuncSetAttribute(gemm_f16w_pre_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    attr_set[ctx.device & 63] = true;
+  }
+  const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
+  const uint64_t rows = ba * p.m;
+  const uint64_t items = rows * (kp / 8);
+  convert_a_f16_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(static_cast<const float *>(p.a), a16, p.k, kp, rows);
+  TA_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  CUtensorMap map_a, map_b;
+  // A16 [ba, M, Kp] f16: 128-byte rows of 64 halves, 128-byte swizzle; columns >= K read as zero (TMA bound K)
+  encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a16, p.k, p.m, ba, (uint64_t)kp * 2,
+              (uint64_t)p.m * kp * 2, PK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, p.n, p.k, bb, (uint64_t)p.n * 2,
+              p.stride_b ? (uint64_t)p.stride_b * 2 : (uint64_t)p.k * p.n * 2, 64, PK, CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
+  const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
+  gemm_f16w_pre_kernel<BN><<<grid, PRE_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);
+  TA_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
 template <int BN>
 void launch_t(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStream_t stream) {
   using C = Cfg<BN>;
@@ -320,10 +549,27 @@ uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_co
   return best;
 }
 
+// Scratch bytes for the f16 copy of A (rows padded to 8 halves).
+size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
+  const uint64_t kp = ((uint64_t)k + 7) & ~7ull;
+  return (size_t)((uint64_t)batch_a * m * kp * 2);
+}
+
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
-                           cudaStream_t stream) {
+                           void *scratch, size_t scratch_bytes, cudaStream_t stream) {
   if (!gemm_f16w_umma_eligible(p))
     fail("f16w tensor-core GEMM needs f32 A, f16 B, K %% 4 == 0 and N %% 8 == 0");
+  const uint32_t batch_a = p.stride_a ? p.batch : 1;
+  const char *env = std::getenv("TA_F16W_PRE");
+  if (scratch && scratch_bytes >= gemm_f16w_umma_scratch_bytes(batch_a, p.m, p.k) &&
+      (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0 && !(env && env[0] == '0')) {
+    const uint32_t kp = (p.k + 7u) & ~7u;
+    __half *a16 = static_cast<__half *>(scratch);
+    if (tile_n >= 256) launch_pre_t<256>(ctx, p, a16, kp, status, stream);
+    else if (tile_n >= 128) launch_pre_t<128>(ctx, p, a16, kp, status, stream);
+    else launch_pre_t<64>(ctx, p, a16, kp, status, stream);
+    return;
+  }
   if (tile_n >= 256) launch_t<256>(ctx, p, status, stream);
   else if (tile_n >= 128) launch_t<128>(ctx, p, status, stream);
   else launch_t<64>(ctx, p, status, stream);

@@ -478,8 +478,11 @@ class Executor {
   RunStats argmax(const Tensor &in, const PosCell &result);
   RunStats embed_gather(const PosCell &token, const Tensor &table, const Tensor &out);
   RunStats embed_gather_rows(const TokenIds &tokens, const Tensor &table, const Tensor &out);
+  // scratch an op wants in its slot beyond split-K planes (the f16 copy of A for the f16w tensor-core GEMM)
+  size_t op_scratch_bytes(const ResolvedMatmul &r, const Route &route) const;
   bool gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route, GemvParams *out) const;
-  std::vector<Launch> plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops, size_t *n_calls) const;
+  std::vector<Launch> plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops, size_t *n_calls,
+                                    size_t *scratch_bytes = nullptr) const;
   RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
                        const Tensor *norm_w, float eps);
   void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
@@ -566,8 +569,10 @@ bool gemm_tf32x3_pair_supported(const GemmParams &p, int sm_count);
 void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStream_t stream);
 bool gemm_f16w_umma_eligible(const GemmParams &p);
 uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_count);
+size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k);
+// scratch (may be null): room for the f16 copy of A; without it A is converted inside the kernel
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
-                           cudaStream_t stream);
+                           void *scratch, size_t scratch_bytes, cudaStream_t stream);
 void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
                         cudaStream_t stream);
 void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream);

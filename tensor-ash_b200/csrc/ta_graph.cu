@@ -421,7 +421,7 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
 // dispatches (HazardCursor, src/executor/graph_ops.rs:587-624); here a launch
 // boundary is the barrier, so independent ops share a launch instead.
 std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops,
-                                            size_t *n_calls) const {
+                                            size_t *n_calls, size_t *scratch_bytes) const {
   struct Cand {
     bool gemv = false;
     GemvParams g{};
@@ -435,6 +435,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     const Route route = plan_op(o.mm, r, false);
     c.gemv = gemv_params_for(o.mm, r, route, &c.g);
     c.flops = r.total_flops;
+    if (scratch_bytes) *scratch_bytes = std::max(*scratch_bytes, op_scratch_bytes(r, route));
     return c;
   };
   auto writes = [](const GemvParams &g) -> const void * { return g.store_kind >= 2 ? g.dst : (const void *)g.c; };
@@ -529,10 +530,12 @@ RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
   if (ops.empty()) return RunStats{std::nullopt, 0, 0};
   uint64_t flops = 0;
   size_t n_calls = 0;
-  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls);
+  size_t scratch_bytes = 0;
+  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls, &scratch_bytes);
   ctx_->make_current();
   Slot &slot = checkout_slot();
   SlotGuard g(*this, slot);
+  if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
   return timed(slot, n_calls, flops, [&](cudaStream_t st) {
     for (const Launch &l : plan) l(slot, st);
   });
@@ -545,7 +548,9 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
   exec.context()->make_current();
   auto prep = std::make_unique<PreparedOps>();
   prep->exec = &exec;
-  std::vector<Launch> plan = exec.plan_exec_ops(ops, &prep->total_flops, &prep->n_calls);
+  size_t scratch_bytes = 0;
+  std::vector<Launch> plan = exec.plan_exec_ops(ops, &prep->total_flops, &prep->n_calls, &scratch_bytes);
+  if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));
   TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
   TA_CUDA(cudaEventCreate(&prep->ev_begin));
   TA_CUDA(cudaEventCreate(&prep->ev_end));
@@ -557,6 +562,8 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
     // the captured launches must not point at state another submission may use later
     Slot slot = real_slot;
     slot.counters = prep->counters;
+    slot.scratch = prep->scratch;
+    slot.scratch_bytes = scratch_bytes;
     // Run once eagerly: first-use set-up (function attributes, tensor maps) must
     // not happen inside the capture, and it proves the batch launches at all.
     for (const Launch &l : plan) l(slot, prep->stream);

@@ -404,6 +404,14 @@ GemmParams make_params(const MatmulOp &op, const ResolvedMatmul &r) {
 }
 }  // namespace
 
+// The f16w tensor-core GEMM rounds A to f16 once per launch when its slot has room for the copy
+// (ops of one submission run in stream order, so they share the region); capped at 256 MiB.
+size_t Executor::op_scratch_bytes(const ResolvedMatmul &r, const Route &route) const {
+  if (route.kernel < 0 || KERNEL_SPECS[route.kernel].family != Family::F16wUmma || route.splits > 1) return 0;
+  const size_t need = gemm_f16w_umma_scratch_bytes(r.batch_stride_a ? r.batch : 1, r.m, r.k);
+  return need <= (256ull << 20) ? need : 0;
+}
+
 // GEMV launch description of an op on the row-GEMV route; false when the route is another family.
 bool Executor::gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route,
                                GemvParams *out) const {
@@ -473,7 +481,7 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
       return;
     case Family::F16wUmma:
       if (gemm_f16w_umma_eligible(p)) {
-        launch_gemm_f16w_umma(*ctx_, p, spec.tile_n, slot.status, stream);
+        launch_gemm_f16w_umma(*ctx_, p, spec.tile_n, slot.status, slot.scratch, slot.scratch_bytes, stream);
         return;
       }
       launch_gemm_ffma(p, (r.m >= 128 && r.n >= 128) ? 128 : 64, stream);  // alignment demotion
@@ -556,6 +564,7 @@ RunStats Executor::run_ops_impl(const std::vector<MatmulOp> &ops, bool graph) {
     if (routes.back().splits > 1)
       scratch_bytes = std::max(scratch_bytes, (size_t)resolved[i].batch * routes.back().splits *
                                                   resolved[i].m * resolved[i].n * 4);
+    scratch_bytes = std::max(scratch_bytes, op_scratch_bytes(resolved[i], routes.back()));
   }
   Slot &slot = checkout_slot();
   SlotGuard g(*this, slot);
@@ -768,11 +777,17 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
   TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
   TA_CUDA(cudaEventCreate(&prep->ev_begin));
   TA_CUDA(cudaEventCreate(&prep->ev_end));
+  size_t scratch_bytes = 0;
+  for (size_t i = 0; i < ops.size(); ++i) scratch_bytes = std::max(scratch_bytes, exec.op_scratch_bytes(resolved[i], routes[i]));
+  if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));
   // Tensor maps and attribute setup happen on first launch of each kernel: run
   // the batch once eagerly so capture sees only launches.
-  Slot &slot = exec.checkout_slot();
+  Slot &real_slot = exec.checkout_slot();
   {
-    SlotGuard g(exec, slot);
+    SlotGuard g(exec, real_slot);
+    Slot slot = real_slot;            // captured launches must point at this object's own scratch
+    slot.scratch = prep->scratch;
+    slot.scratch_bytes = scratch_bytes;
     TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
     try {
       for (size_t i = 0; i < ops.size(); ++i)
@@ -798,6 +813,7 @@ PreparedOps::~PreparedOps() {
   if (ev_end) cudaEventDestroy(ev_end);
   if (stream) cudaStreamDestroy(stream);
   if (counters) cudaFree(counters);
+  if (scratch) cudaFree(scratch);
 }
 
 void PreparedOps::submit() {
