@@ -273,6 +273,7 @@ def bench_gemv(ta, ctx, peaks: dict, reps: int = 30) -> dict:
         bytes_pass = 2 * 2 * k * n + 2 * n * k + 4 * m * (k + n) + 4 * m * (n + k) + 4 * m * n
         res[f"M={m}"] = {"us_per_mlp_pass": med * 1e6, "gbs": bytes_pass / med / 1e9,
                          "hbm_frac": bytes_pass / med / 1e9 / peaks["hbm_gbs"]}
+        prep.close()
     ex.close()
     return {"config": "configs[2]: decode MLP 4096x11008 packed f16 weights, gate+up fused, then down", **res}
 

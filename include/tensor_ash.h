@@ -386,11 +386,16 @@ int ta_token_ids_set(ta_token_ids *ids, const uint32_t *tokens, uint32_t n); /* 
  *   EMBED_GATHER      cell = token id word; in0 table [vocab, embd] (f32/f16), out [embd]
  *   EMBED_GATHER_ROWS tokens; in0 table, out [n, embd]
  *   ALL_REDUCE        out = f32 tensor summed in place over the ranks of comm
- *   ALL_GATHER        in0 [n] f32 of every rank -> out [world * n] in rank order; comm */
+ *   ALL_GATHER        in0 [n] f32 of every rank -> out [world * n] in rank order; comm
+ *   PREFILL_QKV_PACK  in0 qkv [T, H*dh + 2*H_kv*dh] f32, in1 rope table, out q [H, T, dh] f32 (RoPE),
+ *                     in2 kt cache [H_kv, dh, T_max] (RoPE'd k at positions rope.pos_base + t),
+ *                     in3 v cache [H_kv, T_max, dh]; caches f32 or f16; rope = {H, dh, rot_dim,
+ *                     pos_base}, u0 = H_kv (run_prefill_qkv_pack in the reference) */
 enum {
   TA_EXEC_MATMUL = 0, TA_EXEC_RMS_NORM, TA_EXEC_LAYER_NORM, TA_EXEC_SOFTMAX_ROWS, TA_EXEC_ROPE,
   TA_EXEC_ROPE_SCATTER, TA_EXEC_COPY_STRIDED, TA_EXEC_BINARY, TA_EXEC_ATTN_DECODE, TA_EXEC_FLASH_ATTN,
-  TA_EXEC_ARGMAX, TA_EXEC_EMBED_GATHER, TA_EXEC_EMBED_GATHER_ROWS, TA_EXEC_ALL_REDUCE, TA_EXEC_ALL_GATHER
+  TA_EXEC_ARGMAX, TA_EXEC_EMBED_GATHER, TA_EXEC_EMBED_GATHER_ROWS, TA_EXEC_ALL_REDUCE, TA_EXEC_ALL_GATHER,
+  TA_EXEC_PREFILL_QKV_PACK
 };
 
 /* Communicator for tensor-parallel graphs: one rank per process and GPU, NCCL over
@@ -450,7 +455,10 @@ uint32_t ta_default_num_k_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_
                                  uint32_t tile_m, uint32_t tile_n);
 uint32_t ta_heuristic_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
 
-/* Bit-exact software conversions (ref src/dtype.rs:42-112).  Host-only. */
+/* Software conversions (ref src/dtype.rs:42-112): round-to-nearest-even encode and IEEE binary16
+ * decode, bit-exact with the reference on every pattern except subnormal halves, where the
+ * reference's decode (dtype.rs:93-99) normalises one bit too far and this one returns the IEEE
+ * value the device's own f16 loads see.  Host-only. */
 uint16_t ta_f32_to_f16_bits(float value);
 float ta_f16_bits_to_f32(uint16_t bits);
 

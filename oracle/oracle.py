@@ -49,6 +49,8 @@ def lib():
     L.tao_f32_to_f16_bits.restype = C.c_uint16
     L.tao_f16_bits_to_f32.argtypes = [C.c_uint16]
     L.tao_f16_bits_to_f32.restype = C.c_float
+    L.tao_f16_bits_to_f32_reference.argtypes = [C.c_uint16]
+    L.tao_f16_bits_to_f32_reference.restype = C.c_float
     L.tao_round_via_f16.argtypes = [C.c_float]
     L.tao_round_via_f16.restype = C.c_float
     L.tao_round_via_f16_array.argtypes = [_f32p, C.c_size_t]
@@ -128,6 +130,11 @@ def f32_to_f16_bits(v: float) -> int:
 
 def f16_bits_to_f32(b: int) -> np.float32:
     return np.float32(lib().tao_f16_bits_to_f32(b))
+
+
+def f16_bits_to_f32_reference(b: int) -> np.float32:
+    """The reference's host decode, bit for bit (differs from IEEE on subnormal halves only)."""
+    return np.float32(lib().tao_f16_bits_to_f32_reference(b))
 
 
 def round_via_f16(x):

@@ -111,12 +111,17 @@ TAO_API uint16_t tao_f32_to_f16_bits(float value) {
   return sign;
 }
 
-TAO_API float tao_f16_bits_to_f32(uint16_t h) {
+/* src/dtype.rs:87-105.  IEEE binary16 decode, which is what the device's own f16 loads do.
+ * On subnormal halves the reference's host decode normalises with a shift one too large
+ * (leading_zeros() - 21 on a 10-bit field, dtype.rs:95-97), returning a wrong value for the
+ * 1023 * 2 patterns below 2^-14; tao_f16_bits_to_f32_reference restates that behaviour
+ * exactly, and this function is the IEEE decode the parity tests check tensors against. */
+static float tao_decode_half(uint16_t h, uint32_t field_bias) {
   uint32_t sign = ((uint32_t)(h & 0x8000u)) << 16;
   uint32_t exp = (h >> 10) & 0x1fu, mant = h & 0x03ffu, out;
   if (exp == 0 && mant == 0) out = sign;
   else if (exp == 0) {
-    uint32_t shift = (uint32_t)__builtin_clz(mant) - 21;
+    uint32_t shift = (uint32_t)__builtin_clz(mant) - field_bias;
     uint32_t m = (mant << (shift + 1)) & 0x03ffu;
     uint32_t e = 127 - 15 - shift;
     out = sign | (e << 23) | (m << 13);
@@ -124,6 +129,10 @@ TAO_API float tao_f16_bits_to_f32(uint16_t h) {
   else out = sign | ((exp + 127 - 15) << 23) | (mant << 13);
   return bits_f32(out);
 }
+
+TAO_API float tao_f16_bits_to_f32(uint16_t h) { return tao_decode_half(h, 22); }
+
+TAO_API float tao_f16_bits_to_f32_reference(uint16_t h) { return tao_decode_half(h, 21); }
 
 TAO_API float tao_round_via_f16(float v) { return tao_f16_bits_to_f32(tao_f32_to_f16_bits(v)); }
 

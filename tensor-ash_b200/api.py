@@ -377,6 +377,7 @@ class ExecKind(enum.IntEnum):
     EMBED_GATHER_ROWS = 12
     ALL_REDUCE = 13
     ALL_GATHER = 14
+    PREFILL_QKV_PACK = 15
 
 
 class ExecOp:
@@ -477,6 +478,12 @@ class ExecOp:
     @classmethod
     def embed_gather_rows(cls, tokens, table, out):
         return cls(ExecKind.EMBED_GATHER_ROWS, tokens=tokens, in0=table, out=out)
+
+    @classmethod
+    def prefill_qkv_pack(cls, qkv, table, q, kt, v, heads, kv_heads, head_dim, rot_dim, pos_base=0):
+        """RoPE(q) head-major, RoPE(k) into the Kt cache, v into the V cache, from one [T, n_qkv] row."""
+        return cls(ExecKind.PREFILL_QKV_PACK, in0=qkv, in1=table, in2=kt, in3=v, out=q,
+                   rope=(heads, head_dim, rot_dim, pos_base), u0=kv_heads)
 
     @classmethod
     def all_reduce(cls, tensor, comm):

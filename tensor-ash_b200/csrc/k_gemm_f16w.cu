@@ -464,7 +464,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
 
 template <int BN>
 void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t kp, uint32_t *status,
-                  cudaStream_t stream) {
+                  bool a16_ready, cudaStream_t stream) {
   using C = PreCfg<BN>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx.device & 63]) {
@@ -474,9 +474,11 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
   const uint64_t rows = ba * p.m;
   const uint64_t items = rows * (kp / 8);
-  convert_a_f16_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(static_cast<const float *>(p.a), a16, p.k, kp, rows);
-  TA_CUDA(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!a16_ready) {
+    convert_a_f16_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(static_cast<const float *>(p.a), a16, p.k, kp, rows);
+    TA_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
   CUtensorMap map_a, map_b;
   // A16 [ba, M, Kp] f16: 128-byte rows of 64 halves, 128-byte swizzle; columns >= K read as zero (TMA bound K)
   encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a16, p.k, p.m, ba, (uint64_t)kp * 2,
@@ -556,7 +558,7 @@ size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
 }
 
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
-                           void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+                           void *scratch, size_t scratch_bytes, bool a16_ready, cudaStream_t stream) {
   if (!gemm_f16w_umma_eligible(p))
     fail("f16w tensor-core GEMM needs f32 A, f16 B, K %% 4 == 0 and N %% 8 == 0");
   const uint32_t batch_a = p.stride_a ? p.batch : 1;
@@ -565,9 +567,9 @@ void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t til
       (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0 && !(env && env[0] == '0')) {
     const uint32_t kp = (p.k + 7u) & ~7u;
     __half *a16 = static_cast<__half *>(scratch);
-    if (tile_n >= 256) launch_pre_t<256>(ctx, p, a16, kp, status, stream);
-    else if (tile_n >= 128) launch_pre_t<128>(ctx, p, a16, kp, status, stream);
-    else launch_pre_t<64>(ctx, p, a16, kp, status, stream);
+    if (tile_n >= 256) launch_pre_t<256>(ctx, p, a16, kp, status, a16_ready, stream);
+    else if (tile_n >= 128) launch_pre_t<128>(ctx, p, a16, kp, status, a16_ready, stream);
+    else launch_pre_t<64>(ctx, p, a16, kp, status, a16_ready, stream);
     return;
   }
   if (tile_n >= 256) launch_t<256>(ctx, p, status, stream);

@@ -254,6 +254,49 @@ __global__ void rope_scatter_kernel(const float *__restrict__ in, const float *_
   dst[d + s2] = cvt_store<TD>(r1);
 }
 
+// Fused wide-prefill QKV pack (ExecOp::PrefillQkvPack / run_prefill_qkv_pack of the reference,
+// src/executor/elementwise/flash.rs:255-330, here with f32 activations): from one
+// concatenated row [T, H*dh + 2*H_kv*dh] it writes RoPE(q) head-major [H, T, dh], RoPE(k)
+// into the Kt cache [H_kv, dh, T_max] at positions pos_base + t and v into the V cache
+// [H_kv, T_max, dh].  One thread per interleaved pair; the rotation is the rope kernel's.
+template <typename TKV>
+__global__ void prefill_qkv_pack_kernel(const float *__restrict__ qkv, const float *__restrict__ table,
+                                        float *__restrict__ q, TKV *__restrict__ kt, TKV *__restrict__ v,
+                                        uint32_t tokens, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                                        uint32_t rot_dim, uint32_t pos_base, uint32_t t_max) {
+  const uint32_t half_dim = head_dim / 2, all_heads = heads + 2 * kv_heads;
+  const uint64_t total = (uint64_t)tokens * all_heads * half_dim;
+  const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const uint32_t i = (uint32_t)(idx % half_dim);
+  const uint64_t vec = idx / half_dim;
+  const uint32_t t = (uint32_t)(vec / all_heads), h = (uint32_t)(vec % all_heads);
+  const size_t src = (size_t)t * all_heads * head_dim + (size_t)h * head_dim + 2 * i;
+  float r0 = qkv[src], r1 = qkv[src + 1];
+  const bool is_v = h >= heads + kv_heads;
+  if (!is_v && 2 * i < rot_dim) {
+    const float *cs = table + ((size_t)(pos_base + t) * (rot_dim / 2) + i) * 2;
+    const float x0 = r0, x1 = r1;
+    r0 = fmaf(x0, cs[0], -x1 * cs[1]);
+    r1 = fmaf(x0, cs[1], x1 * cs[0]);
+  }
+  if (h < heads) {
+    float *dst = q + ((size_t)h * tokens + t) * head_dim + 2 * i;
+    dst[0] = r0;
+    dst[1] = r1;
+  } else if (!is_v) {
+    const uint32_t kh = h - heads;
+    TKV *dst = kt + ((size_t)kh * head_dim + 2 * i) * t_max + pos_base + t;
+    dst[0] = cvt_store<TKV>(r0);
+    dst[t_max] = cvt_store<TKV>(r1);
+  } else {
+    const uint32_t kh = h - heads - kv_heads;
+    TKV *dst = v + ((size_t)kh * t_max + pos_base + t) * head_dim + 2 * i;
+    dst[0] = cvt_store<TKV>(r0);
+    dst[1] = cvt_store<TKV>(r1);
+  }
+}
+
 inline void launched() {
   TA_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -351,6 +394,20 @@ void launch_rope_scatter(const float *in, const float *table, void *dst, bool ds
     rope_scatter_kernel<<<blocks, 256, 0, stream>>>(in, table, (float *)dst, tokens, heads, head_dim, rot_dim,
                                                     pos_base, dst_off, strides[0], strides[1], strides[2],
                                                     pos_scale, pos_ptr);
+  launched();
+}
+
+void launch_prefill_qkv_pack(const float *qkv, const float *table, float *q, void *kt, void *v, bool kv_f16,
+                             uint32_t tokens, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                             uint32_t rot_dim, uint32_t pos_base, uint32_t t_max, cudaStream_t stream) {
+  const uint64_t total = (uint64_t)tokens * (heads + 2 * kv_heads) * (head_dim / 2);
+  const uint32_t blocks = (uint32_t)((total + 255) / 256);
+  if (kv_f16)
+    prefill_qkv_pack_kernel<<<blocks, 256, 0, stream>>>(qkv, table, q, (__half *)kt, (__half *)v, tokens, heads,
+                                                        kv_heads, head_dim, rot_dim, pos_base, t_max);
+  else
+    prefill_qkv_pack_kernel<<<blocks, 256, 0, stream>>>(qkv, table, q, (float *)kt, (float *)v, tokens, heads,
+                                                        kv_heads, head_dim, rot_dim, pos_base, t_max);
   launched();
 }
 

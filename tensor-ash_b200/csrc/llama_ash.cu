@@ -436,11 +436,10 @@ ExecOp copy_op(const Tensor &src, const Tensor &dst, std::array<uint32_t, 3> ext
   return o;
 }
 
-// forward/prefill.rs:89-291 (f32 activations, composed QKV split, fused flash).
+// forward/prefill.rs:89-291 (f32 activations, fused QKV pack, fused flash).
 std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint32_t pos_base) {
   const ta_llama_config &c = m.cfg;
-  const uint32_t heads = m.heads_l, kv = m.kv_l, dh = c.head_dim, t_max = c.t_max, embd = c.embd;
-  const uint32_t q_w = m.q_w, kv_dim = kv * dh, n_qkv = q_w + 2 * kv_dim;
+  const uint32_t heads = m.heads_l, kv = m.kv_l, dh = c.head_dim, embd = c.embd;
   std::vector<ExecOp> ops;
   {
     ExecOp g;
@@ -455,23 +454,18 @@ std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint
     n.in0 = x_in; n.in1 = &L.attn_norm; n.out = &s.xn; n.f0 = c.rms_eps;
     ops.push_back(n);
     ops.push_back(mm_op(s.xn, L.w_qkv, s.qkv));
-    ops.push_back(copy_op(s.qkv, s.q, {q_w, t, 1}, 0, {1, n_qkv, 0}, 0, {1, q_w, 0}));
-    ops.push_back(copy_op(s.qkv, s.k, {kv_dim, t, 1}, q_w, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
-    ops.push_back(copy_op(s.qkv, s.v, {kv_dim, t, 1}, q_w + kv_dim, {1, n_qkv, 0}, 0, {1, kv_dim, 0}));
-    for (int which = 0; which < 2; ++which) {
-      ExecOp r;
-      r.kind = ExecKind::Rope;
-      r.in0 = which ? &s.k : &s.q; r.in1 = &m.rope_table; r.out = r.in0;
-      r.heads = which ? kv : heads; r.head_dim = dh; r.rot_dim = dh; r.pos_base = pos_base;
-      ops.push_back(r);
+    {  // one launch: RoPE(q) head-major, RoPE(k) and v into the caches (forward/prefill.rs wide path)
+      ExecOp pk;
+      pk.kind = ExecKind::PrefillQkvPack;
+      pk.in0 = &s.qkv; pk.in1 = &m.rope_table; pk.out = &s.q; pk.in2 = &L.kt_cache; pk.in3 = &L.v_cache;
+      pk.heads = heads; pk.u0 = kv; pk.head_dim = dh; pk.rot_dim = dh; pk.pos_base = pos_base;
+      ops.push_back(pk);
     }
-    ops.push_back(copy_op(s.k, L.kt_cache, {dh, kv, t}, 0, {1, dh, kv * dh}, pos_base, {t_max, dh * t_max, 1}));
-    ops.push_back(copy_op(s.v, L.v_cache, {dh, kv, t}, 0, {1, dh, kv * dh}, pos_base * dh, {1, t_max * dh, dh}));
     ExecOp f;
     f.kind = ExecKind::FlashAttn;
     f.in0 = &s.q; f.in1 = &L.kt_cache; f.in2 = &L.v_cache; f.out = &s.attn_flat;
     f.flash.kv_len = pos_base + t; f.flash.pos_base = pos_base; f.flash.scale = 1.0f / std::sqrt((float)dh);
-    f.flash.token_major_heads = heads;
+    f.flash.out_token_major_heads = heads;   // head-major q, token-major out: Wo-ready
     ops.push_back(f);
     push_mlp_ops(m, ops, L, false, s.attn_flat, s.o, s.on, s.up, s.gate, *x_in, *x_out);
     std::swap(x_in, x_out);
@@ -511,6 +505,7 @@ PrefillScratch prefill_view(ta_llama &m, uint32_t n) {
   s.x_a = rows(full.x_a, c.embd); s.x_b = rows(full.x_b, c.embd); s.xn = rows(full.xn, c.embd);
   s.qkv = rows(full.qkv, m.q_w + 2 * kv_dim);
   s.q = rows(full.q, m.q_w); s.k = rows(full.k, kv_dim); s.v = rows(full.v, kv_dim);
+  s.q.shape = {m.heads_l, n, c.head_dim};   // head-major [H, T, dh] over the same n * q_w floats
   s.attn_flat = rows(full.attn_flat, m.q_w); s.o = rows(full.o, c.embd); s.on = rows(full.on, c.embd);
   s.up = rows(full.up, m.ffn_l); s.gate = rows(full.gate, m.ffn_l);
   s.last = full.last; s.last_n = full.last_n;

@@ -147,6 +147,7 @@ struct MatmulOp {
   float normed_eps = 0.0f;
   MatmulStore store;
   bool packed_b = false;
+  bool a16_ready = false;   // planner-internal: the slot scratch already holds this A rounded to f16
 };
 
 struct RunStats {
@@ -360,7 +361,7 @@ struct TokenIds {
 //   EmbedGatherRows  tokens; in0 table, out [n, embd]
 enum class ExecKind : uint32_t {
   Matmul = 0, RmsNorm, LayerNorm, SoftmaxRows, Rope, RopeScatter, CopyStrided, Binary, AttnDecode,
-  FlashAttn, Argmax, EmbedGather, EmbedGatherRows, AllReduce, AllGather
+  FlashAttn, Argmax, EmbedGather, EmbedGatherRows, AllReduce, AllGather, PrefillQkvPack
 };
 
 // ------------------------------------------------------------------ communicator (tensor parallel)
@@ -541,7 +542,8 @@ void validate_op_tensors(const Executor &e, const MatmulOp &op);
 
 // Record-once / replay-many op batch (src/executor/prepared.rs:46-353).
 struct PreparedOps {
-  Executor *exec = nullptr;
+  Executor *exec = nullptr;            // must outlive submit()/wait(); not needed to destroy
+  std::shared_ptr<Context> ctx;        // keeps the device alive for the destructor
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
   cudaStream_t stream = nullptr;
@@ -571,8 +573,9 @@ bool gemm_f16w_umma_eligible(const GemmParams &p);
 uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_count);
 size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k);
 // scratch (may be null): room for the f16 copy of A; without it A is converted inside the kernel
+// a16_ready: the scratch already holds this A (same pointer, M, K) from the launch just before
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
-                           void *scratch, size_t scratch_bytes, cudaStream_t stream);
+                           void *scratch, size_t scratch_bytes, bool a16_ready, cudaStream_t stream);
 void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
                         cudaStream_t stream);
 void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream);
@@ -608,6 +611,9 @@ void launch_binary(const float *a, const float *b, float *out, uint32_t n, uint3
 void launch_argmax(const float *in, uint32_t n, uint32_t *result, cudaStream_t stream);
 void launch_embed_gather(const uint32_t *tokens, uint32_t n_tokens, const void *table, bool table_f16,
                          float *out, uint32_t embd, uint32_t vocab, cudaStream_t stream);
+void launch_prefill_qkv_pack(const float *qkv, const float *table, float *q, void *kt, void *v, bool kv_f16,
+                             uint32_t tokens, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
+                             uint32_t rot_dim, uint32_t pos_base, uint32_t t_max, cudaStream_t stream);
 void launch_rope_scatter(const float *in, const float *table, void *dst, bool dst_f16, uint32_t tokens,
                          uint32_t heads, uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base,
                          uint32_t dst_off, const uint32_t strides[3], uint32_t pos_scale,

@@ -377,6 +377,44 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       float *op = (float *)out.ptr();
       return [=](Slot &, cudaStream_t st) { launch_embed_gather(tp, n_tokens, tab, tf16, op, embd, vocab, st); };
     }
+    case ExecKind::PrefillQkvPack: {
+      const char *nm = "run_prefill_qkv_pack";
+      const Tensor &qkv = need(o.in0, nm, "qkv"), &tab = need(o.in1, nm, "table"), &q = need(o.out, nm, "q"),
+                   &kt = need(o.in2, nm, "kt"), &v = need(o.in3, nm, "v");
+      ensure_f32(*this, qkv, nm, "qkv");
+      ensure_f32(*this, tab, nm, "table");
+      ensure_f32(*this, q, nm, "q");
+      validate_tensor(kt, "kt");
+      validate_tensor(v, "v");
+      if (kt.dtype != v.dtype) fail("%s: kt (%s) and v (%s) must share a storage type", nm, dtype_name(kt.dtype), dtype_name(v.dtype));
+      const uint32_t heads = o.heads, kv_heads = o.u0, dh = o.head_dim, rot = o.rot_dim;
+      if (!heads || !kv_heads || !dh || !rot || (rot & 1u) || rot > dh || (dh & 1u))
+        fail("%s: invalid heads/kv_heads/dh/rot_dim (%u/%u/%u/%u)", nm, heads, kv_heads, dh, rot);
+      if (qkv.shape.size() != 2) fail("%s: qkv must be [T, n_qkv], got %s", nm, qkv.shape_str().c_str());
+      const uint32_t tokens = qkv.shape[0], want = heads * dh + 2 * kv_heads * dh;
+      if (qkv.shape[1] != want) fail("%s: qkv N %u != H*dh + 2*H_kv*dh (%u)", nm, qkv.shape[1], want);
+      if (q.shape != std::vector<uint32_t>{heads, tokens, dh})
+        fail("%s: q must be head-major [H=%u, T=%u, dh=%u], got %s", nm, heads, tokens, dh, q.shape_str().c_str());
+      if (kt.shape.size() != 3 || kt.shape[0] != kv_heads || kt.shape[1] != dh)
+        fail("%s: kt must be [H_kv, dh, T_max], got %s", nm, kt.shape_str().c_str());
+      const uint32_t t_max = kt.shape[2];
+      if (v.shape != std::vector<uint32_t>{kv_heads, t_max, dh})
+        fail("%s: v must be [H_kv=%u, T_max=%u, dh=%u], got %s", nm, kv_heads, t_max, dh, v.shape_str().c_str());
+      if ((uint64_t)o.pos_base + tokens > t_max)
+        fail("%s: pos_base %u + T %u exceeds cache T_max %u", nm, o.pos_base, tokens, t_max);
+      if (tab.len() < (uint64_t)(o.pos_base + tokens) * rot)
+        fail("%s: rope table holds %llu values, positions up to %u need %llu", nm, (unsigned long long)tab.len(),
+             o.pos_base + tokens, (unsigned long long)(o.pos_base + tokens) * rot);
+      if (q.ptr() == qkv.ptr()) fail("%s: q and qkv must be different tensors", nm);
+      const float *sp = (const float *)qkv.ptr(), *tp = (const float *)tab.ptr();
+      float *qp = (float *)q.ptr();
+      void *kp = kt.ptr(), *vp = v.ptr();
+      const bool f16 = kt.dtype == DType::F16;
+      const uint32_t pb = o.pos_base;
+      return [=](Slot &, cudaStream_t st) {
+        launch_prefill_qkv_pack(sp, tp, qp, kp, vp, f16, tokens, heads, kv_heads, dh, rot, pb, t_max, st);
+      };
+    }
     case ExecKind::AllReduce: {
       const Tensor &t = need(o.out, "run_all_reduce", "tensor");
       ensure_f32(*this, t, "run_all_reduce", "tensor");
@@ -452,6 +490,17 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     Cand c0 = candidate(ops[i]);
     if (!c0.gemv) {
       ExecOp op = ops[i];
+      // two f16w tensor-core GEMMs in a row on the same A (up and gate of a prefill MLP): the f16
+      // copy of A made for the first is still in the slot scratch when the second runs
+      if (op.kind == ExecKind::Matmul && i > 0 && ops[i - 1].kind == ExecKind::Matmul) {
+        const MatmulOp &prev = ops[i - 1].mm;
+        const ResolvedMatmul rp = ResolvedMatmul::from_op(prev), rc = ResolvedMatmul::from_op(op.mm);
+        const Route routep = plan_op(prev, rp, false), routec = plan_op(op.mm, rc, false);
+        if (op_scratch_bytes(rp, routep) && op_scratch_bytes(rc, routec) && prev.call.a->ptr() == op.mm.call.a->ptr() &&
+            rp.m == rc.m && rp.k == rc.k && rp.batch == rc.batch && rp.batch_stride_a == rc.batch_stride_a &&
+            prev.call.c->ptr() != op.mm.call.a->ptr())
+          op.mm.a16_ready = true;
+      }
       if (op.kind == ExecKind::AttnDecode) {
         // Decode attention may read the cache ahead of its dependency wait when the launch
         // before it (the only one that can still be running then) appends nothing but
@@ -548,6 +597,7 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
   exec.context()->make_current();
   auto prep = std::make_unique<PreparedOps>();
   prep->exec = &exec;
+  prep->ctx = exec.context();
   size_t scratch_bytes = 0;
   std::vector<Launch> plan = exec.plan_exec_ops(ops, &prep->total_flops, &prep->n_calls, &scratch_bytes);
   if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));

@@ -90,7 +90,7 @@ float f16_bits_to_f32(uint16_t h) {
   const uint32_t frac = h & 0x03ffu;
   if (exp == 0) {
     if (frac == 0) return float_of(sign);
-    const uint32_t lz = (uint32_t)__builtin_clz(frac) - 21;  // leading zeros within 10 bits
+    const uint32_t lz = (uint32_t)__builtin_clz(frac) - 22;  // leading zeros within 10 bits
     return float_of(sign | ((127 - 15 - lz) << 23) | (((frac << (lz + 1)) & 0x03ffu) << 13));
   }
   if (exp == 0x1f) return float_of(sign | (frac ? 0x7fc00000u | (frac << 13) : 0x7f800000u));

@@ -481,7 +481,7 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
       return;
     case Family::F16wUmma:
       if (gemm_f16w_umma_eligible(p)) {
-        launch_gemm_f16w_umma(*ctx_, p, spec.tile_n, slot.status, slot.scratch, slot.scratch_bytes, stream);
+        launch_gemm_f16w_umma(*ctx_, p, spec.tile_n, slot.status, slot.scratch, slot.scratch_bytes, op.a16_ready, stream);
         return;
       }
       launch_gemm_ffma(p, (r.m >= 128 && r.n >= 128) ? 128 : 64, stream);  // alignment demotion
@@ -765,6 +765,7 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
   exec.context()->make_current();
   auto prep = std::make_unique<PreparedOps>();
   prep->exec = &exec;
+  prep->ctx = exec.context();
   std::vector<ResolvedMatmul> resolved;
   std::vector<Route> routes;
   for (const MatmulOp &op : ops) {
@@ -805,7 +806,8 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
 }
 
 PreparedOps::~PreparedOps() {
-  if (exec) cudaSetDevice(exec->context()->device);
+  // the executor may already be gone (handles are destroyed in any order): only the context is touched here
+  if (ctx) cudaSetDevice(ctx->device);
   if (stream) cudaStreamSynchronize(stream);  // wait for in-flight work
   if (graph_exec) cudaGraphExecDestroy(graph_exec);
   if (graph) cudaGraphDestroy(graph);

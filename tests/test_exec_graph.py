@@ -134,6 +134,78 @@ def test_copy_strided_f32_to_f16_rounds_to_nearest_even(gpu, orc):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_prefill_qkv_pack_equals_the_composed_split_rope_and_cache_writes(gpu, orc, kv_f16):
+    """One launch against the seven-op composition it replaces (three strided splits, two
+    RoPE passes, two cache copies): bit-identical q and caches, and both against numpy."""
+    ta, ctx, ex = gpu
+    heads, kv, dh, t_max, t, pos0 = 4, 2, 64, 40, 9, 11
+    q_w, kv_w = heads * dh, kv * dh
+    n_qkv = q_w + 2 * kv_w
+    qkv = orc.fill_det(t * n_qkv, 17).reshape(t, n_qkv)
+    table = rope_table(t_max, dh // 2)
+    tqkv, tt = up(ta, ctx, ex, qkv), up(ta, ctx, ex, table)
+    mk = ta.Tensor.uninit_device_f16 if kv_f16 else ta.Tensor.uninit_device
+
+    def caches():
+        kt, v = mk(ctx, [kv, dh, t_max]), mk(ctx, [kv, t_max, dh])
+        ex.upload(np.zeros(kv * dh * t_max, dtype=np.float32), kt)
+        ex.upload(np.zeros(kv * dh * t_max, dtype=np.float32), v)
+        return kt, v
+
+    kt1, v1 = caches()
+    q1 = ta.Tensor.uninit_device(ctx, [heads, t, dh])
+    ex.run_exec_ops([ta.ExecOp.prefill_qkv_pack(tqkv, tt, q1, kt1, v1, heads, kv, dh, dh, pos0)])
+
+    kt2, v2 = caches()
+    q2 = ta.Tensor.uninit_device(ctx, [t, q_w])
+    k2 = ta.Tensor.uninit_device(ctx, [t, kv_w])
+    vv2 = ta.Tensor.uninit_device(ctx, [t, kv_w])
+    E = ta.ExecOp
+    ex.run_exec_ops([
+        E.copy_strided(tqkv, q2, [q_w, t, 1], 0, [1, n_qkv, 0], 0, [1, q_w, 0]),
+        E.copy_strided(tqkv, k2, [kv_w, t, 1], q_w, [1, n_qkv, 0], 0, [1, kv_w, 0]),
+        E.copy_strided(tqkv, vv2, [kv_w, t, 1], q_w + kv_w, [1, n_qkv, 0], 0, [1, kv_w, 0]),
+        E.rope(q2, tt, q2, heads, dh, dh, pos0),
+        E.rope(k2, tt, k2, kv, dh, dh, pos0),
+        E.copy_strided(k2, kt2, [dh, kv, t], 0, [1, dh, kv * dh], pos0, [t_max, dh * t_max, 1]),
+        E.copy_strided(vv2, v2, [dh, kv, t], 0, [1, dh, kv * dh], pos0 * dh, [1, t_max * dh, dh]),
+    ])
+    got_q = ex.download(q1).reshape(heads, t, dh)
+    np.testing.assert_array_equal(got_q, ex.download(q2).reshape(t, heads, dh).transpose(1, 0, 2))
+    np.testing.assert_array_equal(ex.download(kt1).ravel(), ex.download(kt2).ravel())
+    np.testing.assert_array_equal(ex.download(v1).ravel(), ex.download(v2).ravel())
+
+    want_q = rope_host(qkv[:, :q_w], table, heads, dh, pos0).reshape(t, heads, dh).transpose(1, 0, 2)
+    np.testing.assert_allclose(got_q, want_q, rtol=2e-6, atol=2e-7)
+    want_k = np.zeros((kv, dh, t_max))
+    want_k[:, :, pos0:pos0 + t] = rope_host(qkv[:, q_w:q_w + kv_w], table, kv, dh, pos0).reshape(t, kv, dh).transpose(1, 2, 0)
+    tol = dict(rtol=1e-3, atol=1e-6) if kv_f16 else dict(rtol=2e-6, atol=2e-7)
+    np.testing.assert_allclose(ex.download(kt1).reshape(kv, dh, t_max), want_k, **tol)
+    want_v = np.zeros((kv, t_max, dh), dtype=np.float32)
+    vsrc = qkv[:, q_w + kv_w:]
+    if kv_f16:
+        vsrc = vsrc.astype(np.float16).astype(np.float32)
+    want_v[:, pos0:pos0 + t] = vsrc.reshape(t, kv, dh).transpose(1, 0, 2)
+    np.testing.assert_array_equal(ex.download(v1).reshape(kv, t_max, dh), want_v)
+
+
+@pytest.mark.gpu
+def test_prefill_qkv_pack_rejects_inconsistent_shapes(gpu, orc):
+    ta, ctx, ex = gpu
+    heads, kv, dh, t_max, t = 4, 2, 64, 16, 4
+    n_qkv = (heads + 2 * kv) * dh
+    tqkv = up(ta, ctx, ex, np.zeros((t, n_qkv)))
+    tt = up(ta, ctx, ex, rope_table(t_max, dh // 2))
+    q = ta.Tensor.uninit_device(ctx, [heads, t, dh])
+    kt, v = ta.Tensor.uninit_device(ctx, [kv, dh, t_max]), ta.Tensor.uninit_device(ctx, [kv, t_max, dh])
+    with pytest.raises(ta.TensorAshError):   # positions run past the cache
+        ex.run_exec_ops([ta.ExecOp.prefill_qkv_pack(tqkv, tt, q, kt, v, heads, kv, dh, dh, t_max - t + 1)])
+    with pytest.raises(ta.TensorAshError):   # row width does not match the head counts
+        ex.run_exec_ops([ta.ExecOp.prefill_qkv_pack(tqkv, tt, q, kt, v, heads, kv + 1, dh, dh, 0)])
+
+
+@pytest.mark.gpu
 def test_prepared_mixed_graph_replays_with_position_cell(gpu, orc):
     """norm -> matmul(+rope scatter store through the cell) -> argmax -> gather, replayed at
     three positions from one recording."""

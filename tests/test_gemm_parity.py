@@ -284,6 +284,25 @@ def test_stats_and_dispatch_info(setup, orc):
         assert dp.split_k2 is None and not dp.kernel.startswith("split_k2_")
 
 
+@pytest.mark.gpu
+def test_prepared_handle_may_outlive_its_executor_for_destruction(setup, orc):
+    """Handles are destroyed in any order: closing the executor first must leave the prepared
+    object destroyable and no CUDA error behind for the next launch to trip over."""
+    ta, ctx, ex, _ = setup
+    ex2 = ta.Executor(ctx, 2, 4)
+    a, _ = upload_det(ta, ctx, ex, orc, (64, 64), 71)
+    b, _ = upload_det(ta, ctx, ex, orc, (64, 64), 72)
+    c = ta.Tensor.uninit_device(ctx, (64, 64))
+    prep = ex2.prepare_ops([ta.MatmulOp(ta.MatmulCall(a, b, c))])
+    prep.run()
+    want = ex.download(c)
+    ex2.close()
+    prep.close()
+    ex.upload(np.zeros(64 * 64, np.float32), c)
+    ex.run_matmuls([ta.MatmulCall(a, b, c)])      # would report a stale error if one was left
+    assert (ex.download(c) == want).all()
+
+
 # tests/correctness/replay.rs:13-21, prepared.rs
 def test_prepared_replay_is_bitwise_equal_to_direct(setup, orc):
     ta, ctx, ex, _ = setup

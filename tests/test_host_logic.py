@@ -196,6 +196,26 @@ def test_f16_conversion_bit_exact_vs_oracle(ta, orc):
     assert np.isnan(ta.f16_bits_to_f32(ta.f32_to_f16_bits(float("nan"))))
 
 
+def test_f16_decode_is_ieee_on_every_pattern(ta, orc):
+    """All 65536 halves against numpy's binary16.  The reference's host decode (src/dtype.rs:93-99)
+    is wrong on subnormal halves and only there; the library decodes them as the device does."""
+    bits = np.arange(0x10000, dtype=np.uint16)
+    want = bits.view(np.float16).astype(np.float32)
+    got = np.array([ta.f16_bits_to_f32(int(b)) for b in bits], dtype=np.float32)
+    port = np.array([orc.f16_bits_to_f32(int(b)) for b in bits], dtype=np.float32)
+    ref = np.array([orc.f16_bits_to_f32_reference(int(b)) for b in bits], dtype=np.float32)
+    finite = ~np.isnan(want)
+    assert np.array_equal(got[finite].view(np.uint32), want[finite].view(np.uint32))
+    assert np.array_equal(port[finite].view(np.uint32), want[finite].view(np.uint32))
+    assert np.isnan(got[~finite]).all() and np.isnan(port[~finite]).all()
+    subnormal = ((bits & 0x7C00) == 0) & ((bits & 0x03FF) != 0)
+    differs = ref.view(np.uint32) != want.view(np.uint32)
+    assert np.array_equal(differs & finite, subnormal)
+    # encode(decode(h)) == h for every non-NaN half
+    back = np.array([ta.f32_to_f16_bits(float(v)) for v in want[finite]], dtype=np.uint16)
+    assert np.array_equal(back, bits[finite])
+
+
 def test_pack_and_tile_rule(ta, orc):
     src = np.arange(16, dtype=np.float32)
     assert ta.pack_f16w_row_tiles(src, 4, 4, 2).tolist() == \
