@@ -170,6 +170,37 @@ int ta_matmul(const ta_executor *exec, const ta_tensor *a, const ta_tensor *b, c
 int ta_matmul_batch(const ta_executor *exec, const ta_matmul_call *calls, size_t n_calls,
                     ta_run_stats *stats);
 
+/* Host-resident batched matmul: C[b] = epilogue(alpha * A[b] @ B) with A, D, bias and C in HOST
+ * memory.  One call replaces the reference's ta_upload x3 + ta_run_ops + ta_download sequence
+ * (ref src/executor/transfer.rs:21-84, dispatch.rs:87-188): the planes are cut into chunks and the
+ * host->device copies of chunk i+1, the GEMM of chunk i and the device->host copy of chunk i-1
+ * run at the same time on three streams, so a PCIe-bound call costs about max(bytes in, bytes out)
+ * instead of their sum plus the compute.  Every chunk runs the kernel the tensor path would pick for it, so
+ * results are bit-identical to that path applied chunk by chunk.  For the
+ * copies to overlap the host buffers must be page-locked (ta_pinned_alloc, or memory the caller
+ * pinned); pageable memory works but serialises.  One such call at a time per executor; others
+ * wait.  stats->gpu_time_ns spans the first upload to the last download. */
+typedef struct ta_host_batched_matmul {
+  uint32_t batch, m, n, k;
+  const float *a;          /* host [batch, M, K] */
+  const ta_tensor *b;      /* device [K, N] f32 or f16, shared by all planes; NULL when b_host is set */
+  const float *b_host;     /* host [K, N] f32, uploaded once per call; NULL when b is set */
+  float *c;                /* host [batch, M, N], written */
+  const float *bias;       /* host [N] (bias_per_batch 0) or [batch, N] (1); NULL: none */
+  uint32_t bias_per_batch;
+  const float *d;          /* host [batch, M, N] operand of the binary stage; NULL iff binary is NONE */
+  uint32_t activation;     /* ta_activation */
+  uint32_t binary;         /* ta_binary */
+  float alpha, beta;
+  uint32_t chunk_batch;    /* planes per pipeline stage; 0: the library chooses (about batch / 16) */
+} ta_host_batched_matmul;
+int ta_run_matmul_host_batched(const ta_executor *exec, const ta_host_batched_matmul *desc,
+                               ta_run_stats *stats);
+
+/* Page-locked host memory for the call above (cudaHostAlloc / cudaFreeHost); NULL on failure. */
+void *ta_pinned_alloc(size_t bytes);
+void ta_pinned_free(void *ptr);
+
 /* ref h:166-175; ref src/executor/dispatch.rs:87-188.  ta_run_ops: independent
  * ops, one submission.  ta_run_op_graph: later ops may read earlier outputs. */
 int ta_run_ops(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops,

@@ -32,6 +32,7 @@ from .api import (  # noqa: F401
     default_num_k_splits,
     f16w_row_tile_n,
     f32_to_f16_bits,
+    pinned_empty,
     f16_bits_to_f32,
     heuristic_splits,
     kernel_launch_count,

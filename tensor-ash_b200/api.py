@@ -593,6 +593,47 @@ class Executor:
         _check(lib().ta_run_ops(self._h, _ops_array(ops), len(ops), C.byref(st)))
         return RunStats._from(st)
 
+    def run_matmul_host_batched(self, a: np.ndarray, b, c: np.ndarray, *, bias: Optional[np.ndarray] = None,
+                                d: Optional[np.ndarray] = None, activation: int = 0, binary: int = 0,
+                                alpha: float = 1.0, beta: float = 0.0, chunk_batch: int = 0) -> RunStats:
+        """``c[i] = epilogue(alpha * a[i] @ b)`` with ``a`` [batch, M, K], ``d`` and ``c`` [batch, M, N]
+        and ``bias`` ([N] or [batch, N]) in host memory; ``b`` is a device :class:`Tensor` [K, N] or a
+        host array.  Copies in, compute and copies out are pipelined over chunks of the batch (pin
+        the arrays, e.g. with :func:`pinned_empty`, for them to overlap).  Bit-identical to
+        upload + run_ops + download applied chunk by chunk."""
+        def host(x, name, shape=None):
+            if x.dtype != np.float32 or not x.flags.c_contiguous:
+                raise TypeError(f"{name} must be a C-contiguous float32 array")
+            if shape is not None and tuple(x.shape) != tuple(shape):
+                raise ValueError(f"{name} has shape {tuple(x.shape)}, expected {tuple(shape)}")
+            return x.ctypes.data
+        if a.ndim != 3:
+            raise ValueError("a must be [batch, M, K]")
+        batch, m, k = (int(v) for v in a.shape)
+        n = int(c.shape[-1])
+        desc = capi.HostBatchedMatmulC()
+        desc.batch, desc.m, desc.n, desc.k = batch, m, n, k
+        desc.a = host(a, "a")
+        if isinstance(b, Tensor):
+            desc.b, desc.b_host = b._h, None
+        else:
+            desc.b, desc.b_host = None, host(b, "b", (k, n))
+        if not c.flags.writeable:
+            raise TypeError("c must be writeable")
+        desc.c = host(c, "c", (batch, m, n))
+        if bias is not None:
+            if bias.ndim == 2:
+                desc.bias, desc.bias_per_batch = host(bias, "bias", (batch, n)), 1
+            else:
+                desc.bias, desc.bias_per_batch = host(bias, "bias", (n,)), 0
+        if d is not None:
+            desc.d = host(d, "d", (batch, m, n))
+        desc.activation, desc.binary = int(activation), int(binary)
+        desc.alpha, desc.beta, desc.chunk_batch = float(alpha), float(beta), int(chunk_batch)
+        st = capi.RunStatsC()
+        _check(lib().ta_run_matmul_host_batched(self._h, C.byref(desc), C.byref(st)))
+        return RunStats._from(st)
+
     def run_op_graph(self, ops: Sequence[MatmulOp]) -> RunStats:
         st = capi.RunStatsC()
         _check(lib().ta_run_op_graph(self._h, _ops_array(ops), len(ops), C.byref(st)))
@@ -720,6 +761,35 @@ def pack_f16w_row_tiles(src: np.ndarray, k: int, n: int, tile_n: int) -> np.ndar
 
 def f16w_row_tile_n(k: int, n: int) -> int:
     return int(lib().ta_f16w_row_tile_n(k, n))
+
+
+class _PinnedBlock:
+    """Owner of one page-locked allocation; freed when the last array viewing it is collected."""
+
+    def __init__(self, nbytes: int):
+        self.ptr = lib().ta_pinned_alloc(nbytes)
+        if not self.ptr:
+            raise TensorAshError(f"ta_pinned_alloc({nbytes}) failed")
+
+    def __del__(self):
+        ptr, self.ptr = getattr(self, "ptr", None), None
+        if ptr:
+            try:
+                lib().ta_pinned_free(ptr)
+            except Exception:
+                pass
+
+
+def pinned_empty(shape, dtype=np.float32) -> np.ndarray:
+    """A page-locked NumPy array (for :meth:`Executor.run_matmul_host_batched` and fast transfers).
+    The memory is released when the array and every view of it are gone."""
+    dtype = np.dtype(dtype)
+    count = int(np.prod(shape, dtype=np.int64))
+    nbytes = max(count * dtype.itemsize, 1)
+    block = _PinnedBlock(nbytes)
+    buf = (C.c_char * nbytes).from_address(block.ptr)
+    buf._owner = block            # every array made from buf keeps buf, and so the block, alive
+    return np.frombuffer(buf, dtype=dtype, count=count).reshape(shape)
 
 
 def f32_to_f16_bits(v: float) -> int:

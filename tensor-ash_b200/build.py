@@ -25,6 +25,7 @@ SOURCES = [
     "ta_graph.cu",
     "ta_capi.cu",
     "ta_comm.cu",
+    "ta_host_stream.cu",
     "llama_ash.cu",
     "k_gemm_ffma.cu",
     "k_gemm_tf32x3.cu",

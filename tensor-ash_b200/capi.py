@@ -61,6 +61,14 @@ class MatmulOpExC(C.Structure):
                 ("normed_eps", C.c_float), ("store", StoreDescC)]
 
 
+class HostBatchedMatmulC(C.Structure):
+    _fields_ = [("batch", C.c_uint32), ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
+                ("a", C.c_void_p), ("b", C.c_void_p), ("b_host", C.c_void_p), ("c", C.c_void_p),
+                ("bias", C.c_void_p), ("bias_per_batch", C.c_uint32), ("d", C.c_void_p),
+                ("activation", C.c_uint32), ("binary", C.c_uint32), ("alpha", C.c_float), ("beta", C.c_float),
+                ("chunk_batch", C.c_uint32)]
+
+
 class FlashDescC(C.Structure):
     _fields_ = [("kv_len", C.c_uint32), ("pos_base", C.c_uint32), ("scale", C.c_float),
                 ("token_major_heads", C.c_uint32), ("out_token_major_heads", C.c_uint32), ("simt", C.c_uint32)]
@@ -115,6 +123,9 @@ SIGNATURES = {
     "ta_matmul": (C.c_int, [_P, _P, _P, _P, C.c_float, _U32, _STATS]),
     "ta_matmul_batch": (C.c_int, [_P, C.POINTER(MatmulCallC), _SZ, _STATS]),
     "ta_run_ops": (C.c_int, [_P, C.POINTER(MatmulOpC), _SZ, _STATS]),
+    "ta_run_matmul_host_batched": (C.c_int, [_P, C.POINTER(HostBatchedMatmulC), _STATS]),
+    "ta_pinned_alloc": (C.c_void_p, [_SZ]),
+    "ta_pinned_free": (None, [C.c_void_p]),
     "ta_run_op_graph": (C.c_int, [_P, C.POINTER(MatmulOpC), _SZ, _STATS]),
     "ta_softmax_rows": (C.c_int, [_P, _P, _P, C.c_float, _U32, _U32, _U32, _STATS]),
     "ta_rms_norm": (C.c_int, [_P, _P, _P, _P, C.c_float, _STATS]),

@@ -303,6 +303,40 @@ int ta_run_ops(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops, t
   });
 }
 
+int ta_run_matmul_host_batched(const ta_executor *exec, const ta_host_batched_matmul *desc,
+                               ta_run_stats *stats) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_run_matmul_host_batched: exec is null");
+    if (!desc) fail("ta_run_matmul_host_batched: desc is null");
+    if (desc->activation > 3) fail("ta_run_matmul_host_batched: activation %u is invalid", desc->activation);
+    if (desc->binary > 2) fail("ta_run_matmul_host_batched: binary %u is invalid", desc->binary);
+    HostBatchedMatmul h;
+    h.batch = desc->batch; h.m = desc->m; h.n = desc->n; h.k = desc->k;
+    h.a = desc->a; h.b_host = desc->b_host; h.c = desc->c;
+    h.b = desc->b ? &checked_tensor(e, desc->b, "ta_run_matmul_host_batched", "b") : nullptr;
+    h.bias = desc->bias; h.bias_per_batch = desc->bias_per_batch != 0;
+    h.d = desc->d;
+    h.activation = (Activation)desc->activation;
+    h.binary = (BinaryKind)desc->binary;
+    h.alpha = desc->alpha; h.beta = desc->beta;
+    h.chunk_batch = desc->chunk_batch;
+    write_stats(stats, e.exec->run_matmul_host_batched(h));
+  });
+}
+
+void *ta_pinned_alloc(size_t bytes) {
+  void *p = nullptr;
+  if (!bytes || cudaHostAlloc(&p, bytes, cudaHostAllocDefault) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+
+void ta_pinned_free(void *ptr) {
+  if (ptr) cudaFreeHost(ptr);
+}
+
 int ta_run_op_graph(const ta_executor *exec, const ta_matmul_op *ops, size_t n_ops,
                     ta_run_stats *stats) {
   return status_call([&]() {

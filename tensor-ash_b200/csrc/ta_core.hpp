@@ -436,6 +436,26 @@ struct ExecutorConfig {
 
 struct PreparedOps;
 
+// One batched matmul whose per-plane operands live in HOST memory (page-locked for overlap):
+// C[b] = epilogue(alpha * A[b] @ B).  The planes are cut into chunks and pipelined through a
+// ring of device staging sets on three streams, so that the host->device copies of chunk i+1,
+// the GEMM of chunk i and the device->host copy of chunk i-1 run at the same time.
+struct HostBatchedMatmul {
+  uint32_t batch = 0, m = 0, n = 0, k = 0;
+  const float *a = nullptr;        // host [batch, M, K]
+  const Tensor *b = nullptr;       // device [K, N] (f32 or f16), shared by every plane; or
+  const float *b_host = nullptr;   // host [K, N] f32, uploaded once per call
+  float *c = nullptr;              // host [batch, M, N]
+  const float *bias = nullptr;     // host [N] or [batch, N]
+  bool bias_per_batch = false;
+  const float *d = nullptr;        // host [batch, M, N] epilogue operand
+  Activation activation = Activation::None;
+  BinaryKind binary = BinaryKind::None;
+  float alpha = 1.0f, beta = 0.0f;
+  uint32_t chunk_batch = 0;        // planes per pipeline stage; 0: chosen by the library
+};
+struct HostStreamState;
+
 class Executor {
  public:
   Executor(std::shared_ptr<Context> ctx, int selection, ExecutorConfig cfg);
@@ -502,6 +522,10 @@ class Executor {
 
   void validate_tensor(const Tensor &t, const char *what) const;
 
+  // Host-resident batched matmul, copies overlapped with compute (see HostBatchedMatmul).
+  // gpu_time_ns spans the first upload to the last download.
+  RunStats run_matmul_host_batched(const HostBatchedMatmul &desc);
+
   // Slot checkout (src/executor/submission.rs:37-53): blocks while all busy.
   Slot &checkout_slot();
   void release_slot(Slot &s);
@@ -530,6 +554,8 @@ class Executor {
   mutable std::mutex tune_mu_;
   mutable std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> tuned_;
   std::string tune_path_;
+  std::mutex host_stream_mu_;                     // one host-streamed call at a time per executor
+  std::shared_ptr<HostStreamState> host_stream_;  // copy streams, events and the staging ring
 };
 
 struct SlotGuard {

@@ -288,8 +288,8 @@ def test_stats_and_dispatch_info(setup, orc):
 def test_prepared_handle_may_outlive_its_executor_for_destruction(setup, orc):
     """Handles are destroyed in any order: closing the executor first must leave the prepared
     object destroyable and no CUDA error behind for the next launch to trip over."""
-    ta, ctx, ex, _ = setup
-    ex2 = ta.Executor(ctx, 2, 4)
+    ta, ctx, ex, sel = setup
+    ex2 = ta.Executor(ctx, 2, 4, sel, tune=False)
     a, _ = upload_det(ta, ctx, ex, orc, (64, 64), 71)
     b, _ = upload_det(ta, ctx, ex, orc, (64, 64), 72)
     c = ta.Tensor.uninit_device(ctx, (64, 64))
