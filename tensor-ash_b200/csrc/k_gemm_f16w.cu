@@ -28,6 +28,7 @@
 
 #include "k_epilogue.cuh"
 #include "k_umma.cuh"
+#include "k_trace.cuh"
 #include "ta_core.hpp"
 
 namespace ta {
@@ -216,34 +217,37 @@ gemm_f16w_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
       const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(warp * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        tmem_ld32(taddr + c0, v);
-        const uint32_t col0 = n0 + c0;
-        if (row_ok && col0 < p.n) {
-#pragma unroll
-          for (int q = 0; q < 32; q += 4) {
-            const uint32_t col = col0 + q;
-            if (col < p.n) {  // N % 8 == 0: a float4 is either fully in or fully out
-              float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-              if (p.accumulate) {
-                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
-                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+      epi_dispatch_act(p.act, [&](auto act_tag) {
+        constexpr uint32_t ACT = decltype(act_tag)::value;
+  #pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          tmem_ld32(taddr + c0, v);
+          const uint32_t col0 = n0 + c0;
+          if (row_ok && col0 < p.n) {
+  #pragma unroll
+            for (int q = 0; q < 32; q += 4) {
+              const uint32_t col = col0 + q;
+              if (col < p.n) {  // N % 8 == 0: a float4 is either fully in or fully out
+                float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+                if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+                if (p.accumulate) {
+                  const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+                  o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+                }
+                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+                if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+                if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+                o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
+                o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
+                o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
+                o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
+                *reinterpret_cast<float4 *>(crow + col) = o;
               }
-              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
-              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
-              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
-              o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
-              o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
-              o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
-              o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
-              *reinterpret_cast<float4 *>(crow + col) = o;
             }
           }
         }
-      }
+      });
       tc_fence_before();
       mbar_arrive(acc_empty(buf));
     }
@@ -270,6 +274,7 @@ gemm_f16w_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
 // Both operands take the 128-byte swizzle (A K-major: SBO 1024; B N-major: LBO 64*128, SBO 1024).
 constexpr int PK = 64;                       // K elements per stage
 constexpr int PRE_THREADS = 192;             // warps 0-3 epilogue, 4 TMA, 5 MMA + TMEM
+constexpr int EPI_PITCH = 36;                // floats per row of an epilogue transpose buffer
 
 template <int BN>
 struct PreCfg {
@@ -277,7 +282,9 @@ struct PreCfg {
   static constexpr int B_BYTES = PK * BN * 2;             // 32 KiB at BN = 256
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+  // + per epilogue warp a 32 x 32 f32 transpose buffer (row pitch 36 floats: conflict-free
+  // float4 writes by row and float4 reads by 8-lane row segments)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 4 * 32 * EPI_PITCH * 4 + 1024;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -304,6 +311,21 @@ convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint
   *reinterpret_cast<uint4 *>(out + r * kp + c) = o;
 }
 
+#ifdef TA_KERNEL_TRACE
+#define PRE_TRACE_DECL()                                                                          \
+  __shared__ unsigned int pre_trace_rec;                                                          \
+  if (threadIdx.x == 0) pre_trace_rec = blockIdx.x == 0 ? (atomicAdd(&g_trace_n, 1u) & 4095u) : 0xffffffffu;
+#define PRE_TRACE(i)                                                                              \
+  if (pre_trace_rec != 0xffffffffu) {                                                             \
+    unsigned long long t_;                                                                        \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                        \
+    g_trace[pre_trace_rec][i] = t_;                                                               \
+  }
+#else
+#define PRE_TRACE_DECL()
+#define PRE_TRACE(i)
+#endif
+
 template <int BN>
 __global__ void __launch_bounds__(PRE_THREADS, 1)
 gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
@@ -320,7 +342,10 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   volatile uint32_t *tmem_slot =
       reinterpret_cast<volatile uint32_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
   volatile uint32_t *abort_flag = tmem_slot + 1;
+  float *epi_buf = reinterpret_cast<float *>(smem_gen + C::STAGES * C::STAGE_BYTES + 256);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  PRE_TRACE_DECL();
+  if (threadIdx.x == 0) { PRE_TRACE(0); }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -340,6 +365,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) { PRE_TRACE(1); }
 
   const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const uint32_t tiles_per_batch = tiles_m * tiles_n;
@@ -356,13 +382,20 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
         ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
         if (!ok) break;
-        if (lane == 0) {
-          const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+        const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+        if (elect_one()) {
           mbar_arrive_expect_tx(full(stage), C::STAGE_BYTES);
           tma_load_3d(dst, &map_a, full(stage), (int)(kb * PK), m0, za);
+          if (p.b_grouped) {
+            tma_load_4d(dst + C::A_BYTES, &map_b, full(stage), 0, (int)(kb * PK), n0 / 64, zb);
+          } else {
 #pragma unroll
-          for (int nb = 0; nb < BN / 64; ++nb)
-            tma_load_3d(dst + C::A_BYTES + nb * (PK * 128), &map_b, full(stage), n0 + nb * 64, (int)(kb * PK), zb);
+            for (int nb = 0; nb < BN / 64; ++nb)
+              tma_load_3d(dst + C::A_BYTES + nb * (PK * 128), &map_b, full(stage), n0 + nb * 64, (int)(kb * PK), zb);
+          }
+#ifndef PRE_TRACE_MMA
+          if (tile == blockIdx.x && kb + 1 == (uint32_t)C::STAGES) { PRE_TRACE(2); }
+#endif
         }
         __syncwarp();
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -379,20 +412,38 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * BN;
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+#ifdef PRE_TRACE_MMA
+        if (lane == 0 && tile == blockIdx.x && kb == 16) { PRE_TRACE(2); }
+        if (lane == 0 && tile == blockIdx.x && kb == 17) { PRE_TRACE(5); }
+#endif
         ok = mbar_wait(full(stage), phase, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a16 = smem_base + stage * C::STAGE_BYTES;
-          const uint32_t b16 = a16 + C::A_BYTES;
+#ifdef PRE_TRACE_MMA
+        if (lane == 0 && tile == blockIdx.x && kb == 16) { PRE_TRACE(3); }
+        if (lane == 0 && tile == blockIdx.x && kb == 17) { PRE_TRACE(6); }
+#else
+        if (lane == 0 && tile == blockIdx.x) {
+          if (kb == 0) { PRE_TRACE(3); }
+          if (kb == 8) { PRE_TRACE(4); }
+          if (kb + 1 == k_blocks) { PRE_TRACE(5); }
+        }
+#endif
+        // descriptors are built warp-uniformly; advancing K by 16 halves moves A by 32 bytes
+        // (+2 in the 16-byte address field) and MN-major B by 16 rows of 128 bytes (+128)
+        const uint32_t a16 = smem_base + stage * C::STAGE_BYTES;
+        const uint64_t da0 = make_desc(a16, 16, 1024, LAYOUT_SW128);
+        const uint64_t db0 = make_desc(a16 + C::A_BYTES, PK * 128, 1024, LAYOUT_SW128);
+        if (elect_one()) {
 #pragma unroll
-          for (int j = 0; j < PK / 16; ++j) {
-            const uint64_t da = make_desc(a16 + j * 32, 16, 1024, LAYOUT_SW128);
-            const uint64_t db = make_desc(b16 + j * 2048, PK * 128, 1024, LAYOUT_SW128);
-            mma_f16(d_tmem, da, db, idesc, (kb | (uint32_t)j) != 0u);
-          }
+          for (int j = 0; j < PK / 16; ++j)
+            mma_f16(d_tmem, da0 + (uint64_t)(j * 2), db0 + (uint64_t)(j * 128), idesc, (kb | (uint32_t)j) != 0u);
           tc_commit(empty(stage));
           if (kb + 1 == k_blocks) tc_commit(acc_full(buf));
+#ifdef PRE_TRACE_MMA
+          if (tile == blockIdx.x && kb == 16) { PRE_TRACE(4); }
+          if (tile == blockIdx.x && kb == 17) { PRE_TRACE(7); }
+#endif
         }
         __syncwarp();
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -409,43 +460,61 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t row = m0 + warp * 32 + lane;
-      const bool row_ok = row < p.m;
-      const size_t row_off = (size_t)batch * p.stride_c + (size_t)row * p.n;
-      float *__restrict__ crow = p.c + row_off;
-      const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
+#ifndef PRE_TRACE_MMA
+      if (threadIdx.x == 0 && tile == blockIdx.x) { PRE_TRACE(6); }
+#endif
+      // TMEM gives each lane one row; a row-per-lane store would touch 32 rows per instruction.
+      // Transpose 32 x 32 blocks through shared memory so that every global access of the
+      // epilogue (C, D, the old C when accumulating) covers full 128-byte row segments.
+      float *__restrict__ tbuf = epi_buf + warp * (32 * EPI_PITCH);
+      const uint32_t cq = (uint32_t)(lane & 7) * 4, rsub = (uint32_t)lane >> 3;
+      const size_t plane_off = (size_t)batch * p.stride_c;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(warp * 32) << 16);
+      // one dispatch on the activation per tile; the chunk loop below is compiled per activation
+      epi_dispatch_act(p.act, [&](auto act_tag) {
+        constexpr uint32_t ACT = decltype(act_tag)::value;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        tmem_ld32(taddr + c0, v);
-        const uint32_t col0 = n0 + c0;
-        if (row_ok && col0 < p.n) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          tmem_ld32(taddr + c0, v);
 #pragma unroll
-          for (int q = 0; q < 32; q += 4) {
-            const uint32_t col = col0 + q;
-            if (col < p.n) {
-              float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-              if (p.accumulate) {
-                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
-                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+          for (int q = 0; q < 32; q += 4)
+            *reinterpret_cast<float4 *>(tbuf + lane * EPI_PITCH + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+          __syncwarp();
+          const uint32_t col = n0 + c0 + cq;
+          if (col < p.n) {
+            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t r = (uint32_t)i * 4 + rsub, row = m0 + warp * 32 + r;
+              if (row < p.m) {
+                const size_t off = plane_off + (size_t)row * p.n + col;
+                float4 o = *reinterpret_cast<const float4 *>(tbuf + r * EPI_PITCH + cq);
+                if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+                if (p.accumulate) {
+                  const float4 c_old = *reinterpret_cast<const float4 *>(p.c + off);
+                  o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+                }
+                float4 dv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.d) dv = *reinterpret_cast<const float4 *>(p.d + off);
+                o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
+                o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
+                o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
+                o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
+                *reinterpret_cast<float4 *>(p.c + off) = o;
               }
-              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
-              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
-              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
-              o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
-              o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
-              o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
-              o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
-              *reinterpret_cast<float4 *>(crow + col) = o;
             }
           }
+          __syncwarp();
         }
-      }
+      });
       tc_fence_before();
       mbar_arrive(acc_empty(buf));
+#ifndef PRE_TRACE_MMA
+      if (threadIdx.x == 0 && tile == blockIdx.x) { PRE_TRACE(7); }
+#endif
     }
   }
 
@@ -483,11 +552,18 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   // A16 [ba, M, Kp] f16: 128-byte rows of 64 halves, 128-byte swizzle; columns >= K read as zero (TMA bound K)
   encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a16, p.k, p.m, ba, (uint64_t)kp * 2,
               (uint64_t)p.m * kp * 2, PK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
-  encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, p.n, p.k, bb, (uint64_t)p.n * 2,
-              p.stride_b ? (uint64_t)p.stride_b * 2 : (uint64_t)p.k * p.n * 2, 64, PK, CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t b_batch_bytes = p.stride_b ? (uint64_t)p.stride_b * 2 : (uint64_t)p.k * p.n * 2;
+  GemmParams pg = p;
+  pg.b_grouped = p.n % 64 == 0 ? 1u : 0u;
+  if (pg.b_grouped)   // one TMA per stage for the whole BN-wide B block
+    encode_map_grouped(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, 2, p.n, p.k, bb, b_batch_bytes, 64, PK,
+                       BN / 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, p.n, p.k, bb, (uint64_t)p.n * 2, b_batch_bytes, 64, PK,
+                CU_TENSOR_MAP_SWIZZLE_128B);
   const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
-  gemm_f16w_pre_kernel<BN><<<grid, PRE_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);
+  gemm_f16w_pre_kernel<BN><<<grid, PRE_THREADS, C::SMEM_BYTES, stream>>>(pg, map_a, map_b, status);
   TA_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
@@ -551,10 +627,18 @@ uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_co
   return best;
 }
 
-// Scratch bytes for the f16 copy of A (rows padded to 8 halves).
+// Row pitch (in halves) of the f16 copy of A: K rounded up to 8, plus TA_F16W_APAD halves.
+static uint32_t a16_pitch(uint32_t k) {
+  static const uint32_t pad = [] {
+    const char *e = std::getenv("TA_F16W_APAD");
+    return e ? (uint32_t)std::strtoul(e, nullptr, 10) & ~7u : 0u;
+  }();
+  return ((k + 7u) & ~7u) + pad;
+}
+
+// Scratch bytes for the f16 copy of A.
 size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
-  const uint64_t kp = ((uint64_t)k + 7) & ~7ull;
-  return (size_t)((uint64_t)batch_a * m * kp * 2);
+  return (size_t)((uint64_t)batch_a * m * a16_pitch(k) * 2);
 }
 
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
@@ -565,7 +649,7 @@ void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t til
   const char *env = std::getenv("TA_F16W_PRE");
   if (scratch && scratch_bytes >= gemm_f16w_umma_scratch_bytes(batch_a, p.m, p.k) &&
       (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0 && !(env && env[0] == '0')) {
-    const uint32_t kp = (p.k + 7u) & ~7u;
+    const uint32_t kp = a16_pitch(p.k);
     __half *a16 = static_cast<__half *>(scratch);
     if (tile_n >= 256) launch_pre_t<256>(ctx, p, a16, kp, status, a16_ready, stream);
     else if (tile_n >= 128) launch_pre_t<128>(ctx, p, a16, kp, status, a16_ready, stream);
@@ -578,3 +662,5 @@ void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t til
 }
 
 }  // namespace ta
+
+TA_TRACE_EXPORT(ta_debug_f16w_trace)

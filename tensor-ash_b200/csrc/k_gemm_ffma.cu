@@ -137,28 +137,31 @@ gemm_ffma_kernel(GemmParams p, float *__restrict__ scratch) {
   const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
   const bool alpha_is_one = p.alpha == 1.0f;
 
+  // one dispatch on the activation per tile; the store loop is compiled per activation
+  epi_dispatch_act(SPLITK ? 0u : p.act, [&](auto act_tag) {
+    constexpr uint32_t ACT = decltype(act_tag)::value;
 #pragma unroll
-  for (int i = 0; i < TM; ++i) {
-    const uint32_t gr = row0 + ty * TM + i;
-    if (gr >= p.m) continue;
+    for (int i = 0; i < TM; ++i) {
+      const uint32_t gr = row0 + ty * TM + i;
+      if (gr >= p.m) continue;
 #pragma unroll
-    for (int s = 0; s < TN / 4; ++s) {
+      for (int s = 0; s < TN / 4; ++s) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t gc = col0 + (s * TX + tx) * 4 + q;
-        if (gc >= p.n) continue;
-        const size_t idx = (size_t)gr * p.n + gc;
-        float v = acc[i][s * 4 + q];
-        if (!alpha_is_one) v = p.alpha * v;
-        if (!SPLITK) {
-          if (p.accumulate) v += out[idx];
-          v = epi_apply(v, bias != nullptr, bias ? bias[gc] : 0.0f, p.act, p.binary,
-                        D ? D[idx] : 0.0f, p.beta);
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t gc = col0 + (s * TX + tx) * 4 + q;
+          if (gc >= p.n) continue;
+          const size_t idx = (size_t)gr * p.n + gc;
+          float v = acc[i][s * 4 + q];
+          if (!alpha_is_one) v = p.alpha * v;
+          if (!SPLITK) {
+            if (p.accumulate) v += out[idx];
+            v = epi_apply_t<ACT>(v, bias != nullptr, bias ? bias[gc] : 0.0f, p.binary, D ? D[idx] : 0.0f, p.beta);
+          }
+          out[idx] = v;
         }
-        out[idx] = v;
       }
     }
-  }
+  });
 }
 
 template <int BM, int BN, int TM, int TN, bool SPLITK>

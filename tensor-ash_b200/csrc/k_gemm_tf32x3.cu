@@ -153,14 +153,18 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
         ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
         if (!ok) break;
-        if (lane == 0) {
-          const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+        const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
+        if (elect_one()) {
           mbar_arrive_expect_tx(full_raw(stage), C::HALF_BYTES);
           tma_load_3d(dst, &map_a, full_raw(stage), (int)(kb * BK), m0, za);
+          if (p.b_grouped) {
+            tma_load_4d(dst + C::A_BYTES, &map_b, full_raw(stage), 0, (int)(kb * BK), n0 / 32, zb);
+          } else {
 #pragma unroll
-          for (int nb = 0; nb < BN / 32; ++nb)
-            tma_load_3d(dst + C::A_BYTES + nb * (BK * 128), &map_b, full_raw(stage), n0 + nb * 32,
-                        (int)(kb * BK), zb);
+            for (int nb = 0; nb < BN / 32; ++nb)
+              tma_load_3d(dst + C::A_BYTES + nb * (BK * 128), &map_b, full_raw(stage), n0 + nb * 32,
+                          (int)(kb * BK), zb);
+          }
         }
         __syncwarp();
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -185,16 +189,19 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
           ok = mbar_wait(full_cvt(stage), phase, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
-            const uint32_t a_hi = smem_base + stage * C::STAGE_BYTES;
-            const uint32_t b_hi = a_hi + C::A_BYTES;
-            const uint32_t a_lo = a_hi + C::HALF_BYTES, b_lo = b_hi + C::HALF_BYTES;
+          // descriptors are built warp-uniformly; a K step of 8 floats moves A by 32 bytes (+2 in
+          // the 16-byte address field) and MN-major B by 8 rows of 128 bytes (+64)
+          const uint32_t a_hi = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t b_hi = a_hi + C::A_BYTES;
+          const uint64_t da_hi0 = make_desc(a_hi, 16, 512, LAYOUT_SW64);
+          const uint64_t da_lo0 = make_desc(a_hi + C::HALF_BYTES, 16, 512, LAYOUT_SW64);
+          const uint64_t db_hi0 = make_desc(b_hi, BK * 128, 512, LAYOUT_SW128_BASE32B);
+          const uint64_t db_lo0 = make_desc(b_hi + C::HALF_BYTES, BK * 128, 512, LAYOUT_SW128_BASE32B);
+          if (elect_one()) {
 #pragma unroll
             for (int j = 0; j < BK / 8; ++j) {
-              const uint64_t da_hi = make_desc(a_hi + j * 32, 16, 512, LAYOUT_SW64);
-              const uint64_t da_lo = make_desc(a_lo + j * 32, 16, 512, LAYOUT_SW64);
-              const uint64_t db_hi = make_desc(b_hi + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
-              const uint64_t db_lo = make_desc(b_lo + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
+              const uint64_t da_hi = da_hi0 + (uint64_t)(j * 2), da_lo = da_lo0 + (uint64_t)(j * 2);
+              const uint64_t db_hi = db_hi0 + (uint64_t)(j * 64), db_lo = db_lo0 + (uint64_t)(j * 64);
               mma_tf32(d_tmem, da_lo, db_hi, idesc, ((kb - kb0) | (uint32_t)j) != 0u);
               mma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
               mma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
@@ -276,26 +283,30 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
       const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
       if (row_ok) {
-#pragma unroll
-        for (int q = 0; q < HALF_N; q += 4) {
-          const uint32_t col = n0 + q;
-          if (col < p.n) {  // N % 4 == 0: a float4 is either fully in or fully out
-            float4 o = make_float4(sum[q], sum[q + 1], sum[q + 2], sum[q + 3]);
-            if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-            if (p.accumulate) {
-              const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
-              o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+        // one dispatch on the activation per tile; the store loop is compiled per activation
+        epi_dispatch_act(p.act, [&](auto act_tag) {
+          constexpr uint32_t ACT = decltype(act_tag)::value;
+  #pragma unroll
+          for (int q = 0; q < HALF_N; q += 4) {
+            const uint32_t col = n0 + q;
+            if (col < p.n) {  // N % 4 == 0: a float4 is either fully in or fully out
+              float4 o = make_float4(sum[q], sum[q + 1], sum[q + 2], sum[q + 3]);
+              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+              if (p.accumulate) {
+                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+              }
+              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+              o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
+              o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
+              o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
+              o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
+              *reinterpret_cast<float4 *>(crow + col) = o;
             }
-            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
-            if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
-            if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
-            o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
-            o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
-            o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
-            o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
-            *reinterpret_cast<float4 *>(crow + col) = o;
           }
-        }
+        });
       }
     }
   }
@@ -354,9 +365,14 @@ void launch_t(const Context &ctx, const GemmParams &p_in, uint32_t *status, cuda
              p.stride_a ? (uint64_t)p.stride_a * 4 : (uint64_t)p.m * p.k * 4, BK, BM,
              CU_TENSOR_MAP_SWIZZLE_64B);
   // B [bb, K, N]: dims {N, K, bb}; boxes of 32 columns (128 bytes) x BK rows.
-  encode_map(ctx, &map_b, p.b, p.n, p.k, bb, (uint64_t)p.n * 4,
-             p.stride_b ? (uint64_t)p.stride_b * 4 : (uint64_t)p.k * p.n * 4, 32, BK,
-             CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  const uint64_t b_batch_bytes = p.stride_b ? (uint64_t)p.stride_b * 4 : (uint64_t)p.k * p.n * 4;
+  p.b_grouped = p.n % 32 == 0 ? 1u : 0u;
+  if (p.b_grouped)   // one TMA per stage for the whole BN-wide B block
+    umma::encode_map_grouped(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.b, 4, p.n, p.k, bb, b_batch_bytes, 32, BK,
+                             BN / 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  else
+    encode_map(ctx, &map_b, p.b, p.n, p.k, bb, (uint64_t)p.n * 4, b_batch_bytes, 32, BK,
+               CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
   gemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);

@@ -267,34 +267,37 @@ gemm_tf32x3_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
       const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(warp * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float v[32];
-        tmem_ld32(taddr + c0, v);
-        const uint32_t col0 = n0 + c0;
-        if (row_ok && col0 < p.n) {
-#pragma unroll
-          for (int q = 0; q < 32; q += 4) {
-            const uint32_t col = col0 + q;
-            if (col < p.n) {
-              float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-              if (p.accumulate) {
-                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
-                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+      epi_dispatch_act(p.act, [&](auto act_tag) {
+        constexpr uint32_t ACT = decltype(act_tag)::value;
+  #pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          tmem_ld32(taddr + c0, v);
+          const uint32_t col0 = n0 + c0;
+          if (row_ok && col0 < p.n) {
+  #pragma unroll
+            for (int q = 0; q < 32; q += 4) {
+              const uint32_t col = col0 + q;
+              if (col < p.n) {
+                float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+                if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+                if (p.accumulate) {
+                  const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+                  o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+                }
+                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+                if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+                if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+                o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
+                o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
+                o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
+                o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
+                *reinterpret_cast<float4 *>(crow + col) = o;
               }
-              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
-              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
-              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
-              o.x = epi_apply(o.x, bias != nullptr, bv.x, p.act, p.binary, dv.x, p.beta);
-              o.y = epi_apply(o.y, bias != nullptr, bv.y, p.act, p.binary, dv.y, p.beta);
-              o.z = epi_apply(o.z, bias != nullptr, bv.z, p.act, p.binary, dv.z, p.beta);
-              o.w = epi_apply(o.w, bias != nullptr, bv.w, p.act, p.binary, dv.w, p.beta);
-              *reinterpret_cast<float4 *>(crow + col) = o;
             }
           }
         }
-      }
+      });
       tc_fence_before();
       mbar_arrive_remote(leader_addr(acc_empty(buf)));
     }

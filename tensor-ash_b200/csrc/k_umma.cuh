@@ -72,6 +72,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
                "r"(cols)
@@ -138,6 +147,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
       : "r"(taddr)
       : "memory");
 }
+// One lane of a converged warp, chosen by the hardware.  Unlike `lane == 0`, the compiler knows
+// the elected region runs in exactly one thread and keeps warp-uniform operands (descriptors,
+// barrier and tensor-memory addresses) on the uniform datapath, which is where the TMA and MMA
+// instructions take them from.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Shared-memory matrix descriptor (64-bit): start address, leading / stride
 // byte offsets (all >> 4), descriptor version 1, swizzle mode in the top bits.
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
@@ -168,6 +191,25 @@ inline void encode_map3(const Context &ctx, CUtensorMap *map, CUtensorMapDataTyp
                              CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) fail("cuTensorMapEncodeTiled failed with CUresult %d", (int)rc);
+}
+
+// Rank-4 view of a row-major [batch, K, N] operand as {group columns, K, N / group, batch}: one
+// box {group, box_k, groups, 1} lands in shared memory as `groups` consecutive [box_k][group]
+// blocks -- the image that one TMA per column group produces, in a single instruction.  Only for
+// N % group == 0 (otherwise the last group would wrap into the next row).
+inline void encode_map_grouped(const Context &ctx, CUtensorMap *map, CUtensorMapDataType dtype, const void *base,
+                               uint32_t elem_bytes, uint64_t n, uint64_t k, uint64_t batch, uint64_t batch_stride_bytes,
+                               uint32_t group, uint32_t box_k, uint32_t groups, CUtensorMapSwizzle swz) {
+  auto encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ctx.encode_tiled);
+  if (!encode) fail("cuTensorMapEncodeTiled is unavailable in this CUDA driver");
+  const cuuint64_t dims[4] = {group, k, n / group, batch};
+  const cuuint64_t strides[3] = {n * elem_bytes, (cuuint64_t)group * elem_bytes, batch_stride_bytes};
+  const cuuint32_t box[4] = {group, box_k, groups, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult rc = encode(map, dtype, 4, const_cast<void *>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) fail("cuTensorMapEncodeTiled (grouped) failed with CUresult %d", (int)rc);
 }
 
 }  // namespace umma

@@ -264,6 +264,7 @@ struct GemmParams {
   uint32_t splits;
   // tf32x3 tensor-core kernel: K blocks of 16 accumulated in tensor memory between drains (set by its launcher)
   uint32_t chunk_kb;
+  uint32_t b_grouped = 0;    // launcher-set: the B tensor map is the rank-4 grouped view (one TMA per stage)
 };
 
 // Parameters of the f16-weight GEMV kernel (M <= 8 activation rows).
