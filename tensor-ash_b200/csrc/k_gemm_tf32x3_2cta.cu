@@ -18,6 +18,8 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
+
 #include "k_epilogue.cuh"
 #include "k_umma.cuh"
 #include "ta_core.hpp"
@@ -33,7 +35,15 @@ constexpr int BNH = 128;                   // B columns per CTA (the pair covers
 constexpr int BN = 256;
 constexpr int BK = 16;
 constexpr int CVT_GROUPS = 2;
-constexpr int NUM_THREADS = 192 + CVT_GROUPS * 128;
+// warpgroups (4 warps each) as in the single-CTA kernel: 0-1 epilogue (left / right half of the
+// tile's columns, running sums in registers), 2 = TMA warp + MMA warp + two idle warps, 3-4 converters
+constexpr int EPI_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, CVT_WARP0 = 12;
+constexpr int NUM_THREADS = (CVT_WARP0 + 4 * CVT_GROUPS) * 32;   // 640
+constexpr uint32_t CHUNK_KB = 64;          // K blocks (1024 k) per tensor-memory accumulation
+constexpr int LAUNCH_REGS = 96, EPI_REGS = 168, WORKER_REGS = 48;
+static_assert(EPI_WARPS * 32 * EPI_REGS + (NUM_THREADS - EPI_WARPS * 32) * WORKER_REGS <= NUM_THREADS * LAUNCH_REGS,
+              "setmaxnreg split exceeds the CTA's launch-time register allocation");
+static_assert(NUM_THREADS * (LAUNCH_REGS + 8) > 65536, "LAUNCH_REGS must be what __launch_bounds__ yields");
 constexpr int A_BYTES = BM * BK * 4;       // 8 KiB
 constexpr int B_BYTES = BK * BNH * 4;      // 8 KiB
 constexpr int HALF_BYTES = A_BYTES + B_BYTES;
@@ -41,6 +51,7 @@ constexpr int STAGE_BYTES = 2 * HALF_BYTES;   // hi (raw) + lo
 constexpr int STAGES = 6;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
 constexpr int TMEM_COLS = 512;
+constexpr int ACC_STRIDE = 256;
 
 __device__ __forceinline__ uint32_t split_lo(float x) {
   const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
@@ -141,13 +152,13 @@ gemm_tf32x3_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 256);   // the epilogue threads of both CTAs
+      mbar_init(acc_empty(b), 2 * EPI_WARPS * 32);   // the epilogue threads of both CTAs
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 5) tmem_alloc2(smem_u32((const void *)tmem_slot), TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc2(smem_u32((const void *)tmem_slot), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();   // both CTAs' barriers exist before anyone arrives remotely
@@ -159,7 +170,10 @@ gemm_tf32x3_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
   const uint32_t num_tiles = tiles_per_batch * p.batch;
   const uint32_t k_blocks = (p.k + BK - 1) / BK;
 
-  if (warp == 4) {
+  const int wgroup = warp >> 2;
+  if (wgroup == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WORKER_REGS));
+  if (warp == TMA_WARP) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     uint32_t stage = 0, phase = 0;
     bool ok = true;
@@ -171,61 +185,70 @@ gemm_tf32x3_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
         ok = mbar_wait_cluster(empty(stage), phase ^ 1u, abort_flag);
         if (!ok) break;
-        if (lane == 0) {
-          const uint32_t dst = smem_base + stage * STAGE_BYTES;
+        const uint32_t dst = smem_base + stage * STAGE_BYTES;
+        if (elect_one()) {
           mbar_arrive_expect_tx(full_raw(stage), HALF_BYTES);
           tma_load_3d(dst, &map_a, full_raw(stage), (int)(kb * BK), m0, za);
+          if (p.b_grouped) {
+            tma_load_4d(dst + A_BYTES, &map_b, full_raw(stage), 0, (int)(kb * BK), n0 / 32, zb);
+          } else {
 #pragma unroll
-          for (int nb = 0; nb < BNH / 32; ++nb)
-            tma_load_3d(dst + A_BYTES + nb * (BK * 128), &map_b, full_raw(stage), n0 + nb * 32,
-                        (int)(kb * BK), zb);
+            for (int nb = 0; nb < BNH / 32; ++nb)
+              tma_load_3d(dst + A_BYTES + nb * (BK * 128), &map_b, full_raw(stage), n0 + nb * 32,
+                          (int)(kb * BK), zb);
+          }
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP && rank == 0) {
     // ------------------------------------------------------------ MMA issuer (leader only)
-    if (rank == 0) {
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-      uint32_t stage = 0, phase = 0, acc_it = 0;
-      bool ok = true;
-      for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++acc_it) {
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+    uint32_t stage = 0, phase = 0, acc_it = 0;
+    bool ok = true;
+    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+      for (uint32_t kb0 = 0; ok && kb0 < k_blocks; kb0 += p.chunk_kb, ++acc_it) {
+        // one K chunk per tensor-memory buffer: the epilogue warps drain chunk c while chunk c+1 runs
+        const uint32_t kb1 = min(k_blocks, kb0 + p.chunk_kb);
         const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
         ok = mbar_wait_cluster(acc_empty(buf), acc_phase ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        const uint32_t d_tmem = tmem_base + buf * ACC_STRIDE;
+        for (uint32_t kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait_cluster(full_cvt(stage), phase, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          if (lane == 0) {
-            const uint32_t a_hi = smem_base + stage * STAGE_BYTES;
-            const uint32_t b_hi = a_hi + A_BYTES;
-            const uint32_t a_lo = a_hi + HALF_BYTES, b_lo = b_hi + HALF_BYTES;
+          const uint32_t a_hi = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_hi = a_hi + A_BYTES;
+          const uint64_t da_hi0 = make_desc(a_hi, 16, 512, LAYOUT_SW64);
+          const uint64_t da_lo0 = make_desc(a_hi + HALF_BYTES, 16, 512, LAYOUT_SW64);
+          const uint64_t db_hi0 = make_desc(b_hi, BK * 128, 512, LAYOUT_SW128_BASE32B);
+          const uint64_t db_lo0 = make_desc(b_hi + HALF_BYTES, BK * 128, 512, LAYOUT_SW128_BASE32B);
+          if (elect_one()) {
 #pragma unroll
             for (int j = 0; j < BK / 8; ++j) {
-              const uint64_t da_hi = make_desc(a_hi + j * 32, 16, 512, LAYOUT_SW64);
-              const uint64_t da_lo = make_desc(a_lo + j * 32, 16, 512, LAYOUT_SW64);
-              const uint64_t db_hi = make_desc(b_hi + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
-              const uint64_t db_lo = make_desc(b_lo + j * 1024, BK * 128, 512, LAYOUT_SW128_BASE32B);
-              mma_tf32_pair(d_tmem, da_lo, db_hi, idesc, (kb | (uint32_t)j) != 0u);
+              const uint64_t da_hi = da_hi0 + (uint64_t)(j * 2), da_lo = da_lo0 + (uint64_t)(j * 2);
+              const uint64_t db_hi = db_hi0 + (uint64_t)(j * 64), db_lo = db_lo0 + (uint64_t)(j * 64);
+              mma_tf32_pair(d_tmem, da_lo, db_hi, idesc, ((kb - kb0) | (uint32_t)j) != 0u);
               mma_tf32_pair(d_tmem, da_hi, db_lo, idesc, 1u);
               mma_tf32_pair(d_tmem, da_hi, db_hi, idesc, 1u);
             }
             tc_commit_pair(empty(stage));
-            if (kb + 1 == k_blocks) tc_commit_pair(acc_full(buf));
+            if (kb + 1 == kb1) tc_commit_pair(acc_full(buf));
           }
           __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
-  } else if (warp >= 6) {
+  }
+  } else if (wgroup >= 3) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WORKER_REGS));
     // ------------------------------------------------------------ hi/lo converters (both CTAs)
-    const int t = (threadIdx.x - 6 * 32) & 127, group = (threadIdx.x - 6 * 32) >> 7;
+    const int t = (threadIdx.x - CVT_WARP0 * 32) & 127, group = (threadIdx.x - CVT_WARP0 * 32) >> 7;
     uint32_t stage = 0, phase = 0, it_all = 0;
     bool ok = true;
     for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
@@ -249,57 +272,69 @@ gemm_tf32x3_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 0-3, both CTAs)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EPI_REGS));
+    // ------------------------------------------------------------ epilogue (warps 0-7, both CTAs)
+    // Warp w drains TMEM lanes 32 (w % 4) .. +31 (this CTA's tile rows) and the column half w / 4;
+    // the chunks of a tile are summed in registers, as in the single-CTA kernel.
+    constexpr int HALF_N = BN / 2;
+    const int lane_grp = warp & 3, col_half = warp >> 2;
     uint32_t acc_it = 0;
     bool ok = true;
     const bool alpha_is_one = p.alpha == 1.0f;
-    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++acc_it) {
+    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
       const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-      const uint32_t m0 = (rem / tiles_n) * 2 * BM + rank * BM, n0 = (rem % tiles_n) * BN;
-      const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
-      ok = mbar_wait_cluster(acc_full(buf), acc_phase, abort_flag, 256);
+      const uint32_t m0 = (rem / tiles_n) * 2 * BM + rank * BM, n0 = (rem % tiles_n) * BN + col_half * HALF_N;
+      float sum[HALF_N];
+#pragma unroll
+      for (int i = 0; i < HALF_N; ++i) sum[i] = 0.0f;
+      for (uint32_t kb0 = 0; ok && kb0 < k_blocks; kb0 += p.chunk_kb, ++acc_it) {
+        const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+        ok = mbar_wait_cluster(acc_full(buf), acc_phase, abort_flag, 256);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + buf * ACC_STRIDE + col_half * HALF_N + ((uint32_t)(lane_grp * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < HALF_N; c0 += 16) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) sum[c0 + i] += v[i];
+        }
+        tc_fence_before();
+        mbar_arrive_remote(leader_addr(acc_empty(buf)));
+      }
       if (!ok) break;
-      tc_fence_after();
-      const uint32_t row = m0 + warp * 32 + lane;
+      const uint32_t row = m0 + lane_grp * 32 + lane;
       const bool row_ok = row < p.m;
       const size_t row_off = (size_t)batch * p.stride_c + (size_t)row * p.n;
       float *__restrict__ crow = p.c + row_off;
       const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
-      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(warp * 32) << 16);
-      epi_dispatch_act(p.act, [&](auto act_tag) {
-        constexpr uint32_t ACT = decltype(act_tag)::value;
-  #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          float v[32];
-          tmem_ld32(taddr + c0, v);
-          const uint32_t col0 = n0 + c0;
-          if (row_ok && col0 < p.n) {
-  #pragma unroll
-            for (int q = 0; q < 32; q += 4) {
-              const uint32_t col = col0 + q;
-              if (col < p.n) {
-                float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-                if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-                if (p.accumulate) {
-                  const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
-                  o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
-                }
-                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
-                if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
-                if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
-                o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
-                o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
-                o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
-                o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
-                *reinterpret_cast<float4 *>(crow + col) = o;
+      if (row_ok) {
+        epi_dispatch_act(p.act, [&](auto act_tag) {
+          constexpr uint32_t ACT = decltype(act_tag)::value;
+#pragma unroll
+          for (int q = 0; q < HALF_N; q += 4) {
+            const uint32_t col = n0 + q;
+            if (col < p.n) {  // N % 4 == 0: a float4 is either fully in or fully out
+              float4 o = make_float4(sum[q], sum[q + 1], sum[q + 2], sum[q + 3]);
+              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+              if (p.accumulate) {
+                const float4 c_old = *reinterpret_cast<const float4 *>(crow + col);
+                o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
               }
+              float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+              if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+              if (drow) dv = *reinterpret_cast<const float4 *>(drow + col);
+              o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
+              o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
+              o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
+              o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
+              *reinterpret_cast<float4 *>(crow + col) = o;
             }
           }
-        }
-      });
-      tc_fence_before();
-      mbar_arrive_remote(leader_addr(acc_empty(buf)));
+        });
+      }
     }
   }
 
@@ -312,7 +347,7 @@ gemm_tf32x3_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap 
     __syncthreads();
   }
   cluster_sync_all();   // neither CTA frees tensor memory or leaves while the other may still use the pair
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc2(tmem_base, TMEM_COLS);
   }
@@ -324,7 +359,13 @@ bool gemm_tf32x3_pair_supported(const GemmParams &p, int sm_count) {
   return gemm_tf32x3_eligible(p) && sm_count >= 2;
 }
 
-void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p, uint32_t *status, cudaStream_t stream) {
+void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p_in, uint32_t *status, cudaStream_t stream) {
+  GemmParams p = p_in;
+  p.chunk_kb = CHUNK_KB;
+  if (const char *e = std::getenv("TA_TF32X3_CHUNK_KB")) {   // experiments: K blocks per accumulation
+    const int v = atoi(e);
+    if (v > 0) p.chunk_kb = (uint32_t)v;
+  }
   if (!gemm_tf32x3_pair_supported(p, ctx.sm_count))
     fail("paired tf32x3 GEMM needs f32 operands with K and N multiples of 4");
   static bool attr_set[64] = {};
@@ -336,9 +377,14 @@ void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p, uint32_t *
   const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
   encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.a, p.k, p.m, ba, (uint64_t)p.k * 4,
               p.stride_a ? (uint64_t)p.stride_a * 4 : (uint64_t)p.m * p.k * 4, BK, BM, CU_TENSOR_MAP_SWIZZLE_64B);
-  encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.b, p.n, p.k, bb, (uint64_t)p.n * 4,
-              p.stride_b ? (uint64_t)p.stride_b * 4 : (uint64_t)p.k * p.n * 4, 32, BK,
-              CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  const uint64_t b_batch_bytes = p.stride_b ? (uint64_t)p.stride_b * 4 : (uint64_t)p.k * p.n * 4;
+  p.b_grouped = p.n % 32 == 0 ? 1u : 0u;
+  if (p.b_grouped)   // one TMA per stage for this CTA's 128-column half of the B block
+    encode_map_grouped(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.b, 4, p.n, p.k, bb, b_batch_bytes, 32, BK,
+                       BNH / 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  else
+    encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.b, p.n, p.k, bb, (uint64_t)p.n * 4, b_batch_bytes, 32, BK,
+                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   const uint64_t tiles = (uint64_t)((p.m + 2 * BM - 1) / (2 * BM)) * ((p.n + BN - 1) / BN) * p.batch;
   const uint32_t pairs = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count / 2);
   cudaLaunchConfig_t cfg = {};
