@@ -5,9 +5,9 @@
  * model/forward/{mod,prefill,decode}.rs): the same op graphs -- prefill through
  * one mixed graph with fused causal attention, greedy decode through one
  * prepared (record-once, replay-many) graph whose position comes from a 4-byte
- * cell and whose next token is chosen and embedded on the device.  The GGUF
- * loader is not part of this build; weights are random-initialised from a seed
- * (the benchmark configuration is random-init).
+ * cell and whose next token is chosen and embedded on the device.  Weights come
+ * from an F32 / F16 GGUF file (ta_llama_load_gguf) or are random-initialised from
+ * a seed (the benchmark configuration is random-init).
  */
 #ifndef TENSOR_ASH_LLAMA_H
 #define TENSOR_ASH_LLAMA_H
@@ -52,7 +52,33 @@ ta_llama *ta_llama_create_random(const ta_executor *exec, const ta_llama_config 
  * sum.  Every rank ends a step with the same logits and the same greedy token.  `comm`
  * must outlive the model; all ranks must call prefill / decode in step. */
 ta_llama *ta_llama_create_random_tp(const ta_executor *exec, const ta_llama_config *cfg, const ta_comm *comm);
+/* The same runner on the weights of an F32 / F16 GGUF file of the llama architecture
+ * (ref tools/llama-ash/src/gguf.rs, model/load.rs:14-255): geometry from the llama.* metadata,
+ * vocabulary from token_embd.weight, t_max clamped to llama.context_length; linear weights are
+ * transposed to [n_in, n_out] and stored f16, norm weights must be f32, a missing output.weight
+ * ties the head to the embeddings, quantized tensor types are refused.  `comm` as above (NULL:
+ * one GPU).  weight_sigma / norm_jitter / seed of the reported config are zero. */
+ta_llama *ta_llama_load_gguf(const ta_executor *exec, const char *path, uint32_t t_max, const ta_comm *comm);
+int ta_llama_get_config(const ta_llama *model, ta_llama_config *out);
 void ta_llama_destroy(ta_llama *model);
+
+/* GGUF v2 / v3 inspection, host only (ref tools/llama-ash/src/gguf.rs:62-284).  Scalar and string
+ * metadata are kept, arrays are walked and dropped.  ta_gguf_meta_kind: 0 u64, 1 i64, 2 f64,
+ * 3 bool, 4 string, 5 skipped array, -1 absent.  ta_gguf_meta_u64 accepts unsigned and
+ * non-negative signed values; ta_gguf_meta_f64 returns `fallback` for an absent key.
+ * ta_gguf_tensor_info: ne[] in file order (ne[0] fastest), ggml type 0 = F32, 1 = F16, offset
+ * relative to the data section.  ta_gguf_read_f32 widens f16 exactly and refuses other types. */
+typedef struct ta_gguf ta_gguf;
+ta_gguf *ta_gguf_open(const char *path);
+void ta_gguf_close(ta_gguf *file);
+int ta_gguf_meta_kind(const ta_gguf *file, const char *key);
+int ta_gguf_meta_u64(const ta_gguf *file, const char *key, uint64_t *out);
+int ta_gguf_meta_f64(const ta_gguf *file, const char *key, double fallback, double *out);
+int ta_gguf_meta_str(const ta_gguf *file, const char *key, char *buf, size_t cap);
+int ta_gguf_tensor_info(const ta_gguf *file, const char *name, uint64_t ne[4], uint32_t *n_dims,
+                        uint32_t *ggml_type, uint64_t *offset);
+int ta_gguf_read_f32(ta_gguf *file, const char *name, float *out, size_t len);
+uint64_t ta_gguf_data_start(const ta_gguf *file);
 
 /* Forget the KV cache: the next prefill starts at position 0. */
 int ta_llama_reset(ta_llama *model);

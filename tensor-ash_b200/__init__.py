@@ -43,4 +43,4 @@ from .api import (  # noqa: F401
     version,
 )
 from .capi import lib, lib_path  # noqa: F401
-from .llama import Llama, LlamaConfig, shard_plan  # noqa: F401
+from .llama import GgufFile, Llama, LlamaConfig, shard_plan, write_gguf  # noqa: F401

@@ -21,6 +21,7 @@ LIB = os.path.join(LIB_DIR, "libtensor_ash.so")
 
 SOURCES = [
     "ta_host.cpp",
+    "gguf.cpp",
     "ta_runtime.cu",
     "ta_graph.cu",
     "ta_capi.cu",

@@ -180,6 +180,18 @@ SIGNATURES = {
     # ---- tensor_ash_llama.h
     "ta_llama_create_random": (_P, [_P, C.POINTER(LlamaConfigC)]),
     "ta_llama_create_random_tp": (_P, [_P, C.POINTER(LlamaConfigC), _P]),
+    "ta_llama_load_gguf": (_P, [_P, C.c_char_p, _U32, _P]),
+    "ta_llama_get_config": (C.c_int, [_P, C.POINTER(LlamaConfigC)]),
+    "ta_gguf_open": (_P, [C.c_char_p]),
+    "ta_gguf_close": (None, [_P]),
+    "ta_gguf_meta_kind": (C.c_int, [_P, C.c_char_p]),
+    "ta_gguf_meta_u64": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "ta_gguf_meta_f64": (C.c_int, [_P, C.c_char_p, C.c_double, C.POINTER(C.c_double)]),
+    "ta_gguf_meta_str": (C.c_int, [_P, C.c_char_p, C.c_char_p, _SZ]),
+    "ta_gguf_tensor_info": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(_U32), C.POINTER(_U32),
+                                      C.POINTER(C.c_uint64)]),
+    "ta_gguf_read_f32": (C.c_int, [_P, C.c_char_p, _P, _SZ]),
+    "ta_gguf_data_start": (C.c_uint64, [_P]),
     "ta_llama_destroy": (None, [_P]),
     "ta_llama_reset": (C.c_int, [_P]),
     "ta_llama_prefill": (C.c_int, [_P, C.POINTER(_U32), _U32, C.POINTER(_U32), _STATS]),

@@ -15,11 +15,14 @@
 #include <cmath>
 #include <cstring>
 #include <array>
+#include <memory>
+#include <string>
 #include <thread>
 
 #pragma GCC visibility push(default)
 #include "../../include/tensor_ash_llama.h"
 #pragma GCC visibility pop
+#include "gguf.hpp"
 #include "ta_handles.hpp"
 
 namespace {
@@ -97,6 +100,92 @@ std::vector<uint16_t> slice_rows(const std::vector<uint16_t> &src, size_t cols, 
   return std::vector<uint16_t>(src.begin() + r0 * cols, src.begin() + (r0 + h) * cols);
 }
 
+// Where a model's weights come from.  Linear weights are handed over as f16 bits in the
+// [n_in, n_out] layout every GEMM / GEMV here reads; ids follow include/tensor_ash_llama.h
+// (0 embedding, 1 output norm, 2 lm_head, 16 + 16 L + {0 attn_norm, 1 wq, 2 wk, 3 wv, 4 wo,
+// 5 ffn_norm, 6 w_gate, 7 w_up, 8 w_down}).
+struct WeightSource {
+  virtual ~WeightSource() = default;
+  virtual std::vector<uint16_t> linear(uint32_t id, uint32_t n_in, uint32_t n_out) = 0;
+  virtual std::vector<uint16_t> embedding_f16(uint32_t vocab, uint32_t embd) = 0;
+  virtual bool embedding_is_f32() const { return false; }
+  virtual std::vector<float> embedding_f32(uint32_t, uint32_t) { return {}; }
+  virtual std::vector<float> norm(uint32_t id, uint32_t n) = 0;
+};
+
+struct RandomSource : WeightSource {
+  uint64_t seed;
+  double sigma;
+  float jitter;
+  RandomSource(uint64_t s, double sg, float j) : seed(s), sigma(sg), jitter(j) {}
+  std::vector<uint16_t> linear(uint32_t id, uint32_t n_in, uint32_t n_out) override {
+    return gen_weight_f16(seed, id, (size_t)n_in * n_out, sigma);
+  }
+  std::vector<uint16_t> embedding_f16(uint32_t vocab, uint32_t embd) override {
+    return gen_weight_f16(seed, 0, (size_t)vocab * embd, sigma);
+  }
+  std::vector<float> norm(uint32_t id, uint32_t n) override {
+    std::vector<float> w(n, 1.0f);
+    if (jitter != 0.0f) {
+      std::vector<float> u(n);
+      fill_uniform_chunk(u.data(), u.size(), chunk_seed(seed, id, 0));
+      for (size_t i = 0; i < w.size(); ++i) w[i] = 1.0f + jitter * u[i];
+    }
+    return w;
+  }
+};
+
+// GGUF tensors (tools/llama-ash/src/model/load.rs:104-232): a linear weight `y = W x` is stored
+// with ne = [n_in, n_out], i.e. n_out rows of n_in values, and is transposed to [n_in, n_out];
+// f32 payloads round to f16 (nearest even), f16 payloads are taken bit for bit.  A file without
+// output.weight ties the lm_head to the embedding table.
+struct GgufSource : WeightSource {
+  GgufFile &g;
+  explicit GgufSource(GgufFile &file) : g(file) {}
+  static std::string name_of(uint32_t id) {
+    if (id == 1) return "output_norm.weight";
+    if (id == 2) return "output.weight";
+    const uint32_t layer = (id - 16) / 16, part = (id - 16) % 16;
+    static const char *parts[9] = {"attn_norm", "attn_q", "attn_k", "attn_v", "attn_output",
+                                   "ffn_norm", "ffn_gate", "ffn_up", "ffn_down"};
+    if (id < 16 || part > 8) fail("internal error: no GGUF tensor for weight id %u", id);
+    return "blk." + std::to_string(layer) + "." + parts[part] + ".weight";
+  }
+  static std::vector<uint16_t> transposed(const std::vector<uint16_t> &src, size_t rows, size_t cols) {
+    std::vector<uint16_t> out(src.size());   // [rows, cols] -> [cols, rows], blocked for the cache
+    constexpr size_t B = 64;
+    for (size_t r0 = 0; r0 < rows; r0 += B)
+      for (size_t c0 = 0; c0 < cols; c0 += B)
+        for (size_t r = r0; r < std::min(rows, r0 + B); ++r)
+          for (size_t c = c0; c < std::min(cols, c0 + B); ++c) out[c * rows + r] = src[r * cols + c];
+    return out;
+  }
+  std::vector<uint16_t> linear(uint32_t id, uint32_t n_in, uint32_t n_out) override {
+    if (id == 2 && !g.has_tensor("output.weight"))   // tied head: embedding [vocab, embd] -> [embd, vocab]
+      return transposed(embedding_f16(n_out, n_in), n_out, n_in);
+    const std::string name = name_of(id);
+    const GgufTensorInfo &ti = g.info(name);
+    if (ti.ne != std::vector<uint64_t>{n_in, n_out})
+      fail("%s: ne [%s] != expected [%u, %u]", name.c_str(), ne_str(ti).c_str(), n_in, n_out);
+    return transposed(g.read_f16_bits(name), n_out, n_in);
+  }
+  std::vector<uint16_t> embedding_f16(uint32_t, uint32_t) override { return g.read_f16_bits("token_embd.weight"); }
+  bool embedding_is_f32() const override { return g.info("token_embd.weight").ggml_type == GGML_TYPE_F32; }
+  std::vector<float> embedding_f32(uint32_t, uint32_t) override { return g.read_f32("token_embd.weight"); }
+  std::vector<float> norm(uint32_t id, uint32_t n) override {
+    const std::string name = name_of(id);
+    const GgufTensorInfo &ti = g.info(name);
+    if (ti.ne != std::vector<uint64_t>{n} || ti.ggml_type != GGML_TYPE_F32)
+      fail("%s: expected f32 [%u], got ne [%s] type %u", name.c_str(), n, ne_str(ti).c_str(), ti.ggml_type);
+    return g.read_f32(name);
+  }
+  static std::string ne_str(const GgufTensorInfo &ti) {
+    std::string s;
+    for (size_t i = 0; i < ti.ne.size(); ++i) s += (i ? ", " : "") + std::to_string(ti.ne[i]);
+    return s;
+  }
+};
+
 struct Layer {
   Tensor attn_norm, ffn_norm;
   Tensor wq_p, wk_p, wv_p, w_qkv, wo, w_gate, w_up, w_gate_p, w_up_p, w_down;
@@ -142,13 +231,8 @@ Tensor upload_bits(ta_llama &m, const std::vector<uint16_t> &bits, uint32_t rows
   return t;
 }
 
-Tensor norm_weight(ta_llama &m, uint32_t id) {
-  std::vector<float> w(m.cfg.embd, 1.0f);
-  if (m.cfg.norm_jitter != 0.0f) {
-    std::vector<float> u(m.cfg.embd);
-    fill_uniform_chunk(u.data(), u.size(), chunk_seed(m.cfg.seed, id, 0));
-    for (size_t i = 0; i < w.size(); ++i) w[i] = 1.0f + m.cfg.norm_jitter * u[i];
-  }
+Tensor norm_weight(ta_llama &m, WeightSource &src, uint32_t id) {
+  const std::vector<float> w = src.norm(id, m.cfg.embd);
   Tensor t = make(m.ctx, {m.cfg.embd}, DType::F32);
   m.exec->upload(w.data(), w.size(), t);
   return t;
@@ -174,13 +258,13 @@ ta_llama::~ta_llama() {
 // ------------------------------------------------------------------ construction
 namespace {
 
-void build_model(ta_llama &m) {
+void build_model(ta_llama &m, WeightSource &src) {
   const ta_llama_config &c = m.cfg;
   if (!c.layers || !c.embd || !c.heads || !c.kv_heads || !c.head_dim || !c.ffn || !c.vocab || !c.t_max)
-    fail("ta_llama_create_random: every config dimension must be non-zero");
-  if (c.heads * c.head_dim != c.embd) fail("ta_llama_create_random: heads * head_dim must equal embd");
-  if (c.heads % c.kv_heads || c.heads / c.kv_heads > 8) fail("ta_llama_create_random: GQA group must be 1..8");
-  if (c.head_dim != 64) fail("ta_llama_create_random: head_dim must be 64 (decode attention variant)");
+    fail("ta_llama_create: every config dimension must be non-zero");
+  if (c.heads * c.head_dim != c.embd) fail("ta_llama_create: heads * head_dim must equal embd");
+  if (c.heads % c.kv_heads || c.heads / c.kv_heads > 8) fail("ta_llama_create: GQA group must be 1..8");
+  if (c.head_dim != 64) fail("ta_llama_create: head_dim must be 64 (decode attention variant)");
   const uint32_t kv_dim = c.kv_heads * c.head_dim;
   // Tensor-parallel shard (world 1 keeps everything): query heads and the MLP width split
   // evenly; kv heads split, or are shared by W / kv_heads neighbouring ranks when there are
@@ -200,18 +284,21 @@ void build_model(ta_llama &m) {
   if (m.heads_l % m.kv_l || m.heads_l / m.kv_l > 8) fail("ta_llama_create: local GQA group must be 1..8");
   const uint32_t n_qkv = m.q_w + 2 * m.kv_w;
   for (uint32_t n : {c.embd, kv_dim, c.ffn, c.vocab, m.q_w, m.kv_w, m.ffn_l, m.vocab_l})
-    if (n % 32) fail("ta_llama_create_random: projection widths must be multiples of 32 (got %u)", n);
-  const double sigma = c.weight_sigma;
-  const uint64_t seed = c.seed;
+    if (n % 32) fail("ta_llama_create: projection widths must be multiples of 32 (got %u)", n);
   auto tile = [](uint32_t k, uint32_t n) { return f16w_row_tile_n(k, n); };
   const size_t q0 = (size_t)R * m.q_w, kv0 = (size_t)m.kv_first * c.head_dim, f0 = (size_t)R * m.ffn_l,
                v0 = (size_t)R * m.vocab_l;
 
   {  // token embedding [vocab, embd] (replicated), final norm, lm_head columns [embd, vocab_l]
-    auto e = gen_weight_f16(seed, 0, (size_t)c.vocab * c.embd, sigma);
-    m.embd = upload_bits(m, e, c.vocab, c.embd);
-    m.output_norm = norm_weight(m, 1);
-    auto h = slice_cols(gen_weight_f16(seed, 2, (size_t)c.embd * c.vocab, sigma), c.embd, c.vocab, v0, m.vocab_l);
+    if (src.embedding_is_f32()) {   // an f32 model file keeps its embedding rows in f32 (model/load.rs:205-214)
+      const std::vector<float> e = src.embedding_f32(c.vocab, c.embd);
+      m.embd = make(m.ctx, {c.vocab, c.embd}, DType::F32);
+      m.exec->upload(e.data(), e.size(), m.embd);
+    } else {
+      m.embd = upload_bits(m, src.embedding_f16(c.vocab, c.embd), c.vocab, c.embd);
+    }
+    m.output_norm = norm_weight(m, src, 1);
+    auto h = slice_cols(src.linear(2, c.embd, c.vocab), c.embd, c.vocab, v0, m.vocab_l);
     m.lm_head = upload_bits(m, h, c.embd, m.vocab_l);
     m.lm_head_p = upload_bits(m, pack_bits(h, c.embd, m.vocab_l, tile(c.embd, m.vocab_l)), c.embd, m.vocab_l);
   }
@@ -219,11 +306,11 @@ void build_model(ta_llama &m) {
   for (uint32_t li = 0; li < c.layers; ++li) {
     Layer &L = m.layers[li];
     const uint32_t base = 16 + 16 * li;
-    L.attn_norm = norm_weight(m, base + 0);
-    L.ffn_norm = norm_weight(m, base + 5);
-    auto wq = slice_cols(gen_weight_f16(seed, base + 1, (size_t)c.embd * c.embd, sigma), c.embd, c.embd, q0, m.q_w);
-    auto wk = slice_cols(gen_weight_f16(seed, base + 2, (size_t)c.embd * kv_dim, sigma), c.embd, kv_dim, kv0, m.kv_w);
-    auto wv = slice_cols(gen_weight_f16(seed, base + 3, (size_t)c.embd * kv_dim, sigma), c.embd, kv_dim, kv0, m.kv_w);
+    L.attn_norm = norm_weight(m, src, base + 0);
+    L.ffn_norm = norm_weight(m, src, base + 5);
+    auto wq = slice_cols(src.linear(base + 1, c.embd, c.embd), c.embd, c.embd, q0, m.q_w);
+    auto wk = slice_cols(src.linear(base + 2, c.embd, kv_dim), c.embd, kv_dim, kv0, m.kv_w);
+    auto wv = slice_cols(src.linear(base + 3, c.embd, kv_dim), c.embd, kv_dim, kv0, m.kv_w);
     L.wq_p = upload_bits(m, pack_bits(wq, c.embd, m.q_w, tile(c.embd, m.q_w)), c.embd, m.q_w);
     L.wk_p = upload_bits(m, pack_bits(wk, c.embd, m.kv_w, tile(c.embd, m.kv_w)), c.embd, m.kv_w);
     L.wv_p = upload_bits(m, pack_bits(wv, c.embd, m.kv_w, tile(c.embd, m.kv_w)), c.embd, m.kv_w);
@@ -236,15 +323,15 @@ void build_model(ta_llama &m) {
       }
       L.w_qkv = upload_bits(m, cat, c.embd, n_qkv);
     }
-    L.wo = upload_bits(m, slice_rows(gen_weight_f16(seed, base + 4, (size_t)c.embd * c.embd, sigma), c.embd, q0, m.q_w),
+    L.wo = upload_bits(m, slice_rows(src.linear(base + 4, c.embd, c.embd), c.embd, q0, m.q_w),
                        m.q_w, c.embd);
-    auto wg = slice_cols(gen_weight_f16(seed, base + 6, (size_t)c.embd * c.ffn, sigma), c.embd, c.ffn, f0, m.ffn_l);
-    auto wu = slice_cols(gen_weight_f16(seed, base + 7, (size_t)c.embd * c.ffn, sigma), c.embd, c.ffn, f0, m.ffn_l);
+    auto wg = slice_cols(src.linear(base + 6, c.embd, c.ffn), c.embd, c.ffn, f0, m.ffn_l);
+    auto wu = slice_cols(src.linear(base + 7, c.embd, c.ffn), c.embd, c.ffn, f0, m.ffn_l);
     L.w_gate = upload_bits(m, wg, c.embd, m.ffn_l);
     L.w_up = upload_bits(m, wu, c.embd, m.ffn_l);
     L.w_gate_p = upload_bits(m, pack_bits(wg, c.embd, m.ffn_l, tile(c.embd, m.ffn_l)), c.embd, m.ffn_l);
     L.w_up_p = upload_bits(m, pack_bits(wu, c.embd, m.ffn_l, tile(c.embd, m.ffn_l)), c.embd, m.ffn_l);
-    L.w_down = upload_bits(m, slice_rows(gen_weight_f16(seed, base + 8, (size_t)c.ffn * c.embd, sigma), c.embd, f0, m.ffn_l),
+    L.w_down = upload_bits(m, slice_rows(src.linear(base + 8, c.ffn, c.embd), c.embd, f0, m.ffn_l),
                            m.ffn_l, c.embd);
     L.kt_cache = make(m.ctx, {m.kv_l, c.head_dim, c.t_max}, DType::F16);
     L.v_cache = make(m.ctx, {m.kv_l, c.t_max, c.head_dim}, DType::F16);
@@ -561,13 +648,155 @@ ta_llama *ta_llama_create_random_tp(const ta_executor *exec, const ta_llama_conf
     m->exec = exec->exec.get();
     m->cfg = *cfg;
     m->ctx->make_current();
-    build_model(*m);
+    RandomSource src(cfg->seed, cfg->weight_sigma, cfg->norm_jitter);
+    build_model(*m, src);
   });
   if (rc != 0) {
     delete m;
     return nullptr;
   }
   return m;
+}
+
+// ------------------------------------------------------------------ GGUF inspection (host only)
+struct ta_gguf {
+  std::unique_ptr<GgufFile> file;
+};
+
+ta_gguf *ta_gguf_open(const char *path) {
+  ta_gguf *h = nullptr;
+  const int rc = guarded([&]() {
+    if (!path) fail("ta_gguf_open: path is null");
+    h = new ta_gguf;
+    h->file.reset(new GgufFile(path));
+  });
+  if (rc != 0) {
+    delete h;
+    return nullptr;
+  }
+  return h;
+}
+
+void ta_gguf_close(ta_gguf *file) {
+  ta_set_last_error("");
+  delete file;
+}
+
+int ta_gguf_meta_kind(const ta_gguf *file, const char *key) {
+  int kind = -1;
+  guarded([&]() {
+    if (!file || !key) fail("ta_gguf_meta_kind: file or key is null");
+    if (const GgufValue *v = file->file->find(key)) kind = (int)v->kind;
+  });
+  return kind;
+}
+
+int ta_gguf_meta_u64(const ta_gguf *file, const char *key, uint64_t *out) {
+  return guarded([&]() {
+    if (!file || !key || !out) fail("ta_gguf_meta_u64: null argument");
+    *out = file->file->require_u64(key);
+  });
+}
+
+int ta_gguf_meta_f64(const ta_gguf *file, const char *key, double fallback, double *out) {
+  return guarded([&]() {
+    if (!file || !key || !out) fail("ta_gguf_meta_f64: null argument");
+    *out = file->file->f64_or(key, fallback);
+  });
+}
+
+int ta_gguf_meta_str(const ta_gguf *file, const char *key, char *buf, size_t cap) {
+  return guarded([&]() {
+    if (!file || !key || !buf || !cap) fail("ta_gguf_meta_str: null argument");
+    const GgufValue *v = file->file->find(key);
+    if (!v || v->kind != GgufValue::Str) fail("GGUF metadata missing string key %s", key);
+    if (v->s.size() + 1 > cap) fail("ta_gguf_meta_str: value of %zu bytes does not fit %zu", v->s.size(), cap);
+    memcpy(buf, v->s.c_str(), v->s.size() + 1);
+  });
+}
+
+int ta_gguf_tensor_info(const ta_gguf *file, const char *name, uint64_t ne[4], uint32_t *n_dims,
+                        uint32_t *ggml_type, uint64_t *offset) {
+  return guarded([&]() {
+    if (!file || !name || !ne || !n_dims) fail("ta_gguf_tensor_info: null argument");
+    const GgufTensorInfo &ti = file->file->info(name);
+    *n_dims = (uint32_t)ti.ne.size();
+    for (size_t i = 0; i < 4; ++i) ne[i] = i < ti.ne.size() ? ti.ne[i] : 1;
+    if (ggml_type) *ggml_type = ti.ggml_type;
+    if (offset) *offset = ti.offset;
+  });
+}
+
+int ta_gguf_read_f32(ta_gguf *file, const char *name, float *out, size_t len) {
+  return guarded([&]() {
+    if (!file || !name || !out) fail("ta_gguf_read_f32: null argument");
+    const std::vector<float> v = file->file->read_f32(name);
+    if (v.size() != len) fail("ta_gguf_read_f32: tensor %s has %zu elements, buffer holds %zu", name, v.size(), len);
+    memcpy(out, v.data(), len * 4);
+  });
+}
+
+uint64_t ta_gguf_data_start(const ta_gguf *file) { return file ? file->file->data_start() : 0; }
+
+// tools/llama-ash/src/model/load.rs:14-120: architecture and geometry from the metadata, the
+// vocabulary from the embedding tensor, t_max clamped to the model's context length.
+ta_llama *ta_llama_load_gguf(const ta_executor *exec, const char *path, uint32_t t_max, const ta_comm *comm) {
+  ta_llama *m = nullptr;
+  const int rc = guarded([&]() {
+    if (!exec) fail("ta_llama_load_gguf: exec is null");
+    if (!path) fail("ta_llama_load_gguf: path is null");
+    if (!t_max) fail("ta_llama_load_gguf: t_max must be non-zero");
+    GgufFile g(path);
+    const GgufValue *arch = g.find("general.architecture");
+    if (!arch || arch->kind != GgufValue::Str) fail("GGUF missing general.architecture");
+    if (arch->s != "llama") fail("unsupported architecture %s (want llama)", arch->s.c_str());
+    ta_llama_config c{};
+    c.layers = (uint32_t)g.require_u64("llama.block_count");
+    c.embd = (uint32_t)g.require_u64("llama.embedding_length");
+    c.heads = (uint32_t)g.require_u64("llama.attention.head_count");
+    uint64_t kvh = c.heads;
+    g.get_u64("llama.attention.head_count_kv", &kvh);
+    c.kv_heads = (uint32_t)kvh;
+    c.ffn = (uint32_t)g.require_u64("llama.feed_forward_length");
+    const uint32_t ctx_len = (uint32_t)g.require_u64("llama.context_length");
+    c.rms_eps = (float)g.f64_or("llama.attention.layer_norm_rms_epsilon", 1e-5);
+    c.rope_theta = (float)g.f64_or("llama.rope.freq_base", 10000.0);
+    if (!c.heads || c.embd % c.heads) fail("bad head geometry (embd %u, heads %u)", c.embd, c.heads);
+    if (!c.kv_heads || c.heads % c.kv_heads) fail("heads must divide by kv_heads (%u / %u)", c.heads, c.kv_heads);
+    c.head_dim = c.embd / c.heads;
+    c.t_max = std::min(t_max, ctx_len);
+    const GgufTensorInfo &ei = g.info("token_embd.weight");
+    if (ei.ne.size() != 2 || ei.ne[0] != c.embd)
+      fail("token_embd.weight ne [%s] does not match embd %u", GgufSource::ne_str(ei).c_str(), c.embd);
+    c.vocab = (uint32_t)ei.ne[1];
+    m = new ta_llama;
+    m->prefill_full.reset(new PrefillScratch);
+    if (comm) {
+      if (comm->comm->ctx.get() != exec->ctx.get()) fail("ta_llama_load_gguf: comm belongs to a different context");
+      m->comm = comm->comm.get();
+      m->rank = comm->comm->rank;
+      m->world = comm->comm->world;
+    }
+    m->ctx = exec->ctx;
+    m->exec = exec->exec.get();
+    m->cfg = c;
+    m->ctx->make_current();
+    GgufSource src(g);
+    build_model(*m, src);
+  });
+  if (rc != 0) {
+    delete m;
+    return nullptr;
+  }
+  return m;
+}
+
+int ta_llama_get_config(const ta_llama *model, ta_llama_config *out) {
+  return guarded([&]() {
+    if (!model) fail("ta_llama_get_config: model is null");
+    if (!out) fail("ta_llama_get_config: out is null");
+    *out = model->cfg;
+  });
 }
 
 void ta_llama_destroy(ta_llama *model) {

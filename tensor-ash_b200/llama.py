@@ -2,8 +2,10 @@
 
 Mirrors the reference's ``tools/llama-ash`` model object (``model/mod.rs:59-190``):
 ``prefill`` submits one mixed graph, ``decode`` replays one prepared graph per
-token.  Weights are random-initialised from a seed; ``weight_stream`` documents
-the generator so a checker can rebuild any tensor on the host.
+token.  Weights are random-initialised from a seed (``weight_stream`` documents
+the generator so a checker can rebuild any tensor on the host) or loaded from an
+F32 / F16 GGUF file (``Llama.load_gguf``; ``GgufFile`` / ``write_gguf`` read and
+write the container on the host).
 """
 from __future__ import annotations
 
@@ -81,6 +83,20 @@ class Llama:
             raise TensorAshError(_err())
         self._h, self._exec, self.cfg, self._comm = h, exec_, cfg, comm
 
+    @classmethod
+    def load_gguf(cls, exec_: Executor, path: str, t_max: int = 2048, comm=None) -> "Llama":
+        """Load an F32 / F16 llama GGUF (``tools/llama-ash/src/model/load.rs``); the geometry comes
+        from the file's metadata and ``t_max`` is clamped to its context length."""
+        h = capi.lib().ta_llama_load_gguf(exec_._h, str(path).encode(), t_max, comm._h if comm is not None else None)
+        if not h:
+            raise TensorAshError(_err())
+        c = capi.LlamaConfigC()
+        _check(capi.lib().ta_llama_get_config(h, C.byref(c)))
+        self = cls.__new__(cls)
+        cfg = LlamaConfig(*(getattr(c, name) for name, _ in capi.LlamaConfigC._fields_))
+        self._h, self._exec, self.cfg, self._comm = h, exec_, cfg, comm
+        return self
+
     def reset(self) -> None:
         _check(capi.lib().ta_llama_reset(self._h))
 
@@ -120,3 +136,125 @@ class Llama:
             self.close()
         except Exception:
             pass
+
+
+# ---------------------------------------------------------------------------- GGUF on the host
+GGML_TYPE_F32, GGML_TYPE_F16 = 0, 1
+_GGUF_KINDS = {0: "u64", 1: "i64", 2: "f64", 3: "bool", 4: "str", 5: "skipped"}
+
+
+class GgufFile:
+    """Read-only view of a GGUF v2 / v3 file (``tools/llama-ash/src/gguf.rs``): scalar and string
+    metadata, tensor infos, F32 / F16 payloads as float32.  Needs no GPU."""
+
+    def __init__(self, path: str):
+        self._h = capi.lib().ta_gguf_open(str(path).encode())
+        if not self._h:
+            raise TensorAshError(_err())
+
+    def kind(self, key: str):
+        """'u64' | 'i64' | 'f64' | 'bool' | 'str' | 'skipped' (an array, not kept) | None (absent)."""
+        return _GGUF_KINDS.get(capi.lib().ta_gguf_meta_kind(self._h, key.encode()))
+
+    def require_u64(self, key: str) -> int:
+        v = C.c_uint64(0)
+        _check(capi.lib().ta_gguf_meta_u64(self._h, key.encode(), C.byref(v)))
+        return int(v.value)
+
+    def f64_or(self, key: str, fallback: float) -> float:
+        v = C.c_double(0.0)
+        _check(capi.lib().ta_gguf_meta_f64(self._h, key.encode(), fallback, C.byref(v)))
+        return float(v.value)
+
+    def string(self, key: str) -> str:
+        buf = C.create_string_buffer(1 << 16)
+        _check(capi.lib().ta_gguf_meta_str(self._h, key.encode(), buf, len(buf)))
+        return buf.value.decode()
+
+    def info(self, name: str) -> Tuple[List[int], int, int]:
+        """(ne in file order, ggml type, offset within the data section)."""
+        ne, nd, ty, off = (C.c_uint64 * 4)(), C.c_uint32(0), C.c_uint32(0), C.c_uint64(0)
+        _check(capi.lib().ta_gguf_tensor_info(self._h, name.encode(), ne, C.byref(nd), C.byref(ty), C.byref(off)))
+        return [int(ne[i]) for i in range(nd.value)], int(ty.value), int(off.value)
+
+    def read_f32(self, name: str) -> np.ndarray:
+        ne, _, _ = self.info(name)
+        out = np.empty(int(np.prod(ne, dtype=np.int64)), dtype=np.float32)
+        _check(capi.lib().ta_gguf_read_f32(self._h, name.encode(), out.ctypes.data, out.size))
+        return out
+
+    @property
+    def data_start(self) -> int:
+        return int(capi.lib().ta_gguf_data_start(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            capi.lib().ta_gguf_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def write_gguf(path: str, metadata: dict, tensors: dict, alignment: int = 32, version: int = 3) -> None:
+    """Write a GGUF file.  ``metadata`` values: ``str``, ``bool``, ``int`` (u32 when it fits, else
+    u64; negative: i32 / i64), ``float`` (f32), ``("f64", x)``, ``("u64", x)``, or a list of ``str`` /
+    ``float`` (written as an array).  ``tensors``: name -> ndarray of float32 (F32) or float16 (F16);
+    the array's C-order shape is [..., n1, n0], stored as ne = [n0, n1, ...]."""
+    import struct
+
+    def s(x: str) -> bytes:
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    def value(v) -> bytes:
+        if isinstance(v, tuple):
+            tag, x = v
+            return {"f64": lambda: struct.pack("<Id", 12, x), "u64": lambda: struct.pack("<IQ", 10, x),
+                    "i64": lambda: struct.pack("<Iq", 11, x), "u8": lambda: struct.pack("<IB", 0, x),
+                    "i16": lambda: struct.pack("<Ih", 3, x)}[tag]()
+        if isinstance(v, bool):
+            return struct.pack("<IB", 7, int(v))
+        if isinstance(v, str):
+            return struct.pack("<I", 8) + s(v)
+        if isinstance(v, int):
+            if v < 0:
+                return struct.pack("<Ii", 5, v) if v >= -2 ** 31 else struct.pack("<Iq", 11, v)
+            return struct.pack("<II", 4, v) if v < 2 ** 32 else struct.pack("<IQ", 10, v)
+        if isinstance(v, float):
+            return struct.pack("<If", 6, v)
+        if isinstance(v, (list, tuple)):
+            if all(isinstance(e, str) for e in v):
+                return struct.pack("<IIQ", 9, 8, len(v)) + b"".join(s(e) for e in v)
+            return struct.pack("<IIQ", 9, 6, len(v)) + b"".join(struct.pack("<f", float(e)) for e in v)
+        raise TypeError(f"unsupported GGUF metadata value {v!r}")
+
+    if alignment != 32 and "general.alignment" not in metadata:
+        metadata = {**metadata, "general.alignment": alignment}
+    head = b"GGUF" + struct.pack("<IQQ", version, len(tensors), len(metadata))
+    for k, v in metadata.items():
+        head += s(k) + value(v)
+    blobs, offset = [], 0
+    for name, arr in tensors.items():
+        arr = np.ascontiguousarray(arr)
+        if arr.dtype == np.float32:
+            ty = GGML_TYPE_F32
+        elif arr.dtype == np.float16:
+            ty = GGML_TYPE_F16
+        else:
+            raise TypeError(f"tensor {name}: dtype {arr.dtype} is not float32 / float16")
+        ne = list(reversed(arr.shape))
+        head += s(name) + struct.pack("<I", len(ne)) + b"".join(struct.pack("<Q", d) for d in ne)
+        head += struct.pack("<IQ", ty, offset)
+        raw = arr.tobytes()
+        pad = (-len(raw)) % alignment
+        blobs.append(raw + b"\0" * pad)
+        offset += len(raw) + pad
+    head += b"\0" * ((-len(head)) % alignment)
+    with open(path, "wb") as f:
+        f.write(head)
+        for b in blobs:
+            f.write(b)
