@@ -223,3 +223,55 @@ def test_gguf_model_errors(gpu, tmp_path):
     ta.write_gguf(path, meta, t)
     with pytest.raises(ta.TensorAshError, match=r"blk.1.attn_k.weight: ne \[224, 128\] != expected \[256, 128\]"):
         ta.Llama.load_gguf(ex, path)
+
+
+# ---------------------------------------------------------------------------- the llama_ash tool
+def llama_ash(*args):
+    import os
+    import subprocess
+    import __graft_entry__ as entry
+    exe = os.path.join(entry.PKG_DIR, "bin", "llama_ash")
+    if not os.path.exists(exe):
+        entry.build()
+    return subprocess.run([exe, *args], capture_output=True, text=True, timeout=300)
+
+
+def test_llama_ash_cli_rejects_bad_command_lines():
+    """tools/llama-ash/src/main.rs:26-66: unknown flags and subcommands, missing values, missing model."""
+    r = llama_ash()
+    assert r.returncode != 0 and "usage:" in r.stderr
+    r = llama_ash("bench")
+    assert r.returncode != 0 and "missing -m <gguf>" in r.stderr
+    r = llama_ash("bench", "-m", "x.gguf", "--bogus", "1")
+    assert r.returncode != 0 and "unknown flag --bogus" in r.stderr
+    r = llama_ash("bench", "-m")
+    assert r.returncode != 0 and "flag -m needs a value" in r.stderr
+    r = llama_ash("bench", "-m", "x.gguf", "--pp", "many")
+    assert r.returncode != 0 and "--pp" in r.stderr
+    r = llama_ash("train", "-m", "x.gguf")
+    assert r.returncode != 0 and "unknown subcommand train" in r.stderr
+
+
+@pytest.mark.gpu
+def test_llama_ash_cli_generates_the_library_tokens_and_prints_the_bench_table(gpu, tmp_path):
+    ta, ctx, ex = gpu
+    rng = np.random.default_rng(11)
+    path = str(tmp_path / "tiny.gguf")
+    tiny_model_file(ta, path, rng)
+    prompt = [1, 7, 300, 42, 5]
+    m = ta.Llama.load_gguf(ex, path, t_max=96)
+    first, _ = m.prefill(prompt)
+    rest, _ = m.decode(first, 7)
+    m.close()
+    r = llama_ash("generate", "-m", path, "--ids", ", ".join(map(str, prompt)), "-n", "8", "--ctx", "96")
+    assert r.returncode == 0, r.stderr
+    lines = dict(l.split(":", 1) for l in r.stdout.strip().splitlines())
+    assert lines["prompt_ids   "].strip() == ",".join(map(str, prompt))
+    assert lines["generated_ids"].strip() == ",".join(map(str, [first] + rest))
+    r = llama_ash("bench", "-m", path, "--pp", "40", "--tg", "16", "--ctx", "96")
+    assert r.returncode == 0, r.stderr
+    assert "| pp40 " in r.stdout and "| tg16 " in r.stdout and "tokens/s" in r.stdout
+    r = llama_ash("bench", "-m", path, "--pp", "90", "--tg", "16", "--ctx", "96")
+    assert r.returncode != 0 and "exceeds context 96" in r.stderr
+    r = llama_ash("generate", "-m", path, "--ids", "1,99999")
+    assert r.returncode != 0 and "outside the vocabulary" in r.stderr
