@@ -497,6 +497,8 @@ float ta_f16_bits_to_f32(uint16_t bits);
  * CUDA device pointer of a tensor and the CUDA device ordinal of a context. */
 void *ta_tensor_device_ptr(const ta_tensor *tensor);
 int ta_context_device_index(const ta_context *ctx);
+/* Device name as the driver reports it (valid while the context lives); "" for NULL. */
+const char *ta_context_device_name(const ta_context *ctx);
 
 /* Kernels launched by this library on the calling process since load; a
  * caller can difference it around a region to count launches. */

@@ -99,6 +99,10 @@ class Context:
     def device_index(self) -> int:
         return int(lib().ta_context_device_index(self._h))
 
+    @property
+    def device_name(self) -> str:
+        return (lib().ta_context_device_name(self._h) or b"").decode()
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             lib().ta_context_destroy(self._h)

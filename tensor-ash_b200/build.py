@@ -20,6 +20,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libtensor_ash.so")
 BIN_DIR = os.path.join(HERE, "bin")
 LLAMA_ASH = os.path.join(BIN_DIR, "llama_ash")     # CLI over the C ABI (csrc/llama_ash_main.cpp)
+TOOLS = {"llama_ash": "llama_ash_main.cpp", "ml_bench": "ml_bench_main.cpp"}
 
 SOURCES = [
     "ta_host.cpp",
@@ -100,18 +101,20 @@ def build(verbose: bool = False, force: bool = False) -> str:
 
 
 def build_tools() -> str:
-    """llama_ash: plain C++ against the two public headers, finds the library next to itself."""
+    """llama_ash and ml_bench: plain C++ against the public headers; they find the library next to
+    themselves (rpath $ORIGIN/../lib)."""
     os.makedirs(BIN_DIR, exist_ok=True)
-    src = os.path.join(CSRC, "llama_ash_main.cpp")
-    if os.path.exists(LLAMA_ASH) and os.path.getmtime(LLAMA_ASH) >= max(os.path.getmtime(src), os.path.getmtime(LIB),
-                                                                       _headers_mtime()):
-        return LLAMA_ASH
     cxx = shutil.which("g++") or "g++"
-    cmd = [cxx, "-O2", "-std=c++17", "-Wall", src, "-o", LLAMA_ASH, "-L", LIB_DIR, "-ltensor_ash",
-           "-Wl,-rpath,$ORIGIN/../lib"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"building llama_ash failed:\n{r.stdout}\n{r.stderr}")
+    for name, source in TOOLS.items():
+        src, exe = os.path.join(CSRC, source), os.path.join(BIN_DIR, name)
+        if os.path.exists(exe) and os.path.getmtime(exe) >= max(os.path.getmtime(src), os.path.getmtime(LIB),
+                                                               _headers_mtime()):
+            continue
+        cmd = [cxx, "-O2", "-std=c++17", "-Wall", src, "-o", exe, "-L", LIB_DIR, "-ltensor_ash",
+               "-Wl,-rpath,$ORIGIN/../lib"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"building {name} failed:\n{r.stdout}\n{r.stderr}")
     return LLAMA_ASH
 
 

@@ -171,6 +171,7 @@ SIGNATURES = {
     "ta_f16_bits_to_f32": (C.c_float, [C.c_uint16]),
     "ta_tensor_device_ptr": (_P, [_P]),
     "ta_context_device_index": (C.c_int, [_P]),
+    "ta_context_device_name": (C.c_char_p, [_P]),
     "ta_kernel_launch_count": (C.c_uint64, []),
     "ta_comm_unique_id": (C.c_int, [_P]),
     "ta_comm_create": (_P, [_P, _U32, _U32, _P]),

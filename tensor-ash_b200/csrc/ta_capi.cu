@@ -852,6 +852,7 @@ float ta_f16_bits_to_f32(uint16_t bits) { return f16_bits_to_f32(bits); }
 
 void *ta_tensor_device_ptr(const ta_tensor *tensor) { return tensor ? tensor->tensor.ptr() : nullptr; }
 int ta_context_device_index(const ta_context *ctx) { return ctx ? ctx->ctx->device : -1; }
+const char *ta_context_device_name(const ta_context *ctx) { return ctx ? ctx->ctx->name.c_str() : ""; }
 uint64_t ta_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"
