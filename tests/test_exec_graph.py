@@ -63,9 +63,10 @@ def test_argmax_ties_keep_the_largest_index(gpu, orc, n):
 
 
 @pytest.mark.gpu
-def test_embed_gather_f16_and_f32_tables(gpu, orc):
+@pytest.mark.parametrize("embd", [160, 1030, 2048])      # 1030: rows off the 4-column vector path
+def test_embed_gather_f16_and_f32_tables(gpu, orc, embd):
     ta, ctx, ex = gpu
-    vocab, embd = 97, 160
+    vocab = 97
     tab = orc.fill_det(vocab * embd, 9).reshape(vocab, embd)
     t32 = up(ta, ctx, ex, tab)
     t16 = ta.Tensor.uninit_device_f16(ctx, [vocab, embd])
