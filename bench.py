@@ -234,6 +234,40 @@ def bench_f16w_gemm(ta, ctx, peaks: dict, reps: int = 20) -> dict:
     return res
 
 
+def bench_splitk2(ta, ctx, peaks: dict, reps: int = 20) -> dict:
+    """Configuration 4: deterministic two-stage split-K on M = 64, K = 65536, N in {64, 256},
+    splits in {4 .. 64} and the library's own choice (0).  Two runs are byte-compared; GB/s is
+    over the algorithmic bytes 4 (MK + KN + MN) + 8 S MN."""
+    entry_orc = entry.load_oracle()
+    ex = ta.Executor(ctx, 2, 16)
+    m, k = 64, 65536
+    res = {}
+    for n in (64, 256):
+        a = ta.Tensor.uninit_device(ctx, (m, k))
+        b = ta.Tensor.uninit_device(ctx, (k, n))
+        c = ta.Tensor.uninit_device(ctx, (m, n))
+        ex.upload(entry_orc.fill_det(m * k, 1), a)
+        ex.upload(entry_orc.fill_det(k * n, 2), b)
+        call = [ta.MatmulCall(a, b, c)]
+        row = {}
+        for splits in (4, 8, 16, 32, 64, 0):
+            for _ in range(3):
+                ex.run_matmuls_split_k2(call, splits)
+            first = ex.download(c).copy()
+            med = statistics.median(ex.run_matmuls_split_k2(call, splits).gpu_time_ns for _ in range(reps))
+            same = bool(np.array_equal(first.view(np.uint32), ex.download(c).view(np.uint32)))
+            s_eff = splits or ta.default_num_k_splits(1, m, n, k, 64, 64)
+            nbytes = 4 * (m * k + k * n + m * n) + 8 * s_eff * m * n
+            row[f"S={splits or 'auto'}"] = {"splits": s_eff, "us": med / 1e3, "gbs": nbytes / med,
+                                             "hbm_frac": nbytes / med / peaks["hbm_gbs"],
+                                             "tflops": 2.0 * m * n * k / med / 1e3, "bit_stable": same}
+        res[f"N={n}"] = row
+        for t in (a, b, c):
+            t.close()
+    ex.close()
+    return {"config": "configs[3]: split-K2, A[64,65536] x B[65536,N], uniform[-1,1) inputs", **res}
+
+
 def bench_gemv(ta, ctx, peaks: dict, reps: int = 30) -> dict:
     """Configuration 3: decode MLP at 4096 x 11008, packed f16 weights (tile 32), M in {1, 4, 8}:
     fused silu(x@Wg) * (x@Wup) and the down projection, timed as a replayed graph over two
@@ -316,7 +350,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the GEMV (configs[2]), llama (configs[4]) and f16w GEMM figures under extra_metrics")
-    ap.add_argument("--extras-only", default=None, choices=["gemv", "llama", "f16w_gemm"],
+    ap.add_argument("--extras-only", default=None, choices=["gemv", "llama", "f16w_gemm", "splitk2"],
                     help="run only this extra workload and print its figures (small cases for profiler captures; "
                          "--steps sets its timed repetitions)")
     args = ap.parse_args()
@@ -347,6 +381,8 @@ def main() -> None:
             out = bench_gemv(ta, ctx, peaks, reps=max(1, args.steps))
         elif args.extras_only == "f16w_gemm":
             out = bench_f16w_gemm(ta, ctx, peaks, reps=max(1, args.steps))
+        elif args.extras_only == "splitk2":
+            out = bench_splitk2(ta, ctx, peaks, reps=max(1, args.steps))
         else:
             comm = ta.Comm.from_torch_distributed(ctx) if distributed else None
             out = bench_llama(ta, ctx, comm, world, peaks)
@@ -460,6 +496,7 @@ def main() -> None:
             if world == 1:
                 extras["gemv_f16w"] = bench_gemv(ta, ctx, peaks)
                 extras["f16w_gemm"] = bench_f16w_gemm(ta, ctx, peaks)
+                extras["splitk2"] = bench_splitk2(ta, ctx, peaks)
         except Exception as exc:  # the headline line must still be printed
             extras["error"] = f"{type(exc).__name__}: {exc}"
 

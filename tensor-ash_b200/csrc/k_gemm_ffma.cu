@@ -19,13 +19,18 @@
 
 namespace ta {
 
-constexpr int FFMA_BK = 16;
+// K elements staged per step: 16, and 64 for the 64 x 64 split-K stage-1 tile, whose CTAs walk a
+// long K range of a skinny problem: 256-byte row segments of A per step instead of 64-byte ones
+// and a quarter of the barriers.
+template <int BM, int BN, bool SPLITK>
+constexpr int ffma_bk() { return (SPLITK && BM == 64 && BN == 64) ? 64 : 16; }
 
 template <int BM, int BN, int TM, int TN, bool B_F16, bool SPLITK>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_ffma_kernel(GemmParams p, float *__restrict__ scratch) {
   constexpr int NT = (BM / TM) * (BN / TN);
   constexpr int TX = BN / TN;
+  constexpr int FFMA_BK = ffma_bk<BM, BN, SPLITK>();
   static_assert(TN % 4 == 0 && TM % 4 == 0, "micro tile is built from float4 strips");
   __shared__ __align__(16) float As[FFMA_BK][BM + 4];
   __shared__ __align__(16) float Bs[FFMA_BK][BN + 4];
@@ -63,13 +68,22 @@ gemm_ffma_kernel(GemmParams p, float *__restrict__ scratch) {
   const bool b_vec = !B_F16 && (p.n % 4 == 0) && ((p.stride_b % 4) == 0) &&
                      ((reinterpret_cast<uintptr_t>(p.b) & 15) == 0);
 
-  for (uint32_t k0 = k_lo; k0 < k_hi; k0 += FFMA_BK) {
-    // ---- stage A tile (BM x BK), transposed into As[kk][row]
-    for (int idx = tid; idx < BM * (FFMA_BK / 4); idx += NT) {
+  // Software pipeline: the global loads of the tiles two K steps ahead are in flight (in two
+  // register sets) while the current tile is multiplied out of shared memory, so a CTA with a long
+  // K range (split-K stage 1, deep-K shapes) is not one exposed global round trip per 16 k.  The
+  // arithmetic per output element is unchanged: one fmaf chain over k ascending.
+  constexpr int A_ITERS = BM * (FFMA_BK / 4) / NT, B_ITERS = FFMA_BK * (BN / 4) / NT;
+  static_assert(A_ITERS * NT == BM * (FFMA_BK / 4) && B_ITERS * NT == FFMA_BK * (BN / 4), "tile loads must divide evenly");
+  float4 a_pre[2][A_ITERS], b_pre[2][B_ITERS];
+
+  auto load_tile = [&](float4 (&ar)[A_ITERS], float4 (&br)[B_ITERS], uint32_t k0) {
+#pragma unroll
+    for (int it = 0; it < A_ITERS; ++it) {
+      const int idx = tid + it * NT;
       const int r = idx / (FFMA_BK / 4), kq = (idx % (FFMA_BK / 4)) * 4;
       const uint32_t gr = row0 + r, gk = k0 + kq;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (gr < p.m) {
+      if (gr < p.m && gk < k_hi) {
         const float *src = A + (size_t)gr * p.k + gk;
         if (a_vec && gk + 4 <= k_hi) {
           const float4 t = *reinterpret_cast<const float4 *>(src);
@@ -80,11 +94,11 @@ gemm_ffma_kernel(GemmParams p, float *__restrict__ scratch) {
             if (gk + q < k_hi) v[q] = src[q];
         }
       }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) As[kq + q][r] = v[q];
+      ar[it] = make_float4(v[0], v[1], v[2], v[3]);
     }
-    // ---- stage B tile (BK x BN)
-    for (int idx = tid; idx < FFMA_BK * (BN / 4); idx += NT) {
+#pragma unroll
+    for (int it = 0; it < B_ITERS; ++it) {
+      const int idx = tid + it * NT;
       const int kk = idx / (BN / 4), cq = (idx % (BN / 4)) * 4;
       const uint32_t gk = k0 + kk, gc = col0 + cq;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -103,10 +117,25 @@ gemm_ffma_kernel(GemmParams p, float *__restrict__ scratch) {
             if (gc + q < p.n) v[q] = Bf[off + q];
         }
       }
-      *reinterpret_cast<float4 *>(&Bs[kk][cq]) = make_float4(v[0], v[1], v[2], v[3]);
+      br[it] = make_float4(v[0], v[1], v[2], v[3]);
     }
-    __syncthreads();
-
+  };
+  // registers -> shared memory: A transposed into As[kk][row], B as is
+  auto store_tile = [&](const float4 (&ar)[A_ITERS], const float4 (&br)[B_ITERS]) {
+#pragma unroll
+    for (int it = 0; it < A_ITERS; ++it) {
+      const int idx = tid + it * NT;
+      const int r = idx / (FFMA_BK / 4), kq = (idx % (FFMA_BK / 4)) * 4;
+      As[kq][r] = ar[it].x; As[kq + 1][r] = ar[it].y; As[kq + 2][r] = ar[it].z; As[kq + 3][r] = ar[it].w;
+    }
+#pragma unroll
+    for (int it = 0; it < B_ITERS; ++it) {
+      const int idx = tid + it * NT;
+      const int kk = idx / (BN / 4), cq = (idx % (BN / 4)) * 4;
+      *reinterpret_cast<float4 *>(&Bs[kk][cq]) = br[it];
+    }
+  };
+  auto multiply_tile = [&]() {
 #pragma unroll
     for (int kk = 0; kk < FFMA_BK; ++kk) {
       float a_reg[TM], b_reg[TN];
@@ -125,6 +154,21 @@ gemm_ffma_kernel(GemmParams p, float *__restrict__ scratch) {
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a_reg[i], b_reg[j], acc[i][j]);
     }
+  };
+
+  load_tile(a_pre[0], b_pre[0], k_lo);
+  load_tile(a_pre[1], b_pre[1], k_lo + FFMA_BK);
+  for (uint32_t k0 = k_lo; k0 < k_hi; k0 += 2 * FFMA_BK) {
+    store_tile(a_pre[0], b_pre[0]);
+    __syncthreads();
+    load_tile(a_pre[0], b_pre[0], k0 + 2 * FFMA_BK);
+    multiply_tile();
+    __syncthreads();
+    if (k0 + FFMA_BK >= k_hi) break;
+    store_tile(a_pre[1], b_pre[1]);
+    __syncthreads();
+    load_tile(a_pre[1], b_pre[1], k0 + 3 * FFMA_BK);
+    multiply_tile();
     __syncthreads();
   }
 
@@ -180,9 +224,136 @@ void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream) {
   else launch_ffma_t<64, 64, 4, 4, false>(p, nullptr, stream);
 }
 
+// Stage 1 for skinny deep-K problems (M x N small, K long, f32 B).  The reference's 64 x 64 stage-1
+// tile (src/executor/splitk2.rs:36-42) with a 4 x 4 micro tile gives such a problem
+// tiles x splits x 8 warps: 512 warps at M = N = 64, S = 64, i.e. 3.5 per SM, and the kernel idles on
+// shared-memory latency (ncu: 5 % of warp slots occupied, issue slots 27 % busy, FMA pipe 16 %).  Here a CTA of 256 threads
+// owns a 32 x 32 tile with a 2 x 2 micro tile: four times the threads for the same chains.  Every
+// output element is still one thread's fmaf chain over its split's k range in ascending order, so
+// the planes are bit-identical to the 64 x 64 tile's.
+constexpr int SKINNY_T = 32, SKINNY_BK = 32;
+
+__global__ void __launch_bounds__(256)
+splitk2_skinny_kernel(GemmParams p, float *__restrict__ scratch) {
+  __shared__ __align__(16) float As[SKINNY_BK][SKINNY_T + 2];
+  __shared__ __align__(16) float Bs[SKINNY_BK][SKINNY_T];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const uint32_t split = blockIdx.z % p.splits, batch = blockIdx.z / p.splits;
+  const uint32_t per = p.k / p.splits, rem = p.k % p.splits;
+  const uint32_t k_lo = split * per + min(split, rem), k_hi = k_lo + per + (split < rem ? 1u : 0u);
+  const float *__restrict__ A = (const float *)p.a + (size_t)batch * p.stride_a;
+  const float *__restrict__ B = (const float *)p.b + (size_t)batch * p.stride_b;
+  const uint32_t row0 = blockIdx.y * SKINNY_T, col0 = blockIdx.x * SKINNY_T;
+  const bool a_vec = (p.k % 4 == 0) && ((p.stride_a % 4) == 0) && (k_lo % 4 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0);
+  const bool b_vec = (p.n % 4 == 0) && ((p.stride_b % 4) == 0) && ((reinterpret_cast<uintptr_t>(p.b) & 15) == 0);
+  // one float4 of A (row ar, k offset akq) and one of B (k offset bk, column bcq) per thread and K step
+  const int ar = tid >> 3, akq = (tid & 7) * 4, bk = tid >> 3, bcq = (tid & 7) * 4;
+
+  auto load_a = [&](uint32_t k0) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint32_t gr = row0 + ar, gk = k0 + akq;
+    if (gr < p.m && gk < k_hi) {
+      const float *src = A + (size_t)gr * p.k + gk;
+      if (a_vec && gk + 4 <= k_hi) {
+        v = *reinterpret_cast<const float4 *>(src);
+      } else {
+        v.x = src[0];
+        if (gk + 1 < k_hi) v.y = src[1];
+        if (gk + 2 < k_hi) v.z = src[2];
+        if (gk + 3 < k_hi) v.w = src[3];
+      }
+    }
+    return v;
+  };
+  auto load_b = [&](uint32_t k0) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    const uint32_t gk = k0 + bk, gc = col0 + bcq;
+    if (gk < k_hi && gc < p.n) {
+      const float *src = B + (size_t)gk * p.n + gc;
+      if (b_vec && gc + 4 <= p.n) {
+        v = *reinterpret_cast<const float4 *>(src);
+      } else {
+        v.x = src[0];
+        if (gc + 1 < p.n) v.y = src[1];
+        if (gc + 2 < p.n) v.z = src[2];
+        if (gc + 3 < p.n) v.w = src[3];
+      }
+    }
+    return v;
+  };
+  auto store_tile = [&](const float4 &a, const float4 &b) {
+    As[akq][ar] = a.x; As[akq + 1][ar] = a.y; As[akq + 2][ar] = a.z; As[akq + 3][ar] = a.w;
+    *reinterpret_cast<float4 *>(&Bs[bk][bcq]) = b;
+  };
+  float acc00 = 0.f, acc01 = 0.f, acc10 = 0.f, acc11 = 0.f;
+  auto multiply_tile = [&]() {
+#pragma unroll
+    for (int kk = 0; kk < SKINNY_BK; ++kk) {
+      const float2 a = *reinterpret_cast<const float2 *>(&As[kk][ty * 2]);
+      const float2 b = *reinterpret_cast<const float2 *>(&Bs[kk][tx * 2]);
+      acc00 = fmaf(a.x, b.x, acc00); acc01 = fmaf(a.x, b.y, acc01);
+      acc10 = fmaf(a.y, b.x, acc10); acc11 = fmaf(a.y, b.y, acc11);
+    }
+  };
+  // loads run two K steps ahead of the multiply (a ring of two register sets; four measured the
+  // same, the kernel is bound by shared-memory operand traffic, not by the global round trip)
+  constexpr int DIST = 2;
+  float4 a_pre[DIST], b_pre[DIST];
+#pragma unroll
+  for (int d = 0; d < DIST; ++d) {
+    a_pre[d] = load_a(k_lo + d * SKINNY_BK);
+    b_pre[d] = load_b(k_lo + d * SKINNY_BK);
+  }
+  for (uint32_t k0 = k_lo; k0 < k_hi; k0 += DIST * SKINNY_BK) {
+#pragma unroll
+    for (int d = 0; d < DIST; ++d) {
+      if (k0 + d * SKINNY_BK >= k_hi) break;
+      store_tile(a_pre[d], b_pre[d]);
+      __syncthreads();
+      a_pre[d] = load_a(k0 + (DIST + d) * SKINNY_BK);
+      b_pre[d] = load_b(k0 + (DIST + d) * SKINNY_BK);
+      multiply_tile();
+      __syncthreads();
+    }
+  }
+  float *__restrict__ out = scratch + ((size_t)batch * p.splits + split) * ((size_t)p.m * p.n);
+  const bool alpha_is_one = p.alpha == 1.0f;
+  const float r[2][2] = {{acc00, acc01}, {acc10, acc11}};
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t gr = row0 + ty * 2 + i, gc = col0 + tx * 2 + j;
+      if (gr < p.m && gc < p.n) out[(size_t)gr * p.n + gc] = alpha_is_one ? r[i][j] : p.alpha * r[i][j];
+    }
+}
+
 void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream) {
-  if (tile >= 128) launch_ffma_t<128, 128, 8, 8, true>(p, scratch, stream);
-  else launch_ffma_t<64, 64, 4, 4, true>(p, scratch, stream);
+  if (tile >= 128) {
+    launch_ffma_t<128, 128, 8, 8, true>(p, scratch, stream);
+    return;
+  }
+  const uint64_t ctas64 = (uint64_t)((p.m + 63) / 64) * ((p.n + 63) / 64) * p.batch * p.splits;
+  static const int sms = [] {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  const uint64_t grid_z = (uint64_t)p.batch * p.splits;
+  // measured on M = 64, K = 65536: faster than the 64 x 64 tile up to 64 of its CTAs (N = 64: 165 us
+  // against 359 at S = 8, 51 against 63 at S = 64; N = 256: 171 against 363 at S = 8), slower from
+  // 128 on (2 x 2 micro tiles read four times the shared-memory operands per FMA)
+  if (!p.b_f16 && ctas64 * 2 <= (uint64_t)sms && grid_z <= 65535) {
+    dim3 grid((p.n + SKINNY_T - 1) / SKINNY_T, (p.m + SKINNY_T - 1) / SKINNY_T, (unsigned)grid_z);
+    if (grid.y <= 65535) {
+      splitk2_skinny_kernel<<<grid, 256, 0, stream>>>(p, scratch);
+      TA_CUDA(cudaGetLastError());
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      return;
+    }
+  }
+  launch_ffma_t<64, 64, 4, 4, true>(p, scratch, stream);
 }
 
 // One thread per 4 consecutive outputs; planes added in split order starting
@@ -195,8 +366,16 @@ __global__ void splitk2_reduce_kernel(const float *__restrict__ scratch, float *
     const uint64_t b = base / mn, e = base % mn;
     const float *src = scratch + b * splits * mn + e;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t s = 0; s < splits; ++s) {
-      const float4 v = *reinterpret_cast<const float4 *>(src + (uint64_t)s * mn);
+    uint32_t s = 0;
+    for (; s + 8 <= splits; s += 8) {   // eight plane loads in flight, added in plane order
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)(s + u) * mn));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+    }
+    for (; s < splits; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)s * mn));
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     *reinterpret_cast<float4 *>(c + base) = acc;
