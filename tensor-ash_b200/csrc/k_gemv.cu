@@ -74,18 +74,20 @@ constexpr int RING_STAGE_BYTES = 16384;
 // depend on shared memory (64 KiB per CTA), not on registers.
 // MMA (3 to 8 activation rows): the dot products run on the tensor cores instead of the FMA
 // pipe, which at M = 8 has no headroom left beside a full-rate weight stream.
-// mma.sync m16n8k8 tf32 with x as the A operand (rows = activation rows, padded to 16) split
-// into hi + lo tf32 parts (two MMAs; f16 weights are exact in tf32, so the products carry ~21
-// bits of x) and the weights as the B operand: lane (g, t) = (lane / 4, lane % 4) loads the
-// TN/8 consecutive columns TN/8*g.. of rows k0 + t and k0 + t + 4, which is exactly the B
-// fragment (k = t, t + 4; n = g) of TN/8 MMAs whose column j stands for n = TN/8 * j + q.
+// mma.sync m16n8k16 f16 with x as the A operand (rows = activation rows, padded to 16), split
+// into hi + lo f16 parts (two MMAs, ~22 bits of x; |x| must stay below the f16 range, 65504), and
+// the f16 weights as the B operand exactly as stored -- no conversion at all, one byte-permute
+// per register to pair two k rows.  Lane (g, t) = (lane / 4, lane % 4) loads the TN/8 consecutive
+// columns TN/8*g.. of rows k0 + {2t, 2t+1, 2t+8, 2t+9}: element q of those four vectors is the B
+// fragment (k = 2t, 2t+1 | 2t+8, 2t+9; n = g) of the q-th of TN/8 MMAs, whose column j stands for
+// n = TN/8 * j + q.
 template <int MROWS, int TN, bool BULK, bool MMA>
 __global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (BULK ? 3 : 4) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   static_assert(!MMA || (MROWS == 8 && !BULK), "the tensor-core variant handles up to 8 rows, register path");
-  constexpr int U = GemvCfg<MROWS>::U;
+  constexpr int U = MMA ? 2 : GemvCfg<MROWS>::U;  // MMA: blocks of 16 k rows, four vectors per lane and block (four blocks per pass measured slower)
   constexpr int LPR = TN / 8;                    // lanes per weight row (8 f16 per lane)
-  constexpr int RPL = MMA ? 8 : 32 / LPR;        // weight rows per warp-wide load
+  constexpr int RPL = MMA ? 16 : 32 / LPR;       // weight rows per warp-wide load
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t S = g.ksplit;
@@ -110,7 +112,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   // BULK prepends: ring[RING_STAGES][16 KiB] | full barriers | abort flag (128 bytes reserved)
   constexpr size_t RING_BYTES = BULK ? (size_t)RING_STAGES * RING_STAGE_BYTES + 128 : 0;
   float *xs = reinterpret_cast<float *>(gemv_smem + RING_BYTES);
-  float *wpart = xs + (size_t)g.k_cta * MROWS;
+  float *wpart = xs + (size_t)(g.k_cta + 8) * MROWS;   // +8: row pitch of the MMA variant's xs[m][k]
   float *cpart = wpart + GEMV_WARPS * MROWS * TN;
   float *red = cpart + (size_t)S * 2 * MROWS * TN;
   float *scale = red + GEMV_WARPS * MROWS;
@@ -168,6 +170,31 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   };
 
+  // ---- MMA variant: NQ columns per lane and k row, four k rows per lane and block of 16
+  constexpr int NQ = TN / 8;
+  using WVec = typename std::conditional<NQ == 4, uint2, uint4>::type;
+  const int gq = lane >> 2, tq = lane & 3;
+  const bool mcol_ok = col0 + NQ * gq < p.n;
+  size_t mbase, mstride;   // in halfs
+  if (p.packed) {
+    mbase = ((size_t)tile * p.k) * TN + NQ * gq;
+    mstride = TN;
+  } else {
+    mbase = (size_t)col0 + NQ * gq;
+    mstride = p.n;
+  }
+  auto load_blocks = [&](WVec (&wv)[U][4], uint32_t pass) {
+    const uint32_t k0 = k_lo + pass * rows_per_pass + (uint32_t)wi * 16;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const uint32_t k = k0 + u * nw * 16 + 2 * tq + (h & 1) + 8 * (h >> 1);
+        wv[u][h] = WVec{};
+        if (k < k_hi && mcol_ok) wv[u][h] = __ldcs(reinterpret_cast<const WVec *>(W + mbase + (size_t)k * mstride));
+      }
+  };
+  WVec ma[U][4], mb[U][4];
   TA_TRACE_BEGIN()
   TA_TRACE(0)
   uint4 wa[U], wb[U];
@@ -182,6 +209,9 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   } else if constexpr (!MMA) {
     if (passes > 0) load_pass(wa, 0);
     if (passes > 1) load_pass(wb, 1);
+  } else {
+    if (passes > 0) load_blocks(ma, 0);
+    if (passes > 1) load_blocks(mb, 1);
   }
   TA_TRACE(1)
   // the position cell is written by the host before the launch, never by a kernel:
@@ -252,12 +282,39 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   }
   // ---- stage this CTA's slice of x (times the norm weight) as xs[k][m]
+  if constexpr (!MMA) {
 #pragma unroll
-  for (int it = 0; it < XS_PRE; ++it) {
-    const uint32_t idx = threadIdx.x + it * GEMV_THREADS;
-    if (idx < stage_n) xs[idx] = xv[it] * nwv[it];
+    for (int it = 0; it < XS_PRE; ++it) {
+      const uint32_t idx = threadIdx.x + it * GEMV_THREADS;
+      if (idx < stage_n) xs[idx] = xv[it] * nwv[it];
+    }
   }
-  if constexpr (MROWS >= 4) {
+  if constexpr (MMA) {
+    // tensor-core variant: xs[m][k] with a row pitch of k_cta + 8 floats (the eight rows a half
+    // warp reads as float2 land on distinct banks), filled with 16-byte loads along k
+    const uint32_t pitch = g.k_cta + 8, quads = (k_len + 3) / 4;
+    const bool vec = (p.k & 3u) == 0 && (k_lo & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 &&
+                     (!p.norm_w || (reinterpret_cast<uintptr_t>(p.norm_w) & 15u) == 0);
+    for (uint32_t idx = threadIdx.x; idx < (uint32_t)MROWS * quads; idx += GEMV_THREADS) {
+      const uint32_t m = idx / quads, kq = (idx % quads) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (m < p.m) {
+        const float *src = p.x + (size_t)m * p.k + k_lo + kq;
+        if (vec && kq + 4 <= k_len) {
+          v = *reinterpret_cast<const float4 *>(src);
+          if (p.norm_w) {
+            const float4 w = *reinterpret_cast<const float4 *>(p.norm_w + k_lo + kq);
+            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+          }
+        } else {
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+          for (uint32_t j = 0; j < 4 && kq + j < k_len; ++j) t[j] = src[j] * (p.norm_w ? p.norm_w[k_lo + kq + j] : 1.0f);
+          v = make_float4(t[0], t[1], t[2], t[3]);
+        }
+      }
+      *reinterpret_cast<float4 *>(xs + (size_t)m * pitch + kq) = v;
+    }
+  } else if constexpr (MROWS >= 4) {
     // many rows: walk k within a row so that global reads are contiguous (the first
     // XS_PRE * 256 / MROWS k of every row are staged above)
     const uint32_t kk_done = (XS_PRE * GEMV_THREADS) / MROWS;
@@ -291,65 +348,53 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   }
 
   if constexpr (MMA) {
-    // ---- tensor-core stream: NQ columns per lane and k row, two k rows per k8 block
-    constexpr int NQ = TN / 8;
-    using WVec = typename std::conditional<NQ == 4, uint2, uint4>::type;
-    const int gq = lane >> 2, tq = lane & 3;
-    const bool mcol_ok = col0 + NQ * gq < p.n;
-    size_t mbase, mstride;   // in halfs
-    if (p.packed) {
-      mbase = ((size_t)tile * p.k) * TN + NQ * gq;
-      mstride = TN;
-    } else {
-      mbase = (size_t)col0 + NQ * gq;
-      mstride = p.n;
-    }
-    auto load_blocks = [&](WVec (&wv)[U][2], uint32_t pass) {
-      const uint32_t k0 = k_lo + pass * rows_per_pass + (uint32_t)wi * 8;
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t k = k0 + u * nw * 8 + tq + 4 * h;
-          wv[u][h] = WVec{};
-          if (k < k_hi && mcol_ok) wv[u][h] = __ldcs(reinterpret_cast<const WVec *>(W + mbase + (size_t)k * mstride));
-        }
-    };
+    // ---- tensor-core stream (addresses, block loads and the first two passes: see the prologue)
     float dacc[NQ][4];
 #pragma unroll
     for (int q = 0; q < NQ; ++q)
 #pragma unroll
       for (int i = 0; i < 4; ++i) dacc[q][i] = 0.0f;
-    auto mma_blocks = [&](const WVec (&wv)[U][2], uint32_t pass) {
-      const uint32_t kk0 = pass * rows_per_pass + (uint32_t)wi * 8;
+    // x pair (k, k + 1) of activation row g as half2 hi and half2 lo = x - hi
+    auto x_pair = [&](uint32_t kk, uint32_t &hi, uint32_t &lo) {
+      // k_len is padded with zeros up to a multiple of 4 by the staging loop; kk is even
+      float x0 = 0.0f, x1 = 0.0f;
+      if (kk < ((k_len + 3u) & ~3u)) {
+        const float2 xx = *reinterpret_cast<const float2 *>(xs + (size_t)gq * (g.k_cta + 8) + kk);
+        x0 = xx.x; x1 = xx.y;
+      }
+      const __half2 h = __floats2half2_rn(x0, x1);
+      const float2 hf = __half22float2(h);
+      const __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+      hi = *reinterpret_cast<const uint32_t *>(&h);
+      lo = *reinterpret_cast<const uint32_t *>(&l);
+    };
+    auto mma_blocks = [&](const WVec (&wv)[U][4], uint32_t pass) {
+      const uint32_t kk0 = pass * rows_per_pass + (uint32_t)wi * 16;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const uint32_t kk = kk0 + u * nw * 8 + tq;
-        const float x0 = kk < k_len ? xs[(size_t)kk * MROWS + gq] : 0.0f;
-        const float x1 = kk + 4 < k_len ? xs[(size_t)(kk + 4) * MROWS + gq] : 0.0f;
-        const uint32_t x0h = __float_as_uint(x0) & 0xffffe000u, x1h = __float_as_uint(x1) & 0xffffe000u;
-        const uint32_t x0l = __float_as_uint(x0 - __uint_as_float(x0h)), x1l = __float_as_uint(x1 - __uint_as_float(x1h));
-        const __half *h0 = reinterpret_cast<const __half *>(&wv[u][0]);
-        const __half *h1 = reinterpret_cast<const __half *>(&wv[u][1]);
+        const uint32_t kk = kk0 + u * nw * 16 + 2 * tq;
+        uint32_t a0h, a0l, a2h, a2l;
+        x_pair(kk, a0h, a0l);
+        x_pair(kk + 8, a2h, a2l);
+        const uint32_t *r0 = reinterpret_cast<const uint32_t *>(&wv[u][0]);
+        const uint32_t *r1 = reinterpret_cast<const uint32_t *>(&wv[u][1]);
+        const uint32_t *r2 = reinterpret_cast<const uint32_t *>(&wv[u][2]);
+        const uint32_t *r3 = reinterpret_cast<const uint32_t *>(&wv[u][3]);
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
-          const uint32_t b0 = __float_as_uint(__half2float(h0[q])), b1 = __float_as_uint(__half2float(h1[q]));
+          const uint32_t sel = (q & 1) ? 0x7632u : 0x5410u;   // the q-th half of two rows -> one register
+          const uint32_t b0 = __byte_perm(r0[q >> 1], r1[q >> 1], sel), b1 = __byte_perm(r2[q >> 1], r3[q >> 1], sel);
           asm volatile(
-              "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
               : "+f"(dacc[q][0]), "+f"(dacc[q][1]), "+f"(dacc[q][2]), "+f"(dacc[q][3])
-              : "r"(x0h), "r"(0u), "r"(x1h), "r"(0u), "r"(b0), "r"(b1));
-#ifndef TA_EXP_NOLO
+              : "r"(a0h), "r"(0u), "r"(a2h), "r"(0u), "r"(b0), "r"(b1));
           asm volatile(
-              "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
               : "+f"(dacc[q][0]), "+f"(dacc[q][1]), "+f"(dacc[q][2]), "+f"(dacc[q][3])
-              : "r"(x0l), "r"(0u), "r"(x1l), "r"(0u), "r"(b0), "r"(b1));
-#endif
+              : "r"(a0l), "r"(0u), "r"(a2l), "r"(0u), "r"(b0), "r"(b1));
         }
       }
     };
-    WVec ma[U][2], mb[U][2];
-    if (passes > 0) load_blocks(ma, 0);
-    if (passes > 1) load_blocks(mb, 1);
     for (uint32_t pass = 0; pass < passes; pass += 2) {
       mma_blocks(ma, pass);
       if (pass + 2 < passes) load_blocks(ma, pass + 2);
@@ -530,7 +575,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
 }
 
 size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s, bool bulk = false) {
-  return ((size_t)k_cta * mrows + (size_t)GEMV_WARPS * mrows * tn + (size_t)s * 2 * mrows * tn +
+  return ((size_t)(k_cta + 8) * mrows + (size_t)GEMV_WARPS * mrows * tn + (size_t)s * 2 * mrows * tn +
           (size_t)GEMV_WARPS * mrows + mrows) * sizeof(float) + 16 +
          (bulk ? (size_t)RING_STAGES * RING_STAGE_BYTES + 128 : 0);
 }
@@ -618,12 +663,14 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   g.pdl = (pdl && pdl_enabled()) ? 1u : 0u;
   g.status = status;
   // five rows and more: tensor-core variant (8-row kernel).  Measured on 4096 x 11008: at M = 8 it
-  // is ahead of the FMA path (196 vs 214 us per MLP pass), at M = 4 behind it (160 vs 99 us).
-  bool mma = p0.m >= 5;
+  // is ahead of the FMA path (119 vs 214 us per MLP pass), at M = 4 behind it (109 vs 99 us).
+  uint32_t mma_min = 5;
+  if (const char *e = std::getenv("TA_GEMV_MMA_MIN")) mma_min = (uint32_t)std::max(1, atoi(e));   // experiments
+  bool mma = p0.m >= mma_min;
   if (const char *e = std::getenv("TA_GEMV_MMA")) mma = mma && e[0] != '0';
   const int mrows = mma ? 8 : (p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8);
-  const uint32_t u = 4;
-  const uint32_t rpl = mma ? 8 : 32 / (tn / 8);
+  const uint32_t u = mma ? 2 : 4;
+  const uint32_t rpl = mma ? 16 : 32 / (tn / 8);
   const uint32_t nw = p0.w2 ? GEMV_WARPS / 2 : GEMV_WARPS;
   const uint32_t rows_per_pass = nw * rpl * u;
   // K split over a cluster: about one and a half CTAs per SM.  With four resident
