@@ -313,6 +313,8 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
         }
       }
       *reinterpret_cast<float4 *>(xs + (size_t)m * pitch + kq) = v;
+      // the hi / lo split is in f16: a larger activation cannot be represented -- say so, loudly
+      if (fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))) > 65504.0f && g.status) atomicOr(g.status, 2u);
     }
   } else if constexpr (MROWS >= 4) {
     // many rows: walk k within a row so that global reads are contiguous (the first

@@ -559,6 +559,16 @@ class Executor {
   std::shared_ptr<HostStreamState> host_stream_;  // copy streams, events and the staging ring
 };
 
+// Device status word of a slot: bit 0 = a bounded device-side wait ran out, bit 1 = the tensor-core
+// GEMV met an activation outside the f16 range.  Raises the matching error.
+[[noreturn]] inline void fail_device_status(uint32_t status) {
+  if (status & 2u)
+    fail("f16-weight GEMV (tensor-core variant, 5..8 rows): an activation magnitude exceeds the f16 range "
+         "(65504); results are invalid -- set TA_GEMV_MMA=0 to keep such inputs on the f32 FMA path (status 0x%x)",
+         status);
+  fail("a kernel gave up on a bounded device-side wait (status 0x%x); results are invalid", status);
+}
+
 struct SlotGuard {
   Executor &e;
   Slot &s;

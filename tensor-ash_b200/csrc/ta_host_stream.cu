@@ -214,7 +214,7 @@ RunStats Executor::run_matmul_host_batched(const HostBatchedMatmul &h) {
   TA_CUDA(cudaMemcpy(&status, slot.status, sizeof(status), cudaMemcpyDeviceToHost));
   if (status) {
     cudaMemset(slot.status, 0, sizeof(uint32_t));
-    fail("a kernel gave up on a bounded device-side wait (status 0x%x); results are invalid", status);
+    fail_device_status(status);
   }
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, st.ev_begin, st.ev_end));

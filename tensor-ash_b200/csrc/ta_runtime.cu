@@ -508,7 +508,7 @@ RunStats Executor::timed(Slot &slot, size_t n_calls, uint64_t flops,
   TA_CUDA(cudaMemcpy(&status, slot.status, sizeof(status), cudaMemcpyDeviceToHost));
   if (status) {
     cudaMemset(slot.status, 0, sizeof(uint32_t));
-    fail("a kernel gave up on a bounded device-side wait (status 0x%x); results are invalid", status);
+    fail_device_status(status);
   }
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, slot.ev_begin, slot.ev_end));

@@ -218,3 +218,27 @@ def test_rejections(gpu, orc):
     with pytest.raises(E, match="requires M == 1"):
         ex.run_ops_ex([ta.MatmulOpEx(ta.MatmulCall(x16, w16, c16),
                                      store=ta.MatmulStore(ta.StoreKind.SCATTER, head_dim=64, dst=c16))])
+
+
+def test_tensor_core_rows_refuse_activations_beyond_the_f16_range(gpu, orc, monkeypatch):
+    """5..8 rows run on mma.sync with x split into two f16 halves; an activation above 65504 cannot
+    be split and must fail loudly, and TA_GEMV_MMA=0 keeps such inputs on the f32 FMA path."""
+    ta, ctx, ex = gpu
+    m, k, n = 8, 512, 256
+    hx = orc.fill_det(m * k, 71).reshape(m, k).astype(np.float32)
+    hx[3, 17] = 1.0e5
+    x = ta.Tensor.uninit_device(ctx, (m, k))
+    ex.upload(hx.ravel(), x)
+    w, hw = make_weights(ta, ctx, ex, orc, k, n, 72, False)
+    c = ta.Tensor.uninit_device(ctx, (m, n))
+    with pytest.raises(ta.TensorAshError, match="exceeds the f16 range"):
+        ex.run_matmuls([ta.MatmulCall(x, w, c)])
+    monkeypatch.setenv("TA_GEMV_MMA", "0")
+    ex.run_matmuls([ta.MatmulCall(x, w, c)])
+    ref = orc.cpu_bmm(hx, hw, 1, m, n, k)
+    check(orc, ex.download(c), ref, k, "f32 path with a large activation")
+    monkeypatch.delenv("TA_GEMV_MMA")
+    hx[3, 17] = 0.5
+    ex.upload(hx.ravel(), x)
+    ex.run_matmuls([ta.MatmulCall(x, w, c)])            # the status word was cleared by the failed call
+    check(orc, ex.download(c), orc.cpu_bmm(hx, hw, 1, m, n, k), k, "tensor-core rows after a refused call")
