@@ -493,8 +493,17 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
                 const size_t off = plane_off + (size_t)row * p.n + col;
                 float4 o = *reinterpret_cast<const float4 *>(tbuf + r * EPI_PITCH + cq);
                 if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+                __half *c16 = reinterpret_cast<__half *>(p.c) + off;   // a16 route: C is f16 storage
                 if (p.accumulate) {
-                  const float4 c_old = *reinterpret_cast<const float4 *>(p.c + off);
+                  float4 c_old;
+                  if (p.c_f16) {
+                    const uint2 raw = *reinterpret_cast<const uint2 *>(c16);
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+                    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                    c_old = make_float4(lo.x, lo.y, hi.x, hi.y);
+                  } else {
+                    c_old = *reinterpret_cast<const float4 *>(p.c + off);
+                  }
                   o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
                 }
                 float4 dv = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -503,7 +512,15 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
                 o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
                 o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
                 o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
-                *reinterpret_cast<float4 *>(p.c + off) = o;
+                if (p.c_f16) {
+                  const __half2 lo = __floats2half2_rn(o.x, o.y), hi = __floats2half2_rn(o.z, o.w);
+                  uint2 raw;
+                  raw.x = *reinterpret_cast<const uint32_t *>(&lo);
+                  raw.y = *reinterpret_cast<const uint32_t *>(&hi);
+                  *reinterpret_cast<uint2 *>(c16) = raw;
+                } else {
+                  *reinterpret_cast<float4 *>(p.c + off) = o;
+                }
               }
             }
           }
@@ -639,6 +656,21 @@ static uint32_t a16_pitch(uint32_t k) {
 // Scratch bytes for the f16 copy of A.
 size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
   return (size_t)((uint64_t)batch_a * m * a16_pitch(k) * 2);
+}
+
+void launch_gemm_a16_umma(const Context &ctx, const GemmParams &p_in, uint32_t tile_n, uint32_t *status,
+                          cudaStream_t stream) {
+  if (!p_in.b_f16 || p_in.k % 8 || p_in.n % 8)
+    fail("a16 tensor-core GEMM needs f16 A, B and C with K and N multiples of 8");
+  if ((reinterpret_cast<uintptr_t>(p_in.a) | reinterpret_cast<uintptr_t>(p_in.b) | reinterpret_cast<uintptr_t>(p_in.c)) & 15)
+    fail("a16 tensor-core GEMM needs 16-byte aligned operands");
+  if (p_in.stride_a % 8) fail("a16 tensor-core GEMM needs an A batch stride that is a multiple of 8 halves");
+  GemmParams p = p_in;
+  p.c_f16 = 1;
+  __half *a16 = static_cast<__half *>(const_cast<void *>(p.a));   // A as stored: [batch, M, K] halves, pitch K
+  if (tile_n >= 256) launch_pre_t<256>(ctx, p, a16, p.k, status, true, stream);
+  else if (tile_n >= 128) launch_pre_t<128>(ctx, p, a16, p.k, status, true, stream);
+  else launch_pre_t<64>(ctx, p, a16, p.k, status, true, stream);
 }
 
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,

@@ -265,6 +265,7 @@ struct GemmParams {
   // tf32x3 tensor-core kernel: K blocks of 16 accumulated in tensor memory between drains (set by its launcher)
   uint32_t chunk_kb;
   uint32_t b_grouped = 0;    // launcher-set: the B tensor map is the rank-4 grouped view (one TMA per stage)
+  uint32_t c_f16 = 0;        // a16 route: C (and the old C when accumulating) is f16 storage
 };
 
 // Parameters of the f16-weight GEMV kernel (M <= 8 activation rows).
@@ -609,6 +610,9 @@ void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p, uint32_t *
 bool gemm_f16w_umma_eligible(const GemmParams &p);
 uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_count);
 size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k);
+// a16 route (f16 A, f16 B, f16 C; M, N multiples of 64, K of 32; no fused epilogue): the same
+// TMA -> tcgen05 pipeline reading A as stored, C rounded to f16 (nearest even) at the store
+void launch_gemm_a16_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status, cudaStream_t stream);
 // scratch (may be null): room for the f16 copy of A; without it A is converted inside the kernel
 // a16_ready: the scratch already holds this A (same pointer, M, K) from the launch just before
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,

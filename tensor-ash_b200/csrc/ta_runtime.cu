@@ -419,8 +419,7 @@ size_t Executor::op_scratch_bytes(const ResolvedMatmul &r, const Route &route) c
 bool Executor::gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route,
                                GemvParams *out) const {
   const KernelSpec &spec = KERNEL_SPECS[route.kernel];
-  if (!(spec.family == Family::RowGemv && r.b_f16)) return false;
-  if (r.a_f16) fail("f16 A storage (a16 route) is not built in this library yet");
+  if (!(spec.family == Family::RowGemv && r.b_f16) || r.a_f16) return false;
   const uint32_t tile_n = op.packed_b ? f16w_row_tile_n(r.k, r.n) : 32;
   if (!gemv_f16w_supported(r.m, r.n, r.k, op.packed_b, tile_n) || r.batch != 1)
     fail("row-GEMV route cannot run M=%u N=%u K=%u batch=%u packed=%d", r.m, r.n, r.k, r.batch,
@@ -453,7 +452,13 @@ bool Executor::gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, cons
 
 void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Route &route,
                           Slot &slot, cudaStream_t stream) {
-  if (r.a_f16) fail("f16 A storage (a16 route) is not built in this library yet");
+  if (r.a_f16) {
+    // a16 route (src/matmul/resolution.rs:123-172): f16 A / B / C, aligned shapes, no fused stages;
+    // always the tensor-core pipeline, whatever the selection says (it is the only f16-A kernel)
+    GemmParams p = make_params(op, r);
+    launch_gemm_a16_umma(*ctx_, p, gemm_f16w_umma_tile_n(r.batch, r.m, r.n, ctx_->sm_count), slot.status, stream);
+    return;
+  }
   const KernelSpec &spec = KERNEL_SPECS[route.kernel];
   {
     GemvParams g;
