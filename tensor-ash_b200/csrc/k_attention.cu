@@ -194,16 +194,19 @@ flash_prefill_mma_kernel(const FlashParams p) {
   // Q * scale as f16 A fragments: 4 steps of 16 head dims
   uint32_t qf[4][4];
   {
-    const float *qa = p.q + (size_t)head * p.q_head_stride + (size_t)min(row_a, p.t_q - 1) * p.q_row_stride;
-    const float *qb = p.q + (size_t)head * p.q_head_stride + (size_t)min(row_b, p.t_q - 1) * p.q_row_stride;
+    const size_t off_a = (size_t)head * p.q_head_stride + (size_t)min(row_a, p.t_q - 1) * p.q_row_stride;
+    const size_t off_b = (size_t)head * p.q_head_stride + (size_t)min(row_b, p.t_q - 1) * p.q_row_stride;
     const bool la = row_a < p.t_q, lb = row_b < p.t_q;
+    // two consecutive head dims of a row, from f32 or (io16) f16 storage
+    auto q2 = [&](size_t off, int d, bool live) {
+      if (!live) return make_float2(0.f, 0.f);
+      if (p.io_f16) return __half22float2(*reinterpret_cast<const __half2 *>(reinterpret_cast<const __half *>(p.q) + off + d));
+      return *reinterpret_cast<const float2 *>(p.q + off + d);
+    };
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
       const int d0 = 16 * s + 2 * t;
-      const float2 a0 = la ? *reinterpret_cast<const float2 *>(qa + d0) : make_float2(0.f, 0.f);
-      const float2 b0 = lb ? *reinterpret_cast<const float2 *>(qb + d0) : make_float2(0.f, 0.f);
-      const float2 a1 = la ? *reinterpret_cast<const float2 *>(qa + d0 + 8) : make_float2(0.f, 0.f);
-      const float2 b1 = lb ? *reinterpret_cast<const float2 *>(qb + d0 + 8) : make_float2(0.f, 0.f);
+      const float2 a0 = q2(off_a, d0, la), b0 = q2(off_b, d0, lb), a1 = q2(off_a, d0 + 8, la), b1 = q2(off_b, d0 + 8, lb);
       qf[s][0] = pack_h2(a0.x * p.scale, a0.y * p.scale);
       qf[s][1] = pack_h2(b0.x * p.scale, b0.y * p.scale);
       qf[s][2] = pack_h2(a1.x * p.scale, a1.y * p.scale);
@@ -305,18 +308,20 @@ flash_prefill_mma_kernel(const FlashParams p) {
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
   const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
-  if (valid_a > 0) {
-    float *oa = p.out + (size_t)head * p.o_head_stride + (size_t)row_a * p.o_row_stride;
+  auto store_row = [&](uint32_t row, float inv, int lo) {
+    const size_t off = (size_t)head * p.o_head_stride + (size_t)row * p.o_row_stride;
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      *reinterpret_cast<float2 *>(oa + 8 * j + 2 * t) = make_float2(o[j][0] * inv_a, o[j][1] * inv_a);
-  }
-  if (valid_b > 0) {
-    float *ob = p.out + (size_t)head * p.o_head_stride + (size_t)row_b * p.o_row_stride;
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      *reinterpret_cast<float2 *>(ob + 8 * j + 2 * t) = make_float2(o[j][2] * inv_b, o[j][3] * inv_b);
-  }
+    for (int j = 0; j < 8; ++j) {
+      const float x = o[j][lo] * inv, y = o[j][lo + 1] * inv;
+      if (p.io_f16) {
+        *reinterpret_cast<__half2 *>(reinterpret_cast<__half *>(p.out) + off + 8 * j + 2 * t) = __floats2half2_rn(x, y);
+      } else {
+        *reinterpret_cast<float2 *>(p.out + off + 8 * j + 2 * t) = make_float2(x, y);
+      }
+    }
+  };
+  if (valid_a > 0) store_row(row_a, inv_a, 0);
+  if (valid_b > 0) store_row(row_b, inv_b, 2);
 }
 
 // ------------------------------------------------------------------ decode
@@ -537,7 +542,7 @@ TA_TRACE_EXPORT(ta_debug_attn_trace)
 // The tensor-core route: f16 caches, head dim 64, 16-byte-aligned rows, at least 32 query rows
 // (short prefills keep f32 operands), and not pinned to the f32 kernel by the caller.
 bool flash_prefill_mma_eligible(const FlashParams &p) {
-  return !p.simt && p.kv_f16 && p.dh == 64 && p.t_q >= 32 && (p.t_max % 8u) == 0 &&
+  return !p.simt && p.kv_f16 && p.dh == 64 && (p.t_q >= 32 || p.io_f16) && (p.t_max % 8u) == 0 &&
          (reinterpret_cast<uintptr_t>(p.kt) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.v) & 15u) == 0 &&
          (reinterpret_cast<uintptr_t>(p.q) & 7u) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0 &&
          (p.q_row_stride % 2u) == 0 && (p.q_head_stride % 2u) == 0 && (p.o_row_stride % 2u) == 0 &&
@@ -551,6 +556,9 @@ void launch_flash_prefill(const FlashParams &p, cudaStream_t stream) {
     launched();
     return;
   }
+  if (p.io_f16)
+    fail("run_flash_attention: f16 q/out need the tensor-core kernel (f16 caches, dh 64, T_max %% 8 == 0, "
+         "even strides, 16-byte aligned caches)");
   if (p.dh == 64) flash_prefill_kernel<64><<<grid, 128, 0, stream>>>(p);
   else if (p.dh == 128) flash_prefill_kernel<128><<<grid, 128, 0, stream>>>(p);
   else fail("run_flash_attention: head dim %u is not supported (64 or 128)", p.dh);

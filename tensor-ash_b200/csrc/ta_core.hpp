@@ -309,6 +309,7 @@ struct FlashParams {
   uint32_t q_head_stride, q_row_stride, o_head_stride, o_row_stride;
   uint32_t kv_f16;
   uint32_t simt;   // 1: pin the f32-operand kernel (run_flash_attention_simt of the reference)
+  uint32_t io_f16; // 1: q and out are f16 storage (the reference's kv16 io16 dh64 route); tensor-core kernel only
 };
 
 struct AttnDecodeParams {

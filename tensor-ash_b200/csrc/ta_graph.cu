@@ -35,8 +35,13 @@ void rows_cols(const Tensor &t, const char *label, uint32_t *rows, uint32_t *col
 
 FlashParams Executor::plan_flash_attention(const Tensor &q, const Tensor &kt, const Tensor &v,
                                            const Tensor &out, const FlashAttentionDesc &desc) const {
-  ensure_f32(*this, q, "run_flash_attention", "q");
-  ensure_f32(*this, out, "run_flash_attention", "out");
+  // q / out are both f32, or both f16 (f16 activations: src/executor/elementwise/flash.rs:76-78)
+  validate_tensor(q, "input");
+  validate_tensor(out, "output");
+  if (q.dtype != out.dtype)
+    fail("run_flash_attention: input (%s) and output (%s) must share a storage type", dtype_name(q.dtype),
+         dtype_name(out.dtype));
+  const bool io_f16 = q.dtype == DType::F16;
   validate_tensor(kt, "kt");
   validate_tensor(v, "v");
   if (kt.dtype != v.dtype)
@@ -96,6 +101,10 @@ FlashParams Executor::plan_flash_attention(const Tensor &q, const Tensor &kt, co
   p.kv_len = desc.kv_len; p.pos_base = desc.pos_base; p.scale = desc.scale;
   p.kv_f16 = kt.dtype == DType::F16;
   p.simt = desc.simt;
+  p.io_f16 = io_f16 ? 1u : 0u;
+  if (io_f16 && !(p.kv_f16 && dh == 64 && !desc.simt))   // flash.rs:193-212
+    fail("run_flash_attention: f16 q/out are compiled for f16 KV caches with head dimension 64 on the "
+         "tensor-core route only (kv %s, dh %u)", dtype_name(kt.dtype), dh);
   return p;
 }
 

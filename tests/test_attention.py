@@ -84,6 +84,52 @@ def test_flash_prefill(gpu, orc, case, kv16):
     assert (ex.download(out_tm).reshape(t_q, heads, dh).transpose(1, 0, 2).reshape(-1) == got).all()
 
 
+@pytest.mark.parametrize("case", [(4, 4, 64, 64, 64, 64, 0), (8, 2, 100, 160, 64, 100, 0), (4, 2, 37, 128, 64, 77, 40),
+                                  (4, 4, 16, 64, 64, 10, 0), (32, 4, 512, 640, 64, 512, 0)])
+def test_flash_io16_equals_the_f32_interface_rounded_to_f16(gpu, orc, case):
+    """f16 q and out (the reference's kv16 io16 dh64 route, flash.rs:76-78, 193-212): with a q that
+    f16 holds exactly, the kernel sees the same operands as through the f32 interface, so the f16
+    output is that run's output rounded to nearest even -- and within the tensor-core tolerance of
+    the oracle.  Short prefills (T_q < 32) take the tensor-core kernel too on this interface."""
+    ta, ctx, ex = gpu
+    heads, kv_heads, t_q, t_max, dh, kv_len, pos_base = case
+    scale = 1.0 / np.sqrt(dh)
+    kt_h, v_h = fill_kv(orc, kv_heads, t_max, dh, kv_len, 6e4)
+    kt_h, v_h = orc.round_via_f16(kt_h), orc.round_via_f16(v_h)
+    q_h = orc.round_via_f16(orc.fill_det(heads * t_q * dh, 5104)).reshape(heads, t_q, dh)
+    kt, v = upload(ta, ctx, ex, kt_h, True), upload(ta, ctx, ex, v_h, True)
+    q16, q32 = upload(ta, ctx, ex, q_h, True), upload(ta, ctx, ex, q_h)
+    out16 = ta.Tensor.uninit_device_f16(ctx, (t_q, heads * dh))
+    ex.upload(np.zeros(heads * t_q * dh, np.float32), out16)
+    ex.run_flash_attention(q16, kt, v, out16, kv_len, pos_base, scale, out_token_major_heads=heads)
+    got16 = ex.download(out16).reshape(t_q, heads, dh).transpose(1, 0, 2).reshape(-1)
+    ref = orc.cpu_flash(q_h, kt_h, v_h, heads, kv_heads, t_q, dh, t_max, kv_len, pos_base, scale)
+    assert np.isfinite(got16).all()
+    assert np.abs(got16 - ref).max() <= MMA_TOL + 2.0 ** -11 * np.abs(ref).max()
+    if t_q >= 32:
+        out32 = ta.Tensor.uninit_device(ctx, (t_q, heads * dh))
+        ex.upload(np.zeros(heads * t_q * dh, np.float32), out32)
+        ex.run_flash_attention(q32, kt, v, out32, kv_len, pos_base, scale, out_token_major_heads=heads)
+        want = ex.download(out32).astype(np.float16).astype(np.float32)
+        assert np.array_equal(ex.download(out16), want)
+
+
+def test_flash_io16_rejections(gpu, orc):
+    ta, ctx, ex = gpu
+    E = ta.TensorAshError
+    q16 = ta.Tensor.uninit_device_f16(ctx, (4, 8, 64))
+    out16 = ta.Tensor.uninit_device_f16(ctx, (4, 8, 64))
+    out32 = ta.Tensor.uninit_device(ctx, (4, 8, 64))
+    kt16, v16 = ta.Tensor.uninit_device_f16(ctx, (2, 64, 32)), ta.Tensor.uninit_device_f16(ctx, (2, 32, 64))
+    kt32, v32 = ta.Tensor.uninit_device(ctx, (2, 64, 32)), ta.Tensor.uninit_device(ctx, (2, 32, 64))
+    with pytest.raises(E, match=r"input \(f16\) and output \(f32\) must share a storage type"):
+        ex.run_flash_attention(q16, kt16, v16, out32, 8, 0, 0.125)
+    with pytest.raises(E, match="f16 q/out are compiled for f16 KV caches with head dimension 64"):
+        ex.run_flash_attention(q16, kt32, v32, out16, 8, 0, 0.125)
+    with pytest.raises(E, match="f16 q/out are compiled for f16 KV caches with head dimension 64"):
+        ex.run_flash_attention(q16, kt16, v16, out16, 8, 0, 0.125, simt=True)
+
+
 def test_flash_config5_shape(gpu, orc):
     """32 Q heads / 4 KV heads, dh 64, T_q = kv_len = 512, f16 KV, token-major out."""
     ta, ctx, ex = gpu
