@@ -110,7 +110,7 @@ def build_tools() -> str:
         if os.path.exists(exe) and os.path.getmtime(exe) >= max(os.path.getmtime(src), os.path.getmtime(LIB),
                                                                _headers_mtime()):
             continue
-        cmd = [cxx, "-O2", "-std=c++17", "-Wall", src, "-o", exe, "-L", LIB_DIR, "-ltensor_ash",
+        cmd = [cxx, "-O2", "-std=c++17", "-Wall", "-pthread", src, "-o", exe, "-L", LIB_DIR, "-ltensor_ash",
                "-Wl,-rpath,$ORIGIN/../lib"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

@@ -219,7 +219,146 @@ static void launch_ffma_t(const GemmParams &p, float *scratch, cudaStream_t stre
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
+// The two degenerate shapes of the SIMT family (the reference's col_bda and outer_bda kernels,
+// src/pipeline/catalog.rs:272-281, chosen there only when N == 1 / K == 1, pipeline/mod.rs:530-531):
+// a 64 x 64 tile would spend 63 of its 64 columns (or its whole K loop) on padding.
+//
+// N == 1: C[b, m] = epi(alpha * A[b, m, :] . B[b, :, 0]); one warp per row, lanes stride k with
+// coalesced loads, each lane one fmaf chain over its k ascending, then a fixed xor-shuffle tree.
+template <bool B_F16>
+__global__ void __launch_bounds__(256)
+gemm_col_kernel(GemmParams p) {
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t row = blockIdx.x * 8 + warp, batch = blockIdx.y;
+  if (row >= p.m) return;
+  const float *__restrict__ a = (const float *)p.a + (size_t)batch * p.stride_a + (size_t)row * p.k;
+  const float *__restrict__ bf = (const float *)p.b + (size_t)batch * p.stride_b;
+  const __half *__restrict__ bh = (const __half *)p.b + (size_t)batch * p.stride_b;
+  float acc = 0.0f;
+  for (uint32_t k = lane; k < p.k; k += 32) acc = fmaf(a[k], B_F16 ? __half2float(bh[k]) : bf[k], acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    const size_t idx = (size_t)batch * p.stride_c + row;
+    float v = p.alpha == 1.0f ? acc : p.alpha * acc;
+    if (p.accumulate) v += p.c[idx];
+    const float bias = p.bias ? p.bias[(size_t)batch * p.bias_stride] : 0.0f;
+    const float d = p.d ? p.d[idx] : 0.0f;
+    epi_dispatch_act(p.act, [&](auto act_tag) {
+      v = epi_apply_t<decltype(act_tag)::value>(v, p.bias != nullptr, bias, p.binary, d, p.beta);
+    });
+    p.c[idx] = v;
+  }
+}
+
+// K == 1: C[b, m, n] = epi(alpha * A[b, m] * B[b, n]); one thread per output, rows of C coalesced.
+template <bool B_F16>
+__global__ void __launch_bounds__(256)
+gemm_outer_kernel(GemmParams p) {
+  const uint32_t col = blockIdx.x * 256 + threadIdx.x, row = blockIdx.y, batch = blockIdx.z;
+  if (col >= p.n) return;
+  const float av = ((const float *)p.a)[(size_t)batch * p.stride_a + row];
+  const float bv = B_F16 ? __half2float(((const __half *)p.b)[(size_t)batch * p.stride_b + col])
+                         : ((const float *)p.b)[(size_t)batch * p.stride_b + col];
+  const size_t idx = (size_t)batch * p.stride_c + (size_t)row * p.n + col;
+  float v = fmaf(av, bv, 0.0f);
+  if (p.alpha != 1.0f) v *= p.alpha;
+  if (p.accumulate) v += p.c[idx];
+  const float bias = p.bias ? p.bias[(size_t)batch * p.bias_stride + col] : 0.0f;
+  const float d = p.d ? p.d[idx] : 0.0f;
+  epi_dispatch_act(p.act, [&](auto act_tag) {
+    v = epi_apply_t<decltype(act_tag)::value>(v, p.bias != nullptr, bias, p.binary, d, p.beta);
+  });
+  p.c[idx] = v;
+}
+
+// M <= 8 rows over f32 weights (the reference's row_bda shape; f16 weights have their own GEMV):
+// a CTA owns 64 columns, 16 column quads x 16 k slices; thread (slice, quad) walks k = slice,
+// slice + 16, ... with 16-byte loads of B rows (a warp reads two full 256-byte row segments) and
+// keeps MR x 4 sums; the 16 slices are added in slice order through shared memory.
+template <int MR>
+__global__ void __launch_bounds__(256)
+gemm_rows_f32_kernel(GemmParams p) {
+  __shared__ float red[16][MR][64 + 4];
+  const uint32_t quad = threadIdx.x & 15, slice = threadIdx.x >> 4;
+  const uint32_t col = blockIdx.x * 64 + quad * 4, batch = blockIdx.y;
+  const float *__restrict__ A = (const float *)p.a + (size_t)batch * p.stride_a;
+  const float *__restrict__ B = (const float *)p.b + (size_t)batch * p.stride_b;
+  float acc[MR][4];
+#pragma unroll
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
+  const bool vec = (p.n & 3u) == 0 && (p.stride_b & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.b) & 15u) == 0;
+  if (col < p.n) {
+#pragma unroll 4
+    for (uint32_t k = slice; k < p.k; k += 16) {
+      float w[4] = {0.f, 0.f, 0.f, 0.f};
+      const float *src = B + (size_t)k * p.n + col;
+      if (vec && col + 4 <= p.n) {
+        const float4 t = *reinterpret_cast<const float4 *>(src);
+        w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+      } else {
+        for (uint32_t j = 0; j < 4 && col + j < p.n; ++j) w[j] = src[j];
+      }
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        const float x = (uint32_t)m < p.m ? A[(size_t)m * p.k + k] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[m][j] = fmaf(x, w[j], acc[m][j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) red[slice][m][quad * 4 + j] = acc[m][j];
+  __syncthreads();
+  // thread -> (row, column) of the tile; slices added in order 0..15
+  for (uint32_t i = threadIdx.x; i < (uint32_t)MR * 64; i += 256) {
+    const uint32_t m = i / 64, c = i % 64, gc = blockIdx.x * 64 + c;
+    if (m >= p.m || gc >= p.n) continue;
+    float v = 0.0f;
+#pragma unroll
+    for (int sidx = 0; sidx < 16; ++sidx) v += red[sidx][m][c];
+    const size_t idx = (size_t)batch * p.stride_c + (size_t)m * p.n + gc;
+    if (p.alpha != 1.0f) v *= p.alpha;
+    if (p.accumulate) v += p.c[idx];
+    const float bias = p.bias ? p.bias[(size_t)batch * p.bias_stride + gc] : 0.0f;
+    const float d = p.d ? p.d[idx] : 0.0f;
+    epi_dispatch_act(p.act, [&](auto act_tag) {
+      v = epi_apply_t<decltype(act_tag)::value>(v, p.bias != nullptr, bias, p.binary, d, p.beta);
+    });
+    p.c[idx] = v;
+  }
+}
+
 void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream) {
+  if (p.n == 1 && p.batch <= 65535) {
+    dim3 grid((p.m + 7) / 8, p.batch);
+    if (p.b_f16) gemm_col_kernel<true><<<grid, 256, 0, stream>>>(p);
+    else gemm_col_kernel<false><<<grid, 256, 0, stream>>>(p);
+    TA_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return;
+  }
+  if (p.k == 1 && p.m <= 65535 && p.batch <= 65535) {
+    dim3 grid((p.n + 255) / 256, p.m, p.batch);
+    if (p.b_f16) gemm_outer_kernel<true><<<grid, 256, 0, stream>>>(p);
+    else gemm_outer_kernel<false><<<grid, 256, 0, stream>>>(p);
+    TA_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return;
+  }
+  if (p.m <= 8 && !p.b_f16 && p.n >= 64 && p.k >= 64 && p.batch <= 65535) {
+    dim3 grid((p.n + 63) / 64, p.batch);
+    if (p.m == 1) gemm_rows_f32_kernel<1><<<grid, 256, 0, stream>>>(p);
+    else if (p.m <= 4) gemm_rows_f32_kernel<4><<<grid, 256, 0, stream>>>(p);
+    else gemm_rows_f32_kernel<8><<<grid, 256, 0, stream>>>(p);
+    TA_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return;
+  }
   if (tile >= 128) launch_ffma_t<128, 128, 8, 8, false>(p, nullptr, stream);
   else launch_ffma_t<64, 64, 4, 4, false>(p, nullptr, stream);
 }

@@ -3,11 +3,12 @@
 // environment knobs, compact case specs, sample summaries (min / median / nearest-rank p95),
 // table and CSV columns, and the same sampled validation after timing.
 //
-//   ml_bench self-check | correctness | sweep | single | cases label,b,m,n,k[,f16w] ... | transfer | prepared | all
+//   ml_bench self-check | correctness | sweep | single | cases label,b,m,n,k[,f16w] ... | concurrent | transfer |
+//            prepared | all
 //   ml_bench summary x1 x2 ...      (host only: prints the sample summary of the numbers)
 //
 //   ML_ITERS (20) ML_WARMUP (3) ML_OUTPUT (table | csv) ML_SWEEP (smoke | standard | full)
-//   ML_B ML_M ML_N ML_K   ML_SPLIT_K2 (0)   ML_SLOTS (2)   ML_KERNEL (auto)   ML_DEVICE   ML_VALIDATE
+//   ML_B ML_M ML_N ML_K   ML_SPLIT_K2 (0)   ML_SLOTS (2)   ML_THREADS   ML_KERNEL (auto)   ML_DEVICE   ML_VALIDATE
 //   ML_PEAK_TFLOPS: the "%peak" denominator; default 232.5, the FP32-through-3xTF32 ceiling of a
 //   B200 (measured sustained bf16 rate / 2 / 3); the reference's default is its own GPU's 20.3.
 #include <algorithm>
@@ -18,6 +19,7 @@
 #include <cstring>
 #include <string>
 #include <strings.h>
+#include <thread>
 #include <vector>
 
 #include "../../include/tensor_ash.h"
@@ -530,13 +532,65 @@ void prepared(const Session &s) {
   for (auto &t : c) ta_tensor_destroy(t);
 }
 
+// commands.rs:292-356: ML_THREADS host threads (default: the hardware concurrency) share one
+// executor, each running ML_ITERS (50) products of 512^3 on its own tensors; every output is
+// validated afterwards.
+void concurrent(const Session &s) {
+  const uint32_t hw = std::max(1u, std::thread::hardware_concurrency());
+  const uint32_t n_threads = std::max(1u, env_u32("ML_THREADS", hw ? hw : 4));
+  const uint32_t iters = std::max(1u, env_u32("ML_ITERS", 50));
+  const uint32_t m = 512, n = 512, k = 512, shape_a[2] = {m, k}, shape_b[2] = {k, n}, shape_c[2] = {m, n};
+  struct Triple {
+    ta_tensor *a, *b, *c;
+    std::vector<float> ha, hb;
+  };
+  std::vector<Triple> tr(n_threads);
+  for (uint32_t t = 0; t < n_threads; ++t) {
+    tr[t].a = ta_tensor_create(s.ctx, shape_a, 2);
+    tr[t].b = ta_tensor_create(s.ctx, shape_b, 2);
+    tr[t].c = ta_tensor_create(s.ctx, shape_c, 2);
+    if (!tr[t].a || !tr[t].b || !tr[t].c) die_lib("tensor");
+    tr[t].ha.resize((size_t)m * k);
+    tr[t].hb.resize((size_t)k * n);
+    fill_det(tr[t].ha, 100 + t);
+    fill_det(tr[t].hb, 200 + t);
+    if (ta_upload(s.exec, tr[t].a, tr[t].ha.data(), tr[t].ha.size()) != 0 ||
+        ta_upload(s.exec, tr[t].b, tr[t].hb.data(), tr[t].hb.size()) != 0)
+      die_lib("upload");
+  }
+  std::vector<std::string> errors(n_threads);
+  const double t0 = now_ms();
+  std::vector<std::thread> pool;
+  for (uint32_t t = 0; t < n_threads; ++t)
+    pool.emplace_back([&, t]() {
+      for (uint32_t i = 0; i < iters; ++i)
+        if (ta_matmul(s.exec, tr[t].a, tr[t].b, tr[t].c, 1.0f, 0, nullptr) != 0) {
+          errors[t] = ta_last_error();   // the message is per thread
+          return;
+        }
+    });
+  for (auto &th : pool) th.join();
+  const double dt = (now_ms() - t0) / 1e3;
+  for (uint32_t t = 0; t < n_threads; ++t)
+    if (!errors[t].empty()) die("run_matmuls (thread " + std::to_string(t) + "): " + errors[t]);
+  for (uint32_t t = 0; t < n_threads; ++t) validate_samples(s, tr[t].c, tr[t].ha, tr[t].hb, 1, m, n, k);
+  const double total = 2.0 * m * n * k * (double)iters * n_threads;
+  printf("concurrent: %u threads x %u iters of 512^3   total %.1f GFLOPs  in %.3fs  ->  %.2f TFLOPS (aggregate)\n",
+         n_threads, iters, total * 1e-9, dt, total / dt * 1e-12);
+  for (auto &x : tr) {
+    ta_tensor_destroy(x.a);
+    ta_tensor_destroy(x.b);
+    ta_tensor_destroy(x.c);
+  }
+}
+
 }  // namespace
 
 int main(int argc, char **argv) {
   const std::string cmd = argc > 1 ? argv[1] : "all";
-  static const char *known[] = {"self-check", "correctness", "sweep", "single", "cases", "transfer", "prepared", "all", "summary"};
+  static const char *known[] = {"self-check", "correctness", "sweep", "single", "cases", "concurrent", "transfer", "prepared", "all", "summary"};
   if (std::find_if(std::begin(known), std::end(known), [&](const char *k) { return cmd == k; }) == std::end(known))
-    die("unknown subcommand '" + cmd + "'; expected self-check, correctness, sweep, single, cases, transfer, prepared, or all");
+    die("unknown subcommand '" + cmd + "'; expected self-check, correctness, sweep, single, cases, concurrent, transfer, prepared, or all");
   std::vector<std::string> rest;
   for (int i = 2; i < argc; ++i) rest.push_back(argv[i]);
   if (cmd == "summary") {   // host only: the sample summary of the given numbers (nan / inf / negatives are dropped)
@@ -573,6 +627,8 @@ int main(int argc, char **argv) {
     single(s);
   } else if (cmd == "cases") {
     cases(s, rest);
+  } else if (cmd == "concurrent") {
+    concurrent(s);
   } else if (cmd == "transfer") {
     transfer(s);
   } else if (cmd == "prepared") {

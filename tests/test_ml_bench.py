@@ -97,6 +97,8 @@ def test_table_sweep_single_prepared_and_transfer():
     r = ml_bench("prepared", ML_ITERS=50, ML_WARMUP=5)
     assert r.returncode == 0, r.stderr
     assert "all outputs validated" in r.stdout and "prepared replay" in r.stdout and "pipelined x2" in r.stdout
+    r = ml_bench("concurrent", ML_THREADS=6, ML_ITERS=20, ML_SLOTS=3)
+    assert r.returncode == 0 and "concurrent: 6 threads x 20 iters of 512^3" in r.stdout, r.stderr
     r = ml_bench("transfer", ML_TRANSFER_MB=8, ML_ITERS=4)
     assert r.returncode == 0 and "transfer: 8 MiB x 4 samples" in r.stdout, r.stderr
     r = ml_bench("transfer", ML_TRANSFER_MB=8, ML_ITERS=4, ML_OUTPUT="csv")
