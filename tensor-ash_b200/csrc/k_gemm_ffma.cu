@@ -251,25 +251,44 @@ gemm_col_kernel(GemmParams p) {
   }
 }
 
-// K == 1: C[b, m, n] = epi(alpha * A[b, m] * B[b, n]); one thread per output, rows of C coalesced.
-template <bool B_F16>
+// K == 1: C[b, m, n] = epi(alpha * A[b, m] * B[b, n]); VEC consecutive outputs per thread (four
+// with 16-byte accesses when N, the strides and the bases allow), rows of C coalesced.
+template <bool B_F16, int VEC>
 __global__ void __launch_bounds__(256)
 gemm_outer_kernel(GemmParams p) {
-  const uint32_t col = blockIdx.x * 256 + threadIdx.x, row = blockIdx.y, batch = blockIdx.z;
+  const uint32_t col = (blockIdx.x * 256 + threadIdx.x) * VEC, row = blockIdx.y, batch = blockIdx.z;
   if (col >= p.n) return;
   const float av = ((const float *)p.a)[(size_t)batch * p.stride_a + row];
-  const float bv = B_F16 ? __half2float(((const __half *)p.b)[(size_t)batch * p.stride_b + col])
-                         : ((const float *)p.b)[(size_t)batch * p.stride_b + col];
   const size_t idx = (size_t)batch * p.stride_c + (size_t)row * p.n + col;
-  float v = fmaf(av, bv, 0.0f);
-  if (p.alpha != 1.0f) v *= p.alpha;
-  if (p.accumulate) v += p.c[idx];
-  const float bias = p.bias ? p.bias[(size_t)batch * p.bias_stride + col] : 0.0f;
-  const float d = p.d ? p.d[idx] : 0.0f;
+  float bv[VEC], cv[VEC], dv[VEC], biasv[VEC], v[VEC];
+  if constexpr (VEC == 4) {
+    const float4 t = *reinterpret_cast<const float4 *>((const float *)p.b + (size_t)batch * p.stride_b + col);
+    bv[0] = t.x; bv[1] = t.y; bv[2] = t.z; bv[3] = t.w;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 c4 = p.accumulate ? *reinterpret_cast<const float4 *>(p.c + idx) : z;
+    const float4 d4 = p.d ? *reinterpret_cast<const float4 *>(p.d + idx) : z;
+    const float4 b4 = p.bias ? *reinterpret_cast<const float4 *>(p.bias + (size_t)batch * p.bias_stride + col) : z;
+    cv[0] = c4.x; cv[1] = c4.y; cv[2] = c4.z; cv[3] = c4.w;
+    dv[0] = d4.x; dv[1] = d4.y; dv[2] = d4.z; dv[3] = d4.w;
+    biasv[0] = b4.x; biasv[1] = b4.y; biasv[2] = b4.z; biasv[3] = b4.w;
+  } else {
+    bv[0] = B_F16 ? __half2float(((const __half *)p.b)[(size_t)batch * p.stride_b + col])
+                  : ((const float *)p.b)[(size_t)batch * p.stride_b + col];
+    cv[0] = p.accumulate ? p.c[idx] : 0.0f;
+    dv[0] = p.d ? p.d[idx] : 0.0f;
+    biasv[0] = p.bias ? p.bias[(size_t)batch * p.bias_stride + col] : 0.0f;
+  }
   epi_dispatch_act(p.act, [&](auto act_tag) {
-    v = epi_apply_t<decltype(act_tag)::value>(v, p.bias != nullptr, bias, p.binary, d, p.beta);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      float x = fmaf(av, bv[j], 0.0f);
+      if (p.alpha != 1.0f) x *= p.alpha;
+      if (p.accumulate) x += cv[j];
+      v[j] = epi_apply_t<decltype(act_tag)::value>(x, p.bias != nullptr, biasv[j], p.binary, dv[j], p.beta);
+    }
   });
-  p.c[idx] = v;
+  if constexpr (VEC == 4) *reinterpret_cast<float4 *>(p.c + idx) = make_float4(v[0], v[1], v[2], v[3]);
+  else p.c[idx] = v[0];
 }
 
 // M <= 8 rows over f32 weights (the reference's row_bda shape; f16 weights have their own GEMV):
@@ -343,9 +362,14 @@ void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream) {
     return;
   }
   if (p.k == 1 && p.m <= 65535 && p.batch <= 65535) {
-    dim3 grid((p.n + 255) / 256, p.m, p.batch);
-    if (p.b_f16) gemm_outer_kernel<true><<<grid, 256, 0, stream>>>(p);
-    else gemm_outer_kernel<false><<<grid, 256, 0, stream>>>(p);
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(p.b) | reinterpret_cast<uintptr_t>(p.c) |
+                           reinterpret_cast<uintptr_t>(p.d) | reinterpret_cast<uintptr_t>(p.bias);
+    const bool vec = !p.b_f16 && p.n % 4 == 0 && p.stride_b % 4 == 0 && p.stride_c % 4 == 0 && p.bias_stride % 4 == 0 &&
+                     (ptrs & 15) == 0;
+    dim3 grid((p.n + (vec ? 1023 : 255)) / (vec ? 1024 : 256), p.m, p.batch);
+    if (vec) gemm_outer_kernel<false, 4><<<grid, 256, 0, stream>>>(p);
+    else if (p.b_f16) gemm_outer_kernel<true, 1><<<grid, 256, 0, stream>>>(p);
+    else gemm_outer_kernel<false, 1><<<grid, 256, 0, stream>>>(p);
     TA_CUDA(cudaGetLastError());
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return;
