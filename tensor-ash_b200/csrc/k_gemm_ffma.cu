@@ -292,15 +292,17 @@ gemm_outer_kernel(GemmParams p) {
 }
 
 // M <= 8 rows over f32 weights (the reference's row_bda shape; f16 weights have their own GEMV):
-// a CTA owns 64 columns, 16 column quads x 16 k slices; thread (slice, quad) walks k = slice,
-// slice + 16, ... with 16-byte loads of B rows (a warp reads two full 256-byte row segments) and
-// keeps MR x 4 sums; the 16 slices are added in slice order through shared memory.
+// a CTA owns 32 columns (so that 4096 columns already fill 128 SMs), 8 column quads x 32 k slices;
+// thread (slice, quad) walks k = slice, slice + 32, ... with 16-byte loads of B rows (a warp reads
+// four full 128-byte row segments, eight loads in flight per thread) and keeps MR x 4 sums; the 32
+// slices are added in slice order through shared memory.
+constexpr uint32_t ROWS_QUADS = 8, ROWS_SLICES = 256 / ROWS_QUADS, ROWS_COLS = ROWS_QUADS * 4;
 template <int MR>
 __global__ void __launch_bounds__(256)
 gemm_rows_f32_kernel(GemmParams p) {
-  __shared__ float red[16][MR][64 + 4];
-  const uint32_t quad = threadIdx.x & 15, slice = threadIdx.x >> 4;
-  const uint32_t col = blockIdx.x * 64 + quad * 4, batch = blockIdx.y;
+  __shared__ float red[ROWS_SLICES][MR][ROWS_COLS + 4];
+  const uint32_t quad = threadIdx.x % ROWS_QUADS, slice = threadIdx.x / ROWS_QUADS;
+  const uint32_t col = blockIdx.x * ROWS_COLS + quad * 4, batch = blockIdx.y;
   const float *__restrict__ A = (const float *)p.a + (size_t)batch * p.stride_a;
   const float *__restrict__ B = (const float *)p.b + (size_t)batch * p.stride_b;
   float acc[MR][4];
@@ -310,8 +312,8 @@ gemm_rows_f32_kernel(GemmParams p) {
     for (int j = 0; j < 4; ++j) acc[m][j] = 0.0f;
   const bool vec = (p.n & 3u) == 0 && (p.stride_b & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.b) & 15u) == 0;
   if (col < p.n) {
-#pragma unroll 4
-    for (uint32_t k = slice; k < p.k; k += 16) {
+#pragma unroll 8
+    for (uint32_t k = slice; k < p.k; k += ROWS_SLICES) {
       float w[4] = {0.f, 0.f, 0.f, 0.f};
       const float *src = B + (size_t)k * p.n + col;
       if (vec && col + 4 <= p.n) {
@@ -333,13 +335,13 @@ gemm_rows_f32_kernel(GemmParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) red[slice][m][quad * 4 + j] = acc[m][j];
   __syncthreads();
-  // thread -> (row, column) of the tile; slices added in order 0..15
-  for (uint32_t i = threadIdx.x; i < (uint32_t)MR * 64; i += 256) {
-    const uint32_t m = i / 64, c = i % 64, gc = blockIdx.x * 64 + c;
+  // thread -> (row, column) of the tile; slices added in ascending order
+  for (uint32_t i = threadIdx.x; i < (uint32_t)MR * ROWS_COLS; i += 256) {
+    const uint32_t m = i / ROWS_COLS, c = i % ROWS_COLS, gc = blockIdx.x * ROWS_COLS + c;
     if (m >= p.m || gc >= p.n) continue;
     float v = 0.0f;
 #pragma unroll
-    for (int sidx = 0; sidx < 16; ++sidx) v += red[sidx][m][c];
+    for (uint32_t sidx = 0; sidx < ROWS_SLICES; ++sidx) v += red[sidx][m][c];
     const size_t idx = (size_t)batch * p.stride_c + (size_t)m * p.n + gc;
     if (p.alpha != 1.0f) v *= p.alpha;
     if (p.accumulate) v += p.c[idx];
@@ -375,7 +377,7 @@ void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream) {
     return;
   }
   if (p.m <= 8 && !p.b_f16 && p.n >= 64 && p.k >= 64 && p.batch <= 65535) {
-    dim3 grid((p.n + 63) / 64, p.batch);
+    dim3 grid((p.n + ROWS_COLS - 1) / ROWS_COLS, p.batch);
     if (p.m == 1) gemm_rows_f32_kernel<1><<<grid, 256, 0, stream>>>(p);
     else if (p.m <= 4) gemm_rows_f32_kernel<4><<<grid, 256, 0, stream>>>(p);
     else gemm_rows_f32_kernel<8><<<grid, 256, 0, stream>>>(p);
