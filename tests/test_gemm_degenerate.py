@@ -12,7 +12,8 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("batch,m,n,k", [(1, 300, 1, 517), (3, 64, 1, 4096), (1, 4096, 1, 4096), (1, 1, 1, 1),
                                          (2, 130, 257, 1), (1, 4096, 512, 1), (1, 7, 1, 1),
                                          # M <= 8 rows over f32 weights (row_bda)
-                                         (1, 1, 4096, 4096), (2, 5, 200, 333), (1, 8, 64, 64), (1, 3, 130, 70)])
+                                         (1, 1, 4096, 4096), (2, 5, 200, 333), (1, 8, 64, 64), (1, 3, 130, 70),
+                                         (2, 6, 256, 512), (1, 4, 4096, 1028)])
 @pytest.mark.parametrize("fused", [False, True])
 def test_column_and_outer_shapes(gpu, orc, batch, m, n, k, fused):
     ta, ctx, ex = gpu
