@@ -291,7 +291,8 @@ gemm_outer_kernel(GemmParams p) {
   else p.c[idx] = v[0];
 }
 
-// M <= 8 rows over f32 weights (the reference's row_bda shape; f16 weights have their own GEMV):
+// M <= 32 rows over f32 weights (the reference's row_bda shape, widened: the 64 x 64 tile takes
+// 215 us for 9..32 rows of 4096 x 4096; f16 weights have their own GEMV).  grid.z walks groups of MR rows:
 // a CTA owns 32 columns (so that 4096 columns already fill 128 SMs), 8 column quads x 32 k slices;
 // thread (slice, quad) walks k = slice, slice + 32, ... with 16-byte loads of B rows (a warp reads
 // four full 128-byte row segments, eight loads in flight per thread) and keeps MR x 4 sums; the 32
@@ -300,10 +301,12 @@ constexpr uint32_t ROWS_QUADS = 8, ROWS_SLICES = 256 / ROWS_QUADS, ROWS_COLS = R
 template <int MR>
 __global__ void __launch_bounds__(256)
 gemm_rows_f32_kernel(GemmParams p) {
-  __shared__ float red[ROWS_SLICES][MR][ROWS_COLS + 4];
+  constexpr int RB = MR < 8 ? MR : 8;   // rows reduced per pass through shared memory
+  __shared__ float red[ROWS_SLICES][RB][ROWS_COLS + 4];
   const uint32_t quad = threadIdx.x % ROWS_QUADS, slice = threadIdx.x / ROWS_QUADS;
   const uint32_t col = blockIdx.x * ROWS_COLS + quad * 4, batch = blockIdx.y;
-  const float *__restrict__ A = (const float *)p.a + (size_t)batch * p.stride_a;
+  const uint32_t m0 = blockIdx.z * MR, rows = p.m - m0;   // rows of this group that exist (may exceed MR)
+  const float *__restrict__ A = (const float *)p.a + (size_t)batch * p.stride_a + (size_t)m0 * p.k;
   const float *__restrict__ B = (const float *)p.b + (size_t)batch * p.stride_b;
   float acc[MR][4];
 #pragma unroll
@@ -323,7 +326,7 @@ gemm_rows_f32_kernel(GemmParams p) {
       for (int r = 0; r < 4; ++r) w[r] = *reinterpret_cast<const float4 *>(B + (size_t)(k + r) * p.n + col);
 #pragma unroll
       for (int m = 0; m < MR; ++m) {
-        const float4 x = (uint32_t)m < p.m ? *reinterpret_cast<const float4 *>(A + (size_t)m * p.k + k)
+        const float4 x = (uint32_t)m < rows ? *reinterpret_cast<const float4 *>(A + (size_t)m * p.k + k)
                                            : make_float4(0.f, 0.f, 0.f, 0.f);
         const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
@@ -348,33 +351,37 @@ gemm_rows_f32_kernel(GemmParams p) {
       }
 #pragma unroll
       for (int m = 0; m < MR; ++m) {
-        const float x = (uint32_t)m < p.m ? A[(size_t)m * p.k + k] : 0.0f;
+        const float x = (uint32_t)m < rows ? A[(size_t)m * p.k + k] : 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[m][j] = fmaf(x, w[j], acc[m][j]);
       }
     }
   }
 #pragma unroll
-  for (int m = 0; m < MR; ++m)
+  for (int h = 0; h < MR; h += RB) {
+    if (h) __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 4; ++j) red[slice][m][quad * 4 + j] = acc[m][j];
-  __syncthreads();
-  // thread -> (row, column) of the tile; slices added in ascending order
-  for (uint32_t i = threadIdx.x; i < (uint32_t)MR * ROWS_COLS; i += 256) {
-    const uint32_t m = i / ROWS_COLS, c = i % ROWS_COLS, gc = blockIdx.x * ROWS_COLS + c;
-    if (m >= p.m || gc >= p.n) continue;
-    float v = 0.0f;
+    for (int m = 0; m < RB; ++m)
 #pragma unroll
-    for (uint32_t sidx = 0; sidx < ROWS_SLICES; ++sidx) v += red[sidx][m][c];
-    const size_t idx = (size_t)batch * p.stride_c + (size_t)m * p.n + gc;
-    if (p.alpha != 1.0f) v *= p.alpha;
-    if (p.accumulate) v += p.c[idx];
-    const float bias = p.bias ? p.bias[(size_t)batch * p.bias_stride + gc] : 0.0f;
-    const float d = p.d ? p.d[idx] : 0.0f;
-    epi_dispatch_act(p.act, [&](auto act_tag) {
-      v = epi_apply_t<decltype(act_tag)::value>(v, p.bias != nullptr, bias, p.binary, d, p.beta);
-    });
-    p.c[idx] = v;
+      for (int j = 0; j < 4; ++j) red[slice][m][quad * 4 + j] = acc[h + m][j];
+    __syncthreads();
+    // thread -> (row, column) of the tile; slices added in ascending order
+    for (uint32_t i = threadIdx.x; i < (uint32_t)RB * ROWS_COLS; i += 256) {
+      const uint32_t m = i / ROWS_COLS, c = i % ROWS_COLS, gc = blockIdx.x * ROWS_COLS + c;
+      if (h + m >= rows || gc >= p.n) continue;
+      float v = 0.0f;
+#pragma unroll
+      for (uint32_t sidx = 0; sidx < ROWS_SLICES; ++sidx) v += red[sidx][m][c];
+      const size_t idx = (size_t)batch * p.stride_c + (size_t)(m0 + h + m) * p.n + gc;
+      if (p.alpha != 1.0f) v *= p.alpha;
+      if (p.accumulate) v += p.c[idx];
+      const float bias = p.bias ? p.bias[(size_t)batch * p.bias_stride + gc] : 0.0f;
+      const float d = p.d ? p.d[idx] : 0.0f;
+      epi_dispatch_act(p.act, [&](auto act_tag) {
+        v = epi_apply_t<decltype(act_tag)::value>(v, p.bias != nullptr, bias, p.binary, d, p.beta);
+      });
+      p.c[idx] = v;
+    }
   }
 }
 
@@ -400,11 +407,13 @@ void launch_gemm_ffma(const GemmParams &p, uint32_t tile, cudaStream_t stream) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return;
   }
-  if (p.m <= 8 && !p.b_f16 && p.n >= 64 && p.k >= 64 && p.batch <= 65535) {
-    dim3 grid((p.n + ROWS_COLS - 1) / ROWS_COLS, p.batch);
-    if (p.m == 1) gemm_rows_f32_kernel<1><<<grid, 256, 0, stream>>>(p);
-    else if (p.m <= 4) gemm_rows_f32_kernel<4><<<grid, 256, 0, stream>>>(p);
-    else gemm_rows_f32_kernel<8><<<grid, 256, 0, stream>>>(p);
+  if (p.m <= 32 && !p.b_f16 && p.n >= 64 && p.k >= 64 && p.batch <= 65535) {
+    const uint32_t mr = p.m == 1 ? 1 : p.m <= 4 ? 4 : p.m <= 8 ? 8 : 16;
+    dim3 grid((p.n + ROWS_COLS - 1) / ROWS_COLS, p.batch, (p.m + mr - 1) / mr);
+    if (mr == 1) gemm_rows_f32_kernel<1><<<grid, 256, 0, stream>>>(p);
+    else if (mr == 4) gemm_rows_f32_kernel<4><<<grid, 256, 0, stream>>>(p);
+    else if (mr == 8) gemm_rows_f32_kernel<8><<<grid, 256, 0, stream>>>(p);
+    else gemm_rows_f32_kernel<16><<<grid, 256, 0, stream>>>(p);
     TA_CUDA(cudaGetLastError());
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return;

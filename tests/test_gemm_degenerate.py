@@ -1,4 +1,4 @@
-"""N == 1 (column), K == 1 (outer product) and M <= 8 over f32 weights (rows): the reference's
+"""N == 1 (column), K == 1 (outer product) and M <= 32 over f32 weights (rows): the reference's
 col_bda / outer_bda / row_bda routes (src/pipeline/catalog.rs:264-281, pipeline/mod.rs:530-531),
 here three small kernels of the SIMT family.  Against the f64 oracle with the reference's tolerance, with every fused stage."""
 import numpy as np
@@ -11,9 +11,12 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("batch,m,n,k", [(1, 300, 1, 517), (3, 64, 1, 4096), (1, 4096, 1, 4096), (1, 1, 1, 1),
                                          (2, 130, 257, 1), (1, 4096, 512, 1), (1, 7, 1, 1),
-                                         # M <= 8 rows over f32 weights (row_bda)
+                                         # M <= 32 rows over f32 weights (row_bda, widened)
                                          (1, 1, 4096, 4096), (2, 5, 200, 333), (1, 8, 64, 64), (1, 3, 130, 70),
-                                         (2, 6, 256, 512), (1, 4, 4096, 1028)])
+                                         (2, 6, 256, 512), (1, 4, 4096, 1028),
+                                         # 9..32 rows: groups of 16 rows (one or two per column block)
+                                         (1, 9, 128, 256), (2, 16, 200, 333), (1, 17, 96, 68), (3, 32, 160, 512),
+                                         (1, 29, 70, 65)])
 @pytest.mark.parametrize("fused", [False, True])
 def test_column_and_outer_shapes(gpu, orc, batch, m, n, k, fused):
     ta, ctx, ex = gpu
