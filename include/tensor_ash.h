@@ -486,6 +486,12 @@ uint32_t ta_default_num_k_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_
                                  uint32_t tile_m, uint32_t tile_n);
 uint32_t ta_heuristic_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
 
+/* The kernel the heuristic stage of the routing order (explicit selection > tuned winner > heuristic,
+ * ref src/pipeline/mod.rs:259-360) picks for a plain shape on a device of sm_count SMs: a name of the
+ * kernel registry (static storage).  weights_f16 != 0 selects the f16-storage B family.  Host-only. */
+const char *ta_heuristic_kernel(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int weights_f16,
+                                int sm_count);
+
 /* Software conversions (ref src/dtype.rs:42-112): round-to-nearest-even encode and IEEE binary16
  * decode, bit-exact with the reference on every pattern except subnormal halves, where the
  * reference's decode (dtype.rs:93-99) normalises one bit too far and this one returns the IEEE

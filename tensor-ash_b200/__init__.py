@@ -34,6 +34,7 @@ from .api import (  # noqa: F401
     f32_to_f16_bits,
     pinned_empty,
     f16_bits_to_f32,
+    heuristic_kernel,
     heuristic_splits,
     kernel_launch_count,
     kernel_selection_parse,

@@ -812,6 +812,11 @@ def heuristic_splits(batch, m, n, k) -> Optional[int]:
     return int(lib().ta_heuristic_splits(batch, m, n, k)) or None
 
 
+def heuristic_kernel(batch, m, n, k, weights_f16: bool = False, sm_count: int = 148) -> str:
+    """Registry name the routing heuristic picks for a plain shape (no explicit selection, no tuned entry)."""
+    return lib().ta_heuristic_kernel(batch, m, n, k, int(weights_f16), sm_count).decode()
+
+
 def kernel_specs():
     out = []
     for i in range(lib().ta_kernel_spec_count()):

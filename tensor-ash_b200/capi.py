@@ -167,6 +167,7 @@ SIGNATURES = {
                                     C.POINTER(_U32)]),
     "ta_default_num_k_splits": (_U32, [_U32] * 6),
     "ta_heuristic_splits": (_U32, [_U32] * 4),
+    "ta_heuristic_kernel": (C.c_char_p, [_U32] * 4 + [C.c_int, C.c_int]),
     "ta_f32_to_f16_bits": (C.c_uint16, [C.c_float]),
     "ta_f16_bits_to_f32": (C.c_float, [C.c_uint16]),
     "ta_tensor_device_ptr": (_P, [_P]),

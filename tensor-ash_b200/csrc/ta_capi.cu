@@ -847,6 +847,11 @@ uint32_t ta_heuristic_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k)
   return heuristic_splits(batch, m, n, k).value_or(0);
 }
 
+const char *ta_heuristic_kernel(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int weights_f16, int sm_count) {
+  const int idx = heuristic_kernel_index(batch, m, n, k, weights_f16 != 0, sm_count > 0 ? sm_count : 1);
+  return KERNEL_SPECS[idx].name;
+}
+
 uint16_t ta_f32_to_f16_bits(float value) { return f32_to_f16_bits(value); }
 float ta_f16_bits_to_f32(uint16_t bits) { return f16_bits_to_f32(bits); }
 

@@ -204,6 +204,8 @@ extern const size_t KERNEL_SPEC_COUNT;
 // Returns -2 for "auto"/"", an index into KERNEL_SPECS, or throws.
 int kernel_selection_parse(const std::string &value);
 int kernel_index_by_name(const char *name);  // -1 when absent
+// Heuristic stage of the routing order: index into KERNEL_SPECS for a plain shape.
+int heuristic_kernel_index(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16, int sm_count);
 
 // Row-GEMV routing (src/pipeline/routing.rs:10-41).
 bool f16w_row_uses_k16(uint32_t k, uint32_t n);

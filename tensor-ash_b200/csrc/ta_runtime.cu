@@ -325,6 +325,10 @@ bool family_matches_dtype(const KernelSpec &spec, bool b_f16) { return spec.weig
 
 }  // namespace
 
+int heuristic_kernel_index(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16, int sm_count) {
+  return heuristic_kernel(batch, m, n, k, b_f16, sm_count);
+}
+
 Route Executor::plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16,
                            bool allow_split_k2) const {
   Route r;

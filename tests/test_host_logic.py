@@ -251,3 +251,29 @@ def test_c_smoke_source_compiles_against_the_header(tmp_path, ta):
                     "-o", str(exe), "-L", libdir, "-ltensor_ash", f"-Wl,-rpath,{libdir}"], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True)
     assert out.stdout.strip() == "2.0.0"
+
+
+def test_heuristic_kernel_routing_table(ta):
+    """Heuristic stage of explicit > tuned > heuristic (src/pipeline/mod.rs:259-360), on a 148-SM device:
+    aligned f32 problems of 64 rows or more use the tensor-core tiles (the narrow tile when the wide one
+    would leave SMs idle), 33..63 rows only over a large weight matrix, everything else the SIMT tiles;
+    f16-storage weights use the row GEMV to 8 rows and the f16 tensor-core tiles from 32 rows."""
+    hk = ta.heuristic_kernel
+    assert hk(32, 2048, 2048, 2048) == "tf32x3_m128n256"          # the benchmark configuration
+    assert hk(1, 1024, 1024, 1024) == "tf32x3_m128n128"           # 32 wide tiles would idle 116 SMs
+    assert hk(1, 512, 128, 512) == "tf32x3_m128n128"              # narrow N
+    assert hk(1, 64, 4096, 4096) == "tf32x3_m128n128"
+    assert hk(1, 48, 4096, 4096) == "tf32x3_m128n128"             # 33..63 rows over 2^24 weights
+    assert hk(1, 48, 256, 256) == "ffma_m64n64"                   # 33..63 rows over small weights
+    assert hk(1, 32, 4096, 4096) == "ffma_m64n64"                 # the rows kernel lives in this family
+    assert hk(1, 1023, 1025, 1027) == "ffma_m128n128"             # unaligned: no TMA
+    assert hk(1, 100, 100, 100) == "tf32x3_m128n128"              # aligned and 64 or more each way
+    assert hk(1, 50, 50, 50) == "ffma_m64n64"
+    assert hk(1, 1, 11008, 4096, True).startswith("f16w_row_bda_k16")
+    assert hk(1, 8, 4096, 11008, True).startswith("f16w_row_bda_k16")
+    assert hk(1, 512, 2048, 2048, True).startswith("f16w_umma_m128n")
+    assert hk(1, 16, 2048, 2048, True) == "f16w_ffma_m64n64"
+    assert hk(1, 512, 2047, 2048, True) == "f16w_ffma_m128n128"   # N not a multiple of 8
+    names = {name for name, _tile in ta.kernel_specs()}
+    for shape in [(1, 7, 9, 11), (4, 300, 300, 300), (1, 4096, 4096, 4096)]:
+        assert hk(*shape) in names and hk(*shape, True) in names
