@@ -262,16 +262,23 @@ int ta_matmul_split_k2(const ta_executor *exec, const ta_matmul_call *calls, siz
  * library, until the process exits) and calls no cudaMalloc, cudaFree or any
  * other allocating routine.
  *
- * C[M,N] = alpha * A[M,K] @ B[K,N], row-major f32, one matrix per call, same
- * two kernels and therefore bit-identical results to ta_matmul_split_k2.
+ * C[M,N] = alpha * A[M,K] @ B[K,N], row-major f32, one matrix per call, on the
+ * SIMT stage-1 kernel (one sequential fma chain per output and split) and the
+ * plane-order reduce: bit-identical to ta_matmul_split_k2 on an executor whose
+ * kernel selection names that stage 1 ("split_k2_m64n64" / "split_k2_m128n128";
+ * an "auto" executor may take its tensor-core stage 1, equal within rounding).
  * a, b, c are device pointers on the CURRENT CUDA device; the caller owns them.
  * Limits: splits >= 2, splits <= K, splits * M * N <=
  * TA_SPLIT_K2_NOALLOC_MAX_FLOATS; anything larger is rejected with -1 and a
- * message.  The call enqueues on `stream` (NULL = default stream) and returns
- * after that stream has finished the two kernels.
+ * message.  The call enqueues on `stream` (NULL = default stream) and then
+ * synchronises that stream: it returns after the two kernels have finished.
  *
  * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call before any stream capture.
+ * (cudaGetSymbolAddress) and, if nothing of the library ran on that device
+ * before, pays the CUDA runtime's lazy load of the library's device code, which
+ * may reserve device memory of its own; make that first call at start-up,
+ * before any stream capture.  Later calls allocate nothing
+ * (cudaMemGetInfo reads the same before and after them).
  * Every call uses the same array and leaves its partials there: nothing needs
  * clearing between calls (each plane element is stored before it is read), but
  * two calls that overlap on the GPU, from any thread or stream, race. */
@@ -440,6 +447,13 @@ typedef struct ta_comm ta_comm;
 int ta_comm_unique_id(uint8_t out[TA_COMM_ID_BYTES]);
 ta_comm *ta_comm_create(const ta_context *ctx, uint32_t rank, uint32_t world, const uint8_t *id);
 void ta_comm_destroy(ta_comm *comm);
+/* Small all-reduces of the group travel as peer stores with flags; a rank waits on the device for
+ * its peers' flags at most this long (default 10 s: ranks of one job drift by whole milliseconds
+ * while one still loads weights), then the kernel returns, the call fails (-1, "... wait for a peer
+ * rank ...") and the context stays usable.  After such a failure every rank calls ta_comm_resync
+ * (collective: two NCCL meetings around zeroing the flags) before the next exchange. */
+int ta_comm_set_wait_limit_ns(ta_comm *comm, uint64_t limit_ns);
+int ta_comm_resync(ta_comm *comm);
 uint32_t ta_comm_rank(const ta_comm *comm);
 uint32_t ta_comm_world(const ta_comm *comm);
 
@@ -485,6 +499,38 @@ int ta_resolve_shapes(const uint32_t *a, size_t a_rank, const uint32_t *b, size_
 uint32_t ta_default_num_k_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k,
                                  uint32_t tile_m, uint32_t tile_n);
 uint32_t ta_heuristic_splits(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
+
+/* Measured tuner, additions (ref src/executor/tuning.rs:18-344, src/pipeline/tuning.rs:60-199).
+ * ta_tune_shape (PART 1) tunes an f32 shape; ta_tune_shape_f16w the same shape with f16-storage B
+ * (the reference keys winners by (B, M, N, K, b_f16), src/pipeline/tuning.rs:33-45). */
+int ta_tune_shape_f16w(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
+/* Host-only tuner arithmetic, as the reference pins it in src/executor/tuning.rs:319-374:
+ * ta_tune_median: median of n u64 samples, the middle pair's mean rounded down when n is even;
+ *   returns 0 with *out set, 1 when n == 0 (no median), -1 on a null argument.
+ * ta_tune_candidate_at: index of the candidate measured at position `offset` of `round` for a list
+ *   of `len` candidates (round 0 = warm-up in index order; measured rounds alternate direction). */
+int ta_tune_median(const uint64_t *samples, size_t n, uint64_t *out);
+size_t ta_tune_candidate_at(size_t len, uint32_t round, size_t offset);
+/* Tuned-winner store: path of the store for a device name under $XDG_CACHE_HOME (or ~/.cache), and
+ * load-then-save of a store file: reads `in_path` with the loader the executor uses (a stale
+ * header discards the file, malformed lines are skipped, `splitk2=S` needs 2 <= S <= 65535,
+ * `bf16` marks f16-storage B), reports the entries kept and, when out_path is not NULL, writes
+ * them back sorted by shape.  Host-only. */
+int ta_tune_store_path(const char *device_name, char *buf, size_t cap);
+int ta_tune_store_rewrite(const char *in_path, const char *out_path, size_t *n_entries);
+
+/* Experiment switches: the library reads ONE environment variable, TA_EXPERIMENT, a comma-separated
+ * list of name=value pairs (see INTEGRATION.md for the names), once per process.
+ * ta_experiment_check parses a string the same way and reports an unknown name (-1). Host-only. */
+int ta_experiment_check(const char *spec);
+
+/* Self-test of the bounded device-side waits: launches one warp that waits, with the helper and the
+ * status word every tensor-core kernel of the library uses, on a barrier nothing completes.  After
+ * limit_ns (1 .. 1e9) the wait gives up and the kernel returns normally; the call then fails (-1)
+ * with the library's "gave up on a bounded device-side wait" message and the executor and context
+ * remain usable.  No counterpart in the reference (its chain kernel spins without a limit,
+ * ref shaders/matmul_gemv_chain_kernel.glsl:93-132). */
+int ta_selftest_bounded_wait(const ta_executor *exec, uint32_t limit_ns);
 
 /* The kernel the heuristic stage of the routing order (explicit selection > tuned winner > heuristic,
  * ref src/pipeline/mod.rs:259-360) picks for a plain shape on a device of sm_count SMs: a name of the

@@ -28,6 +28,20 @@ def build(force: bool = False) -> str:
     return _SO
 
 
+REF_C_SMOKE = os.path.join(_HERE, "_ref", "c_smoke")
+
+
+def build_ref_c_smoke(reference_root: str = "/root/reference"):
+    """Compiles the reference's own C acceptance program (examples/c_smoke.c), unchanged and from
+    where it lies, against this repository's header and library.  Returns the binary's path, or
+    None when the reference tree is not present (the prebuilt binary, if any, is left alone)."""
+    src = os.path.join(reference_root, "examples", "c_smoke.c")
+    if not os.path.exists(src):
+        return REF_C_SMOKE if os.path.exists(REF_C_SMOKE) else None
+    subprocess.run(["make", "-C", _HERE, "ref_c_smoke", f"REF={reference_root}"], check=True, capture_output=True)
+    return REF_C_SMOKE
+
+
 _lib = None
 
 

@@ -41,6 +41,11 @@ from .api import (  # noqa: F401
     kernel_specs,
     pack_f16w_row_tiles,
     resolve_shapes,
+    experiment_check,
+    tune_candidate_at,
+    tune_median,
+    tune_store_path,
+    tune_store_rewrite,
     version,
 )
 from .capi import lib, lib_path  # noqa: F401

@@ -353,6 +353,14 @@ class Comm:
         dist.broadcast(t, src=0)
         return cls(ctx, rank, world, bytes(t.cpu().numpy().tobytes()))
 
+    def set_wait_limit_ns(self, limit_ns: int) -> None:
+        """How long a rank waits on the device for a peer's flag before the call fails."""
+        _check(lib().ta_comm_set_wait_limit_ns(self._h, limit_ns))
+
+    def resync(self) -> None:
+        """Collective: brings the peer exchange back to a common state after a failed wait."""
+        _check(lib().ta_comm_resync(self._h))
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             lib().ta_comm_destroy(self._h)
@@ -705,8 +713,13 @@ class Executor:
         return DispatchInfo(out.kernel.decode(), tuple(out.tile),
                             int(out.split_k2_splits) if out.has_split_k2 else None)
 
-    def tune_shape(self, batch: int, m: int, n: int, k: int) -> None:
-        _check(lib().ta_tune_shape(self._h, batch, m, n, k))
+    def tune_shape(self, batch: int, m: int, n: int, k: int, b_f16: bool = False) -> None:
+        fn = lib().ta_tune_shape_f16w if b_f16 else lib().ta_tune_shape
+        _check(fn(self._h, batch, m, n, k))
+
+    def selftest_bounded_wait(self, limit_ns: int) -> None:
+        """Launches the bounded-wait self-test kernel; always raises the bounded-wait error."""
+        _check(lib().ta_selftest_bounded_wait(self._h, limit_ns))
 
     # ---- model ops
     def softmax_rows(self, inp: Tensor, out: Tensor, scale: float = 1.0, mask_kind: int = 0,
@@ -815,6 +828,37 @@ def heuristic_splits(batch, m, n, k) -> Optional[int]:
 def heuristic_kernel(batch, m, n, k, weights_f16: bool = False, sm_count: int = 148) -> str:
     """Registry name the routing heuristic picks for a plain shape (no explicit selection, no tuned entry)."""
     return lib().ta_heuristic_kernel(batch, m, n, k, int(weights_f16), sm_count).decode()
+
+
+def tune_median(samples) -> Optional[int]:
+    """Median as the tuner takes it (src/executor/tuning.rs:319-331); None for no samples."""
+    arr = (C.c_uint64 * max(1, len(samples)))(*samples)
+    out = C.c_uint64()
+    rc = lib().ta_tune_median(arr, len(samples), C.byref(out))
+    if rc < 0:
+        raise TensorAshError(_err())
+    return None if rc == 1 else int(out.value)
+
+
+def tune_candidate_at(length: int, round_: int, offset: int) -> int:
+    return int(lib().ta_tune_candidate_at(length, round_, offset))
+
+
+def tune_store_path(device_name: str) -> str:
+    buf = C.create_string_buffer(4096)
+    _check(lib().ta_tune_store_path(device_name.encode(), buf, 4096))
+    return buf.value.decode()
+
+
+def tune_store_rewrite(in_path: str, out_path: Optional[str] = None) -> int:
+    """Loads a tuned-winner store as the executor does and (optionally) writes it back; returns the entries kept."""
+    n = C.c_size_t()
+    _check(lib().ta_tune_store_rewrite(in_path.encode(), out_path.encode() if out_path else None, C.byref(n)))
+    return int(n.value)
+
+
+def experiment_check(spec: str) -> None:
+    _check(lib().ta_experiment_check(spec.encode()))
 
 
 def kernel_specs():

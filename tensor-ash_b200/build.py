@@ -36,6 +36,7 @@ SOURCES = [
     "k_gemm_tf32x3_2cta.cu",
     "k_gemm_f16w.cu",
     "k_gemv.cu",
+    "k_gemv_umma.cu",
     "k_attention.cu",
     "k_ops.cu",
 ]

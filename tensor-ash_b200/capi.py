@@ -174,9 +174,18 @@ SIGNATURES = {
     "ta_context_device_index": (C.c_int, [_P]),
     "ta_context_device_name": (C.c_char_p, [_P]),
     "ta_kernel_launch_count": (C.c_uint64, []),
+    "ta_tune_shape_f16w": (C.c_int, [_P, _U32, _U32, _U32, _U32]),
+    "ta_tune_median": (C.c_int, [C.POINTER(C.c_uint64), _SZ, C.POINTER(C.c_uint64)]),
+    "ta_tune_candidate_at": (_SZ, [_SZ, _U32, _SZ]),
+    "ta_tune_store_path": (C.c_int, [C.c_char_p, C.c_char_p, _SZ]),
+    "ta_tune_store_rewrite": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(_SZ)]),
+    "ta_experiment_check": (C.c_int, [C.c_char_p]),
+    "ta_selftest_bounded_wait": (C.c_int, [_P, _U32]),
     "ta_comm_unique_id": (C.c_int, [_P]),
     "ta_comm_create": (_P, [_P, _U32, _U32, _P]),
     "ta_comm_destroy": (None, [_P]),
+    "ta_comm_set_wait_limit_ns": (C.c_int, [_P, C.c_uint64]),
+    "ta_comm_resync": (C.c_int, [_P]),
     "ta_comm_rank": (_U32, [_P]),
     "ta_comm_world": (_U32, [_P]),
     # ---- tensor_ash_llama.h

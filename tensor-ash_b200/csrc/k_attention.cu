@@ -18,7 +18,6 @@
 // device, so a captured graph serves every position.
 #include <cuda_fp16.h>
 
-#include "k_trace.cuh"
 #include "ta_core.hpp"
 
 namespace ta {
@@ -348,11 +347,8 @@ attn_decode_kernel(const AttnDecodeParams p) {
   const uint32_t row = tid / DEC_LANES, lane = tid % DEC_LANES;
   const bool live = row < p.group;
 
-  TA_TRACE_BEGIN_IF(blockIdx.y == 0)
-  TA_TRACE(0)
   // the position cell is host-written before the launch: read it ahead of the dependency wait
   const uint32_t kv_len = p.kv_len + (p.pos_ptr ? *p.pos_ptr : 0u);
-  TA_TRACE(1)
   // positions per chunk, a multiple of 8 so that f16 K rows start on 16 bytes
   const uint32_t chunk_size = (((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u;
   const uint32_t p0 = min(kv_len, chunk * chunk_size), p1 = min(p0 + chunk_size, kv_len);
@@ -386,7 +382,6 @@ attn_decode_kernel(const AttnDecodeParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
-  TA_TRACE(2)
   // q: group x 64 floats, one float4 per thread (requested before the late tile loads)
   float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool q_vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
@@ -479,7 +474,6 @@ attn_decode_kernel(const AttnDecodeParams p) {
     __syncthreads();
   }
 
-  TA_TRACE(3)
   const uint32_t stride = DEC_DH + 2;
   if (live) {
     float *dst = p.scratch + (((size_t)kv_head * p.num_chunks + chunk) * p.group + row) * stride;
@@ -498,8 +492,6 @@ attn_decode_kernel(const AttnDecodeParams p) {
     if (last_flag) p.counters[kv_head] = 0u;   // ready for the next launch on this stream
   }
   __syncthreads();
-  TA_TRACE(4)
-  if (last_flag) { TA_TRACE(6) }
   if (!last_flag || !live) return;
   __threadfence();
   const float *base = p.scratch + ((size_t)kv_head * p.num_chunks * p.group + row) * stride;
@@ -526,7 +518,6 @@ attn_decode_kernel(const AttnDecodeParams p) {
   const float inv = l_total > 0.0f ? 1.0f / l_total : 0.0f;
   float *o = p.out + ((size_t)kv_head * p.group + row) * DEC_DH + lane * 4;
   *reinterpret_cast<float4 *>(o) = make_float4(num[0] * inv, num[1] * inv, num[2] * inv, num[3] * inv);
-  TA_TRACE(5)
 }
 
 
@@ -536,8 +527,6 @@ inline void launched() {
 }
 
 }  // namespace
-
-TA_TRACE_EXPORT(ta_debug_attn_trace)
 
 // The tensor-core route: f16 caches, head dim 64, 16-byte-aligned rows, at least 32 query rows
 // (short prefills keep f32 operands), and not pinned to the f32 kernel by the caller.

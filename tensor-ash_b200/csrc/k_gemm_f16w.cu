@@ -28,7 +28,6 @@
 
 #include "k_epilogue.cuh"
 #include "k_umma.cuh"
-#include "k_trace.cuh"
 #include "ta_core.hpp"
 
 namespace ta {
@@ -311,20 +310,6 @@ convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint
   *reinterpret_cast<uint4 *>(out + r * kp + c) = o;
 }
 
-#ifdef TA_KERNEL_TRACE
-#define PRE_TRACE_DECL()                                                                          \
-  __shared__ unsigned int pre_trace_rec;                                                          \
-  if (threadIdx.x == 0) pre_trace_rec = blockIdx.x == 0 ? (atomicAdd(&g_trace_n, 1u) & 4095u) : 0xffffffffu;
-#define PRE_TRACE(i)                                                                              \
-  if (pre_trace_rec != 0xffffffffu) {                                                             \
-    unsigned long long t_;                                                                        \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                        \
-    g_trace[pre_trace_rec][i] = t_;                                                               \
-  }
-#else
-#define PRE_TRACE_DECL()
-#define PRE_TRACE(i)
-#endif
 
 template <int BN>
 __global__ void __launch_bounds__(PRE_THREADS, 1)
@@ -344,8 +329,6 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   volatile uint32_t *abort_flag = tmem_slot + 1;
   float *epi_buf = reinterpret_cast<float *>(smem_gen + C::STAGES * C::STAGE_BYTES + 256);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  PRE_TRACE_DECL();
-  if (threadIdx.x == 0) { PRE_TRACE(0); }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -365,7 +348,6 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) { PRE_TRACE(1); }
 
   const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const uint32_t tiles_per_batch = tiles_m * tiles_n;
@@ -393,9 +375,6 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
             for (int nb = 0; nb < BN / 64; ++nb)
               tma_load_3d(dst + C::A_BYTES + nb * (PK * 128), &map_b, full(stage), n0 + nb * 64, (int)(kb * PK), zb);
           }
-#ifndef PRE_TRACE_MMA
-          if (tile == blockIdx.x && kb + 1 == (uint32_t)C::STAGES) { PRE_TRACE(2); }
-#endif
         }
         __syncwarp();
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -412,23 +391,9 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * BN;
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-#ifdef PRE_TRACE_MMA
-        if (lane == 0 && tile == blockIdx.x && kb == 16) { PRE_TRACE(2); }
-        if (lane == 0 && tile == blockIdx.x && kb == 17) { PRE_TRACE(5); }
-#endif
         ok = mbar_wait(full(stage), phase, abort_flag);
         if (!ok) break;
         tc_fence_after();
-#ifdef PRE_TRACE_MMA
-        if (lane == 0 && tile == blockIdx.x && kb == 16) { PRE_TRACE(3); }
-        if (lane == 0 && tile == blockIdx.x && kb == 17) { PRE_TRACE(6); }
-#else
-        if (lane == 0 && tile == blockIdx.x) {
-          if (kb == 0) { PRE_TRACE(3); }
-          if (kb == 8) { PRE_TRACE(4); }
-          if (kb + 1 == k_blocks) { PRE_TRACE(5); }
-        }
-#endif
         // descriptors are built warp-uniformly; advancing K by 16 halves moves A by 32 bytes
         // (+2 in the 16-byte address field) and MN-major B by 16 rows of 128 bytes (+128)
         const uint32_t a16 = smem_base + stage * C::STAGE_BYTES;
@@ -440,10 +405,6 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
             mma_f16(d_tmem, da0 + (uint64_t)(j * 2), db0 + (uint64_t)(j * 128), idesc, (kb | (uint32_t)j) != 0u);
           tc_commit(empty(stage));
           if (kb + 1 == k_blocks) tc_commit(acc_full(buf));
-#ifdef PRE_TRACE_MMA
-          if (tile == blockIdx.x && kb == 16) { PRE_TRACE(4); }
-          if (tile == blockIdx.x && kb == 17) { PRE_TRACE(7); }
-#endif
         }
         __syncwarp();
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -460,9 +421,6 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
       if (!ok) break;
       tc_fence_after();
-#ifndef PRE_TRACE_MMA
-      if (threadIdx.x == 0 && tile == blockIdx.x) { PRE_TRACE(6); }
-#endif
       // TMEM gives each lane one row; a row-per-lane store would touch 32 rows per instruction.
       // Transpose 32 x 32 blocks through shared memory so that every global access of the
       // epilogue (C, D, the old C when accumulating) covers full 128-byte row segments.
@@ -529,9 +487,6 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       });
       tc_fence_before();
       mbar_arrive(acc_empty(buf));
-#ifndef PRE_TRACE_MMA
-      if (threadIdx.x == 0 && tile == blockIdx.x) { PRE_TRACE(7); }
-#endif
     }
   }
 
@@ -644,14 +599,8 @@ uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_co
   return best;
 }
 
-// Row pitch (in halves) of the f16 copy of A: K rounded up to 8, plus TA_F16W_APAD halves.
-static uint32_t a16_pitch(uint32_t k) {
-  static const uint32_t pad = [] {
-    const char *e = std::getenv("TA_F16W_APAD");
-    return e ? (uint32_t)std::strtoul(e, nullptr, 10) & ~7u : 0u;
-  }();
-  return ((k + 7u) & ~7u) + pad;
-}
+// Row pitch (in halves) of the f16 copy of A: K rounded up to 8, plus the experiment switch f16w_apad.
+static uint32_t a16_pitch(uint32_t k) { return ((k + 7u) & ~7u) + tunables().f16w_apad; }
 
 // Scratch bytes for the f16 copy of A.
 size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
@@ -678,9 +627,8 @@ void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t til
   if (!gemm_f16w_umma_eligible(p))
     fail("f16w tensor-core GEMM needs f32 A, f16 B, K %% 4 == 0 and N %% 8 == 0");
   const uint32_t batch_a = p.stride_a ? p.batch : 1;
-  const char *env = std::getenv("TA_F16W_PRE");
   if (scratch && scratch_bytes >= gemm_f16w_umma_scratch_bytes(batch_a, p.m, p.k) &&
-      (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0 && !(env && env[0] == '0')) {
+      (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0 && tunables().f16w_pre) {
     const uint32_t kp = a16_pitch(p.k);
     __half *a16 = static_cast<__half *>(scratch);
     if (tile_n >= 256) launch_pre_t<256>(ctx, p, a16, kp, status, a16_ready, stream);
@@ -694,5 +642,3 @@ void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t til
 }
 
 }  // namespace ta
-
-TA_TRACE_EXPORT(ta_debug_f16w_trace)

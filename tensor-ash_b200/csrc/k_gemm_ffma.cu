@@ -599,6 +599,66 @@ void launch_splitk2_reduce(const float *scratch, float *c, uint64_t total, uint6
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
+// Reduce for many planes over few outputs (the tensor-core stage 1 writes about one plane per SM):
+// a block of 256 threads owns 32 float4 outputs; thread (g, e) adds the planes of group g
+// (planes [g P/8, (g+1) P/8), in plane order, eight loads in flight) for output e, then thread
+// (0, e) adds the eight group sums in group order.  The order depends on the plane count only, so
+// two runs are bit-identical.  Launched with programmatic stream serialization: the grid may be
+// resident while stage 1 still runs and waits for it here.
+constexpr int RW_GROUPS = 8, RW_COLS = 32;
+
+__global__ void __launch_bounds__(RW_GROUPS * RW_COLS)
+splitk2_reduce_wide_kernel(const float *__restrict__ scratch, float *__restrict__ c, uint64_t total, uint64_t mn,
+                           uint32_t planes) {
+  __shared__ float4 part[RW_GROUPS][RW_COLS];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int e = threadIdx.x % RW_COLS, g = threadIdx.x / RW_COLS;
+  const uint64_t base = ((uint64_t)blockIdx.x * RW_COLS + e) * 4;   // mn % 4 == 0: a float4 never straddles a batch
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (base < total) {
+    const uint64_t b = base / mn, off = base % mn;
+    const uint32_t per = (planes + RW_GROUPS - 1) / RW_GROUPS;
+    const uint32_t p0 = min(planes, (uint32_t)g * per), p1 = min(planes, p0 + per);
+    const float *src = scratch + b * planes * mn + off;
+    uint32_t s = p0;
+    for (; s + 8 <= p1; s += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)(s + u) * mn));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+    }
+    for (; s < p1; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)s * mn));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+  }
+  part[g][e] = acc;
+  __syncthreads();
+  if (g == 0 && base < total) {
+    float4 r = part[0][e];
+#pragma unroll
+    for (int q = 1; q < RW_GROUPS; ++q) { r.x += part[q][e].x; r.y += part[q][e].y; r.z += part[q][e].z; r.w += part[q][e].w; }
+    *reinterpret_cast<float4 *>(c + base) = r;
+  }
+}
+
+void launch_splitk2_reduce_wide(const float *scratch, float *c, uint64_t total, uint64_t mn, uint32_t planes,
+                                cudaStream_t stream) {
+  if (mn % 4) fail("internal: wide split-K reduce needs M*N to be a multiple of 4");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((total / 4 + RW_COLS - 1) / RW_COLS), 1, 1);
+  cfg.blockDim = dim3(RW_GROUPS * RW_COLS, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, splitk2_reduce_wide_kernel, scratch, c, total, mn, planes));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
 // ---------------------------------------------------------------------------
 // Split-K2 without any allocation: the partial planes live in a fixed array
 // that is part of the loaded module (4 MiB per GPU that loads the library, held

@@ -32,9 +32,18 @@
 // buffer; a tile's epilogue runs on the running sums.  Draining tensor memory takes bandwidth
 // from the MMAs writing it (measured on 32 x 2048^3: 197 TFLOP/s with one drain per tile, 190
 // with chunks of 1024, 172 with chunks of 512), so the default chunk is 1024 (at most ~1e-5
-// relative at any K); TA_TF32X3_CHUNK_KB=32 selects chunks of 512 (4.2e-6 at any K).
+// relative at any K); the experiment switch tf32x3_chunk_kb=32 selects chunks of 512 (4.2e-6 at any K).
 // Every mbarrier wait is bounded (about two seconds); on a timeout the CTA
 // raises a flag, all roles leave their loops, and the host reports an error.
+//
+// SPLITK = true turns the same pipeline into stage 1 of the two-stage split-K route
+// (src/executor/reduction.rs:21-70; shaders/matmul_splitk2_kernel.glsl:121-216 is the SIMT form):
+// a work unit is (batch, output tile, K sub-range), the sub-range's product is accumulated in one
+// tensor-memory buffer (at most 64 K blocks = 1024 k, so the truncating accumulator stays inside
+// the chunk bound above) and alpha * partial is plain-stored to the unit's scratch plane; a
+// separate kernel adds the planes in a fixed order.  The caller's split s covers K blocks
+// [s KB/S, (s+1) KB/S) as the reference's partition does; each split is cut further into
+// `c` equal sub-ranges so that units fill the machine whatever the requested split count.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -70,11 +79,11 @@ struct Cfg {
   static constexpr int B_BYTES = BK * BN * 4;             // 16 KiB at BN = 256
   static constexpr int HALF_BYTES = A_BYTES + B_BYTES;    // hi (raw) region, then lo region
   static constexpr int STAGE_BYTES = 2 * HALF_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
   static constexpr int TMEM_COLS = 512;                   // two accumulator buffers at BN = 256
-  static constexpr int ACC_STRIDE = (BN == 256) ? 256 : 128;
+  static constexpr int ACC_STRIDE = (BN == 256) ? 256 : (BN == 128 ? 128 : 64);
 };
 
 using namespace umma;
@@ -90,11 +99,16 @@ __device__ __forceinline__ uint32_t split_lo(float x) {
 }
 
 // ---------------------------------------------------------------- kernel
-template <int BN>
+template <int BN, bool SPLITK>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
                    const __grid_constant__ CUtensorMap map_b, uint32_t *__restrict__ status) {
   using C = Cfg<BN>;
+  if constexpr (SPLITK) {
+    // the reduce kernel behind this one in the stream may be scheduled now; it waits for this
+    // grid to finish before it reads a plane
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -133,8 +147,29 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
 
   const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const uint32_t tiles_per_batch = tiles_m * tiles_n;
-  const uint32_t num_tiles = tiles_per_batch * p.batch;
-  const uint32_t k_blocks = (p.k + BK - 1) / BK;
+  const uint32_t k_blocks_all = (p.k + BK - 1) / BK;
+  // split-K stage 1: a unit is (batch, tile, K sub-range); the sub-range index runs fastest
+  const uint32_t subs = SPLITK ? p.sk_subs : 1u;
+  const uint32_t num_tiles = tiles_per_batch * p.batch * subs;
+  // unit -> batch, tile within the batch, K blocks [kb_lo, kb_hi)
+  auto decode = [&](uint32_t unit, uint32_t &batch, uint32_t &rem, uint32_t &sub, uint32_t &kb_lo, uint32_t &kb_hi) {
+    if constexpr (SPLITK) {
+      sub = unit % subs;
+      const uint32_t t = unit / subs;
+      batch = t / tiles_per_batch;
+      rem = t % tiles_per_batch;
+      // sub-ranges never straddle a caller-visible split: split = sub / c, piece = sub % c
+      const uint32_t split = sub / p.sk_c, piece = sub % p.sk_c;
+      kb_lo = split * p.sk_kb_per_split + piece * p.sk_kb_per_sub;
+      kb_hi = min((split + 1u) * p.sk_kb_per_split, kb_lo + p.sk_kb_per_sub);
+    } else {
+      sub = 0;
+      batch = unit / tiles_per_batch;
+      rem = unit % tiles_per_batch;
+      kb_lo = 0;
+      kb_hi = k_blocks_all;
+    }
+  };
 
   // Register budget by warpgroup (setmaxnreg is a warpgroup-wide instruction, so the split is on
   // warp / 4 first): the epilogue warpgroups keep a whole tile's running sums in registers,
@@ -147,10 +182,11 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      uint32_t batch, rem, sub, kb_lo, kb_hi;
+      decode(tile, batch, rem, sub, kb_lo, kb_hi);
       const int m0 = (int)(rem / tiles_n) * BM, n0 = (int)(rem % tiles_n) * BN;
       const int za = p.stride_a ? (int)batch : 0, zb = p.stride_b ? (int)batch : 0;
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+      for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
         if (!ok) break;
         const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
@@ -177,9 +213,11 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
     uint32_t stage = 0, phase = 0, acc_it = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      for (uint32_t kb0 = 0; ok && kb0 < k_blocks; kb0 += p.chunk_kb, ++acc_it) {
+      uint32_t batch, rem, sub, kb_lo, kb_hi;
+      decode(tile, batch, rem, sub, kb_lo, kb_hi);
+      for (uint32_t kb0 = kb_lo; ok && kb0 < kb_hi; kb0 += p.chunk_kb, ++acc_it) {
         // one K chunk per tensor-memory buffer: the epilogue warps drain chunk c while chunk c+1 runs
-        const uint32_t kb1 = min(k_blocks, kb0 + p.chunk_kb);
+        const uint32_t kb1 = min(kb_hi, kb0 + p.chunk_kb);
         const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
         ok = mbar_wait(acc_empty(buf), acc_phase ^ 1u, abort_flag);
         if (!ok) break;
@@ -222,7 +260,9 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
     uint32_t stage = 0, phase = 0, it_all = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it_all) {
+      uint32_t batch, rem, sub, kb_lo, kb_hi;
+      decode(tile, batch, rem, sub, kb_lo, kb_hi);
+      for (uint32_t kb = kb_lo; kb < kb_hi; ++kb, ++it_all) {
         if ((int)(it_all % CVT_GROUPS) == group) {
           ok = mbar_wait(full_raw(stage), phase, abort_flag);
           if (!ok) break;
@@ -254,12 +294,13 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
     bool ok = true;
     const bool alpha_is_one = p.alpha == 1.0f;
     for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-      const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
+      uint32_t batch, rem, sub, kb_lo, kb_hi;
+      decode(tile, batch, rem, sub, kb_lo, kb_hi);
       const uint32_t m0 = (rem / tiles_n) * BM, n0 = (rem % tiles_n) * BN + col_half * HALF_N;
       float sum[HALF_N];
 #pragma unroll
       for (int i = 0; i < HALF_N; ++i) sum[i] = 0.0f;
-      for (uint32_t kb0 = 0; ok && kb0 < k_blocks; kb0 += p.chunk_kb, ++acc_it) {
+      for (uint32_t kb0 = kb_lo; ok && kb0 < kb_hi; kb0 += p.chunk_kb, ++acc_it) {
         const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
         ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
         if (!ok) break;
@@ -278,6 +319,22 @@ gemm_tf32x3_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a
       if (!ok) break;
       const uint32_t row = m0 + lane_grp * 32 + lane;
       const bool row_ok = row < p.m;
+      if constexpr (SPLITK) {
+        // alpha * partial to this unit's plane (plane = batch * subs + sub), nothing else
+        float *__restrict__ prow = p.sk_planes + ((size_t)batch * subs + sub) * ((size_t)p.m * p.n) + (size_t)row * p.n;
+        if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < HALF_N; q += 4) {
+            const uint32_t col = n0 + q;
+            if (col < p.n) {
+              float4 o = make_float4(sum[q], sum[q + 1], sum[q + 2], sum[q + 3]);
+              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+              *reinterpret_cast<float4 *>(prow + col) = o;
+            }
+          }
+        }
+        continue;
+      }
       const size_t row_off = (size_t)batch * p.stride_c + (size_t)row * p.n;
       float *__restrict__ crow = p.c + row_off;
       const float *__restrict__ drow = p.d ? p.d + row_off : nullptr;
@@ -343,18 +400,15 @@ void encode_map(const Context &ctx, CUtensorMap *map, const void *base, uint64_t
   if (rc != CUDA_SUCCESS) fail("cuTensorMapEncodeTiled failed with CUresult %d", (int)rc);
 }
 
-template <int BN>
+template <int BN, bool SPLITK>
 void launch_t(const Context &ctx, const GemmParams &p_in, uint32_t *status, cudaStream_t stream) {
   using C = Cfg<BN>;
   GemmParams p = p_in;
   p.chunk_kb = CHUNK_KB;
-  if (const char *e = std::getenv("TA_TF32X3_CHUNK_KB")) {   // experiments: K blocks per accumulation
-    const int v = atoi(e);
-    if (v > 0) p.chunk_kb = (uint32_t)v;
-  }
+  if (tunables().tf32x3_chunk_kb) p.chunk_kb = tunables().tf32x3_chunk_kb;
   static bool attr_set[64] = {};
   if (!attr_set[ctx.device & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TA_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  C::SMEM_BYTES));
     attr_set[ctx.device & 63] = true;
   }
@@ -373,9 +427,9 @@ void launch_t(const Context &ctx, const GemmParams &p_in, uint32_t *status, cuda
   else
     encode_map(ctx, &map_b, p.b, p.n, p.k, bb, (uint64_t)p.n * 4, b_batch_bytes, 32, BK,
                CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
+  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch * (SPLITK ? p.sk_subs : 1u);
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
-  gemm_tf32x3_kernel<BN><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);
+  gemm_tf32x3_kernel<BN, SPLITK><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p, map_a, map_b, status);
   TA_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
@@ -399,8 +453,52 @@ bool gemm_tf32x3_eligible(const GemmParams &p) {
 void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
                         cudaStream_t stream) {
   if (!gemm_tf32x3_eligible(p)) fail("tf32x3 GEMM needs f32 operands with K and N multiples of 4");
-  if (tile_n >= 256) launch_t<256>(ctx, p, status, stream);
-  else launch_t<128>(ctx, p, status, stream);
+  if (tile_n >= 256) launch_t<256, false>(ctx, p, status, stream);
+  else launch_t<128, false>(ctx, p, status, stream);
+}
+
+// ---------------------------------------------------------------- split-K2 stage 1 on the tensor cores
+// Eligible when the reference's partition (src/executor/splitk2.rs, shaders/matmul_splitk2_kernel.glsl:138-142:
+// K / S per split, the first K % S splits one longer) lands on K-block boundaries: K a multiple
+// of 16 * S.  Each split is then cut into c equal pieces of at most 64 K blocks so that
+// tiles * S * c work units fill the SMs whatever S the caller asked for; piece j of split s is
+// plane s * c + j, and the reduce adds planes in that order.
+SplitK2TensorPlan splitk2_tensor_plan(const GemmParams &p, uint32_t splits, int sm_count) {
+  SplitK2TensorPlan plan;
+  if (!tunables().splitk2_tensor || splits < 2 || p.b_f16 || !gemm_tf32x3_eligible(p)) return plan;
+  if (p.k % (BK * splits) != 0 || p.m < 16 || p.n < 16) return plan;
+  const uint32_t kb_per_split = p.k / BK / splits;
+  const uint32_t bn = p.n <= 64 ? 64u : (p.n <= 128 || p.n % 256 != 0) ? 128u : 256u;
+  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + bn - 1) / bn) * p.batch;
+  uint64_t c = std::max<uint64_t>(1, (uint64_t)sm_count / (tiles * splits));
+  c = std::min<uint64_t>(c, kb_per_split);
+  c = std::max<uint64_t>(c, (kb_per_split + CHUNK_KB - 1) / CHUNK_KB);   // one accumulation holds at most 1024 k
+  const uint32_t kb_per_sub = (uint32_t)((kb_per_split + c - 1) / c);
+  c = (kb_per_split + kb_per_sub - 1) / kb_per_sub;                      // no empty piece
+  if ((uint64_t)splits * c > 65535) return plan;
+  plan.eligible = true;
+  plan.tile_n = bn;
+  plan.c = (uint32_t)c;
+  plan.kb_per_split = kb_per_split;
+  plan.kb_per_sub = kb_per_sub;
+  plan.planes = splits * (uint32_t)c;
+  return plan;
+}
+
+void launch_splitk2_tensor(const Context &ctx, const GemmParams &p_in, const SplitK2TensorPlan &plan, float *scratch,
+                           uint32_t *status, cudaStream_t stream) {
+  if (!plan.eligible) fail("internal: tensor-core split-K stage 1 launched on an ineligible problem");
+  GemmParams p = p_in;
+  p.sk_subs = plan.planes;
+  p.sk_c = plan.c;
+  p.sk_kb_per_split = plan.kb_per_split;
+  p.sk_kb_per_sub = plan.kb_per_sub;
+  p.sk_planes = scratch;
+  p.bias = nullptr; p.d = nullptr; p.accumulate = 0; p.act = 0; p.binary = 0;
+  if (plan.tile_n >= 256) launch_t<256, true>(ctx, p, status, stream);
+  else if (plan.tile_n >= 128) launch_t<128, true>(ctx, p, status, stream);
+  else launch_t<64, true>(ctx, p, status, stream);
+  launch_splitk2_reduce_wide(scratch, p.c, (uint64_t)p.batch * p.m * p.n, (uint64_t)p.m * p.n, plan.planes, stream);
 }
 
 }  // namespace ta

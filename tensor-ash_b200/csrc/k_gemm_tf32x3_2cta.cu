@@ -362,10 +362,7 @@ bool gemm_tf32x3_pair_supported(const GemmParams &p, int sm_count) {
 void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p_in, uint32_t *status, cudaStream_t stream) {
   GemmParams p = p_in;
   p.chunk_kb = CHUNK_KB;
-  if (const char *e = std::getenv("TA_TF32X3_CHUNK_KB")) {   // experiments: K blocks per accumulation
-    const int v = atoi(e);
-    if (v > 0) p.chunk_kb = (uint32_t)v;
-  }
+  if (tunables().tf32x3_chunk_kb) p.chunk_kb = tunables().tf32x3_chunk_kb;
   if (!gemm_tf32x3_pair_supported(p, ctx.sm_count))
     fail("paired tf32x3 GEMM needs f32 operands with K and N multiples of 4");
   static bool attr_set[64] = {};

@@ -44,7 +44,6 @@
 #include <type_traits>
 
 #include "k_epilogue.cuh"
-#include "k_trace.cuh"
 #include "k_umma.cuh"
 #include "ta_core.hpp"
 
@@ -72,22 +71,13 @@ constexpr int RING_STAGE_BYTES = 16384;
 // counts), four passes ahead and starting before the dependency wait; the warps read their
 // 16-byte pieces from the ring instead of from global memory.  In-flight bytes per SM then
 // depend on shared memory (64 KiB per CTA), not on registers.
-// MMA (3 to 8 activation rows): the dot products run on the tensor cores instead of the FMA
-// pipe, which at M = 8 has no headroom left beside a full-rate weight stream.
-// mma.sync m16n8k16 f16 with x as the A operand (rows = activation rows, padded to 16), split
-// into hi + lo f16 parts (two MMAs, ~22 bits of x; |x| must stay below the f16 range, 65504), and
-// the f16 weights as the B operand exactly as stored -- no conversion at all, one byte-permute
-// per register to pair two k rows.  Lane (g, t) = (lane / 4, lane % 4) loads the TN/8 consecutive
-// columns TN/8*g.. of rows k0 + {2t, 2t+1, 2t+8, 2t+9}: element q of those four vectors is the B
-// fragment (k = 2t, 2t+1 | 2t+8, 2t+9; n = g) of the q-th of TN/8 MMAs, whose column j stands for
-// n = TN/8 * j + q.
-template <int MROWS, int TN, bool BULK, bool MMA>
+// Three to eight rows over shapes the tensor-memory kernel (k_gemv_umma.cu) takes go there instead.
+template <int MROWS, int TN, bool BULK>
 __global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (BULK ? 3 : 4) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
-  static_assert(!MMA || (MROWS == 8 && !BULK), "the tensor-core variant handles up to 8 rows, register path");
-  constexpr int U = MMA ? 2 : GemvCfg<MROWS>::U;  // MMA: blocks of 16 k rows, four vectors per lane and block (four blocks per pass measured slower)
+  constexpr int U = GemvCfg<MROWS>::U;
   constexpr int LPR = TN / 8;                    // lanes per weight row (8 f16 per lane)
-  constexpr int RPL = MMA ? 16 : 32 / LPR;       // weight rows per warp-wide load
+  constexpr int RPL = 32 / LPR;                  // weight rows per warp-wide load
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const uint32_t S = g.ksplit;
@@ -112,7 +102,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   // BULK prepends: ring[RING_STAGES][16 KiB] | full barriers | abort flag (128 bytes reserved)
   constexpr size_t RING_BYTES = BULK ? (size_t)RING_STAGES * RING_STAGE_BYTES + 128 : 0;
   float *xs = reinterpret_cast<float *>(gemv_smem + RING_BYTES);
-  float *wpart = xs + (size_t)(g.k_cta + 8) * MROWS;   // +8: row pitch of the MMA variant's xs[m][k]
+  float *wpart = xs + (size_t)(g.k_cta + 8) * MROWS;
   float *cpart = wpart + GEMV_WARPS * MROWS * TN;
   float *red = cpart + (size_t)S * 2 * MROWS * TN;
   float *scale = red + GEMV_WARPS * MROWS;
@@ -170,33 +160,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   };
 
-  // ---- MMA variant: NQ columns per lane and k row, four k rows per lane and block of 16
-  constexpr int NQ = TN / 8;
-  using WVec = typename std::conditional<NQ == 4, uint2, uint4>::type;
-  const int gq = lane >> 2, tq = lane & 3;
-  const bool mcol_ok = col0 + NQ * gq < p.n;
-  size_t mbase, mstride;   // in halfs
-  if (p.packed) {
-    mbase = ((size_t)tile * p.k) * TN + NQ * gq;
-    mstride = TN;
-  } else {
-    mbase = (size_t)col0 + NQ * gq;
-    mstride = p.n;
-  }
-  auto load_blocks = [&](WVec (&wv)[U][4], uint32_t pass) {
-    const uint32_t k0 = k_lo + pass * rows_per_pass + (uint32_t)wi * 16;
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const uint32_t k = k0 + u * nw * 16 + 2 * tq + (h & 1) + 8 * (h >> 1);
-        wv[u][h] = WVec{};
-        if (k < k_hi && mcol_ok) wv[u][h] = __ldcs(reinterpret_cast<const WVec *>(W + mbase + (size_t)k * mstride));
-      }
-  };
-  WVec ma[U][4], mb[U][4];
-  TA_TRACE_BEGIN()
-  TA_TRACE(0)
   uint4 wa[U], wb[U];
   if constexpr (BULK) {
     if (threadIdx.x == 0) {
@@ -206,14 +169,10 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       for (uint32_t ps = 0; ps < passes && ps < (uint32_t)RING_STAGES; ++ps) issue_pass(ps);
     }
-  } else if constexpr (!MMA) {
+  } else {
     if (passes > 0) load_pass(wa, 0);
     if (passes > 1) load_pass(wb, 1);
-  } else {
-    if (passes > 0) load_blocks(ma, 0);
-    if (passes > 1) load_blocks(mb, 1);
   }
-  TA_TRACE(1)
   // the position cell is written by the host before the launch, never by a kernel:
   // fetch it now (it may live in host memory) so its latency hides behind the weights
   uint32_t pos = p.pos_base;
@@ -239,7 +198,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
-  TA_TRACE(2)
 
   // ---- activations: one L2 round trip.  The first slice elements of every thread
   // and (rank 0) the whole rows for the RMSNorm sum of squares are requested back
@@ -282,41 +240,12 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   }
   // ---- stage this CTA's slice of x (times the norm weight) as xs[k][m]
-  if constexpr (!MMA) {
 #pragma unroll
-    for (int it = 0; it < XS_PRE; ++it) {
-      const uint32_t idx = threadIdx.x + it * GEMV_THREADS;
-      if (idx < stage_n) xs[idx] = xv[it] * nwv[it];
-    }
+  for (int it = 0; it < XS_PRE; ++it) {
+    const uint32_t idx = threadIdx.x + it * GEMV_THREADS;
+    if (idx < stage_n) xs[idx] = xv[it] * nwv[it];
   }
-  if constexpr (MMA) {
-    // tensor-core variant: xs[m][k] with a row pitch of k_cta + 8 floats (the eight rows a half
-    // warp reads as float2 land on distinct banks), filled with 16-byte loads along k
-    const uint32_t pitch = g.k_cta + 8, quads = (k_len + 3) / 4;
-    const bool vec = (p.k & 3u) == 0 && (k_lo & 3u) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 &&
-                     (!p.norm_w || (reinterpret_cast<uintptr_t>(p.norm_w) & 15u) == 0);
-    for (uint32_t idx = threadIdx.x; idx < (uint32_t)MROWS * quads; idx += GEMV_THREADS) {
-      const uint32_t m = idx / quads, kq = (idx % quads) * 4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (m < p.m) {
-        const float *src = p.x + (size_t)m * p.k + k_lo + kq;
-        if (vec && kq + 4 <= k_len) {
-          v = *reinterpret_cast<const float4 *>(src);
-          if (p.norm_w) {
-            const float4 w = *reinterpret_cast<const float4 *>(p.norm_w + k_lo + kq);
-            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
-          }
-        } else {
-          float t[4] = {0.f, 0.f, 0.f, 0.f};
-          for (uint32_t j = 0; j < 4 && kq + j < k_len; ++j) t[j] = src[j] * (p.norm_w ? p.norm_w[k_lo + kq + j] : 1.0f);
-          v = make_float4(t[0], t[1], t[2], t[3]);
-        }
-      }
-      *reinterpret_cast<float4 *>(xs + (size_t)m * pitch + kq) = v;
-      // the hi / lo split is in f16: a larger activation cannot be represented -- say so, loudly
-      if (fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))) > 65504.0f && g.status) atomicOr(g.status, 2u);
-    }
-  } else if constexpr (MROWS >= 4) {
+  if constexpr (MROWS >= 4) {
     // many rows: walk k within a row so that global reads are contiguous (the first
     // XS_PRE * 256 / MROWS k of every row are staged above)
     const uint32_t kk_done = (XS_PRE * GEMV_THREADS) / MROWS;
@@ -341,7 +270,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     }
   }
   __syncthreads();
-  TA_TRACE(3)
   if (p.norm_w && rank == 0 && threadIdx.x < MROWS) {
     float s = 0.0f;
 #pragma unroll
@@ -349,71 +277,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     scale[threadIdx.x] = rsqrtf(s / (float)p.k + p.norm_eps);   // read after the reduction barriers below
   }
 
-  if constexpr (MMA) {
-    // ---- tensor-core stream (addresses, block loads and the first two passes: see the prologue)
-    float dacc[NQ][4];
-#pragma unroll
-    for (int q = 0; q < NQ; ++q)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) dacc[q][i] = 0.0f;
-    // x pair (k, k + 1) of activation row g as half2 hi and half2 lo = x - hi
-    auto x_pair = [&](uint32_t kk, uint32_t &hi, uint32_t &lo) {
-      // k_len is padded with zeros up to a multiple of 4 by the staging loop; kk is even
-      float x0 = 0.0f, x1 = 0.0f;
-      if (kk < ((k_len + 3u) & ~3u)) {
-        const float2 xx = *reinterpret_cast<const float2 *>(xs + (size_t)gq * (g.k_cta + 8) + kk);
-        x0 = xx.x; x1 = xx.y;
-      }
-      const __half2 h = __floats2half2_rn(x0, x1);
-      const float2 hf = __half22float2(h);
-      const __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
-      hi = *reinterpret_cast<const uint32_t *>(&h);
-      lo = *reinterpret_cast<const uint32_t *>(&l);
-    };
-    auto mma_blocks = [&](const WVec (&wv)[U][4], uint32_t pass) {
-      const uint32_t kk0 = pass * rows_per_pass + (uint32_t)wi * 16;
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const uint32_t kk = kk0 + u * nw * 16 + 2 * tq;
-        uint32_t a0h, a0l, a2h, a2l;
-        x_pair(kk, a0h, a0l);
-        x_pair(kk + 8, a2h, a2l);
-        const uint32_t *r0 = reinterpret_cast<const uint32_t *>(&wv[u][0]);
-        const uint32_t *r1 = reinterpret_cast<const uint32_t *>(&wv[u][1]);
-        const uint32_t *r2 = reinterpret_cast<const uint32_t *>(&wv[u][2]);
-        const uint32_t *r3 = reinterpret_cast<const uint32_t *>(&wv[u][3]);
-#pragma unroll
-        for (int q = 0; q < NQ; ++q) {
-          const uint32_t sel = (q & 1) ? 0x7632u : 0x5410u;   // the q-th half of two rows -> one register
-          const uint32_t b0 = __byte_perm(r0[q >> 1], r1[q >> 1], sel), b1 = __byte_perm(r2[q >> 1], r3[q >> 1], sel);
-          asm volatile(
-              "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-              : "+f"(dacc[q][0]), "+f"(dacc[q][1]), "+f"(dacc[q][2]), "+f"(dacc[q][3])
-              : "r"(a0h), "r"(0u), "r"(a2h), "r"(0u), "r"(b0), "r"(b1));
-          asm volatile(
-              "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-              : "+f"(dacc[q][0]), "+f"(dacc[q][1]), "+f"(dacc[q][2]), "+f"(dacc[q][3])
-              : "r"(a0l), "r"(0u), "r"(a2l), "r"(0u), "r"(b0), "r"(b1));
-        }
-      }
-    };
-    for (uint32_t pass = 0; pass < passes; pass += 2) {
-      mma_blocks(ma, pass);
-      if (pass + 2 < passes) load_blocks(ma, pass + 2);
-      if (pass + 1 < passes) {
-        mma_blocks(mb, pass + 1);
-        if (pass + 3 < passes) load_blocks(mb, pass + 3);
-      }
-    }
-    TA_TRACE(4)
-    // lane (g, t) holds row g, columns [2 NQ t, 2 NQ (t + 1)): d0 -> column NQ*2t + q, d1 -> NQ*(2t+1) + q
-    float *dst = wpart + ((size_t)warp * MROWS + gq) * TN + 2 * NQ * tq;
-#pragma unroll
-    for (int q = 0; q < NQ; ++q) {
-      dst[q] = dacc[q][0];
-      dst[NQ + q] = dacc[q][1];
-    }
-  } else {
+  {
     // ---- stream the weights: pass i multiplies while pass i+1 is in flight
     float2 acc[MROWS][4];
   #pragma unroll
@@ -467,7 +331,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
           if (threadIdx.x == 0 && ring_ok) issue_pass(pass + RING_STAGES);
         }
       }
-      if (!ring_ok && threadIdx.x == 0 && g.status) atomicOr(g.status, 2u);   // the host call fails
+      if (!ring_ok && threadIdx.x == 0 && g.status) atomicOr(g.status, 1u);   // bounded wait ran out: the host call fails
     } else {
       for (uint32_t pass = 0; pass < passes; pass += 2) {
         mul_pass(wa, pass);
@@ -479,7 +343,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       }
     }
 
-    TA_TRACE(4)
     // ---- fixed-order reduction: lanes sharing a column group, then warps, then cluster ranks
   #pragma unroll
     for (int m = 0; m < MROWS; ++m)
@@ -509,7 +372,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     for (int w = 0; w < nw; ++w) s += wpart[((size_t)(mt * nw + w)) * MROWS * TN + rem];
     cdst[(size_t)rank * 2 * MROWS * TN + idx] = s;
   }
-  TA_TRACE(5)
   if (S > 1) {
     cluster.barrier_arrive();          // release: the pushed partials are visible to rank 0 after its wait
     if (rank != 0) return;
@@ -517,7 +379,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   } else {
     __syncthreads();
   }
-  TA_TRACE(6)
 
   // ---- rank 0: sum ranks in order, epilogue, store
   float *fin = wpart;   // reuse: final pre-store values [MROWS][TN]
@@ -573,7 +434,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       }
     }
   }
-  TA_TRACE(7)
 }
 
 size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s, bool bulk = false) {
@@ -582,22 +442,16 @@ size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s, bool bulk 
          (bulk ? (size_t)RING_STAGES * RING_STAGE_BYTES + 128 : 0);
 }
 
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char *e = std::getenv("TA_NO_PDL");
-    return !(e && e[0] == '1');
-  }();
-  return on;
-}
+bool pdl_enabled() { return tunables().pdl; }
 
-template <int MROWS, int TN, bool BULK, bool MMA = false>
+template <int MROWS, int TN, bool BULK>
 void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   const size_t smem = gemv_smem_bytes(g.k_cta, MROWS, TN, g.ksplit, BULK);
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  200 * 1024));
     attr_done[dev & 63] = true;
   }
@@ -620,7 +474,7 @@ void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK, MMA>, g));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK>, g));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -648,9 +502,25 @@ static bool bulk_possible(const GemvParams *segs, int nseg) {
   return true;
 }
 
-void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, uint32_t *status,
+// Rows from which a lone GEMV (or SwiGLU pair) goes to the tensor-memory kernel when its shape
+// and the slot's workspace allow: 3 by default; the experiment switch gemv_umma forces it on for
+// every row count (1) or off (0).
+bool gemv_routes_to_umma(const GemvParams &p) {
+  const int force = tunables().gemv_umma;
+  if (force == 0) return false;
+  return (force == 1 || p.m >= 3) && gemv_umma_eligible(p);
+}
+
+void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg, bool pdl, const GemvWorkspace &ws,
                             cudaStream_t stream) {
   if (nseg < 1 || nseg > GEMV_MAX_SEGS) fail("GEMV group of %d segments (1..%d)", nseg, GEMV_MAX_SEGS);
+  const int sm_count = ctx.sm_count;
+  uint32_t *status = ws.status;
+  if (nseg == 1 && gemv_routes_to_umma(segs[0]) && ws.scratch && ws.counters &&
+      ws.scratch_bytes >= gemv_umma_scratch_bytes(segs[0].n, segs[0].k, segs[0].w2 != nullptr, sm_count)) {
+    launch_gemv_umma(ctx, segs[0], static_cast<float *>(ws.scratch), ws.scratch_bytes, ws.counters, status, pdl, stream);
+    return;
+  }
   GemvGroup g{};
   const GemvParams &p0 = segs[0];
   const uint32_t tn = p0.packed ? p0.tile_n : 32;
@@ -664,15 +534,9 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   g.nseg = (uint32_t)nseg;
   g.pdl = (pdl && pdl_enabled()) ? 1u : 0u;
   g.status = status;
-  // five rows and more: tensor-core variant (8-row kernel).  Measured on 4096 x 11008: at M = 8 it
-  // is ahead of the FMA path (119 vs 214 us per MLP pass), at M = 4 behind it (109 vs 99 us).
-  uint32_t mma_min = 5;
-  if (const char *e = std::getenv("TA_GEMV_MMA_MIN")) mma_min = (uint32_t)std::max(1, atoi(e));   // experiments
-  bool mma = p0.m >= mma_min;
-  if (const char *e = std::getenv("TA_GEMV_MMA")) mma = mma && e[0] != '0';
-  const int mrows = mma ? 8 : (p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8);
-  const uint32_t u = mma ? 2 : 4;
-  const uint32_t rpl = mma ? 16 : 32 / (tn / 8);
+  const int mrows = p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8;
+  const uint32_t u = 4;
+  const uint32_t rpl = 32 / (tn / 8);
   const uint32_t nw = p0.w2 ? GEMV_WARPS / 2 : GEMV_WARPS;
   const uint32_t rows_per_pass = nw * rpl * u;
   // K split over a cluster: about one and a half CTAs per SM.  With four resident
@@ -686,7 +550,7 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
   // measured: the ring wins on long streams (4096 x 11008: 3.8 -> 4.8 TB/s) and is neutral to
   // slightly slower on the few-MB matrices of a decode step, which are latency-bound
   if (weight_bytes < (64ull << 20)) bulk = false;
-  if (const char *e = std::getenv("TA_GEMV_BULK")) bulk = e[0] != '0' && p0.m <= 2 && bulk_possible(segs, nseg);
+  if (tunables().gemv_bulk >= 0) bulk = tunables().gemv_bulk != 0 && p0.m <= 2 && bulk_possible(segs, nseg);
   uint32_t best_s = 1;
   if (weight_bytes >= (64ull << 20) && mrows <= 2) {
     // Large matrices stream: about eight passes per CTA amortise its prologue and epilogue
@@ -710,8 +574,8 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
       if (s < 8 && (uint64_t)tiles * s * 2 * 2 > 8ull * (uint64_t)sm_count) break;   // the next split would not fit one wave
     }
   }
-  if (const char *e = std::getenv("TA_GEMV_KSPLIT")) {   // experiments: force the cluster split
-    const uint32_t v = (uint32_t)atoi(e);
+  {   // experiment switch: force the cluster split
+    const uint32_t v = (uint32_t)std::max(0, tunables().gemv_ksplit);
     if ((v == 1 || v == 2 || v == 4 || v == 8) && p0.k / v >= rows_per_pass) best_s = v;
   }
   g.ksplit = best_s;
@@ -729,11 +593,6 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
     }                                                                             \
     return;                                                                       \
   }
-  if (mma) {
-    if (tn == 64) launch_t<8, 64, false, true>(g, tiles, stream);
-    else launch_t<8, 32, false, true>(g, tiles, stream);
-    return;
-  }
   TA_GEMV_CASE(1)
   TA_GEMV_CASE(2)
   TA_GEMV_CASE(4)
@@ -741,10 +600,8 @@ void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool
 #undef TA_GEMV_CASE
 }
 
-TA_TRACE_EXPORT(ta_debug_gemv_trace)
-
-void launch_gemv_f16w(GemvParams p, int sm_count, uint32_t *status, cudaStream_t stream) {
-  launch_gemv_f16w_group(&p, 1, sm_count, true, status, stream);
+void launch_gemv_f16w(const Context &ctx, GemvParams p, const GemvWorkspace &ws, cudaStream_t stream) {
+  launch_gemv_f16w_group(ctx, &p, 1, true, ws, stream);
 }
 
 }  // namespace ta

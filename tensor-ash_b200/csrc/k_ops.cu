@@ -8,6 +8,7 @@
 // tree reductions so results do not depend on scheduling.
 #include <cuda_fp16.h>
 
+#include "k_umma.cuh"
 #include "ta_core.hpp"
 
 namespace ta {
@@ -428,6 +429,30 @@ void launch_prefill_qkv_pack(const float *qkv, const float *table, float *q, voi
   else
     prefill_qkv_pack_kernel<<<blocks, 256, 0, stream>>>(qkv, table, q, (float *)kt, (float *)v, tokens, heads,
                                                         kv_heads, head_dim, rot_dim, pos_base, t_max);
+  launched();
+}
+
+// Self-test of the bounded-wait machinery every tensor-core kernel here relies on: one warp waits,
+// through the same helper and status word those kernels use, on a barrier that nothing ever
+// completes.  After `limit_ns` the wait gives up, the kernel raises status bit 0 and returns
+// normally, so the host call fails with the bounded-wait message and the context stays usable.
+// Nothing faults, traps or spins without limit.
+__global__ void bounded_wait_probe_kernel(uint32_t *status, uint32_t limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    umma::mbar_init(umma::smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const bool ok = umma::mbar_wait(umma::smem_u32(&bar), 0, &abort_flag, 64, limit_ns);
+  __syncthreads();
+  if (!ok && threadIdx.x == 0) atomicOr(status, 1u);
+}
+
+void launch_bounded_wait_probe(uint32_t *status, uint32_t limit_ns, cudaStream_t stream) {
+  bounded_wait_probe_kernel<<<1, 32, 0, stream>>>(status, limit_ns);
   launched();
 }
 

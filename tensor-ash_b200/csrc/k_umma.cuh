@@ -46,7 +46,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // sleep_ns > 0 backs off between polls: for the long waits (a whole tile's main
 // loop) so that idle warps do not burn issue slots and shared-memory bandwidth.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort,
-                                          uint32_t sleep_ns = 0) {
+                                          uint32_t sleep_ns = 0, uint32_t limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -54,7 +54,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (sleep_ns) __nanosleep(sleep_ns);
     if ((++spins & 63u) == 0) {
       if (*abort) return false;
-      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort = 1;
         return false;
       }

@@ -844,13 +844,7 @@ int ta_llama_decode(ta_llama *model, uint32_t first_token, uint32_t n, uint32_t 
     // first input embedding: gather on the device from the token word
     *(volatile uint32_t *)m.token_cell.host = first_token;
     m.exec->embed_gather(m.token_cell, m.embd, m.x_a);
-    if (!m.decode_graph) {
-      *(volatile uint32_t *)m.pos_cell.host = m.pos;   // the eager pass inside prepare writes this slot
-      m.decode_graph = prepare_exec_ops(*m.exec, decode_ops(m));
-      // the eager pass and capture consumed x_a and rewrote it with the argmax token: restore the input
-      *(volatile uint32_t *)m.token_cell.host = first_token;
-      m.exec->embed_gather(m.token_cell, m.embd, m.x_a);
-    }
+    if (!m.decode_graph) m.decode_graph = prepare_exec_ops(*m.exec, decode_ops(m));   // records only
     for (uint32_t i = 0; i < n; ++i) {
       *(volatile uint32_t *)m.pos_cell.host = m.pos;
       const RunStats st = m.decode_graph->run();

@@ -474,6 +474,64 @@ int ta_tune_shape(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t 
 
 // ===================================================================== PART 2
 
+int ta_tune_shape_f16w(const ta_executor *exec, uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_tune_shape_f16w: exec is null");
+    if (!batch || !m || !n || !k)
+      fail("matmul dimensions must be non-zero, got B=%u rows=%u cols=%u", batch, m, n);
+    e.exec->tune_shape(batch, m, n, k, true);
+  });
+}
+
+int ta_tune_median(const uint64_t *samples, size_t n, uint64_t *out) {
+  g_last_error.clear();
+  if ((n && !samples) || !out) {
+    g_last_error = "ta_tune_median: null argument";
+    return -1;
+  }
+  const auto med = tune_median(std::vector<uint64_t>(samples, samples + n));
+  if (!med) return 1;
+  *out = *med;
+  return 0;
+}
+
+size_t ta_tune_candidate_at(size_t len, uint32_t round, size_t offset) {
+  return len ? tune_candidate_at(len, round, offset) : 0;
+}
+
+static int copy_out(const std::string &v, char *buf, size_t cap, const char *who) {
+  return status_call([&]() {
+    if (!buf || v.size() + 1 > cap) fail("%s: buffer of %zu bytes cannot hold %zu", who, cap, v.size() + 1);
+    memcpy(buf, v.c_str(), v.size() + 1);
+  });
+}
+
+int ta_tune_store_path(const char *device_name, char *buf, size_t cap) {
+  return copy_out(tune_store_path(device_name ? device_name : ""), buf, cap, "ta_tune_store_path");
+}
+
+int ta_tune_store_rewrite(const char *in_path, const char *out_path, size_t *n_entries) {
+  return status_call([&]() {
+    if (!in_path) fail("ta_tune_store_rewrite: in_path is null");
+    const auto map = load_tuned(in_path);
+    if (n_entries) *n_entries = map.size();
+    if (out_path) save_tuned(out_path, map);
+  });
+}
+
+int ta_experiment_check(const char *spec) {
+  return status_call([&]() { (void)parse_tunables(spec); });
+}
+
+int ta_selftest_bounded_wait(const ta_executor *exec, uint32_t limit_ns) {
+  return status_call([&]() {
+    const ta_executor &e = checked_ref(exec, "ta_selftest_bounded_wait: exec is null");
+    if (limit_ns == 0 || limit_ns > 1000000000u)
+      fail("ta_selftest_bounded_wait: limit_ns %u out of range (1 .. 1e9)", limit_ns);
+    e.exec->selftest_bounded_wait(limit_ns);
+  });
+}
+
 int ta_matmul_split_k2(const ta_executor *exec, const ta_matmul_call *calls, size_t n_calls,
                        uint32_t splits, ta_run_stats *stats) {
   return status_call([&]() {
@@ -635,6 +693,22 @@ void ta_comm_destroy(ta_comm *comm) {
   g_last_error.clear();
   delete comm;
 }
+int ta_comm_set_wait_limit_ns(ta_comm *comm, uint64_t limit_ns) {
+  return status_call([&]() {
+    if (!comm) fail("ta_comm_set_wait_limit_ns: comm is null");
+    if (limit_ns < 1000 || limit_ns > 600000000000ull)
+      fail("ta_comm_set_wait_limit_ns: %llu ns is outside 1 us .. 600 s", (unsigned long long)limit_ns);
+    comm->comm->peer_wait_limit_ns = limit_ns;
+  });
+}
+
+int ta_comm_resync(ta_comm *comm) {
+  return status_call([&]() {
+    if (!comm) fail("ta_comm_resync: comm is null");
+    comm->comm->resync();
+  });
+}
+
 uint32_t ta_comm_rank(const ta_comm *comm) { return comm ? comm->comm->rank : 0; }
 uint32_t ta_comm_world(const ta_comm *comm) { return comm ? comm->comm->world : 0; }
 

@@ -108,7 +108,7 @@ __device__ __forceinline__ uint32_t *peer_flag(uint8_t *buf, uint32_t parity, ui
 // peer (it needs the peer's flag of call e to finish call e), so the slot a peer still reads
 // is never the one being written.
 __global__ void __launch_bounds__(PEER_THREADS)
-peer_all_reduce_kernel(float *data, uint32_t count, PeerTable t, uint32_t *status, uint32_t pdl) {
+peer_all_reduce_kernel(float *data, uint32_t count, PeerTable t, uint32_t *status, uint32_t pdl, uint64_t limit_ns) {
   if (pdl) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -143,7 +143,7 @@ peer_all_reduce_kernel(float *data, uint32_t count, PeerTable t, uint32_t *statu
       if (seen == ticket) break;
       if ((++spins & 255u) == 0) {
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if (now - t0 > 1000000000ull) {   // one second: give up, report, carry on with what is there
+        if (now - t0 > limit_ns) {   // give up, report, carry on with what is there
           ok_flag = 0u;
           break;
         }
@@ -194,15 +194,17 @@ std::unique_ptr<Comm> Comm::create(const std::shared_ptr<Context> &ctx, uint32_t
 // NCCL all-gather.  Any failure (no peer access, IPC unavailable) leaves the communicator
 // on NCCL for all sizes.
 void Comm::setup_peer_exchange() {
-  const char *env = std::getenv("TA_PEER_ALLREDUCE");
-  if (env && env[0] == '0') return;
-  if (world > PEER_MAX_WORLD) return;
+  // Every rank takes part in both collectives below whatever happened locally: a rank that cannot
+  // (or is told not to) use the peer path carries a failure flag through them, so that no rank is
+  // left waiting inside NCCL for one that returned early.
+  bool ok = tunables().peer_allreduce && world <= PEER_MAX_WORLD;
   NcclApi &api = nccl();
   void *buf = nullptr;
-  if (cudaMalloc(&buf, PEER_BUF_BYTES) != cudaSuccess) { cudaGetLastError(); return; }
-  cudaMemset(buf, 0, PEER_BUF_BYTES);
   cudaIpcMemHandle_t mine;
-  if (cudaIpcGetMemHandle(&mine, buf) != cudaSuccess) { cudaGetLastError(); cudaFree(buf); return; }
+  memset(&mine, 0, sizeof(mine));
+  if (ok && cudaMalloc(&buf, PEER_BUF_BYTES) != cudaSuccess) { cudaGetLastError(); buf = nullptr; ok = false; }
+  if (ok) cudaMemset(buf, 0, PEER_BUF_BYTES);
+  if (ok && cudaIpcGetMemHandle(&mine, buf) != cudaSuccess) { cudaGetLastError(); ok = false; }
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "ipc handle size");
   uint8_t *dev_handles = nullptr;   // [world + 1][64]: slot world holds this rank's handle and an ok byte
   TA_CUDA(cudaMalloc((void **)&dev_handles, (size_t)(world + 1) * 64));
@@ -216,7 +218,6 @@ void Comm::setup_peer_exchange() {
   TA_CUDA(cudaMemcpy(all.data(), dev_handles, (size_t)world * 64, cudaMemcpyDeviceToHost));
   cudaFree(dev_handles);
   std::vector<void *> mapped(world, nullptr);
-  bool ok = true;
   for (uint32_t r = 0; r < world && ok; ++r) {
     if (r == rank) { mapped[r] = buf; continue; }
     if (cudaIpcOpenMemHandle(&mapped[r], all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
@@ -238,7 +239,7 @@ void Comm::setup_peer_exchange() {
   if (total_bad != 0.0f) {
     for (uint32_t r = 0; r < world; ++r)
       if (r != rank && mapped[r]) cudaIpcCloseMemHandle(mapped[r]);
-    cudaFree(buf);
+    if (buf) cudaFree(buf);
     return;
   }
   peer_own = buf;
@@ -263,9 +264,33 @@ bool Comm::peer_all_reduce_sum(float *data, size_t count, uint32_t *status, bool
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, peer_all_reduce_kernel, data, (uint32_t)count, t, status, pdl ? 1u : 0u));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, peer_all_reduce_kernel, data, (uint32_t)count, t, status, pdl ? 1u : 0u, peer_wait_limit_ns));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return true;
+}
+
+// Collective: every rank of the group calls it.  Brings the peer exchange back to a common state
+// after a rank gave up on a wait (status bit 2): all ranks meet in NCCL, each zeroes its own
+// flags and call counters, and they meet again before anyone pushes.
+void Comm::resync() {
+  if (world == 1 || !handle) return;
+  ctx->make_current();
+  TA_CUDA(cudaDeviceSynchronize());
+  float *word = nullptr;
+  TA_CUDA(cudaMalloc((void **)&word, sizeof(float)));
+  TA_CUDA(cudaMemset(word, 0, sizeof(float)));
+  cudaStream_t st;
+  TA_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  for (int pass = 0; pass < 2; ++pass) {
+    nccl_check(nccl().AllReduce(word, word, 1, NCCL_FLOAT32, NCCL_SUM, handle, st), "ncclAllReduce (resync)");
+    TA_CUDA(cudaStreamSynchronize(st));
+    if (pass == 0 && peer_own) {
+      TA_CUDA(cudaMemset(static_cast<uint8_t *>(peer_own) + PEER_DATA_BYTES, 0, PEER_BUF_BYTES - PEER_DATA_BYTES));
+      TA_CUDA(cudaDeviceSynchronize());
+    }
+  }
+  cudaStreamDestroy(st);
+  cudaFree(word);
 }
 
 Comm::~Comm() {

@@ -46,6 +46,28 @@ void cuda_check(cudaError_t e, const char *what);
 // Launch counter behind ta_kernel_launch_count().
 extern std::atomic<uint64_t> g_launches;
 
+// ------------------------------------------------------------------ experiment switches
+// Every A/B switch of the kernels lives here, read once per process from the ONE environment
+// variable TA_EXPERIMENT, a comma-separated list of `name=value` pairs, e.g.
+//   TA_EXPERIMENT="tf32x3_chunk_kb=32,peer_allreduce=0"
+// Unknown names are an error at first use.  Defaults are the shipped configuration; nothing on
+// the launch path calls getenv.
+struct Tunables {
+  uint32_t tf32x3_chunk_kb = 0;   // K blocks of 16 per tensor-memory accumulation (0 = kernel default)
+  int gemv_ksplit = 0;            // force the GEMV cluster split along K (1/2/4/8; 0 = chosen per shape)
+  int gemv_bulk = -1;             // 1/0: force the bulk-copy ring of the 1-2 row GEMV on/off (-1 = per shape)
+  int gemv_umma = -1;             // 1/0: force the tensor-memory GEMV (3..8 rows) on/off (-1 = per shape)
+  bool f16w_pre = true;           // f16w tensor-core GEMM: convert A once per launch into scratch
+  uint32_t f16w_apad = 0;         // extra halves of row pitch of that f16 copy (multiple of 8)
+  bool pdl = true;                // programmatic dependent launch between decode kernels
+  bool peer_allreduce = true;     // one-launch peer-write all-reduce for small tensor-parallel exchanges
+  bool splitk2_tensor = true;     // split-K2 stage 1 on the tensor cores where the shape allows
+  int f16w_splitk = -1;           // f16w tensor-core GEMM: K split for grids under one wave (-1 = per shape, 0/1 = off)
+};
+const Tunables &tunables();
+// parses `name=value,...` into a Tunables (throws on an unknown name); exposed for the host tests
+Tunables parse_tunables(const char *spec);
+
 // ------------------------------------------------------------------ dtype
 enum class DType : uint8_t { F32 = 0, F16 = 1 };
 inline uint64_t dtype_size(DType d) { return d == DType::F32 ? 4 : 2; }
@@ -243,6 +265,12 @@ struct TuneKeyHash {
     return (size_t)h;
   }
 };
+// Tuner arithmetic (src/executor/tuning.rs:319-344): median of u64 samples (mean of the middle pair,
+// rounded down, for an even count; nullopt when empty) and the candidate measured at `offset` of
+// `round` (round 0 in index order; measured rounds come in pairs, forward then backward from a
+// start that moves by half the list per pair, so every candidate sees every rank sum equally).
+std::optional<uint64_t> tune_median(std::vector<uint64_t> samples);
+size_t tune_candidate_at(size_t len, uint32_t round, size_t offset);
 uint64_t registry_hash();
 std::string tune_store_path(const std::string &device_name);
 std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> load_tuned(const std::string &path);
@@ -268,7 +296,19 @@ struct GemmParams {
   uint32_t chunk_kb;
   uint32_t b_grouped = 0;    // launcher-set: the B tensor map is the rank-4 grouped view (one TMA per stage)
   uint32_t c_f16 = 0;        // a16 route: C (and the old C when accumulating) is f16 storage
+  // tensor-core split-K stage 1 (launcher-set): planes per batch = splits * sk_c, K blocks of 16 per
+  // caller-visible split and per plane, destination of the planes
+  uint32_t sk_subs = 0, sk_c = 0, sk_kb_per_split = 0, sk_kb_per_sub = 0;
+  float *sk_planes = nullptr;
 };
+
+// How the tensor-core stage 1 of split-K2 cuts a problem (see k_gemm_tf32x3.cu).  `planes` per batch
+// = splits * c; eligible = false keeps the problem on the SIMT stage 1.
+struct SplitK2TensorPlan {
+  bool eligible = false;
+  uint32_t tile_n = 0, c = 0, kb_per_split = 0, kb_per_sub = 0, planes = 0;
+};
+SplitK2TensorPlan splitk2_tensor_plan(const GemmParams &p, uint32_t splits, int sm_count);
 
 // Parameters of the f16-weight GEMV kernel (M <= 8 activation rows).
 struct GemvParams {
@@ -377,8 +417,13 @@ struct Comm {
   uint32_t rank = 0, world = 1;
   void *handle = nullptr;   // ncclComm_t; null when world == 1
   void *peer_own = nullptr;            // this rank's exchange buffer (small all-reduces), null = NCCL only
+  // how long a rank waits on the device for a peer's flag before it gives up and reports (status bit
+  // 2): generous by default, because ranks of one job drift apart by whole milliseconds while one
+  // of them still loads weights or instantiates a graph
+  uint64_t peer_wait_limit_ns = 10000000000ull;
   std::vector<void *> peer_bufs;       // every rank's buffer as mapped here (index = rank)
   void setup_peer_exchange();
+  void resync();
   // one-launch peer-write all-reduce; false when the request does not fit it (caller uses NCCL)
   bool peer_all_reduce_sum(float *data, size_t count, uint32_t *status, bool pdl, cudaStream_t stream) const;
   static std::unique_ptr<Comm> create(const std::shared_ptr<Context> &ctx, uint32_t rank, uint32_t world,
@@ -410,6 +455,8 @@ using Launch = std::function<void(Slot &, cudaStream_t)>;
 
 constexpr uint32_t ATTN_DECODE_MAX_CHUNKS = 32;
 constexpr uint32_t ATTN_DECODE_MAX_KV_HEADS = 256;
+// ticket words per slot / prepared object: [0, 256) decode attention (one per kv head), the rest GEMV column groups
+constexpr uint32_t SLOT_COUNTERS = 256 + 4096;
 inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
   const uint32_t c = (kv_len + 31) / 32;
   return c < 8 ? 8 : (c > ATTN_DECODE_MAX_CHUNKS ? ATTN_DECODE_MAX_CHUNKS : c);
@@ -428,10 +475,28 @@ struct Slot {
   size_t scratch_bytes = 0;
   void *staging = nullptr;       // grow-only pinned host staging
   size_t staging_bytes = 0;
-  uint32_t *status = nullptr;    // device word: kernels report bounded-wait timeouts here
-  uint32_t *counters = nullptr;  // ATTN_DECODE_MAX_KV_HEADS zeroed device words (decode attention tickets)
+  uint32_t *status = nullptr;       // status word as kernels address it (raised only on a failure)
+  uint32_t *status_host = nullptr;  // the same word in page-locked host memory: read after a sync, no copy
+  uint32_t *counters = nullptr;  // SLOT_COUNTERS zeroed device words (tickets of the decode attention and the GEMV finishers)
   bool busy = false;
 };
+// Status word shared by host and device: page-locked, device-mapped host memory.  Kernels write it
+// only when something went wrong (a bounded wait ran out), so it costs nothing per launch, and the
+// host reads it after the stream synchronised without a device-to-host copy.
+void alloc_status_word(uint32_t **host, uint32_t **device);
+void free_status_word(uint32_t *host);
+// reads and clears the word; raises the matching error when a bit is set
+void check_status_word(uint32_t *host);
+
+// What a GEMV launch may use of its slot (or prepared object): the status word, and for the
+// tensor-memory kernel the plane scratch and the ticket words.
+struct GemvWorkspace {
+  uint32_t *status = nullptr;
+  void *scratch = nullptr;
+  size_t scratch_bytes = 0;
+  uint32_t *counters = nullptr;
+};
+inline GemvWorkspace gemv_workspace(const Slot &s) { return GemvWorkspace{s.status, s.scratch, s.scratch_bytes, s.counters}; }
 
 struct ExecutorConfig {
   size_t n_slots = 2;
@@ -502,16 +567,22 @@ class Executor {
                         uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base, uint32_t dst_offset,
                         const uint32_t strides[3], uint32_t pos_scale, const PosCell *cell);
   RunStats argmax(const Tensor &in, const PosCell &result);
+  // launches the bounded-wait self-test kernel; always ends in the bounded-wait error
+  void selftest_bounded_wait(uint32_t limit_ns);
   RunStats embed_gather(const PosCell &token, const Tensor &table, const Tensor &out);
   RunStats embed_gather_rows(const TokenIds &tokens, const Tensor &table, const Tensor &out);
   // scratch an op wants in its slot beyond split-K planes (the f16 copy of A for the f16w tensor-core GEMM)
   size_t op_scratch_bytes(const ResolvedMatmul &r, const Route &route) const;
+  SplitK2TensorPlan splitk2_plan_for(const GemmParams &p, uint32_t splits) const;
+  size_t splitk2_scratch_bytes(const MatmulOp &op, const ResolvedMatmul &r, uint32_t splits) const;
   bool gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route, GemvParams *out) const;
   std::vector<Launch> plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops, size_t *n_calls,
                                     size_t *scratch_bytes = nullptr) const;
   RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
                        const Tensor *norm_w, float eps);
-  void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k);
+  void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16 = false);
+  // candidate kernels the tuner measures for a shape (src/pipeline/mod.rs:491-535)
+  std::vector<int> tune_candidates(uint32_t m, uint32_t n, uint32_t k, bool b_f16) const;
 
   // Model ops (src/executor/elementwise/ops.rs).
   RunStats softmax_rows(const Tensor &in, const Tensor &out, float scale, uint32_t mask_kind,
@@ -563,13 +634,12 @@ class Executor {
   std::shared_ptr<HostStreamState> host_stream_;  // copy streams, events and the staging ring
 };
 
-// Device status word of a slot: bit 0 = a bounded device-side wait ran out, bit 1 = the tensor-core
-// GEMV met an activation outside the f16 range.  Raises the matching error.
+// Device status word of a slot: bit 0 = a bounded wait inside a kernel ran out (a barrier, a copy),
+// bit 2 = the peer exchange of a tensor-parallel all-reduce waited for a rank that did not arrive.
 [[noreturn]] inline void fail_device_status(uint32_t status) {
-  if (status & 2u)
-    fail("f16-weight GEMV (tensor-core variant, 5..8 rows): an activation magnitude exceeds the f16 range "
-         "(65504); results are invalid -- set TA_GEMV_MMA=0 to keep such inputs on the f32 FMA path (status 0x%x)",
-         status);
+  if (status & 4u)
+    fail("a kernel gave up on a bounded device-side wait for a peer rank of the tensor-parallel exchange "
+         "(status 0x%x); results are invalid", status);
   fail("a kernel gave up on a bounded device-side wait (status 0x%x); results are invalid", status);
 }
 
@@ -590,7 +660,8 @@ struct PreparedOps {
   cudaStream_t stream = nullptr;
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   void *scratch = nullptr;
-  uint32_t *counters = nullptr;   // this object's own decode-attention tickets
+  uint32_t *counters = nullptr;   // this object's own ticket words
+  uint32_t *status = nullptr, *status_host = nullptr;   // this object's own status word (see Slot)
   size_t n_calls = 0;
   uint64_t total_flops = 0;
   bool in_flight = false;
@@ -623,6 +694,13 @@ void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t til
 void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
                         cudaStream_t stream);
 void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream);
+// stage 1 on the tensor cores (plan.eligible) followed by the fixed-order reduce of plan.planes planes
+void launch_splitk2_tensor(const Context &ctx, const GemmParams &p, const SplitK2TensorPlan &plan, float *scratch,
+                           uint32_t *status, cudaStream_t stream);
+// sum of `planes` planes per batch in plane order inside fixed groups, groups in order; launched so
+// that it may be scheduled while the producer of the planes still runs (it waits for it on the device)
+void launch_splitk2_reduce_wide(const float *scratch, float *c, uint64_t total, uint64_t mn, uint32_t planes,
+                                cudaStream_t stream);
 void launch_splitk2_reduce(const float *scratch, float *c, uint64_t total, uint64_t mn,
                            uint32_t splits, cudaStream_t stream);
 // Split-K2 on the module's fixed scratch array: no allocation of any kind.
@@ -630,9 +708,15 @@ constexpr uint64_t SPLITK2_STATIC_MAX_FLOATS = 1ull << 20;  // 4 MiB
 void launch_splitk2_static(const GemmParams &p, cudaStream_t stream);
 
 bool gemv_f16w_supported(uint32_t m, uint32_t n, uint32_t k, bool packed, uint32_t tile_n);
-void launch_gemv_f16w(GemvParams p, int sm_count, uint32_t *status, cudaStream_t stream);
+void launch_gemv_f16w(const Context &ctx, GemvParams p, const GemvWorkspace &ws, cudaStream_t stream);
+// tensor-memory kernel for 3..8 rows (k_gemv_umma.cu)
+bool gemv_umma_eligible(const GemvParams &p);
+bool gemv_routes_to_umma(const GemvParams &p);
+size_t gemv_umma_scratch_bytes(uint32_t n, uint32_t k, bool dual, int sm_count);
+void launch_gemv_umma(const Context &ctx, const GemvParams &p, float *scratch, size_t scratch_bytes, uint32_t *counters,
+                      uint32_t *status, bool pdl, cudaStream_t stream);
 bool gemv_f16w_groupable(const GemvParams &a, const GemvParams &b);
-void launch_gemv_f16w_group(const GemvParams *segs, int nseg, int sm_count, bool pdl, uint32_t *status,
+void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg, bool pdl, const GemvWorkspace &ws,
                             cudaStream_t stream);
 
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream);
@@ -658,6 +742,7 @@ void launch_embed_gather(const uint32_t *tokens, uint32_t n_tokens, const void *
 void launch_prefill_qkv_pack(const float *qkv, const float *table, float *q, void *kt, void *v, bool kv_f16,
                              uint32_t tokens, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
                              uint32_t rot_dim, uint32_t pos_base, uint32_t t_max, cudaStream_t stream);
+void launch_bounded_wait_probe(uint32_t *status, uint32_t limit_ns, cudaStream_t stream);
 void launch_rope_scatter(const float *in, const float *table, void *dst, bool dst_f16, uint32_t tokens,
                          uint32_t heads, uint32_t head_dim, uint32_t rot_dim, uint32_t pos_base,
                          uint32_t dst_off, const uint32_t strides[3], uint32_t pos_scale,

@@ -490,7 +490,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     return ptr == g.x || ptr == g.d || ptr == g.bias || ptr == g.norm_w || ptr == g.table ||
            (g.accumulate && ptr == g.c);
   };
-  const int sms = ctx_->sm_count;
+  const Context *cx = ctx_.get();
   std::vector<Launch> plan;
   plan.reserve(ops.size());
   std::vector<GemvParams> prev_gemv;   // segments of the launch planned last, when it was a GEMV
@@ -548,7 +548,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         f.act = 0; f.binary = 0; f.d = nullptr;
         if (flops) *flops += c0.flops + c1.flops;
         if (n_calls) *n_calls += 2;
-        plan.push_back([f, sms](Slot &slot, cudaStream_t st) { launch_gemv_f16w_group(&f, 1, sms, true, slot.status, st); });
+        plan.push_back([f, cx](Slot &slot, cudaStream_t st) { launch_gemv_f16w_group(*cx, &f, 1, true, gemv_workspace(slot), st); });
         prev_gemv.assign(1, f);
         i += 2;
         continue;
@@ -575,8 +575,8 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     }
     if (flops) *flops += fl;
     if (n_calls) *n_calls += segs.size();
-    plan.push_back([segs, sms](Slot &slot, cudaStream_t st) {
-      launch_gemv_f16w_group(segs.data(), (int)segs.size(), sms, true, slot.status, st);
+    plan.push_back([segs, cx](Slot &slot, cudaStream_t st) {
+      launch_gemv_f16w_group(*cx, segs.data(), (int)segs.size(), true, gemv_workspace(slot), st);
     });
     prev_gemv = segs;
     i = j;
@@ -601,6 +601,13 @@ RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
 
 RunStats Executor::run_single(const ExecOp &op) { return run_exec_ops({op}); }
 
+void Executor::selftest_bounded_wait(uint32_t limit_ns) {
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  timed(slot, 1, 0, [&](cudaStream_t st) { launch_bounded_wait_probe(slot.status, limit_ns, st); });
+}
+
 std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<ExecOp> &ops) {
   if (ops.empty()) fail("prepare_exec_ops: empty op list");
   exec.context()->make_current();
@@ -613,8 +620,9 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
   TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
   TA_CUDA(cudaEventCreate(&prep->ev_begin));
   TA_CUDA(cudaEventCreate(&prep->ev_end));
-  TA_CUDA(cudaMalloc((void **)&prep->counters, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
-  TA_CUDA(cudaMemset(prep->counters, 0, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
+  TA_CUDA(cudaMalloc((void **)&prep->counters, SLOT_COUNTERS * sizeof(uint32_t)));
+  TA_CUDA(cudaMemset(prep->counters, 0, SLOT_COUNTERS * sizeof(uint32_t)));
+  alloc_status_word(&prep->status_host, &prep->status);
   Slot &real_slot = exec.checkout_slot();
   {
     SlotGuard g(exec, real_slot);
@@ -623,10 +631,12 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
     slot.counters = prep->counters;
     slot.scratch = prep->scratch;
     slot.scratch_bytes = scratch_bytes;
-    // Run once eagerly: first-use set-up (function attributes, tensor maps) must
-    // not happen inside the capture, and it proves the batch launches at all.
-    for (const Launch &l : plan) l(slot, prep->stream);
-    TA_CUDA(cudaStreamSynchronize(prep->stream));
+    slot.status = prep->status;
+    slot.status_host = prep->status_host;
+    // Recorded only, as the reference's prepare_exec_ops does (src/executor/graph_ops.rs:249-353):
+    // nothing executes until the first run, so accumulating ops, in-place residuals, cache appends
+    // and the argmax cell are untouched by creating the object.  First-use set-up (function
+    // attributes, tensor maps) consists of host calls, which a capture allows.
     TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
     try {
       for (const Launch &l : plan) l(slot, prep->stream);

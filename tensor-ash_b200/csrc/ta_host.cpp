@@ -2,6 +2,7 @@
 // registry, routing heuristics, packed-weight layout, tuned-winner store.
 // Nothing here touches a device, so it is exercised on machines without one.
 #include <sys/stat.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <cctype>
@@ -10,6 +11,7 @@
 #include <fstream>
 #include <functional>
 #include <sstream>
+#include <tuple>
 
 #include "ta_core.hpp"
 
@@ -42,6 +44,46 @@ void fail(const char *fmt, ...) {
   std::string s = vstrf(fmt, ap);
   va_end(ap);
   throw Error(s);
+}
+
+// ------------------------------------------------------------------ experiment switches
+Tunables parse_tunables(const char *spec) {
+  Tunables t;
+  if (!spec) return t;
+  std::string all(spec);
+  size_t pos = 0;
+  while (pos < all.size()) {
+    size_t end = all.find(',', pos);
+    if (end == std::string::npos) end = all.size();
+    std::string item = all.substr(pos, end - pos);
+    pos = end + 1;
+    while (!item.empty() && isspace((unsigned char)item.front())) item.erase(item.begin());
+    while (!item.empty() && isspace((unsigned char)item.back())) item.pop_back();
+    if (item.empty()) continue;
+    const size_t eq = item.find('=');
+    if (eq == std::string::npos) fail("TA_EXPERIMENT: '%s' is not name=value", item.c_str());
+    const std::string name = item.substr(0, eq);
+    const long v = strtol(item.c_str() + eq + 1, nullptr, 10);
+    if (name == "tf32x3_chunk_kb") t.tf32x3_chunk_kb = v > 0 ? (uint32_t)v : 0;
+    else if (name == "gemv_ksplit") t.gemv_ksplit = (int)v;
+    else if (name == "gemv_bulk") t.gemv_bulk = (int)v;
+    else if (name == "gemv_umma") t.gemv_umma = (int)v;
+    else if (name == "f16w_pre") t.f16w_pre = v != 0;
+    else if (name == "f16w_apad") t.f16w_apad = (uint32_t)(v > 0 ? v : 0) & ~7u;
+    else if (name == "pdl") t.pdl = v != 0;
+    else if (name == "peer_allreduce") t.peer_allreduce = v != 0;
+    else if (name == "splitk2_tensor") t.splitk2_tensor = v != 0;
+    else if (name == "f16w_splitk") t.f16w_splitk = (int)v;
+    else
+      fail("TA_EXPERIMENT: unknown switch '%s' (known: tf32x3_chunk_kb, gemv_ksplit, gemv_bulk, gemv_umma, "
+           "f16w_pre, f16w_apad, pdl, peer_allreduce, splitk2_tensor, f16w_splitk)", name.c_str());
+  }
+  return t;
+}
+
+const Tunables &tunables() {
+  static const Tunables t = parse_tunables(getenv("TA_EXPERIMENT"));
+  return t;
 }
 
 // ------------------------------------------------------------------ f16 (src/dtype.rs:42-112)
@@ -445,6 +487,23 @@ void pack_f16w_row_tiles(const float *src, float *dst, size_t k, size_t n, size_
       memcpy(dst + (t * k + kk) * tile_n, src + kk * n + t * tile_n, tile_n * sizeof(float));
 }
 
+// ------------------------------------------------------------------ tuner arithmetic
+std::optional<uint64_t> tune_median(std::vector<uint64_t> v) {
+  if (v.empty()) return std::nullopt;
+  std::sort(v.begin(), v.end());
+  const size_t mid = v.size() / 2;
+  if (v.size() % 2 == 0) return (uint64_t)(((unsigned __int128)v[mid - 1] + v[mid]) / 2);
+  return v[mid];
+}
+
+size_t tune_candidate_at(size_t len, uint32_t round, size_t offset) {
+  if (round == 0) return offset;
+  const size_t pair = (round - 1) / 2;
+  const size_t start = pair * ((len + 1) / 2) % len;
+  if (round % 2) return (start + offset) % len;
+  return (start + len - 1 - offset) % len;
+}
+
 // ------------------------------------------------------------------ tuned-winner store
 uint64_t registry_hash() {
   uint64_t h = 1469598103934665603ull;  // FNV-1a over names and tiles
@@ -472,6 +531,9 @@ static std::string tune_header() {
               (unsigned long long)registry_hash());
 }
 
+// One line per shape: `B M N K kernel [splitk2=S] [bf16]`; a file whose first line is not this
+// build's header (another registry) is ignored as a whole, a malformed line alone
+// (src/pipeline/tuning.rs:96-155).
 std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> load_tuned(const std::string &path) {
   std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> out;
   if (path.empty()) return out;
@@ -487,32 +549,41 @@ std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> load_tuned(const std::strin
     TunedEntry e;
     e.kernel = kernel_index_by_name(kernel.c_str());
     if (e.kernel < 0) continue;
-    key.b_f16 = KERNEL_SPECS[e.kernel].weights_f16;
+    key.b_f16 = false;
     while (ss >> tok) {
-      if (tok.rfind("splitk2=", 0) == 0) e.splits = (uint32_t)strtoul(tok.c_str() + 8, nullptr, 10);
-      else if (tok == "bf16") key.b_f16 = true;
+      if (tok.rfind("splitk2=", 0) == 0) {
+        char *end = nullptr;
+        const unsigned long v = strtoul(tok.c_str() + 8, &end, 10);
+        if (end != tok.c_str() + 8 && *end == 0 && v >= 2 && v <= 0xffff) e.splits = (uint32_t)v;
+      } else if (tok == "bf16") {
+        key.b_f16 = true;
+      }
     }
     out[key] = e;
   }
   return out;
 }
 
+// Rewrites the whole store (it is small), sorted by shape, through a uniquely named temporary
+// file and an atomic rename (src/pipeline/tuning.rs:158-199).
 void save_tuned(const std::string &path,
                 const std::unordered_map<TuneKey, TunedEntry, TuneKeyHash> &map) {
   if (path.empty()) return;
   const std::string dir = path.substr(0, path.find_last_of('/'));
-  std::string cmd_dir;
   for (size_t i = 1; i <= dir.size(); ++i)
-    if (i == dir.size() || dir[i] == '/') {
-      cmd_dir = dir.substr(0, i);
-      ::mkdir(cmd_dir.c_str(), 0755);
-    }
-  const std::string tmp = path + ".tmp";
+    if (i == dir.size() || dir[i] == '/') ::mkdir(dir.substr(0, i).c_str(), 0755);
+  std::vector<std::pair<TuneKey, TunedEntry>> entries(map.begin(), map.end());
+  std::sort(entries.begin(), entries.end(), [](const auto &x, const auto &y) {
+    const TuneKey &a = x.first, &b = y.first;
+    return std::make_tuple(a.batch, a.m, a.n, a.k, a.b_f16) < std::make_tuple(b.batch, b.m, b.n, b.k, b.b_f16);
+  });
+  static std::atomic<uint64_t> next_tmp{0};
+  const std::string tmp = path + ".tmp." + std::to_string((long)getpid()) + "." + std::to_string(next_tmp.fetch_add(1));
   {
     std::ofstream f(tmp, std::ios::trunc);
     if (!f) return;
     f << tune_header() << "\n";
-    for (const auto &kv : map) {
+    for (const auto &kv : entries) {
       f << kv.first.batch << " " << kv.first.m << " " << kv.first.n << " " << kv.first.k << " "
         << KERNEL_SPECS[kv.second.kernel].name;
       if (kv.second.splits > 1) f << " splitk2=" << kv.second.splits;

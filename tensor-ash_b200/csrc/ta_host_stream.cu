@@ -210,12 +210,7 @@ RunStats Executor::run_matmul_host_batched(const HostBatchedMatmul &h) {
   TA_CUDA(cudaStreamSynchronize(st.d2h));
   TA_CUDA(cudaStreamSynchronize(comp));
   TA_CUDA(cudaStreamSynchronize(st.h2d));
-  uint32_t status = 0;
-  TA_CUDA(cudaMemcpy(&status, slot.status, sizeof(status), cudaMemcpyDeviceToHost));
-  if (status) {
-    cudaMemset(slot.status, 0, sizeof(uint32_t));
-    fail_device_status(status);
-  }
+  check_status_word(slot.status_host);
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, st.ev_begin, st.ev_end));
   RunStats out;

@@ -132,10 +132,9 @@ Executor::Executor(std::shared_ptr<Context> ctx, int selection, ExecutorConfig c
     TA_CUDA(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
     TA_CUDA(cudaEventCreate(&s.ev_begin));
     TA_CUDA(cudaEventCreate(&s.ev_end));
-    TA_CUDA(cudaMalloc(&s.status, sizeof(uint32_t)));
-    TA_CUDA(cudaMemset(s.status, 0, sizeof(uint32_t)));
-    TA_CUDA(cudaMalloc((void **)&s.counters, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
-    TA_CUDA(cudaMemset(s.counters, 0, ATTN_DECODE_MAX_KV_HEADS * sizeof(uint32_t)));
+    alloc_status_word(&s.status_host, &s.status);
+    TA_CUDA(cudaMalloc((void **)&s.counters, SLOT_COUNTERS * sizeof(uint32_t)));
+    TA_CUDA(cudaMemset(s.counters, 0, SLOT_COUNTERS * sizeof(uint32_t)));
   }
   tune_path_ = tune_store_path(ctx_->name);
   tuned_ = load_tuned(tune_path_);
@@ -151,7 +150,7 @@ Executor::~Executor() {
     if (s.stream) cudaStreamSynchronize(s.stream);
     if (s.scratch) cudaFree(s.scratch);
     if (s.staging) cudaFreeHost(s.staging);
-    if (s.status) cudaFree(s.status);
+    free_status_word(s.status_host);
     if (s.counters) cudaFree(s.counters);
     if (s.ev_begin) cudaEventDestroy(s.ev_begin);
     if (s.ev_end) cudaEventDestroy(s.ev_end);
@@ -200,6 +199,21 @@ void Executor::ensure_scratch(Slot &slot, size_t bytes) {
   slot.scratch_bytes = 0;
   TA_CUDA(cudaMalloc(&slot.scratch, bytes));
   slot.scratch_bytes = bytes;
+}
+
+void alloc_status_word(uint32_t **host, uint32_t **device) {
+  TA_CUDA(cudaHostAlloc((void **)host, sizeof(uint32_t), cudaHostAllocMapped));
+  **host = 0;
+  TA_CUDA(cudaHostGetDevicePointer((void **)device, *host, 0));
+}
+void free_status_word(uint32_t *host) {
+  if (host) cudaFreeHost(host);
+}
+void check_status_word(uint32_t *host) {
+  const uint32_t status = *(volatile uint32_t *)host;
+  if (!status) return;
+  *(volatile uint32_t *)host = 0;
+  fail_device_status(status);
 }
 
 void Executor::validate_tensor(const Tensor &t, const char *what) const {
@@ -414,10 +428,31 @@ GemmParams make_params(const MatmulOp &op, const ResolvedMatmul &r) {
 }
 }  // namespace
 
+// Stage 1 of the split-K2 route runs on the tensor cores where the partition allows; an executor
+// whose kernel selection names a split_k2_* kernel explicitly keeps the SIMT stage 1, whose
+// planes hold the reference shader's sequential fma chains.
+SplitK2TensorPlan Executor::splitk2_plan_for(const GemmParams &p, uint32_t splits) const {
+  if (selection_ >= 0 && KERNEL_SPECS[selection_].family == Family::SplitK2) return SplitK2TensorPlan{};
+  return splitk2_tensor_plan(p, splits, ctx_->sm_count);
+}
+
+// Bytes of plane scratch the split-K2 route of this problem needs in its slot.
+size_t Executor::splitk2_scratch_bytes(const MatmulOp &op, const ResolvedMatmul &r, uint32_t splits) const {
+  if (splits <= 1) return 0;
+  const SplitK2TensorPlan tplan = splitk2_plan_for(make_params(op, r), splits);
+  const uint64_t planes = tplan.eligible ? tplan.planes : splits;
+  return (size_t)((uint64_t)r.batch * planes * r.m * r.n * 4);
+}
+
 // The f16w tensor-core GEMM rounds A to f16 once per launch when its slot has room for the copy
 // (ops of one submission run in stream order, so they share the region); capped at 256 MiB.
 size_t Executor::op_scratch_bytes(const ResolvedMatmul &r, const Route &route) const {
-  if (route.kernel < 0 || KERNEL_SPECS[route.kernel].family != Family::F16wUmma || route.splits > 1) return 0;
+  if (route.kernel < 0 || route.splits > 1) return 0;
+  if (KERNEL_SPECS[route.kernel].family == Family::RowGemv && r.b_f16 && !r.a_f16 && r.batch == 1 && r.m <= 8 &&
+      r.k % 16 == 0 && (tunables().gemv_umma == 1 || (r.m >= 3 && tunables().gemv_umma != 0)))
+    // records of the tensor-memory GEMV; sized for the SwiGLU pair too (twice the groups)
+    return gemv_umma_scratch_bytes(r.n, r.k, true, ctx_->sm_count);
+  if (KERNEL_SPECS[route.kernel].family != Family::F16wUmma) return 0;
   const size_t need = gemm_f16w_umma_scratch_bytes(r.batch_stride_a ? r.batch : 1, r.m, r.k);
   return need <= (256ull << 20) ? need : 0;
 }
@@ -470,7 +505,7 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
   {
     GemvParams g;
     if (gemv_params_for(op, r, route, &g)) {
-      launch_gemv_f16w(g, ctx_->sm_count, slot.status, stream);
+      launch_gemv_f16w(*ctx_, g, gemv_workspace(slot), stream);
       return;
     }
   }
@@ -480,6 +515,11 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
   if (route.splits > 1) {
     p.splits = route.splits;
     float *scratch = static_cast<float *>(slot.scratch);
+    const SplitK2TensorPlan tplan = splitk2_plan_for(p, route.splits);
+    if (tplan.eligible) {
+      launch_splitk2_tensor(*ctx_, p, tplan, scratch, slot.status, stream);
+      return;
+    }
     launch_splitk2_stage1(p, spec.tile_m, scratch, stream);
     launch_splitk2_reduce(scratch, p.c, (uint64_t)r.batch * r.m * r.n, (uint64_t)r.m * r.n,
                           route.splits, stream);
@@ -516,12 +556,7 @@ RunStats Executor::timed(Slot &slot, size_t n_calls, uint64_t flops,
   record(slot.stream);
   TA_CUDA(cudaEventRecord(slot.ev_end, slot.stream));
   TA_CUDA(cudaStreamSynchronize(slot.stream));
-  uint32_t status = 0;
-  TA_CUDA(cudaMemcpy(&status, slot.status, sizeof(status), cudaMemcpyDeviceToHost));
-  if (status) {
-    cudaMemset(slot.status, 0, sizeof(uint32_t));
-    fail_device_status(status);
-  }
+  check_status_word(slot.status_host);
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, slot.ev_begin, slot.ev_end));
   RunStats st;
@@ -568,7 +603,9 @@ RunStats Executor::run_ops_impl(const std::vector<MatmulOp> &ops, bool graph) {
       std::lock_guard<std::mutex> lk(tune_mu_);
       known = tuned_.count(TuneKey{r.batch, r.m, r.n, r.k, r.b_f16}) != 0;
     }
-    if (plain && !known && !r.b_f16 && selection_ == -2) tune_shape(r.batch, r.m, r.n, r.k);
+    // row-GEMV shapes (f16 B, M <= 8) are a route of their own and are not tuned
+    if (plain && !known && selection_ == -2 && !r.a_f16 && !ops[0].packed_b && !(r.b_f16 && r.m <= 8))
+      tune_shape(r.batch, r.m, r.n, r.k, r.b_f16);
   }
   std::vector<Route> routes;
   routes.reserve(ops.size());
@@ -576,9 +613,7 @@ RunStats Executor::run_ops_impl(const std::vector<MatmulOp> &ops, bool graph) {
   for (size_t i = 0; i < ops.size(); ++i) {
     // split-K2 auto route only for a lone plain op (dispatch.rs:171-176)
     routes.push_back(plan_op(ops[i], resolved[i], ops.size() == 1));
-    if (routes.back().splits > 1)
-      scratch_bytes = std::max(scratch_bytes, (size_t)resolved[i].batch * routes.back().splits *
-                                                  resolved[i].m * resolved[i].n * 4);
+    scratch_bytes = std::max(scratch_bytes, splitk2_scratch_bytes(ops[i], resolved[i], routes.back().splits));
     scratch_bytes = std::max(scratch_bytes, op_scratch_bytes(resolved[i], routes.back()));
   }
   Slot &slot = checkout_slot();
@@ -631,7 +666,7 @@ RunStats Executor::run_matmuls_split_k2(const std::vector<MatmulCall> &calls, ui
       route.kernel = kernel_index_by_name(name);
       route.splits = s;
       any_split = true;
-      const uint64_t bytes = (uint64_t)r.batch * s * r.m * r.n * 4;
+      const uint64_t bytes = splitk2_scratch_bytes(ops[i], r, s);
       if (bytes > (4ull << 30)) fail("split-K2 scratch of %llu bytes exceeds the 4 GiB cap", (unsigned long long)bytes);
       scratch_bytes = std::max(scratch_bytes, (size_t)bytes);
     }
@@ -643,9 +678,7 @@ RunStats Executor::run_matmuls_split_k2(const std::vector<MatmulCall> &calls, ui
   if (calls.size() > 1 && scratch_bytes) {
     // ops in one submission share the slot scratch: give each its own region
     size_t total = 0;
-    for (size_t i = 0; i < calls.size(); ++i)
-      if (routes[i].splits > 1)
-        total += (size_t)resolved[i].batch * routes[i].splits * resolved[i].m * resolved[i].n * 4;
+    for (size_t i = 0; i < calls.size(); ++i) total += splitk2_scratch_bytes(ops[i], resolved[i], routes[i].splits);
     scratch_bytes = total;
   }
   ctx_->make_current();
@@ -691,22 +724,40 @@ RunStats Executor::swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &
   ctx_->make_current();
   Slot &slot = checkout_slot();
   SlotGuard guard(*this, slot);
-  return timed(slot, 1, 2 * r.total_flops, [&](cudaStream_t s) { launch_gemv_f16w(g, ctx_->sm_count, slot.status, s); });
+  if (gemv_routes_to_umma(g)) ensure_scratch(slot, gemv_umma_scratch_bytes(g.n, g.k, true, ctx_->sm_count));
+  return timed(slot, 1, 2 * r.total_flops, [&](cudaStream_t s) { launch_gemv_f16w(*ctx_, g, gemv_workspace(slot), s); });
 }
 
 // ------------------------------------------------------------------ measured tuner
-// (src/executor/tuning.rs:18-313): one warm launch, round 0 discarded, then
-// interleaved measured rounds in alternating order, median per candidate; a
-// challenger must beat the heuristic pick by more than 2 %.
-void Executor::tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
+// (src/executor/tuning.rs:18-313): one clock-warming launch, then round 0 (discarded) plus R
+// measured rounds over all candidates, interleaved in the alternating order of `tune_candidate_at`
+// so that clock drift biases no kernel; median per candidate; the heuristic's pick stays unless a
+// challenger beats it by more than 2 %; then the split-K2 probe {4 .. 64} against the winner.
+std::vector<int> Executor::tune_candidates(uint32_t m, uint32_t n, uint32_t k, bool b_f16) const {
+  std::vector<int> out;
+  const bool tma_ok = (k % 4 == 0) && (n % 4 == 0), umma_ok = (k % 4 == 0) && (n % 8 == 0);
+  for (size_t i = 0; i < KERNEL_SPEC_COUNT; ++i) {
+    const KernelSpec &spec = KERNEL_SPECS[i];
+    if (spec.weights_f16 != b_f16) continue;
+    // row kernels, packed layouts and the split-K stage-1 kernels are routes of their own
+    // (src/pipeline/mod.rs:491-535 leaves the same families out)
+    if (spec.family == Family::RowGemv || spec.family == Family::SplitK2) continue;
+    if (spec.family == Family::Tf32x3 && (!tma_ok || m < 33)) continue;
+    if (spec.family == Family::F16wUmma && (!umma_ok || m < 32)) continue;
+    out.push_back((int)i);
+  }
+  return out;
+}
+
+void Executor::tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16) {
   {
     std::lock_guard<std::mutex> lk(tune_mu_);
-    if (tuned_.count(TuneKey{batch, m, n, k, false})) return;
+    if (tuned_.count(TuneKey{batch, m, n, k, b_f16})) return;
   }
   ctx_->make_current();
   const uint32_t sa[3] = {batch, m, k}, sb[2] = {k, n}, sc[3] = {batch, m, n};
   Tensor a = Tensor::uninit_device(ctx_, sa, 3, DType::F32);
-  Tensor b = Tensor::uninit_device(ctx_, sb, 2, DType::F32);
+  Tensor b = Tensor::uninit_device(ctx_, sb, 2, b_f16 ? DType::F16 : DType::F32);
   Tensor c = Tensor::uninit_device(ctx_, sc, 3, DType::F32);
   TA_CUDA(cudaMemset(a.ptr(), 0, a.size_bytes()));
   TA_CUDA(cudaMemset(b.ptr(), 0, b.size_bytes()));
@@ -714,56 +765,74 @@ void Executor::tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k) {
   op.call = MatmulCall{&a, &b, &c, 1.0f, false};
   const ResolvedMatmul r = ResolvedMatmul::from_op(op);
 
-  std::vector<Route> cands;
-  const int heuristic = heuristic_kernel(batch, m, n, k, false, ctx_->sm_count);
-  cands.push_back(Route{heuristic, 0});
-  for (const char *name : {"tf32x3_m128n256", "tf32x3_m128n128", "tf32x3_m256n256", "ffma_m128n128", "ffma_m64n64"}) {
-    const int idx = idx_of(name);
-    if (idx == heuristic) continue;
-    if (KERNEL_SPECS[idx].family == Family::Tf32x3 && (k % 4 || n % 4)) continue;
-    cands.push_back(Route{idx, 0});
-  }
-  const char *sk_name;
-  uint32_t sk_tile[3];
-  splitk2_stage1_tile(m, n, &sk_name, sk_tile);
-  for (uint32_t s : {4u, 8u, 16u, 32u, 64u})
-    if (k / s >= 128 && (uint64_t)batch * s <= 65535 && (uint64_t)batch * s * m * n * 4 <= (256ull << 20))
-      cands.push_back(Route{idx_of(sk_name), s});
+  const std::vector<int> cands = tune_candidates(m, n, k, b_f16);
+  if (cands.empty()) fail("no tunable kernel fits this shape");
+  int heuristic = heuristic_kernel(batch, m, n, k, b_f16, ctx_->sm_count);
+  // fewer rounds for expensive shapes (src/executor/tuning.rs:105-108, scaled to this device)
+  const double est_ms = (double)r.total_flops / 200e12 * 1e3;
+  const uint32_t rounds = est_ms > 8.0 ? 2 : 4;
 
-  Slot &slot = checkout_slot();
-  SlotGuard g(*this, slot);
-  size_t scratch = 0;
-  for (const Route &rt : cands)
-    if (rt.splits > 1) scratch = std::max(scratch, (size_t)batch * rt.splits * m * n * 4);
-  if (scratch) ensure_scratch(slot, scratch);
-
-  const int rounds = 5;  // round 0 discarded
-  std::vector<std::vector<double>> times(cands.size());
-  for (int round = 0; round < rounds; ++round) {
+  std::vector<std::vector<uint64_t>> samples(cands.size());
+  uint64_t winner_ns = 0;
+  int winner = -1;
+  {
+    Slot &slot = checkout_slot();
+    SlotGuard g(*this, slot);
+    size_t scratch = 0;
+    for (int ci : cands) scratch = std::max(scratch, op_scratch_bytes(r, Route{ci, 0}));
+    if (scratch) ensure_scratch(slot, scratch);
+    auto run_forced = [&](int kernel) {
+      const Route rt{kernel, 0};
+      return *timed(slot, 1, r.total_flops, [&](cudaStream_t st) { enqueue_op(op, r, rt, slot, st); }).gpu_time_ns;
+    };
+    const bool heur_in = std::find(cands.begin(), cands.end(), heuristic) != cands.end();
+    run_forced(heur_in ? heuristic : cands[0]);   // spin the clocks up before anything is timed
+    for (uint32_t round = 0; round <= rounds; ++round)
+      for (size_t offset = 0; offset < cands.size(); ++offset) {
+        const size_t ci = tune_candidate_at(cands.size(), round, offset);
+        const uint64_t ns = run_forced(cands[ci]);
+        if (round > 0) samples[ci].push_back(ns);   // round 0 is warm-up
+      }
+    std::optional<uint64_t> heur_ns;
     for (size_t ci = 0; ci < cands.size(); ++ci) {
-      const size_t i = (round & 1) ? cands.size() - 1 - ci : ci;
-      RunStats st = timed(slot, 1, r.total_flops,
-                          [&](cudaStream_t s) { enqueue_op(op, r, cands[i], slot, s); });
-      if (round > 0) times[i].push_back((double)*st.gpu_time_ns);
+      const auto med = tune_median(samples[ci]);
+      if (!med) continue;
+      if (cands[ci] == heuristic) heur_ns = med;
+      if (winner < 0 || *med < winner_ns) {
+        winner = cands[ci];
+        winner_ns = *med;
+      }
     }
-  }
-  auto median = [](std::vector<double> v) {
-    std::sort(v.begin(), v.end());
-    return v.size() % 2 ? v[v.size() / 2] : 0.5 * (v[v.size() / 2 - 1] + v[v.size() / 2]);
-  };
-  size_t best = 0;
-  const double base = median(times[0]);
-  double best_t = base;
-  for (size_t i = 1; i < cands.size(); ++i) {
-    const double t = median(times[i]);
-    if (t < best_t && t < base * 0.98) {
-      best_t = t;
-      best = i;
+    if (winner < 0) fail("no candidate produced a measurement");
+    if (heur_ns && (double)winner_ns >= (double)*heur_ns * 0.98) {
+      winner = heuristic;
+      winner_ns = *heur_ns;
     }
+  }   // the split-K2 probe checks out its own slot
+
+  // Reduction-strategy pass on deep-K, few-tile shapes (src/executor/tuning.rs:214-262).
+  uint32_t best_splits = 0;
+  const uint64_t tiles = (uint64_t)((m + 127) / 128) * ((n + 127) / 128) * batch;
+  if (!b_f16 && k >= 1024 && tiles <= 48) {
+    uint64_t best_ns = 0;
+    for (uint32_t sp : {4u, 8u, 16u, 32u, 64u}) {
+      if (k / sp < 128 || (uint64_t)batch * sp > 65535 || (uint64_t)batch * sp * m * n * 4 > (256ull << 20)) continue;
+      std::vector<uint64_t> v;
+      for (uint32_t round = 0; round <= rounds; ++round) {
+        const RunStats st = run_matmuls_split_k2({op.call}, sp);
+        if (round > 0 && st.gpu_time_ns) v.push_back(*st.gpu_time_ns);
+      }
+      const auto med = tune_median(v);
+      if (med && (!best_splits || *med < best_ns)) {
+        best_ns = *med;
+        best_splits = sp;
+      }
+    }
+    if (best_splits && !((double)best_ns < (double)winner_ns * 0.98)) best_splits = 0;
   }
   {
     std::lock_guard<std::mutex> lk(tune_mu_);
-    tuned_[TuneKey{batch, m, n, k, false}] = TunedEntry{cands[best].kernel, cands[best].splits};
+    tuned_[TuneKey{batch, m, n, k, b_f16}] = TunedEntry{winner, best_splits};
     save_tuned(tune_path_, tuned_);
   }
 }
@@ -796,14 +865,17 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
   size_t scratch_bytes = 0;
   for (size_t i = 0; i < ops.size(); ++i) scratch_bytes = std::max(scratch_bytes, exec.op_scratch_bytes(resolved[i], routes[i]));
   if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));
-  // Tensor maps and attribute setup happen on first launch of each kernel: run
-  // the batch once eagerly so capture sees only launches.
+  alloc_status_word(&prep->status_host, &prep->status);
+  // Captured directly, nothing runs at create time: encoding tensor maps and setting function
+  // attributes are host calls, which a stream capture allows.
   Slot &real_slot = exec.checkout_slot();
   {
     SlotGuard g(exec, real_slot);
-    Slot slot = real_slot;            // captured launches must point at this object's own scratch
+    Slot slot = real_slot;            // captured launches must point at this object's own scratch and status word
     slot.scratch = prep->scratch;
     slot.scratch_bytes = scratch_bytes;
+    slot.status = prep->status;
+    slot.status_host = prep->status_host;
     TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
     try {
       for (size_t i = 0; i < ops.size(); ++i)
@@ -831,6 +903,7 @@ PreparedOps::~PreparedOps() {
   if (stream) cudaStreamDestroy(stream);
   if (counters) cudaFree(counters);
   if (scratch) cudaFree(scratch);
+  free_status_word(status_host);
 }
 
 void PreparedOps::submit() {
@@ -847,6 +920,8 @@ RunStats PreparedOps::wait() {
   exec->context()->make_current();
   TA_CUDA(cudaStreamSynchronize(stream));
   in_flight = false;
+  // a kernel of the replayed graph that gave up on a bounded wait reports here, as for an eager run
+  if (status_host) check_status_word(status_host);
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, ev_begin, ev_end));
   RunStats st;

@@ -12,13 +12,37 @@ def chunk_seed(seed, tensor_id, chunk):
     return ((seed * 1000003 + tensor_id) * 4096 + chunk) & 0xFFFFFFFFFFFFFFFF
 
 
-def gen_weight(orc, seed, tensor_id, rows, cols, sigma):
+def gen_weight(orc, seed, tensor_id, rows, cols, sigma, keep_f16=False):
+    """Tensor `tensor_id` of the documented seed stream, rounded to f16.  keep_f16 returns the
+    float16 array itself (a quarter of the memory; every value converts to f64 exactly)."""
     n = rows * cols
-    out = np.empty(n, dtype=np.float32)
-    for c in range((n + CHUNK - 1) // CHUNK):
+    out = np.empty(n, dtype=np.float16)
+
+    def chunk(c):
         lo, hi = c * CHUNK, min(n, (c + 1) * CHUNK)
-        out[lo:hi] = orc.fill_normal((hi - lo,), chunk_seed(seed, tensor_id, c), sigma)
-    return out.astype(np.float16).astype(np.float64).reshape(rows, cols)
+        out[lo:hi] = orc.fill_normal((hi - lo,), chunk_seed(seed, tensor_id, c), sigma).astype(np.float16)
+
+    chunks = range((n + CHUNK - 1) // CHUNK)
+    if len(chunks) > 4:      # the C generator releases the GIL: chunks in parallel
+        from concurrent.futures import ThreadPoolExecutor
+        import os
+        with ThreadPoolExecutor(max_workers=min(32, os.cpu_count() or 1)) as pool:
+            list(pool.map(chunk, chunks))
+    else:
+        for c in chunks:
+            chunk(c)
+    out = out.reshape(rows, cols)
+    return out if keep_f16 else out.astype(np.float64)
+
+
+def lcg_tokens(n, vocab, seed=12345):
+    """Prompt ids from the reference's LcgRng stream (tools/test-support/src/lib.rs:20-55)."""
+    s = (seed * 0x9E3779B97F4A7C15 | 1) & 0xFFFFFFFFFFFFFFFF
+    out = []
+    for _ in range(n):
+        s = (s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        out.append((s >> 33) % vocab)
+    return out
 
 
 def gen_norm(orc, seed, tensor_id, n, jitter):
@@ -29,26 +53,29 @@ def gen_norm(orc, seed, tensor_id, n, jitter):
 
 
 class RefLlama:
-    def __init__(self, orc, cfg):
+    def __init__(self, orc, cfg, lean=False):
+        """lean=True keeps the weights as float16 arrays and widens one matrix at a time while it is
+        used: the 22-layer configuration then needs 2.2 GB instead of 8.8 GB of host memory."""
         self.cfg = c = cfg
         s, sg = c.seed, c.weight_sigma
         kv_dim = c.kv_heads * c.head_dim
-        self.embd = gen_weight(orc, s, 0, c.vocab, c.embd, sg)
+        w = lambda tid, r, cc: gen_weight(orc, s, tid, r, cc, sg, keep_f16=lean)  # noqa: E731
+        self.embd = w(0, c.vocab, c.embd)
         self.output_norm = gen_norm(orc, s, 1, c.embd, c.norm_jitter)
-        self.lm_head = gen_weight(orc, s, 2, c.embd, c.vocab, sg)
+        self.lm_head = w(2, c.embd, c.vocab)
         self.layers = []
         for li in range(c.layers):
             b = 16 + 16 * li
             self.layers.append(dict(
                 attn_norm=gen_norm(orc, s, b + 0, c.embd, c.norm_jitter),
-                wq=gen_weight(orc, s, b + 1, c.embd, c.embd, sg),
-                wk=gen_weight(orc, s, b + 2, c.embd, kv_dim, sg),
-                wv=gen_weight(orc, s, b + 3, c.embd, kv_dim, sg),
-                wo=gen_weight(orc, s, b + 4, c.embd, c.embd, sg),
+                wq=w(b + 1, c.embd, c.embd),
+                wk=w(b + 2, c.embd, kv_dim),
+                wv=w(b + 3, c.embd, kv_dim),
+                wo=w(b + 4, c.embd, c.embd),
                 ffn_norm=gen_norm(orc, s, b + 5, c.embd, c.norm_jitter),
-                w_gate=gen_weight(orc, s, b + 6, c.embd, c.ffn, sg),
-                w_up=gen_weight(orc, s, b + 7, c.embd, c.ffn, sg),
-                w_down=gen_weight(orc, s, b + 8, c.ffn, c.embd, sg),
+                w_gate=w(b + 6, c.embd, c.ffn),
+                w_up=w(b + 7, c.embd, c.ffn),
+                w_down=w(b + 8, c.ffn, c.embd),
                 k=np.zeros((0, c.kv_heads, c.head_dim)), v=np.zeros((0, c.kv_heads, c.head_dim))))
         half = c.head_dim // 2
         p = np.arange(c.t_max, dtype=np.float64)[:, None]
@@ -72,19 +99,33 @@ class RefLlama:
         a, b = xh[..., 0], xh[..., 1]
         return np.stack([a * cos - b * sin, a * sin + b * cos], axis=-1).reshape(t, heads * c.head_dim)
 
+    def reset(self):
+        c = self.cfg
+        for L in self.layers:
+            L["k"] = np.zeros((0, c.kv_heads, c.head_dim))
+            L["v"] = np.zeros((0, c.kv_heads, c.head_dim))
+        self.pos = 0
+
     def forward(self, tokens):
         """Consumes tokens at the current position; returns logits of the last one ([vocab])."""
+        return self.forward_positions(tokens, 1)[0]
+
+    def forward_positions(self, tokens, n_last):
+        """Consumes tokens at the current position; returns the logits of the last n_last of them
+        ([n_last, vocab]).  Attention is causal, so row i equals what a token-by-token run that was
+        fed tokens[: i + 1] would have produced at that position (teacher forcing in one pass)."""
         c = self.cfg
+        W = lambda a: a.astype(np.float64) if a.dtype != np.float64 else a  # noqa: E731
         t, pos0 = len(tokens), self.pos
-        x = self.embd[np.asarray(tokens, dtype=np.int64)]
+        x = W(self.embd[np.asarray(tokens, dtype=np.int64)])
         group = c.heads // c.kv_heads
         scale = float(np.float32(1.0) / np.sqrt(np.float32(c.head_dim)))
         f16 = lambda a: a.astype(np.float32).astype(np.float16).astype(np.float64)  # noqa: E731
         for L in self.layers:
             xn = self._rms(x, L["attn_norm"])
-            q = self._rope(xn @ L["wq"], c.heads, pos0).reshape(t, c.heads, c.head_dim)
-            k = f16(self._rope(xn @ L["wk"], c.kv_heads, pos0)).reshape(t, c.kv_heads, c.head_dim)
-            v = f16(xn @ L["wv"]).reshape(t, c.kv_heads, c.head_dim)
+            q = self._rope(xn @ W(L["wq"]), c.heads, pos0).reshape(t, c.heads, c.head_dim)
+            k = f16(self._rope(xn @ W(L["wk"]), c.kv_heads, pos0)).reshape(t, c.kv_heads, c.head_dim)
+            v = f16(xn @ W(L["wv"])).reshape(t, c.kv_heads, c.head_dim)
             L["k"] = np.concatenate([L["k"], k]); L["v"] = np.concatenate([L["v"], v])
             K, V = L["k"], L["v"]
             out = np.empty((t, c.heads, c.head_dim))
@@ -97,12 +138,12 @@ class RefLlama:
                 s = s - s.max(axis=1, keepdims=True)
                 p = np.exp(s)
                 out[:, h, :] = (p @ V[:, g, :]) / p.sum(axis=1, keepdims=True)
-            o = out.reshape(t, c.embd) @ L["wo"] + x
+            o = out.reshape(t, c.embd) @ W(L["wo"]) + x
             on = self._rms(o, L["ffn_norm"])
-            up = on @ L["w_up"]
-            gate = on @ L["w_gate"]
+            up = on @ W(L["w_up"])
+            gate = on @ W(L["w_gate"])
             act = gate / (1.0 + np.exp(-gate)) * up
-            x = act @ L["w_down"] + o
+            x = act @ W(L["w_down"]) + o
         self.pos += t
-        last = self._rms(x[-1:], self.output_norm)
-        return (last @ self.lm_head)[0]
+        last = self._rms(x[-n_last:], self.output_norm)
+        return last @ W(self.lm_head)

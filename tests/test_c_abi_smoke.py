@@ -29,3 +29,19 @@ def test_c_program_runs(tmp_path, ta):
     out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "smoke OK" in out.stdout
+
+
+@pytest.mark.gpu
+def test_reference_c_smoke_runs_unchanged(orc):
+    """The reference's own acceptance program (examples/c_smoke.c:21-244), compiled unchanged from
+    the reference tree by `make -C oracle ref_c_smoke` (the build step does it wherever that tree
+    exists; the binary travels with the built libraries), passes against this library."""
+    exe = orc.build_ref_c_smoke()
+    if exe is None:
+        pytest.skip("oracle/_ref/c_smoke was not built: the reference tree is not present on this machine")
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "tensor-ash C smoke OK" in out.stdout
+    for line in ("plain matmul OK", "bias+silu op OK", "prepared replay OK", "f16 matmul OK", "rms_norm OK",
+                 "softmax(prefix=2) OK", "copy_strided transpose OK"):
+        assert line in out.stdout, out.stdout

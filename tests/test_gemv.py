@@ -220,25 +220,69 @@ def test_rejections(gpu, orc):
                                      store=ta.MatmulStore(ta.StoreKind.SCATTER, head_dim=64, dst=c16))])
 
 
-def test_tensor_core_rows_refuse_activations_beyond_the_f16_range(gpu, orc, monkeypatch):
-    """5..8 rows run on mma.sync with x split into two f16 halves; an activation above 65504 cannot
-    be split and must fail loudly, and TA_GEMV_MMA=0 keeps such inputs on the f32 FMA path."""
+# ---- 3..8 rows: the tensor-memory kernel (tcgen05 with the weights as the A operand)
+@pytest.mark.parametrize("k,n,packed", [(2048, 2048, True), (2048, 5632, True), (5632, 2048, False), (4096, 1024, True),
+                                        (1008, 200, False), (64, 32, True), (16384, 64, True), (2048, 32000, True),
+                                        (11008, 4096, True), (80, 136, False)])
+def test_umma_rows_match_the_oracle(gpu, orc, k, n, packed):
+    """Packed tiles of 32 and 64, row-major weights, column counts that leave partial groups, K that is
+    not a multiple of the ring's 64-row box, K long enough for many K slices."""
     ta, ctx, ex = gpu
-    m, k, n = 8, 512, 256
-    hx = orc.fill_det(m * k, 71).reshape(m, k).astype(np.float32)
-    hx[3, 17] = 1.0e5
+    for m in (3, 5, 8):
+        x, hx = upload_det(ta, ctx, ex, orc, (m, k), 560 + m)
+        w, hw = make_weights(ta, ctx, ex, orc, k, n, 561, packed)
+        c = ta.Tensor.uninit_device(ctx, (m, n))
+        ex.upload(np.full(m * n, 9.0, np.float32), c)
+        ex.run_ops_ex([ta.MatmulOpEx(ta.MatmulCall(x, w, c), packed_b=packed)])
+        first = ex.download(c).copy()
+        check(orc, first, orc.cpu_bmm(hx, hw, 1, m, n, k), k, f"{m}x{n}x{k} packed={packed}")
+        ex.run_ops_ex([ta.MatmulOpEx(ta.MatmulCall(x, w, c), packed_b=packed)])
+        assert ex.download(c).tobytes() == first.tobytes(), "two runs differ"
+
+
+def test_umma_rows_full_epilogue_and_accumulate(gpu, orc):
+    """alpha, accumulate, bias, GELU and AddScaled in one op; then normed-A with SiLU * Mul (the fused
+    RMSNorm statistic is summed over the K slices of several CTAs)."""
+    ta, ctx, ex = gpu
+    m, k, n = 6, 4096, 1536
+    x, hx = upload_det(ta, ctx, ex, orc, (m, k), 570)
+    w, hw = make_weights(ta, ctx, ex, orc, k, n, 571, True)
+    bias, hb = upload_det(ta, ctx, ex, orc, (n,), 572)
+    d, hd = upload_det(ta, ctx, ex, orc, (m, n), 573)
+    c, hc = upload_det(ta, ctx, ex, orc, (m, n), 574)
+    ex.run_ops_ex([ta.MatmulOpEx(ta.MatmulCall(x, w, c, 0.5, True),
+                                 ta.Epilogue(bias, ta.Activation.GELU, ta.Binary.ADD_SCALED, d, 0.25), packed_b=True)])
+    ref = orc.cpu_epilogue(orc.cpu_bmm(hx, hw, 1, m, n, k, alpha=0.5, c_init=hc, accumulate=True), 1, m, n,
+                           bias=hb, act="gelu", binary="add_scaled", d=hd, beta=0.25)
+    check(orc, ex.download(c), ref, k, "alpha + accumulate + bias + gelu + add_scaled")
+    nw = ta.Tensor.uninit_device(ctx, (k,))
+    hnw = 1.0 + 0.1 * orc.fill_det(k, 575)
+    ex.upload(hnw, nw)
+    ex.run_ops_ex([ta.MatmulOpEx(ta.MatmulCall(x, w, c), ta.Epilogue(activation=ta.Activation.SILU, binary=ta.Binary.MUL, d=d),
+                                 packed_b=True, normed_a=(nw, 1e-5))])
+    xn = orc.cpu_rmsnorm(hx.reshape(m, k), hnw, 1e-5)
+    ref = orc.cpu_epilogue(orc.cpu_bmm(xn, hw, 1, m, n, k), 1, m, n, act="silu", binary="mul", d=hd)
+    check(orc, ex.download(c), ref, k, "normed-A silu*mul M=6")
+
+
+def test_umma_rows_take_any_activation_range(gpu, orc):
+    """The f16 split of x is taken after a per-row power-of-two scaling of each K slice, so rows with
+    huge, tiny and mixed magnitudes all keep about 22 bits: no activation range is excluded."""
+    ta, ctx, ex = gpu
+    m, k, n = 8, 2048, 256
+    hx = orc.fill_det(m * k, 580).reshape(m, k).astype(np.float32)
+    hx[0] *= 1.0e6          # far beyond the f16 range
+    hx[1] *= 1.0e-9         # far below the f16 normal range
+    hx[2, 17] = 1.0e5       # one outlier in an ordinary row
+    hx[3] = 0.0
     x = ta.Tensor.uninit_device(ctx, (m, k))
     ex.upload(hx.ravel(), x)
-    w, hw = make_weights(ta, ctx, ex, orc, k, n, 72, False)
+    w, hw = make_weights(ta, ctx, ex, orc, k, n, 581, False)
     c = ta.Tensor.uninit_device(ctx, (m, n))
-    with pytest.raises(ta.TensorAshError, match="exceeds the f16 range"):
-        ex.run_matmuls([ta.MatmulCall(x, w, c)])
-    monkeypatch.setenv("TA_GEMV_MMA", "0")
     ex.run_matmuls([ta.MatmulCall(x, w, c)])
-    ref = orc.cpu_bmm(hx, hw, 1, m, n, k)
-    check(orc, ex.download(c), ref, k, "f32 path with a large activation")
-    monkeypatch.delenv("TA_GEMV_MMA")
-    hx[3, 17] = 0.5
-    ex.upload(hx.ravel(), x)
-    ex.run_matmuls([ta.MatmulCall(x, w, c)])            # the status word was cleared by the failed call
-    check(orc, ex.download(c), orc.cpu_bmm(hx, hw, 1, m, n, k), k, "tensor-core rows after a refused call")
+    got = ex.download(c).reshape(m, n)
+    ref = orc.cpu_bmm(hx, hw, 1, m, n, k).reshape(m, n)
+    for row in range(m):
+        scale = max(float(np.abs(ref[row]).max()), 1e-30)
+        assert np.abs(got[row] - ref[row]).max() <= 2e-3 * scale, f"row {row}"
+    assert not got[3].any()

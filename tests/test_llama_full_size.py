@@ -1,0 +1,110 @@
+"""Configuration 5 at its own size (22 layers, hidden 2048, 32 q / 4 kv heads, SwiGLU 5632,
+vocabulary 32000, random-init f16 weights, f16 KV cache) against the float64 host forward.
+
+The criterion is the reference's for greedy decoding (tests/correctness/decoder.rs:344-416 and the
+T7 token gate of tools/ml-bench/src/bench/thesis/model_theses.rs:460-531): logits inside the path's
+tolerance, and identical greedy tokens wherever the float64 top-2 margin is larger than the logit
+error the path may carry.  Teacher forcing: the host forward is fed the device's own tokens in ONE
+causal pass over prompt + generated tokens, so a near-tie cannot derail the comparison after it.
+
+Tolerances (relative to max |logit| of the position):
+  * prefill of 512 tokens: projections run on the f16 tensor-core GEMM, which rounds activations
+    to f16 on the way in -- the f16-weight bound 2e-3;
+  * greedy steps after that prefill: f32 activations through the GEMV path, but they attend over
+    the KV cache the prefill wrote, so they inherit its bound, 2e-3;
+  * the decode graph alone (a short prompt fed token by token): 2e-4.
+The 128 tokens must also equal tests/golden/llama_config5_tokens.json, the list the benchmark
+checks at every tensor-parallel width.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from llama_ref import RefLlama, lcg_tokens
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llama_config5_tokens.json")
+PREFILL_TOL, DECODE_TOL = 2e-3, 2e-4
+N_PROMPT, N_DECODE = 512, 128
+
+
+@pytest.fixture(scope="module")
+def full(ta, orc):
+    ctx = ta.Context(False, "index:0")
+    ex = ta.Executor(ctx, 2, 1024)
+    cfg = ta.LlamaConfig(t_max=1024, seed=5)          # the benchmark's model: BASELINE configs[4]
+    model = ta.Llama(ex, cfg)
+    ref = RefLlama(orc, cfg, lean=True)
+    yield ta, model, ref, cfg
+    model.close()
+    ex.close()
+    ctx.close()
+
+
+def rel_err(got, want):
+    return float(np.abs(got.astype(np.float64) - want).max() / np.abs(want).max())
+
+
+def margin_rel(logits):
+    top = np.sort(logits)[-2:]
+    return float((top[1] - top[0]) / np.abs(logits).max())
+
+
+def test_prefill_512_then_128_greedy_tokens_match_float64(full):
+    ta, model, ref, cfg = full
+    prompt = lcg_tokens(N_PROMPT, cfg.vocab)
+    model.reset()
+    nxt, _ = model.prefill(prompt)
+    logits_prefill = model.logits()
+    toks, _ = model.decode(nxt, N_DECODE)
+    logits_last = model.logits()
+    assert model.position == N_PROMPT + N_DECODE
+
+    # one causal pass over what the device consumed: row i = logits after prompt + i generated tokens
+    ref.reset()
+    fed = prompt + [nxt] + toks[:-1]
+    want = ref.forward_positions(fed, N_DECODE + 1)
+
+    e_prefill = rel_err(logits_prefill, want[0])
+    e_last = rel_err(logits_last, want[N_DECODE])
+    assert e_prefill <= PREFILL_TOL, f"prefill logits rel err {e_prefill:.3e}"
+    assert e_last <= PREFILL_TOL, f"logits after {N_DECODE} greedy steps rel err {e_last:.3e}"
+
+    gate = 2.0 * PREFILL_TOL          # a margin the path's logit error cannot flip
+    got = [nxt] + toks
+    below, wrong = [], []
+    for i in range(N_DECODE + 1):
+        if margin_rel(want[i]) <= gate:
+            below.append(i)
+        elif got[i] != int(np.argmax(want[i])):
+            wrong.append((i, got[i], int(np.argmax(want[i]))))
+    print(f"config 5: prefill rel err {e_prefill:.2e}, last-step rel err {e_last:.2e}, "
+          f"{len(below)} of {N_DECODE + 1} steps under the margin gate {gate:.0e}: {below}")
+    assert not wrong, f"greedy tokens differ from the float64 forward at margin-qualified steps: {wrong}"
+
+    with open(GOLDEN) as f:
+        golden = json.load(f)
+    assert golden["prompt_seed"] == 12345 and golden["n_prompt"] == N_PROMPT
+    assert [nxt] + toks == golden["tokens"], "token stream differs from tests/golden/llama_config5_tokens.json"
+
+
+def test_decode_graph_alone_matches_float64_at_full_size(full):
+    """16 prompt tokens fed one by one through the prepared decode graph (no tensor-core prefill in
+    front of it): f32 activations end to end, tolerance 2e-4."""
+    ta, model, ref, cfg = full
+    prompt = lcg_tokens(16, cfg.vocab, seed=777)
+    model.reset()
+    ref.reset()
+    want = ref.forward_positions(prompt, len(prompt))
+    worst = 0.0
+    for i, tok in enumerate(prompt):
+        out, _ = model.decode(tok, 1)
+        e = rel_err(model.logits(), want[i])
+        worst = max(worst, e)
+        if margin_rel(want[i]) > 10 * DECODE_TOL:
+            assert out[0] == int(np.argmax(want[i])), f"position {i}"
+    print(f"config 5 decode graph alone: worst logits rel err {worst:.2e}")
+    assert worst <= DECODE_TOL, f"decode-graph logits rel err {worst:.3e}"

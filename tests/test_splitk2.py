@@ -27,13 +27,32 @@ def test_splitk2_matches_cpu(gpu, orc, case):
     assert e <= 2.0 * orc.tolerance(case[3]), f"{case}: err {e} at {idx}"
 
 
-def test_splitk2_is_deterministic_and_matches_shader_order(gpu, orc):
-    got1, _, (ha, hb) = run_case(gpu, orc, 1, 128, 128, 4096, 16, 1.0)
-    got2, _, _ = run_case(gpu, orc, 1, 128, 128, 4096, 16, 1.0)
+def test_splitk2_simt_stage1_is_deterministic_and_matches_shader_order(gpu, orc):
+    """An executor whose kernel selection names the split-K2 stage-1 kernel keeps the SIMT stage 1:
+    the same per-split fma chains and the same ordered plane sum as the reference shaders, bit for bit."""
+    ta, ctx, _ = gpu
+    ex = ta.Executor(ctx, 2, 8, "split_k2_m128n128")
+    pinned = (ta, ctx, ex)
+    got1, _, (ha, hb) = run_case(pinned, orc, 1, 128, 128, 4096, 16, 1.0)
+    got2, _, _ = run_case(pinned, orc, 1, 128, 128, 4096, 16, 1.0)
     assert got1.tobytes() == got2.tobytes(), "split-K2 results differ across runs"
-    # same per-split fma chains and the same ordered plane sum as the reference shaders
     emu = orc.splitk2_f32(ha, hb, 128, 128, 4096, 16)
     assert got1.tobytes() == emu.tobytes()
+    ex.close()
+
+
+@pytest.mark.parametrize("case", [(1, 128, 128, 4096, 16, 1.0), (1, 64, 64, 65536, 64, 1.0), (1, 64, 256, 65536, 4, 0.5),
+                                  (2, 96, 200, 8192, 8, 1.0), (1, 300, 72, 16384, 32, 1.0)])
+def test_splitk2_tensor_stage1_is_deterministic_and_within_the_bound(gpu, orc, case):
+    """The default route: stage 1 on the tensor cores (3xTF32) wherever K is a multiple of 16 * splits.
+    Fixed issue order and a fixed plane order in the reduce: two runs are bit-identical; the result
+    stays inside the reference's bound (tests/correctness/splitk2.rs:114-122) and inside 1e-5 of max|C|."""
+    got1, ref, _ = run_case(gpu, orc, *case)
+    got2, _, _ = run_case(gpu, orc, *case)
+    assert got1.tobytes() == got2.tobytes(), "split-K2 results differ across runs"
+    e, idx = orc.max_abs_err(got1, ref)
+    assert e <= 2.0 * orc.tolerance(case[3]), f"{case}: err {e} at {idx}"
+    assert e / float(np.abs(ref).max()) <= 1e-5, f"{case}: rel {e / float(np.abs(ref).max()):.3e}"
 
 
 def test_deep_k_config_sweep(gpu, orc):

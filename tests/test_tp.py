@@ -81,3 +81,14 @@ def test_sharded_llama_on_devices_matches_host_forward(ta, orc, world, port):
     for rc, out in outs:
         assert rc == 0, out
         assert "TP-GPU-OK" in out, out
+
+
+@pytest.mark.gpu
+def test_peer_exchange_wait_runs_out_and_recovers(ta):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    outs = run_workers("wait", 2, 29616)
+    for rc, out in outs:
+        assert rc == 0, out
+        assert "TP-WAIT-OK" in out, out

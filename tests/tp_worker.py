@@ -143,5 +143,48 @@ def main_gpu():
     print("TP-GPU-OK", rank)
 
 
+def main_wait():
+    """A bounded wait of the peer exchange runs out without faulting anything: rank 1 sits one
+    all-reduce out (a host-side choice, nothing of it is in flight), rank 0's kernel gives up after
+    5 ms, its call fails with the peer-wait message, and after a collective resync the next matched
+    all-reduce is correct on both ranks."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    ta = entry.load_package()
+    ctx = ta.Context(False, f"index:{rank}")
+    ex = ta.Executor(ctx, 2, 16)
+    comm = ta.Comm.from_torch_distributed(ctx)
+    n = 2048
+    t = ta.Tensor.uninit_device(ctx, (1, n))
+    mine = np.arange(n, dtype=np.float32) * (rank + 1)
+    ex.upload(mine, t)
+    ex.run_exec_ops([ta.ExecOp.all_reduce(t, comm)])                      # a matched call first
+    assert np.array_equal(ex.download(t), np.arange(n, dtype=np.float32) * 3)
+    dist.barrier()
+    comm.set_wait_limit_ns(5_000_000)
+    if rank == 0:
+        ex.upload(mine, t)
+        try:
+            ex.run_exec_ops([ta.ExecOp.all_reduce(t, comm)])
+            raise AssertionError("the unmatched all-reduce returned success")
+        except ta.TensorAshError as exc:
+            assert "wait for a peer rank" in str(exc), str(exc)
+    dist.barrier()                                                         # rank 1 learns of it on the host
+    comm.resync()
+    comm.set_wait_limit_ns(10_000_000_000)
+    ex.upload(mine, t)
+    ex.run_exec_ops([ta.ExecOp.all_reduce(t, comm)])
+    assert np.array_equal(ex.download(t), np.arange(n, dtype=np.float32) * 3), f"rank {rank}: sum after resync"
+    dist.barrier()
+    t.close()
+    comm.close()
+    ex.close()
+    dist.destroy_process_group()
+    print("TP-WAIT-OK", rank)
+
+
 if __name__ == "__main__":
-    (main_cpu if sys.argv[1] == "cpu" else main_gpu)()
+    {"cpu": main_cpu, "gpu": main_gpu, "wait": main_wait}[sys.argv[1]]()
