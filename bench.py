@@ -12,7 +12,14 @@ the tcgen05 3xTF32 kernel.
 Multi-GPU: independent batch planes partition with no collective.  Every rank
 owns one GPU and runs the full 32-plane workload on its own data (weak
 scaling); `value` is the flops all ranks completed divided by the slowest
-rank's device time.
+rank's device time.  The strong-scaling form of the same configuration (the 32
+planes cut into contiguous blocks of 32/N per GPU) is reported beside it under
+`extra_metrics.config2_strong`.
+
+Timed region: after a fixed burn-in (the same number of launches on every rank,
+reported as `burn_in_launches`; it brings every GPU to its power-capped clock
+and gives the clock sampler samples under load) exactly `--warmup` untimed
+steps run, then exactly `--steps` timed ones.
 
   python bench.py --gpus N --steps K --warmup W          this library
   python bench.py --impl reference ...                   the reference's CPU GEMM
@@ -39,6 +46,7 @@ METRIC = "fp32_batched_gemm_fused_epilogue_tflops"
 UNIT = "TFLOP/s"
 FLOPS_PER_STEP = 2 * BATCH * M * N * K
 WORKLOAD = "configs[1]: batched FP32 GEMM 32x2048x2048x2048, shared B, per-batch bias, silu, +R"
+BURN_IN_LAUNCHES = 220   # untimed launches before the warm-up steps, identical on every rank
 
 
 def measured_peaks():
@@ -130,12 +138,22 @@ def spot_check(ta_out: np.ndarray, host, samples: int = 64) -> float:
     return worst
 
 
+def host_threads() -> int:
+    """All cores of the host, whatever OMP_NUM_THREADS says (torchrun exports OMP_NUM_THREADS=1 to its
+    workers; only rank 0 runs the CPU legs, so it may use every core)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_baseline(budget_s: float = 12.0) -> dict:
     """The reference's test-suite CPU GEMM (f64-accumulating cpu_bmm, restated in
     oracle/ta_oracle.c) plus its epilogue, timed on this host's cores over a
     bounded sample of the same workload: `rows` rows of one batch plane."""
+    threads = host_threads()
+    os.environ["OMP_NUM_THREADS"] = str(threads)      # read by the OpenMP runtime when the oracle loads
     orc = entry.load_oracle()
-    threads = orc.num_threads()
     rng = np.random.default_rng(1)
     sig = np.float32(1.0 / np.sqrt(K))
     b = rng.standard_normal((K, N), dtype=np.float32) * sig
@@ -145,7 +163,7 @@ def cpu_baseline(budget_s: float = 12.0) -> dict:
         bias = rng.standard_normal((planes, N), dtype=np.float32) * sig
         r = rng.standard_normal((planes, rows, N), dtype=np.float32) * sig
         t0 = time.perf_counter()
-        c = orc.cpu_bmm(a, b, planes, rows, N, K, threads=0)
+        c = orc.cpu_bmm(a, b, planes, rows, N, K, threads=threads)
         orc.cpu_epilogue(c, planes, rows, N, bias=bias, act="silu", binary="add_scaled", d=r, beta=1.0)
         return time.perf_counter() - t0
 
@@ -161,6 +179,29 @@ def cpu_baseline(budget_s: float = 12.0) -> dict:
     return {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port",
             "sample": f"{planes} plane(s) x {rows} rows of the {BATCH} x {M} output rows (N={N}, K={K}), "
                       f"f64-accumulating cpu_bmm + epilogue on {threads} threads, {t:.2f} s"}
+
+
+def config_dict(world: int) -> dict:
+    """The workload description both arms print (identical keys and values)."""
+    return {"workload": WORKLOAD if BATCH == 32 else f"REDUCED profiling case, {BATCH} planes (not a bench value)",
+            "batch_per_gpu": BATCH, "m": M, "n": N, "k": K, "parallelism": f"batch-replicated x{world}",
+            "l2": "operands per launch (1.63 GB) exceed the 126 MB L2; no flush needed"}
+
+
+def profile_traffic_per_plane():
+    """DRAM bytes per batch plane of the dominant kernel, read from the committed ncu summary
+    (dram__bytes_read.sum + dram__bytes_write.sum of a 4-plane launch; traffic is proportional to
+    planes: every plane streams its own A, R and C once).  None when the summary has no such line."""
+    import re
+    path = os.path.join(ROOT, "profiles", "gemm_tf32x3_m128n256_batch4_ncu_full.md")
+    try:
+        text = open(path).read()
+    except OSError:
+        return None, None
+    m = re.search(r"traffic_bytes_per_launch_4_planes:\s*([0-9.eE+]+)", text)
+    if not m:
+        return None, None
+    return float(m.group(1)) / 4.0, "profiles/gemm_tf32x3_m128n256_batch4_ncu_full.md (ncu capture at 4 planes, per plane)"
 
 
 def lcg_tokens(n: int, vocab: int, seed: int = 12345):
@@ -195,9 +236,16 @@ def bench_llama(ta, ctx, comm, world: int, peaks: dict) -> dict:
     pre, dec, dec_wall = statistics.median(pre_ms), statistics.median(dec_ms_tok), statistics.median(dec_wall_tok)
     wbytes = model.weight_bytes_per_token                # this rank's shard; KV reads (a few MB) not counted
     gbs = wbytes / (dec * 1e-3) / 1e9
+    # the 129 greedy tokens (prefill's + 128 decoded) of the 1-GPU run that was checked against the
+    # float64 host forward (tests/test_llama_full_size.py): every tensor-parallel width must reproduce them
+    golden_path = os.path.join(ROOT, "tests", "golden", "llama_config5_tokens.json")
+    tokens_match = None
+    if os.path.exists(golden_path):
+        with open(golden_path) as f:
+            tokens_match = ([int(nxt)] + [int(t) for t in toks]) == json.load(f)["tokens"]
     out = {
         "config": "configs[4]: llama 22L/2048/32q/4kv/5632/32000 f16 weights, f16 KV, pp512 + tg128",
-        "tp": world,
+        "tp": world, "tokens_match_golden": tokens_match,
         "prefill_tok_s": 512 / (pre * 1e-3), "prefill_ms": pre,
         "decode_tok_s": 1e3 / dec_wall, "decode_ms_per_token_device": dec, "decode_ms_per_token_wall": dec_wall,
         "weight_bytes_per_token_per_rank": wbytes,
@@ -330,7 +378,8 @@ def run_reference_arm(args, rank: int) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / max(1, args.steps) * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "note": "bounded CPU sample per step"},
+        "data": "synthetic", "config": config_dict(int(os.environ.get("WORLD_SIZE", "1"))),
+        "note": f"each step is a bounded CPU sample of the workload on {last['cores']} host threads",
         "cpu_baseline": last,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -412,11 +461,14 @@ def main() -> None:
     # The clock sampler starts before the warm-up so that short timed regions still
     # see several samples under load (nvidia-smi needs ~100 ms per sample).
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    warm_t0 = time.perf_counter()
-    n_warm = 0
-    while n_warm < max(args.warmup, 3) or (rank == 0 and time.perf_counter() - warm_t0 < 0.6 and n_warm < 400):
+    # burn-in: the same fixed number of launches on every rank (about 0.6 s of this kernel), so that
+    # all GPUs reach the same power-capped state; then exactly --warmup untimed steps
+    burn_in = BURN_IN_LAUNCHES if BATCH == 32 else 20
+    for _ in range(burn_in):
         ex.run_ops([op])
-        n_warm += 1
+    barrier()
+    for _ in range(args.warmup):
+        ex.run_ops([op])
     barrier()
     launches0 = ta.kernel_launch_count()
     dev_ns = []
@@ -435,6 +487,35 @@ def main() -> None:
     ms_per_step = total_ms / args.steps
     value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
 
+    # ---- strong-scaling form of the same configuration: the 32 planes cut into contiguous blocks of
+    # 32 / N per GPU, no collective; time = slowest rank's device time for its block
+    strong = None
+    if BATCH == 32 and 32 % world == 0:
+        pp = 32 // world
+        sl = slice(rank * pp, (rank + 1) * pp)
+        sdev = {"a": ta.Tensor.uninit_device(ctx, (pp, M, K)), "bias": ta.Tensor.uninit_device(ctx, (pp, N)),
+                "r": ta.Tensor.uninit_device(ctx, (pp, M, N)), "c": ta.Tensor.uninit_device(ctx, (pp, M, N))}
+        for key in ("a", "bias", "r"):
+            ex.upload(np.ascontiguousarray(host[key][1][sl]), sdev[key])
+        sop = ta.MatmulOp(ta.MatmulCall(sdev["a"], dev["b"], sdev["c"]),
+                          ta.Epilogue(sdev["bias"], ta.Activation.SILU, ta.Binary.ADD_SCALED, sdev["r"], 1.0))
+        for _ in range(max(args.warmup, 3)):
+            ex.run_ops([sop])
+        barrier()
+        s_ns = [ex.run_ops([sop]).gpu_time_ns for _ in range(args.steps)]
+        barrier()
+        s_ms = sum(s_ns) / 1e6 / args.steps
+        if distributed:
+            t = torch.tensor([s_ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            s_ms = float(t[0])
+        tiles = pp * (M // 128) * (N // 256)
+        strong = {"scaling": "strong", "planes_per_gpu": pp, "ms_per_step": s_ms,
+                  "value": 2.0 * 32 * M * N * K / (s_ms * 1e-3) / 1e12, "unit": UNIT,
+                  "tiles_per_gpu": tiles, "waves_of_148": tiles / 148.0}
+        for t_ in sdev.values():
+            t_.close()
+
     out_host_t = torch.empty((BATCH, M, N), dtype=torch.float32).pin_memory()
     out_host = out_host_t.numpy()
     ex.download_into(dev["c"], out_host)
@@ -443,7 +524,7 @@ def main() -> None:
     # ---- end-to-end leg: pinned host buffers in, host buffer out, every step.
     e2e = None
     if not args.no_e2e:
-        e2e_steps = min(args.steps, 10)
+        e2e_steps = args.steps
         h2d = sum(v[1].nbytes for v in host.values())
         d2h = out_host.nbytes
 
@@ -477,7 +558,7 @@ def main() -> None:
         e2e_s = timed_loop(e2e_step)
         e2e_rel = spot_check(out_host, host)        # the pipelined call's own output, checked
         e2e = {"value": FLOPS_PER_STEP * world * e2e_steps / e2e_s / 1e12, "unit": UNIT,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps, "warmup": 1,
                "ms_per_step": e2e_s / e2e_steps * 1e3,
                "call": "ta_run_matmul_host_batched (pinned host operands in, host result out)",
                "spot_check_max_rel_err": e2e_rel,
@@ -487,6 +568,8 @@ def main() -> None:
     # ---- the other configurations of the metric, reported beside the headline
     peaks = measured_peaks()
     extras = {}
+    if strong:
+        extras["config2_strong"] = strong
     if not args.no_extras and BATCH == 32:
         comm = ta.Comm.from_torch_distributed(ctx) if distributed else None
         for k in list(dev):
@@ -510,24 +593,25 @@ def main() -> None:
         # tf32 issues at half the bf16 rate and 3xTF32 spends three MMAs per logical product
         peak = bf16 / 2.0 / 3.0
         achieved = FLOPS_PER_STEP / (statistics.mean(dev_ns) * 1e-9) / 1e12
+        per_plane, traffic_source = profile_traffic_per_plane()
+        sm_med, sm_max = (clocks or {}).get("sm_mhz"), (clocks or {}).get("sm_max_mhz")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": args.warmup, "burn_in_launches": burn_in, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core split, f32 accumulate)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD if BATCH == 32 else f"REDUCED profiling case, {BATCH} planes (not a bench value)",
-                       "batch_per_gpu": BATCH, "m": M, "n": N, "k": K,
-                       "kernel": route.kernel, "tile": list(route.tile), "parallelism": f"batch-replicated x{world}",
-                       "l2": "operands per launch (1.63 GB) exceed the 126 MB L2; no flush needed"},
+            "config": config_dict(world),
+            "route": {"kernel": route.kernel, "tile": list(route.tile)},
+            # the same figure at the maximum SM clock: value x max / median clock of the timed region
+            # (the timed region runs power-capped; this separates kernel quality from the clock it got)
+            "value_at_max_clock": value * sm_max / sm_med if sm_med and sm_max else None,
             "wall_ms_per_step": wall_s / args.steps * 1e3,
             "median_ms": statistics.median(dev_ns) / 1e6, "min_ms": min(dev_ns) / 1e6,
             "spot_check_max_rel_err": worst_rel,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
-                         # dram__bytes_read + write of one ncu capture at 4 planes (196.7 MB per launch,
-                         # profiles/gemm_tf32x3_m128n256_batch4_ncu_full.md), scaled by planes
-                         "traffic": 196.7e6 / 4 * BATCH,
+                         "traffic": per_plane * BATCH if per_plane else None, "traffic_source": traffic_source,
                          "algorithmic_bytes": 4.0 * (2 * BATCH * M * K + K * N + BATCH * N + BATCH * M * N),
                          "peak_basis": f"{peaks['source']} bf16 {'sustained' if long_run else 'burst'} "
                                        f"{bf16:.1f} TFLOP/s / 2 (tf32 rate) / 3 (MMA passes per product)",
@@ -538,10 +622,15 @@ def main() -> None:
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()
         assert worst_rel <= 1e-5, f"bench-time validation failed: rel err {worst_rel:.3e}"
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
+    # greedy tokens of configuration 5 that differ from the committed list fail the run (after the
+    # line is out): every tensor-parallel width must reproduce the 1-GPU stream
+    if rank == 0 and extras.get("llama", {}).get("tokens_match_golden") is False:
+        sys.stderr.write("bench: llama greedy tokens differ from tests/golden/llama_config5_tokens.json\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -95,6 +95,21 @@ int ta_llama_prefill(ta_llama *model, const uint32_t *tokens, uint32_t n, uint32
 int ta_llama_decode(ta_llama *model, uint32_t first_token, uint32_t n, uint32_t *out_tokens,
                     ta_run_stats *stats);
 
+/* One decode step with the device time of every launch measured separately (CUDA events around each
+ * launch; the reference's LLAMA_ASH_BREAKDOWN=1 table, ref tools/llama-ash/src/main.rs:161-193,
+ * whose per-dispatch times come from its per-op mode).  The step consumes `token` at the current
+ * position like ta_llama_decode(model, token, 1, ..).  rows[0 .. min(cap, *n_rows)) receive one row per
+ * op class, largest first; class names are static strings in the reference's vocabulary
+ * (qkv_matmul, attn_decode, o_proj_mm, ffn_up_mm = the fused up + gate launch, ffn_down_mm,
+ * lm_head_mm) plus argmax, embed_gather, all_reduce, all_gather.  *n_launches = launches of the step. */
+typedef struct ta_llama_breakdown_row {
+  const char *op_class;
+  uint64_t gpu_ns;
+  uint32_t calls;
+} ta_llama_breakdown_row;
+int ta_llama_decode_breakdown(ta_llama *model, uint32_t token, ta_llama_breakdown_row *rows, size_t cap,
+                              size_t *n_rows, size_t *n_launches, uint32_t *next_token);
+
 /* Logits of the most recent step ([vocab] floats), for margin checks. */
 int ta_llama_logits(ta_llama *model, float *out, size_t len);
 

@@ -87,6 +87,10 @@ class ExecOpC(C.Structure):
                 ("attn", AttnDecodeDescC), ("cell", C.c_void_p), ("tokens", C.c_void_p), ("comm", C.c_void_p)]
 
 
+class LlamaBreakdownRowC(C.Structure):
+    _fields_ = [("op_class", C.c_char_p), ("gpu_ns", C.c_uint64), ("calls", C.c_uint32)]
+
+
 class LlamaConfigC(C.Structure):
     _fields_ = [("layers", C.c_uint32), ("embd", C.c_uint32), ("heads", C.c_uint32), ("kv_heads", C.c_uint32),
                 ("head_dim", C.c_uint32), ("ffn", C.c_uint32), ("vocab", C.c_uint32), ("t_max", C.c_uint32),
@@ -207,6 +211,8 @@ SIGNATURES = {
     "ta_llama_reset": (C.c_int, [_P]),
     "ta_llama_prefill": (C.c_int, [_P, C.POINTER(_U32), _U32, C.POINTER(_U32), _STATS]),
     "ta_llama_decode": (C.c_int, [_P, _U32, _U32, C.POINTER(_U32), _STATS]),
+    "ta_llama_decode_breakdown": (C.c_int, [_P, _U32, C.POINTER(LlamaBreakdownRowC), _SZ, C.POINTER(_SZ), C.POINTER(_SZ),
+                                          C.POINTER(_U32)]),
     "ta_llama_logits": (C.c_int, [_P, _P, _SZ]),
     "ta_llama_position": (_U32, [_P]),
     "ta_llama_weight_bytes_per_token": (C.c_uint64, [_P]),

@@ -12,6 +12,7 @@
 // + residual; then lm_head with the final norm fused, argmax into a host-visible
 // word, and the next token's embedding row gathered on the device.  A step is
 // one position write, one graph launch and one token read.
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <array>
@@ -458,6 +459,29 @@ void push_head_ops(ta_llama &m, std::vector<ExecOp> &ops, ExecOp head) {
 
 // forward/decode.rs:172-246 decode_ops + forward/mod.rs:316-328 decode_close_ops,
 // position-relative (pos_base 0 + *pos_cell).
+// Op class of every entry of decode_ops(), in the reference's vocabulary for its
+// LLAMA_ASH_BREAKDOWN table (tools/llama-ash/src/model/forward/*.rs `note(class, ..)`), plus the
+// classes this runner has on top (collectives, argmax and the embedding gather run on the device).
+std::vector<const char *> decode_op_classes(ta_llama &m) {
+  std::vector<const char *> cls;
+  const bool tp = m.world > 1;
+  for (size_t l = 0; l < m.layers.size(); ++l) {
+    for (int i = 0; i < 3; ++i) cls.push_back("qkv_matmul");
+    cls.push_back("attn_decode");
+    cls.push_back("o_proj_mm");
+    if (tp) cls.push_back("all_reduce");
+    cls.push_back("ffn_up_mm");
+    cls.push_back("ffn_gate_mm");
+    cls.push_back("ffn_down_mm");
+    if (tp) cls.push_back("all_reduce");
+  }
+  cls.push_back("lm_head_mm");
+  if (tp) cls.push_back("all_gather");
+  cls.push_back("argmax");
+  cls.push_back("embed_gather");
+  return cls;
+}
+
 std::vector<ExecOp> decode_ops(ta_llama &m) {
   const ta_llama_config &c = m.cfg;
   const float eps = c.rms_eps;
@@ -855,6 +879,41 @@ int ta_llama_decode(ta_llama *model, uint32_t first_token, uint32_t n, uint32_t 
       total.total_flops += st.total_flops;
     }
     write_stats(stats, total);
+  });
+}
+
+int ta_llama_decode_breakdown(ta_llama *model, uint32_t token, ta_llama_breakdown_row *rows, size_t cap,
+                              size_t *n_rows, size_t *n_launches, uint32_t *next_token) {
+  return guarded([&]() {
+    if (!model) fail("ta_llama_decode_breakdown: model is null");
+    if (!rows || !n_rows) fail("ta_llama_decode_breakdown: rows / n_rows is null");
+    ta_llama &m = *model;
+    if (m.pos + 1 > m.cfg.t_max) fail("ta_llama_decode_breakdown: KV cache overflow (%u + 1 > %u)", m.pos, m.cfg.t_max);
+    m.ctx->make_current();
+    *(volatile uint32_t *)m.token_cell.host = token;
+    m.exec->embed_gather(m.token_cell, m.embd, m.x_a);
+    *(volatile uint32_t *)m.pos_cell.host = m.pos;
+    const std::vector<ExecOp> ops = decode_ops(m);
+    const std::vector<const char *> cls = decode_op_classes(m);
+    if (cls.size() != ops.size()) fail("internal: %zu op classes for %zu decode ops", cls.size(), ops.size());
+    std::vector<std::pair<size_t, uint64_t>> per_launch;
+    m.exec->run_exec_ops_timed(ops, &per_launch);
+    m.pos += 1;
+    if (next_token) *next_token = *(volatile uint32_t *)m.token_cell.host;
+    if (n_launches) *n_launches = per_launch.size();
+    // a launch that fuses several ops (q, k, v; up + gate) is booked under its first op's class
+    std::vector<ta_llama_breakdown_row> acc;
+    for (const auto &pl : per_launch) {
+      const char *name = cls[pl.first];
+      size_t i = 0;
+      while (i < acc.size() && strcmp(acc[i].op_class, name)) ++i;
+      if (i == acc.size()) acc.push_back(ta_llama_breakdown_row{name, 0, 0});
+      acc[i].gpu_ns += pl.second;
+      acc[i].calls += 1;
+    }
+    std::sort(acc.begin(), acc.end(), [](const ta_llama_breakdown_row &a, const ta_llama_breakdown_row &b) { return a.gpu_ns > b.gpu_ns; });
+    *n_rows = acc.size();
+    for (size_t i = 0; i < acc.size() && i < cap; ++i) rows[i] = acc[i];
   });
 }
 

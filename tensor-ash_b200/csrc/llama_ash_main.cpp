@@ -165,6 +165,21 @@ int bench(const Args &a) {
     fprintf(stderr, "decode timing: %.3f ms/token GPU vs %.3f ms/token wall (%.3f ms host)\n",
             st.gpu_time_ns / 1e6 / a.tg, decode_s * 1e3 / a.tg, decode_s * 1e3 / a.tg - st.gpu_time_ns / 1e6 / a.tg);
 
+  // Per-op-class GPU-time breakdown of one more decode step (main.rs:161-193).
+  if (const char *e = getenv("LLAMA_ASH_BREAKDOWN"); e && !strcmp(e, "1") && a.tg) {
+    ta_llama_breakdown_row rows[32];
+    size_t n_rows = 0, n_launches = 0;
+    uint32_t tok = 0;
+    if (ta_llama_decode_breakdown(s.model, out[a.tg - 1], rows, 32, &n_rows, &n_launches, &tok) != 0) die_lib("breakdown");
+    uint64_t total = 0;
+    for (size_t i = 0; i < n_rows && i < 32; ++i) total += rows[i].gpu_ns;
+    printf("decode GPU breakdown (one token, %zu dispatches):\n", n_launches);
+    for (size_t i = 0; i < n_rows && i < 32; ++i)
+      printf("  %-16s %8.1f us  (%3u calls, %4.1f%%)\n", rows[i].op_class, rows[i].gpu_ns / 1e3, rows[i].calls,
+             total ? rows[i].gpu_ns * 100.0 / total : 0.0);
+    printf("  %-16s %8.1f us  (GPU-timestamped total)\n", "sum", total / 1e3);
+  }
+
   printf("model    : %s\n", a.random ? "(random-init, llama 22L/2048/32q/4kv/5632/32000)" : a.model.c_str());
   printf("load     : %.2f s\n", s.load_s);
   printf("| test        | tokens | time (s) | tokens/s |\n");

@@ -6,6 +6,12 @@
 //   ml_bench self-check | correctness | sweep | single | cases label,b,m,n,k[,f16w] ... | concurrent | transfer |
 //            prepared | all
 //   ml_bench summary x1 x2 ...      (host only: prints the sample summary of the numbers)
+//   ml_bench thesis [--all] [t1 t2 t4 t6 t7 ...] [--list] [-m model.gguf | --random]
+//            the performance-thesis harness (tools/ml-bench/src/bench/thesis/*.rs, benchmarks/THESES.md):
+//            prediction / measurement / verdict rows against the per-GPU section of
+//            thesis-expectations.toml (beside the package; $ML_THESIS_EXPECT overrides); a FAIL row
+//            makes the exit status non-zero.  `thesis parse <file> <device>` (host only) prints the
+//            section a device name selects.
 //
 //   ML_ITERS (20) ML_WARMUP (3) ML_OUTPUT (table | csv) ML_SWEEP (smoke | standard | full)
 //   ML_B ML_M ML_N ML_K   ML_SPLIT_K2 (0)   ML_SLOTS (2)   ML_THREADS   ML_KERNEL (auto)   ML_DEVICE   ML_VALIDATE
@@ -14,6 +20,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cmath>
+#include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -22,7 +29,12 @@
 #include <thread>
 #include <vector>
 
+#include <map>
+#include <optional>
+#include <unistd.h>
+
 #include "../../include/tensor_ash.h"
+#include "../../include/tensor_ash_llama.h"
 
 namespace {
 
@@ -584,13 +596,507 @@ void concurrent(const Session &s) {
   }
 }
 
+// ===================================================================== thesis harness
+// (tools/ml-bench/src/bench/thesis/{mod,expect,gemv,micro,model_theses}.rs, benchmarks/THESES.md)
+using Section = std::map<std::string, double>;
+
+std::string trim(const std::string &v) {
+  const size_t b = v.find_first_not_of(" \t\r"), e = v.find_last_not_of(" \t\r");
+  return b == std::string::npos ? "" : v.substr(b, e - b + 1);
+}
+
+// Strict TOML subset (expect.rs:66-112): ["quoted" or bare] section headers, key = <float>, # comments.
+// Returns false with *err set on a malformed line.
+bool parse_expectations(const std::string &text, std::map<std::string, Section> *out, std::string *err) {
+  std::string current;
+  bool have_section = false;
+  size_t lineno = 0, pos = 0;
+  while (pos <= text.size()) {
+    size_t nl = text.find('\n', pos);
+    if (nl == std::string::npos) nl = text.size();
+    std::string line = text.substr(pos, nl - pos);
+    pos = nl + 1;
+    ++lineno;
+    line = trim(line.substr(0, line.find('#')));
+    if (line.empty()) continue;
+    auto bad = [&](const char *what) {
+      *err = "line " + std::to_string(lineno) + ": " + what;
+      return false;
+    };
+    if (line[0] == '[') {
+      if (line.back() != ']') return bad("unterminated section header");
+      std::string name = trim(line.substr(1, line.size() - 2));
+      if (name.size() >= 2 && name.front() == '"' && name.back() == '"') name = name.substr(1, name.size() - 2);
+      if (name.empty()) return bad("empty section name");
+      (*out)[name];
+      current = name;
+      have_section = true;
+      continue;
+    }
+    const size_t eq = line.find('=');
+    if (eq == std::string::npos) return bad("expected key = value");
+    if (!have_section) return bad("key before any [section]");
+    const std::string value = trim(line.substr(eq + 1));
+    char *end = nullptr;
+    const double v = strtod(value.c_str(), &end);
+    if (value.empty() || *end) return bad("value is not a number");
+    (*out)[current][trim(line.substr(0, eq))] = v;
+  }
+  return true;
+}
+
+std::string expectations_path() {
+  if (const char *e = getenv("ML_THESIS_EXPECT")) return e;
+  char exe[4096];
+  const ssize_t n = readlink("/proc/self/exe", exe, sizeof exe - 1);
+  if (n > 0) {
+    std::string dir(exe, (size_t)n);
+    dir = dir.substr(0, dir.find_last_of('/'));            // .../bin
+    return dir.substr(0, dir.find_last_of('/')) + "/thesis-expectations.toml";
+  }
+  return "thesis-expectations.toml";
+}
+
+bool read_file(const std::string &path, std::string *out) {
+  FILE *f = fopen(path.c_str(), "rb");
+  if (!f) return false;
+  char buf[4096];
+  size_t n;
+  while ((n = fread(buf, 1, sizeof buf, f)) > 0) out->append(buf, n);
+  fclose(f);
+  return true;
+}
+
+enum class Verdict { Pass, Fail, Info, Skip };
+const char *verdict_str(Verdict v) {
+  switch (v) {
+    case Verdict::Pass: return "PASS";
+    case Verdict::Fail: return "FAIL";
+    case Verdict::Info: return "info";
+    default: return "SKIP";
+  }
+}
+struct Row {
+  std::string thesis, item, prediction, measured;
+  Verdict verdict;
+};
+std::optional<double> key(const Section *s, const char *name) {
+  if (!s) return std::nullopt;
+  auto it = s->find(name);
+  return it == s->end() ? std::nullopt : std::optional<double>(it->second);
+}
+Verdict check_min(double value, std::optional<double> min) { return !min ? Verdict::Info : (value >= *min ? Verdict::Pass : Verdict::Fail); }
+std::string fmt(const char *f, ...) __attribute__((format(printf, 1, 2)));
+std::string fmt(const char *f, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, f);
+  vsnprintf(buf, sizeof buf, f, ap);
+  va_end(ap);
+  return buf;
+}
+
+void print_thesis_table(const std::string &device, const std::vector<Row> &rows) {
+  const char *headers[5] = {"thesis", "item", "prediction", "measured", "verdict"};
+  size_t w[5];
+  for (int i = 0; i < 5; ++i) w[i] = strlen(headers[i]);
+  for (const Row &r : rows) {
+    const std::string cells[5] = {r.thesis, r.item, r.prediction, r.measured, verdict_str(r.verdict)};
+    for (int i = 0; i < 5; ++i) w[i] = std::max(w[i], cells[i].size());
+  }
+  auto line = [&](const std::string cells[5]) {
+    std::string out = "|";
+    for (int i = 0; i < 5; ++i) out += " " + cells[i] + std::string(w[i] - cells[i].size(), ' ') + " |";
+    printf("%s\n", out.c_str());
+  };
+  printf("\nperformance-thesis results — %s\n", device.c_str());
+  const std::string h[5] = {headers[0], headers[1], headers[2], headers[3], headers[4]};
+  line(h);
+  const std::string sep[5] = {std::string(w[0], '-'), std::string(w[1], '-'), std::string(w[2], '-'), std::string(w[3], '-'),
+                              std::string(w[4], '-')};
+  line(sep);
+  for (const Row &r : rows) {
+    const std::string cells[5] = {r.thesis, r.item, r.prediction, r.measured, verdict_str(r.verdict)};
+    line(cells);
+  }
+  printf("\n");
+}
+
+// ~300 ms of 1024^3 GEMMs before anything is timed (mod.rs:209-230)
+void thesis_burn_in(const Session &s) {
+  Tensors t;
+  const uint32_t sh[2] = {1024, 1024};
+  t.a = ta_tensor_create(s.ctx, sh, 2);
+  t.b = ta_tensor_create(s.ctx, sh, 2);
+  t.c = ta_tensor_create(s.ctx, sh, 2);
+  if (!t.a || !t.b || !t.c) die_lib("tensor");
+  std::vector<float> host(1024 * 1024);
+  fill_det(host, 3);
+  if (ta_upload(s.exec, t.a, host.data(), host.size()) != 0 || ta_upload(s.exec, t.b, host.data(), host.size()) != 0)
+    die_lib("upload");
+  const double deadline = now_ms() + 300.0;
+  while (now_ms() < deadline)
+    if (ta_matmul(s.exec, t.a, t.b, t.c, 1.0f, 0, nullptr) != 0) die_lib("burn-in");
+}
+
+// T2 (gemv.rs:35-128): every decode GEMV class against its bandwidth floor.  The weights of one
+// class fit this GPU's 126 MB L2, so the launches rotate over enough copies of the matrix to stream
+// at least 384 MB before one repeats: what is measured is memory bandwidth, as on the reference's GPU.
+std::vector<Row> t2_gemv_efficiency(const Session &s, const Section *sec) {
+  static const struct { const char *label; uint32_t k, n; } shapes[] = {
+      {"q/o 2048x2048", 2048, 2048}, {"k/v 2048x256", 2048, 256}, {"gate/up 2048x5632", 2048, 5632},
+      {"down 5632x2048", 5632, 2048}, {"lm_head 2048x32000", 2048, 32000}};
+  const uint32_t iters = std::max(1u, env_u32("ML_ITERS", 50)), warmup = env_u32("ML_WARMUP", 5);
+  const auto bw = key(sec, "mem_bw_gbps"), min_frac = key(sec, "t2_min_bw_frac");
+  std::vector<Row> rows;
+  for (const auto &sh : shapes) {
+    const double wbytes = 2.0 * sh.k * sh.n;
+    const size_t copies = (size_t)std::max(2.0, std::ceil(384e6 / wbytes));
+    const uint32_t sa[2] = {1, sh.k}, sb[2] = {sh.k, sh.n}, sc[2] = {1, sh.n};
+    ta_tensor *a = ta_tensor_create(s.ctx, sa, 2), *c = ta_tensor_create(s.ctx, sc, 2);
+    std::vector<ta_tensor *> bs(copies);
+    std::vector<float> ha(sh.k), hb((size_t)sh.k * sh.n);
+    fill_det(ha, 7);
+    fill_det(hb, 11);
+    if (!a || !c || ta_upload(s.exec, a, ha.data(), ha.size()) != 0) die_lib("tensor");
+    for (size_t i = 0; i < copies; ++i) {
+      bs[i] = ta_tensor_create_f16(s.ctx, sb, 2);
+      if (!bs[i] || ta_upload(s.exec, bs[i], hb.data(), hb.size()) != 0) die_lib("tensor");
+    }
+    ta_dispatch_info info{};
+    if (ta_dispatch_info_for(s.exec, 1, 1, sh.n, sh.k, 1, &info) != 0) die_lib("dispatch_info_for");
+    std::vector<double> gpu;
+    ta_run_stats st{};
+    for (uint32_t i = 0; i < warmup + iters; ++i) {
+      if (ta_matmul(s.exec, a, bs[i % copies], c, 1.0f, 0, &st) != 0) die_lib("matmul");
+      if (i >= warmup && st.has_gpu_time) gpu.push_back(st.gpu_time_ns / 1e6);
+    }
+    for (float &v : hb) v = ta_f16_bits_to_f32(ta_f32_to_f16_bits(v));
+    validate_samples(s, c, ha, hb, 1, 1, sh.n, sh.k);
+    const Summary sm = summarize(gpu);
+    const double bytes = wbytes + 4.0 * ((double)sh.k + sh.n);      // f16 weights + f32 row in + f32 row out
+    const double gbps = bytes / (sm.median * 1e6);
+    Row r{"T2", std::string("GEMV ") + sh.label + " f16w", "", "", Verdict::Info};
+    if (bw) {
+      const double frac = gbps / *bw;
+      r.prediction = fmt(">= %.0f%% of BW floor (%.1f us at %.0f GB/s)", min_frac.value_or(NAN) * 100.0, bytes / (*bw * 1e3), *bw);
+      r.measured = fmt("%.1f us = %.0f GB/s = %.0f%% [%s]", sm.median * 1e3, gbps, frac * 100.0, info.kernel);
+      r.verdict = check_min(frac, min_frac);
+    } else {
+      r.prediction = "unrecorded (needs mem_bw_gbps)";
+      r.measured = fmt("%.1f us = %.0f GB/s [%s]", sm.median * 1e3, gbps, info.kernel);
+    }
+    rows.push_back(r);
+    ta_tensor_destroy(a);
+    ta_tensor_destroy(c);
+    for (ta_tensor *b : bs) ta_tensor_destroy(b);
+  }
+  return rows;
+}
+
+// T6 (gemv.rs:130-200): the f16-weight tensor-core GEMM on the real 512-row prefill shapes, with
+// 4096^3 as the regression reference.  A shape that routes away from the tensor cores fails its row.
+std::vector<Row> t6_tensor_core_ceiling(const Session &s, const Section *sec) {
+  const uint32_t iters = std::max(1u, env_u32("ML_ITERS", 20)), warmup = env_u32("ML_WARMUP", 3);
+  const auto min_tf = key(sec, "t6_min_tflops"), ref_tf = key(sec, "t6_ref_tflops");
+  const double ref_tol = key(sec, "t6_ref_rel_tol").value_or(0.15);
+  static const struct { const char *label; uint32_t m, n, k; } shapes[] = {
+      {"prefill q/o 512x2048x2048", 512, 2048, 2048}, {"prefill gate/up 512x5632x2048", 512, 5632, 2048},
+      {"prefill down 512x2048x5632", 512, 2048, 5632}};
+  std::vector<Row> rows;
+  auto measure = [&](const char *label, uint32_t m, uint32_t n, uint32_t k, double *tflops, std::string *kernel) {
+    const Result r = run_case(s, Case{std::string("tensor ") + label, 1, m, n, k, true}, iters, warmup);
+    *tflops = r.tflops;
+    *kernel = r.dispatch.kernel;
+    return fmt("%.2f TF/s (%.0f us) [%s]", r.tflops, r.gpu.median * 1e3, r.dispatch.kernel);
+  };
+  for (const auto &sh : shapes) {
+    double tf;
+    std::string kernel;
+    const std::string measured = measure(sh.label, sh.m, sh.n, sh.k, &tf, &kernel);
+    Verdict v = check_min(tf, min_tf);
+    if (kernel.find("umma") == std::string::npos && min_tf) v = Verdict::Fail;
+    rows.push_back(Row{"T6", std::string("tensor-core ") + sh.label + " f16w", min_tf ? fmt(">= %.0f TF/s", *min_tf) : "unrecorded",
+                       measured, v});
+  }
+  double tf;
+  std::string kernel;
+  const std::string measured = measure("reference 4096^3", 4096, 4096, 4096, &tf, &kernel);
+  rows.push_back(Row{"T6", "tensor-core reference 4096^3 f16w",
+                     ref_tf ? fmt("~%.1f TF/s (-%.0f%% floor)", *ref_tf, ref_tol * 100.0) : "unrecorded", measured,
+                     check_min(tf, ref_tf ? std::optional<double>(*ref_tf * (1.0 - ref_tol)) : std::nullopt)});
+  return rows;
+}
+
+// T4 (micro.rs): one submission round trip.  N = 64 single-op submissions against one submission of
+// the same 64 independent trivial ops, nine times; per-submit cost = (median_many - median_one) / (N - 1).
+std::vector<Row> t4_submission_cost(const Session &s, const Section *sec) {
+  constexpr int N = 64;
+  const uint32_t sh[1] = {256};
+  std::vector<ta_tensor *> a(N), b(N), o(N);
+  std::vector<float> host(256, 1.0f);
+  for (int i = 0; i < N; ++i) {
+    a[i] = ta_tensor_create(s.ctx, sh, 1);
+    b[i] = ta_tensor_create(s.ctx, sh, 1);
+    o[i] = ta_tensor_create(s.ctx, sh, 1);
+    if (!a[i] || !b[i] || !o[i] || ta_upload(s.exec, a[i], host.data(), 256) != 0 || ta_upload(s.exec, b[i], host.data(), 256) != 0)
+      die_lib("tensor");
+  }
+  std::vector<ta_exec_op> ops(N);
+  for (int i = 0; i < N; ++i) {
+    memset(&ops[i], 0, sizeof(ta_exec_op));
+    ops[i].kind = TA_EXEC_BINARY;
+    ops[i].in0 = a[i]; ops[i].in1 = b[i]; ops[i].out = o[i];
+    ops[i].u0 = 0; ops[i].f0 = 1.0f;
+  }
+  std::vector<double> many, one;
+  for (int rep = 0; rep < 10; ++rep) {
+    double t0 = now_ms();
+    for (int i = 0; i < N; ++i)
+      if (ta_run_exec_ops(s.exec, &ops[i], 1, nullptr) != 0) die_lib("run_exec_ops");
+    const double tm = now_ms() - t0;
+    t0 = now_ms();
+    if (ta_run_exec_ops(s.exec, ops.data(), N, nullptr) != 0) die_lib("run_exec_ops");
+    const double to = now_ms() - t0;
+    if (rep) {   // the first repetition warms the path
+      many.push_back(tm);
+      one.push_back(to);
+    }
+  }
+  const double per_submit_us = (summarize(many).median - summarize(one).median) / (N - 1) * 1e3;
+  for (int i = 0; i < N; ++i) {
+    ta_tensor_destroy(a[i]);
+    ta_tensor_destroy(b[i]);
+    ta_tensor_destroy(o[i]);
+  }
+  const auto lo = key(sec, "t4_submit_us_lo"), hi = key(sec, "t4_submit_us_hi");
+  const double tol = key(sec, "t4_edge_tol").value_or(0.20);
+  Row r{"T4", "submission round trip (launch + stream wait)", "", fmt("%.1f us per submission", per_submit_us), Verdict::Info};
+  if (lo && hi) {
+    r.prediction = fmt("%.0f-%.0f us (+-%.0f%% at the edges)", *lo, *hi, tol * 100.0);
+    r.verdict = (per_submit_us >= *lo * (1.0 - tol) && per_submit_us <= *hi * (1.0 + tol)) ? Verdict::Pass : Verdict::Fail;
+  } else {
+    r.prediction = "unrecorded";
+  }
+  return {r};
+}
+
+struct ThesisModel {
+  ta_llama *model = nullptr;
+  ta_llama_config cfg{};
+  ~ThesisModel() { ta_llama_destroy(model); }
+};
+
+void load_thesis_model(const Session &s, const std::string &path, bool random, ThesisModel *m) {
+  if (random) {
+    ta_llama_config c{};
+    c.layers = 22; c.embd = 2048; c.heads = 32; c.kv_heads = 4; c.head_dim = 64; c.ffn = 5632; c.vocab = 32000;
+    c.t_max = 1024; c.rms_eps = 1e-5f; c.rope_theta = 1e4f; c.weight_sigma = 0.02f; c.norm_jitter = 0.0f; c.seed = 1;
+    m->model = ta_llama_create_random(s.exec, &c);
+  } else {
+    m->model = ta_llama_load_gguf(s.exec, path.c_str(), 1024, nullptr);
+  }
+  if (!m->model) die_lib("model");
+  if (ta_llama_get_config(m->model, &m->cfg) != 0) die_lib("config");
+}
+
+std::vector<uint32_t> thesis_prompt(uint32_t n, uint32_t vocab) {   // BOS, then arbitrary in-vocabulary ids
+  std::vector<uint32_t> p(n);
+  p[0] = 1 % vocab;
+  for (uint32_t i = 1; i < n; ++i) p[i] = (100 + (i % 1000)) % vocab;
+  return p;
+}
+
+// T1 (model_theses.rs:60-170): decode GPU time per token priced by weight traffic.
+std::vector<Row> t1_decode_bandwidth(const Section *sec, ThesisModel &m) {
+  constexpr uint32_t PP = 512, TG = 128;
+  if (m.cfg.t_max < PP + TG) return {Row{"T1", "decode weight bandwidth", "-", "context shorter than pp512 + tg128", Verdict::Skip}};
+  const std::vector<uint32_t> prompt = thesis_prompt(PP, m.cfg.vocab);
+  std::vector<uint32_t> out(TG);
+  uint32_t next = 0;
+  ta_run_stats st{};
+  // warm-up: prefill + 16 decode steps, then reset
+  if (ta_llama_prefill(m.model, prompt.data(), PP, &next, &st) != 0 || ta_llama_decode(m.model, next, 16, out.data(), &st) != 0 ||
+      ta_llama_reset(m.model) != 0)
+    die_lib("T1 warm-up");
+  if (ta_llama_prefill(m.model, prompt.data(), PP, &next, &st) != 0) die_lib("T1 prefill");
+  const uint64_t launches0 = ta_kernel_launch_count();
+  const double t0 = now_ms();
+  if (ta_llama_decode(m.model, next, TG, out.data(), &st) != 0) die_lib("T1 decode");
+  const double wall_ms_tok = (now_ms() - t0) / TG;
+  const double launches_tok = (double)(ta_kernel_launch_count() - launches0) / TG;
+  ta_llama_reset(m.model);
+  const double gpu_ms_tok = st.gpu_time_ns / 1e6 / TG;
+  const double bytes = (double)ta_llama_weight_bytes_per_token(m.model);
+  const double gbps = bytes / (st.gpu_time_ns / (double)TG);          // bytes per token / ns per token = GB/s
+  const auto bw = key(sec, "mem_bw_gbps"), min_frac = key(sec, "t1_min_bw_frac");
+  std::vector<Row> rows;
+  Row r{"T1", "decode weight bandwidth (prepared graph, f16 KV, tg128 after pp512)", "", "", Verdict::Info};
+  if (bw && min_frac) {
+    r.prediction = fmt(">= %.0f GB/s (%.0f%% of %.0f)", *bw * *min_frac, *min_frac * 100.0, *bw);
+    r.verdict = check_min(gbps / *bw, min_frac);
+  } else {
+    r.prediction = "unrecorded (needs mem_bw_gbps, t1_min_bw_frac)";
+  }
+  r.measured = fmt("%.3f ms/token GPU = %.0f GB/s of %.2f GB weights%s", gpu_ms_tok, gbps, bytes / 1e9,
+                   bw ? fmt(" = %.0f%%", gbps / *bw * 100.0).c_str() : "");
+  rows.push_back(r);
+  rows.push_back(Row{"T1", "decode graph census", "-",
+                     fmt("%.0f launches/token, %.3f ms/token wall (%.3f ms host)", launches_tok, wall_ms_tok, wall_ms_tok - gpu_ms_tok),
+                     Verdict::Info});
+  return rows;
+}
+
+// T7 (model_theses.rs:460-531): greedy generation is identical across execution strategies and
+// prefill widths.  Strategies here: the replayed prepared graph, and the same op list submitted launch
+// by launch with events in between (the per-op mode); the KV cache of this runner is always f16.
+// Widths 1 / 64 / 300 / 512 take the single-token, small-row and tensor-core prefill branches.
+std::vector<Row> t7_token_exactness(ThesisModel &m) {
+  std::vector<Row> rows;
+  for (uint32_t width : {1u, 64u, 300u, 512u}) {
+    if (m.cfg.t_max < width + 17) continue;
+    const std::vector<uint32_t> prompt = thesis_prompt(width, m.cfg.vocab);
+    std::vector<uint32_t> a(17), b(17);
+    ta_run_stats st{};
+    if (ta_llama_reset(m.model) != 0 || ta_llama_prefill(m.model, prompt.data(), width, &a[0], &st) != 0 ||
+        ta_llama_decode(m.model, a[0], 16, a.data() + 1, &st) != 0)
+      die_lib("T7 prepared");
+    if (ta_llama_reset(m.model) != 0 || ta_llama_prefill(m.model, prompt.data(), width, &b[0], &st) != 0) die_lib("T7 per-op");
+    for (int i = 0; i < 16; ++i) {
+      ta_llama_breakdown_row tmp[32];
+      size_t n_rows = 0, n_launches = 0;
+      if (ta_llama_decode_breakdown(m.model, b[i], tmp, 32, &n_rows, &n_launches, &b[i + 1]) != 0) die_lib("T7 per-op step");
+    }
+    size_t first = 17;
+    for (size_t i = 0; i < 17; ++i)
+      if (a[i] != b[i]) { first = i; break; }
+    rows.push_back(Row{"T7", fmt("token exactness, prefill width %u + 16 greedy steps", width), "identical across strategies",
+                       first == 17 ? "17 / 17 tokens identical (prepared graph vs per-launch)"
+                                   : fmt("diverges at token %zu: %u vs %u", first, a[first], b[first]),
+                       first == 17 ? Verdict::Pass : Verdict::Fail});
+  }
+  ta_llama_reset(m.model);
+  return rows;
+}
+
+int thesis(int argc, char **argv) {
+  static const char *USAGE = "usage: ml_bench thesis [--all] [t1 t2 t4 t6 t7 ...] [--list] [-m/--model <gguf> | --random]\n"
+                             "  model path fallback: $ML_MODEL; --random runs the model theses on the random-init 22-layer\n"
+                             "  configuration; expectations: thesis-expectations.toml beside the package ($ML_THESIS_EXPECT)";
+  static const char *DESCRIPTIONS[][2] = {
+      {"t1", "decode-bandwidth-bound: weight bytes/token over decode GPU ms against the device bandwidth"},
+      {"t2", "GEMV efficiency: each decode GEMV class against its bandwidth floor"},
+      {"t4", "submission cost: one launch + stream-wait round trip"},
+      {"t6", "tensor-core ceiling: f16-weight GEMM TF/s on the real 512-row prefill shapes"},
+      {"t7", "token exactness: prepared-graph and per-launch decoding emit identical tokens at every prefill width"}};
+  std::vector<int> theses;
+  std::string model;
+  bool list = false, all = false, random = false;
+  if (argc >= 1 && !strcmp(argv[0], "parse")) {   // host only: thesis parse <file> <device>
+    if (argc < 3) die("thesis parse <file> <device name>");
+    std::string text, err;
+    if (!read_file(argv[1], &text)) die(std::string("cannot read ") + argv[1]);
+    std::map<std::string, Section> secs;
+    if (!parse_expectations(text, &secs, &err)) die("parsing " + std::string(argv[1]) + ": " + err);
+    auto it = secs.find(argv[2]);
+    if (it == secs.end()) {
+      printf("no section for '%s'\n", argv[2]);
+      return 0;
+    }
+    for (const auto &kv : it->second) printf("%s = %g\n", kv.first.c_str(), kv.second);
+    return 0;
+  }
+  for (int i = 0; i < argc; ++i) {
+    const std::string arg = argv[i];
+    if (arg == "--all") all = true;
+    else if (arg == "--list") list = true;
+    else if (arg == "--random") random = true;
+    else if (arg == "-m" || arg == "--model") {
+      if (i + 1 >= argc) die(arg + " needs a value\n" + USAGE);
+      model = argv[++i];
+    } else {
+      const bool t = (arg[0] == 't' || arg[0] == 'T') && arg.size() == 2 && arg[1] >= '1' && arg[1] <= '7';
+      if (!t) die("unknown thesis '" + arg + "'\n" + USAGE);
+      theses.push_back(arg[1] - '0');
+    }
+  }
+  if (list) {
+    printf("performance theses:\n");
+    for (auto &d : DESCRIPTIONS) printf("  %s  %s\n", d[0], d[1]);
+    printf("  t3, t5  not measured here: one in-order stream per submission has no barrier to price\n");
+    return 0;
+  }
+  if (all || theses.empty()) theses = {1, 2, 4, 6, 7};
+  std::sort(theses.begin(), theses.end());
+  theses.erase(std::unique(theses.begin(), theses.end()), theses.end());
+  auto wants = [&](int id) { return std::find(theses.begin(), theses.end(), id) != theses.end(); };
+  if (model.empty())
+    if (const char *e = getenv("ML_MODEL")) model = e;
+
+  Session s;
+  s.ctx = ta_context_create(0, getenv("ML_DEVICE"));
+  if (!s.ctx) die_lib("context");
+  s.exec = ta_executor_create_v2(s.ctx, 2, 1024, getenv("ML_KERNEL"), 0);
+  if (!s.exec) die_lib("executor");
+  const std::string device = ta_context_device_name(s.ctx);
+  const std::string path = expectations_path();
+  std::map<std::string, Section> secs;
+  std::string text, err;
+  const Section *sec = nullptr;
+  if (!read_file(path, &text)) {
+    fprintf(stderr, "expectations file %s not found; all verdicts will be informational\n", path.c_str());
+  } else {
+    if (!parse_expectations(text, &secs, &err)) die("parsing " + path + ": " + err);
+    auto it = secs.find(device);
+    if (it == secs.end())
+      fprintf(stderr, "no recorded expectations for device '%s' in %s; all verdicts will be informational\n", device.c_str(), path.c_str());
+    else {
+      sec = &it->second;
+      fprintf(stderr, "expectations: %s [%s]\n", path.c_str(), device.c_str());
+    }
+  }
+  fprintf(stderr, "burn-in: ~300 ms of 1024^3 GEMMs before first measurement\n");
+  thesis_burn_in(s);
+  std::vector<Row> rows;
+  auto add = [&](std::vector<Row> r) { rows.insert(rows.end(), r.begin(), r.end()); };
+  if (wants(3) || wants(5))
+    rows.push_back(Row{wants(3) ? "T3" : "T5", "barrier cost / prefill accounting", "-",
+                       "not measured: a submission is one in-order stream, there is no barrier to price", Verdict::Skip});
+  if (wants(4)) add(t4_submission_cost(s, sec));
+  if (wants(2)) add(t2_gemv_efficiency(s, sec));
+  if (wants(6)) add(t6_tensor_core_ceiling(s, sec));
+  if (wants(1) || wants(7)) {
+    if (model.empty() && !random) {
+      for (int id : {1, 7})
+        if (wants(id))
+          rows.push_back(Row{id == 1 ? "T1" : "T7", "model-level thesis", "-", "no GGUF model (pass -m/--model, set ML_MODEL, or --random)",
+                             Verdict::Skip});
+    } else {
+      ThesisModel m;
+      load_thesis_model(s, model, random, &m);
+      if (wants(1)) add(t1_decode_bandwidth(sec, m));
+      if (wants(7)) add(t7_token_exactness(m));
+    }
+  }
+  std::stable_sort(rows.begin(), rows.end(), [](const Row &a, const Row &b) { return a.thesis < b.thesis; });
+  print_thesis_table(device, rows);
+  size_t failures = 0;
+  for (const Row &r : rows) failures += r.verdict == Verdict::Fail;
+  if (failures) {
+    fprintf(stderr, "ml_bench: %zu thesis measurement(s) FAILED against recorded expectations\n", failures);
+    return 1;
+  }
+  return 0;
+}
+
 }  // namespace
 
 int main(int argc, char **argv) {
   const std::string cmd = argc > 1 ? argv[1] : "all";
+  if (cmd == "thesis") return thesis(argc - 2, argv + 2);
   static const char *known[] = {"self-check", "correctness", "sweep", "single", "cases", "concurrent", "transfer", "prepared", "all", "summary"};
   if (std::find_if(std::begin(known), std::end(known), [&](const char *k) { return cmd == k; }) == std::end(known))
-    die("unknown subcommand '" + cmd + "'; expected self-check, correctness, sweep, single, cases, concurrent, transfer, prepared, or all");
+    die("unknown subcommand '" + cmd + "'; expected self-check, correctness, sweep, single, cases, concurrent, transfer, prepared, thesis, or all");
   std::vector<std::string> rest;
   for (int i = 2; i < argc; ++i) rest.push_back(argv[i]);
   if (cmd == "summary") {   // host only: the sample summary of the given numbers (nan / inf / negatives are dropped)

@@ -576,8 +576,10 @@ class Executor {
   SplitK2TensorPlan splitk2_plan_for(const GemmParams &p, uint32_t splits) const;
   size_t splitk2_scratch_bytes(const MatmulOp &op, const ResolvedMatmul &r, uint32_t splits) const;
   bool gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route, GemvParams *out) const;
+  // first_op (optional): for every planned launch, the index of the first op of `ops` it executes
   std::vector<Launch> plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops, size_t *n_calls,
-                                    size_t *scratch_bytes = nullptr) const;
+                                    size_t *scratch_bytes = nullptr, std::vector<size_t> *first_op = nullptr) const;
+  RunStats run_exec_ops_timed(const std::vector<ExecOp> &ops, std::vector<std::pair<size_t, uint64_t>> *per_launch);
   RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
                        const Tensor *norm_w, float eps);
   void tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bool b_f16 = false);

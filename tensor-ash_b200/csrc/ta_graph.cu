@@ -468,7 +468,8 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
 // dispatches (HazardCursor, src/executor/graph_ops.rs:587-624); here a launch
 // boundary is the barrier, so independent ops share a launch instead.
 std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops,
-                                            size_t *n_calls, size_t *scratch_bytes) const {
+                                            size_t *n_calls, size_t *scratch_bytes,
+                                            std::vector<size_t> *first_op) const {
   struct Cand {
     bool gemv = false;
     GemvParams g{};
@@ -528,6 +529,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         op.u0 = ok ? 1u : 0u;
       }
       plan.push_back(plan_exec_op(op, flops, n_calls));
+      if (first_op) first_op->push_back(i);
       prev_gemv.clear();
       ++i;
       continue;
@@ -549,6 +551,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         if (flops) *flops += c0.flops + c1.flops;
         if (n_calls) *n_calls += 2;
         plan.push_back([f, cx](Slot &slot, cudaStream_t st) { launch_gemv_f16w_group(*cx, &f, 1, true, gemv_workspace(slot), st); });
+        if (first_op) first_op->push_back(i);
         prev_gemv.assign(1, f);
         i += 2;
         continue;
@@ -578,6 +581,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     plan.push_back([segs, cx](Slot &slot, cudaStream_t st) {
       launch_gemv_f16w_group(*cx, segs.data(), (int)segs.size(), true, gemv_workspace(slot), st);
     });
+    if (first_op) first_op->push_back(i);
     prev_gemv = segs;
     i = j;
   }
@@ -597,6 +601,45 @@ RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
   return timed(slot, n_calls, flops, [&](cudaStream_t st) {
     for (const Launch &l : plan) l(slot, st);
   });
+}
+
+// One submission with a pair of events around every planned launch: per_launch receives
+// (index of the launch's first source op, device nanoseconds).  Diagnostics only: the events
+// between launches remove the overlap programmatic dependent launch gives the plain path.
+RunStats Executor::run_exec_ops_timed(const std::vector<ExecOp> &ops, std::vector<std::pair<size_t, uint64_t>> *per_launch) {
+  uint64_t flops = 0;
+  size_t n_calls = 0, scratch_bytes = 0;
+  std::vector<size_t> first_op;
+  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls, &scratch_bytes, &first_op);
+  ctx_->make_current();
+  Slot &slot = checkout_slot();
+  SlotGuard g(*this, slot);
+  if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
+  std::vector<cudaEvent_t> ev(plan.size() + 1);
+  for (cudaEvent_t &e : ev) TA_CUDA(cudaEventCreate(&e));
+  RunStats st;
+  try {
+    st = timed(slot, n_calls, flops, [&](cudaStream_t s) {
+      for (size_t i = 0; i < plan.size(); ++i) {
+        TA_CUDA(cudaEventRecord(ev[i], s));
+        plan[i](slot, s);
+      }
+      TA_CUDA(cudaEventRecord(ev[plan.size()], s));
+    });
+    if (per_launch) {
+      per_launch->clear();
+      for (size_t i = 0; i < plan.size(); ++i) {
+        float ms = 0.0f;
+        TA_CUDA(cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
+        per_launch->emplace_back(first_op[i], (uint64_t)((double)ms * 1e6 + 0.5));
+      }
+    }
+  } catch (...) {
+    for (cudaEvent_t e : ev) cudaEventDestroy(e);
+    throw;
+  }
+  for (cudaEvent_t e : ev) cudaEventDestroy(e);
+  return st;
 }
 
 RunStats Executor::run_single(const ExecOp &op) { return run_exec_ops({op}); }

@@ -113,6 +113,16 @@ class Llama:
         _check(capi.lib().ta_llama_decode(self._h, first_token, n, out, C.byref(st)))
         return [int(out[i]) for i in range(n)], RunStats._from(st)
 
+    def decode_breakdown(self, token: int):
+        """One decode step with every launch timed separately: (next token, launches, rows) where rows
+        is a list of (op class, device ns, calls), largest first (the LLAMA_ASH_BREAKDOWN table)."""
+        rows = (capi.LlamaBreakdownRowC * 32)()
+        n_rows, n_launches, nxt = C.c_size_t(), C.c_size_t(), C.c_uint32()
+        _check(capi.lib().ta_llama_decode_breakdown(self._h, token, rows, 32, C.byref(n_rows), C.byref(n_launches),
+                                                    C.byref(nxt)))
+        out = [(rows[i].op_class.decode(), int(rows[i].gpu_ns), int(rows[i].calls)) for i in range(min(32, n_rows.value))]
+        return int(nxt.value), int(n_launches.value), out
+
     def logits(self) -> np.ndarray:
         out = np.empty(self.cfg.vocab, dtype=np.float32)
         _check(capi.lib().ta_llama_logits(self._h, out.ctypes.data, out.size))

@@ -97,6 +97,31 @@ def test_decode_continues_across_calls_and_reset(ta, orc, gpu):
 
 
 @pytest.mark.gpu
+def test_decode_breakdown_step_equals_a_graph_step(ta, orc, gpu):
+    """The instrumented step (every launch between two events, the LLAMA_ASH_BREAKDOWN table of
+    tools/llama-ash/src/main.rs:161-193) computes what a replayed graph step computes: same token,
+    same logits; its rows cover every launch once and name the reference's op classes."""
+    cfg = small_cfg(ta, seed=13)
+    ctx = ta.Context()
+    ex = ta.Executor(ctx, max_calls_per_submit=256)
+    model = ta.Llama(ex, cfg)
+    prompt = [3, 14, 159, 26, 535]
+    nxt, _ = model.prefill(prompt)
+    toks, _ = model.decode(nxt, 3)
+    want_logits = model.logits().copy()
+    model.reset()
+    nxt2, _ = model.prefill(prompt)
+    a, _ = model.decode(nxt2, 2)
+    tok, launches, rows = model.decode_breakdown(a[-1])
+    assert a + [tok] == toks and np.array_equal(model.logits(), want_logits)
+    assert model.position == len(prompt) + 3
+    classes = {name for name, _, _ in rows}
+    assert {"qkv_matmul", "attn_decode", "o_proj_mm", "ffn_up_mm", "ffn_down_mm", "lm_head_mm", "argmax"} <= classes
+    assert sum(calls for _, _, calls in rows) == launches == 5 * cfg.layers + 3
+    assert all(ns > 0 for _, ns, _ in rows) and [ns for _, ns, _ in rows] == sorted((ns for _, ns, _ in rows), reverse=True)
+
+
+@pytest.mark.gpu
 def test_chunked_prefill_matches_single_prefill(ta, orc, gpu):
     cfg = small_cfg(ta, seed=3)
     ctx = ta.Context()

@@ -103,3 +103,56 @@ def test_table_sweep_single_prepared_and_transfer():
     assert r.returncode == 0 and "transfer: 8 MiB x 4 samples" in r.stdout, r.stderr
     r = ml_bench("transfer", ML_TRANSFER_MB=8, ML_ITERS=4, ML_OUTPUT="csv")
     assert r.returncode == 0 and r.stdout.splitlines()[0].startswith("device,kind,bytes,iters,upload_gibs")
+
+
+# ---- thesis harness (tools/ml-bench/src/bench/thesis/*.rs, benchmarks/THESES.md)
+def test_thesis_expectations_parser(tmp_path):
+    """expect.rs:114-136: sections, keys, comments; malformed lines are errors."""
+    f = tmp_path / "e.toml"
+    f.write_text('\n# top comment\n["NVIDIA GeForce RTX 3070"]\nmem_bw_gbps = 448.0   # spec sheet\nt3_barrier_us = 7.7\n\n'
+                 '[bare-name]\nx = 1\n')
+    r = ml_bench("thesis", "parse", str(f), "NVIDIA GeForce RTX 3070")
+    assert r.returncode == 0 and r.stdout.splitlines() == ["mem_bw_gbps = 448", "t3_barrier_us = 7.7"], r.stdout + r.stderr
+    assert ml_bench("thesis", "parse", str(f), "bare-name").stdout.strip() == "x = 1"
+    assert "no section for 'unknown'" in ml_bench("thesis", "parse", str(f), "unknown").stdout
+    for text, why in [("key = 1.0", "key before any [section]"), ("[sec]\nkey 1.0", "expected key = value"),
+                      ("[sec]\nkey = fast", "value is not a number"), ("[unterminated\n", "unterminated section header")]:
+        f.write_text(text)
+        r = ml_bench("thesis", "parse", str(f), "sec")
+        assert r.returncode != 0 and why in r.stderr, (text, r.stderr)
+
+
+def test_thesis_options_and_committed_expectations():
+    """mod.rs:365-378: selection and validation of thesis ids; the committed file has a B200 section."""
+    r = ml_bench("thesis", "--list")
+    assert r.returncode == 0 and all(f"  t{i}  " in r.stdout for i in (1, 2, 4, 6, 7))
+    r = ml_bench("thesis", "t9")
+    assert r.returncode != 0 and "unknown thesis 't9'" in r.stderr
+    r = ml_bench("thesis", "--model")
+    assert r.returncode != 0 and "--model needs a value" in r.stderr
+    path = os.path.join(entry.PKG_DIR, "thesis-expectations.toml")
+    r = ml_bench("thesis", "parse", path, "NVIDIA B200")
+    keys = dict(line.split(" = ") for line in r.stdout.splitlines())
+    assert {"mem_bw_gbps", "t1_min_bw_frac", "t2_min_bw_frac", "t6_min_tflops", "t6_ref_tflops"} <= set(keys)
+    assert float(keys["mem_bw_gbps"]) > 1000
+
+
+@pytest.mark.gpu
+def test_thesis_kernel_level_rows_on_the_gpu():
+    """t2, t4 and t6 need no model: every row is printed with a verdict and none FAILs against the
+    committed B200 section (the tool's exit status is the gate)."""
+    r = ml_bench("thesis", "t2", "t4", "t6", ML_ITERS=10)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "performance-thesis results" in r.stdout
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("| T")]
+    assert sum(ln.startswith("| T2") for ln in lines) == 5 and sum(ln.startswith("| T6") for ln in lines) == 4
+    assert not any("FAIL" in ln for ln in lines)
+    assert all("umma" in ln for ln in lines if ln.startswith("| T6"))
+
+
+@pytest.mark.gpu
+def test_thesis_token_exactness_on_the_random_model():
+    r = ml_bench("thesis", "t7", "--random")
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("| T7")]
+    assert len(lines) == 4 and all("PASS" in ln and "17 / 17" in ln for ln in lines), r.stdout
