@@ -428,12 +428,19 @@ int ta_token_ids_set(ta_token_ids *ids, const uint32_t *tokens, uint32_t n); /* 
  *   PREFILL_QKV_PACK  in0 qkv [T, H*dh + 2*H_kv*dh] f32, in1 rope table, out q [H, T, dh] f32 (RoPE),
  *                     in2 kt cache [H_kv, dh, T_max] (RoPE'd k at positions rope.pos_base + t),
  *                     in3 v cache [H_kv, T_max, dh]; caches f32 or f16; rope = {H, dh, rot_dim,
- *                     pos_base}, u0 = H_kv (run_prefill_qkv_pack in the reference) */
+ *                     pos_base}, u0 = H_kv (run_prefill_qkv_pack in the reference)
+ *   ARGMAX_SHARDED    in0 = this rank's column slice of a row, u0 = global index of in0[0], comm, cell: every rank
+ *                     receives the index of the maximum over all ranks' slices (ties keep the largest index);
+ *                     one launch per rank, the ranks exchange one (value, index) pair each over peer memory.
+ *                     Needs a communicator with peer access; no counterpart in the reference.
+ * Inside a graph, `row-parallel GEMV (M = 1) -> ALL_REDUCE of its output -> GEMV reading that output`
+ * runs as two launches: the first pushes its partial row to every rank, the second sums the
+ * ranks' rows in rank order while it stages its activation; the tensor holds the sum afterwards. */
 enum {
   TA_EXEC_MATMUL = 0, TA_EXEC_RMS_NORM, TA_EXEC_LAYER_NORM, TA_EXEC_SOFTMAX_ROWS, TA_EXEC_ROPE,
   TA_EXEC_ROPE_SCATTER, TA_EXEC_COPY_STRIDED, TA_EXEC_BINARY, TA_EXEC_ATTN_DECODE, TA_EXEC_FLASH_ATTN,
   TA_EXEC_ARGMAX, TA_EXEC_EMBED_GATHER, TA_EXEC_EMBED_GATHER_ROWS, TA_EXEC_ALL_REDUCE, TA_EXEC_ALL_GATHER,
-  TA_EXEC_PREFILL_QKV_PACK
+  TA_EXEC_PREFILL_QKV_PACK, TA_EXEC_ARGMAX_SHARDED
 };
 
 /* Communicator for tensor-parallel graphs: one rank per process and GPU, NCCL over

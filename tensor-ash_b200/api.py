@@ -390,6 +390,7 @@ class ExecKind(enum.IntEnum):
     ALL_REDUCE = 13
     ALL_GATHER = 14
     PREFILL_QKV_PACK = 15
+    ARGMAX_SHARDED = 16
 
 
 class ExecOp:
@@ -496,6 +497,10 @@ class ExecOp:
         """RoPE(q) head-major, RoPE(k) into the Kt cache, v into the V cache, from one [T, n_qkv] row."""
         return cls(ExecKind.PREFILL_QKV_PACK, in0=qkv, in1=table, in2=kt, in3=v, out=q,
                    rope=(heads, head_dim, rot_dim, pos_base), u0=kv_heads)
+
+    @classmethod
+    def argmax_sharded(cls, inp, index_offset, result_cell, comm):
+        return cls(ExecKind.ARGMAX_SHARDED, in0=inp, u0=index_offset, cell=result_cell, comm=comm)
 
     @classmethod
     def all_reduce(cls, tensor, comm):

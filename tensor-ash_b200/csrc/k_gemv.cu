@@ -72,9 +72,22 @@ constexpr int RING_STAGE_BYTES = 16384;
 // 16-byte pieces from the ring instead of from global memory.  In-flight bytes per SM then
 // depend on shared memory (64 KiB per CTA), not on registers.
 // Three to eight rows over shapes the tensor-memory kernel (k_gemv_umma.cu) takes go there instead.
-template <int MROWS, int TN, bool BULK>
+// PEER: the launch takes part in a tensor-parallel exchange fused into it.  Pull: the activation x
+// is not read from memory but summed, in rank order, from what every rank pushed into this rank's
+// exchange buffer at the launch's exchange point (after a bounded wait for their arrival counts);
+// the first column tile also writes the sum to x_out for later readers.  Push: a segment's outputs
+// go to every rank's buffer instead of C, followed by one arrival per rank.  No extra launch.
+__device__ __forceinline__ const float *peer_slot(const PeerLink &l, uint32_t owner, uint32_t slot, uint32_t src) {
+  return reinterpret_cast<const float *>(l.buf[owner] + PEER_X_DATA_OFF) + ((size_t)slot * PEER_MAX_WORLD + src) * PEER_MAX_FLOATS;
+}
+__device__ __forceinline__ uint32_t *peer_arrivals(const PeerLink &l, uint32_t owner, uint32_t point, uint32_t src) {
+  return reinterpret_cast<uint32_t *>(l.buf[owner] + PEER_X_FLAG_OFF) + (size_t)point * PEER_MAX_WORLD + src;
+}
+
+template <int MROWS, int TN, bool BULK, bool PEER = false>
 __global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (BULK ? 3 : 4) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
+  static_assert(!PEER || !BULK, "the exchange variant is built for the register-streamed path");
   constexpr int U = GemvCfg<MROWS>::U;
   constexpr int LPR = TN / 8;                    // lanes per weight row (8 f16 per lane)
   constexpr int RPL = 32 / LPR;                  // weight rows per warp-wide load
@@ -177,6 +190,9 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   // fetch it now (it may live in host memory) so its latency hides behind the weights
   uint32_t pos = p.pos_base;
   if (p.pos_ptr && rank == 0 && p.store_kind != 0) pos += *p.pos_ptr;
+  uint32_t want = 0;   // arrivals per source rank that complete this use of the pulled point
+  if constexpr (PEER)
+    if (g.peer.pull_point1) want = *g.peer.expect_ptr;   // host-written before the submission, like the position
   // also independent of earlier kernels: the norm weights of the first slice elements
   // and this thread's rope table entry; epilogue operands (D, bias, old C) follow the wait
   float nwv[XS_PRE];
@@ -205,12 +221,52 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   // x'[k] = x[k] * s * w[k] with one scalar s per row, so s factors out of the dot
   // product: the slice is staged as x[k] * w[k] and rank 0 multiplies the finished
   // sums by s.  Only rank 0 needs s, and nothing waits for it before the epilogue.
+  const bool pull = PEER && g.peer.pull_point1 != 0;
+  if constexpr (PEER) {
+    if (pull) {
+      // every rank's push of this step must have landed here: arrivals[point][src] counts them
+      if (threadIdx.x < g.peer.world) {
+        const uint32_t *f = peer_arrivals(g.peer, g.peer.rank, g.peer.pull_point1 - 1, threadIdx.x);
+        const uint64_t t0 = umma::global_timer_ns();
+        uint32_t seen = 0, spins = 0;
+        for (;;) {
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+          if ((int32_t)(seen - want) >= 0) break;
+          if ((++spins & 255u) == 0 && umma::global_timer_ns() - t0 > g.peer.limit_ns) {
+            if (g.status) atomicOr(g.status, 4u);     // reported by the host; the sums below are then invalid
+            break;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  // x[m, k]: from memory, or the rank-ordered sum of the pushed partial rows
+  auto xval = [&](uint32_t m, uint32_t k) -> float {
+    if constexpr (PEER) {
+      if (pull) {
+        float acc = 0.0f;
+        for (uint32_t r = 0; r < g.peer.world; ++r)
+          acc += __ldcg(peer_slot(g.peer, g.peer.rank, g.peer.pull_slot, r) + (size_t)m * p.k + k);
+        return acc;
+      }
+    }
+    return p.x[(size_t)m * p.k + k];
+  };
   const uint32_t stage_n = k_len * MROWS;
   float xv[XS_PRE];
 #pragma unroll
   for (int it = 0; it < XS_PRE; ++it) {
     const uint32_t idx = threadIdx.x + it * GEMV_THREADS, kk = idx / MROWS, m = idx % MROWS;
-    xv[it] = (idx < stage_n && m < p.m) ? p.x[(size_t)m * p.k + k_lo + kk] : 0.0f;
+    xv[it] = (idx < stage_n && m < p.m) ? xval(m, k_lo + kk) : 0.0f;
+  }
+  if constexpr (PEER) {
+    // the first column tile leaves the summed activation where later launches expect x
+    if (pull && g.peer.x_out && tile_all == 0)
+      for (uint32_t idx = threadIdx.x; idx < stage_n; idx += GEMV_THREADS) {
+        const uint32_t kk = idx / MROWS, m = idx % MROWS;
+        if (m < p.m) g.peer.x_out[(size_t)m * p.k + k_lo + kk] = xval(m, k_lo + kk);
+      }
   }
   if (e_valid && p.store_kind == 0) {
     if (p.d) pre_d = p.d[e_ci];
@@ -222,7 +278,12 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
 #pragma unroll
     for (int m = 0; m < MROWS; ++m) {
       ss[m] = 0.0f;
-      if ((uint32_t)m < p.m) {
+      if ((uint32_t)m < p.m && pull) {
+        for (uint32_t k = threadIdx.x; k < p.k; k += GEMV_THREADS) {
+          const float a = xval(m, k);
+          ss[m] = fmaf(a, a, ss[m]);
+        }
+      } else if ((uint32_t)m < p.m) {
         const float *xr = p.x + (size_t)m * p.k;
         if ((p.k & 3u) == 0 && (reinterpret_cast<uintptr_t>(xr) & 15u) == 0) {
           for (uint32_t k = threadIdx.x * 4; k < p.k; k += GEMV_THREADS * 4) {
@@ -253,7 +314,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     for (int m = 0; m < MROWS; ++m) {
       const bool row = (uint32_t)m < p.m;
       for (uint32_t kk = kk_done + threadIdx.x; kk < k_len; kk += GEMV_THREADS) {
-        float v = row ? p.x[(size_t)m * p.k + k_lo + kk] : 0.0f;
+        float v = row ? xval(m, k_lo + kk) : 0.0f;
         if (row && p.norm_w) v *= p.norm_w[k_lo + kk];
         xs[(size_t)kk * MROWS + m] = v;
       }
@@ -263,7 +324,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       const uint32_t kk = idx / MROWS, m = idx % MROWS;
       float v = 0.0f;
       if (m < p.m) {
-        v = p.x[(size_t)m * p.k + k_lo + kk];
+        v = xval(m, k_lo + kk);
         if (p.norm_w) v *= p.norm_w[k_lo + kk];
       }
       xs[idx] = v;
@@ -415,7 +476,15 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       const float bv = p.bias ? (first ? pre_bias : p.bias[c]) : 0.0f;
       const float dv = p.d ? (first ? pre_d : p.d[ci]) : 0.0f;
       v = epi_apply(v, p.bias != nullptr, bv, p.act, p.binary, dv, p.beta);
-      p.c[ci] = v;
+      bool pushed = false;
+      if constexpr (PEER) {
+        if (p.push_point1) {     // this rank's partial row into every rank's buffer (its own included)
+          for (uint32_t r = 0; r < g.peer.world; ++r)
+            const_cast<float *>(peer_slot(g.peer, r, p.push_slot, g.peer.rank))[ci] = v;
+          pushed = true;
+        }
+      }
+      if (!pushed) p.c[ci] = v;
     } else {
       if (p.store_kind != 2) {   // rope with the partner column (c ^ 1)
         const float partner = fin[idx ^ 1];
@@ -434,6 +503,16 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       }
     }
   }
+  if constexpr (PEER) {
+    if (p.push_point1) {
+      // this tile's stores are out: make them visible system-wide, then one arrival per rank
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < g.peer.world)
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_arrivals(g.peer, threadIdx.x, p.push_point1 - 1, g.peer.rank))
+                     : "memory");
+    }
+  }
 }
 
 size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s, bool bulk = false) {
@@ -444,14 +523,14 @@ size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s, bool bulk 
 
 bool pdl_enabled() { return tunables().pdl; }
 
-template <int MROWS, int TN, bool BULK>
+template <int MROWS, int TN, bool BULK, bool PEER = false>
 void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   const size_t smem = gemv_smem_bytes(g.k_cta, MROWS, TN, g.ksplit, BULK);
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  200 * 1024));
     attr_done[dev & 63] = true;
   }
@@ -474,7 +553,7 @@ void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK>, g));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK, PEER>, g));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -512,11 +591,13 @@ bool gemv_routes_to_umma(const GemvParams &p) {
 }
 
 void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg, bool pdl, const GemvWorkspace &ws,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, const PeerLink *peer) {
   if (nseg < 1 || nseg > GEMV_MAX_SEGS) fail("GEMV group of %d segments (1..%d)", nseg, GEMV_MAX_SEGS);
   const int sm_count = ctx.sm_count;
   uint32_t *status = ws.status;
-  if (nseg == 1 && gemv_routes_to_umma(segs[0]) && ws.scratch && ws.counters &&
+  if (peer && (segs[0].m != 1 || peer->world < 2 || peer->world > PEER_MAX_WORLD))
+    fail("internal: the fused tensor-parallel exchange is built for single-row GEMVs on 2..%u ranks", PEER_MAX_WORLD);
+  if (!peer && nseg == 1 && gemv_routes_to_umma(segs[0]) && ws.scratch && ws.counters &&
       ws.scratch_bytes >= gemv_umma_scratch_bytes(segs[0].n, segs[0].k, segs[0].w2 != nullptr, sm_count)) {
     launch_gemv_umma(ctx, segs[0], static_cast<float *>(ws.scratch), ws.scratch_bytes, ws.counters, status, pdl, stream);
     return;
@@ -534,6 +615,7 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
   g.nseg = (uint32_t)nseg;
   g.pdl = (pdl && pdl_enabled()) ? 1u : 0u;
   g.status = status;
+  if (peer) g.peer = *peer;
   const int mrows = p0.m <= 1 ? 1 : p0.m <= 2 ? 2 : p0.m <= 4 ? 4 : 8;
   const uint32_t u = 4;
   const uint32_t rpl = 32 / (tn / 8);
@@ -543,14 +625,14 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
   // per SM that is one wave for this launch and leaves room for the early CTAs of
   // the next launch, which prefetch their weights while this one finishes.  Never
   // split below one pass of rows.
-  bool bulk = bulk_possible(segs, nseg);   // bulk-copy ring: packed tiles (contiguous per CTA), 16-byte aligned bases
+  bool bulk = !peer && bulk_possible(segs, nseg);   // bulk-copy ring: packed tiles (contiguous per CTA), 16-byte aligned bases
   uint64_t weight_bytes = 0;
   for (int i = 0; i < nseg; ++i) weight_bytes += (uint64_t)segs[i].k * segs[i].n * 2 * (segs[i].w2 ? 2 : 1);
   if (p0.m > 2) bulk = false;   // more rows: the staged x slice and the accumulators need the space
   // measured: the ring wins on long streams (4096 x 11008: 3.8 -> 4.8 TB/s) and is neutral to
   // slightly slower on the few-MB matrices of a decode step, which are latency-bound
   if (weight_bytes < (64ull << 20)) bulk = false;
-  if (tunables().gemv_bulk >= 0) bulk = tunables().gemv_bulk != 0 && p0.m <= 2 && bulk_possible(segs, nseg);
+  if (tunables().gemv_bulk >= 0) bulk = !peer && tunables().gemv_bulk != 0 && p0.m <= 2 && bulk_possible(segs, nseg);
   uint32_t best_s = 1;
   if (weight_bytes >= (64ull << 20) && mrows <= 2) {
     // Large matrices stream: about eight passes per CTA amortise its prologue and epilogue
@@ -593,11 +675,23 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
     }                                                                             \
     return;                                                                       \
   }
+  if (peer) {
+    if (tn == 64) launch_t<1, 64, false, true>(g, tiles, stream);
+    else launch_t<1, 32, false, true>(g, tiles, stream);
+    return;
+  }
   TA_GEMV_CASE(1)
   TA_GEMV_CASE(2)
   TA_GEMV_CASE(4)
   TA_GEMV_CASE(8)
 #undef TA_GEMV_CASE
+}
+
+uint32_t gemv_f16w_tiles(const GemvParams *segs, int nseg) {
+  const uint32_t tn = segs[0].packed ? segs[0].tile_n : 32;
+  uint32_t tiles = 0;
+  for (int i = 0; i < nseg; ++i) tiles += (segs[i].n + tn - 1) / tn;
+  return tiles;
 }
 
 void launch_gemv_f16w(const Context &ctx, GemvParams p, const GemvWorkspace &ws, cudaStream_t stream) {

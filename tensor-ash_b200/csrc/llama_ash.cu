@@ -215,6 +215,8 @@ struct ta_llama {
   TokenIds token_ids;
   std::unique_ptr<PreparedOps> decode_graph;
   std::unique_ptr<PrefillScratch> prefill_full;
+  bool logits_stale = false;   // sharded decode: `logits` holds the last gathered row, not the last step's
+  bool pos_last_decode = false;   // the most recent step was a decode step (not a prefill)
   uint32_t pos = 0;
   ~ta_llama();
 };
@@ -439,10 +441,21 @@ void push_mlp_ops(ta_llama &m, std::vector<ExecOp> &ops, Layer &L, bool decode, 
 
 // lm_head on one normed row; sharded ranks gather their logit slices (rank order =
 // vocabulary order) so that every rank takes the same argmax over the whole vocabulary.
-void push_head_ops(ta_llama &m, std::vector<ExecOp> &ops, ExecOp head) {
+void push_head_ops(ta_llama &m, std::vector<ExecOp> &ops, ExecOp head, bool decode) {
   if (m.world == 1) {
     head.mm.call.c = &m.logits;
     ops.push_back(head);
+  } else if (decode && m.comm->fused_exchange_ready()) {
+    // every rank folds its own slice and the ranks exchange one (value, index) pair each: no
+    // gather of the vocabulary on the token path (ta_llama_logits gathers on demand)
+    head.mm.call.c = &m.logits_l;
+    ops.push_back(head);
+    ExecOp am;
+    am.kind = ExecKind::ArgmaxSharded;
+    am.in0 = &m.logits_l; am.cell = &m.token_cell; am.comm = m.comm; am.u0 = m.rank * m.vocab_l;
+    ops.push_back(am);
+    m.logits_stale = true;
+    return;
   } else {
     head.mm.call.c = &m.logits_l;
     ops.push_back(head);
@@ -476,7 +489,7 @@ std::vector<const char *> decode_op_classes(ta_llama &m) {
     if (tp) cls.push_back("all_reduce");
   }
   cls.push_back("lm_head_mm");
-  if (tp) cls.push_back("all_gather");
+  if (tp && !m.comm->fused_exchange_ready()) cls.push_back("all_gather");
   cls.push_back("argmax");
   cls.push_back("embed_gather");
   return cls;
@@ -516,7 +529,7 @@ std::vector<ExecOp> decode_ops(ta_llama &m) {
   }
   ExecOp head = mm_op(*x_in, m.lm_head_p, m.logits);
   head.mm.packed_b = true; head.mm.normed_weight = &m.output_norm; head.mm.normed_eps = eps;
-  push_head_ops(m, ops, head);
+  push_head_ops(m, ops, head, true);
   ExecOp eg;
   eg.kind = ExecKind::EmbedGather;
   eg.cell = &m.token_cell; eg.in0 = &m.embd; eg.out = &m.x_a;
@@ -587,7 +600,7 @@ std::vector<ExecOp> prefill_ops(ta_llama &m, PrefillScratch &s, uint32_t t, uint
   n.kind = ExecKind::RmsNorm;
   n.in0 = &s.last; n.in1 = &m.output_norm; n.out = &s.last_n; n.f0 = c.rms_eps;
   ops.push_back(n);
-  push_head_ops(m, ops, mm_op(s.last_n, m.lm_head, m.logits));
+  push_head_ops(m, ops, mm_op(s.last_n, m.lm_head, m.logits), false);
   return ops;
 }
 
@@ -849,6 +862,7 @@ int ta_llama_prefill(ta_llama *model, const uint32_t *tokens, uint32_t n, uint32
     m.token_ids.len = n;
     const RunStats st = m.exec->run_exec_ops(prefill_ops(m, s, n, m.pos));
     m.pos += n;
+    m.pos_last_decode = false;
     if (next_token) *next_token = *(volatile uint32_t *)m.token_cell.host;
     write_stats(stats, st);
   });
@@ -874,6 +888,7 @@ int ta_llama_decode(ta_llama *model, uint32_t first_token, uint32_t n, uint32_t 
       const RunStats st = m.decode_graph->run();
       out_tokens[i] = *(volatile uint32_t *)m.token_cell.host;
       m.pos += 1;
+      m.pos_last_decode = true;
       *total.gpu_time_ns += st.gpu_time_ns.value_or(0);
       total.n_calls += st.n_calls;
       total.total_flops += st.total_flops;
@@ -899,6 +914,7 @@ int ta_llama_decode_breakdown(ta_llama *model, uint32_t token, ta_llama_breakdow
     std::vector<std::pair<size_t, uint64_t>> per_launch;
     m.exec->run_exec_ops_timed(ops, &per_launch);
     m.pos += 1;
+    m.pos_last_decode = true;
     if (next_token) *next_token = *(volatile uint32_t *)m.token_cell.host;
     if (n_launches) *n_launches = per_launch.size();
     // a launch that fuses several ops (q, k, v; up + gate) is booked under its first op's class
@@ -921,7 +937,15 @@ int ta_llama_logits(ta_llama *model, float *out, size_t len) {
   return guarded([&]() {
     if (!model) fail("ta_llama_logits: model is null");
     if (!out) fail("ta_llama_logits: out is null");
-    model->exec->download(model->logits, out, std::min(len, (size_t)model->cfg.vocab));
+    ta_llama &m = *model;
+    if (m.world > 1 && m.logits_stale && m.pos_last_decode) {
+      // the sharded decode step keeps only this rank's slice: gather now (collective: every rank calls)
+      ExecOp ag;
+      ag.kind = ExecKind::AllGather;
+      ag.in0 = &m.logits_l; ag.out = &m.logits; ag.comm = m.comm;
+      m.exec->run_exec_ops({ag});
+    }
+    m.exec->download(m.logits, out, std::min(len, (size_t)m.cfg.vocab));
   });
 }
 

@@ -609,7 +609,7 @@ static std::vector<ExecOp> checked_exec_ops(const ta_executor &e, const ta_exec_
     const ta_exec_op &r = ops[i];
     const std::string label = strf("%s: op %zu", operation, i);
     ExecOp &o = v[i];
-    if (r.kind > TA_EXEC_PREFILL_QKV_PACK) fail("%s: kind %u is invalid", label.c_str(), r.kind);
+    if (r.kind > TA_EXEC_ARGMAX_SHARDED) fail("%s: kind %u is invalid", label.c_str(), r.kind);
     o.kind = (ExecKind)r.kind;
     if (r.kind == TA_EXEC_MATMUL) o.mm = checked_op_ex(e, r.mm, label);
     auto opt = [&](const ta_tensor *t, const char *name) -> const Tensor * {

@@ -86,10 +86,12 @@ NcclApi &nccl_required() {
 // ------------------------------------------------------------------ peer-write all-reduce
 // Exchange buffer of one rank: data[2 parities][world][PEER_MAX_FLOATS] then
 // flags[2][world][PEER_MAX_CTAS] then epoch[PEER_MAX_CTAS] (this rank's call counters).
-constexpr uint32_t PEER_MAX_FLOATS = 8192, PEER_MAX_CTAS = 8, PEER_MAX_WORLD = 8, PEER_THREADS = 256;
-constexpr size_t PEER_DATA_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_FLOATS * sizeof(float);
-constexpr size_t PEER_FLAG_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_CTAS * sizeof(uint32_t);
-constexpr size_t PEER_BUF_BYTES = PEER_DATA_BYTES + PEER_FLAG_BYTES + PEER_MAX_CTAS * sizeof(uint32_t);
+constexpr uint32_t PEER_MAX_CTAS = 8, PEER_THREADS = 256;
+constexpr size_t PEER_DATA_BYTES = PEER_AR_DATA_BYTES;
+constexpr size_t PEER_FLAG_BYTES = PEER_AR_FLAG_BYTES;
+static_assert(PEER_AR_FLAG_BYTES == 2ull * PEER_MAX_WORLD * PEER_MAX_CTAS * sizeof(uint32_t), "flag layout");
+static_assert(PEER_AR_BYTES % 16 == 0 && PEER_AR_BYTES >= PEER_DATA_BYTES + PEER_FLAG_BYTES + PEER_MAX_CTAS * sizeof(uint32_t), "layout");
+constexpr size_t PEER_BUF_BYTES = PEER_BUF_TOTAL;   // all-reduce kernel region + fused-exchange region
 
 struct PeerTable {
   uint8_t *buf[PEER_MAX_WORLD];   // every rank's exchange buffer as mapped in this process
@@ -164,6 +166,111 @@ peer_all_reduce_kernel(float *data, uint32_t count, PeerTable t, uint32_t *statu
     *epoch_p = ticket;
     if (!ok_flag && status) atomicOr(status, 4u);
   }
+}
+
+// ------------------------------------------------------------------ sharded argmax
+// Greedy pick over a vocabulary whose logits are split by column over the ranks: every rank folds
+// its own slice to one (value, global index) pair, pushes the pair into every rank's buffer, waits
+// (bounded) for the others' pairs and folds the `world` pairs in rank order with the same rule as
+// the single-device kernel -- the maximum, ties to the LARGEST index
+// (shaders/op_argmax_f32.comp:44-75) -- so that all ranks write the same token.  One launch per
+// rank; replaces gathering the whole vocabulary.  NaNs never win.
+constexpr int AMAX_THREADS = 1024;
+__device__ __forceinline__ void amax_fold(float &bv, uint32_t &bi, float v, uint32_t i) {
+  if (v > bv || (v == bv && i > bi)) {
+    bv = v;
+    bi = i;
+  }
+}
+__global__ void __launch_bounds__(AMAX_THREADS)
+argmax_sharded_kernel(const float *__restrict__ in, uint32_t n, uint32_t index_offset, PeerLink l, uint32_t *result,
+                      uint32_t *status, uint32_t pdl) {
+  __shared__ float sval[AMAX_THREADS / 32];
+  __shared__ uint32_t sidx[AMAX_THREADS / 32];
+  const uint32_t tid = threadIdx.x;
+  const uint32_t step = *l.expect_ptr;    // arrivals word of the pair exchange, host-written before the submission
+  if (pdl) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+  float bv = -INFINITY;
+  uint32_t bi = 0;
+  for (uint32_t i = tid; i < n; i += AMAX_THREADS) amax_fold(bv, bi, in[i], i);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    amax_fold(bv, bi, ov, oi);
+  }
+  if ((tid & 31u) == 0) {
+    sval[tid >> 5] = bv;
+    sidx[tid >> 5] = bi;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    bv = sval[tid];
+    bi = sidx[tid];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      amax_fold(bv, bi, ov, oi);
+    }
+    // lanes 0 .. world-1: lane r hands this rank's pair to rank r, then raises the arrival word there
+    if (tid < l.world) {
+      // pairs alternate between two slots by use parity: a rank can be one use ahead of a peer, never two
+      uint2 *pair = reinterpret_cast<uint2 *>(l.buf[tid] + PEER_AMAX_PAIR_OFF) + (step & 1u) * PEER_MAX_WORLD + l.rank;
+      uint32_t *flag = reinterpret_cast<uint32_t *>(l.buf[tid] + PEER_AMAX_FLAG_OFF) + l.rank;
+      *pair = make_uint2(__float_as_uint(bv), bi + index_offset);
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+      // ... and waits for rank r's pair in this rank's own buffer
+      const uint32_t *mine = reinterpret_cast<const uint32_t *>(l.buf[l.rank] + PEER_AMAX_FLAG_OFF) + tid;
+      const uint64_t t0 = [] { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }();
+      uint32_t seen = 0, spins = 0;
+      for (;;) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if ((int32_t)(seen - step) >= 0) break;
+        if ((++spins & 255u) == 0) {
+          uint64_t now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (now - t0 > l.limit_ns) {
+            if (status) atomicOr(status, 4u);
+            break;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (tid == 0) {
+      float fv = -INFINITY;
+      uint32_t fi = 0;
+      for (uint32_t r = 0; r < l.world; ++r) {   // rank order; the fold is order-independent anyway
+        const uint2 pr = __ldcg(reinterpret_cast<const uint2 *>(l.buf[l.rank] + PEER_AMAX_PAIR_OFF) + (step & 1u) * PEER_MAX_WORLD + r);
+        amax_fold(fv, fi, __uint_as_float(pr.x), pr.y);
+      }
+      *result = fi;
+    }
+  }
+}
+
+bool Comm::argmax_sharded(const float *in, uint32_t n, uint32_t index_offset, uint32_t *result, uint32_t *status,
+                          cudaStream_t stream) const {
+  if (!fused_exchange_ready() || world < 2 || world > PEER_MAX_WORLD) return false;
+  PeerLink l = link();
+  l.expect_ptr = expect_device + PEER_MAX_POINTS;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, 1, 1);
+  cfg.blockDim = dim3(AMAX_THREADS, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, argmax_sharded_kernel, in, n, index_offset, l, result, status, 1u));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return true;
 }
 
 void comm_unique_id(uint8_t out[COMM_ID_BYTES]) {
@@ -244,6 +351,23 @@ void Comm::setup_peer_exchange() {
   }
   peer_own = buf;
   peer_bufs = mapped;
+  if (cudaHostAlloc((void **)&expect_host, (PEER_MAX_POINTS + 1) * sizeof(uint32_t), cudaHostAllocMapped) == cudaSuccess) {
+    memset(expect_host, 0, (PEER_MAX_POINTS + 1) * sizeof(uint32_t));
+    if (cudaHostGetDevicePointer((void **)&expect_device, expect_host, 0) != cudaSuccess) expect_device = nullptr;
+  } else {
+    cudaGetLastError();
+    expect_host = nullptr;
+  }
+}
+
+PeerLink Comm::link() const {
+  PeerLink l{};
+  for (uint32_t r = 0; r < world && r < PEER_MAX_WORLD; ++r) l.buf[r] = static_cast<uint8_t *>(peer_bufs[r]);
+  l.rank = rank;
+  l.world = world;
+  l.expect_ptr = nullptr;
+  l.limit_ns = peer_wait_limit_ns;
+  return l;
 }
 
 bool Comm::peer_all_reduce_sum(float *data, size_t count, uint32_t *status, bool pdl, cudaStream_t stream) const {
@@ -287,6 +411,7 @@ void Comm::resync() {
     if (pass == 0 && peer_own) {
       TA_CUDA(cudaMemset(static_cast<uint8_t *>(peer_own) + PEER_DATA_BYTES, 0, PEER_BUF_BYTES - PEER_DATA_BYTES));
       TA_CUDA(cudaDeviceSynchronize());
+      if (expect_host) memset(expect_host, 0, (PEER_MAX_POINTS + 1) * sizeof(uint32_t));
     }
   }
   cudaStreamDestroy(st);
@@ -301,6 +426,7 @@ Comm::~Comm() {
       if (r != rank && r < peer_bufs.size() && peer_bufs[r]) cudaIpcCloseMemHandle(peer_bufs[r]);
     cudaFree(peer_own);
   }
+  if (expect_host) cudaFreeHost(expect_host);
   if (handle) nccl().CommDestroy(handle);
 }
 

@@ -329,6 +329,25 @@ struct GemvParams {
   const float *table;
   void *dst;
   const uint32_t *pos_ptr;
+  // tensor-parallel exchange fused into the store: instead of C, the outputs go to slot `push_slot`
+  // of every rank's exchange buffer as this rank's contribution to exchange point push_point1 - 1
+  // (0 = off: an ordinary store)
+  uint32_t push_point1, push_slot;
+};
+
+// Exchange buffers of a tensor-parallel group as one rank sees them, and what a GEMV launch pulls
+// from them: its activation x is the sum over ranks (rank order) of what they pushed at
+// `pull_point1 - 1` (0 = off).  `pull_tiles` arrivals per rank and step complete a push.
+constexpr uint32_t PEER_MAX_WORLD = 8, PEER_MAX_FLOATS = 8192, PEER_MAX_POINTS = 256;
+struct PeerLink {
+  uint8_t *buf[PEER_MAX_WORLD];
+  uint32_t rank, world;
+  uint32_t pull_point1, pull_tiles, pull_slot;
+  float *x_out;                 // where the summed activation is also written (by the first column tile)
+  // arrivals per source rank that complete the current use of the pulled point (or, for the sharded
+  // argmax, of the pair exchange): a host-written word the host advances before every submission
+  const uint32_t *expect_ptr;
+  uint64_t limit_ns;            // bounded wait for the peers' arrivals
 };
 
 // Up to three GEMVs sharing x, M, K, norm and tile width in one launch.
@@ -340,6 +359,7 @@ struct GemvGroup {
   uint32_t ksplit, k_cta;             // cluster size along K and rows per rank
   uint32_t pdl;                       // 1: launched with programmatic stream serialization
   uint32_t *status;                   // device word for bounded-wait timeouts (may be null)
+  PeerLink peer;                      // world == 0: no tensor-parallel exchange in this launch
 };
 
 struct FlashParams {
@@ -404,13 +424,29 @@ struct TokenIds {
 //   Argmax           in0 input; cell = result word
 //   EmbedGather      cell = token word; in0 table, out
 //   EmbedGatherRows  tokens; in0 table, out [n, embd]
+//   ArgmaxSharded    in0 this rank's slice of the row, comm, cell = result word; u0 = global index of in0[0]
 enum class ExecKind : uint32_t {
   Matmul = 0, RmsNorm, LayerNorm, SoftmaxRows, Rope, RopeScatter, CopyStrided, Binary, AttnDecode,
-  FlashAttn, Argmax, EmbedGather, EmbedGatherRows, AllReduce, AllGather, PrefillQkvPack
+  FlashAttn, Argmax, EmbedGather, EmbedGatherRows, AllReduce, AllGather, PrefillQkvPack, ArgmaxSharded
 };
 
 // ------------------------------------------------------------------ communicator (tensor parallel)
 constexpr size_t COMM_ID_BYTES = 128;
+// Layout of one rank's exchange buffer (all ranks map all buffers):
+//   [0, PEER_AR_BYTES)        the one-launch all-reduce kernel: data, flags, call counters
+//   then the fused exchange:  data[2 slots][world][PEER_MAX_FLOATS] f32,
+//                             arrivals[PEER_MAX_POINTS][world] u32 (monotonic),
+//                             argmax pairs[2][world] (value bits, index; slot = use parity) and arrivals[world] u32
+constexpr size_t PEER_AR_DATA_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_FLOATS * sizeof(float);
+constexpr size_t PEER_AR_FLAG_BYTES = 2ull * PEER_MAX_WORLD * 8 * sizeof(uint32_t);
+constexpr size_t PEER_AR_BYTES = PEER_AR_DATA_BYTES + PEER_AR_FLAG_BYTES + 8 * sizeof(uint32_t) + 96;   // 16-byte multiple
+constexpr size_t PEER_X_DATA_OFF = PEER_AR_BYTES;
+constexpr size_t PEER_X_DATA_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_FLOATS * sizeof(float);
+constexpr size_t PEER_X_FLAG_OFF = PEER_X_DATA_OFF + PEER_X_DATA_BYTES;
+constexpr size_t PEER_X_FLAG_BYTES = (size_t)PEER_MAX_POINTS * PEER_MAX_WORLD * sizeof(uint32_t);
+constexpr size_t PEER_AMAX_PAIR_OFF = PEER_X_FLAG_OFF + PEER_X_FLAG_BYTES;
+constexpr size_t PEER_AMAX_FLAG_OFF = PEER_AMAX_PAIR_OFF + 2 * PEER_MAX_WORLD * 8;   // pairs of two consecutive uses
+constexpr size_t PEER_BUF_TOTAL = PEER_AMAX_FLAG_OFF + PEER_MAX_WORLD * sizeof(uint32_t);
 void comm_unique_id(uint8_t out[COMM_ID_BYTES]);
 struct Comm {
   std::shared_ptr<Context> ctx;
@@ -422,6 +458,17 @@ struct Comm {
   // of them still loads weights or instantiates a graph
   uint64_t peer_wait_limit_ns = 10000000000ull;
   std::vector<void *> peer_bufs;       // every rank's buffer as mapped here (index = rank)
+  // Exchanges fused into kernels count arrivals: word p of this pinned, device-mapped array is the
+  // number of arrivals per source rank that completes the current use of exchange point p (word
+  // PEER_MAX_POINTS: of the argmax pair exchange).  The host advances the words of the points a
+  // submission uses before it launches; kernels read them like the position cell.  Every rank
+  // submits the same plans in the same order, so the words agree across ranks.
+  uint32_t *expect_host = nullptr, *expect_device = nullptr;
+  bool fused_exchange_ready() const { return peer_own != nullptr && expect_device != nullptr; }
+  PeerLink link() const;   // buffers, rank, world, wait limit; pull fields zero
+  // one-launch greedy pick over column-sharded logits; false when the peer path is unavailable
+  bool argmax_sharded(const float *in, uint32_t n, uint32_t index_offset, uint32_t *result, uint32_t *status,
+                      cudaStream_t stream) const;
   void setup_peer_exchange();
   void resync();
   // one-launch peer-write all-reduce; false when the request does not fit it (caller uses NCCL)
@@ -431,6 +478,18 @@ struct Comm {
   ~Comm();
   void all_reduce_sum(float *data, size_t count, cudaStream_t stream) const;   // in place
   void all_gather(const float *src, float *dst, size_t count_per_rank, cudaStream_t stream) const;
+};
+
+// The fused exchange points one submission uses: (point, arrivals per source rank), point
+// PEER_MAX_POINTS standing for the argmax pair exchange.  advance() is called on the host right
+// before the submission is launched.
+struct ExchangeUse {
+  const Comm *comm = nullptr;
+  std::vector<std::pair<uint32_t, uint32_t>> points;
+  void advance() const {
+    if (!comm || !comm->expect_host) return;
+    for (const auto &pt : points) *(volatile uint32_t *)(comm->expect_host + pt.first) += pt.second;
+  }
 };
 
 struct ExecOp {
@@ -577,8 +636,11 @@ class Executor {
   size_t splitk2_scratch_bytes(const MatmulOp &op, const ResolvedMatmul &r, uint32_t splits) const;
   bool gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route, GemvParams *out) const;
   // first_op (optional): for every planned launch, the index of the first op of `ops` it executes
+  // exchange (optional): receives the fused exchange points of the plan; the caller advances them
+  // before every submission
   std::vector<Launch> plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops, size_t *n_calls,
-                                    size_t *scratch_bytes = nullptr, std::vector<size_t> *first_op = nullptr) const;
+                                    size_t *scratch_bytes = nullptr, std::vector<size_t> *first_op = nullptr,
+                                    ExchangeUse *exchange = nullptr) const;
   RunStats run_exec_ops_timed(const std::vector<ExecOp> &ops, std::vector<std::pair<size_t, uint64_t>> *per_launch);
   RunStats swiglu_gemv(const Tensor &x, const Tensor &wg, const Tensor &wup, const Tensor &out,
                        const Tensor *norm_w, float eps);
@@ -664,6 +726,7 @@ struct PreparedOps {
   void *scratch = nullptr;
   uint32_t *counters = nullptr;   // this object's own ticket words
   uint32_t *status = nullptr, *status_host = nullptr;   // this object's own status word (see Slot)
+  ExchangeUse exchange;              // fused exchange points every submission of this object uses
   size_t n_calls = 0;
   uint64_t total_flops = 0;
   bool in_flight = false;
@@ -718,8 +781,11 @@ size_t gemv_umma_scratch_bytes(uint32_t n, uint32_t k, bool dual, int sm_count);
 void launch_gemv_umma(const Context &ctx, const GemvParams &p, float *scratch, size_t scratch_bytes, uint32_t *counters,
                       uint32_t *status, bool pdl, cudaStream_t stream);
 bool gemv_f16w_groupable(const GemvParams &a, const GemvParams &b);
+// peer (optional): the launch takes part in a fused tensor-parallel exchange (single-row GEMVs)
 void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg, bool pdl, const GemvWorkspace &ws,
-                            cudaStream_t stream);
+                            cudaStream_t stream, const PeerLink *peer = nullptr);
+// number of column tiles (= pushing CTAs) of a GEMV launch over these segments
+uint32_t gemv_f16w_tiles(const GemvParams *segs, int nseg);
 
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream);
 void launch_attn_decode(const AttnDecodeParams &p, cudaStream_t stream);

@@ -357,6 +357,25 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       uint32_t *rp = o.cell->device;
       return [=](Slot &, cudaStream_t st) { launch_argmax(ip, n, rp, st); };
     }
+    case ExecKind::ArgmaxSharded: {
+      const Tensor &in = need(o.in0, "run_argmax_sharded", "input");
+      ensure_f32(*this, in, "run_argmax_sharded", "input");
+      if (!o.cell) fail("run_argmax_sharded: result cell is null");
+      if (o.cell->ctx.get() != ctx_.get()) fail("run_argmax_sharded: result buffer belongs to a different context");
+      if (!o.comm) fail("run_argmax_sharded: communicator is null");
+      if (o.comm->ctx.get() != ctx_.get()) fail("run_argmax_sharded: communicator belongs to a different context");
+      if (in.len() > 0xffffffffull) fail("run_argmax_sharded: input too large");
+      if (!o.comm->fused_exchange_ready())
+        fail("run_argmax_sharded: the communicator has no peer exchange (one rank, or peer access unavailable); "
+             "gather the slices and use the plain argmax");
+      const Comm *comm = o.comm;
+      const float *ip = (const float *)in.ptr();
+      const uint32_t n = (uint32_t)in.len(), off = o.u0;
+      uint32_t *rp = o.cell->device;
+      return [=](Slot &slot, cudaStream_t st) {
+        if (!comm->argmax_sharded(ip, n, off, rp, slot.status, st)) fail("run_argmax_sharded: peer exchange unavailable");
+      };
+    }
     case ExecKind::EmbedGather:
     case ExecKind::EmbedGatherRows: {
       const bool rows = o.kind == ExecKind::EmbedGatherRows;
@@ -469,7 +488,7 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
 // boundary is the barrier, so independent ops share a launch instead.
 std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint64_t *flops,
                                             size_t *n_calls, size_t *scratch_bytes,
-                                            std::vector<size_t> *first_op) const {
+                                            std::vector<size_t> *first_op, ExchangeUse *exchange) const {
   struct Cand {
     bool gemv = false;
     GemvParams g{};
@@ -495,9 +514,58 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
   std::vector<Launch> plan;
   plan.reserve(ops.size());
   std::vector<GemvParams> prev_gemv;   // segments of the launch planned last, when it was a GEMV
+  // Tensor-parallel exchange fused into its neighbours.  `row-parallel GEMV -> all-reduce of its
+  // one-row output -> GEMV reading that row` becomes two launches: the first pushes its partial
+  // row into every rank's exchange buffer, the second waits for all ranks' rows, adds them in rank
+  // order while it stages x, and leaves the sum in the tensor for later readers.  The same values
+  // in the same order on every rank, as the separate all-reduce gives.
+  struct Pending {
+    const void *tensor = nullptr;
+    uint32_t point = 0, tiles = 0, slot = 0;
+    const Comm *comm = nullptr;
+  } pending;
+  uint32_t next_point = 0;
+  auto fusable_push = [&](size_t at, const Cand &c) -> const Comm * {
+    if (!tunables().peer_allreduce || !c.gemv || at + 2 >= ops.size() || next_point >= PEER_MAX_POINTS) return nullptr;
+    const ExecOp &ar = ops[at + 1];
+    if (ar.kind != ExecKind::AllReduce || !ar.comm || !ar.out || !ar.comm->fused_exchange_ready()) return nullptr;
+    const GemvParams &gp = c.g;
+    if (gp.m != 1 || gp.store_kind != 0 || gp.w2 || (uint64_t)gp.m * gp.n > PEER_MAX_FLOATS) return nullptr;
+    if (ar.out->ptr() != (const void *)gp.c || ar.out->len() != (uint64_t)gp.m * gp.n) return nullptr;
+    const Cand nxt = candidate(ops[at + 2]);
+    if (!nxt.gemv || nxt.g.m != 1 || (const void *)nxt.g.x != (const void *)gp.c || nxt.g.k != gp.n) return nullptr;
+    return ar.comm;
+  };
+  // exchange link of a GEMV launch: pulls `pending` when the launch reads that tensor as x
+  auto link_for = [&](const GemvParams &first_seg, const Comm *push_comm, bool *has_link) {
+    PeerLink link{};
+    *has_link = false;
+    const Comm *comm = push_comm;
+    if (pending.tensor && (const void *)first_seg.x == pending.tensor) {
+      comm = pending.comm;
+      link = comm->link();
+      link.pull_point1 = pending.point + 1;
+      link.pull_tiles = pending.tiles;
+      link.pull_slot = pending.slot;
+      link.x_out = const_cast<float *>(first_seg.x);
+      link.expect_ptr = comm->expect_device + pending.point;
+      if (exchange) {
+        exchange->comm = comm;
+        exchange->points.emplace_back(pending.point, pending.tiles);
+      }
+      pending = Pending{};
+      *has_link = true;
+    } else if (comm) {
+      link = comm->link();
+      *has_link = true;
+    }
+    return link;
+  };
   size_t i = 0;
   while (i < ops.size()) {
     Cand c0 = candidate(ops[i]);
+    if (pending.tensor && !(c0.gemv && (const void *)c0.g.x == pending.tensor))
+      fail("internal: a fused tensor-parallel push is not followed by the launch that pulls it");
     if (!c0.gemv) {
       ExecOp op = ops[i];
       // two f16w tensor-core GEMMs in a row on the same A (up and gate of a prefill MLP): the f16
@@ -528,6 +596,10 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         }
         op.u0 = ok ? 1u : 0u;
       }
+      if (op.kind == ExecKind::ArgmaxSharded && exchange && op.comm) {
+        exchange->comm = op.comm;
+        exchange->points.emplace_back(PEER_MAX_POINTS, 1u);
+      }
       plan.push_back(plan_exec_op(op, flops, n_calls));
       if (first_op) first_op->push_back(i);
       prev_gemv.clear();
@@ -550,12 +622,39 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         f.act = 0; f.binary = 0; f.d = nullptr;
         if (flops) *flops += c0.flops + c1.flops;
         if (n_calls) *n_calls += 2;
-        plan.push_back([f, cx](Slot &slot, cudaStream_t st) { launch_gemv_f16w_group(*cx, &f, 1, true, gemv_workspace(slot), st); });
+        bool has_link = false;
+        const PeerLink link = link_for(f, nullptr, &has_link);
+        plan.push_back([f, cx, link, has_link](Slot &slot, cudaStream_t st) {
+          launch_gemv_f16w_group(*cx, &f, 1, true, gemv_workspace(slot), st, has_link ? &link : nullptr);
+        });
         if (first_op) first_op->push_back(i);
         prev_gemv.assign(1, f);
         i += 2;
         continue;
       }
+    }
+    // a row-parallel projection whose one-row output is all-reduced next and read by a GEMV after that
+    if (const Comm *push_comm = fusable_push(i, c0)) {
+      GemvParams f = c0.g;
+      f.push_point1 = next_point + 1;
+      f.push_slot = next_point & 1u;
+      bool has_link = false;
+      const PeerLink link = link_for(f, push_comm, &has_link);
+      pending.tensor = f.c;
+      pending.point = next_point;
+      pending.slot = f.push_slot;
+      pending.tiles = gemv_f16w_tiles(&f, 1);
+      pending.comm = push_comm;
+      ++next_point;
+      if (flops) *flops += c0.flops;
+      if (n_calls) *n_calls += 2;   // the projection and the all-reduce it carries
+      plan.push_back([f, cx, link](Slot &slot, cudaStream_t st) {
+        launch_gemv_f16w_group(*cx, &f, 1, true, gemv_workspace(slot), st, &link);
+      });
+      if (first_op) first_op->push_back(i);
+      prev_gemv.assign(1, f);
+      i += 2;
+      continue;
     }
     // group of independent GEMVs on the same x
     std::vector<GemvParams> segs{c0.g};
@@ -578,13 +677,16 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     }
     if (flops) *flops += fl;
     if (n_calls) *n_calls += segs.size();
-    plan.push_back([segs, cx](Slot &slot, cudaStream_t st) {
-      launch_gemv_f16w_group(*cx, segs.data(), (int)segs.size(), true, gemv_workspace(slot), st);
+    bool has_link = false;
+    const PeerLink link = link_for(segs[0], nullptr, &has_link);
+    plan.push_back([segs, cx, link, has_link](Slot &slot, cudaStream_t st) {
+      launch_gemv_f16w_group(*cx, segs.data(), (int)segs.size(), true, gemv_workspace(slot), st, has_link ? &link : nullptr);
     });
     if (first_op) first_op->push_back(i);
     prev_gemv = segs;
     i = j;
   }
+  if (pending.tensor) fail("internal: a fused tensor-parallel push is not followed by the launch that pulls it");
   return plan;
 }
 
@@ -593,11 +695,13 @@ RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
   uint64_t flops = 0;
   size_t n_calls = 0;
   size_t scratch_bytes = 0;
-  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls, &scratch_bytes);
+  ExchangeUse exchange;
+  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls, &scratch_bytes, nullptr, &exchange);
   ctx_->make_current();
   Slot &slot = checkout_slot();
   SlotGuard g(*this, slot);
   if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
+  exchange.advance();   // kernels with fused exchanges wait for the arrival counts of this submission
   return timed(slot, n_calls, flops, [&](cudaStream_t st) {
     for (const Launch &l : plan) l(slot, st);
   });
@@ -610,11 +714,13 @@ RunStats Executor::run_exec_ops_timed(const std::vector<ExecOp> &ops, std::vecto
   uint64_t flops = 0;
   size_t n_calls = 0, scratch_bytes = 0;
   std::vector<size_t> first_op;
-  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls, &scratch_bytes, &first_op);
+  ExchangeUse exchange;
+  std::vector<Launch> plan = plan_exec_ops(ops, &flops, &n_calls, &scratch_bytes, &first_op, &exchange);
   ctx_->make_current();
   Slot &slot = checkout_slot();
   SlotGuard g(*this, slot);
   if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
+  exchange.advance();
   std::vector<cudaEvent_t> ev(plan.size() + 1);
   for (cudaEvent_t &e : ev) TA_CUDA(cudaEventCreate(&e));
   RunStats st;
@@ -658,7 +764,8 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
   prep->exec = &exec;
   prep->ctx = exec.context();
   size_t scratch_bytes = 0;
-  std::vector<Launch> plan = exec.plan_exec_ops(ops, &prep->total_flops, &prep->n_calls, &scratch_bytes);
+  std::vector<Launch> plan = exec.plan_exec_ops(ops, &prep->total_flops, &prep->n_calls, &scratch_bytes, nullptr,
+                                                &prep->exchange);
   if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));
   TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
   TA_CUDA(cudaEventCreate(&prep->ev_begin));

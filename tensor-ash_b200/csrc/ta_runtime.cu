@@ -909,6 +909,7 @@ PreparedOps::~PreparedOps() {
 void PreparedOps::submit() {
   if (in_flight) fail("PreparedOps::submit: a submission is already in flight; call wait() first");
   exec->context()->make_current();
+  exchange.advance();   // the replay's fused exchanges wait for the arrival counts of this submission
   TA_CUDA(cudaEventRecord(ev_begin, stream));
   TA_CUDA(cudaGraphLaunch(graph_exec, stream));
   TA_CUDA(cudaEventRecord(ev_end, stream));

@@ -95,6 +95,28 @@ def main_cpu():
         got = sh.forward(step_tokens)
         err = np.abs(got - want).max() / np.abs(want).max()
         assert err < 1e-12, f"rank {rank}: sharded host forward differs, rel {err:.3e}"
+    # sharded greedy pick: every rank folds its vocabulary slice to one (value, global index) pair, the
+    # ranks exchange the pairs and fold them with the same rule -- the maximum, ties to the LARGEST
+    # index (shaders/op_argmax_f32.comp:44-75) -- so a tie that spans ranks resolves as on one device
+    def fold(pairs):
+        bv, bi = -np.inf, 0
+        for v, i in pairs:
+            if v > bv or (v == bv and i > bi):
+                bv, bi = v, i
+        return bv, bi
+
+    vocab_l = 96
+    full = np.random.default_rng(99).standard_normal(world * vocab_l).astype(np.float32)
+    top = float(full.max()) + 1.0
+    tie_at = [5, vocab_l + 7, (world - 1) * vocab_l + 3]         # the same maximum on the first, second and last rank
+    full[tie_at] = top
+    mine = full[rank * vocab_l:(rank + 1) * vocab_l]
+    local = fold((float(v), rank * vocab_l + i) for i, v in enumerate(mine))
+    gathered = [None] * world
+    dist.all_gather_object(gathered, local)
+    _, picked = fold(gathered)
+    want = max(i for i, v in enumerate(full) if v == top)
+    assert picked == want == max(tie_at), f"rank {rank}: sharded argmax picked {picked}, one device picks {want}"
     dist.barrier()
     dist.destroy_process_group()
     print("TP-CPU-OK", rank)
@@ -131,6 +153,23 @@ def main_gpu():
         if top[1] - top[0] > 1e-3 * np.abs(want).max():
             assert toks[i] == int(np.argmax(want)), f"rank {rank} step {i}"
         fed = toks[i]
+    # logits after sharded decode steps are gathered on demand and must match the host forward
+    got = model.logits().astype(np.float64)
+    err = np.abs(got - want).max() / np.abs(want).max()
+    assert err <= 2e-4, f"rank {rank}: decode logits rel err {err:.3e}"
+    # the sharded argmax op on its own, with the same maximum placed on the first and the last rank
+    vocab_l = 4000
+    sl = np.random.default_rng(7 + rank).standard_normal(vocab_l).astype(np.float32)
+    if rank == 0:
+        sl[11] = 50.0
+    if rank == world - 1:
+        sl[123] = 50.0
+    t_sl = ta.Tensor.uninit_device(ctx, (vocab_l,))
+    ex.upload(sl, t_sl)
+    cell = ta.PosCell(ctx)
+    for _ in range(3):      # repeated uses advance the arrival words in step on every rank
+        ex.run_exec_ops([ta.ExecOp.argmax_sharded(t_sl, rank * vocab_l, cell, comm)])
+        assert cell.get() == (world - 1) * vocab_l + 123, f"rank {rank}: sharded argmax {cell.get()}"
     # every rank must hold the same token stream
     t = torch.tensor(toks, dtype=torch.int64, device="cuda")
     ref_t = t.clone()
