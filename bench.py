@@ -238,11 +238,23 @@ def bench_llama(ta, ctx, comm, world: int, peaks: dict) -> dict:
     gbs = wbytes / (dec * 1e-3) / 1e9
     # the 129 greedy tokens (prefill's + 128 decoded) of the 1-GPU run that was checked against the
     # float64 host forward (tests/test_llama_full_size.py): every tensor-parallel width must reproduce them
+    # A tensor-parallel width adds the ranks' partial sums in another order than one GPU does, so a
+    # step whose float64 top-2 margin lies under the gate recorded in the file may legitimately pick
+    # the runner-up; from there the streams differ.  A difference at a step above the gate is an error.
     golden_path = os.path.join(ROOT, "tests", "golden", "llama_config5_tokens.json")
     tokens_match = None
     if os.path.exists(golden_path):
         with open(golden_path) as f:
-            tokens_match = ([int(nxt)] + [int(t) for t in toks]) == json.load(f)["tokens"]
+            gold = json.load(f)
+        got = [int(nxt)] + [int(t) for t in toks]
+        first = next((i for i, (a, b) in enumerate(zip(got, gold["tokens"])) if a != b), None)
+        if first is None:
+            tokens_match = True
+        elif first in gold["steps_under_margin_gate"]:
+            tokens_match = f"identical up to step {first}, whose float64 top-2 margin " \
+                           f"{gold['float64_top2_margin_rel'][first]:.1e} is under the gate {gold['margin_gate']:.0e}"
+        else:
+            tokens_match = False
     out = {
         "config": "configs[4]: llama 22L/2048/32q/4kv/5632/32000 f16 weights, f16 KV, pp512 + tg128",
         "tp": world, "tokens_match_golden": tokens_match,

@@ -349,28 +349,52 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
         const float *grp_rec = g.scratch + (size_t)grp * g.teams * GU_REC_FLOATS;
         const uint32_t col = grp * cols_per_group + (g.dual ? (tid & 63u) : tid);
         if (col >= p.n || (g.dual && tid >= 64)) continue;
-#pragma unroll 1
-        for (uint32_t m = 0; m < p.m; ++m) {
-          float s0 = 0.0f, s1 = 0.0f, ss = 0.0f;
-          for (uint32_t sl = 0; sl < g.teams; ++sl) {
-            const float *r = grp_rec + (size_t)sl * GU_REC_FLOATS;
-            s0 += __ldcg(r + m * 128 + tid);
-            if (g.dual) s1 += __ldcg(r + m * 128 + 64 + tid);
-            if (p.norm_w) ss += __ldcg(r + 8 * 128 + m);
+        // every record's values for all rows are requested before any is consumed: one L2 round
+        // trip per group, whatever the row count (slices in order: a fixed sum)
+        float s0[8], s1[8], ssum[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) { s0[m] = 0.0f; s1[m] = 0.0f; ssum[m] = 0.0f; }
+#pragma unroll 2
+        for (uint32_t sl = 0; sl < g.teams; ++sl) {
+          const float *r = grp_rec + (size_t)sl * GU_REC_FLOATS;
+          float a[8], b[8], q[8];
+#pragma unroll
+          for (int m = 0; m < 8; ++m) {
+            const bool live = (uint32_t)m < p.m;
+            a[m] = live ? __ldcg(r + m * 128 + tid) : 0.0f;
+            b[m] = (live && g.dual) ? __ldcg(r + m * 128 + 64 + tid) : 0.0f;
+            q[m] = (live && p.norm_w) ? __ldcg(r + 8 * 128 + m) : 0.0f;
           }
+#pragma unroll
+          for (int m = 0; m < 8; ++m) { s0[m] += a[m]; s1[m] += b[m]; ssum[m] += q[m]; }
+        }
+        // epilogue operands of all rows, again in one batch
+        float oldc[8], dv[8];
+        const float bv = p.bias ? p.bias[col] : 0.0f;
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          const bool live = (uint32_t)m < p.m;
+          const size_t ci = (size_t)m * p.n + col;
+          oldc[m] = (live && p.accumulate) ? p.c[ci] : 0.0f;
+          dv[m] = (live && p.d) ? p.d[ci] : 0.0f;
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          if ((uint32_t)m >= p.m) break;
+          float v0 = s0[m], v1 = s1[m];
           if (p.norm_w) {
-            const float rs = rsqrtf(ss / (float)p.k + p.norm_eps);
-            s0 *= rs;
-            s1 *= rs;
+            const float rs = rsqrtf(ssum[m] / (float)p.k + p.norm_eps);
+            v0 *= rs;
+            v1 *= rs;
           }
           const size_t ci = (size_t)m * p.n + col;
-          float o = p.alpha == 1.0f ? s0 : p.alpha * s0;
+          float o = p.alpha == 1.0f ? v0 : p.alpha * v0;
           if (g.dual) {
-            o = epi_activate(o, 2) * s1;
-            if (p.c2) p.c2[ci] = s1;
+            o = epi_activate(o, 2) * v1;
+            if (p.c2) p.c2[ci] = v1;
           }
-          if (p.accumulate) o += p.c[ci];
-          o = epi_apply(o, p.bias != nullptr, p.bias ? p.bias[col] : 0.0f, p.act, p.binary, p.d ? p.d[ci] : 0.0f, p.beta);
+          if (p.accumulate) o += oldc[m];
+          o = epi_apply(o, p.bias != nullptr, bv, p.act, p.binary, dv[m], p.beta);
           p.c[ci] = o;
         }
       }

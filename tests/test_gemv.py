@@ -117,7 +117,8 @@ def test_normed_a_and_epilogue(gpu, orc):
                                      packed_b=True, normed_a=(nw, eps))], as_graph=True)
         ex.swiglu_gemv(x, w, w2, fused, nw, eps)
         a, b = ex.download(gated), ex.download(fused)
-        assert np.abs(a - b).max() <= 1e-6 * max(1.0, float(np.abs(a).max()))
+        # the pair launch and the two single launches may cut K differently: same values up to f32 summation order
+        assert np.abs(a - b).max() <= 1e-5 * max(1.0, float(np.abs(a).max()))
     # residual add (AddScaled) on the row-major route, as the o / down projections use it
     x, hx = upload_det(ta, ctx, ex, orc, (1, 5632), 545)
     w, hw = make_weights(ta, ctx, ex, orc, 5632, 2048, 546, False)
