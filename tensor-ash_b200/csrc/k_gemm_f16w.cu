@@ -280,16 +280,20 @@ struct PreCfg {
   static constexpr int A_BYTES = BM * PK * 2;             // 16 KiB
   static constexpr int B_BYTES = PK * BN * 2;             // 32 KiB at BN = 256
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
   // + per epilogue warp a 32 x 32 f32 transpose buffer (row pitch 36 floats: conflict-free
   // float4 writes by row and float4 reads by 8-lane row segments)
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 4 * 32 * EPI_PITCH * 4 + 1024;
-  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;  // tensor-memory columns between the two accumulators
+  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;         // 128, 256 or 512: powers of two
 };
 
 __global__ void __launch_bounds__(256)
 convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint32_t k, uint32_t kp, uint64_t rows) {
   // one thread per 8 output halves (16 bytes); the pad columns k..kp-1 are zeros
+  // the GEMM launched behind this kernel may set itself up while this one runs; it waits for this
+  // grid to finish before it reads the copy
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const uint32_t per_row = kp / 8;
   if (idx >= rows * per_row) return;
@@ -311,7 +315,14 @@ convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint
 }
 
 
-template <int BN>
+// SPLITK: for problems whose tiles fill less than one wave of SMs.  A unit is (tile, K slice s of S);
+// units = tiles * S is at most the SM count, so every unit has its own resident CTA.  Each CTA
+// accumulates its K slice in tensor memory and stores the raw 128 x BN partial tile to scratch;
+// when all S partials of a tile have arrived (a ticket per tile, bounded wait), each of the S CTAs
+// adds the partials of ITS column slice of the tile in slice order and runs the epilogue on it.
+// The order of the sum is fixed, so results are run-to-run bit-identical, and the reduction is
+// spread over the CTAs that would otherwise idle.
+template <int BN, bool SPLITK>
 __global__ void __launch_bounds__(PRE_THREADS, 1)
 gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, uint32_t *__restrict__ status) {
@@ -348,20 +359,36 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // launched with programmatic stream serialization behind the conversion of A: barriers, tensor
+  // memory and the tensor maps are set up by now; nothing below touches global memory before the
+  // conversion kernel has finished
+  if (p.pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const uint32_t tiles_per_batch = tiles_m * tiles_n;
-  const uint32_t num_tiles = tiles_per_batch * p.batch;
-  const uint32_t k_blocks = (p.k + PK - 1) / PK;
+  const uint32_t splits = SPLITK ? p.fw_splits : 1u;
+  const uint32_t num_tiles = tiles_per_batch * p.batch * splits;     // work units
+  const uint32_t k_blocks_all = (p.k + PK - 1) / PK;
+  // unit -> tile (batch, position), K slice and its K blocks [kb_lo, kb_hi): slices of one tile are
+  // neighbouring units, so their CTAs run side by side
+  auto decode = [&](uint32_t unit, uint32_t &tile_id, uint32_t &slice, uint32_t &kb_lo, uint32_t &kb_hi) {
+    tile_id = unit / splits;
+    slice = unit % splits;
+    const uint32_t per = k_blocks_all / splits, rem = k_blocks_all % splits;
+    kb_lo = slice * per + min(slice, rem);
+    kb_hi = kb_lo + per + (slice < rem ? 1u : 0u);
+  };
 
   if (warp == 4) {
     uint32_t stage = 0, phase = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    for (uint32_t unit = blockIdx.x; ok && unit < num_tiles; unit += gridDim.x) {
+      uint32_t tile, slice, kb_lo, kb_hi;
+      decode(unit, tile, slice, kb_lo, kb_hi);
       const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
       const int m0 = (int)(rem % tiles_m) * BM, n0 = (int)(rem / tiles_m) * BN;
       const int za = p.stride_a ? (int)batch : 0, zb = p.stride_b ? (int)batch : 0;
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+      for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
         if (!ok) break;
         const uint32_t dst = smem_base + stage * C::STAGE_BYTES;
@@ -384,13 +411,15 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
     const uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     uint32_t stage = 0, phase = 0, acc_it = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+    for (uint32_t unit = blockIdx.x; ok && unit < num_tiles; unit += gridDim.x, ++acc_it) {
+      uint32_t tile, slice, kb_lo, kb_hi;
+      decode(unit, tile, slice, kb_lo, kb_hi);
       const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
       ok = mbar_wait(acc_empty(buf), acc_phase ^ 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * BN;
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+      const uint32_t d_tmem = tmem_base + buf * C::ACC_STRIDE;
+      for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         ok = mbar_wait(full(stage), phase, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -402,9 +431,9 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
         if (elect_one()) {
 #pragma unroll
           for (int j = 0; j < PK / 16; ++j)
-            mma_f16(d_tmem, da0 + (uint64_t)(j * 2), db0 + (uint64_t)(j * 128), idesc, (kb | (uint32_t)j) != 0u);
+            mma_f16(d_tmem, da0 + (uint64_t)(j * 2), db0 + (uint64_t)(j * 128), idesc, ((kb - kb_lo) | (uint32_t)j) != 0u);
           tc_commit(empty(stage));
-          if (kb + 1 == k_blocks) tc_commit(acc_full(buf));
+          if (kb + 1 == kb_hi) tc_commit(acc_full(buf));
         }
         __syncwarp();
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -414,13 +443,101 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
     uint32_t acc_it = 0;
     bool ok = true;
     const bool alpha_is_one = p.alpha == 1.0f;
-    for (uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++acc_it) {
+    for (uint32_t unit = blockIdx.x; ok && unit < num_tiles; unit += gridDim.x, ++acc_it) {
+      uint32_t tile, slice, kb_lo, kb_hi;
+      decode(unit, tile, slice, kb_lo, kb_hi);
       const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
       const uint32_t m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
       const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
       ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
       if (!ok) break;
       tc_fence_after();
+      if constexpr (SPLITK) {
+        // ---- raw partial tile to scratch, transposed so that stores cover full row segments
+        float *__restrict__ tbuf = epi_buf + warp * (32 * EPI_PITCH);
+        const uint32_t cq = (uint32_t)(lane & 7) * 4, rsub = (uint32_t)lane >> 3;
+        float *__restrict__ part = p.fw_partials + (size_t)unit * (BM * BN);
+        const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          tmem_ld32(taddr + c0, v);
+#pragma unroll
+          for (int q = 0; q < 32; q += 4)
+            *reinterpret_cast<float4 *>(tbuf + lane * EPI_PITCH + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t r = (uint32_t)i * 4 + rsub;
+            *reinterpret_cast<float4 *>(part + (size_t)(warp * 32 + r) * BN + c0 + cq) =
+                *reinterpret_cast<const float4 *>(tbuf + r * EPI_PITCH + cq);
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        mbar_arrive(acc_empty(buf));
+        // ---- ticket: wait (bounded) until every slice of this tile has stored its partial
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0) {
+          atomicAdd(&p.fw_counters[2 * tile], 1u);
+          const uint64_t t0 = global_timer_ns();
+          uint32_t seen = 0, spins = 0;
+          for (;;) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.fw_counters + 2 * tile) : "memory");
+            if (seen >= splits) break;
+            if ((++spins & 63u) == 0 && (*abort_flag || global_timer_ns() - t0 > WAIT_LIMIT_NS)) {
+              *abort_flag = 1;
+              break;
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abort_flag) { ok = false; break; }
+        __threadfence();
+        // ---- this CTA's column slice of the tile: add the S partials in slice order, epilogue, store
+        const uint32_t cols = BN / splits;                      // splits divides BN / 4
+        const uint32_t lanes_per_row = cols / 4;
+        const float *__restrict__ tile_parts = p.fw_partials + (size_t)tile * splits * (BM * BN);
+        const size_t plane_off = (size_t)batch * p.stride_c;
+        const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
+        epi_dispatch_act(p.act, [&](auto act_tag) {
+          constexpr uint32_t ACT = decltype(act_tag)::value;
+          for (uint32_t idx = lane; idx < 32u * lanes_per_row; idx += 32) {
+            const uint32_t r = warp * 32 + idx / lanes_per_row, c = slice * cols + (idx % lanes_per_row) * 4;
+            const uint32_t row = m0 + r, col = n0 + c;
+            if (row >= p.m || col >= p.n) continue;
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t t = 0; t < splits; ++t) {
+              const float4 v = __ldcg(reinterpret_cast<const float4 *>(tile_parts + (size_t)t * (BM * BN) + (size_t)r * BN + c));
+              o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+            }
+            if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+            const size_t off = plane_off + (size_t)row * p.n + col;
+            if (p.accumulate) {
+              const float4 c_old = *reinterpret_cast<const float4 *>(p.c + off);
+              o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+            }
+            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+            if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+            if (p.d) dv = *reinterpret_cast<const float4 *>(p.d + off);
+            o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
+            o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
+            o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
+            o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
+            *reinterpret_cast<float4 *>(p.c + off) = o;
+          }
+        });
+        // ---- the last slice to finish reading puts the tile's two ticket words back to zero
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0) {
+          if (atomicAdd(&p.fw_counters[2 * tile + 1], 1u) == splits - 1) {
+            p.fw_counters[2 * tile] = 0u;
+            p.fw_counters[2 * tile + 1] = 0u;
+          }
+        }
+        continue;
+      }
       // TMEM gives each lane one row; a row-per-lane store would touch 32 rows per instruction.
       // Transpose 32 x 32 blocks through shared memory so that every global access of the
       // epilogue (C, D, the old C when accumulating) covers full 128-byte row segments.
@@ -428,7 +545,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       const uint32_t cq = (uint32_t)(lane & 7) * 4, rsub = (uint32_t)lane >> 3;
       const size_t plane_off = (size_t)batch * p.stride_c;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
-      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(warp * 32) << 16);
+      const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(warp * 32) << 16);
       // one dispatch on the activation per tile; the chunk loop below is compiled per activation
       epi_dispatch_act(p.act, [&](auto act_tag) {
         constexpr uint32_t ACT = decltype(act_tag)::value;
@@ -503,13 +620,13 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   }
 }
 
-template <int BN>
+template <int BN, bool SPLITK = false>
 void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t kp, uint32_t *status,
                   bool a16_ready, cudaStream_t stream) {
   using C = PreCfg<BN>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx.device & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemm_f16w_pre_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    TA_CUDA(cudaFuncSetAttribute(gemm_f16w_pre_kernel<BN, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set[ctx.device & 63] = true;
   }
   const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
@@ -533,10 +650,22 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   else
     encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, p.n, p.k, bb, (uint64_t)p.n * 2, b_batch_bytes, 64, PK,
                 CU_TENSOR_MAP_SWIZZLE_128B);
-  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch;
+  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch * (SPLITK ? p.fw_splits : 1u);
+  if (SPLITK && tiles > (uint64_t)ctx.sm_count) fail("internal: split-K units (%llu) exceed the SM count", (unsigned long long)tiles);
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
-  gemm_f16w_pre_kernel<BN><<<grid, PRE_THREADS, C::SMEM_BYTES, stream>>>(pg, map_a, map_b, status);
-  TA_CUDA(cudaGetLastError());
+  // right behind the conversion kernel: start early, wait on the device (see the kernel)
+  pg.pdl_wait = (!a16_ready && tunables().pdl) ? 1u : 0u;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(PRE_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pg.pdl_wait ? 1 : 0;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemm_f16w_pre_kernel<BN, SPLITK>, pg, map_a, map_b, status));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -602,9 +731,48 @@ uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_co
 // Row pitch (in halves) of the f16 copy of A: K rounded up to 8, plus the experiment switch f16w_apad.
 static uint32_t a16_pitch(uint32_t k) { return ((k + 7u) & ~7u) + tunables().f16w_apad; }
 
-// Scratch bytes for the f16 copy of A.
-size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
-  return (size_t)((uint64_t)batch_a * m * a16_pitch(k) * 2);
+// Scratch bytes for the f16 copy of A (rounded up to 256) ...
+static size_t a16_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
+  return ((size_t)((uint64_t)batch_a * m * a16_pitch(k) * 2) + 255u) & ~(size_t)255u;
+}
+size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) { return a16_bytes(batch_a, m, k); }
+
+// Tile width and K split for a problem on the pre-converted-A kernel.  The 512-row prefill shapes
+// have 32..176 tiles for 148 SMs and measure about 60 GB/s of operand traffic per CTA, so what a
+// CTA moves decides the time: cost = K blocks per CTA x bytes per block (A 16 KiB + B BN x 128 B),
+// plus a fixed charge for the split's partial-tile round trip.  Units (tiles x splits) must not
+// exceed the SM count when splitting; several waves without a split are charged in full.
+F16wPlan gemm_f16w_umma_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count, bool allow_split) {
+  F16wPlan best;
+  double best_cost = 1e300;
+  const uint32_t kb = (k + PK - 1) / PK;
+  const int force = tunables().f16w_splitk;
+  for (uint32_t bn : {256u, 192u, 128u, 64u}) {
+    const uint64_t tiles = (uint64_t)batch * ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
+    const double block_kb = 16.0 + bn * 0.125;
+    for (uint32_t s : {1u, 2u, 3u, 4u, 6u, 8u}) {
+      if (s > 1 && (!allow_split || force == 0 || force == 1)) break;
+      if (s > 1 && (tiles * s > (uint64_t)sm_count || kb / s < 4 || (bn / 4) % s != 0)) continue;
+      if (force > 1 && s != (uint32_t)force && tiles * (uint64_t)force <= (uint64_t)sm_count && kb / force >= 4 && (bn / 4) % force == 0) continue;
+      const uint64_t waves = s > 1 ? 1 : (tiles + sm_count - 1) / sm_count;
+      const double cost = (double)waves * ((kb + s - 1) / s) * block_kb + (s > 1 ? 150.0 : 0.0) + 90.0 +
+                          (bn == 192 && n % 192 ? 8.0 : 0.0);   // a partial last tile wastes part of its columns
+      if (cost < best_cost) {
+        best_cost = cost;
+        best.tile_n = bn;
+        best.splits = s;
+      }
+    }
+  }
+  best.partial_bytes = best.splits > 1
+                           ? (size_t)batch * ((m + BM - 1) / BM) * ((n + best.tile_n - 1) / best.tile_n) * best.splits * BM * best.tile_n * 4
+                           : 0;
+  return best;
+}
+
+size_t gemm_f16w_umma_scratch_bytes_split(uint32_t batch, uint32_t batch_a, uint32_t m, uint32_t n, uint32_t k, int sm_count) {
+  const F16wPlan plan = gemm_f16w_umma_plan(batch, m, n, k, sm_count, true);
+  return a16_bytes(batch_a, m, k) + plan.partial_bytes;
 }
 
 void launch_gemm_a16_umma(const Context &ctx, const GemmParams &p_in, uint32_t tile_n, uint32_t *status,
@@ -622,20 +790,41 @@ void launch_gemm_a16_umma(const Context &ctx, const GemmParams &p_in, uint32_t t
   else launch_pre_t<64>(ctx, p, a16, p.k, status, true, stream);
 }
 
-void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
-                           void *scratch, size_t scratch_bytes, bool a16_ready, cudaStream_t stream) {
-  if (!gemm_f16w_umma_eligible(p))
+void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p_in, uint32_t tile_n, uint32_t *status,
+                           void *scratch, size_t scratch_bytes, bool a16_ready, cudaStream_t stream,
+                           uint32_t *counters, bool auto_plan) {
+  if (!gemm_f16w_umma_eligible(p_in))
     fail("f16w tensor-core GEMM needs f32 A, f16 B, K %% 4 == 0 and N %% 8 == 0");
-  const uint32_t batch_a = p.stride_a ? p.batch : 1;
-  if (scratch && scratch_bytes >= gemm_f16w_umma_scratch_bytes(batch_a, p.m, p.k) &&
+  const uint32_t batch_a = p_in.stride_a ? p_in.batch : 1;
+  if (scratch && scratch_bytes >= gemm_f16w_umma_scratch_bytes(batch_a, p_in.m, p_in.k) &&
       (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0 && tunables().f16w_pre) {
-    const uint32_t kp = a16_pitch(p.k);
+    const uint32_t kp = a16_pitch(p_in.k);
     __half *a16 = static_cast<__half *>(scratch);
+    GemmParams p = p_in;
+    if (auto_plan) {
+      // the routing heuristic's call: tile width and K split chosen together for this shape
+      const F16wPlan plan = gemm_f16w_umma_plan(p.batch, p.m, p.n, p.k, ctx.sm_count, counters != nullptr);
+      const size_t a16b = a16_bytes(batch_a, p.m, p.k);
+      if (plan.splits > 1 && counters && scratch_bytes >= a16b + plan.partial_bytes) {
+        p.fw_splits = plan.splits;
+        p.fw_partials = reinterpret_cast<float *>(static_cast<uint8_t *>(scratch) + a16b);
+        p.fw_counters = counters + F16W_SPLIT_COUNTER0;
+        if (plan.tile_n == 256) launch_pre_t<256, true>(ctx, p, a16, kp, status, a16_ready, stream);
+        else if (plan.tile_n == 192) launch_pre_t<192, true>(ctx, p, a16, kp, status, a16_ready, stream);
+        else if (plan.tile_n == 128) launch_pre_t<128, true>(ctx, p, a16, kp, status, a16_ready, stream);
+        else launch_pre_t<64, true>(ctx, p, a16, kp, status, a16_ready, stream);
+        return;
+      }
+      const F16wPlan whole = plan.splits > 1 ? gemm_f16w_umma_plan(p.batch, p.m, p.n, p.k, ctx.sm_count, false) : plan;
+      tile_n = whole.tile_n;
+    }
     if (tile_n >= 256) launch_pre_t<256>(ctx, p, a16, kp, status, a16_ready, stream);
+    else if (tile_n == 192) launch_pre_t<192>(ctx, p, a16, kp, status, a16_ready, stream);
     else if (tile_n >= 128) launch_pre_t<128>(ctx, p, a16, kp, status, a16_ready, stream);
     else launch_pre_t<64>(ctx, p, a16, kp, status, a16_ready, stream);
     return;
   }
+  const GemmParams &p = p_in;
   if (tile_n >= 256) launch_t<256>(ctx, p, status, stream);
   else if (tile_n >= 128) launch_t<128>(ctx, p, status, stream);
   else launch_t<64>(ctx, p, status, stream);

@@ -300,7 +300,21 @@ struct GemmParams {
   // caller-visible split and per plane, destination of the planes
   uint32_t sk_subs = 0, sk_c = 0, sk_kb_per_split = 0, sk_kb_per_sub = 0;
   float *sk_planes = nullptr;
+  // f16-weight tensor-core GEMM with an in-kernel K split (launcher-set): slices per tile, partial
+  // tiles in scratch, two ticket words per tile
+  uint32_t fw_splits = 0;
+  float *fw_partials = nullptr;
+  uint32_t *fw_counters = nullptr;
+  uint32_t pdl_wait = 0;     // launcher-set: the kernel was launched to overlap its predecessor and waits for it on the device
 };
+
+// Tile width / K split of the f16-weight tensor-core GEMM for a shape (see k_gemm_f16w.cu)
+struct F16wPlan {
+  uint32_t tile_n = 256, splits = 1;
+  size_t partial_bytes = 0;
+};
+F16wPlan gemm_f16w_umma_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count, bool allow_split);
+size_t gemm_f16w_umma_scratch_bytes_split(uint32_t batch, uint32_t batch_a, uint32_t m, uint32_t n, uint32_t k, int sm_count);
 
 // How the tensor-core stage 1 of split-K2 cuts a problem (see k_gemm_tf32x3.cu).  `planes` per batch
 // = splits * c; eligible = false keeps the problem on the SIMT stage 1.
@@ -514,8 +528,9 @@ using Launch = std::function<void(Slot &, cudaStream_t)>;
 
 constexpr uint32_t ATTN_DECODE_MAX_CHUNKS = 32;
 constexpr uint32_t ATTN_DECODE_MAX_KV_HEADS = 256;
-// ticket words per slot / prepared object: [0, 256) decode attention (one per kv head), the rest GEMV column groups
-constexpr uint32_t SLOT_COUNTERS = 256 + 4096;
+// ticket words per slot / prepared object: [0, 256) decode attention (one per kv head), then GEMV column groups
+constexpr uint32_t F16W_SPLIT_COUNTER0 = 256 + 4096;   // then two words per tile of a split f16-weight GEMM
+constexpr uint32_t SLOT_COUNTERS = F16W_SPLIT_COUNTER0 + 512;
 inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
   const uint32_t c = (kv_len + 31) / 32;
   return c < 8 ? 8 : (c > ATTN_DECODE_MAX_CHUNKS ? ATTN_DECODE_MAX_CHUNKS : c);
@@ -524,6 +539,7 @@ inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
 struct Route {
   int kernel = -1;       // index into KERNEL_SPECS
   uint32_t splits = 0;   // >1: two-stage split-K route
+  bool tuned = false;    // the kernel is a measured winner from the tuned store
 };
 
 // ------------------------------------------------------------------ executor
@@ -754,8 +770,11 @@ size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k);
 void launch_gemm_a16_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status, cudaStream_t stream);
 // scratch (may be null): room for the f16 copy of A; without it A is converted inside the kernel
 // a16_ready: the scratch already holds this A (same pointer, M, K) from the launch just before
+// counters (may be null): the slot's ticket words, needed for the in-kernel K split; auto_plan: the
+// tile width came from the routing heuristic, so width and split are chosen together for the shape
 void launch_gemm_f16w_umma(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
-                           void *scratch, size_t scratch_bytes, bool a16_ready, cudaStream_t stream);
+                           void *scratch, size_t scratch_bytes, bool a16_ready, cudaStream_t stream,
+                           uint32_t *counters = nullptr, bool auto_plan = false);
 void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n, uint32_t *status,
                         cudaStream_t stream);
 void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream);

@@ -364,6 +364,7 @@ Route Executor::plan_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, b
     auto it = tuned_.find(TuneKey{batch, m, n, k, b_f16});
     if (it != tuned_.end()) {
       r.kernel = it->second.kernel;
+      r.tuned = true;
       r.splits = allow_split_k2 ? it->second.splits : 0;
       if (KERNEL_SPECS[r.kernel].family != Family::SplitK2 || r.splits > 1) return r;
     }
@@ -453,8 +454,9 @@ size_t Executor::op_scratch_bytes(const ResolvedMatmul &r, const Route &route) c
     // records of the tensor-memory GEMV; sized for the SwiGLU pair too (twice the groups)
     return gemv_umma_scratch_bytes(r.n, r.k, true, ctx_->sm_count);
   if (KERNEL_SPECS[route.kernel].family != Family::F16wUmma) return 0;
-  const size_t need = gemm_f16w_umma_scratch_bytes(r.batch_stride_a ? r.batch : 1, r.m, r.k);
-  return need <= (256ull << 20) ? need : 0;
+  // the f16 copy of A, and behind it the partial tiles of an in-kernel K split
+  const size_t need = gemm_f16w_umma_scratch_bytes_split(r.batch, r.batch_stride_a ? r.batch : 1, r.m, r.n, r.k, ctx_->sm_count);
+  return need <= (256ull << 20) ? need : gemm_f16w_umma_scratch_bytes(r.batch_stride_a ? r.batch : 1, r.m, r.k);
 }
 
 // GEMV launch description of an op on the row-GEMV route; false when the route is another family.
@@ -536,7 +538,9 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
       return;
     case Family::F16wUmma:
       if (gemm_f16w_umma_eligible(p)) {
-        launch_gemm_f16w_umma(*ctx_, p, spec.tile_n, slot.status, slot.scratch, slot.scratch_bytes, op.a16_ready, stream);
+        // an executor on automatic selection lets the launcher pick tile width and K split together
+        launch_gemm_f16w_umma(*ctx_, p, spec.tile_n, slot.status, slot.scratch, slot.scratch_bytes, op.a16_ready, stream,
+                              slot.counters, selection_ == -2 && route.tuned == false);
         return;
       }
       launch_gemm_ffma(p, (r.m >= 128 && r.n >= 128) ? 128 : 64, stream);  // alignment demotion
@@ -782,7 +786,7 @@ void Executor::tune_shape(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, bo
     for (int ci : cands) scratch = std::max(scratch, op_scratch_bytes(r, Route{ci, 0}));
     if (scratch) ensure_scratch(slot, scratch);
     auto run_forced = [&](int kernel) {
-      const Route rt{kernel, 0};
+      const Route rt{kernel, 0, true};   // forced: the launcher must run exactly this tile
       return *timed(slot, 1, r.total_flops, [&](cudaStream_t st) { enqueue_op(op, r, rt, slot, st); }).gpu_time_ns;
     };
     const bool heur_in = std::find(cands.begin(), cands.end(), heuristic) != cands.end();
@@ -865,6 +869,8 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
   size_t scratch_bytes = 0;
   for (size_t i = 0; i < ops.size(); ++i) scratch_bytes = std::max(scratch_bytes, exec.op_scratch_bytes(resolved[i], routes[i]));
   if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));
+  TA_CUDA(cudaMalloc((void **)&prep->counters, SLOT_COUNTERS * sizeof(uint32_t)));
+  TA_CUDA(cudaMemset(prep->counters, 0, SLOT_COUNTERS * sizeof(uint32_t)));
   alloc_status_word(&prep->status_host, &prep->status);
   // Captured directly, nothing runs at create time: encoding tensor maps and setting function
   // attributes are host calls, which a stream capture allows.
@@ -874,6 +880,7 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
     Slot slot = real_slot;            // captured launches must point at this object's own scratch and status word
     slot.scratch = prep->scratch;
     slot.scratch_bytes = scratch_bytes;
+    slot.counters = prep->counters;
     slot.status = prep->status;
     slot.status_host = prep->status_host;
     TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
