@@ -92,11 +92,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
     with cf.ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose), SOURCES))
     if not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
-        cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs,
+        # link beside the target and rename: a reader never sees a half-written library
+        tmp = LIB + ".partial"
+        cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp, *objs,
                "-Xlinker", "--exclude-libs,ALL", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
     build_tools()
     return LIB
 

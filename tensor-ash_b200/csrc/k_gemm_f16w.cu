@@ -453,26 +453,18 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       if (!ok) break;
       tc_fence_after();
       if constexpr (SPLITK) {
-        // ---- raw partial tile to scratch, transposed so that stores cover full row segments
-        float *__restrict__ tbuf = epi_buf + warp * (32 * EPI_PITCH);
-        const uint32_t cq = (uint32_t)(lane & 7) * 4, rsub = (uint32_t)lane >> 3;
-        float *__restrict__ part = p.fw_partials + (size_t)unit * (BM * BN);
+        // ---- raw partial tile to scratch in the accumulator's own layout: float4 column group g of row r
+        // at part4[g * 128 + r].  A lane holds one row, so a warp's store covers 512 contiguous bytes
+        // and nothing is transposed; the reducing pass below reads the same layout.
+        float4 *__restrict__ part4 = reinterpret_cast<float4 *>(p.fw_partials + (size_t)unit * (BM * BN));
         const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
           tmem_ld32(taddr + c0, v);
 #pragma unroll
-          for (int q = 0; q < 32; q += 4)
-            *reinterpret_cast<float4 *>(tbuf + lane * EPI_PITCH + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-          __syncwarp();
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t r = (uint32_t)i * 4 + rsub;
-            *reinterpret_cast<float4 *>(part + (size_t)(warp * 32 + r) * BN + c0 + cq) =
-                *reinterpret_cast<const float4 *>(tbuf + r * EPI_PITCH + cq);
-          }
-          __syncwarp();
+          for (int q = 0; q < 8; ++q)
+            part4[(size_t)(c0 / 4 + q) * BM + warp * 32 + lane] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
         tc_fence_before();
         mbar_arrive(acc_empty(buf));
@@ -495,37 +487,80 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*abort_flag) { ok = false; break; }
         __threadfence();
-        // ---- this CTA's column slice of the tile: add the S partials in slice order, epilogue, store
-        const uint32_t cols = BN / splits;                      // splits divides BN / 4
-        const uint32_t lanes_per_row = cols / 4;
-        const float *__restrict__ tile_parts = p.fw_partials + (size_t)tile * splits * (BM * BN);
+        // ---- this CTA's column slice of the tile: add the S partials in slice order, epilogue, store.
+        // A warp-wide access takes 4 rows x 8 column groups: 64 contiguous bytes per column group of
+        // a partial (whole sectors) and 128 contiguous bytes per row of C.  Four such blocks and two
+        // slices at a time: eight independent loads in flight per thread.
+        const uint32_t g4n = BN / splits / 4;                   // float4 column groups of this CTA's slice (splits divides BN / 4)
+        const uint32_t g4_base = slice * g4n;
+        const uint32_t cblocks = (g4n + 7u) / 8u, blocks = 8u * cblocks;   // per warp: 8 row blocks x cblocks
+        const float4 *__restrict__ tile_parts4 = reinterpret_cast<const float4 *>(p.fw_partials + (size_t)tile * splits * (BM * BN));
         const size_t plane_off = (size_t)batch * p.stride_c;
         const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
+        const uint32_t r4 = (uint32_t)lane & 3u, cc = (uint32_t)lane >> 2;
         epi_dispatch_act(p.act, [&](auto act_tag) {
           constexpr uint32_t ACT = decltype(act_tag)::value;
-          for (uint32_t idx = lane; idx < 32u * lanes_per_row; idx += 32) {
-            const uint32_t r = warp * 32 + idx / lanes_per_row, c = slice * cols + (idx % lanes_per_row) * 4;
-            const uint32_t row = m0 + r, col = n0 + c;
-            if (row >= p.m || col >= p.n) continue;
-            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t t = 0; t < splits; ++t) {
-              const float4 v = __ldcg(reinterpret_cast<const float4 *>(tile_parts + (size_t)t * (BM * BN) + (size_t)r * BN + c));
-              o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+          constexpr int U = 4;
+          for (uint32_t base = 0; base < blocks; base += U) {
+            float4 acc[U];
+            const float4 *src[U];
+            size_t off[U];
+            uint32_t colu[U];
+            bool live[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint32_t b = base + (uint32_t)u;
+              const uint32_t r = warp * 32 + (b & 7u) * 4 + r4, g4 = (b >> 3) * 8 + cc;
+              const uint32_t row = m0 + r, col = n0 + (g4_base + g4) * 4;
+              live[u] = b < blocks && g4 < g4n && row < p.m && col < p.n;
+              src[u] = tile_parts4 + (size_t)(g4_base + g4) * BM + r;
+              off[u] = plane_off + (size_t)row * p.n + col;
+              colu[u] = col;
+              acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-            const size_t off = plane_off + (size_t)row * p.n + col;
-            if (p.accumulate) {
-              const float4 c_old = *reinterpret_cast<const float4 *>(p.c + off);
-              o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
+            constexpr size_t PLANE4 = (size_t)BM * BN / 4;
+            uint32_t t = 0;
+            for (; t + 1 < splits; t += 2) {
+              float4 v0[U], v1[U];
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                v0[u] = live[u] ? __ldcg(src[u] + (size_t)t * PLANE4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[u] = live[u] ? __ldcg(src[u] + (size_t)(t + 1) * PLANE4) : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                acc[u].x += v0[u].x; acc[u].y += v0[u].y; acc[u].z += v0[u].z; acc[u].w += v0[u].w;
+                acc[u].x += v1[u].x; acc[u].y += v1[u].y; acc[u].z += v1[u].z; acc[u].w += v1[u].w;
+              }
             }
-            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
-            if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
-            if (p.d) dv = *reinterpret_cast<const float4 *>(p.d + off);
-            o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
-            o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
-            o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
-            o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
-            *reinterpret_cast<float4 *>(p.c + off) = o;
+            if (t < splits) {
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const float4 v = live[u] ? __ldcg(src[u] + (size_t)t * PLANE4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                acc[u].x += v.x; acc[u].y += v.y; acc[u].z += v.z; acc[u].w += v.w;
+              }
+            }
+            float4 c_old[U], dv[U], bv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              c_old[u] = dv[u] = bv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (!live[u]) continue;
+              if (p.accumulate) c_old[u] = *reinterpret_cast<const float4 *>(p.c + off[u]);
+              if (bias) bv[u] = __ldg(reinterpret_cast<const float4 *>(bias + colu[u]));
+              if (p.d) dv[u] = *reinterpret_cast<const float4 *>(p.d + off[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              if (!live[u]) continue;
+              float4 o = acc[u];
+              if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+              if (p.accumulate) { o.x += c_old[u].x; o.y += c_old[u].y; o.z += c_old[u].z; o.w += c_old[u].w; }
+              o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv[u].x, p.binary, dv[u].x, p.beta);
+              o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv[u].y, p.binary, dv[u].y, p.beta);
+              o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv[u].z, p.binary, dv[u].z, p.beta);
+              o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv[u].w, p.binary, dv[u].w, p.beta);
+              *reinterpret_cast<float4 *>(p.c + off[u]) = o;
+            }
           }
         });
         // ---- the last slice to finish reading puts the tile's two ticket words back to zero
@@ -632,11 +667,6 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
   const uint64_t rows = ba * p.m;
   const uint64_t items = rows * (kp / 8);
-  if (!a16_ready) {
-    convert_a_f16_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(static_cast<const float *>(p.a), a16, p.k, kp, rows);
-    TA_CUDA(cudaGetLastError());
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-  }
   CUtensorMap map_a, map_b;
   // A16 [ba, M, Kp] f16: 128-byte rows of 64 halves, 128-byte swizzle; columns >= K read as zero (TMA bound K)
   encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a16, p.k, p.m, ba, (uint64_t)kp * 2,
@@ -653,6 +683,13 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch * (SPLITK ? p.fw_splits : 1u);
   if (SPLITK && tiles > (uint64_t)ctx.sm_count) fail("internal: split-K units (%llu) exceed the SM count", (unsigned long long)tiles);
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
+  // the conversion is launched only now, with the tensor maps encoded: the two launches reach the
+  // device back to back, so the device does not idle between them while the host encodes
+  if (!a16_ready) {
+    convert_a_f16_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(static_cast<const float *>(p.a), a16, p.k, kp, rows);
+    TA_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
   // right behind the conversion kernel: start early, wait on the device (see the kernel)
   pg.pdl_wait = (!a16_ready && tunables().pdl) ? 1u : 0u;
   cudaLaunchConfig_t cfg = {};
@@ -747,7 +784,9 @@ F16wPlan gemm_f16w_umma_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k,
   double best_cost = 1e300;
   const uint32_t kb = (k + PK - 1) / PK;
   const int force = tunables().f16w_splitk;
+  const uint32_t force_bn = tunables().f16w_bn;
   for (uint32_t bn : {256u, 192u, 128u, 64u}) {
+    if (force_bn && bn != force_bn) continue;
     const uint64_t tiles = (uint64_t)batch * ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
     const double block_kb = 16.0 + bn * 0.125;
     for (uint32_t s : {1u, 2u, 3u, 4u, 6u, 8u}) {

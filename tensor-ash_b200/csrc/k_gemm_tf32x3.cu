@@ -25,14 +25,15 @@
 // warpgroups (48 each) to the epilogue warpgroups (168 each).
 //
 // Accuracy: the tensor-memory accumulator truncates after every MMA, an error that grows
-// linearly with the number of MMAs it absorbs (measured: 9e-6 relative at K = 1024, 1.6e-5 at
-// K = 2048 when a whole K runs in one accumulator).  K is therefore cut into chunks: a chunk
-// accumulates in one of the two tensor-memory buffers, the epilogue warps drain it into
-// per-thread running sums (round-to-nearest f32 adds) while the next chunk runs in the other
-// buffer; a tile's epilogue runs on the running sums.  Draining tensor memory takes bandwidth
-// from the MMAs writing it (measured on 32 x 2048^3: 197 TFLOP/s with one drain per tile, 190
-// with chunks of 1024, 172 with chunks of 512), so the default chunk is 1024 (at most ~1e-5
-// relative at any K); the experiment switch tf32x3_chunk_kb=32 selects chunks of 512 (4.2e-6 at any K).
+// linearly with the number of MMAs one accumulation absorbs (measured worst case over 32 operand
+// pairs, relative to max |C|: 4.8e-6 at 32 K blocks, 6.9e-6 at 43, 7.4e-6 at 44, 9.7e-6 at 64,
+// 1.6e-5 when a whole K = 2048 runs in one accumulator).  K is therefore cut into equal chunks of at
+// most 38 K blocks (608 k): a chunk accumulates in one of the two tensor-memory buffers, the
+// epilogue warps drain it into per-thread running sums (round-to-nearest f32 adds) while the next
+// chunk runs in the other buffer; a tile's epilogue runs on the running sums.  The error then
+// stays under 6.5e-6 at any K, against the 1e-5 criterion.  Draining tensor memory takes bandwidth
+// from the MMAs writing it (32 x 2048^3: 205 TFLOP/s with two chunks per tile, 202 with three), so
+// the chunks are as long as the margin allows; the experiment switch tf32x3_chunk_kb sets the cap.
 // Every mbarrier wait is bounded (about two seconds); on a timeout the CTA
 // raises a flag, all roles leave their loops, and the host reports an error.
 //
@@ -64,7 +65,7 @@ constexpr int CVT_GROUPS = 2;               // converter groups of 4 warps, alte
 // warp + MMA warp + two idle warps, 3-4 converters
 constexpr int EPI_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, CVT_WARP0 = 12;
 constexpr int NUM_THREADS = (CVT_WARP0 + 4 * CVT_GROUPS) * 32;   // 640
-constexpr uint32_t CHUNK_KB = 64;           // K blocks (1024 k) per tensor-memory accumulation
+constexpr uint32_t CHUNK_KB = 38;           // most K blocks (608 k) one tensor-memory accumulation absorbs
 // setmaxnreg only redistributes the registers the CTA was launched with (threads x the
 // per-thread count the compiler reports, 96 for 640 threads), and `inc` blocks until they are
 // there: the split must fit that pool or the kernel never starts.
@@ -404,8 +405,13 @@ template <int BN, bool SPLITK>
 void launch_t(const Context &ctx, const GemmParams &p_in, uint32_t *status, cudaStream_t stream) {
   using C = Cfg<BN>;
   GemmParams p = p_in;
-  p.chunk_kb = CHUNK_KB;
-  if (tunables().tf32x3_chunk_kb) p.chunk_kb = tunables().tf32x3_chunk_kb;
+  // equal chunks of at most CHUNK_KB blocks: the truncation error follows the longest chunk
+  {
+    const uint32_t cap = tunables().tf32x3_chunk_kb ? tunables().tf32x3_chunk_kb : CHUNK_KB;
+    const uint32_t kb_all = (p.k + 15u) / 16u, chunks = (kb_all + cap - 1) / cap;
+    p.chunk_kb = chunks ? (kb_all + chunks - 1) / chunks : cap;
+    if (SPLITK) p.chunk_kb = std::max(cap, p.sk_kb_per_sub);   // a unit's sub-range is one accumulation (the plan caps it)
+  }
   static bool attr_set[64] = {};
   if (!attr_set[ctx.device & 63]) {
     TA_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -460,7 +466,7 @@ void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n
 // ---------------------------------------------------------------- split-K2 stage 1 on the tensor cores
 // Eligible when the reference's partition (src/executor/splitk2.rs, shaders/matmul_splitk2_kernel.glsl:138-142:
 // K / S per split, the first K % S splits one longer) lands on K-block boundaries: K a multiple
-// of 16 * S.  Each split is then cut into c equal pieces of at most 64 K blocks so that
+// of 16 * S.  Each split is then cut into c equal pieces of at most CHUNK_KB K blocks so that
 // tiles * S * c work units fill the SMs whatever S the caller asked for; piece j of split s is
 // plane s * c + j, and the reduce adds planes in that order.
 SplitK2TensorPlan splitk2_tensor_plan(const GemmParams &p, uint32_t splits, int sm_count) {
@@ -472,7 +478,7 @@ SplitK2TensorPlan splitk2_tensor_plan(const GemmParams &p, uint32_t splits, int 
   const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + bn - 1) / bn) * p.batch;
   uint64_t c = std::max<uint64_t>(1, (uint64_t)sm_count / (tiles * splits));
   c = std::min<uint64_t>(c, kb_per_split);
-  c = std::max<uint64_t>(c, (kb_per_split + CHUNK_KB - 1) / CHUNK_KB);   // one accumulation holds at most 1024 k
+  c = std::max<uint64_t>(c, (kb_per_split + CHUNK_KB - 1) / CHUNK_KB);   // one accumulation holds at most CHUNK_KB blocks
   const uint32_t kb_per_sub = (uint32_t)((kb_per_split + c - 1) / c);
   c = (kb_per_split + kb_per_sub - 1) / kb_per_sub;                      // no empty piece
   if ((uint64_t)splits * c > 65535) return plan;

@@ -39,7 +39,7 @@ constexpr int CVT_GROUPS = 2;
 // tile's columns, running sums in registers), 2 = TMA warp + MMA warp + two idle warps, 3-4 converters
 constexpr int EPI_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, CVT_WARP0 = 12;
 constexpr int NUM_THREADS = (CVT_WARP0 + 4 * CVT_GROUPS) * 32;   // 640
-constexpr uint32_t CHUNK_KB = 64;          // K blocks (1024 k) per tensor-memory accumulation
+constexpr uint32_t CHUNK_KB = 38;           // most K blocks (608 k) one tensor-memory accumulation absorbs
 constexpr int LAUNCH_REGS = 96, EPI_REGS = 168, WORKER_REGS = 48;
 static_assert(EPI_WARPS * 32 * EPI_REGS + (NUM_THREADS - EPI_WARPS * 32) * WORKER_REGS <= NUM_THREADS * LAUNCH_REGS,
               "setmaxnreg split exceeds the CTA's launch-time register allocation");
@@ -361,8 +361,12 @@ bool gemm_tf32x3_pair_supported(const GemmParams &p, int sm_count) {
 
 void launch_gemm_tf32x3_pair(const Context &ctx, const GemmParams &p_in, uint32_t *status, cudaStream_t stream) {
   GemmParams p = p_in;
-  p.chunk_kb = CHUNK_KB;
-  if (tunables().tf32x3_chunk_kb) p.chunk_kb = tunables().tf32x3_chunk_kb;
+  // equal chunks of at most CHUNK_KB blocks: the truncation error follows the longest chunk
+  {
+    const uint32_t cap = tunables().tf32x3_chunk_kb ? tunables().tf32x3_chunk_kb : CHUNK_KB;
+    const uint32_t kb_all = (p.k + 15u) / 16u, chunks = (kb_all + cap - 1) / cap;
+    p.chunk_kb = chunks ? (kb_all + chunks - 1) / chunks : cap;
+  }
   if (!gemm_tf32x3_pair_supported(p, ctx.sm_count))
     fail("paired tf32x3 GEMM needs f32 operands with K and N multiples of 4");
   static bool attr_set[64] = {};

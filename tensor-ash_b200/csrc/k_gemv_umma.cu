@@ -50,6 +50,8 @@ constexpr int GU_STAGES = 8;
 constexpr int GU_XS_MAX_K = 2048;                    // resident x slice: 16 rows x 2048 halves = 64 KiB
 constexpr int GU_XS_BYTES = GU_XS_MAX_K * 16 * 2;
 constexpr int GU_REC_FLOATS = 8 * 128 + 8;           // scratch record: 8 rows x 128 sums, then 8 sums of squares
+constexpr uint32_t GU_MAX_GROUPS = 4094;             // ticket words [0, 4094), then the finish cursor and the exit count
+constexpr uint32_t GU_CURSOR = 4094, GU_DONE = 4095;
 constexpr int GU_MISC_BYTES = 1024;                  // barriers, tensor-memory slot, flags, per-row scalars
 constexpr int GU_SMEM_BYTES = GU_STAGES * GU_STAGE_BYTES + GU_XS_BYTES + GU_MISC_BYTES + 1024;
 
@@ -318,65 +320,50 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
       }
     } else {
       // ---------------------------------------------------------- drain + finish (warps 0-3)
+      // Draining and finishing are decoupled.  A drained group costs a record and a ticket, nothing
+      // else; complete groups are finished in group order by whichever CTA claims them from a cursor:
+      // without waiting between two drains (a claim succeeds only on a complete group), and with a
+      // bounded wait once the CTA's own groups are drained.  So the finishing work is spread over all
+      // CTAs instead of falling on the slowest slice, and no drain waits behind a finish.
       uint32_t acc_it = 0;
       bool ok = true;
       const uint32_t tid = threadIdx.x;                    // 0..127 = weight column within the group
-      for (uint32_t grp = rank; ok && grp < g.groups; grp += g.team_size, ++acc_it) {
-        const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
-        ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 128);
-        if (!ok) break;
-        tc_fence_after();
-        float v[16];
-        tmem_ld16(tmem_base + buf * 16u + ((uint32_t)(warp * 32) << 16), v);
-        tc_fence_before();
-        mbar_arrive(acc_empty(buf));
-        float *rec = g.scratch + ((size_t)grp * g.teams + slice) * GU_REC_FLOATS;
-#pragma unroll
-        for (int m = 0; m < 8; ++m)
-          if ((uint32_t)m < p.m) rec[m * 128 + tid] = (v[m] + v[8 + m]) * unscale[m];
-        if (tid < 8) rec[8 * 128 + tid] = ssq[tid];
-        __threadfence();
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (tid == 0) {
-          const uint32_t ticket = atomicAdd(&g.counters[grp], 1u);
-          if (ticket == g.teams - 1) g.counters[grp] = 0u;    // every slice has arrived: ready for the next launch
-          *ticket_slot = ticket;
-        }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (*ticket_slot != g.teams - 1) continue;
-        __threadfence();
-        // ---- last arrival of this group: add the slices in slice order, epilogue, store
+      uint32_t *cursor = g.counters + GU_CURSOR, *done = g.counters + GU_DONE;
+
+      auto finish_group = [&](uint32_t grp) {
         const float *grp_rec = g.scratch + (size_t)grp * g.teams * GU_REC_FLOATS;
         const uint32_t col = grp * cols_per_group + (g.dual ? (tid & 63u) : tid);
-        if (col >= p.n || (g.dual && tid >= 64)) continue;
-        // every record's values for all rows are requested before any is consumed: one L2 round
-        // trip per group, whatever the row count (slices in order: a fixed sum)
-        float s0[8], s1[8], ssum[8];
-#pragma unroll
-        for (int m = 0; m < 8; ++m) { s0[m] = 0.0f; s1[m] = 0.0f; ssum[m] = 0.0f; }
-#pragma unroll 2
-        for (uint32_t sl = 0; sl < g.teams; ++sl) {
-          const float *r = grp_rec + (size_t)sl * GU_REC_FLOATS;
-          float a[8], b[8], q[8];
-#pragma unroll
-          for (int m = 0; m < 8; ++m) {
-            const bool live = (uint32_t)m < p.m;
-            a[m] = live ? __ldcg(r + m * 128 + tid) : 0.0f;
-            b[m] = (live && g.dual) ? __ldcg(r + m * 128 + 64 + tid) : 0.0f;
-            q[m] = (live && p.norm_w) ? __ldcg(r + 8 * 128 + m) : 0.0f;
-          }
-#pragma unroll
-          for (int m = 0; m < 8; ++m) { s0[m] += a[m]; s1[m] += b[m]; ssum[m] += q[m]; }
-        }
-        // epilogue operands of all rows, again in one batch
-        float oldc[8], dv[8];
+        if (col >= p.n || (g.dual && tid >= 64)) return;
+        // records of four slices are requested together (slices in order: a fixed sum), the epilogue
+        // operands of all rows with the first of them: two or three L2 round trips per group
+        float s0[8], s1[8], ssum[8], oldc[8], dv[8];
         const float bv = p.bias ? p.bias[col] : 0.0f;
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
           const bool live = (uint32_t)m < p.m;
           const size_t ci = (size_t)m * p.n + col;
+          s0[m] = 0.0f; s1[m] = 0.0f; ssum[m] = 0.0f;
           oldc[m] = (live && p.accumulate) ? p.c[ci] : 0.0f;
           dv[m] = (live && p.d) ? p.d[ci] : 0.0f;
+        }
+        for (uint32_t sl0 = 0; sl0 < g.teams; sl0 += 4) {
+          float a[4][8], b[4][8], q[4][8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float *r = grp_rec + (size_t)(sl0 + u) * GU_REC_FLOATS;
+            const bool have = sl0 + u < g.teams;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+              const bool live = have && (uint32_t)m < p.m;
+              a[u][m] = live ? __ldcg(r + m * 128 + tid) : 0.0f;
+              b[u][m] = (live && g.dual) ? __ldcg(r + m * 128 + 64 + tid) : 0.0f;
+              q[u][m] = (live && p.norm_w) ? __ldcg(r + 8 * 128 + m) : 0.0f;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int m = 0; m < 8; ++m) { s0[m] += a[u][m]; s1[m] += b[u][m]; ssum[m] += q[u][m]; }
         }
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
@@ -397,6 +384,78 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
           o = epi_apply(o, p.bias != nullptr, bv, p.act, p.binary, dv[m], p.beta);
           p.c[ci] = o;
         }
+      };
+      // claim the next group in order; `block`: wait (bounded) for it to be complete, else take it only
+      // if it already is.  Returns the group or ~0u.  Thread 0 decides, all 128 threads learn it.
+      auto claim = [&](bool block) -> uint32_t {
+        if (tid == 0) {
+          uint32_t got = ~0u;
+          if (block) {
+            const uint32_t c = atomicAdd(cursor, 1u);
+            if (c < g.groups) {
+              const uint64_t t0 = global_timer_ns();
+              uint32_t seen = 0, spins = 0;
+              for (;;) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.counters + c) : "memory");
+                if (seen >= g.teams) { got = c; break; }
+                if ((++spins & 63u) == 0 && (*abort_flag || global_timer_ns() - t0 > WAIT_LIMIT_NS)) {
+                  *abort_flag = 1;
+                  break;
+                }
+              }
+            }
+          } else {
+            uint32_t c, seen = 0;
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(cursor) : "memory");
+            if (c < g.groups) {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(g.counters + c) : "memory");
+              if (seen >= g.teams && atomicCAS(cursor, c, c + 1u) == c) got = c;
+            }
+          }
+          *ticket_slot = got;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        const uint32_t got = *ticket_slot;
+        asm volatile("bar.sync 2, 128;" ::: "memory");       // the slot may be rewritten after this
+        return got;
+      };
+      auto finish_claimed = [&](uint32_t grp) {
+        __threadfence();                                       // the acquire of thread 0, for all threads
+        finish_group(grp);
+        if (tid == 0) g.counters[grp] = 0u;                    // every slice has arrived: ready for the next launch
+      };
+
+      for (uint32_t grp = rank; ok && grp < g.groups; grp += g.team_size, ++acc_it) {
+        const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+        ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 128);
+        if (!ok) break;
+        tc_fence_after();
+        float v[16];
+        tmem_ld16(tmem_base + buf * 16u + ((uint32_t)(warp * 32) << 16), v);
+        tc_fence_before();
+        mbar_arrive(acc_empty(buf));
+        float *rec = g.scratch + ((size_t)grp * g.teams + slice) * GU_REC_FLOATS;
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          if ((uint32_t)m < p.m) rec[m * 128 + tid] = (v[m] + v[8 + m]) * unscale[m];
+        if (tid < 8) rec[8 * 128 + tid] = ssq[tid];
+        __threadfence();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (tid == 0) atomicAdd(&g.counters[grp], 1u);
+        const uint32_t ready = claim(false);
+        if (ready != ~0u) finish_claimed(ready);
+      }
+      // own groups drained: help until every group has been claimed
+      while (ok) {
+        const uint32_t grp = claim(true);
+        if (grp == ~0u) break;
+        finish_claimed(grp);
+      }
+      // the last CTA to leave puts the cursor back (claims beyond the last group overshoot it)
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (tid == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+        *cursor = 0u;
+        *done = 0u;
       }
     }
   }
@@ -449,7 +508,7 @@ size_t gemv_umma_scratch_bytes(uint32_t n, uint32_t k, bool dual, int sm_count) 
 
 // Shapes this kernel takes: plain epilogue (no fused RoPE / scatter store), K a multiple of 16 (the
 // tensor core's k step; a partial step would multiply rows of the next packed tile), 16-byte
-// aligned weights, at most 4096 column groups (one ticket word each).
+// aligned weights, at most 4094 column groups (one ticket word each).
 bool gemv_umma_eligible(const GemvParams &p) {
   if (p.m == 0 || p.m > 8 || p.store_kind != 0) return false;
   if (p.k % 16 || p.k < 64) return false;
@@ -461,7 +520,7 @@ bool gemv_umma_eligible(const GemvParams &p) {
     return false;
   }
   const uint32_t cols = p.w2 ? 64u : 128u;
-  if ((p.n + cols - 1) / cols > SLOT_COUNTERS - ATTN_DECODE_MAX_KV_HEADS) return false;
+  if ((p.n + cols - 1) / cols > GU_MAX_GROUPS) return false;
   if (((uint64_t)(p.k + GU_BOX_K - 1) / GU_BOX_K) > 64ull * (GU_XS_MAX_K / GU_BOX_K)) return false;   // x slice at 64 teams
   return true;
 }

@@ -168,6 +168,126 @@ peer_all_reduce_kernel(float *data, uint32_t count, PeerTable t, uint32_t *statu
   }
 }
 
+// ------------------------------------------------------------------ two-step all-reduce (prefill activations)
+// A [T, embd] activation of a prefill step is a few MB: too large for the one-launch kernel above,
+// and NCCL spends most of its time on launch and protocol at this size.  The tensor is cut into
+// `world` slices; rank r owns slice r.  CTA b of every rank handles part b of every slice and
+// synchronises only with CTA b of the peers, through two flag words per (rank, CTA):
+//   step 1  push my values of slice s into rank s's `in` region, for every s != me; raise flag 1 there;
+//   step 2  wait for the peers' flag 1; add the `world` versions of my own slice in rank order (mine
+//           from the tensor itself), write the sum into the tensor and into every peer's `out`
+//           region; raise flag 2 there;
+//   step 3  wait for the peers' flag 2; copy their reduced slices from my `out` region into the tensor.
+// Every rank adds in the same order: results are bit-identical across ranks.  Flags carry a per-CTA
+// call count kept in the rank's own buffer, so no host word is involved; waits are bounded.
+// A rank enters call e + 1 only after it has read every peer's step-2 push of call e, i.e. after
+// every peer finished reading its `in` region: one buffer per region is enough.
+__global__ void __launch_bounds__(256)
+peer_all_reduce_big_kernel(float *data, uint32_t count, uint32_t slice, uint32_t part, PeerTable t, uint32_t *status,
+                           uint64_t limit_ns) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const uint32_t b = blockIdx.x, me = t.rank, W = t.world;
+  uint8_t *mine = t.buf[me];
+  uint32_t *epoch_p = reinterpret_cast<uint32_t *>(mine + PEER_BIG_EPOCH_OFF) + b;
+  const uint32_t ticket = *epoch_p + 1u;
+  auto in_of = [&](uint32_t owner, uint32_t src) { return reinterpret_cast<float *>(t.buf[owner] + PEER_BIG_IN_OFF) + (size_t)src * slice; };
+  auto out_of = [&](uint32_t owner, uint32_t s) { return reinterpret_cast<float *>(t.buf[owner] + PEER_BIG_OUT_OFF) + (size_t)s * slice; };
+  auto flag_of = [&](uint32_t owner, uint32_t step, uint32_t src) {
+    return reinterpret_cast<uint32_t *>(t.buf[owner] + PEER_BIG_FLAG_OFF) + ((size_t)step * PEER_MAX_WORLD + src) * PEER_BIG_CTAS + b;
+  };
+  __shared__ uint32_t ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1u;
+  const uint32_t lo = b * part, hi = min(slice, lo + part);     // this CTA's range inside a slice (multiples of 4)
+  auto wait_peers = [&](uint32_t step) {
+    if (threadIdx.x < W && threadIdx.x != me) {
+      const uint32_t *f = flag_of(me, step, threadIdx.x);
+      uint64_t t0, now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+      uint32_t seen = 0, spins = 0;
+      for (;;) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+        if (seen == ticket) break;
+        if ((++spins & 255u) == 0) {
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+          if (now - t0 > limit_ns) { ok_flag = 0u; break; }
+        }
+      }
+    }
+    __syncthreads();
+  };
+  auto raise = [&](uint32_t step) {     // after this CTA's pushes: visible system-wide, then one flag per peer
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < W && threadIdx.x != me)
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag_of(threadIdx.x, step, me)), "r"(ticket) : "memory");
+  };
+  // ---- step 1
+  for (uint32_t s = 0; s < W; ++s) {
+    if (s == me) continue;
+    float *dst = in_of(s, me);
+    for (uint32_t i = lo + threadIdx.x * 4; i < hi; i += 256 * 4) {
+      const size_t g = (size_t)s * slice + i;
+      if (g < count) *reinterpret_cast<float4 *>(dst + i) = *reinterpret_cast<const float4 *>(data + g);
+    }
+  }
+  raise(0);
+  // ---- step 2
+  wait_peers(0);
+  for (uint32_t i = lo + threadIdx.x * 4; i < hi; i += 256 * 4) {
+    const size_t g = (size_t)me * slice + i;
+    if (g >= count) continue;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t r = 0; r < W; ++r) {
+      const float4 x = r == me ? *reinterpret_cast<const float4 *>(data + g)
+                               : __ldcg(reinterpret_cast<const float4 *>(in_of(me, r) + i));
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    *reinterpret_cast<float4 *>(data + g) = acc;
+    for (uint32_t r = 0; r < W; ++r)
+      if (r != me) *reinterpret_cast<float4 *>(out_of(r, me) + i) = acc;
+  }
+  raise(1);
+  // ---- step 3
+  wait_peers(1);
+  for (uint32_t s = 0; s < W; ++s) {
+    if (s == me) continue;
+    const float *src = out_of(me, s);
+    for (uint32_t i = lo + threadIdx.x * 4; i < hi; i += 256 * 4) {
+      const size_t g = (size_t)s * slice + i;
+      if (g < count) *reinterpret_cast<float4 *>(data + g) = __ldcg(reinterpret_cast<const float4 *>(src + i));
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *epoch_p = ticket;
+    if (!ok_flag && status) atomicOr(status, 4u);
+  }
+}
+
+bool Comm::peer_all_reduce_big(float *data, size_t count, uint32_t *status, cudaStream_t stream) const {
+  if (!peer_own || count == 0 || count > PEER_BIG_MAX_FLOATS || (count & 3u) || (reinterpret_cast<uintptr_t>(data) & 15u))
+    return false;
+  PeerTable t{};
+  for (uint32_t r = 0; r < world; ++r) t.buf[r] = static_cast<uint8_t *>(peer_bufs[r]);
+  t.rank = rank;
+  t.world = world;
+  const uint32_t slice = (uint32_t)(((count + world - 1) / world + 3) & ~(size_t)3);        // floats per rank, a multiple of 4
+  const uint32_t part = ((slice + PEER_BIG_CTAS - 1) / PEER_BIG_CTAS + 3) & ~3u;           // floats per CTA within a slice
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(PEER_BIG_CTAS, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, peer_all_reduce_big_kernel, data, (uint32_t)count, slice, part, t, status, peer_wait_limit_ns));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return true;
+}
+
 // ------------------------------------------------------------------ sharded argmax
 // Greedy pick over a vocabulary whose logits are split by column over the ranks: every rank folds
 // its own slice to one (value, global index) pair, pushes the pair into every rank's buffer, waits

@@ -63,6 +63,7 @@ struct Tunables {
   bool peer_allreduce = true;     // one-launch peer-write all-reduce for small tensor-parallel exchanges
   bool splitk2_tensor = true;     // split-K2 stage 1 on the tensor cores where the shape allows
   int f16w_splitk = -1;           // f16w tensor-core GEMM: K split for grids under one wave (-1 = per shape, 0/1 = off)
+  uint32_t f16w_bn = 0;           // f16w tensor-core GEMM: tile width of the planned route (0 = per shape; 64 / 128 / 192 / 256)
 };
 const Tunables &tunables();
 // parses `name=value,...` into a Tunables (throws on an unknown name); exposed for the host tests
@@ -460,7 +461,16 @@ constexpr size_t PEER_X_FLAG_OFF = PEER_X_DATA_OFF + PEER_X_DATA_BYTES;
 constexpr size_t PEER_X_FLAG_BYTES = (size_t)PEER_MAX_POINTS * PEER_MAX_WORLD * sizeof(uint32_t);
 constexpr size_t PEER_AMAX_PAIR_OFF = PEER_X_FLAG_OFF + PEER_X_FLAG_BYTES;
 constexpr size_t PEER_AMAX_FLAG_OFF = PEER_AMAX_PAIR_OFF + 2 * PEER_MAX_WORLD * 8;   // pairs of two consecutive uses
-constexpr size_t PEER_BUF_TOTAL = PEER_AMAX_FLAG_OFF + PEER_MAX_WORLD * sizeof(uint32_t);
+constexpr size_t PEER_SMALL_TOTAL = PEER_AMAX_FLAG_OFF + PEER_MAX_WORLD * sizeof(uint32_t);
+//   then the two-step all-reduce of larger tensors (up to PEER_BIG_MAX_FLOATS, a prefill activation):
+//   in[world][slice] (partial slices pushed by the peers), out[world][slice] (reduced slices pushed
+//   by their owners), flags of both steps [2][world][PEER_BIG_CTAS] and per-CTA call counters
+constexpr uint32_t PEER_BIG_MAX_FLOATS = 1u << 20, PEER_BIG_CTAS = 64;
+constexpr size_t PEER_BIG_IN_OFF = (PEER_SMALL_TOTAL + 255) & ~(size_t)255;
+constexpr size_t PEER_BIG_OUT_OFF = PEER_BIG_IN_OFF + (size_t)PEER_BIG_MAX_FLOATS * sizeof(float) + 4096;
+constexpr size_t PEER_BIG_FLAG_OFF = PEER_BIG_OUT_OFF + (size_t)PEER_BIG_MAX_FLOATS * sizeof(float) + 4096;
+constexpr size_t PEER_BIG_EPOCH_OFF = PEER_BIG_FLAG_OFF + 2ull * PEER_MAX_WORLD * PEER_BIG_CTAS * sizeof(uint32_t);
+constexpr size_t PEER_BUF_TOTAL = PEER_BIG_EPOCH_OFF + PEER_BIG_CTAS * sizeof(uint32_t);
 void comm_unique_id(uint8_t out[COMM_ID_BYTES]);
 struct Comm {
   std::shared_ptr<Context> ctx;
@@ -487,6 +497,9 @@ struct Comm {
   void resync();
   // one-launch peer-write all-reduce; false when the request does not fit it (caller uses NCCL)
   bool peer_all_reduce_sum(float *data, size_t count, uint32_t *status, bool pdl, cudaStream_t stream) const;
+  // two-step (reduce-scatter by pushes, then the reduced slices pushed back) all-reduce over peer
+  // memory for tensors of up to PEER_BIG_MAX_FLOATS floats; false when the request does not fit it
+  bool peer_all_reduce_big(float *data, size_t count, uint32_t *status, cudaStream_t stream) const;
   static std::unique_ptr<Comm> create(const std::shared_ptr<Context> &ctx, uint32_t rank, uint32_t world,
                                       const uint8_t id[COMM_ID_BYTES]);
   ~Comm();

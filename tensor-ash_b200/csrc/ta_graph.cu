@@ -452,7 +452,9 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       float *ptr = (float *)t.ptr();
       const size_t count = (size_t)t.len();
       return [=](Slot &slot, cudaStream_t st) {
-        if (!comm->peer_all_reduce_sum(ptr, count, slot.status, true, st)) comm->all_reduce_sum(ptr, count, st);
+        // one-launch peer exchange for a row or two, the two-step peer kernel for a prefill activation, NCCL beyond
+        if (!comm->peer_all_reduce_sum(ptr, count, slot.status, true, st) && !comm->peer_all_reduce_big(ptr, count, slot.status, st))
+          comm->all_reduce_sum(ptr, count, st);
       };
     }
     case ExecKind::AllGather: {

@@ -170,6 +170,17 @@ def main_gpu():
     for _ in range(3):      # repeated uses advance the arrival words in step on every rank
         ex.run_exec_ops([ta.ExecOp.argmax_sharded(t_sl, rank * vocab_l, cell, comm)])
         assert cell.get() == (world - 1) * vocab_l + 123, f"rank {rank}: sharded argmax {cell.get()}"
+    # all-reduce of prefill-sized activations (the two-step peer kernel): exact on integer-valued
+    # inputs, repeated so that the per-CTA call counts advance, at a ragged and at the largest size
+    for rows, cols in ((300, 256), (37, 1028), (512, 2048)):
+        t_big = ta.Tensor.uninit_device(ctx, (rows, cols))
+        base = (np.arange(rows * cols, dtype=np.int64) % 8191).astype(np.float32).reshape(rows, cols)
+        for rep in range(3):
+            ex.upload(base * (rank + 1) + rep, t_big)
+            ex.run_exec_ops([ta.ExecOp.all_reduce(t_big, comm)])
+            want_sum = base * (world * (world + 1) // 2) + rep * world
+            assert np.array_equal(ex.download(t_big), want_sum), f"rank {rank}: all-reduce {rows}x{cols} rep {rep}"
+        t_big.close()
     # every rank must hold the same token stream
     t = torch.tensor(toks, dtype=torch.int64, device="cuda")
     ref_t = t.clone()
