@@ -65,7 +65,7 @@ flash_prefill_kernel(const FlashParams p) {
     }
     for (uint32_t i = tid; i < BK * DH; i += 128) {
       const uint32_t j = i / DH, d = i % DH, pos = k0 + j;
-      Vsh[i] = pos < p.t_max ? kv_load(p.v, v_base + (size_t)pos * DH + d, p.kv_f16) : 0.0f;
+      Vsh[i] = (pos < p.t_max && pos < p.kv_len) ? kv_load(p.v, v_base + (size_t)pos * DH + d, p.kv_f16) : 0.0f;
     }
     __syncthreads();
 
@@ -183,7 +183,9 @@ flash_prefill_mma_kernel(const FlashParams p) {
       __half *vd = &Vsh[buf][r * FM_LD + c8];
       if (k0 + c8 + 8 <= p.t_max) cp_async16(kd, kt + (size_t)r * p.t_max + k0 + c8);
       else *reinterpret_cast<uint4 *>(kd) = make_uint4(0u, 0u, 0u, 0u);
-      if (k0 + r < p.t_max) cp_async16(vd, vv + (size_t)(k0 + r) * FM_DH + c8);
+      // rows at or beyond kv_len get probability 0: they must be zeros, not whatever the cache holds
+      // there (0 x Inf or 0 x NaN from a never-written row would poison the whole output row)
+      if (k0 + r < p.t_max && k0 + r < p.kv_len) cp_async16(vd, vv + (size_t)(k0 + r) * FM_DH + c8);
       else *reinterpret_cast<uint4 *>(vd) = make_uint4(0u, 0u, 0u, 0u);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -348,7 +350,11 @@ attn_decode_kernel(const AttnDecodeParams p) {
   const bool live = row < p.group;
 
   // the position cell is host-written before the launch: read it ahead of the dependency wait
-  const uint32_t kv_len = p.kv_len + (p.pos_ptr ? *p.pos_ptr : 0u);
+  uint32_t kv_len = p.kv_len + (p.pos_ptr ? *p.pos_ptr : 0u);
+  if (kv_len > p.t_max || kv_len < p.kv_len) {   // a position the cache does not hold: stay inside it and report
+    if (tid == 0 && chunk == 0 && kv_head == 0 && p.status) atomicOr(p.status, 8u);
+    kv_len = p.t_max;
+  }
   // positions per chunk, a multiple of 8 so that f16 K rows start on 16 bytes
   const uint32_t chunk_size = (((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u;
   const uint32_t p0 = min(kv_len, chunk * chunk_size), p1 = min(p0 + chunk_size, kv_len);

@@ -74,14 +74,32 @@ constexpr int RING_STAGE_BYTES = 16384;
 // Three to eight rows over shapes the tensor-memory kernel (k_gemv_umma.cu) takes go there instead.
 // PEER: the launch takes part in a tensor-parallel exchange fused into it.  Pull: the activation x
 // is not read from memory but summed, in rank order, from what every rank pushed into this rank's
-// exchange buffer at the launch's exchange point (after a bounded wait for their arrival counts);
-// the first column tile also writes the sum to x_out for later readers.  Push: a segment's outputs
-// go to every rank's buffer instead of C, followed by one arrival per rank.  No extra launch.
-__device__ __forceinline__ const float *peer_slot(const PeerLink &l, uint32_t owner, uint32_t slot, uint32_t src) {
-  return reinterpret_cast<const float *>(l.buf[owner] + PEER_X_DATA_OFF) + ((size_t)slot * PEER_MAX_WORLD + src) * PEER_MAX_FLOATS;
+// exchange buffer at the launch's exchange point; every element is a (value, flag) pair and a reader
+// spins (bounded) on the pair itself until it carries this submission's flag.  The first column
+// tile also writes the sum to x_out for later readers.  Push: a segment's outputs go to every
+// rank's buffer as such pairs instead of C.  No extra launch, no fence, no counter.
+__device__ __forceinline__ uint2 *peer_slot(const PeerLink &l, uint32_t owner, uint32_t slot, uint32_t src) {
+  return reinterpret_cast<uint2 *>(l.buf[owner] + PEER_X_DATA_OFF) + ((size_t)slot * PEER_MAX_WORLD + src) * PEER_MAX_FLOATS;
 }
-__device__ __forceinline__ uint32_t *peer_arrivals(const PeerLink &l, uint32_t owner, uint32_t point, uint32_t src) {
-  return reinterpret_cast<uint32_t *>(l.buf[owner] + PEER_X_FLAG_OFF) + (size_t)point * PEER_MAX_WORLD + src;
+// One pushed element: the value once its flag is this submission's.  `dead` is the caller's
+// give-up state: after one wait has run out no later element waits again.
+__device__ __forceinline__ float peer_pair_load(const uint2 *p, uint32_t flag, uint64_t limit_ns, uint32_t *status, bool &dead) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  if (v.y != flag && !dead) {
+    const uint64_t t0 = umma::global_timer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+      if (v.y == flag) break;
+      if ((++spins & 255u) == 0 && umma::global_timer_ns() - t0 > limit_ns) {
+        if (status) atomicOr(status, 4u);     // reported by the host; the sums are then invalid
+        dead = true;
+        break;
+      }
+    }
+  }
+  return __uint_as_float(v.x);
 }
 
 template <int MROWS, int TN, bool BULK, bool PEER = false>
@@ -190,9 +208,16 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   // fetch it now (it may live in host memory) so its latency hides behind the weights
   uint32_t pos = p.pos_base;
   if (p.pos_ptr && rank == 0 && p.store_kind != 0) pos += *p.pos_ptr;
-  uint32_t want = 0;   // arrivals per source rank that complete this use of the pulled point
-  if constexpr (PEER)
-    if (g.peer.pull_point1) want = *g.peer.expect_ptr;   // host-written before the submission, like the position
+  // a position the rope table or the scatter destination does not hold: every access that uses it
+  // is skipped and the host is told (status bit 3)
+  const bool pos_bad = p.store_kind != 0 && rank == 0 && pos >= p.pos_limit;
+  if (pos_bad) {
+    if (threadIdx.x == 0 && g.status) atomicOr(g.status, 8u);
+    pos = 0;
+  }
+  uint32_t pull_flag = 0;   // what every element of this submission's push carries
+  if constexpr (PEER)       // the use counts were staged by the submission's first stream operation, long before this launch
+    if (g.peer.pull_point1) pull_flag = peer_flag_of(g.peer.expect_base[g.peer.pull_point1 - 1], g.peer.pull_point1);
   // also independent of earlier kernels: the norm weights of the first slice elements
   // and this thread's rope table entry; epilogue operands (D, bias, old C) follow the wait
   float nwv[XS_PRE];
@@ -222,32 +247,15 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   // product: the slice is staged as x[k] * w[k] and rank 0 multiplies the finished
   // sums by s.  Only rank 0 needs s, and nothing waits for it before the epilogue.
   const bool pull = PEER && g.peer.pull_point1 != 0;
-  if constexpr (PEER) {
-    if (pull) {
-      // every rank's push of this step must have landed here: arrivals[point][src] counts them
-      if (threadIdx.x < g.peer.world) {
-        const uint32_t *f = peer_arrivals(g.peer, g.peer.rank, g.peer.pull_point1 - 1, threadIdx.x);
-        const uint64_t t0 = umma::global_timer_ns();
-        uint32_t seen = 0, spins = 0;
-        for (;;) {
-          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-          if ((int32_t)(seen - want) >= 0) break;
-          if ((++spins & 255u) == 0 && umma::global_timer_ns() - t0 > g.peer.limit_ns) {
-            if (g.status) atomicOr(g.status, 4u);     // reported by the host; the sums below are then invalid
-            break;
-          }
-        }
-      }
-      __syncthreads();
-    }
-  }
+  bool peer_dead = false;
   // x[m, k]: from memory, or the rank-ordered sum of the pushed partial rows
   auto xval = [&](uint32_t m, uint32_t k) -> float {
     if constexpr (PEER) {
       if (pull) {
         float acc = 0.0f;
         for (uint32_t r = 0; r < g.peer.world; ++r)
-          acc += __ldcg(peer_slot(g.peer, g.peer.rank, g.peer.pull_slot, r) + (size_t)m * p.k + k);
+          acc += peer_pair_load(peer_slot(g.peer, g.peer.rank, g.peer.pull_slot, r) + (size_t)m * p.k + k, pull_flag,
+                                g.peer.limit_ns, g.status, peer_dead);
         return acc;
       }
     }
@@ -479,13 +487,15 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
       bool pushed = false;
       if constexpr (PEER) {
         if (p.push_point1) {     // this rank's partial row into every rank's buffer (its own included)
+          const uint32_t flag = peer_flag_of(g.peer.expect_base[p.push_point1 - 1], p.push_point1);
           for (uint32_t r = 0; r < g.peer.world; ++r)
-            const_cast<float *>(peer_slot(g.peer, r, p.push_slot, g.peer.rank))[ci] = v;
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(peer_slot(g.peer, r, p.push_slot, g.peer.rank) + ci),
+                         "r"(__float_as_uint(v)), "r"(flag) : "memory");
           pushed = true;
         }
       }
       if (!pushed) p.c[ci] = v;
-    } else {
+    } else if (!pos_bad) {
       if (p.store_kind != 2) {   // rope with the partner column (c ^ 1)
         const float partner = fin[idx ^ 1];
         const uint32_t dim = c % p.head_dim;
@@ -501,16 +511,6 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
         if (p.dst_f16) reinterpret_cast<__half *>(p.dst)[di] = __float2half_rn(v);
         else reinterpret_cast<float *>(p.dst)[di] = v;
       }
-    }
-  }
-  if constexpr (PEER) {
-    if (p.push_point1) {
-      // this tile's stores are out: make them visible system-wide, then one arrival per rank
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x < g.peer.world)
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(peer_arrivals(g.peer, threadIdx.x, p.push_point1 - 1, g.peer.rank))
-                     : "memory");
     }
   }
 }

@@ -308,7 +308,7 @@ argmax_sharded_kernel(const float *__restrict__ in, uint32_t n, uint32_t index_o
   __shared__ float sval[AMAX_THREADS / 32];
   __shared__ uint32_t sidx[AMAX_THREADS / 32];
   const uint32_t tid = threadIdx.x;
-  const uint32_t step = *l.expect_ptr;    // arrivals word of the pair exchange, host-written before the submission
+  const uint32_t step = *l.expect_ptr;    // arrivals word of the pair exchange: host-advanced, staged to the device by the submission
   if (pdl) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -378,7 +378,7 @@ bool Comm::argmax_sharded(const float *in, uint32_t n, uint32_t index_offset, ui
                           cudaStream_t stream) const {
   if (!fused_exchange_ready() || world < 2 || world > PEER_MAX_WORLD) return false;
   PeerLink l = link();
-  l.expect_ptr = expect_device + PEER_MAX_POINTS;
+  l.expect_ptr = expect_copy + PEER_MAX_POINTS;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1, 1, 1);
   cfg.blockDim = dim3(AMAX_THREADS, 1, 1);
@@ -471,9 +471,14 @@ void Comm::setup_peer_exchange() {
   }
   peer_own = buf;
   peer_bufs = mapped;
-  if (cudaHostAlloc((void **)&expect_host, (PEER_MAX_POINTS + 1) * sizeof(uint32_t), cudaHostAllocMapped) == cudaSuccess) {
+  if (cudaHostAlloc((void **)&expect_host, (PEER_MAX_POINTS + 1) * sizeof(uint32_t), cudaHostAllocDefault) == cudaSuccess) {
     memset(expect_host, 0, (PEER_MAX_POINTS + 1) * sizeof(uint32_t));
-    if (cudaHostGetDevicePointer((void **)&expect_device, expect_host, 0) != cudaSuccess) expect_device = nullptr;
+    if (cudaMalloc((void **)&expect_copy, (PEER_MAX_POINTS + 1) * sizeof(uint32_t)) != cudaSuccess) {
+      cudaGetLastError();
+      expect_copy = nullptr;
+    } else {
+      cudaMemset(expect_copy, 0, (PEER_MAX_POINTS + 1) * sizeof(uint32_t));
+    }
   } else {
     cudaGetLastError();
     expect_host = nullptr;
@@ -485,6 +490,7 @@ PeerLink Comm::link() const {
   for (uint32_t r = 0; r < world && r < PEER_MAX_WORLD; ++r) l.buf[r] = static_cast<uint8_t *>(peer_bufs[r]);
   l.rank = rank;
   l.world = world;
+  l.expect_base = expect_copy;
   l.expect_ptr = nullptr;
   l.limit_ns = peer_wait_limit_ns;
   return l;
@@ -532,6 +538,7 @@ void Comm::resync() {
       TA_CUDA(cudaMemset(static_cast<uint8_t *>(peer_own) + PEER_DATA_BYTES, 0, PEER_BUF_BYTES - PEER_DATA_BYTES));
       TA_CUDA(cudaDeviceSynchronize());
       if (expect_host) memset(expect_host, 0, (PEER_MAX_POINTS + 1) * sizeof(uint32_t));
+      if (expect_copy) TA_CUDA(cudaMemset(expect_copy, 0, (PEER_MAX_POINTS + 1) * sizeof(uint32_t)));
     }
   }
   cudaStreamDestroy(st);
@@ -547,6 +554,7 @@ Comm::~Comm() {
     cudaFree(peer_own);
   }
   if (expect_host) cudaFreeHost(expect_host);
+  if (expect_copy) cudaFree(expect_copy);
   if (handle) nccl().CommDestroy(handle);
 }
 

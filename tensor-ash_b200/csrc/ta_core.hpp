@@ -344,6 +344,8 @@ struct GemvParams {
   const float *table;
   void *dst;
   const uint32_t *pos_ptr;
+  uint32_t pos_limit;   // positions the rope table and the scatter destination hold; pos_base + *pos_ptr beyond it
+                        // raises status bit 3 and the kernel skips every access that uses the position
   // tensor-parallel exchange fused into the store: instead of C, the outputs go to slot `push_slot`
   // of every rank's exchange buffer as this rank's contribution to exchange point push_point1 - 1
   // (0 = off: an ordinary store)
@@ -352,18 +354,23 @@ struct GemvParams {
 
 // Exchange buffers of a tensor-parallel group as one rank sees them, and what a GEMV launch pulls
 // from them: its activation x is the sum over ranks (rank order) of what they pushed at
-// `pull_point1 - 1` (0 = off).  `pull_tiles` arrivals per rank and step complete a push.
+// `pull_point1 - 1` (0 = off).  A pushed element is an 8-byte (value, flag) pair written with one
+// store; flag = use count of the point * 512 + point + 1, unique per point and submission, so a
+// reader knows each element is this submission's by looking at it: no fence and no counter on the
+// path, one NVLink crossing between a producer's store and its readers.
 constexpr uint32_t PEER_MAX_WORLD = 8, PEER_MAX_FLOATS = 8192, PEER_MAX_POINTS = 256;
 struct PeerLink {
   uint8_t *buf[PEER_MAX_WORLD];
   uint32_t rank, world;
-  uint32_t pull_point1, pull_tiles, pull_slot;
+  uint32_t pull_point1, pull_slot;
   float *x_out;                 // where the summed activation is also written (by the first column tile)
-  // arrivals per source rank that complete the current use of the pulled point (or, for the sharded
-  // argmax, of the pair exchange): a host-written word the host advances before every submission
-  const uint32_t *expect_ptr;
-  uint64_t limit_ns;            // bounded wait for the peers' arrivals
+  // use counts of the exchange points (and, at PEER_MAX_POINTS, of the argmax pair exchange): advanced by
+  // the host before every submission and staged to device memory by the submission's first operation
+  const uint32_t *expect_base;
+  const uint32_t *expect_ptr;   // the sharded argmax's word
+  uint64_t limit_ns;            // bounded wait for the peers' data
 };
+__host__ __device__ inline uint32_t peer_flag_of(uint32_t use_count, uint32_t point1) { return use_count * 512u + point1; }
 
 // Up to three GEMVs sharing x, M, K, norm and tile width in one launch.
 constexpr int GEMV_MAX_SEGS = 3;
@@ -397,6 +404,7 @@ struct AttnDecodeParams {
   float scale;
   uint32_t kv_f16;
   const uint32_t *pos_ptr;
+  uint32_t *status;     // bit 3 is raised when kv_len + *pos_ptr exceeds t_max (the length is then clamped)
   uint32_t *counters;   // per-kv-head tickets (zero between launches), owned by the submitting slot
   uint32_t pdl;
   uint32_t prefetch_kv; // 1: the launch before this one wrote at most position kv_len - 1 of the cache
@@ -449,17 +457,14 @@ enum class ExecKind : uint32_t {
 constexpr size_t COMM_ID_BYTES = 128;
 // Layout of one rank's exchange buffer (all ranks map all buffers):
 //   [0, PEER_AR_BYTES)        the one-launch all-reduce kernel: data, flags, call counters
-//   then the fused exchange:  data[2 slots][world][PEER_MAX_FLOATS] f32,
-//                             arrivals[PEER_MAX_POINTS][world] u32 (monotonic),
+//   then the fused exchange:  data[2 slots][world][PEER_MAX_FLOATS] pairs of (f32 bits, flag),
 //                             argmax pairs[2][world] (value bits, index; slot = use parity) and arrivals[world] u32
 constexpr size_t PEER_AR_DATA_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_FLOATS * sizeof(float);
 constexpr size_t PEER_AR_FLAG_BYTES = 2ull * PEER_MAX_WORLD * 8 * sizeof(uint32_t);
 constexpr size_t PEER_AR_BYTES = PEER_AR_DATA_BYTES + PEER_AR_FLAG_BYTES + 8 * sizeof(uint32_t) + 96;   // 16-byte multiple
 constexpr size_t PEER_X_DATA_OFF = PEER_AR_BYTES;
-constexpr size_t PEER_X_DATA_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_FLOATS * sizeof(float);
-constexpr size_t PEER_X_FLAG_OFF = PEER_X_DATA_OFF + PEER_X_DATA_BYTES;
-constexpr size_t PEER_X_FLAG_BYTES = (size_t)PEER_MAX_POINTS * PEER_MAX_WORLD * sizeof(uint32_t);
-constexpr size_t PEER_AMAX_PAIR_OFF = PEER_X_FLAG_OFF + PEER_X_FLAG_BYTES;
+constexpr size_t PEER_X_DATA_BYTES = 2ull * PEER_MAX_WORLD * PEER_MAX_FLOATS * 8;
+constexpr size_t PEER_AMAX_PAIR_OFF = PEER_X_DATA_OFF + PEER_X_DATA_BYTES;
 constexpr size_t PEER_AMAX_FLAG_OFF = PEER_AMAX_PAIR_OFF + 2 * PEER_MAX_WORLD * 8;   // pairs of two consecutive uses
 constexpr size_t PEER_SMALL_TOTAL = PEER_AMAX_FLAG_OFF + PEER_MAX_WORLD * sizeof(uint32_t);
 //   then the two-step all-reduce of larger tensors (up to PEER_BIG_MAX_FLOATS, a prefill activation):
@@ -487,8 +492,11 @@ struct Comm {
   // PEER_MAX_POINTS: of the argmax pair exchange).  The host advances the words of the points a
   // submission uses before it launches; kernels read them like the position cell.  Every rank
   // submits the same plans in the same order, so the words agree across ranks.
-  uint32_t *expect_host = nullptr, *expect_device = nullptr;
-  bool fused_exchange_ready() const { return peer_own != nullptr && expect_device != nullptr; }
+  // expected-arrival words: written by the host (pinned memory) right before a submission and copied
+  // to device memory by the submission's first stream operation; kernels read only the device copy
+  // (a word in host memory costs every reading warp a PCIe round trip)
+  uint32_t *expect_host = nullptr, *expect_copy = nullptr;
+  bool fused_exchange_ready() const { return peer_own != nullptr && expect_host != nullptr && expect_copy != nullptr; }
   PeerLink link() const;   // buffers, rank, world, wait limit; pull fields zero
   // one-launch greedy pick over column-sharded logits; false when the peer path is unavailable
   bool argmax_sharded(const float *in, uint32_t n, uint32_t index_offset, uint32_t *result, uint32_t *status,
@@ -509,13 +517,21 @@ struct Comm {
 
 // The fused exchange points one submission uses: (point, arrivals per source rank), point
 // PEER_MAX_POINTS standing for the argmax pair exchange.  advance() is called on the host right
-// before the submission is launched.
+// before the submission is launched; stage() is the submission's first stream operation (recorded
+// into a prepared graph like any launch) and brings the words to the device.  Submissions that use
+// one communicator's exchange follow one another on the host: the next advance() comes after the
+// previous submission has completed.
 struct ExchangeUse {
   const Comm *comm = nullptr;
   std::vector<std::pair<uint32_t, uint32_t>> points;
   void advance() const {
     if (!comm || !comm->expect_host) return;
     for (const auto &pt : points) *(volatile uint32_t *)(comm->expect_host + pt.first) += pt.second;
+  }
+  void stage(cudaStream_t stream) const {
+    if (!comm || !comm->expect_host || !comm->expect_copy || points.empty()) return;
+    TA_CUDA(cudaMemcpyAsync(comm->expect_copy, comm->expect_host, (PEER_MAX_POINTS + 1) * sizeof(uint32_t),
+                            cudaMemcpyHostToDevice, stream));
   }
 };
 
@@ -730,6 +746,9 @@ class Executor {
 // Device status word of a slot: bit 0 = a bounded wait inside a kernel ran out (a barrier, a copy),
 // bit 2 = the peer exchange of a tensor-parallel all-reduce waited for a rank that did not arrive.
 [[noreturn]] inline void fail_device_status(uint32_t status) {
+  if (status & 8u)
+    fail("a position cell held a position outside the cache / rope table a kernel addresses with it "
+         "(status 0x%x); the kernel skipped those accesses, results are invalid", status);
   if (status & 4u)
     fail("a kernel gave up on a bounded device-side wait for a peer rank of the tensor-parallel exchange "
          "(status 0x%x); results are invalid", status);

@@ -335,6 +335,7 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       return [p, prefetch](Slot &slot, cudaStream_t st) {
         AttnDecodeParams q = p;
         q.counters = slot.counters;
+        q.status = slot.status;
         q.pdl = 1;
         q.prefetch_kv = prefetch;
         launch_attn_decode(q, st);
@@ -520,7 +521,8 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
   // one-row output -> GEMV reading that row` becomes two launches: the first pushes its partial
   // row into every rank's exchange buffer, the second waits for all ranks' rows, adds them in rank
   // order while it stages x, and leaves the sum in the tensor for later readers.  The same values
-  // in the same order on every rank, as the separate all-reduce gives.
+  // in the same order on every rank, as the separate all-reduce gives.  Every pushed element carries
+  // its own flag (see PeerLink), so nothing but the data crosses NVLink.
   struct Pending {
     const void *tensor = nullptr;
     uint32_t point = 0, tiles = 0, slot = 0;
@@ -547,13 +549,11 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
       comm = pending.comm;
       link = comm->link();
       link.pull_point1 = pending.point + 1;
-      link.pull_tiles = pending.tiles;
       link.pull_slot = pending.slot;
       link.x_out = const_cast<float *>(first_seg.x);
-      link.expect_ptr = comm->expect_device + pending.point;
       if (exchange) {
         exchange->comm = comm;
-        exchange->points.emplace_back(pending.point, pending.tiles);
+        exchange->points.emplace_back(pending.point, 1u);   // one use of the point per submission
       }
       pending = Pending{};
       *has_link = true;
@@ -705,6 +705,7 @@ RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
   if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
   exchange.advance();   // kernels with fused exchanges wait for the arrival counts of this submission
   return timed(slot, n_calls, flops, [&](cudaStream_t st) {
+    exchange.stage(st);
     for (const Launch &l : plan) l(slot, st);
   });
 }
@@ -728,6 +729,7 @@ RunStats Executor::run_exec_ops_timed(const std::vector<ExecOp> &ops, std::vecto
   RunStats st;
   try {
     st = timed(slot, n_calls, flops, [&](cudaStream_t s) {
+      exchange.stage(s);
       for (size_t i = 0; i < plan.size(); ++i) {
         TA_CUDA(cudaEventRecord(ev[i], s));
         plan[i](slot, s);
@@ -791,6 +793,7 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
     // attributes, tensor maps) consists of host calls, which a capture allows.
     TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
     try {
+      prep->exchange.stage(prep->stream);
       for (const Launch &l : plan) l(slot, prep->stream);
     } catch (...) {
       cudaGraph_t dead = nullptr;

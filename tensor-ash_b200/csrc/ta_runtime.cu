@@ -490,6 +490,19 @@ bool Executor::gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, cons
   g.dst = op.store.dst ? op.store.dst->ptr() : nullptr;
   g.dst_f16 = op.store.dst && op.store.dst->dtype == DType::F16;
   g.pos_ptr = op.store.pos_cell ? op.store.pos_cell->device : nullptr;
+  // the largest position count for which every table row and destination element the store touches exists
+  uint64_t limit = 0xffffffffull;
+  if (g.store_kind != 0 && g.head_dim) {
+    if (op.store.table && g.store_kind != 2) limit = std::min<uint64_t>(limit, op.store.table->len() / g.head_dim);
+    if (op.store.dst && g.store_kind >= 2) {
+      const uint64_t heads = r.n / g.head_dim;
+      const uint64_t rest = (heads ? heads - 1 : 0) * (uint64_t)g.stride_head + (uint64_t)(g.head_dim - 1) * g.stride_dim;
+      const uint64_t len = op.store.dst->len();
+      if (len <= rest) limit = 0;
+      else if (g.pos_scale) limit = std::min<uint64_t>(limit, (len - 1 - rest) / g.pos_scale + 1);
+    }
+  }
+  g.pos_limit = (uint32_t)limit;
   *out = g;
   return true;
 }

@@ -206,6 +206,26 @@ def test_attn_decode(gpu, orc, case, kv16):
     assert np.abs(got2 - ref).max() <= TOL
 
 
+def test_attn_decode_position_outside_the_cache_is_reported_not_read(gpu, orc):
+    """A position cell beyond the cache: the kernel clamps the length to t_max (no access outside the
+    cache), raises its status bit, the call fails with the position message, and the next call works."""
+    ta, ctx, ex = gpu
+    kv_heads, group, t_max, dh, scale = 2, 4, 128, 64, 0.125
+    kt_h, v_h = fill_kv(orc, kv_heads, t_max, dh, t_max, 1e30, seed=5301)
+    q_h = orc.fill_det(kv_heads * group * dh, 5302).reshape(kv_heads, group, dh)
+    q, kt, v = upload(ta, ctx, ex, q_h), upload(ta, ctx, ex, kt_h), upload(ta, ctx, ex, v_h)
+    scratch = ta.Tensor.uninit_device(ctx, (kv_heads * 32 * group * (dh + 2),))
+    out = ta.Tensor.uninit_device(ctx, (kv_heads, group, dh))
+    cell = ta.PosCell(ctx)
+    cell.set(t_max + 5)
+    with pytest.raises(ta.TensorAshError, match="position cell"):
+        ex.run_attn_decode(q, kt, v, scratch, out, 1, scale, pos_cell=cell)
+    cell.set(63)
+    ex.run_attn_decode(q, kt, v, scratch, out, 1, scale, pos_cell=cell)
+    ref = orc.cpu_attn_decode(q_h, kt_h, v_h, kv_heads, group, dh, t_max, 64, scale)
+    assert np.abs(ex.download(out).reshape(-1) - ref).max() <= TOL
+
+
 def test_attn_decode_rejections(gpu, orc):
     ta, ctx, ex = gpu
     E = ta.TensorAshError

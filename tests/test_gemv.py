@@ -182,6 +182,31 @@ def test_fused_stores(gpu, orc):
     check(orc, got[:, pos, :], vref, k, "scatter store")
 
 
+def test_fused_store_position_outside_the_cache_is_reported_not_written(gpu, orc):
+    """A position cell beyond the scatter destination: nothing is stored, the call fails with the
+    position message, and the same op with a valid position works afterwards."""
+    ta, ctx, ex = gpu
+    k, kv_heads, dh, t_max = 512, 2, 64, 32
+    x, hx = upload_det(ta, ctx, ex, orc, (1, k), 560)
+    wv, hwv = make_weights(ta, ctx, ex, orc, k, kv_heads * dh, 561, True)
+    v = ta.Tensor.uninit_device(ctx, (kv_heads, t_max, dh))
+    ex.upload(np.zeros(kv_heads * dh * t_max, np.float32), v)
+    dummy = ta.Tensor.uninit_device(ctx, (1, kv_heads * dh))
+    cell = ta.PosCell(ctx)
+    op = ta.MatmulOpEx(ta.MatmulCall(x, wv, dummy), packed_b=True,
+                       store=ta.MatmulStore(ta.StoreKind.SCATTER, head_dim=dh, pos_scale=dh,
+                                            stride_head=t_max * dh, stride_dim=1, dst=v, pos_cell=cell))
+    cell.set(t_max)                       # first position the destination does not hold
+    with pytest.raises(ta.TensorAshError, match="position cell"):
+        ex.run_ops_ex([op])
+    assert (ex.download(v) == 0).all()
+    cell.set(t_max - 1)
+    ex.run_ops_ex([op])
+    got = ex.download(v).reshape(kv_heads, t_max, dh)
+    assert (got[:, : t_max - 1, :] == 0).all()
+    check(orc, got[:, t_max - 1, :], orc.cpu_bmm(hx, hwv, 1, 1, kv_heads * dh, k).reshape(kv_heads, dh), k, "scatter at the last position")
+
+
 # src/matmul/resolution.rs:176-313 validation
 def test_rejections(gpu, orc):
     ta, ctx, ex = gpu

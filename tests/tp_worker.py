@@ -212,7 +212,7 @@ def main_wait():
     mine = np.arange(n, dtype=np.float32) * (rank + 1)
     ex.upload(mine, t)
     ex.run_exec_ops([ta.ExecOp.all_reduce(t, comm)])                      # a matched call first
-    assert np.array_equal(ex.download(t), np.arange(n, dtype=np.float32) * 3)
+    assert np.array_equal(ex.download(t).reshape(-1), np.arange(n, dtype=np.float32) * 3)
     dist.barrier()
     comm.set_wait_limit_ns(5_000_000)
     if rank == 0:
@@ -227,7 +227,7 @@ def main_wait():
     comm.set_wait_limit_ns(10_000_000_000)
     ex.upload(mine, t)
     ex.run_exec_ops([ta.ExecOp.all_reduce(t, comm)])
-    assert np.array_equal(ex.download(t), np.arange(n, dtype=np.float32) * 3), f"rank {rank}: sum after resync"
+    assert np.array_equal(ex.download(t).reshape(-1), np.arange(n, dtype=np.float32) * 3), f"rank {rank}: sum after resync"
     dist.barrier()
     t.close()
     comm.close()
