@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(128)
 flash_prefill_mma_kernel(const FlashParams p) {
   __shared__ __align__(16) __half Ksh[2][FM_DH * FM_LD];    // [d][pos]
   __shared__ __align__(16) __half Vsh[2][FM_BKV * FM_LD];   // [pos][d]
+  TA_CHAIN_ENTER();
   const uint32_t head = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t g = lane >> 2, t = lane & 3;
   const uint32_t q0 = blockIdx.x * FM_BQ;
@@ -547,7 +548,7 @@ bool flash_prefill_mma_eligible(const FlashParams &p) {
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream) {
   dim3 grid((p.t_q + 63) / 64, p.heads);
   if (flash_prefill_mma_eligible(p)) {
-    flash_prefill_mma_kernel<<<grid, 128, 0, stream>>>(p);
+    launch_chained(flash_prefill_mma_kernel, grid, dim3(128), 0, stream, p);
     launched();
     return;
   }

@@ -291,9 +291,9 @@ struct PreCfg {
 __global__ void __launch_bounds__(256)
 convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint32_t k, uint32_t kp, uint64_t rows) {
   // one thread per 8 output halves (16 bytes); the pad columns k..kp-1 are zeros
-  // the GEMM launched behind this kernel may set itself up while this one runs; it waits for this
-  // grid to finish before it reads the copy
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // chained launch: this kernel waits for the producer of A; the GEMM launched behind it may set
+  // itself up while this one runs and waits for this grid to finish before it reads the copy
+  TA_CHAIN_ENTER();
   const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const uint32_t per_row = kp / 8;
   if (idx >= rows * per_row) return;
@@ -338,6 +338,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   volatile uint32_t *tmem_slot =
       reinterpret_cast<volatile uint32_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
   volatile uint32_t *abort_flag = tmem_slot + 1;
+  const uint32_t red_bar = bar_base + 8u * (2 * C::STAGES + 4) + 16u;   // the split reduce's bulk copies land on it
   float *epi_buf = reinterpret_cast<float *>(smem_gen + C::STAGES * C::STAGE_BYTES + 256);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -350,6 +351,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       mbar_init(acc_full(b), 1);
       mbar_init(acc_empty(b), 128);
     }
+    mbar_init(red_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -362,7 +364,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   // launched with programmatic stream serialization behind the conversion of A: barriers, tensor
   // memory and the tensor maps are set up by now; nothing below touches global memory before the
   // conversion kernel has finished
-  if (p.pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (p.pdl_wait) TA_CHAIN_ENTER();
 
   const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const uint32_t tiles_per_batch = tiles_m * tiles_n;
@@ -488,70 +490,60 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
         if (*abort_flag) { ok = false; break; }
         __threadfence();
         // ---- this CTA's column slice of the tile: add the S partials in slice order, epilogue, store.
-        // A warp-wide access takes 4 rows x 8 column groups: 64 contiguous bytes per column group of
-        // a partial (whole sectors) and 128 contiguous bytes per row of C.  Four such blocks and two
-        // slices at a time: eight independent loads in flight per thread.
+        // In the partial layout the slice of one partial is contiguous (column groups x 128 rows x 16
+        // bytes), so S bulk copies bring all of it into the idle pipeline stages in one round trip;
+        // a lane then owns a row, reads conflict-free from shared memory and writes its 16-byte
+        // pieces of C (the slice is 32 KiB per CTA: the row-strided stores are not what costs).
         const uint32_t g4n = BN / splits / 4;                   // float4 column groups of this CTA's slice (splits divides BN / 4)
         const uint32_t g4_base = slice * g4n;
-        const uint32_t cblocks = (g4n + 7u) / 8u, blocks = 8u * cblocks;   // per warp: 8 row blocks x cblocks
-        const float4 *__restrict__ tile_parts4 = reinterpret_cast<const float4 *>(p.fw_partials + (size_t)tile * splits * (BM * BN));
+        const uint32_t slice_bytes = g4n * BM * 16u;
+        if (threadIdx.x == 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");     // the partials were written through the generic proxy
+          mbar_arrive_expect_tx(red_bar, slice_bytes * splits);
+          const uint8_t *src = reinterpret_cast<const uint8_t *>(p.fw_partials + (size_t)tile * splits * (BM * BN)) +
+                               (size_t)g4_base * BM * 16u;
+          for (uint32_t t = 0; t < splits; ++t)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_base + t * slice_bytes), "l"(src + (size_t)t * (BM * BN * 4)), "r"(slice_bytes), "r"(red_bar)
+                         : "memory");
+        }
+        ok = mbar_wait(red_bar, acc_it & 1u, abort_flag, 64);
+        if (!ok) break;
+        const float4 *__restrict__ sm4 = reinterpret_cast<const float4 *>(smem_gen);
         const size_t plane_off = (size_t)batch * p.stride_c;
         const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
-        const uint32_t r4 = (uint32_t)lane & 3u, cc = (uint32_t)lane >> 2;
+        const uint32_t r = warp * 32 + lane, row = m0 + r;
+        const bool row_ok = row < p.m;
         epi_dispatch_act(p.act, [&](auto act_tag) {
           constexpr uint32_t ACT = decltype(act_tag)::value;
-          constexpr int U = 4;
-          for (uint32_t base = 0; base < blocks; base += U) {
-            float4 acc[U];
-            const float4 *src[U];
-            size_t off[U];
-            uint32_t colu[U];
+          constexpr uint32_t U = 4;
+          for (uint32_t g0 = 0; g0 < g4n; g0 += U) {
+            float4 acc[U], c_old[U], dv[U], bv[U];
             bool live[U];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const uint32_t b = base + (uint32_t)u;
-              const uint32_t r = warp * 32 + (b & 7u) * 4 + r4, g4 = (b >> 3) * 8 + cc;
-              const uint32_t row = m0 + r, col = n0 + (g4_base + g4) * 4;
-              live[u] = b < blocks && g4 < g4n && row < p.m && col < p.n;
-              src[u] = tile_parts4 + (size_t)(g4_base + g4) * BM + r;
-              off[u] = plane_off + (size_t)row * p.n + col;
-              colu[u] = col;
-              acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t u = 0; u < U; ++u) {
+              const uint32_t g4 = g0 + u, col = n0 + (g4_base + g4) * 4;
+              live[u] = g4 < g4n && row_ok && col < p.n;
+              c_old[u] = dv[u] = bv[u] = acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (!live[u]) continue;
+              const size_t off = plane_off + (size_t)row * p.n + col;
+              if (p.accumulate) c_old[u] = *reinterpret_cast<const float4 *>(p.c + off);
+              if (bias) bv[u] = __ldg(reinterpret_cast<const float4 *>(bias + col));
+              if (p.d) dv[u] = *reinterpret_cast<const float4 *>(p.d + off);
             }
-            constexpr size_t PLANE4 = (size_t)BM * BN / 4;
-            uint32_t t = 0;
-            for (; t + 1 < splits; t += 2) {
-              float4 v0[U], v1[U];
+            for (uint32_t t = 0; t < splits; ++t) {
 #pragma unroll
-              for (int u = 0; u < U; ++u) {
-                v0[u] = live[u] ? __ldcg(src[u] + (size_t)t * PLANE4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                v1[u] = live[u] ? __ldcg(src[u] + (size_t)(t + 1) * PLANE4) : make_float4(0.f, 0.f, 0.f, 0.f);
-              }
-#pragma unroll
-              for (int u = 0; u < U; ++u) {
-                acc[u].x += v0[u].x; acc[u].y += v0[u].y; acc[u].z += v0[u].z; acc[u].w += v0[u].w;
-                acc[u].x += v1[u].x; acc[u].y += v1[u].y; acc[u].z += v1[u].z; acc[u].w += v1[u].w;
-              }
-            }
-            if (t < splits) {
-#pragma unroll
-              for (int u = 0; u < U; ++u) {
-                const float4 v = live[u] ? __ldcg(src[u] + (size_t)t * PLANE4) : make_float4(0.f, 0.f, 0.f, 0.f);
+              for (uint32_t u = 0; u < U; ++u) {
+                if (g0 + u >= g4n) continue;
+                const float4 v = sm4[(size_t)t * (slice_bytes / 16u) + (size_t)(g0 + u) * BM + r];
                 acc[u].x += v.x; acc[u].y += v.y; acc[u].z += v.z; acc[u].w += v.w;
               }
             }
-            float4 c_old[U], dv[U], bv[U];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-              c_old[u] = dv[u] = bv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t u = 0; u < U; ++u) {
               if (!live[u]) continue;
-              if (p.accumulate) c_old[u] = *reinterpret_cast<const float4 *>(p.c + off[u]);
-              if (bias) bv[u] = __ldg(reinterpret_cast<const float4 *>(bias + colu[u]));
-              if (p.d) dv[u] = *reinterpret_cast<const float4 *>(p.d + off[u]);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              if (!live[u]) continue;
+              const uint32_t col = n0 + (g4_base + g0 + u) * 4;
+              const size_t off = plane_off + (size_t)row * p.n + col;
               float4 o = acc[u];
               if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
               if (p.accumulate) { o.x += c_old[u].x; o.y += c_old[u].y; o.z += c_old[u].z; o.w += c_old[u].w; }
@@ -559,7 +551,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
               o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv[u].y, p.binary, dv[u].y, p.beta);
               o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv[u].z, p.binary, dv[u].z, p.beta);
               o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv[u].w, p.binary, dv[u].w, p.beta);
-              *reinterpret_cast<float4 *>(p.c + off[u]) = o;
+              *reinterpret_cast<float4 *>(p.c + off) = o;
             }
           }
         });
@@ -594,43 +586,65 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
           __syncwarp();
           const uint32_t col = n0 + c0 + cq;
           if (col < p.n) {
+            // One warp per scheduler runs this code, so nothing hides a dependent instruction's latency:
+            // all loads of the chunk (shared-memory tile, D, old C) are issued first, the arithmetic
+            // and the stores follow, and the loop-invariant cases are decided outside the row loop.
             float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
             if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+            float4 o[8], dv[8], c_old[8];
+            const bool rows_all = m0 + warp * 32 + 32 <= p.m;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const uint32_t r = (uint32_t)i * 4 + rsub, row = m0 + warp * 32 + r;
-              if (row < p.m) {
+              const uint32_t r = (uint32_t)i * 4 + rsub;
+              o[i] = *reinterpret_cast<const float4 *>(tbuf + r * EPI_PITCH + cq);
+              dv[i] = c_old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            if (p.d) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const uint32_t row = m0 + warp * 32 + (uint32_t)i * 4 + rsub;
+                if (rows_all || row < p.m) dv[i] = *reinterpret_cast<const float4 *>(p.d + plane_off + (size_t)row * p.n + col);
+              }
+            }
+            if (p.accumulate) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const uint32_t row = m0 + warp * 32 + (uint32_t)i * 4 + rsub;
+                if (!(rows_all || row < p.m)) continue;
                 const size_t off = plane_off + (size_t)row * p.n + col;
-                float4 o = *reinterpret_cast<const float4 *>(tbuf + r * EPI_PITCH + cq);
-                if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
-                __half *c16 = reinterpret_cast<__half *>(p.c) + off;   // a16 route: C is f16 storage
-                if (p.accumulate) {
-                  float4 c_old;
-                  if (p.c_f16) {
-                    const uint2 raw = *reinterpret_cast<const uint2 *>(c16);
-                    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-                    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-                    c_old = make_float4(lo.x, lo.y, hi.x, hi.y);
-                  } else {
-                    c_old = *reinterpret_cast<const float4 *>(p.c + off);
-                  }
-                  o.x += c_old.x; o.y += c_old.y; o.z += c_old.z; o.w += c_old.w;
-                }
-                float4 dv = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (p.d) dv = *reinterpret_cast<const float4 *>(p.d + off);
-                o.x = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv.x, p.beta);
-                o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv.y, p.beta);
-                o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv.z, p.beta);
-                o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv.w, p.beta);
                 if (p.c_f16) {
-                  const __half2 lo = __floats2half2_rn(o.x, o.y), hi = __floats2half2_rn(o.z, o.w);
-                  uint2 raw;
-                  raw.x = *reinterpret_cast<const uint32_t *>(&lo);
-                  raw.y = *reinterpret_cast<const uint32_t *>(&hi);
-                  *reinterpret_cast<uint2 *>(c16) = raw;
+                  const uint2 raw = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(p.c) + off);
+                  const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+                  const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+                  c_old[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
                 } else {
-                  *reinterpret_cast<float4 *>(p.c + off) = o;
+                  c_old[i] = *reinterpret_cast<const float4 *>(p.c + off);
                 }
+              }
+            }
+            const bool plain = ACT == 0 && !bias && !p.d && !p.accumulate && alpha_is_one && p.binary == 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t row = m0 + warp * 32 + (uint32_t)i * 4 + rsub;
+              if (!(rows_all || row < p.m)) continue;
+              const size_t off = plane_off + (size_t)row * p.n + col;
+              float4 v = o[i];
+              if (!plain) {
+                if (!alpha_is_one) { v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha; }
+                if (p.accumulate) { v.x += c_old[i].x; v.y += c_old[i].y; v.z += c_old[i].z; v.w += c_old[i].w; }
+                v.x = epi_apply_t<ACT>(v.x, bias != nullptr, bv.x, p.binary, dv[i].x, p.beta);
+                v.y = epi_apply_t<ACT>(v.y, bias != nullptr, bv.y, p.binary, dv[i].y, p.beta);
+                v.z = epi_apply_t<ACT>(v.z, bias != nullptr, bv.z, p.binary, dv[i].z, p.beta);
+                v.w = epi_apply_t<ACT>(v.w, bias != nullptr, bv.w, p.binary, dv[i].w, p.beta);
+              }
+              if (p.c_f16) {
+                const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                uint2 raw;
+                raw.x = *reinterpret_cast<const uint32_t *>(&lo);
+                raw.y = *reinterpret_cast<const uint32_t *>(&hi);
+                *reinterpret_cast<uint2 *>(reinterpret_cast<__half *>(p.c) + off) = raw;
+              } else {
+                *reinterpret_cast<float4 *>(p.c + off) = v;
               }
             }
           }
@@ -686,12 +700,13 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   // the conversion is launched only now, with the tensor maps encoded: the two launches reach the
   // device back to back, so the device does not idle between them while the host encodes
   if (!a16_ready) {
-    convert_a_f16_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(static_cast<const float *>(p.a), a16, p.k, kp, rows);
-    TA_CUDA(cudaGetLastError());
+    launch_chained(convert_a_f16_kernel, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, stream,
+                   static_cast<const float *>(p.a), a16, p.k, kp, rows);
     g_launches.fetch_add(1, std::memory_order_relaxed);
   }
-  // right behind the conversion kernel: start early, wait on the device (see the kernel)
-  pg.pdl_wait = (!a16_ready && tunables().pdl) ? 1u : 0u;
+  // chained launch (right behind the conversion kernel, or behind whatever produced the operands):
+  // start early, wait on the device (see the kernel)
+  pg.pdl_wait = tunables().pdl ? 1u : 0u;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(PRE_THREADS, 1, 1);
@@ -775,10 +790,12 @@ static size_t a16_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
 size_t gemm_f16w_umma_scratch_bytes(uint32_t batch_a, uint32_t m, uint32_t k) { return a16_bytes(batch_a, m, k); }
 
 // Tile width and K split for a problem on the pre-converted-A kernel.  The 512-row prefill shapes
-// have 32..176 tiles for 148 SMs and measure about 60 GB/s of operand traffic per CTA, so what a
-// CTA moves decides the time: cost = K blocks per CTA x bytes per block (A 16 KiB + B BN x 128 B),
-// plus a fixed charge for the split's partial-tile round trip.  Units (tiles x splits) must not
-// exceed the SM count when splitting; several waves without a split are charged in full.
+// have 32..176 tiles for 148 SMs and a CTA takes in about 130 GB/s of operands, so what a CTA moves
+// decides the time: cost = K blocks per CTA x KiB per block (A 16 + B BN / 8), plus a fixed charge
+// for the split's partial-tile round trip.  Measured over tile widths and splits on 512 x {2048,
+// 2560, 5632} x 2048, 512 x 2048 x 5632 and 1024 x 4096 x 1024: time = 17 us + 7.6 ns per KiB, a
+// split adds 4.5 to 6 us (650 KiB-equivalents).  Units (tiles x splits) must not exceed the SM count
+// when splitting; several waves without a split are charged in full.
 F16wPlan gemm_f16w_umma_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count, bool allow_split) {
   F16wPlan best;
   double best_cost = 1e300;
@@ -794,7 +811,7 @@ F16wPlan gemm_f16w_umma_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k,
       if (s > 1 && (tiles * s > (uint64_t)sm_count || kb / s < 4 || (bn / 4) % s != 0)) continue;
       if (force > 1 && s != (uint32_t)force && tiles * (uint64_t)force <= (uint64_t)sm_count && kb / force >= 4 && (bn / 4) % force == 0) continue;
       const uint64_t waves = s > 1 ? 1 : (tiles + sm_count - 1) / sm_count;
-      const double cost = (double)waves * ((kb + s - 1) / s) * block_kb + (s > 1 ? 150.0 : 0.0) + 90.0 +
+      const double cost = (double)waves * ((kb + s - 1) / s) * block_kb + (s > 1 ? 650.0 : 0.0) + 90.0 +
                           (bn == 192 && n % 192 ? 8.0 : 0.0);   // a partial last tile wastes part of its columns
       if (cost < best_cost) {
         best_cost = cost;

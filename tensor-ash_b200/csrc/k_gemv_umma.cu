@@ -210,8 +210,11 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
           }
         }
       }
+      // rows at or beyond p.m are skipped from here on: their operand rows stay unwritten, and the
+      // output columns they produce are never read
 #pragma unroll
-      for (int m = 0; m < 8; ++m)
+      for (int m = 0; m < 8; ++m) {
+        if ((uint32_t)m >= p.m) continue;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float x = xr[i][m][j];
@@ -220,9 +223,11 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
           xr[i][m][j] = v;
           mx[m] = fmaxf(mx[m], fabsf(v));
         }
+      }
     }
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
+      if ((uint32_t)m >= p.m) continue;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], o));
@@ -234,7 +239,7 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
       }
     }
     asm volatile("bar.sync 1, 160;" ::: "memory");
-    if (st < 8) {
+    if (st < 8 && (uint32_t)st < p.m) {
       float rmx = 0.0f, rss = 0.0f;
       for (int w = 0; w < 5; ++w) {       // warp order: a fixed sum
         rmx = fmaxf(rmx, red_max[w * 8 + st]);
@@ -258,7 +263,8 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
         uint8_t *base = xs_gen + (size_t)blk * 1024;
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
-          const float sc = (uint32_t)m < p.m ? 1.0f / unscale[m] : 0.0f;   // exact: a power of two
+          if ((uint32_t)m >= p.m) continue;
+          const float sc = 1.0f / unscale[m];   // exact: a power of two
           uint32_t hi[4], lo[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -334,8 +340,8 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
         const float *grp_rec = g.scratch + (size_t)grp * g.teams * GU_REC_FLOATS;
         const uint32_t col = grp * cols_per_group + (g.dual ? (tid & 63u) : tid);
         if (col >= p.n || (g.dual && tid >= 64)) return;
-        // records of four slices are requested together (slices in order: a fixed sum), the epilogue
-        // operands of all rows with the first of them: two or three L2 round trips per group
+        // records of four or eight slices are requested together (slices in order: a fixed sum), the
+        // epilogue operands of all rows with the first of them: one to three L2 round trips per group
         float s0[8], s1[8], ssum[8], oldc[8], dv[8];
         const float bv = p.bias ? p.bias[col] : 0.0f;
 #pragma unroll
@@ -346,24 +352,47 @@ gemv_umma_kernel(const __grid_constant__ GemvUmmaParams g, const __grid_constant
           oldc[m] = (live && p.accumulate) ? p.c[ci] : 0.0f;
           dv[m] = (live && p.d) ? p.d[ci] : 0.0f;
         }
-        for (uint32_t sl0 = 0; sl0 < g.teams; sl0 += 4) {
-          float a[4][8], b[4][8], q[4][8];
+        if (p.m <= 4) {
+          // up to four live rows: eight slices per batch fit the registers
+          for (uint32_t sl0 = 0; sl0 < g.teams; sl0 += 8) {
+            float a[8][4], b[8][4], q[8][4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float *r = grp_rec + (size_t)(sl0 + u) * GU_REC_FLOATS;
-            const bool have = sl0 + u < g.teams;
+            for (int u = 0; u < 8; ++u) {
+              const float *r = grp_rec + (size_t)(sl0 + u) * GU_REC_FLOATS;
+              const bool have = sl0 + u < g.teams;
 #pragma unroll
-            for (int m = 0; m < 8; ++m) {
-              const bool live = have && (uint32_t)m < p.m;
-              a[u][m] = live ? __ldcg(r + m * 128 + tid) : 0.0f;
-              b[u][m] = (live && g.dual) ? __ldcg(r + m * 128 + 64 + tid) : 0.0f;
-              q[u][m] = (live && p.norm_w) ? __ldcg(r + 8 * 128 + m) : 0.0f;
+              for (int m = 0; m < 4; ++m) {
+                const bool live = have && (uint32_t)m < p.m;
+                a[u][m] = live ? __ldcg(r + m * 128 + tid) : 0.0f;
+                b[u][m] = (live && g.dual) ? __ldcg(r + m * 128 + 64 + tid) : 0.0f;
+                q[u][m] = (live && p.norm_w) ? __ldcg(r + 8 * 128 + m) : 0.0f;
+              }
             }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+              for (int m = 0; m < 4; ++m) { s0[m] += a[u][m]; s1[m] += b[u][m]; ssum[m] += q[u][m]; }
           }
+        } else {
+          for (uint32_t sl0 = 0; sl0 < g.teams; sl0 += 4) {
+            float a[4][8], b[4][8], q[4][8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 4; ++u) {
+              const float *r = grp_rec + (size_t)(sl0 + u) * GU_REC_FLOATS;
+              const bool have = sl0 + u < g.teams;
 #pragma unroll
-            for (int m = 0; m < 8; ++m) { s0[m] += a[u][m]; s1[m] += b[u][m]; ssum[m] += q[u][m]; }
+              for (int m = 0; m < 8; ++m) {
+                const bool live = have && (uint32_t)m < p.m;
+                a[u][m] = live ? __ldcg(r + m * 128 + tid) : 0.0f;
+                b[u][m] = (live && g.dual) ? __ldcg(r + m * 128 + 64 + tid) : 0.0f;
+                q[u][m] = (live && p.norm_w) ? __ldcg(r + 8 * 128 + m) : 0.0f;
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int m = 0; m < 8; ++m) { s0[m] += a[u][m]; s1[m] += b[u][m]; ssum[m] += q[u][m]; }
+          }
         }
 #pragma unroll
         for (int m = 0; m < 8; ++m) {

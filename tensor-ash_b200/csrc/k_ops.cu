@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(ROW_THREADS)
 norm_rows_kernel(const float *__restrict__ in, const float *__restrict__ w,
                  const float *__restrict__ b, float *__restrict__ out, uint32_t cols, float eps,
                  bool layer_norm) {
+  TA_CHAIN_ENTER();
   __shared__ float sh[32];
   const float *x = in + (size_t)blockIdx.x * cols;
   float *y = out + (size_t)blockIdx.x * cols;
@@ -285,6 +286,7 @@ __global__ void prefill_qkv_pack_kernel(const float *__restrict__ qkv, const flo
                                         float *__restrict__ q, TKV *__restrict__ kt, TKV *__restrict__ v,
                                         uint32_t tokens, uint32_t heads, uint32_t kv_heads, uint32_t head_dim,
                                         uint32_t rot_dim, uint32_t pos_base, uint32_t t_max) {
+  TA_CHAIN_ENTER();
   const uint32_t half_dim = head_dim / 2, all_heads = heads + 2 * kv_heads;
   const uint64_t total = (uint64_t)tokens * all_heads * half_dim;
   const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -335,13 +337,13 @@ void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t co
 
 void launch_rms_norm(const float *in, const float *w, float *out, uint32_t rows, uint32_t cols,
                      float eps, cudaStream_t stream) {
-  norm_rows_kernel<<<rows, ROW_THREADS, 0, stream>>>(in, w, nullptr, out, cols, eps, false);
+  launch_chained(norm_rows_kernel, dim3(rows), dim3(ROW_THREADS), 0, stream, in, w, (const float *)nullptr, out, cols, eps, false);
   launched();
 }
 
 void launch_layer_norm(const float *in, const float *w, const float *b, float *out, uint32_t rows,
                        uint32_t cols, float eps, cudaStream_t stream) {
-  norm_rows_kernel<<<rows, ROW_THREADS, 0, stream>>>(in, w, b, out, cols, eps, true);
+  launch_chained(norm_rows_kernel, dim3(rows), dim3(ROW_THREADS), 0, stream, in, w, b, out, cols, eps, true);
   launched();
 }
 
@@ -424,11 +426,11 @@ void launch_prefill_qkv_pack(const float *qkv, const float *table, float *q, voi
   const uint64_t total = (uint64_t)tokens * (heads + 2 * kv_heads) * (head_dim / 2);
   const uint32_t blocks = (uint32_t)((total + 255) / 256);
   if (kv_f16)
-    prefill_qkv_pack_kernel<<<blocks, 256, 0, stream>>>(qkv, table, q, (__half *)kt, (__half *)v, tokens, heads,
-                                                        kv_heads, head_dim, rot_dim, pos_base, t_max);
+    launch_chained(prefill_qkv_pack_kernel<__half>, dim3(blocks), dim3(256), 0, stream, qkv, table, q, (__half *)kt, (__half *)v,
+                   tokens, heads, kv_heads, head_dim, rot_dim, pos_base, t_max);
   else
-    prefill_qkv_pack_kernel<<<blocks, 256, 0, stream>>>(qkv, table, q, (float *)kt, (float *)v, tokens, heads,
-                                                        kv_heads, head_dim, rot_dim, pos_base, t_max);
+    launch_chained(prefill_qkv_pack_kernel<float>, dim3(blocks), dim3(256), 0, stream, qkv, table, q, (float *)kt, (float *)v,
+                   tokens, heads, kv_heads, head_dim, rot_dim, pos_base, t_max);
   launched();
 }
 

@@ -755,6 +755,33 @@ class Executor {
   fail("a kernel gave up on a bounded device-side wait (status 0x%x); results are invalid", status);
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor
+// in the stream still runs and must execute TA_CHAIN_ENTER() before it touches global memory (the
+// wait returns when the predecessor has completed and its writes are visible; the trigger lets the
+// next kernel of the stream be scheduled in turn).  What is saved is the launch latency between
+// dependent kernels of a chain.  In a kernel launched without the attribute both instructions do nothing.
+#ifdef __CUDACC__
+#define TA_CHAIN_ENTER()                                             \
+  do {                                                               \
+    asm volatile("griddepcontrol.wait;" ::: "memory");               \
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); \
+  } while (0)
+template <typename... P, typename... A>
+inline void launch_chained(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tunables().pdl ? 1 : 0;
+  TA_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...));
+}
+#endif
+
 struct SlotGuard {
   Executor &e;
   Slot &s;
