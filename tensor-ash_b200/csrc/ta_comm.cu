@@ -169,8 +169,10 @@ peer_all_reduce_kernel(float *data, uint32_t count, PeerTable t, uint32_t *statu
 }
 
 // ------------------------------------------------------------------ two-step all-reduce (prefill activations)
-// A [T, embd] activation of a prefill step is a few MB: too large for the one-launch kernel above,
-// and NCCL spends most of its time on launch and protocol at this size.  The tensor is cut into
+// A [T, embd] activation of a prefill step is a few MB: too large for the one-launch kernel above.
+// This kernel is an experiment switch (peer_allreduce_big), off by default: with its two system-scope
+// fences per call it measured slower than NCCL at this size (512-token prefill of the 1.1 B model on
+// 4 GPUs: 4.25 ms against 3.85 ms), so NCCL carries these tensors.  The tensor is cut into
 // `world` slices; rank r owns slice r.  CTA b of every rank handles part b of every slice and
 // synchronises only with CTA b of the peers, through two flag words per (rank, CTA):
 //   step 1  push my values of slice s into rank s's `in` region, for every s != me; raise flag 1 there;
@@ -266,7 +268,8 @@ peer_all_reduce_big_kernel(float *data, uint32_t count, uint32_t slice, uint32_t
 }
 
 bool Comm::peer_all_reduce_big(float *data, size_t count, uint32_t *status, cudaStream_t stream) const {
-  if (!peer_own || count == 0 || count > PEER_BIG_MAX_FLOATS || (count & 3u) || (reinterpret_cast<uintptr_t>(data) & 15u))
+  if (!tunables().peer_allreduce_big || !peer_own || count == 0 || count > PEER_BIG_MAX_FLOATS || (count & 3u) ||
+      (reinterpret_cast<uintptr_t>(data) & 15u))
     return false;
   PeerTable t{};
   for (uint32_t r = 0; r < world; ++r) t.buf[r] = static_cast<uint8_t *>(peer_bufs[r]);

@@ -61,6 +61,7 @@ struct Tunables {
   uint32_t f16w_apad = 0;         // extra halves of row pitch of that f16 copy (multiple of 8)
   bool pdl = true;                // programmatic dependent launch between decode kernels
   bool peer_allreduce = true;     // one-launch peer-write all-reduce for small tensor-parallel exchanges
+  bool peer_allreduce_big = false; // all-reduce of prefill-sized tensors by the two-step peer kernel instead of NCCL (measured slower: 4.25 vs 3.85 ms per 512-token prefill on 4 GPUs)
   bool splitk2_tensor = true;     // split-K2 stage 1 on the tensor cores where the shape allows
   int f16w_splitk = -1;           // f16w tensor-core GEMM: K split for grids under one wave (-1 = per shape, 0/1 = off)
   uint32_t f16w_bn = 0;           // f16w tensor-core GEMM: tile width of the planned route (0 = per shape; 64 / 128 / 192 / 256)

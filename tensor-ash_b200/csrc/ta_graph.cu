@@ -453,7 +453,7 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       float *ptr = (float *)t.ptr();
       const size_t count = (size_t)t.len();
       return [=](Slot &slot, cudaStream_t st) {
-        // one-launch peer exchange for a row or two, the two-step peer kernel for a prefill activation, NCCL beyond
+        // one-launch peer exchange for a row or two; NCCL beyond (or, as an experiment, the two-step peer kernel)
         if (!comm->peer_all_reduce_sum(ptr, count, slot.status, true, st) && !comm->peer_all_reduce_big(ptr, count, slot.status, st))
           comm->all_reduce_sum(ptr, count, st);
       };

@@ -72,12 +72,13 @@ Tunables parse_tunables(const char *spec) {
     else if (name == "f16w_apad") t.f16w_apad = (uint32_t)(v > 0 ? v : 0) & ~7u;
     else if (name == "pdl") t.pdl = v != 0;
     else if (name == "peer_allreduce") t.peer_allreduce = v != 0;
+    else if (name == "peer_allreduce_big") t.peer_allreduce_big = v != 0;
     else if (name == "splitk2_tensor") t.splitk2_tensor = v != 0;
     else if (name == "f16w_splitk") t.f16w_splitk = (int)v;
     else if (name == "f16w_bn") t.f16w_bn = (uint32_t)v;
     else
       fail("TA_EXPERIMENT: unknown switch '%s' (known: tf32x3_chunk_kb, gemv_ksplit, gemv_bulk, gemv_umma, "
-           "f16w_pre, f16w_apad, pdl, peer_allreduce, splitk2_tensor, f16w_splitk, f16w_bn)", name.c_str());
+           "f16w_pre, f16w_apad, pdl, peer_allreduce, peer_allreduce_big, splitk2_tensor, f16w_splitk, f16w_bn)", name.c_str());
   }
   return t;
 }

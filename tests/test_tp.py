@@ -21,9 +21,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "tp_worker.py")
 
 
-def run_workers(mode: str, world: int, port: int, timeout: int = 600):
+def run_workers(mode: str, world: int, port: int, timeout: int = 600, **extra_env):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(world),
-               NCCL_NVLS_ENABLE="0")
+               NCCL_NVLS_ENABLE="0", **extra_env)
     procs = []
     for rank in range(world):
         e = dict(env, RANK=str(rank), LOCAL_RANK=str(rank))
@@ -78,6 +78,19 @@ def test_sharded_llama_on_devices_matches_host_forward(ta, orc, world, port):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     outs = run_workers("gpu", world, port)
+    for rc, out in outs:
+        assert rc == 0, out
+        assert "TP-GPU-OK" in out, out
+
+
+@pytest.mark.gpu
+def test_two_step_peer_all_reduce_experiment_is_exact(ta, orc):
+    """The same worker with the prefill-sized all-reduces routed to the two-step peer kernel (an
+    experiment switch; NCCL carries them by default): integer-valued sums must be exact."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    outs = run_workers("gpu", 2, 29618, TA_EXPERIMENT="peer_allreduce_big=1")
     for rc, out in outs:
         assert rc == 0, out
         assert "TP-GPU-OK" in out, out

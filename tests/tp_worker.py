@@ -170,7 +170,7 @@ def main_gpu():
     for _ in range(3):      # repeated uses advance the arrival words in step on every rank
         ex.run_exec_ops([ta.ExecOp.argmax_sharded(t_sl, rank * vocab_l, cell, comm)])
         assert cell.get() == (world - 1) * vocab_l + 123, f"rank {rank}: sharded argmax {cell.get()}"
-    # all-reduce of prefill-sized activations (the two-step peer kernel): exact on integer-valued
+    # all-reduce of prefill-sized activations (NCCL, or the two-step peer kernel under its switch): exact on integer-valued
     # inputs, repeated so that the per-CTA call counts advance, at a ragged and at the largest size
     for rows, cols in ((300, 256), (37, 1028), (512, 2048)):
         t_big = ta.Tensor.uninit_device(ctx, (rows, cols))
