@@ -319,6 +319,9 @@ flash_prefill_mma_kernel(const FlashParams p) {
         *reinterpret_cast<__half2 *>(reinterpret_cast<__half *>(p.out) + off + 8 * j + 2 * t) = __floats2half2_rn(x, y);
       } else {
         *reinterpret_cast<float2 *>(p.out + off + 8 * j + 2 * t) = make_float2(x, y);
+        if (p.out16)   // token-major output also as the f16 A of the projection that follows
+          *reinterpret_cast<__half2 *>(static_cast<__half *>(p.out16) + (size_t)head * p.o_head_stride +
+                                       (size_t)row * p.out16_row_stride + 8 * j + 2 * t) = __floats2half2_rn(x, y);
       }
     }
   };
@@ -552,6 +555,7 @@ void launch_flash_prefill(const FlashParams &p, cudaStream_t stream) {
     launched();
     return;
   }
+  if (p.out16) fail("internal: the f16 mirror of an attention output was planned on a problem the tensor-core kernel does not take");
   if (p.io_f16)
     fail("run_flash_attention: f16 q/out need the tensor-core kernel (f16 caches, dh 64, T_max %% 8 == 0, "
          "even strides, 16-byte aligned caches)");

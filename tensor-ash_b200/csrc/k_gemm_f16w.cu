@@ -783,6 +783,8 @@ uint32_t gemm_f16w_umma_tile_n(uint32_t batch, uint32_t m, uint32_t n, int sm_co
 // Row pitch (in halves) of the f16 copy of A: K rounded up to 8, plus the experiment switch f16w_apad.
 static uint32_t a16_pitch(uint32_t k) { return ((k + 7u) & ~7u) + tunables().f16w_apad; }
 
+uint32_t gemm_f16w_umma_a16_pitch(uint32_t k) { return a16_pitch(k); }
+
 // Scratch bytes for the f16 copy of A (rounded up to 256) ...
 static size_t a16_bytes(uint32_t batch_a, uint32_t m, uint32_t k) {
   return ((size_t)((uint64_t)batch_a * m * a16_pitch(k) * 2) + 255u) & ~(size_t)255u;

@@ -65,7 +65,7 @@ softmax_rows_kernel(const float *__restrict__ in, float *__restrict__ out, uint3
 __global__ void __launch_bounds__(ROW_THREADS)
 norm_rows_kernel(const float *__restrict__ in, const float *__restrict__ w,
                  const float *__restrict__ b, float *__restrict__ out, uint32_t cols, float eps,
-                 bool layer_norm) {
+                 bool layer_norm, __half *__restrict__ out16, uint32_t pitch16) {
   TA_CHAIN_ENTER();
   __shared__ float sh[32];
   const float *x = in + (size_t)blockIdx.x * cols;
@@ -84,10 +84,15 @@ norm_rows_kernel(const float *__restrict__ in, const float *__restrict__ w,
   ss = block_reduce(ss, false, sh);
   const float inv = rsqrtf(ss / (float)cols + eps);
   // the row may be normalised in place: every read of x[j] happens before the write of y[j]
+  __half *y16 = out16 ? out16 + (size_t)blockIdx.x * pitch16 : nullptr;
   for (uint32_t j = threadIdx.x; j < cols; j += ROW_THREADS) {
     const float v = (x[j] - mean) * inv * w[j];
-    y[j] = layer_norm ? v + b[j] : v;
+    const float r = layer_norm ? v + b[j] : v;
+    y[j] = r;
+    if (y16) y16[j] = __float2half_rn(r);   // the f16 copy a tensor-core GEMM reading this row next takes as its A
   }
+  if (y16)
+    for (uint32_t j = cols + threadIdx.x; j < pitch16; j += ROW_THREADS) y16[j] = __float2half_rn(0.0f);
 }
 
 __global__ void rope_kernel(const float *__restrict__ in, const float *__restrict__ table,
@@ -336,14 +341,16 @@ void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t co
 }
 
 void launch_rms_norm(const float *in, const float *w, float *out, uint32_t rows, uint32_t cols,
-                     float eps, cudaStream_t stream) {
-  launch_chained(norm_rows_kernel, dim3(rows), dim3(ROW_THREADS), 0, stream, in, w, (const float *)nullptr, out, cols, eps, false);
+                     float eps, cudaStream_t stream, void *out16, uint32_t pitch16) {
+  launch_chained(norm_rows_kernel, dim3(rows), dim3(ROW_THREADS), 0, stream, in, w, (const float *)nullptr, out, cols, eps, false,
+                 static_cast<__half *>(out16), pitch16);
   launched();
 }
 
 void launch_layer_norm(const float *in, const float *w, const float *b, float *out, uint32_t rows,
                        uint32_t cols, float eps, cudaStream_t stream) {
-  launch_chained(norm_rows_kernel, dim3(rows), dim3(ROW_THREADS), 0, stream, in, w, b, out, cols, eps, true);
+  launch_chained(norm_rows_kernel, dim3(rows), dim3(ROW_THREADS), 0, stream, in, w, b, out, cols, eps, true,
+                 (__half *)nullptr, 0u);
   launched();
 }
 

@@ -395,6 +395,9 @@ struct FlashParams {
   uint32_t kv_f16;
   uint32_t simt;   // 1: pin the f32-operand kernel (run_flash_attention_simt of the reference)
   uint32_t io_f16; // 1: q and out are f16 storage (the reference's kv16 io16 dh64 route); tensor-core kernel only
+  // optional f16 mirror of a token-major f32 output ([T, heads * dh], row pitch out16_row_stride halves)
+  void *out16;
+  uint32_t out16_row_stride;
 };
 
 struct AttnDecodeParams {
@@ -542,6 +545,10 @@ struct ExecOp {
   const Tensor *in0 = nullptr, *in1 = nullptr, *in2 = nullptr, *in3 = nullptr, *out = nullptr;
   float f0 = 0.0f;
   uint32_t u0 = 0, u1 = 0, u2 = 0;
+  // planner-internal (never set through the C ABI): the op also leaves its output rounded to f16, row
+  // pitch a16_pitch halves, at the start of the slot scratch, where the f16-weight tensor-core GEMM
+  // that reads the output next expects the f16 copy of its A (RmsNorm and token-major flash attention)
+  uint32_t a16_pitch = 0;
   uint32_t heads = 0, head_dim = 0, rot_dim = 0, pos_base = 0;
   uint32_t extent[3] = {0, 0, 0}, src_offset = 0, src_strides[3] = {0, 0, 0};
   uint32_t dst_offset = 0, strides[3] = {0, 0, 0}, pos_scale = 0;
@@ -866,14 +873,17 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
 // number of column tiles (= pushing CTAs) of a GEMV launch over these segments
 uint32_t gemv_f16w_tiles(const GemvParams *segs, int nseg);
 
+bool flash_prefill_mma_eligible(const FlashParams &p);   // the tensor-core kernel takes this problem (it alone writes out16)
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream);
 void launch_attn_decode(const AttnDecodeParams &p, cudaStream_t stream);
 
 void launch_softmax_rows(const float *in, float *out, uint32_t rows, uint32_t cols, float scale,
                          uint32_t mask_kind, uint32_t valid_or_prefix, uint32_t rows_per_group,
                          cudaStream_t stream);
+uint32_t gemm_f16w_umma_a16_pitch(uint32_t k);   // row pitch (halves) of the f16 copy of A that GEMM family reads
+// out16 / pitch16: optional f16 mirror of the output (row pitch in halves; columns cols..pitch16-1 are zeroed)
 void launch_rms_norm(const float *in, const float *w, float *out, uint32_t rows, uint32_t cols,
-                     float eps, cudaStream_t stream);
+                     float eps, cudaStream_t stream, void *out16 = nullptr, uint32_t pitch16 = 0);
 void launch_layer_norm(const float *in, const float *w, const float *b, float *out, uint32_t rows,
                        uint32_t cols, float eps, cudaStream_t stream);
 void launch_rope(const float *in, const float *table, float *out, uint32_t tokens, uint32_t heads,

@@ -219,7 +219,15 @@ Launch Executor::plan_exec_op(const ExecOp &o, uint64_t *flops, size_t *n_calls)
       float *op = (float *)out.ptr();
       const float eps = o.f0;
       if (ln) return [=](Slot &, cudaStream_t st) { launch_layer_norm(ip, wp, bp, op, rows, cols, eps, st); };
-      return [=](Slot &, cudaStream_t st) { launch_rms_norm(ip, wp, op, rows, cols, eps, st); };
+      const uint32_t pitch16 = o.a16_pitch;
+      return [=](Slot &slot, cudaStream_t st) {
+        void *out16 = nullptr;
+        if (pitch16) {   // planned only in front of a GEMM whose scratch demand covers this copy
+          if (!slot.scratch || slot.scratch_bytes < (size_t)rows * pitch16 * 2) fail("internal: no scratch for the f16 copy of a norm output");
+          out16 = slot.scratch;
+        }
+        launch_rms_norm(ip, wp, op, rows, cols, eps, st, out16, pitch16);
+      };
     }
     case ExecKind::SoftmaxRows: {
       const Tensor &in = need(o.in0, "run_softmax_rows", "input"), &out = need(o.out, "run_softmax_rows", "output");
@@ -345,7 +353,16 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
       const FlashParams p = plan_flash_attention(need(o.in0, "run_flash_attention", "q"), need(o.in1, "run_flash_attention", "kt"),
                                                  need(o.in2, "run_flash_attention", "v"), need(o.out, "run_flash_attention", "out"),
                                                  o.flash);
-      return [p](Slot &, cudaStream_t st) { launch_flash_prefill(p, st); };
+      const uint32_t pitch16 = o.a16_pitch;
+      return [p, pitch16](Slot &slot, cudaStream_t st) {
+        FlashParams q = p;
+        if (pitch16) {
+          if (!slot.scratch || slot.scratch_bytes < (size_t)q.t_q * pitch16 * 2) fail("internal: no scratch for the f16 copy of an attention output");
+          q.out16 = slot.scratch;
+          q.out16_row_stride = pitch16;
+        }
+        launch_flash_prefill(q, st);
+      };
     }
     case ExecKind::Argmax: {
       const Tensor &in = need(o.in0, "run_argmax", "input");
@@ -563,13 +580,40 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     }
     return link;
   };
-  size_t i = 0;
+  size_t i = 0, a16_ready_for = (size_t)-1;
   while (i < ops.size()) {
     Cand c0 = candidate(ops[i]);
     if (pending.tensor && !(c0.gemv && (const void *)c0.g.x == pending.tensor))
       fail("internal: a fused tensor-parallel push is not followed by the launch that pulls it");
     if (!c0.gemv) {
       ExecOp op = ops[i];
+      // A norm or a token-major flash attention whose output is the A of the f16-weight tensor-core
+      // GEMM right behind it also writes that A rounded to f16 where the GEMM expects its copy: the
+      // separate conversion launch disappears (same values: the GEMM's own conversion rounds the same
+      // f32 numbers to nearest even).
+      if ((op.kind == ExecKind::RmsNorm || op.kind == ExecKind::FlashAttn) && op.out && i + 1 < ops.size() &&
+          ops[i + 1].kind == ExecKind::Matmul && ops[i + 1].mm.call.a && ops[i + 1].mm.call.a->ptr() == op.out->ptr() &&
+          !candidate(ops[i + 1]).gemv) {
+        const MatmulOp &nx = ops[i + 1].mm;
+        const ResolvedMatmul rn = ResolvedMatmul::from_op(nx);
+        const Route rt = plan_op(nx, rn, false);
+        const uint32_t pitch = gemm_f16w_umma_a16_pitch(rn.k);
+        bool ok = KERNEL_SPECS[rt.kernel].family == Family::F16wUmma && op_scratch_bytes(rn, rt) > 0 && rn.batch == 1 &&
+                  !rn.a_f16 && pitch == rn.k && op.out->dtype == DType::F32 && op.out->len() == (uint64_t)rn.m * rn.k;
+        if (ok && op.kind == ExecKind::FlashAttn) {   // token-major f32 output of the tensor-core kernel only
+          ok = op.flash.out_token_major_heads != 0 && op.in0 && op.in1 && op.in2;
+          if (ok) {
+            const FlashParams fp = plan_flash_attention(*op.in0, *op.in1, *op.in2, *op.out, op.flash);
+            ok = flash_prefill_mma_eligible(fp) && !fp.io_f16 && fp.o_head_stride == fp.dh &&
+                 fp.o_row_stride == fp.heads * fp.dh && fp.t_q == rn.m;
+          }
+        }
+        if (ok) {
+          op.a16_pitch = pitch;
+          a16_ready_for = i + 1;
+        }
+      }
+      if (op.kind == ExecKind::Matmul && a16_ready_for == i) op.mm.a16_ready = true;
       // two f16w tensor-core GEMMs in a row on the same A (up and gate of a prefill MLP): the f16
       // copy of A made for the first is still in the slot scratch when the second runs
       if (op.kind == ExecKind::Matmul && i > 0 && ops[i - 1].kind == ExecKind::Matmul) {

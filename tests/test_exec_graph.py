@@ -246,3 +246,70 @@ def test_prepared_mixed_graph_replays_with_position_cell(gpu, orc):
         np.testing.assert_array_equal(ex.download(nxt).ravel(), emb[tok.get()])
     got = ex.download(kt).reshape(heads, dh, t_max)
     np.testing.assert_allclose(got, want, rtol=3e-5, atol=3e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(128, 512, 256), (200, 1024, 384)])
+def test_norm_then_f16w_gemm_in_one_graph_equals_the_ops_run_apart(gpu, orc, m, k, n):
+    """In one submission the planner lets the RMSNorm also write its output rounded to f16 where the
+    tensor-core GEMM behind it expects the f16 copy of its A (the conversion launch disappears); run
+    apart, the GEMM converts for itself.  Same f32 values rounded the same way: bit-identical C."""
+    ta, ctx, ex = gpu
+    rng = np.random.default_rng(811)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    nw = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    w = (rng.standard_normal((k, n), dtype=np.float32) * 0.05).astype(np.float16)
+    tx, tnw = ta.Tensor.uninit_device(ctx, (m, k)), ta.Tensor.uninit_device(ctx, (k,))
+    xn = ta.Tensor.uninit_device(ctx, (m, k))
+    tw = ta.Tensor.uninit_device_f16(ctx, (k, n))
+    c1, c2 = ta.Tensor.uninit_device(ctx, (m, n)), ta.Tensor.uninit_device(ctx, (m, n))
+    ex.upload(x, tx)
+    ex.upload(nw, tnw)
+    ex.upload_f16(w.view(np.uint16), tw)
+    before = ta.kernel_launch_count()
+    ex.run_exec_ops([ta.ExecOp.rms_norm(tx, tnw, xn, 1e-5), ta.ExecOp.matmul(ta.MatmulOp(ta.MatmulCall(xn, tw, c1)))])
+    fused_launches = ta.kernel_launch_count() - before
+    xn_fused = ex.download(xn).copy()
+    before = ta.kernel_launch_count()
+    ex.run_exec_ops([ta.ExecOp.rms_norm(tx, tnw, xn, 1e-5)])
+    ex.run_exec_ops([ta.ExecOp.matmul(ta.MatmulOp(ta.MatmulCall(xn, tw, c2)))])
+    apart_launches = ta.kernel_launch_count() - before
+    assert fused_launches == apart_launches - 1          # norm + GEMM against norm + conversion + GEMM
+    assert np.array_equal(xn_fused.view(np.uint32), ex.download(xn).view(np.uint32))
+    assert np.array_equal(ex.download(c1).view(np.uint32), ex.download(c2).view(np.uint32))
+    ref = (xn_fused.astype(np.float64) @ w.astype(np.float64))
+    assert np.abs(ex.download(c1) - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.gpu
+def test_flash_then_f16w_gemm_in_one_graph_equals_the_ops_run_apart(gpu, orc):
+    """The token-major output of the tensor-core flash kernel also lands as the f16 A of the
+    projection behind it; bit-identical to attention and projection run as two submissions."""
+    ta, ctx, ex = gpu
+    heads, kv_heads, t, t_max, dh, n = 8, 2, 96, 128, 64, 320
+    rng = np.random.default_rng(812)
+    q = rng.standard_normal((heads, t, dh), dtype=np.float32)
+    kt = (rng.standard_normal((kv_heads, dh, t_max), dtype=np.float32)).astype(np.float16)
+    v = (rng.standard_normal((kv_heads, t_max, dh), dtype=np.float32)).astype(np.float16)
+    w = (rng.standard_normal((heads * dh, n), dtype=np.float32) * 0.05).astype(np.float16)
+    tq = ta.Tensor.uninit_device(ctx, q.shape)
+    tkt, tv = ta.Tensor.uninit_device_f16(ctx, kt.shape), ta.Tensor.uninit_device_f16(ctx, v.shape)
+    tw = ta.Tensor.uninit_device_f16(ctx, w.shape)
+    attn = ta.Tensor.uninit_device(ctx, (t, heads * dh))
+    c1, c2 = ta.Tensor.uninit_device(ctx, (t, n)), ta.Tensor.uninit_device(ctx, (t, n))
+    ex.upload(q, tq)
+    ex.upload_f16(kt.view(np.uint16), tkt)
+    ex.upload_f16(v.view(np.uint16), tv)
+    ex.upload_f16(w.view(np.uint16), tw)
+    flash = ta.ExecOp.flash_attn(tq, tkt, tv, attn, t, 0, 0.125, out_token_major_heads=heads)
+    before = ta.kernel_launch_count()
+    ex.run_exec_ops([flash, ta.ExecOp.matmul(ta.MatmulOp(ta.MatmulCall(attn, tw, c1)))])
+    fused_launches = ta.kernel_launch_count() - before
+    attn_fused = ex.download(attn).copy()
+    before = ta.kernel_launch_count()
+    ex.run_exec_ops([flash])
+    ex.run_exec_ops([ta.ExecOp.matmul(ta.MatmulOp(ta.MatmulCall(attn, tw, c2)))])
+    assert fused_launches == ta.kernel_launch_count() - before - 1
+    assert np.array_equal(attn_fused.view(np.uint32), ex.download(attn).view(np.uint32))
+    assert np.array_equal(ex.download(c1).view(np.uint32), ex.download(c2).view(np.uint32))
+    assert np.isfinite(ex.download(c1)).all()
