@@ -281,9 +281,10 @@ struct PreCfg {
   static constexpr int B_BYTES = PK * BN * 2;             // 32 KiB at BN = 256
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 4 : (BN == 128 ? 6 : 8));
-  // + per epilogue warp a 32 x 32 f32 transpose buffer (row pitch 36 floats: conflict-free
-  // float4 writes by row and float4 reads by 8-lane row segments)
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 4 * 32 * EPI_PITCH * 4 + 1024;
+  // + per epilogue warp two 32 x 32 f32 blocks (4 KiB each, 1 KiB aligned): the sources of the TMA
+  // stores of C in the 128-byte swizzle, or one transpose buffer of row pitch 36 floats
+  static constexpr int EPI_BYTES = 4 * 2 * 4096;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 256 + 1024;
   static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;  // tensor-memory columns between the two accumulators
   static constexpr int TMEM_COLS = 2 * ACC_STRIDE;         // 128, 256 or 512: powers of two
 };
@@ -325,21 +326,23 @@ convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint
 template <int BN, bool SPLITK>
 __global__ void __launch_bounds__(PRE_THREADS, 1)
 gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
-                     const __grid_constant__ CUtensorMap map_b, uint32_t *__restrict__ status) {
+                     const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                     uint32_t *__restrict__ status) {
   using C = PreCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+  const uint32_t epi_base = smem_base + C::STAGES * C::STAGE_BYTES;      // 1 KiB aligned: stages are multiples of 1 KiB
+  const uint32_t bar_base = epi_base + C::EPI_BYTES;
   auto full = [&](int s) { return bar_base + 8u * s; };
   auto empty = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
   auto acc_full = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
   auto acc_empty = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
   volatile uint32_t *tmem_slot =
-      reinterpret_cast<volatile uint32_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
+      reinterpret_cast<volatile uint32_t *>(smem_gen + C::STAGES * C::STAGE_BYTES + C::EPI_BYTES + 8 * (2 * C::STAGES + 4));
   volatile uint32_t *abort_flag = tmem_slot + 1;
   const uint32_t red_bar = bar_base + 8u * (2 * C::STAGES + 4) + 16u;   // the split reduce's bulk copies land on it
-  float *epi_buf = reinterpret_cast<float *>(smem_gen + C::STAGES * C::STAGE_BYTES + 256);
+  float *epi_buf = reinterpret_cast<float *>(smem_gen + C::STAGES * C::STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -514,10 +517,14 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
         const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
         const uint32_t r = warp * 32 + lane, row = m0 + r;
         const bool row_ok = row < p.m;
+        // blocks of 32 columns (8 float4 groups); a slice whose width is a multiple of 32 leaves
+        // through TMA stores like the unsplit tile, any other one is stored by the lanes
+        const bool tma_out = p.c_tma && (g4n % 8u) == 0;
+        uint32_t blk = 0;
         epi_dispatch_act(p.act, [&](auto act_tag) {
           constexpr uint32_t ACT = decltype(act_tag)::value;
-          constexpr uint32_t U = 4;
-          for (uint32_t g0 = 0; g0 < g4n; g0 += U) {
+          constexpr uint32_t U = 8;
+          for (uint32_t g0 = 0; g0 < g4n; g0 += U, ++blk) {
             float4 acc[U], c_old[U], dv[U], bv[U];
             bool live[U];
 #pragma unroll
@@ -541,9 +548,6 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
             }
 #pragma unroll
             for (uint32_t u = 0; u < U; ++u) {
-              if (!live[u]) continue;
-              const uint32_t col = n0 + (g4_base + g0 + u) * 4;
-              const size_t off = plane_off + (size_t)row * p.n + col;
               float4 o = acc[u];
               if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
               if (p.accumulate) { o.x += c_old[u].x; o.y += c_old[u].y; o.z += c_old[u].z; o.w += c_old[u].w; }
@@ -551,10 +555,38 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
               o.y = epi_apply_t<ACT>(o.y, bias != nullptr, bv[u].y, p.binary, dv[u].y, p.beta);
               o.z = epi_apply_t<ACT>(o.z, bias != nullptr, bv[u].z, p.binary, dv[u].z, p.beta);
               o.w = epi_apply_t<ACT>(o.w, bias != nullptr, bv[u].w, p.binary, dv[u].w, p.beta);
-              *reinterpret_cast<float4 *>(p.c + off) = o;
+              acc[u] = o;
+            }
+            const uint32_t col0 = n0 + (g4_base + g0) * 4;
+            if (tma_out) {
+              if (col0 >= p.n) break;                      // warp-uniform
+              const uint32_t sbuf = epi_base + (uint32_t)warp * 8192u + (blk & 1u) * 4096u;
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              __syncwarp();
+#pragma unroll
+              for (uint32_t u = 0; u < U; ++u) {
+                const uint32_t dst = sbuf + (uint32_t)lane * 128u + ((u ^ ((uint32_t)lane & 7u)) << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc[u].x), "f"(acc[u].y), "f"(acc[u].z),
+                             "f"(acc[u].w) : "memory");
+              }
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c),
+                             "r"((int)col0), "r"((int)(m0 + warp * 32)), "r"((int)batch), "r"(sbuf) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              }
+            } else {
+#pragma unroll
+              for (uint32_t u = 0; u < U; ++u)
+                if (live[u]) *reinterpret_cast<float4 *>(p.c + plane_off + (size_t)row * p.n + col0 + 4 * u) = acc[u];
             }
           }
         });
+        if (tma_out) {
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+        }
         // ---- the last slice to finish reading puts the tile's two ticket words back to zero
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 0) {
@@ -565,10 +597,83 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
         }
         continue;
       }
+      if (p.c_tma) {
+        // C leaves through TMA: a lane holds one row of a 32 x 32 block, applies the epilogue to it
+        // and writes it into a shared-memory block in the 128-byte swizzle (16-byte chunk c of row r
+        // at chunk c ^ (r & 7): conflict-free); one lane then issues a bulk tensor store of the
+        // block.  The stores are asynchronous: the warp goes on with the next block in its second
+        // buffer and only waits, before reusing a buffer, until the store issued from it has READ it.
+        // Rows and columns beyond M / N are clipped by the tensor map.  D and old C are read by
+        // rows (16 bytes per lane and instruction; the eight instructions of a block use every
+        // sector they touch).
+        const size_t plane_off = (size_t)batch * p.stride_c;
+        const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
+        const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(warp * 32) << 16);
+        const uint32_t row = m0 + warp * 32 + lane;
+        const bool row_ok = row < p.m;
+        epi_dispatch_act(p.act, [&](auto act_tag) {
+          constexpr uint32_t ACT = decltype(act_tag)::value;
+          const bool plain = ACT == 0 && !bias && !p.d && !p.accumulate && alpha_is_one && p.binary == 0;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            if (n0 + c0 >= p.n) break;
+            const uint32_t sbuf = epi_base + (uint32_t)warp * 8192u + (uint32_t)((c0 >> 5) & 1) * 4096u;
+            float v[32];
+            tmem_ld32(taddr + c0, v);
+            if (!plain) {
+              float4 dv[8], co[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                dv[q] = co[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                const uint32_t col = n0 + c0 + 4 * q;
+                if (row_ok && col < p.n) {
+                  const size_t off = plane_off + (size_t)row * p.n + col;
+                  if (p.d) dv[q] = *reinterpret_cast<const float4 *>(p.d + off);
+                  if (p.accumulate) co[q] = *reinterpret_cast<const float4 *>(p.c + off);
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint32_t col = n0 + c0 + 4 * q;
+                float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (bias && col < p.n) bv = __ldg(reinterpret_cast<const float4 *>(bias + col));
+                float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                if (!alpha_is_one) { o.x *= p.alpha; o.y *= p.alpha; o.z *= p.alpha; o.w *= p.alpha; }
+                if (p.accumulate) { o.x += co[q].x; o.y += co[q].y; o.z += co[q].z; o.w += co[q].w; }
+                v[4 * q] = epi_apply_t<ACT>(o.x, bias != nullptr, bv.x, p.binary, dv[q].x, p.beta);
+                v[4 * q + 1] = epi_apply_t<ACT>(o.y, bias != nullptr, bv.y, p.binary, dv[q].y, p.beta);
+                v[4 * q + 2] = epi_apply_t<ACT>(o.z, bias != nullptr, bv.z, p.binary, dv[q].z, p.beta);
+                v[4 * q + 3] = epi_apply_t<ACT>(o.w, bias != nullptr, bv.w, p.binary, dv[q].w, p.beta);
+              }
+            }
+            // the store issued from this buffer two blocks ago must have read it
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const uint32_t dst = sbuf + (uint32_t)lane * 128u + (((uint32_t)q ^ ((uint32_t)lane & 7u)) << 4);
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v[4 * q]), "f"(v[4 * q + 1]),
+                           "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c),
+                           "r"((int)(n0 + c0)), "r"((int)(m0 + warp * 32)), "r"((int)batch), "r"(sbuf) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        });
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // both buffers free for the next tile
+        __syncwarp();
+        tc_fence_before();
+        mbar_arrive(acc_empty(buf));
+        continue;
+      }
       // TMEM gives each lane one row; a row-per-lane store would touch 32 rows per instruction.
       // Transpose 32 x 32 blocks through shared memory so that every global access of the
       // epilogue (C, D, the old C when accumulating) covers full 128-byte row segments.
-      float *__restrict__ tbuf = epi_buf + warp * (32 * EPI_PITCH);
+      float *__restrict__ tbuf = epi_buf + warp * 2048;
       const uint32_t cq = (uint32_t)(lane & 7) * 4, rsub = (uint32_t)lane >> 3;
       const size_t plane_off = (size_t)batch * p.stride_c;
       const float *__restrict__ bias = p.bias ? p.bias + (size_t)batch * p.bias_stride : nullptr;
@@ -681,7 +786,7 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
   const uint64_t rows = ba * p.m;
   const uint64_t items = rows * (kp / 8);
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_c;
   // A16 [ba, M, Kp] f16: 128-byte rows of 64 halves, 128-byte swizzle; columns >= K read as zero (TMA bound K)
   encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a16, p.k, p.m, ba, (uint64_t)kp * 2,
               (uint64_t)p.m * kp * 2, PK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -694,6 +799,15 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   else
     encode_map3(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, p.n, p.k, bb, (uint64_t)p.n * 2, b_batch_bytes, 64, PK,
                 CU_TENSOR_MAP_SWIZZLE_128B);
+  // C [batch, M, N] f32 leaves through TMA stores of 32 x 32 blocks (128-byte rows, 128-byte swizzle)
+  // when it is f32 and addressable by a tensor map; the kernel otherwise stores it itself
+  pg.c_tma = (!p.c_f16 && p.n % 4 == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0 &&
+              (p.stride_c % 4) == 0 && tunables().f16w_tma_store) ? 1u : 0u;
+  if (pg.c_tma)
+    encode_map3(ctx, &map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.c, p.n, p.m, p.batch, (uint64_t)p.n * 4,
+                p.stride_c ? (uint64_t)p.stride_c * 4 : (uint64_t)p.m * p.n * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    map_c = map_a;
   const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch * (SPLITK ? p.fw_splits : 1u);
   if (SPLITK && tiles > (uint64_t)ctx.sm_count) fail("internal: split-K units (%llu) exceed the SM count", (unsigned long long)tiles);
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
@@ -717,7 +831,7 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pg.pdl_wait ? 1 : 0;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemm_f16w_pre_kernel<BN, SPLITK>, pg, map_a, map_b, status));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemm_f16w_pre_kernel<BN, SPLITK>, pg, map_a, map_b, map_c, status));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 

@@ -65,6 +65,7 @@ struct Tunables {
   bool splitk2_tensor = true;     // split-K2 stage 1 on the tensor cores where the shape allows
   int f16w_splitk = -1;           // f16w tensor-core GEMM: K split for grids under one wave (-1 = per shape, 0/1 = off)
   uint32_t f16w_bn = 0;           // f16w tensor-core GEMM: tile width of the planned route (0 = per shape; 64 / 128 / 192 / 256)
+  bool f16w_tma_store = true;     // f16w tensor-core GEMM: C leaves through TMA stores (0: the kernel stores it itself)
 };
 const Tunables &tunables();
 // parses `name=value,...` into a Tunables (throws on an unknown name); exposed for the host tests
@@ -308,6 +309,7 @@ struct GemmParams {
   float *fw_partials = nullptr;
   uint32_t *fw_counters = nullptr;
   uint32_t pdl_wait = 0;     // launcher-set: the kernel was launched to overlap its predecessor and waits for it on the device
+  uint32_t c_tma = 0;        // launcher-set (f16w tensor-core GEMM): C leaves through TMA stores of the launch's C tensor map
 };
 
 // Tile width / K split of the f16-weight tensor-core GEMM for a shape (see k_gemm_f16w.cu)

@@ -120,6 +120,33 @@ def test_fused_epilogues(setup, orc):
     assert rel_err(ex.download(c), ref) <= F16W_TOL
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 520, 8192), (130, 192, 4096), (512, 2048, 5632)])
+def test_in_kernel_k_split_with_partial_tiles_and_fused_epilogue(setup, orc, m, n, k):
+    """Deep-K shapes with few tiles take the in-kernel K split (partials in scratch, ticket, slice-wise
+    reduce): partial row and column tiles, bias + SiLU + scaled residual in the reducing pass, then
+    alpha with accumulation; two runs are bit-identical (fixed slice order)."""
+    ta, ctx, ex, _ = setup
+    a, ha = upload_det(ta, ctx, ex, orc, (m, k), 111)
+    b, hb = upload_f16w(ta, ctx, ex, orc, (k, n), 112)
+    bias, hbias = upload_det(ta, ctx, ex, orc, (n,), 113)
+    d, hd = upload_det(ta, ctx, ex, orc, (m, n), 114)
+    c = ta.Tensor.uninit_device(ctx, (m, n))
+    base = (ha.reshape(m, k).astype(np.float64) @ hb.reshape(k, n).astype(np.float64))
+    op = ta.MatmulOp(ta.MatmulCall(a, b, c),
+                     ta.Epilogue(bias=bias, activation=ta.Activation.SILU, binary=ta.Binary.ADD_SCALED, d=d, beta=0.5))
+    ex.run_ops([op])
+    z = base + hbias[None, :]
+    ref = z / (1.0 + np.exp(-z)) + 0.5 * hd.reshape(m, n)
+    first = ex.download(c).copy()
+    assert rel_err(first, ref) <= F16W_TOL
+    ex.run_ops([op])
+    assert np.array_equal(first.view(np.uint32), ex.download(c).view(np.uint32))
+    init = orc.fill_det(m * n, 115)
+    ex.upload(init, c)
+    ex.run_matmuls([ta.MatmulCall(a, b, c, 0.25, True)])
+    assert rel_err(ex.download(c), 0.25 * base + init.reshape(m, n)) <= F16W_TOL
+
+
 def test_prepared_replay_matches_direct_bitwise(setup, orc):
     ta, ctx, ex, _ = setup
     m, n, k = 256, 512, 256
