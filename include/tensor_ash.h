@@ -276,9 +276,9 @@ int ta_matmul_split_k2(const ta_executor *exec, const ta_matmul_call *calls, siz
  * The first call on each device looks up the array's device address
  * (cudaGetSymbolAddress) and, if nothing of the library ran on that device
  * before, pays the CUDA runtime's lazy load of the library's device code, which
- * may reserve device memory of its own; make that first call at start-up,
- * before any stream capture.  Later calls allocate nothing
- * (cudaMemGetInfo reads the same before and after them).
+ * may reserve device memory of its own; make that first call at start-up.
+ * Later calls allocate nothing (cudaMemGetInfo reads the same before and
+ * after them).
  * Every call uses the same array and leaves its partials there: nothing needs
  * clearing between calls (each plane element is stored before it is read), but
  * two calls that overlap on the GPU, from any thread or stream, race. */
