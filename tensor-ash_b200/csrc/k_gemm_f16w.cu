@@ -323,11 +323,15 @@ convert_a_f16_kernel(const float *__restrict__ a, __half *__restrict__ out, uint
 // adds the partials of ITS column slice of the tile in slice order and runs the epilogue on it.
 // The order of the sum is fixed, so results are run-to-run bit-identical, and the reduction is
 // spread over the CTAs that would otherwise idle.
-template <int BN, bool SPLITK>
+template <int BN, bool SPLITK, bool DUAL = false>
 __global__ void __launch_bounds__(PRE_THREADS, 1)
 gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                     const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c2,
                      uint32_t *__restrict__ status) {
+  static_assert(!DUAL || (!SPLITK && BN % 128 == 0), "the dual form takes whole 64-column groups of each matrix and no K split");
+  // DUAL: a tile is BN / 2 output columns; the B stage holds those columns of b, then of b2
+  constexpr int BNO = DUAL ? BN / 2 : BN;
   using C = PreCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -369,7 +373,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   // conversion kernel has finished
   if (p.pdl_wait) TA_CHAIN_ENTER();
 
-  const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
+  const uint32_t tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BNO - 1) / BNO;
   const uint32_t tiles_per_batch = tiles_m * tiles_n;
   const uint32_t splits = SPLITK ? p.fw_splits : 1u;
   const uint32_t num_tiles = tiles_per_batch * p.batch * splits;     // work units
@@ -391,7 +395,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       uint32_t tile, slice, kb_lo, kb_hi;
       decode(unit, tile, slice, kb_lo, kb_hi);
       const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-      const int m0 = (int)(rem % tiles_m) * BM, n0 = (int)(rem / tiles_m) * BN;
+      const int m0 = (int)(rem % tiles_m) * BM, n0 = (int)(rem / tiles_m) * BNO;
       const int za = p.stride_a ? (int)batch : 0, zb = p.stride_b ? (int)batch : 0;
       for (uint32_t kb = kb_lo; kb < kb_hi; ++kb) {
         ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag);
@@ -400,7 +404,10 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
         if (elect_one()) {
           mbar_arrive_expect_tx(full(stage), C::STAGE_BYTES);
           tma_load_3d(dst, &map_a, full(stage), (int)(kb * PK), m0, za);
-          if (p.b_grouped) {
+          if constexpr (DUAL) {   // grouped views only (N % 64 == 0): BN / 128 groups of each matrix
+            tma_load_4d(dst + C::A_BYTES, &map_b, full(stage), 0, (int)(kb * PK), n0 / 64, zb);
+            tma_load_4d(dst + C::A_BYTES + (BNO / 64) * (PK * 128), &map_b2, full(stage), 0, (int)(kb * PK), n0 / 64, zb);
+          } else if (p.b_grouped) {
             tma_load_4d(dst + C::A_BYTES, &map_b, full(stage), 0, (int)(kb * PK), n0 / 64, zb);
           } else {
 #pragma unroll
@@ -452,7 +459,7 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
       uint32_t tile, slice, kb_lo, kb_hi;
       decode(unit, tile, slice, kb_lo, kb_hi);
       const uint32_t batch = tile / tiles_per_batch, rem = tile % tiles_per_batch;
-      const uint32_t m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
+      const uint32_t m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BNO;
       const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
       ok = mbar_wait(acc_full(buf), acc_phase, abort_flag, 256);
       if (!ok) break;
@@ -595,6 +602,65 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
             p.fw_counters[2 * tile + 1] = 0u;
           }
         }
+        continue;
+      }
+      if constexpr (DUAL) {
+        // gate columns [0, BN/2) and up columns [BN/2, BN) of the accumulator: a lane reads its row of a
+        // 32-column block of both, forms silu(gate) * up with the formulas of the separate epilogue
+        // (activation, then the multiplying binary stage), and both blocks leave through TMA stores
+        // (the product to C, the plain up values to C2): the warp's two staging buffers alternate
+        const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(warp * 32) << 16);
+        const uint32_t sbuf0 = epi_base + (uint32_t)warp * 8192u, sbuf1 = sbuf0 + 4096u;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BNO; c0 += 32) {
+          if (n0 + c0 >= p.n) break;
+          float g[32], u[32];
+          tmem_ld32(taddr + c0, g);
+          tmem_ld32(taddr + BNO + c0, u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            g[i] = epi_apply_t<(uint32_t)Activation::Silu>(g[i], false, 0.0f, (uint32_t)BinaryKind::Mul, u[i], 0.0f);
+          // the product block of the chunk before must have been read (with C2 a second store is in flight)
+          if (lane == 0) {
+            if (p.c2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t dst = sbuf0 + (uint32_t)lane * 128u + (((uint32_t)q ^ ((uint32_t)lane & 7u)) << 4);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(g[4 * q]), "f"(g[4 * q + 1]), "f"(g[4 * q + 2]),
+                         "f"(g[4 * q + 3]) : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c),
+                         "r"((int)(n0 + c0)), "r"((int)(m0 + warp * 32)), "r"((int)batch), "r"(sbuf0) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          if (p.c2) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the up block of the chunk before
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const uint32_t dst = sbuf1 + (uint32_t)lane * 128u + (((uint32_t)q ^ ((uint32_t)lane & 7u)) << 4);
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(u[4 * q]), "f"(u[4 * q + 1]), "f"(u[4 * q + 2]),
+                           "f"(u[4 * q + 3]) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&map_c2),
+                           "r"((int)(n0 + c0)), "r"((int)(m0 + warp * 32)), "r"((int)batch), "r"(sbuf1) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+        tc_fence_before();
+        mbar_arrive(acc_empty(buf));
         continue;
       }
       if (p.c_tma) {
@@ -774,26 +840,33 @@ gemm_f16w_pre_kernel(const GemmParams p, const __grid_constant__ CUtensorMap map
   }
 }
 
-template <int BN, bool SPLITK = false>
+template <int BN, bool SPLITK = false, bool DUAL = false>
 void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t kp, uint32_t *status,
                   bool a16_ready, cudaStream_t stream) {
   using C = PreCfg<BN>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx.device & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemm_f16w_pre_kernel<BN, SPLITK>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    TA_CUDA(cudaFuncSetAttribute(gemm_f16w_pre_kernel<BN, SPLITK, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set[ctx.device & 63] = true;
   }
   const uint64_t ba = p.stride_a ? p.batch : 1, bb = p.stride_b ? p.batch : 1;
   const uint64_t rows = ba * p.m;
   const uint64_t items = rows * (kp / 8);
-  CUtensorMap map_a, map_b, map_c;
+  CUtensorMap map_a, map_b, map_c, map_b2, map_c2;
   // A16 [ba, M, Kp] f16: 128-byte rows of 64 halves, 128-byte swizzle; columns >= K read as zero (TMA bound K)
   encode_map3(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a16, p.k, p.m, ba, (uint64_t)kp * 2,
               (uint64_t)p.m * kp * 2, PK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
   const uint64_t b_batch_bytes = p.stride_b ? (uint64_t)p.stride_b * 2 : (uint64_t)p.k * p.n * 2;
   GemmParams pg = p;
   pg.b_grouped = p.n % 64 == 0 ? 1u : 0u;
-  if (pg.b_grouped)   // one TMA per stage for the whole BN-wide B block
+  constexpr int BNO = DUAL ? BN / 2 : BN;      // output columns per tile
+  if (DUAL) {         // BN / 128 column groups of each of the two matrices per stage
+    if (!pg.b_grouped || !p.b2) fail("internal: dual f16w GEMM launched without a second matrix or with N %% 64 != 0");
+    encode_map_grouped(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, 2, p.n, p.k, bb, b_batch_bytes, 64, PK,
+                       BNO / 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    encode_map_grouped(ctx, &map_b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b2, 2, p.n, p.k, bb, b_batch_bytes, 64, PK,
+                       BNO / 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else if (pg.b_grouped)   // one TMA per stage for the whole BN-wide B block
     encode_map_grouped(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.b, 2, p.n, p.k, bb, b_batch_bytes, 64, PK,
                        BN / 64, CU_TENSOR_MAP_SWIZZLE_128B);
   else
@@ -808,7 +881,15 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
                 p.stride_c ? (uint64_t)p.stride_c * 4 : (uint64_t)p.m * p.n * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
   else
     map_c = map_a;
-  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.batch * (SPLITK ? p.fw_splits : 1u);
+  if (!DUAL) map_b2 = map_b;
+  map_c2 = map_c;
+  if (DUAL) {
+    if (!pg.c_tma) fail("internal: dual f16w GEMM needs a TMA-addressable f32 C");
+    if (p.c2)
+      encode_map3(ctx, &map_c2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.c2, p.n, p.m, p.batch, (uint64_t)p.n * 4,
+                  p.stride_c ? (uint64_t)p.stride_c * 4 : (uint64_t)p.m * p.n * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  const uint64_t tiles = (uint64_t)((p.m + BM - 1) / BM) * ((p.n + BNO - 1) / BNO) * p.batch * (SPLITK ? p.fw_splits : 1u);
   if (SPLITK && tiles > (uint64_t)ctx.sm_count) fail("internal: split-K units (%llu) exceed the SM count", (unsigned long long)tiles);
   const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)ctx.sm_count);
   // the conversion is launched only now, with the tensor maps encoded: the two launches reach the
@@ -831,7 +912,7 @@ void launch_pre_t(const Context &ctx, const GemmParams &p, __half *a16, uint32_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pg.pdl_wait ? 1 : 0;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemm_f16w_pre_kernel<BN, SPLITK>, pg, map_a, map_b, map_c, status));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemm_f16w_pre_kernel<BN, SPLITK, DUAL>, pg, map_a, map_b, map_c, map_b2, map_c2, status));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -945,6 +1026,24 @@ F16wPlan gemm_f16w_umma_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k,
 size_t gemm_f16w_umma_scratch_bytes_split(uint32_t batch, uint32_t batch_a, uint32_t m, uint32_t n, uint32_t k, int sm_count) {
   const F16wPlan plan = gemm_f16w_umma_plan(batch, m, n, k, sm_count, true);
   return a16_bytes(batch_a, m, k) + plan.partial_bytes;
+}
+
+// The SwiGLU pair as one launch: plain products (alpha 1, no bias / accumulate / D), f32 C and C2,
+// one matrix per call, N a multiple of 64 (grouped weight views), everything 16-byte aligned, and
+// the tunables that give the pre-converted-A kernel with TMA stores.
+bool gemm_f16w_umma_dual_eligible(const GemmParams &p) {
+  if (!gemm_f16w_umma_eligible(p) || !p.b2 || p.batch != 1 || p.n % 64 || p.c_f16) return false;
+  if (p.alpha != 1.0f || p.accumulate || p.bias) return false;
+  if ((reinterpret_cast<uintptr_t>(p.b2) | reinterpret_cast<uintptr_t>(p.c) | reinterpret_cast<uintptr_t>(p.c2)) & 15u) return false;
+  return tunables().f16w_pre && tunables().f16w_tma_store && tunables().f16w_dual;
+}
+
+void launch_gemm_f16w_umma_dual(const Context &ctx, const GemmParams &p, uint32_t *status, void *scratch, size_t scratch_bytes,
+                                bool a16_ready, cudaStream_t stream) {
+  if (!gemm_f16w_umma_dual_eligible(p)) fail("internal: dual f16w GEMM launched on an ineligible problem");
+  if (!scratch || scratch_bytes < gemm_f16w_umma_scratch_bytes(1, p.m, p.k) || (reinterpret_cast<uintptr_t>(scratch) & 15u))
+    fail("internal: dual f16w GEMM needs scratch for the f16 copy of A");
+  launch_pre_t<256, false, true>(ctx, p, static_cast<__half *>(scratch), a16_pitch(p.k), status, a16_ready, stream);
 }
 
 void launch_gemm_a16_umma(const Context &ctx, const GemmParams &p_in, uint32_t tile_n, uint32_t *status,

@@ -66,6 +66,7 @@ struct Tunables {
   int f16w_splitk = -1;           // f16w tensor-core GEMM: K split for grids under one wave (-1 = per shape, 0/1 = off)
   uint32_t f16w_bn = 0;           // f16w tensor-core GEMM: tile width of the planned route (0 = per shape; 64 / 128 / 192 / 256)
   bool f16w_tma_store = true;     // f16w tensor-core GEMM: C leaves through TMA stores (0: the kernel stores it itself)
+  bool f16w_dual = true;          // f16w tensor-core GEMM: up and gate of a SwiGLU pair as one dual-matrix launch
 };
 const Tunables &tunables();
 // parses `name=value,...` into a Tunables (throws on an unknown name); exposed for the host tests
@@ -310,6 +311,11 @@ struct GemmParams {
   uint32_t *fw_counters = nullptr;
   uint32_t pdl_wait = 0;     // launcher-set: the kernel was launched to overlap its predecessor and waits for it on the device
   uint32_t c_tma = 0;        // launcher-set (f16w tensor-core GEMM): C leaves through TMA stores of the launch's C tensor map
+  // f16w tensor-core GEMM, two weight matrices sharing A (the SwiGLU pair of a prefill MLP): a tile
+  // holds BN/2 columns of b (gate) and the same BN/2 columns of b2 (up); C = silu(A b) * (A b2), and
+  // c2, when set, receives A b2
+  const void *b2 = nullptr;
+  float *c2 = nullptr;
 };
 
 // Tile width / K split of the f16-weight tensor-core GEMM for a shape (see k_gemm_f16w.cu)
@@ -318,6 +324,11 @@ struct F16wPlan {
   size_t partial_bytes = 0;
 };
 F16wPlan gemm_f16w_umma_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count, bool allow_split);
+// C = silu(A @ b) * (A @ b2) (and c2 = A @ b2) in one launch; p.b2 / p.c2 set.  Eligibility: the
+// checks of gemm_f16w_umma_dual_eligible; scratch as for the single GEMM (the f16 copy of A).
+bool gemm_f16w_umma_dual_eligible(const GemmParams &p);
+void launch_gemm_f16w_umma_dual(const Context &ctx, const GemmParams &p, uint32_t *status, void *scratch, size_t scratch_bytes,
+                                bool a16_ready, cudaStream_t stream);
 size_t gemm_f16w_umma_scratch_bytes_split(uint32_t batch, uint32_t batch_a, uint32_t m, uint32_t n, uint32_t k, int sm_count);
 
 // How the tensor-core stage 1 of split-K2 cuts a problem (see k_gemm_tf32x3.cu).  `planes` per batch
@@ -688,6 +699,9 @@ class Executor {
   // scratch an op wants in its slot beyond split-K planes (the f16 copy of A for the f16w tensor-core GEMM)
   size_t op_scratch_bytes(const ResolvedMatmul &r, const Route &route) const;
   SplitK2TensorPlan splitk2_plan_for(const GemmParams &p, uint32_t splits) const;
+  // `up` (plain) followed by `gate` = silu(A Wg) * up on the same A, both on the f16-weight tensor-core
+  // route: the parameters of the one dual-matrix launch that computes both, or false
+  bool dual_f16w_params(const MatmulOp &up, const MatmulOp &gate, GemmParams *out) const;
   size_t splitk2_scratch_bytes(const MatmulOp &op, const ResolvedMatmul &r, uint32_t splits) const;
   bool gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, const Route &route, GemvParams *out) const;
   // first_op (optional): for every planned launch, the index of the first op of `ops` it executes

@@ -614,6 +614,26 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         }
       }
       if (op.kind == ExecKind::Matmul && a16_ready_for == i) op.mm.a16_ready = true;
+      // up, then gate = silu(A Wg) * up, both on the f16-weight tensor-core route: one dual-matrix
+      // launch computes both (the same MMA sequence per output element and the same epilogue
+      // formulas as the two launches: bit-identical), A is staged once and `up` is not re-read
+      if (op.kind == ExecKind::Matmul && i + 1 < ops.size() && ops[i + 1].kind == ExecKind::Matmul) {
+        GemmParams dp;
+        if (dual_f16w_params(op.mm, ops[i + 1].mm, &dp)) {
+          validate_op_tensors(*this, op.mm);
+          validate_op_tensors(*this, ops[i + 1].mm);
+          const bool ready = op.mm.a16_ready;
+          if (flops) *flops += 2ull * 2ull * dp.m * dp.n * dp.k;
+          if (n_calls) *n_calls += 2;
+          plan.push_back([dp, cx, ready](Slot &slot, cudaStream_t st) {
+            launch_gemm_f16w_umma_dual(*cx, dp, slot.status, slot.scratch, slot.scratch_bytes, ready, st);
+          });
+          if (first_op) first_op->push_back(i);
+          prev_gemv.clear();
+          i += 2;
+          continue;
+        }
+      }
       // two f16w tensor-core GEMMs in a row on the same A (up and gate of a prefill MLP): the f16
       // copy of A made for the first is still in the slot scratch when the second runs
       if (op.kind == ExecKind::Matmul && i > 0 && ops[i - 1].kind == ExecKind::Matmul) {

@@ -437,6 +437,37 @@ SplitK2TensorPlan Executor::splitk2_plan_for(const GemmParams &p, uint32_t split
   return splitk2_tensor_plan(p, splits, ctx_->sm_count);
 }
 
+bool Executor::dual_f16w_params(const MatmulOp &up, const MatmulOp &gate, GemmParams *out) const {
+  if (!up.call.a || !gate.call.a || up.call.a->ptr() != gate.call.a->ptr()) return false;
+  const ResolvedMatmul ru = ResolvedMatmul::from_op(up), rg = ResolvedMatmul::from_op(gate);
+  if (ru.a_f16 || rg.a_f16 || !ru.b_f16 || !rg.b_f16 || ru.batch != 1 || rg.batch != 1) return false;
+  if (ru.m != rg.m || ru.n != rg.n || ru.k != rg.k) return false;
+  const Route tu = plan_op(up, ru, false), tg = plan_op(gate, rg, false);
+  if (tu.kernel < 0 || tg.kernel < 0 || tu.splits > 1 || tg.splits > 1) return false;
+  if (KERNEL_SPECS[tu.kernel].family != Family::F16wUmma || KERNEL_SPECS[tg.kernel].family != Family::F16wUmma) return false;
+  if (selection_ != -2 || tu.tuned || tg.tuned) return false;          // an explicit or tuned kernel choice is kept as given
+  if (!op_scratch_bytes(ru, tu) || !op_scratch_bytes(rg, tg)) return false;
+  // up: plain product; gate: silu, times the up output, nothing else
+  const Epilogue &eu = up.epilogue, &eg = gate.epilogue;
+  if (up.call.alpha != 1.0f || up.call.accumulate || eu.bias || eu.d || eu.activation != Activation::None ||
+      eu.binary != BinaryKind::None)
+    return false;
+  if (gate.call.alpha != 1.0f || gate.call.accumulate || eg.bias || eg.activation != Activation::Silu ||
+      eg.binary != BinaryKind::Mul || !eg.d || eg.d->ptr() != up.call.c->ptr())
+    return false;
+  if (up.call.c->ptr() == gate.call.c->ptr() || up.call.c->ptr() == up.call.a->ptr() || gate.call.c->ptr() == up.call.a->ptr())
+    return false;
+  GemmParams p = make_params(gate, rg);
+  p.d = nullptr;
+  p.act = 0;
+  p.binary = 0;
+  p.b2 = up.call.b->ptr();
+  p.c2 = static_cast<float *>(up.call.c->ptr());
+  if (!gemm_f16w_umma_dual_eligible(p)) return false;
+  *out = p;
+  return true;
+}
+
 // Bytes of plane scratch the split-K2 route of this problem needs in its slot.
 size_t Executor::splitk2_scratch_bytes(const MatmulOp &op, const ResolvedMatmul &r, uint32_t splits) const {
   if (splits <= 1) return 0;

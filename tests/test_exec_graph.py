@@ -313,3 +313,44 @@ def test_flash_then_f16w_gemm_in_one_graph_equals_the_ops_run_apart(gpu, orc):
     assert np.array_equal(attn_fused.view(np.uint32), ex.download(attn).view(np.uint32))
     assert np.array_equal(ex.download(c1).view(np.uint32), ex.download(c2).view(np.uint32))
     assert np.isfinite(ex.download(c1)).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n", [(512, 2048, 5632), (200, 512, 320), (128, 256, 64)])
+def test_up_then_gated_gemm_in_one_graph_equals_the_ops_run_apart(gpu, orc, m, k, n):
+    """`up = A Wu` followed by `gate = silu(A Wg) * up` on the f16-weight tensor-core route becomes one
+    dual-matrix launch in a graph: every output element goes through the same MMA sequence and the
+    same epilogue formulas as in the two launches, so both outputs are bit-identical to the ops run
+    as two submissions (incl. partial row tiles and a last partial column tile)."""
+    ta, ctx, ex = gpu
+    rng = np.random.default_rng(813)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    wu = (rng.standard_normal((k, n), dtype=np.float32) * 0.05).astype(np.float16)
+    wg = (rng.standard_normal((k, n), dtype=np.float32) * 0.05).astype(np.float16)
+    ta_a = ta.Tensor.uninit_device(ctx, (m, k))
+    twu, twg = ta.Tensor.uninit_device_f16(ctx, (k, n)), ta.Tensor.uninit_device_f16(ctx, (k, n))
+    up1, g1 = ta.Tensor.uninit_device(ctx, (m, n)), ta.Tensor.uninit_device(ctx, (m, n))
+    up2, g2 = ta.Tensor.uninit_device(ctx, (m, n)), ta.Tensor.uninit_device(ctx, (m, n))
+    ex.upload(a, ta_a)
+    ex.upload_f16(wu.view(np.uint16), twu)
+    ex.upload_f16(wg.view(np.uint16), twg)
+
+    def ops(up, gate):
+        return [ta.ExecOp.matmul(ta.MatmulOp(ta.MatmulCall(ta_a, twu, up))),
+                ta.ExecOp.matmul(ta.MatmulOp(ta.MatmulCall(ta_a, twg, gate),
+                                             ta.Epilogue(activation=ta.Activation.SILU, binary=ta.Binary.MUL, d=up)))]
+    before = ta.kernel_launch_count()
+    ex.run_exec_ops(ops(up1, g1))
+    fused = ta.kernel_launch_count() - before
+    first, second = ops(up2, g2)
+    before = ta.kernel_launch_count()
+    ex.run_exec_ops([first])
+    ex.run_exec_ops([second])
+    apart = ta.kernel_launch_count() - before
+    assert fused == 2 and apart == 4                    # conversion + dual GEMM against 2 x (conversion + GEMM)
+    assert np.array_equal(ex.download(up1).view(np.uint32), ex.download(up2).view(np.uint32))
+    assert np.array_equal(ex.download(g1).view(np.uint32), ex.download(g2).view(np.uint32))
+    u = a.astype(np.float64) @ wu.astype(np.float64)
+    z = a.astype(np.float64) @ wg.astype(np.float64)
+    ref = z / (1.0 + np.exp(-z)) * u
+    assert np.abs(ex.download(g1) - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
