@@ -509,9 +509,9 @@ attn_decode_kernel(const AttnDecodeParams p) {
   // chunks past the valid length hold nothing; partials come from other CTAs: L2 loads
   const uint32_t live_chunks = chunk_size ? min(p.num_chunks, (kv_len + chunk_size - 1) / chunk_size) : 0u;
   // one pass in chunk order with a running maximum (the rescale of an online softmax):
-  // no load depends on a computed value, so eight chunks' partials are in flight at once
+  // no load depends on a computed value, so sixteen chunks' partials are in flight at once
   float m_star = NEG_BIG, l_total = 0.0f, num[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
+#pragma unroll 16
   for (uint32_t i = 0; i < live_chunks; ++i) {
     const float m_i = __ldcg(&base[i * chunk_step + DEC_DH]);
     const float l_i = __ldcg(&base[i * chunk_step + DEC_DH + 1]);

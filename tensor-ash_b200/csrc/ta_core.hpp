@@ -67,6 +67,7 @@ struct Tunables {
   uint32_t f16w_bn = 0;           // f16w tensor-core GEMM: tile width of the planned route (0 = per shape; 64 / 128 / 192 / 256)
   bool f16w_tma_store = true;     // f16w tensor-core GEMM: C leaves through TMA stores (0: the kernel stores it itself)
   bool f16w_dual = true;          // f16w tensor-core GEMM: up and gate of a SwiGLU pair as one dual-matrix launch
+  uint32_t attn_chunks = 0;       // decode attention with a position cell: chunk grid (0 = one 64-position tile per chunk, 8..32)
 };
 const Tunables &tunables();
 // parses `name=value,...` into a Tunables (throws on an unknown name); exposed for the host tests

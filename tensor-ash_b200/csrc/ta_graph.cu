@@ -136,7 +136,12 @@ AttnDecodeParams Executor::plan_attn_decode(const Tensor &q, const Tensor &kt, c
   if (desc.kv_len == 0 || desc.kv_len > t_max) fail("run_attn_decode: kv_len %u out of range 1..=%u", desc.kv_len, t_max);
   if (desc.pos_cell && desc.pos_cell->ctx.get() != ctx_.get())
     fail("run_attn_decode: pos cell belongs to a different context");
-  const uint32_t num_chunks = desc.pos_cell ? ATTN_DECODE_MAX_CHUNKS : attn_decode_num_chunks(desc.kv_len);
+  // with a position cell the length is not known when the launch is recorded: the chunk grid is sized for
+  // the whole cache, one 64-position tile per chunk where that fits the 8..32 chunk range (fewer chunks
+  // = fewer partials for the last CTA to combine)
+  uint32_t num_chunks = desc.pos_cell ? std::min(ATTN_DECODE_MAX_CHUNKS, std::max(8u, (t_max + 63u) / 64u))
+                                      : attn_decode_num_chunks(desc.kv_len);
+  if (desc.pos_cell && tunables().attn_chunks >= 1) num_chunks = tunables().attn_chunks;
   const uint64_t needed = (uint64_t)kv_heads * num_chunks * group * (dh + 2);
   if (scratch.len() < needed)
     fail("run_attn_decode: scratch length %llu < required %llu (kv_heads %u * chunks %u * group %llu * (dh+2))",
