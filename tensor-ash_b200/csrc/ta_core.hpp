@@ -68,6 +68,7 @@ struct Tunables {
   bool f16w_tma_store = true;     // f16w tensor-core GEMM: C leaves through TMA stores (0: the kernel stores it itself)
   bool f16w_dual = true;          // f16w tensor-core GEMM: up and gate of a SwiGLU pair as one dual-matrix launch
   uint32_t attn_chunks = 0;       // decode attention with a position cell: chunk grid (0 = one 64-position tile per chunk, 8..32)
+  bool pos_stage = true;          // position cells read by graph launches are staged to device memory per submission
 };
 const Tunables &tunables();
 // parses `name=value,...` into a Tunables (throws on an unknown name); exposed for the host tests
@@ -359,6 +360,7 @@ struct GemvParams {
   const float *table;
   void *dst;
   const uint32_t *pos_ptr;
+  int32_t pos_stage_idx;   // planner-internal: >= 0 when the launch reads the position from the slot's staged device word
   uint32_t pos_limit;   // positions the rope table and the scatter destination hold; pos_base + *pos_ptr beyond it
                         // raises status bit 3 and the kernel skips every access that uses the position
   // tensor-parallel exchange fused into the store: instead of C, the outputs go to slot `push_slot`
@@ -546,7 +548,16 @@ struct ExchangeUse {
     if (!comm || !comm->expect_host) return;
     for (const auto &pt : points) *(volatile uint32_t *)(comm->expect_host + pt.first) += pt.second;
   }
-  void stage(cudaStream_t stream) const {
+  // Position cells the submission's GEMV stores and decode attentions read (pinned host words):
+  // copied to the slot's device words by the same first stream operation, so that the kernels read
+  // device memory (a word in host memory costs every reading warp a PCIe round trip, and the
+  // late-starting blocks of a launch cannot hide it behind their predecessor).  The host sets a cell
+  // before it submits and leaves it alone until the submission has completed.
+  std::vector<const uint32_t *> pos_cells_host;
+  void stage(cudaStream_t stream, uint32_t *pos_stage = nullptr) const {
+    if (pos_stage)
+      for (size_t i = 0; i < pos_cells_host.size(); ++i)
+        TA_CUDA(cudaMemcpyAsync(pos_stage + i, pos_cells_host[i], sizeof(uint32_t), cudaMemcpyHostToDevice, stream));
     if (!comm || !comm->expect_host || !comm->expect_copy || points.empty()) return;
     TA_CUDA(cudaMemcpyAsync(comm->expect_copy, comm->expect_host, (PEER_MAX_POINTS + 1) * sizeof(uint32_t),
                             cudaMemcpyHostToDevice, stream));
@@ -582,6 +593,9 @@ constexpr uint32_t ATTN_DECODE_MAX_KV_HEADS = 256;
 // ticket words per slot / prepared object: [0, 256) decode attention (one per kv head), then GEMV column groups
 constexpr uint32_t F16W_SPLIT_COUNTER0 = 256 + 4096;   // then two words per tile of a split f16-weight GEMM
 constexpr uint32_t SLOT_COUNTERS = F16W_SPLIT_COUNTER0 + 512;
+// behind the ticket words of a slot / prepared object: device copies of the position cells a submission reads
+constexpr uint32_t POS_STAGE_WORDS = 8;
+inline uint32_t *pos_stage_of(uint32_t *counters) { return counters + SLOT_COUNTERS; }
 inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
   const uint32_t c = (kv_len + 31) / 32;
   return c < 8 ? 8 : (c > ATTN_DECODE_MAX_CHUNKS ? ATTN_DECODE_MAX_CHUNKS : c);

@@ -345,8 +345,10 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
                                                   need(o.in2, "run_attn_decode", "v"), need(o.in3, "run_attn_decode", "scratch"),
                                                   need(o.out, "run_attn_decode", "out"), o.attn);
       const uint32_t prefetch = o.u0;   // internal hint from plan_exec_ops (the C ABI clears it)
-      return [p, prefetch](Slot &slot, cudaStream_t st) {
+      const int pos_idx = (int)o.u1 - 1;   // internal: index of the position cell's staged device word (u1 = index + 1)
+      return [p, prefetch, pos_idx](Slot &slot, cudaStream_t st) {
         AttnDecodeParams q = p;
+        if (pos_idx >= 0 && q.pos_ptr) q.pos_ptr = pos_stage_of(slot.counters) + pos_idx;
         q.counters = slot.counters;
         q.status = slot.status;
         q.pdl = 1;
@@ -585,6 +587,19 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     }
     return link;
   };
+  // position cells read by GEMV stores and decode attentions get a device word of the slot, filled by
+  // the submission's first stream operation; the launch closures swap the pointer in
+  auto stage_index = [&](const PosCell *cell) -> int {
+    if (!cell || !exchange || !tunables().pos_stage) return -1;
+    for (size_t k = 0; k < exchange->pos_cells_host.size(); ++k)
+      if (exchange->pos_cells_host[k] == cell->host) return (int)k;
+    if (exchange->pos_cells_host.size() >= POS_STAGE_WORDS) return -1;
+    exchange->pos_cells_host.push_back(cell->host);
+    return (int)exchange->pos_cells_host.size() - 1;
+  };
+  auto stage_gemv = [&](GemvParams &g, const ExecOp &op) {
+    if (g.pos_ptr && op.kind == ExecKind::Matmul) g.pos_stage_idx = stage_index(op.mm.store.pos_cell);
+  };
   size_t i = 0, a16_ready_for = (size_t)-1;
   while (i < ops.size()) {
     Cand c0 = candidate(ops[i]);
@@ -666,6 +681,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
           if ((const void *)e.c2 == kt || (const void *)e.c2 == v) ok = false;
         }
         op.u0 = ok ? 1u : 0u;
+        op.u1 = (uint32_t)(stage_index(op.attn.pos_cell) + 1);
       }
       if (op.kind == ExecKind::ArgmaxSharded && exchange && op.comm) {
         exchange->comm = op.comm;
@@ -688,6 +704,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
           gt.binary == (uint32_t)BinaryKind::Mul && gt.d == u.c && gt.store_kind == 0 && gt.c != u.c &&
           gt.x != u.c) {
         GemvParams f = gt;
+        stage_gemv(f, ops[i + 1]);
         f.w2 = u.w;
         f.c2 = u.c;
         f.act = 0; f.binary = 0; f.d = nullptr;
@@ -696,7 +713,9 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
         bool has_link = false;
         const PeerLink link = link_for(f, nullptr, &has_link);
         plan.push_back([f, cx, link, has_link](Slot &slot, cudaStream_t st) {
-          launch_gemv_f16w_group(*cx, &f, 1, true, gemv_workspace(slot), st, has_link ? &link : nullptr);
+          GemvParams fs = f;
+          if (fs.pos_stage_idx >= 0) fs.pos_ptr = pos_stage_of(slot.counters) + fs.pos_stage_idx;
+          launch_gemv_f16w_group(*cx, &fs, 1, true, gemv_workspace(slot), st, has_link ? &link : nullptr);
         });
         if (first_op) first_op->push_back(i);
         prev_gemv.assign(1, f);
@@ -707,6 +726,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     // a row-parallel projection whose one-row output is all-reduced next and read by a GEMV after that
     if (const Comm *push_comm = fusable_push(i, c0)) {
       GemvParams f = c0.g;
+      stage_gemv(f, ops[i]);
       f.push_point1 = next_point + 1;
       f.push_slot = next_point & 1u;
       bool has_link = false;
@@ -720,7 +740,9 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
       if (flops) *flops += c0.flops;
       if (n_calls) *n_calls += 2;   // the projection and the all-reduce it carries
       plan.push_back([f, cx, link](Slot &slot, cudaStream_t st) {
-        launch_gemv_f16w_group(*cx, &f, 1, true, gemv_workspace(slot), st, &link);
+        GemvParams fs = f;
+        if (fs.pos_stage_idx >= 0) fs.pos_ptr = pos_stage_of(slot.counters) + fs.pos_stage_idx;
+        launch_gemv_f16w_group(*cx, &fs, 1, true, gemv_workspace(slot), st, &link);
       });
       if (first_op) first_op->push_back(i);
       prev_gemv.assign(1, f);
@@ -729,6 +751,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     }
     // group of independent GEMVs on the same x
     std::vector<GemvParams> segs{c0.g};
+    stage_gemv(segs[0], ops[i]);
     uint64_t fl = c0.flops;
     size_t j = i + 1;
     while (j < ops.size() && segs.size() < (size_t)GEMV_MAX_SEGS) {
@@ -743,6 +766,7 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
       }
       if (!independent) break;
       segs.push_back(cj.g);
+      stage_gemv(segs.back(), ops[j]);
       fl += cj.flops;
       ++j;
     }
@@ -751,7 +775,10 @@ std::vector<Launch> Executor::plan_exec_ops(const std::vector<ExecOp> &ops, uint
     bool has_link = false;
     const PeerLink link = link_for(segs[0], nullptr, &has_link);
     plan.push_back([segs, cx, link, has_link](Slot &slot, cudaStream_t st) {
-      launch_gemv_f16w_group(*cx, segs.data(), (int)segs.size(), true, gemv_workspace(slot), st, has_link ? &link : nullptr);
+      std::vector<GemvParams> ss = segs;
+      for (GemvParams &e : ss)
+        if (e.pos_stage_idx >= 0) e.pos_ptr = pos_stage_of(slot.counters) + e.pos_stage_idx;
+      launch_gemv_f16w_group(*cx, ss.data(), (int)ss.size(), true, gemv_workspace(slot), st, has_link ? &link : nullptr);
     });
     if (first_op) first_op->push_back(i);
     prev_gemv = segs;
@@ -774,7 +801,7 @@ RunStats Executor::run_exec_ops(const std::vector<ExecOp> &ops) {
   if (scratch_bytes) ensure_scratch(slot, scratch_bytes);
   exchange.advance();   // kernels with fused exchanges wait for the arrival counts of this submission
   return timed(slot, n_calls, flops, [&](cudaStream_t st) {
-    exchange.stage(st);
+    exchange.stage(st, pos_stage_of(slot.counters));
     for (const Launch &l : plan) l(slot, st);
   });
 }
@@ -798,7 +825,7 @@ RunStats Executor::run_exec_ops_timed(const std::vector<ExecOp> &ops, std::vecto
   RunStats st;
   try {
     st = timed(slot, n_calls, flops, [&](cudaStream_t s) {
-      exchange.stage(s);
+      exchange.stage(s, pos_stage_of(slot.counters));
       for (size_t i = 0; i < plan.size(); ++i) {
         TA_CUDA(cudaEventRecord(ev[i], s));
         plan[i](slot, s);
@@ -843,8 +870,8 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
   TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
   TA_CUDA(cudaEventCreate(&prep->ev_begin));
   TA_CUDA(cudaEventCreate(&prep->ev_end));
-  TA_CUDA(cudaMalloc((void **)&prep->counters, SLOT_COUNTERS * sizeof(uint32_t)));
-  TA_CUDA(cudaMemset(prep->counters, 0, SLOT_COUNTERS * sizeof(uint32_t)));
+  TA_CUDA(cudaMalloc((void **)&prep->counters, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
+  TA_CUDA(cudaMemset(prep->counters, 0, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
   alloc_status_word(&prep->status_host, &prep->status);
   Slot &real_slot = exec.checkout_slot();
   {
@@ -862,7 +889,7 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
     // attributes, tensor maps) consists of host calls, which a capture allows.
     TA_CUDA(cudaStreamBeginCapture(prep->stream, cudaStreamCaptureModeThreadLocal));
     try {
-      prep->exchange.stage(prep->stream);
+      prep->exchange.stage(prep->stream, pos_stage_of(slot.counters));
       for (const Launch &l : plan) l(slot, prep->stream);
     } catch (...) {
       cudaGraph_t dead = nullptr;

@@ -133,8 +133,8 @@ Executor::Executor(std::shared_ptr<Context> ctx, int selection, ExecutorConfig c
     TA_CUDA(cudaEventCreate(&s.ev_begin));
     TA_CUDA(cudaEventCreate(&s.ev_end));
     alloc_status_word(&s.status_host, &s.status);
-    TA_CUDA(cudaMalloc((void **)&s.counters, SLOT_COUNTERS * sizeof(uint32_t)));
-    TA_CUDA(cudaMemset(s.counters, 0, SLOT_COUNTERS * sizeof(uint32_t)));
+    TA_CUDA(cudaMalloc((void **)&s.counters, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
+    TA_CUDA(cudaMemset(s.counters, 0, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
   }
   tune_path_ = tune_store_path(ctx_->name);
   tuned_ = load_tuned(tune_path_);
@@ -521,6 +521,7 @@ bool Executor::gemv_params_for(const MatmulOp &op, const ResolvedMatmul &r, cons
   g.dst = op.store.dst ? op.store.dst->ptr() : nullptr;
   g.dst_f16 = op.store.dst && op.store.dst->dtype == DType::F16;
   g.pos_ptr = op.store.pos_cell ? op.store.pos_cell->device : nullptr;
+  g.pos_stage_idx = -1;
   // the largest position count for which every table row and destination element the store touches exists
   uint64_t limit = 0xffffffffull;
   if (g.store_kind != 0 && g.head_dim) {
@@ -913,8 +914,8 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
   size_t scratch_bytes = 0;
   for (size_t i = 0; i < ops.size(); ++i) scratch_bytes = std::max(scratch_bytes, exec.op_scratch_bytes(resolved[i], routes[i]));
   if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));
-  TA_CUDA(cudaMalloc((void **)&prep->counters, SLOT_COUNTERS * sizeof(uint32_t)));
-  TA_CUDA(cudaMemset(prep->counters, 0, SLOT_COUNTERS * sizeof(uint32_t)));
+  TA_CUDA(cudaMalloc((void **)&prep->counters, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
+  TA_CUDA(cudaMemset(prep->counters, 0, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
   alloc_status_word(&prep->status_host, &prep->status);
   // Captured directly, nothing runs at create time: encoding tensor maps and setting function
   // attributes are host calls, which a stream capture allows.
