@@ -129,14 +129,30 @@ flash_prefill_kernel(const FlashParams p) {
 // The f16-operand route of the reference (its coopmat2 flash kernels round Q*scale, K, V and
 // the softmax weights through f16 and accumulate in f32, tests/correctness/flash.rs:481-485):
 // mma.sync m16n8k16 for S = (Q*scale) K^T and O = P V, online softmax in registers.
-// CTA = 4 warps x 16 query rows; K/V tiles of 64 positions arrive through cp.async into a
-// double-buffered shared-memory pair (Kt rows [d][pos], V rows [pos][d], 16-byte padded) and
+// A warp group = 4 warps x 16 query rows; K/V tiles of 64 positions arrive through cp.async into the
+// group's own ring of shared-memory stages (Kt rows [d][pos], V rows [pos][d], 16-byte padded) and
 // reach the B fragments with ldmatrix.trans.  f16 caches with dh = 64 only.
+//
+// A CTA holds NG warp groups over the SAME 64 query rows; group g walks tiles g, g + NG, ... and the
+// groups' (max, sum, accumulator) triples meet through shared memory at the end, group 0 first, so the
+// result does not depend on timing.  The kernel is a chain of dependent steps per query block (the
+// causal block of the last 64 rows of a 512-token prompt walks 8 tiles while the first walks one), and
+// each step is latency, not throughput: two groups halve the longest chain and double the warps a
+// scheduler can pick from.
 constexpr int FM_BQ = 64, FM_BKV = 64, FM_DH = 64, FM_PAD = 8, FM_LD = FM_BKV + FM_PAD;
+constexpr int FM_TILE_HALVES = FM_DH * FM_LD;                         // one K or V tile
+constexpr int FM_STAGES_TOTAL = 4;                                    // stages of a CTA, split between its groups
+constexpr int FM_SMEM_BYTES = FM_STAGES_TOTAL * 2 * FM_TILE_HALVES * 2;   // 73 728 bytes of dynamic shared memory
+constexpr float FM_LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -155,12 +171,25 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
 }
 
-__global__ void __launch_bounds__(128)
+template <int NG>
+__global__ void __launch_bounds__(128 * NG, 2)
 flash_prefill_mma_kernel(const FlashParams p) {
-  __shared__ __align__(16) __half Ksh[2][FM_DH * FM_LD];    // [d][pos]
-  __shared__ __align__(16) __half Vsh[2][FM_BKV * FM_LD];   // [pos][d]
+  constexpr int STAGES = FM_STAGES_TOTAL / NG;               // of one group
+  static_assert(STAGES >= 2, "a group needs a stage to fill while it reads another");
+  static_assert(NG == 1 || NG == 2, "one named barrier per group: 1 and 2");
+  extern __shared__ __align__(16) __half fm_smem[];          // per group and stage: K tile [d][pos], then V tile [pos][d]
+  const uint32_t grp = threadIdx.x >> 7, tid = threadIdx.x & 127u, warp = tid >> 5, lane = tid & 31;
+  __half *const grp_smem = fm_smem + (size_t)grp * STAGES * 2 * FM_TILE_HALVES;
+  auto Ksh = [&](int b) { return grp_smem + (size_t)b * 2 * FM_TILE_HALVES; };
+  auto Vsh = [&](int b) { return grp_smem + (size_t)b * 2 * FM_TILE_HALVES + FM_TILE_HALVES; };
+  // the 128 threads of a group meet on a barrier of their own: the groups never wait for one another inside the loop
+  auto group_sync = [&]() {
+    if (NG == 1) __syncthreads();
+    else if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+  };
   TA_CHAIN_ENTER();
-  const uint32_t head = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t head = blockIdx.y;
   const uint32_t g = lane >> 2, t = lane & 3;
   const uint32_t q0 = blockIdx.x * FM_BQ;
   const uint32_t kv_head = head / p.group;
@@ -170,9 +199,13 @@ flash_prefill_mma_kernel(const FlashParams p) {
   const uint32_t row_a = q0 + warp * 16 + g, row_b = row_a + 8;   // this thread's two query rows
   const uint32_t valid_a = row_a < p.t_q ? (uint32_t)min((uint64_t)p.kv_len, (uint64_t)p.pos_base + row_a + 1u) : 0u;
   const uint32_t valid_b = row_b < p.t_q ? (uint32_t)min((uint64_t)p.kv_len, (uint64_t)p.pos_base + row_b + 1u) : 0u;
+  // a tile that ends at or before this bound is visible to every row of the warp: no masking there
+  const uint32_t warp_min_valid = __reduce_min_sync(0xffffffffu, min(valid_a, valid_b));
   const uint32_t last_row = min(q0 + FM_BQ, p.t_q) - 1u;
   const uint32_t valid_max = (uint32_t)min((uint64_t)p.kv_len, (uint64_t)p.pos_base + last_row + 1u);
   const uint32_t num_tiles = (valid_max + FM_BKV - 1) / FM_BKV;
+  // this group's tiles: grp, grp + NG, ...
+  const uint32_t my_tiles = num_tiles > grp ? (num_tiles - grp + NG - 1) / NG : 0u;
 
   auto load_tile = [&](uint32_t tile, int buf) {
     const uint32_t k0 = tile * FM_BKV;
@@ -180,8 +213,8 @@ flash_prefill_mma_kernel(const FlashParams p) {
     for (int it = 0; it < 4; ++it) {
       const uint32_t i = tid + it * 128, r = i >> 3, c8 = (i & 7u) * 8u;
       // K: row r = head dim d, 8 positions k0 + c8..; V: row r = position k0 + r, 8 dims c8..
-      __half *kd = &Ksh[buf][r * FM_LD + c8];
-      __half *vd = &Vsh[buf][r * FM_LD + c8];
+      __half *kd = Ksh(buf) + r * FM_LD + c8;
+      __half *vd = Vsh(buf) + r * FM_LD + c8;
       if (k0 + c8 + 8 <= p.t_max) cp_async16(kd, kt + (size_t)r * p.t_max + k0 + c8);
       else *reinterpret_cast<uint4 *>(kd) = make_uint4(0u, 0u, 0u, 0u);
       // rows at or beyond kv_len get probability 0: they must be zeros, not whatever the cache holds
@@ -191,7 +224,13 @@ flash_prefill_mma_kernel(const FlashParams p) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  if (num_tiles > 0) load_tile(0, 0);
+  // look-ahead of STAGES - 1 tiles; a group is committed per tile slot whether or not a tile is left,
+  // so that "all but the newest STAGES - 1 groups" always means "this tile has landed"
+#pragma unroll
+  for (uint32_t i = 0; i < (uint32_t)STAGES - 1; ++i) {
+    if (i < my_tiles) load_tile(grp + i * NG, (int)i);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
 
   // Q * scale as f16 A fragments: 4 steps of 16 head dims
   uint32_t qf[4][4];
@@ -226,16 +265,14 @@ flash_prefill_mma_kernel(const FlashParams p) {
   // ldmatrix row addressing: lane -> matrix lane / 8, row lane % 8
   const uint32_t lm = lane >> 3, lr = lane & 7;
 
-  for (uint32_t tile = 0; tile < num_tiles; ++tile) {
-    const int buf = (int)(tile & 1u);
-    if (tile + 1 < num_tiles) {
-      load_tile(tile + 1, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
-    const uint32_t k0 = tile * FM_BKV;
+  for (uint32_t step = 0; step < my_tiles; ++step) {
+    const int buf = (int)(step % STAGES);
+    // the stage refilled here held the tile of the step before, whose reads ended at the barrier that closed it
+    if (step + STAGES - 1 < my_tiles) load_tile(grp + (step + STAGES - 1) * NG, (int)((step + STAGES - 1) % STAGES));
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
+    group_sync();
+    const uint32_t k0 = (grp + step * NG) * FM_BKV;
 
     // ---- S = (Q*scale) K^T : 8 blocks of 8 positions
     float sc[8][4];
@@ -249,20 +286,26 @@ flash_prefill_mma_kernel(const FlashParams p) {
       for (int jp = 0; jp < 4; ++jp) {   // position blocks 2jp, 2jp+1
         uint32_t b[4];
         // matrices: (d 16s..+7, blk 2jp), (d 16s+8.., blk 2jp), (d 16s.., blk 2jp+1), (d 16s+8.., blk 2jp+1)
-        ldmatrix_x4_trans(b, &Ksh[buf][(16 * s + (lm & 1u) * 8 + lr) * FM_LD + (2 * jp + (lm >> 1)) * 8]);
+        ldmatrix_x4_trans(b, Ksh(buf) + (16 * s + (lm & 1u) * 8 + lr) * FM_LD + (2 * jp + (lm >> 1)) * 8);
         mma_f16_16816(sc[2 * jp], qf[s], b[0], b[1]);
         mma_f16_16816(sc[2 * jp + 1], qf[s], b[2], b[3]);
       }
     }
-    // ---- mask, running max, probabilities
+    // ---- mask (only a tile that reaches past some row's visible range), running max, probabilities
+    const bool masked = k0 + FM_BKV > warp_min_valid;   // the same for the whole warp
+    if (masked) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t pos = k0 + 8 * j + 2 * t;
+        sc[j][0] = pos < valid_a ? sc[j][0] : NEG_BIG;
+        sc[j][1] = pos + 1 < valid_a ? sc[j][1] : NEG_BIG;
+        sc[j][2] = pos < valid_b ? sc[j][2] : NEG_BIG;
+        sc[j][3] = pos + 1 < valid_b ? sc[j][3] : NEG_BIG;
+      }
+    }
     float mx_a = NEG_BIG, mx_b = NEG_BIG;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const uint32_t pos = k0 + 8 * j + 2 * t;
-      sc[j][0] = pos < valid_a ? sc[j][0] : NEG_BIG;
-      sc[j][1] = pos + 1 < valid_a ? sc[j][1] : NEG_BIG;
-      sc[j][2] = pos < valid_b ? sc[j][2] : NEG_BIG;
-      sc[j][3] = pos + 1 < valid_b ? sc[j][3] : NEG_BIG;
       mx_a = fmaxf(mx_a, fmaxf(sc[j][0], sc[j][1]));
       mx_b = fmaxf(mx_b, fmaxf(sc[j][2], sc[j][3]));
     }
@@ -271,18 +314,27 @@ flash_prefill_mma_kernel(const FlashParams p) {
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
     const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-    const float corr_a = expf(m_a - mn_a), corr_b = expf(m_b - mn_b);   // 1 while nothing is visible yet
+    // exp(x - m) as 2^(x log2e - m log2e): one fused multiply-add and one ex2 per weight (the weights
+    // are rounded to f16 next, far coarser than the approximation); 1 while nothing is visible yet
+    const float corr_a = ex2_approx((m_a - mn_a) * FM_LOG2E), corr_b = ex2_approx((m_b - mn_b) * FM_LOG2E);
     m_a = mn_a;
     m_b = mn_b;
     l_a *= corr_a;
     l_b *= corr_b;
+    const float nml_a = -mn_a * FM_LOG2E, nml_b = -mn_b * FM_LOG2E;
     uint32_t pf[4][4];   // P as A fragments: 4 steps of 16 positions
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float p0 = sc[j][0] > -3.0e38f ? expf(sc[j][0] - mn_a) : 0.0f;
-      const float p1 = sc[j][1] > -3.0e38f ? expf(sc[j][1] - mn_a) : 0.0f;
-      const float p2 = sc[j][2] > -3.0e38f ? expf(sc[j][2] - mn_b) : 0.0f;
-      const float p3 = sc[j][3] > -3.0e38f ? expf(sc[j][3] - mn_b) : 0.0f;
+      float p0 = ex2_approx(fmaf(sc[j][0], FM_LOG2E, nml_a));
+      float p1 = ex2_approx(fmaf(sc[j][1], FM_LOG2E, nml_a));
+      float p2 = ex2_approx(fmaf(sc[j][2], FM_LOG2E, nml_b));
+      float p3 = ex2_approx(fmaf(sc[j][3], FM_LOG2E, nml_b));
+      if (masked) {   // a masked score against a row maximum that is itself "nothing visible" is not a number
+        p0 = sc[j][0] > -3.0e38f ? p0 : 0.0f;
+        p1 = sc[j][1] > -3.0e38f ? p1 : 0.0f;
+        p2 = sc[j][2] > -3.0e38f ? p2 : 0.0f;
+        p3 = sc[j][3] > -3.0e38f ? p3 : 0.0f;
+      }
       l_a += p0 + p1;
       l_b += p2 + p3;
       pf[j >> 1][(j & 1) * 2] = pack_h2(p0, p1);
@@ -297,18 +349,60 @@ flash_prefill_mma_kernel(const FlashParams p) {
       for (int jp = 0; jp < 4; ++jp) {   // head-dim blocks 2jp, 2jp+1
         uint32_t b[4];
         // matrices: (pos 16ks..+7, dblk 2jp), (pos 16ks+8.., dblk 2jp), (pos 16ks.., dblk 2jp+1), (pos 16ks+8.., 2jp+1)
-        ldmatrix_x4_trans(b, &Vsh[buf][(16 * ks + (lm & 1u) * 8 + lr) * FM_LD + (2 * jp + (lm >> 1)) * 8]);
+        ldmatrix_x4_trans(b, Vsh(buf) + (16 * ks + (lm & 1u) * 8 + lr) * FM_LD + (2 * jp + (lm >> 1)) * 8);
         mma_f16_16816(o[2 * jp], pf[ks], b[0], b[1]);
         mma_f16_16816(o[2 * jp + 1], pf[ks], b[2], b[3]);
       }
     }
-    __syncthreads();   // the buffer is refilled by the load issued in the next iteration
+    group_sync();   // the buffer is refilled by the load issued in the next step
   }
 
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+  if (NG > 1) {
+    // groups 1.. hand (o, m, l) to group 0 through the stage memory, [value][thread] so that a warp's
+    // accesses are consecutive; group 0 folds them in group order
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();   // every group is done with its stages
+    float *xch = reinterpret_cast<float *>(fm_smem);
+    constexpr int XW = 36;   // 32 accumulators, 2 maxima, 2 sums
+    if (grp > 0) {
+      float *mine = xch + (size_t)(grp - 1) * XW * 128 + tid;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mine[(j * 4 + i) * 128] = o[j][i];
+      mine[32 * 128] = m_a;
+      mine[33 * 128] = m_b;
+      mine[34 * 128] = l_a;
+      mine[35 * 128] = l_b;
+    }
+    __syncthreads();
+    if (grp > 0) return;
+#pragma unroll
+    for (int og = 1; og < NG; ++og) {
+      const float *theirs = xch + (size_t)(og - 1) * XW * 128 + tid;
+      const float tm_a = theirs[32 * 128], tm_b = theirs[33 * 128];
+      const float mn_a = fmaxf(m_a, tm_a), mn_b = fmaxf(m_b, tm_b);
+      const float ca = ex2_approx((m_a - mn_a) * FM_LOG2E), cb = ex2_approx((m_b - mn_b) * FM_LOG2E);
+      const float ta = ex2_approx((tm_a - mn_a) * FM_LOG2E), tb = ex2_approx((tm_b - mn_b) * FM_LOG2E);
+      l_a = l_a * ca + theirs[34 * 128] * ta;
+      l_b = l_b * cb + theirs[35 * 128] * tb;
+      m_a = mn_a;
+      m_b = mn_b;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j][0] = o[j][0] * ca + theirs[(j * 4 + 0) * 128] * ta;
+        o[j][1] = o[j][1] * ca + theirs[(j * 4 + 1) * 128] * ta;
+        o[j][2] = o[j][2] * cb + theirs[(j * 4 + 2) * 128] * tb;
+        o[j][3] = o[j][3] * cb + theirs[(j * 4 + 3) * 128] * tb;
+      }
+    }
+  }
+
   const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
   auto store_row = [&](uint32_t row, float inv, int lo) {
     const size_t off = (size_t)head * p.o_head_stride + (size_t)row * p.o_row_stride;
@@ -551,7 +645,18 @@ bool flash_prefill_mma_eligible(const FlashParams &p) {
 void launch_flash_prefill(const FlashParams &p, cudaStream_t stream) {
   dim3 grid((p.t_q + 63) / 64, p.heads);
   if (flash_prefill_mma_eligible(p)) {
-    launch_chained(flash_prefill_mma_kernel, grid, dim3(128), 0, stream, p);
+    // two warp groups per query block unless the experiment switch asks for one
+    const bool two = tunables().flash_groups != 1;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+      TA_CUDA(cudaFuncSetAttribute(flash_prefill_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FM_SMEM_BYTES));
+      TA_CUDA(cudaFuncSetAttribute(flash_prefill_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FM_SMEM_BYTES));
+      attr_set[dev & 63] = true;
+    }
+    if (two) launch_chained(flash_prefill_mma_kernel<2>, grid, dim3(256), (size_t)FM_SMEM_BYTES, stream, p);
+    else launch_chained(flash_prefill_mma_kernel<1>, grid, dim3(128), (size_t)FM_SMEM_BYTES, stream, p);
     launched();
     return;
   }

@@ -68,6 +68,7 @@ struct Tunables {
   bool f16w_tma_store = true;     // f16w tensor-core GEMM: C leaves through TMA stores (0: the kernel stores it itself)
   bool f16w_dual = true;          // f16w tensor-core GEMM: up and gate of a SwiGLU pair as one dual-matrix launch
   uint32_t attn_chunks = 0;       // decode attention with a position cell: chunk grid (0 = one 64-position tile per chunk, 8..32)
+  uint32_t flash_groups = 2;     // tensor-core prefill attention: warp groups per query block that split its K/V tiles (1 or 2)
   bool pos_stage = true;          // position cells read by graph launches are staged to device memory per submission
 };
 const Tunables &tunables();
