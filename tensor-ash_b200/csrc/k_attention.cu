@@ -425,23 +425,33 @@ flash_prefill_mma_kernel(const FlashParams p) {
 
 // ------------------------------------------------------------------ decode
 // One CTA per (chunk, kv head), 128 threads = 8 query rows x 16 lanes.  A chunk
-// is walked in tiles of 64 positions: the K tile [d][j] and the V tile [j][d]
-// are staged in shared memory with 16-byte loads issued up front (one round trip
+// is walked in tiles of 64 positions whose loads are issued up front (one round trip
 // of latency per tile), thread (r, c) computes the four scores j = 4c..4c+3 of
 // row r, the tile's max / sum meet through xor-shuffles inside the 16-lane
 // group, probabilities go through shared memory, and thread (r, c) accumulates
 // the four output dims d = 4c..4c+3.  Partials [kv_heads, chunks, group, dh+2]
 // (acc, m, l) go to caller scratch.  The last CTA of a kv head to finish (a
-// ticket counter, reset for the next launch) rescales every chunk to the global
-// max while summing in chunk order, so the result does not depend on which CTA that is.
+// ticket counter, reset for the next launch) weighs every chunk by exp(m_i - max m)
+// and sums in chunk order, so the result does not depend on which CTA that is.
 constexpr int DEC_DH = 64, DEC_LANES = 16, DEC_THREADS = 128, DEC_BP = 64;
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_kernel(const AttnDecodeParams p) {
-  __shared__ __align__(16) float Ksh[DEC_DH * DEC_BP];   // [d][j]
-  __shared__ __align__(16) float Vsh[DEC_BP * DEC_DH];   // [j][d]
-  __shared__ __align__(16) float Qsh[8 * DEC_DH];
-  __shared__ float Psh[8 * DEC_BP];
+  // f16 caches with 16-byte rows (the decode graph's case): a thread keeps ITS K values in registers
+  // (row r, positions 4 lane..4 lane + 3, all 64 head dims: 64 eight-byte loads, issued before the
+  // dependency wait), V rows sit in shared memory as f16, q as [d][row] and the weights as
+  // [position][row], so that a warp's shared-memory reads are one or two wavefronts.  Any other
+  // cache goes through f32 tiles in shared memory.  Both routes add in the same order.
+  __shared__ __align__(16) float Ksh[DEC_DH * DEC_BP];   // [d][j], f32 route only
+  __shared__ __align__(16) float Vsh[DEC_BP * DEC_DH];   // [j][d] f32, or (f16 route) [j][64 halves] in its first half
+  __shared__ __align__(16) float Qsh[DEC_DH * 8];        // [d][row]
+  __shared__ __align__(16) float Psh[DEC_BP * 8];        // [j][row]
   __shared__ uint32_t last_flag;
   const uint32_t chunk = blockIdx.x, kv_head = blockIdx.y, tid = threadIdx.x;
   const uint32_t row = tid / DEC_LANES, lane = tid % DEC_LANES;
@@ -460,17 +470,18 @@ attn_decode_kernel(const AttnDecodeParams p) {
   const bool vec16 = p.kv_f16 && (p.t_max % 8u) == 0 &&
                      (reinterpret_cast<uintptr_t>(p.kt) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.v) & 15u) == 0;
 
-  // K: 64 d-rows x 8 groups of 8 positions; V: 64 position rows x 8 groups of 8 dims
-  uint4 kraw[4], vraw[4];
+  uint2 kreg[DEC_DH];   // f16 route: K[d][t0 + 4 lane .. + 3]
+  uint4 vraw[4];        // f16 route: 64 position rows x 8 groups of 8 dims, four groups per thread
   auto load_tile = [&](uint32_t t0, uint32_t n) {
+    const __half *kcol = static_cast<const __half *>(p.kt) + kt_base + t0 + lane * 4u;
+    const bool k_ok = lane * 4u < n;   // a group may run past kv_len inside t_max (a multiple of 8): masked at the scores
+#pragma unroll
+    for (int d = 0; d < DEC_DH; ++d)
+      kreg[d] = k_ok ? *reinterpret_cast<const uint2 *>(kcol + (size_t)d * p.t_max) : make_uint2(0u, 0u);
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
-      const uint32_t i = tid + it * DEC_THREADS, d = i >> 3, jg = (i & 7u) * 8u;
-      kraw[it] = make_uint4(0u, 0u, 0u, 0u);
+      const uint32_t i = tid + it * DEC_THREADS, j = i >> 3, dg = (i & 7u) * 8u;
       vraw[it] = make_uint4(0u, 0u, 0u, 0u);
-      if (jg < n)   // a group may run past kv_len inside t_max: masked at the scores
-        kraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.kt) + kt_base + (size_t)d * p.t_max + t0 + jg);
-      const uint32_t j = i >> 3, dg = (i & 7u) * 8u;
       if (j < n)
         vraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)(t0 + j) * DEC_DH + dg);
     }
@@ -479,27 +490,54 @@ attn_decode_kernel(const AttnDecodeParams p) {
   // sets prefetch_kv when that holds): every other position is read before the wait.
   const uint32_t n_first = min((uint32_t)DEC_BP, p1 - p0);
   const bool newest_here = kv_len > 0 && kv_len - 1 >= p0 && kv_len - 1 < p0 + n_first;
-  const bool early = vec16 && n_first > 0 && p.prefetch_kv && !newest_here;
-  if (early) load_tile(p0, n_first);
+  const bool early = vec16 && n_first > 0 && p.prefetch_kv;
+  if (early) load_tile(p0, n_first);   // in the chunk of the newest position that one column / row is stale: re-read below
+  // the launch count of this kv head was last written by the attention launch before this one on
+  // the slot, which ended launches ago
+  uint32_t pair_flag = 0;
+  if (p.pairs) {
+    pair_flag = __ldcg(p.pair_seq + kv_head) + 1u;
+    if (pair_flag == 0u) pair_flag = 1u;   // zero is what untouched pairs hold
+  }
 
   if (p.pdl) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
-  // q: group x 64 floats, one float4 per thread (requested before the late tile loads)
+  // q: group x 64 floats, one float4 per thread (requested before the late tile loads), staged as [d][row]
   float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool q_vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
   if (q_vec) {
     if (tid * 4 < p.group * DEC_DH) qv = *reinterpret_cast<const float4 *>(p.q + (size_t)kv_head * p.group * DEC_DH + tid * 4);
   }
   if (vec16 && n_first > 0 && !early) load_tile(p0, n_first);
+  if (early && newest_here) {
+    // the appended position, now that its writer has finished: the K column group that holds it
+    // (the threads of one lane index) and its V row, from L2 instead of a whole tile from memory
+    const uint32_t jn = kv_len - 1u - p0;
+    if (lane == (jn >> 2)) {
+      const __half *kcol = static_cast<const __half *>(p.kt) + kt_base + p0 + lane * 4u;
+#pragma unroll
+      for (int d = 0; d < DEC_DH; ++d) kreg[d] = __ldcg(reinterpret_cast<const uint2 *>(kcol + (size_t)d * p.t_max));   // past L1, which may hold the line as it was
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const uint32_t i = tid + it * DEC_THREADS, j = i >> 3, dg = (i & 7u) * 8u;
+      if (j == jn) vraw[it] = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)(p0 + j) * DEC_DH + dg));
+    }
+  }
   if (q_vec) {
-    if (tid * 4 < p.group * DEC_DH) *reinterpret_cast<float4 *>(&Qsh[tid * 4]) = qv;
+    if (tid * 4 < p.group * DEC_DH) {
+      const uint32_t qr = (tid * 4) / DEC_DH, qd = (tid * 4) % DEC_DH;
+      Qsh[(qd + 0) * 8 + qr] = qv.x; Qsh[(qd + 1) * 8 + qr] = qv.y;
+      Qsh[(qd + 2) * 8 + qr] = qv.z; Qsh[(qd + 3) * 8 + qr] = qv.w;
+    }
   } else {
-    for (uint32_t i = tid; i < p.group * DEC_DH; i += DEC_THREADS) Qsh[i] = p.q[(size_t)kv_head * p.group * DEC_DH + i];
+    for (uint32_t i = tid; i < p.group * DEC_DH; i += DEC_THREADS) Qsh[(i % DEC_DH) * 8 + i / DEC_DH] = p.q[(size_t)kv_head * p.group * DEC_DH + i];
   }
 
   float m_run = NEG_BIG, l_run = 0.0f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  __half *Vh = reinterpret_cast<__half *>(Vsh);
 
   for (uint32_t t0 = p0; t0 < p1; t0 += DEC_BP) {
     const uint32_t n = min((uint32_t)DEC_BP, p1 - t0);
@@ -507,17 +545,8 @@ attn_decode_kernel(const AttnDecodeParams p) {
       if (t0 != p0) load_tile(t0, n);
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
-        const uint32_t i = tid + it * DEC_THREADS, r8 = i >> 3, g8 = (i & 7u) * 8u;
-        const __half2 *hk = reinterpret_cast<const __half2 *>(&kraw[it]);
-        const __half2 *hv = reinterpret_cast<const __half2 *>(&vraw[it]);
-        float4 *kd = reinterpret_cast<float4 *>(&Ksh[r8 * DEC_BP + g8]);
-        float4 *vd = reinterpret_cast<float4 *>(&Vsh[r8 * DEC_DH + g8]);
-        const float2 k0 = __half22float2(hk[0]), k1 = __half22float2(hk[1]), k2 = __half22float2(hk[2]), k3 = __half22float2(hk[3]);
-        const float2 v0 = __half22float2(hv[0]), v1 = __half22float2(hv[1]), v2 = __half22float2(hv[2]), v3 = __half22float2(hv[3]);
-        kd[0] = make_float4(k0.x, k0.y, k1.x, k1.y);
-        kd[1] = make_float4(k2.x, k2.y, k3.x, k3.y);
-        vd[0] = make_float4(v0.x, v0.y, v1.x, v1.y);
-        vd[1] = make_float4(v2.x, v2.y, v3.x, v3.y);
+        const uint32_t i = tid + it * DEC_THREADS;   // row i / 8, group i % 8: 16 bytes at halves [8 i, 8 i + 8)
+        *reinterpret_cast<uint4 *>(Vh + (size_t)i * 8) = vraw[it];
       }
     } else {
       for (uint32_t i = tid; i < DEC_DH * DEC_BP; i += DEC_THREADS) {
@@ -533,13 +562,36 @@ attn_decode_kernel(const AttnDecodeParams p) {
 
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     if (live) {
-      const float *qr = &Qsh[row * DEC_DH];
+      if (vec16) {
+        // eight q values are requested while the eight before them are used: with K filling the
+        // register file the compiler does not move these loads ahead on its own
+        float qn[8], qc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) qn[u] = Qsh[u * 8 + row];
+#pragma unroll
+        for (int d0 = 0; d0 < DEC_DH; d0 += 8) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) qc[u] = qn[u];
+          if (d0 + 8 < DEC_DH) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) qn[u] = Qsh[(d0 + 8 + u) * 8 + row];
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const float2 k01 = __half22float2(*reinterpret_cast<const __half2 *>(&kreg[d0 + u].x));
+            const float2 k23 = __half22float2(*reinterpret_cast<const __half2 *>(&kreg[d0 + u].y));
+            s[0] = fmaf(qc[u], k01.x, s[0]); s[1] = fmaf(qc[u], k01.y, s[1]);
+            s[2] = fmaf(qc[u], k23.x, s[2]); s[3] = fmaf(qc[u], k23.y, s[3]);
+          }
+        }
+      } else {
 #pragma unroll 16
-      for (int d = 0; d < DEC_DH; ++d) {
-        const float qd = qr[d];
-        const float4 kk = *reinterpret_cast<const float4 *>(&Ksh[d * DEC_BP + lane * 4]);
-        s[0] = fmaf(qd, kk.x, s[0]); s[1] = fmaf(qd, kk.y, s[1]);
-        s[2] = fmaf(qd, kk.z, s[2]); s[3] = fmaf(qd, kk.w, s[3]);
+        for (int d = 0; d < DEC_DH; ++d) {
+          const float qd = Qsh[d * 8 + row];
+          const float4 kk = *reinterpret_cast<const float4 *>(&Ksh[d * DEC_BP + lane * 4]);
+          s[0] = fmaf(qd, kk.x, s[0]); s[1] = fmaf(qd, kk.y, s[1]);
+          s[2] = fmaf(qd, kk.z, s[2]); s[3] = fmaf(qd, kk.w, s[3]);
+        }
       }
     }
     float tmax = NEG_BIG;
@@ -557,7 +609,7 @@ attn_decode_kernel(const AttnDecodeParams p) {
     for (int q = 0; q < 4; ++q) {
       const float pe = (lane * 4 + q) < n ? expf(s[q] - m_new) : 0.0f;
       lsum += pe;
-      Psh[row * DEC_BP + lane * 4 + q] = pe;
+      Psh[(lane * 4 + q) * 8 + row] = pe;
     }
 #pragma unroll
     for (int off = DEC_LANES / 2; off >= 1; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
@@ -567,18 +619,142 @@ attn_decode_kernel(const AttnDecodeParams p) {
     if (live) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) acc[q] *= corr;
-      const float *pr = &Psh[row * DEC_BP];
-      for (uint32_t j = 0; j < n; ++j) {
-        const float pj = pr[j];
-        const float4 vv = *reinterpret_cast<const float4 *>(&Vsh[j * DEC_DH + lane * 4]);
-        acc[0] = fmaf(pj, vv.x, acc[0]); acc[1] = fmaf(pj, vv.y, acc[1]);
-        acc[2] = fmaf(pj, vv.z, acc[2]); acc[3] = fmaf(pj, vv.w, acc[3]);
+      // whole groups of eight positions with their loads issued together: rows at or past n hold
+      // weight 0 and (staged from zeroed registers) value 0, so they add nothing
+      for (uint32_t j0 = 0; j0 < n; j0 += 8) {
+        float pj[8];
+        float4 vv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          pj[u] = Psh[(j0 + u) * 8 + row];
+          if (vec16) {
+            const uint2 h = *reinterpret_cast<const uint2 *>(Vh + (size_t)(j0 + u) * DEC_DH + lane * 4);
+            const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
+            const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&h.y));
+            vv[u] = make_float4(v01.x, v01.y, v23.x, v23.y);
+          } else {
+            vv[u] = *reinterpret_cast<const float4 *>(&Vsh[(j0 + u) * DEC_DH + lane * 4]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc[0] = fmaf(pj[u], vv[u].x, acc[0]); acc[1] = fmaf(pj[u], vv[u].y, acc[1]);
+          acc[2] = fmaf(pj[u], vv[u].z, acc[2]); acc[3] = fmaf(pj[u], vv[u].w, acc[3]);
+        }
       }
     }
     __syncthreads();
   }
 
   const uint32_t stride = DEC_DH + 2;
+  if (p.pairs) {
+    // ---- flagged hand-over through the slot's pair region.  Every partial value travels as an
+    // 8-byte (value, flag) pair, two pairs per 16-byte store, flag = this kv head's launch count + 1:
+    // a reader knows a value is this launch's by looking at it, so no fence and no ticket lie
+    // between a chunk's stores and the combine.  The CTA of chunk 0 combines: it polls (bounded)
+    // the pairs themselves, lane u of a row fetching the (max, sum) of chunk u, every lane the four
+    // sums of its head dims for sixteen chunks at once, adds with the arithmetic of the ticket route
+    // below and advances the count.  Every CTA of the grid is resident or will be (none waits for
+    // the combiner), so the poll cannot starve its producers.
+    constexpr uint32_t ROW_V4 = (DEC_DH + 2) / 2;   // 33 sixteen-byte pieces per row
+    uint4 *pair_rows = reinterpret_cast<uint4 *>(p.pairs) + (size_t)kv_head * p.num_chunks * 8u * ROW_V4;
+    auto st_pair = [&](uint4 *dst, float a, float b) {
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(pair_flag),
+                   "r"(__float_as_uint(b)), "r"(pair_flag) : "memory");
+    };
+    auto ld_pair = [](const uint4 *src) {
+      uint4 v;
+      asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+      return v;
+    };
+    if (live && p0 < p1) {
+      uint4 *dst = pair_rows + ((size_t)chunk * 8u + row) * ROW_V4;
+      st_pair(dst + lane * 2, acc[0], acc[1]);
+      st_pair(dst + lane * 2 + 1, acc[2], acc[3]);
+      if (lane == 0) st_pair(dst + DEC_DH / 2, m_run, l_run);
+    }
+    if (chunk != 0 || !live) return;
+    const uint32_t live_chunks = chunk_size ? min(p.num_chunks, (kv_len + chunk_size - 1) / chunk_size) : 0u;
+    const uint32_t half_mask = 0xffffu << (16u * (row & 1u));   // the sixteen lanes of this row
+    const uint4 *rbase = pair_rows + (size_t)row * ROW_V4;
+    constexpr size_t CSTEP = 8u * ROW_V4;
+    const uint64_t t_begin = global_timer_ns();
+    bool gave_up = false;
+    // a pair is there when both of its flags are set.  A poll re-requests EVERY pair that is not
+    // there yet before it looks at any (one L2 round trip per poll, whatever the number missing),
+    // bounded at about a second.
+    auto there = [&](const uint4 &v) { return v.y == pair_flag && v.w == pair_flag; };
+    float num[4] = {0.f, 0.f, 0.f, 0.f}, l_total = 0.0f;
+    constexpr int MAXB = ATTN_DECODE_MAX_CHUNKS / 16;
+    uint4 ml[MAXB], pa[16], pb[16];   // this lane's (max, sum) pair per batch of sixteen chunks; a batch's sums
+#pragma unroll
+    for (int b = 0; b < MAXB; ++b) ml[b] = make_uint4(__float_as_uint(NEG_BIG), 0u, 0u, 0u);
+    auto poll_batch = [&](uint32_t c0, bool with_ml) {
+#pragma unroll
+      for (int u = 0; u < 16; ++u) pa[u] = pb[u] = make_uint4(0u, 0u, 0u, 0u);
+      uint32_t spins = 0;
+      for (;;) {
+        if (with_ml) {
+#pragma unroll
+          for (int b = 0; b < MAXB; ++b) {
+            const uint32_t c = 16u * b + lane;
+            if (c < live_chunks && !there(ml[b])) ml[b] = ld_pair(rbase + c * CSTEP + DEC_DH / 2);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const uint32_t c = c0 + u;
+          if (c < live_chunks) {
+            if (!there(pa[u])) pa[u] = ld_pair(rbase + c * CSTEP + lane * 2);
+            if (!there(pb[u])) pb[u] = ld_pair(rbase + c * CSTEP + lane * 2 + 1);
+          }
+        }
+        bool all = true;
+        if (with_ml) {
+#pragma unroll
+          for (int b = 0; b < MAXB; ++b) all = all && (16u * b + lane >= live_chunks || there(ml[b]));
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) all = all && (c0 + u >= live_chunks || (there(pa[u]) && there(pb[u])));
+        if (all) break;
+        if ((++spins & 63u) == 0 && global_timer_ns() - t_begin > 1000000000ull) {
+          gave_up = true;
+          break;
+        }
+      }
+    };
+    poll_batch(0, true);
+    float m_star = NEG_BIG, w_l[MAXB], l_l[MAXB];
+#pragma unroll
+    for (int b = 0; b < MAXB; ++b) m_star = fmaxf(m_star, 16u * b + lane < live_chunks ? __uint_as_float(ml[b].x) : NEG_BIG);
+#pragma unroll
+    for (int off = DEC_LANES / 2; off >= 1; off >>= 1) m_star = fmaxf(m_star, __shfl_xor_sync(half_mask, m_star, off, 16));
+#pragma unroll
+    for (int b = 0; b < MAXB; ++b) {
+      w_l[b] = 16u * b + lane < live_chunks ? expf(__uint_as_float(ml[b].x) - m_star) : 0.0f;
+      l_l[b] = __uint_as_float(ml[b].z);
+    }
+#pragma unroll
+    for (int b = 0; b < MAXB; ++b) {
+      if (16u * b < live_chunks) {   // the same for the sixteen lanes of the row
+        if (b > 0) poll_batch(16u * b, false);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          // past the live count: weight 0 (from the lane that holds no chunk) times the zeros of an unfetched pair
+          const float w = __shfl_sync(half_mask, w_l[b], u, 16), lc = __shfl_sync(half_mask, l_l[b], u, 16);
+          l_total = fmaf(lc, w, l_total);
+          num[0] = fmaf(__uint_as_float(pa[u].x), w, num[0]); num[1] = fmaf(__uint_as_float(pa[u].z), w, num[1]);
+          num[2] = fmaf(__uint_as_float(pb[u].x), w, num[2]); num[3] = fmaf(__uint_as_float(pb[u].z), w, num[3]);
+        }
+      }
+    }
+    if (gave_up && p.status) atomicOr(p.status, 1u);
+    const float inv = l_total > 0.0f ? 1.0f / l_total : 0.0f;
+    float *o = p.out + ((size_t)kv_head * p.group + row) * DEC_DH + lane * 4;
+    *reinterpret_cast<float4 *>(o) = make_float4(num[0] * inv, num[1] * inv, num[2] * inv, num[3] * inv);
+    if (tid == 0) p.pair_seq[kv_head] = pair_flag;   // the next launch on this slot tags with the next count
+    return;
+  }
   if (live) {
     float *dst = p.scratch + (((size_t)kv_head * p.num_chunks + chunk) * p.group + row) * stride;
     dst[lane * 4] = acc[0]; dst[lane * 4 + 1] = acc[1]; dst[lane * 4 + 2] = acc[2]; dst[lane * 4 + 3] = acc[3];
@@ -602,22 +778,43 @@ attn_decode_kernel(const AttnDecodeParams p) {
   const size_t chunk_step = (size_t)p.group * stride;
   // chunks past the valid length hold nothing; partials come from other CTAs: L2 loads
   const uint32_t live_chunks = chunk_size ? min(p.num_chunks, (kv_len + chunk_size - 1) / chunk_size) : 0u;
-  // one pass in chunk order with a running maximum (the rescale of an online softmax):
-  // no load depends on a computed value, so sixteen chunks' partials are in flight at once
+  // the reference's combine: the maximum over the chunks, one weight exp(m_i - m*) per chunk, sums
+  // in chunk order.  Sixteen chunks' partials are requested together under a fixed trip count (a
+  // loop bounded by the live count keeps each load behind the arithmetic of the chunk before: one
+  // L2 round trip per chunk); up to sixteen live chunks that is the only round trip.
   float m_star = NEG_BIG, l_total = 0.0f, num[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 16
-  for (uint32_t i = 0; i < live_chunks; ++i) {
-    const float m_i = __ldcg(&base[i * chunk_step + DEC_DH]);
-    const float l_i = __ldcg(&base[i * chunk_step + DEC_DH + 1]);
-    // rows are dh + 2 floats long: 8-byte aligned, not 16
-    const float2 a = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4]));
-    const float2 b = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4 + 2]));
-    const float m_new = fmaxf(m_star, m_i);
-    const float c_old = expf(m_star - m_new), w = expf(m_i - m_new);
-    l_total = fmaf(l_i, w, l_total * c_old);
-    num[0] = fmaf(a.x, w, num[0] * c_old); num[1] = fmaf(a.y, w, num[1] * c_old);
-    num[2] = fmaf(b.x, w, num[2] * c_old); num[3] = fmaf(b.y, w, num[3] * c_old);
-    m_star = m_new;
+  float m_c[16], l_c[16];
+  float2 a_c[16], b_c[16];
+  auto load_batch = [&](uint32_t c0) {
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const uint32_t i = min(c0 + u, live_chunks - 1);   // past the end: the last chunk again, weight 0 below
+      m_c[u] = __ldcg(&base[i * chunk_step + DEC_DH]);
+      l_c[u] = __ldcg(&base[i * chunk_step + DEC_DH + 1]);
+      // rows are dh + 2 floats long: 8-byte aligned, not 16
+      a_c[u] = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4]));
+      b_c[u] = __ldcg(reinterpret_cast<const float2 *>(&base[i * chunk_step + lane * 4 + 2]));
+    }
+  };
+  auto add_batch = [&](uint32_t c0) {
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const float w = c0 + u < live_chunks ? expf(m_c[u] - m_star) : 0.0f;
+      l_total = fmaf(l_c[u], w, l_total);
+      num[0] = fmaf(a_c[u].x, w, num[0]); num[1] = fmaf(a_c[u].y, w, num[1]);
+      num[2] = fmaf(b_c[u].x, w, num[2]); num[3] = fmaf(b_c[u].y, w, num[3]);
+    }
+  };
+  if (live_chunks > 0) {
+    load_batch(0);
+#pragma unroll
+    for (int u = 0; u < 16; ++u) m_star = fmaxf(m_star, m_c[u]);
+    for (uint32_t i = 16; i < live_chunks; ++i) m_star = fmaxf(m_star, __ldcg(&base[i * chunk_step + DEC_DH]));
+    add_batch(0);
+    for (uint32_t c0 = 16; c0 < live_chunks; c0 += 16) {
+      load_batch(c0);
+      add_batch(c0);
+    }
   }
   const float inv = l_total > 0.0f ? 1.0f / l_total : 0.0f;
   float *o = p.out + ((size_t)kv_head * p.group + row) * DEC_DH + lane * 4;

@@ -463,6 +463,136 @@ void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n
   else launch_t<128, false>(ctx, p, status, stream);
 }
 
+// ---------------------------------------------------------------- K split of a lone few-tile GEMM
+// A GEMM whose output tiles cover a fraction of the SMs (1024^3: 32 or 64 tiles on 148) leaves the
+// rest idle for the whole K loop.  Such an op runs as the split-K stage 1 above over `c` equal K
+// ranges per tile (planes of alpha * partial in the slot scratch) followed by one kernel that adds a
+// tile's planes in plane order and applies the op's epilogue: same formulas, the sum's rounding
+// order differs from the one-launch kernel's (shorter accumulations: the error is smaller).
+namespace {
+SplitK2TensorPlan ksplit_plan_for_width(uint32_t bn, uint32_t batch, uint32_t m, uint32_t n, uint32_t kb_all, int sm_count) {
+  SplitK2TensorPlan plan;
+  const uint64_t tiles = (uint64_t)((m + BM - 1) / BM) * ((n + bn - 1) / bn) * batch;
+  if (tiles * 2 > (uint64_t)sm_count) return plan;                         // more than half a wave already
+  uint64_t c = std::min<uint64_t>((uint64_t)sm_count / tiles, kb_all / 16); // a range keeps at least 256 k
+  if (c < 2) return plan;
+  c = std::max<uint64_t>(c, (kb_all + CHUNK_KB - 1) / CHUNK_KB);           // one accumulation holds at most CHUNK_KB blocks
+  const uint32_t kb_per_sub = (uint32_t)((kb_all + c - 1) / c);
+  c = (kb_all + kb_per_sub - 1) / kb_per_sub;
+  plan.eligible = true;
+  plan.tile_n = bn;
+  plan.c = (uint32_t)c;
+  plan.kb_per_split = kb_all;
+  plan.kb_per_sub = kb_per_sub;
+  plan.planes = (uint32_t)c;
+  return plan;
+}
+}  // namespace
+
+// Tile width: the one whose units (tiles x ranges) fill more of one wave; when the accumulation cap
+// forces more ranges than a wave holds, the wider tile (fewer units).  Measured on 1024 x 512 x 1024
+// (27.7 us at 256 wide, 21.6 at 128), 512 x 512 x 4096 (30.4 / 28.1) and 1024 x 1024 x 4096 (69.5 / 82.0).
+SplitK2TensorPlan gemm_tf32x3_ksplit_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count) {
+  const int mode = tunables().tf32x3_ksplit;
+  if (mode == 0 || k % BK != 0 || n % 4 != 0) return SplitK2TensorPlan{};
+  if ((uint64_t)m * n * k < (1ull << 29)) return SplitK2TensorPlan{};      // small ops: the second launch costs more than it saves
+  const uint32_t kb_all = k / BK;
+  const SplitK2TensorPlan narrow = ksplit_plan_for_width(128, batch, m, n, kb_all, sm_count);
+  if (mode == 128 || n % 256 != 0) return narrow;
+  const SplitK2TensorPlan wide = ksplit_plan_for_width(256, batch, m, n, kb_all, sm_count);
+  if (mode == 256 || !narrow.eligible) return wide;
+  if (!wide.eligible) return narrow;
+  const uint64_t sm = (uint64_t)sm_count;
+  const uint64_t un = (uint64_t)((m + BM - 1) / BM) * ((n + 127) / 128) * batch * narrow.c;
+  const uint64_t uw = (uint64_t)((m + BM - 1) / BM) * ((n + 255) / 256) * batch * wide.c;
+  if (un <= sm && uw <= sm) return un > uw ? narrow : wide;
+  return uw <= un ? wide : narrow;
+}
+
+size_t gemm_tf32x3_ksplit_scratch_bytes(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count) {
+  const SplitK2TensorPlan plan = gemm_tf32x3_ksplit_plan(batch, m, n, k, sm_count);
+  return plan.eligible ? (size_t)batch * plan.planes * m * n * 4 : 0;
+}
+
+namespace {
+// One thread per four consecutive outputs of a row: planes in plane order from 0.0f, then
+// (+ C_old) -> + bias -> activation -> binary stage, as the tile epilogues do.
+template <uint32_t ACT>
+__global__ void __launch_bounds__(256)
+ksplit_reduce_epilogue_kernel(const float *__restrict__ planes, const GemmParams p, uint32_t nplanes) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const uint64_t mn = (uint64_t)p.m * p.n, total = mn * p.batch;
+  const uint64_t base = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (base >= total) return;
+  const uint64_t batch = base / mn, e = base % mn;
+  const uint32_t row = (uint32_t)(e / p.n), col = (uint32_t)(e % p.n);
+  const float *src = planes + batch * nplanes * mn + e;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  uint32_t s = 0;
+  for (; s + 4 <= nplanes; s += 4) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)(s + u) * mn));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+  }
+  for (; s < nplanes; ++s) {
+    const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (uint64_t)s * mn));
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  const size_t off = (size_t)batch * p.stride_c + (size_t)row * p.n + col;
+  if (p.accumulate) {
+    const float4 c_old = *reinterpret_cast<const float4 *>(p.c + off);
+    acc.x += c_old.x; acc.y += c_old.y; acc.z += c_old.z; acc.w += c_old.w;
+  }
+  float4 bv = make_float4(0.f, 0.f, 0.f, 0.f), dv = bv;
+  if (p.bias) bv = __ldg(reinterpret_cast<const float4 *>(p.bias + (size_t)batch * p.bias_stride + col));
+  if (p.d) dv = *reinterpret_cast<const float4 *>(p.d + off);
+  const bool hb = p.bias != nullptr;
+  acc.x = epi_apply_t<ACT>(acc.x, hb, bv.x, p.binary, dv.x, p.beta);
+  acc.y = epi_apply_t<ACT>(acc.y, hb, bv.y, p.binary, dv.y, p.beta);
+  acc.z = epi_apply_t<ACT>(acc.z, hb, bv.z, p.binary, dv.z, p.beta);
+  acc.w = epi_apply_t<ACT>(acc.w, hb, bv.w, p.binary, dv.w, p.beta);
+  *reinterpret_cast<float4 *>(p.c + off) = acc;
+}
+
+template <uint32_t ACT>
+void launch_ksplit_reduce_t(const float *planes, const GemmParams &p, uint32_t nplanes, cudaStream_t stream) {
+  const uint64_t threads = (uint64_t)p.batch * p.m * p.n / 4;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((threads + 255) / 256), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;   // stage 1 releases its dependents at entry; this grid waits for it before the first plane read
+  TA_CUDA(cudaLaunchKernelEx(&cfg, ksplit_reduce_epilogue_kernel<ACT>, planes, p, nplanes));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+}  // namespace
+
+void launch_gemm_tf32x3_ksplit(const Context &ctx, const GemmParams &p_in, const SplitK2TensorPlan &plan, float *scratch,
+                               uint32_t *status, cudaStream_t stream) {
+  if (!plan.eligible || !gemm_tf32x3_eligible(p_in)) fail("internal: K-split 3xTF32 GEMM launched on an ineligible problem");
+  GemmParams p = p_in;
+  p.sk_subs = plan.planes;
+  p.sk_c = plan.c;
+  p.sk_kb_per_split = plan.kb_per_split;
+  p.sk_kb_per_sub = plan.kb_per_sub;
+  p.sk_planes = scratch;
+  p.bias = nullptr; p.d = nullptr; p.accumulate = 0; p.act = 0; p.binary = 0;
+  if (plan.tile_n >= 256) launch_t<256, true>(ctx, p, status, stream);
+  else launch_t<128, true>(ctx, p, status, stream);
+  switch (p_in.act) {
+    case 1: launch_ksplit_reduce_t<1>(scratch, p_in, plan.planes, stream); break;
+    case 2: launch_ksplit_reduce_t<2>(scratch, p_in, plan.planes, stream); break;
+    case 3: launch_ksplit_reduce_t<3>(scratch, p_in, plan.planes, stream); break;
+    default: launch_ksplit_reduce_t<0>(scratch, p_in, plan.planes, stream); break;
+  }
+}
+
 // ---------------------------------------------------------------- split-K2 stage 1 on the tensor cores
 // Eligible when the reference's partition (src/executor/splitk2.rs, shaders/matmul_splitk2_kernel.glsl:138-142:
 // K / S per split, the first K % S splits one longer) lands on K-block boundaries: K a multiple

@@ -54,6 +54,7 @@ extern std::atomic<uint64_t> g_launches;
 // the launch path calls getenv.
 struct Tunables {
   uint32_t tf32x3_chunk_kb = 0;   // K blocks of 16 per tensor-memory accumulation (0 = kernel default)
+  int tf32x3_ksplit = 1;          // few-tile 3xTF32 GEMM split along K over the idle SMs (0 = off, 1 = on, 128 / 256 = on with that tile width)
   int gemv_ksplit = 0;            // force the GEMV cluster split along K (1/2/4/8; 0 = chosen per shape)
   int gemv_bulk = -1;             // 1/0: force the bulk-copy ring of the 1-2 row GEMV on/off (-1 = per shape)
   int gemv_umma = -1;             // 1/0: force the tensor-memory GEMV (3..8 rows) on/off (-1 = per shape)
@@ -69,6 +70,7 @@ struct Tunables {
   bool f16w_dual = true;          // f16w tensor-core GEMM: up and gate of a SwiGLU pair as one dual-matrix launch
   uint32_t attn_chunks = 0;       // decode attention with a position cell: chunk grid (0 = one 64-position tile per chunk, 8..32)
   uint32_t flash_groups = 2;     // tensor-core prefill attention: warp groups per query block that split its K/V tiles (1 or 2)
+  bool attn_pairs = true;         // decode attention hands its chunk partials over as flagged pairs (no fence, no ticket)
   bool pos_stage = true;          // position cells read by graph launches are staged to device memory per submission
 };
 const Tunables &tunables();
@@ -341,6 +343,9 @@ struct SplitK2TensorPlan {
   uint32_t tile_n = 0, c = 0, kb_per_split = 0, kb_per_sub = 0, planes = 0;
 };
 SplitK2TensorPlan splitk2_tensor_plan(const GemmParams &p, uint32_t splits, int sm_count);
+// K split of a lone 3xTF32 GEMM with few output tiles (stage 1 planes + reduce with the op's epilogue)
+SplitK2TensorPlan gemm_tf32x3_ksplit_plan(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count);
+size_t gemm_tf32x3_ksplit_scratch_bytes(uint32_t batch, uint32_t m, uint32_t n, uint32_t k, int sm_count);
 
 // Parameters of the f16-weight GEMV kernel (M <= 8 activation rows).
 struct GemvParams {
@@ -429,6 +434,8 @@ struct AttnDecodeParams {
   uint32_t *counters;   // per-kv-head tickets (zero between launches), owned by the submitting slot
   uint32_t pdl;
   uint32_t prefetch_kv; // 1: the launch before this one wrote at most position kv_len - 1 of the cache
+  uint32_t *pairs;      // flagged partials (attn_pairs_of the slot) when the launch fits them, else null: tickets
+  uint32_t *pair_seq;   // with pairs: launch counts, one per kv head
 };
 
 struct FlashAttentionDesc {
@@ -597,6 +604,15 @@ constexpr uint32_t SLOT_COUNTERS = F16W_SPLIT_COUNTER0 + 512;
 // behind the ticket words of a slot / prepared object: device copies of the position cells a submission reads
 constexpr uint32_t POS_STAGE_WORDS = 8;
 inline uint32_t *pos_stage_of(uint32_t *counters) { return counters + SLOT_COUNTERS; }
+// behind those: one launch count per kv head and the (value, flag) pairs of the decode attention's chunk
+// partials.  Only the attention kernel touches them: a launch tags its pairs with its kv head's count + 1,
+// the combining CTA advances the count, so a pair of an earlier launch never looks current.
+constexpr uint32_t ATTN_SEQ_OFFSET = SLOT_COUNTERS + POS_STAGE_WORDS;       // ATTN_DECODE_MAX_KV_HEADS words
+constexpr uint32_t ATTN_PAIR_ROWS = 1024;                                   // kv heads x chunks x 8 query rows it holds
+constexpr uint32_t ATTN_PAIR_ROW_WORDS = (64 + 2) * 2;                      // dh + (max, sum), two words each
+constexpr uint32_t ATTN_PAIRS_OFFSET = (ATTN_SEQ_OFFSET + ATTN_DECODE_MAX_KV_HEADS + 3u) & ~3u;   // 16-byte aligned
+constexpr uint32_t SLOT_WORDS = ATTN_PAIRS_OFFSET + ATTN_PAIR_ROWS * ATTN_PAIR_ROW_WORDS;   // whole allocation
+inline uint32_t *attn_pairs_of(uint32_t *counters) { return counters + ATTN_PAIRS_OFFSET; }
 inline uint32_t attn_decode_num_chunks(uint32_t kv_len) {
   const uint32_t c = (kv_len + 31) / 32;
   return c < 8 ? 8 : (c > ATTN_DECODE_MAX_CHUNKS ? ATTN_DECODE_MAX_CHUNKS : c);
@@ -627,7 +643,7 @@ struct Slot {
 void alloc_status_word(uint32_t **host, uint32_t **device);
 void free_status_word(uint32_t *host);
 // reads and clears the word; raises the matching error when a bit is set
-void check_status_word(uint32_t *host);
+void check_status_word(uint32_t *host, uint32_t *counters = nullptr);
 
 // What a GEMV launch may use of its slot (or prepared object): the status word, and for the
 // tensor-memory kernel the plane scratch and the ticket words.
@@ -878,6 +894,8 @@ void launch_gemm_tf32x3(const Context &ctx, const GemmParams &p, uint32_t tile_n
                         cudaStream_t stream);
 void launch_splitk2_stage1(const GemmParams &p, uint32_t tile, float *scratch, cudaStream_t stream);
 // stage 1 on the tensor cores (plan.eligible) followed by the fixed-order reduce of plan.planes planes
+void launch_gemm_tf32x3_ksplit(const Context &ctx, const GemmParams &p, const SplitK2TensorPlan &plan, float *scratch,
+                               uint32_t *status, cudaStream_t stream);
 void launch_splitk2_tensor(const Context &ctx, const GemmParams &p, const SplitK2TensorPlan &plan, float *scratch,
                            uint32_t *status, cudaStream_t stream);
 // sum of `planes` planes per batch in plane order inside fixed groups, groups in order; launched so

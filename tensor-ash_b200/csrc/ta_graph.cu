@@ -353,6 +353,10 @@ Launch Executor::plan_exec_op_tail(const ExecOp &o, size_t *n_calls) const {
         q.status = slot.status;
         q.pdl = 1;
         q.prefetch_kv = prefetch;
+        if (tunables().attn_pairs && q.kv_f16 && q.kv_heads * q.num_chunks * 8u <= ATTN_PAIR_ROWS) {
+          q.pairs = attn_pairs_of(slot.counters);
+          q.pair_seq = slot.counters + ATTN_SEQ_OFFSET;
+        }
         launch_attn_decode(q, st);
       };
     }
@@ -870,8 +874,8 @@ std::unique_ptr<PreparedOps> prepare_exec_ops(Executor &exec, const std::vector<
   TA_CUDA(cudaStreamCreateWithFlags(&prep->stream, cudaStreamNonBlocking));
   TA_CUDA(cudaEventCreate(&prep->ev_begin));
   TA_CUDA(cudaEventCreate(&prep->ev_end));
-  TA_CUDA(cudaMalloc((void **)&prep->counters, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
-  TA_CUDA(cudaMemset(prep->counters, 0, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
+  TA_CUDA(cudaMalloc((void **)&prep->counters, SLOT_WORDS * sizeof(uint32_t)));
+  TA_CUDA(cudaMemset(prep->counters, 0, SLOT_WORDS * sizeof(uint32_t)));
   alloc_status_word(&prep->status_host, &prep->status);
   Slot &real_slot = exec.checkout_slot();
   {

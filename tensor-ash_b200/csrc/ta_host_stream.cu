@@ -210,7 +210,7 @@ RunStats Executor::run_matmul_host_batched(const HostBatchedMatmul &h) {
   TA_CUDA(cudaStreamSynchronize(st.d2h));
   TA_CUDA(cudaStreamSynchronize(comp));
   TA_CUDA(cudaStreamSynchronize(st.h2d));
-  check_status_word(slot.status_host);
+  check_status_word(slot.status_host, slot.counters);
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, st.ev_begin, st.ev_end));
   RunStats out;

@@ -133,8 +133,8 @@ Executor::Executor(std::shared_ptr<Context> ctx, int selection, ExecutorConfig c
     TA_CUDA(cudaEventCreate(&s.ev_begin));
     TA_CUDA(cudaEventCreate(&s.ev_end));
     alloc_status_word(&s.status_host, &s.status);
-    TA_CUDA(cudaMalloc((void **)&s.counters, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
-    TA_CUDA(cudaMemset(s.counters, 0, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
+    TA_CUDA(cudaMalloc((void **)&s.counters, SLOT_WORDS * sizeof(uint32_t)));
+    TA_CUDA(cudaMemset(s.counters, 0, SLOT_WORDS * sizeof(uint32_t)));
   }
   tune_path_ = tune_store_path(ctx_->name);
   tuned_ = load_tuned(tune_path_);
@@ -209,10 +209,12 @@ void alloc_status_word(uint32_t **host, uint32_t **device) {
 void free_status_word(uint32_t *host) {
   if (host) cudaFreeHost(host);
 }
-void check_status_word(uint32_t *host) {
+void check_status_word(uint32_t *host, uint32_t *counters) {
   const uint32_t status = *(volatile uint32_t *)host;
   if (!status) return;
   *(volatile uint32_t *)host = 0;
+  // a launch that gave up may have left tickets and partial flags behind: back to the state a new slot has
+  if (counters) cudaMemset(counters, 0, SLOT_WORDS * sizeof(uint32_t));
   fail_device_status(status);
 }
 
@@ -484,6 +486,11 @@ size_t Executor::op_scratch_bytes(const ResolvedMatmul &r, const Route &route) c
       r.k % 16 == 0 && (tunables().gemv_umma == 1 || (r.m >= 3 && tunables().gemv_umma != 0)))
     // records of the tensor-memory GEMV; sized for the SwiGLU pair too (twice the groups)
     return gemv_umma_scratch_bytes(r.n, r.k, true, ctx_->sm_count);
+  if (KERNEL_SPECS[route.kernel].family == Family::Tf32x3 && KERNEL_SPECS[route.kernel].tile_m != 256 && !r.b_f16 && !r.a_f16) {
+    // planes of the K split a few-tile op runs as
+    const size_t need = gemm_tf32x3_ksplit_scratch_bytes(r.batch, r.m, r.n, r.k, ctx_->sm_count);
+    return need <= (256ull << 20) ? need : 0;
+  }
   if (KERNEL_SPECS[route.kernel].family != Family::F16wUmma) return 0;
   // the f16 copy of A, and behind it the partial tiles of an in-kernel K split
   const size_t need = gemm_f16w_umma_scratch_bytes_split(r.batch, r.batch_stride_a ? r.batch : 1, r.m, r.n, r.k, ctx_->sm_count);
@@ -575,6 +582,14 @@ void Executor::enqueue_op(const MatmulOp &op, const ResolvedMatmul &r, const Rou
   switch (spec.family) {
     case Family::Tf32x3:
       if (gemm_tf32x3_eligible(p)) {
+        if (spec.tile_m != 256) {
+          // few output tiles: split K over the idle SMs when the slot holds the planes
+          const SplitK2TensorPlan kplan = gemm_tf32x3_ksplit_plan(r.batch, r.m, r.n, r.k, ctx_->sm_count);
+          if (kplan.eligible && slot.scratch && slot.scratch_bytes >= (size_t)r.batch * kplan.planes * r.m * r.n * 4) {
+            launch_gemm_tf32x3_ksplit(*ctx_, p, kplan, static_cast<float *>(slot.scratch), slot.status, stream);
+            return;
+          }
+        }
         if (spec.tile_m == 256) launch_gemm_tf32x3_pair(*ctx_, p, slot.status, stream);
         else launch_gemm_tf32x3(*ctx_, p, spec.tile_n, slot.status, stream);
         return;
@@ -605,7 +620,7 @@ RunStats Executor::timed(Slot &slot, size_t n_calls, uint64_t flops,
   record(slot.stream);
   TA_CUDA(cudaEventRecord(slot.ev_end, slot.stream));
   TA_CUDA(cudaStreamSynchronize(slot.stream));
-  check_status_word(slot.status_host);
+  check_status_word(slot.status_host, slot.counters);
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, slot.ev_begin, slot.ev_end));
   RunStats st;
@@ -914,8 +929,8 @@ std::unique_ptr<PreparedOps> prepare_ops(Executor &exec, const std::vector<Matmu
   size_t scratch_bytes = 0;
   for (size_t i = 0; i < ops.size(); ++i) scratch_bytes = std::max(scratch_bytes, exec.op_scratch_bytes(resolved[i], routes[i]));
   if (scratch_bytes) TA_CUDA(cudaMalloc(&prep->scratch, scratch_bytes));
-  TA_CUDA(cudaMalloc((void **)&prep->counters, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
-  TA_CUDA(cudaMemset(prep->counters, 0, (SLOT_COUNTERS + POS_STAGE_WORDS) * sizeof(uint32_t)));
+  TA_CUDA(cudaMalloc((void **)&prep->counters, SLOT_WORDS * sizeof(uint32_t)));
+  TA_CUDA(cudaMemset(prep->counters, 0, SLOT_WORDS * sizeof(uint32_t)));
   alloc_status_word(&prep->status_host, &prep->status);
   // Captured directly, nothing runs at create time: encoding tensor maps and setting function
   // attributes are host calls, which a stream capture allows.
@@ -974,7 +989,7 @@ RunStats PreparedOps::wait() {
   TA_CUDA(cudaStreamSynchronize(stream));
   in_flight = false;
   // a kernel of the replayed graph that gave up on a bounded wait reports here, as for an eager run
-  if (status_host) check_status_word(status_host);
+  if (status_host) check_status_word(status_host, counters);
   float ms = 0.0f;
   TA_CUDA(cudaEventElapsedTime(&ms, ev_begin, ev_end));
   RunStats st;

@@ -344,6 +344,34 @@ def test_config1_gelu_1024(setup, orc):
     check(orc, ex.download(c), ref, epi_tol(orc, n), "config 1")
 
 
+def test_few_tile_ops_split_along_k(setup, orc):
+    """Ops whose output tiles cover under half of the SMs run as K ranges over the idle SMs plus a
+    reduce that applies the epilogue (3xTF32 routes; the other routes run the same cases in one
+    launch): every epilogue stage, alpha, accumulate, an in-place residual, a batch with per-batch
+    bias.  Twice: the planes live in slot scratch that the second run reuses."""
+    ta, ctx, ex, _ = setup
+    A = ta.Activation
+    for case in (((512, 512, 4096), 0.5, True, True, A.SILU, (0.75, False)),     # 16 planes
+                 ((1024, 512, 1024), 1.0, False, True, A.RELU, (0.0, True)),
+                 ((640, 384, 2320), 2.0, False, False, A.NONE, None)):            # partial tiles, a shorter last K range
+        run_epilogue_case(setup, orc, *case)
+        run_epilogue_case(setup, orc, *case)
+    batch, m, n, k = 2, 512, 1024, 1024
+    sig = 1.0 / np.sqrt(k)
+    ha, hb = orc.fill_normal((batch, m, k), 20, sig), orc.fill_normal((k, n), 21, sig)
+    hbias, hr = orc.fill_normal((batch, n), 22, sig), orc.fill_normal((batch, m, n), 23, sig)
+    a, b = ta.Tensor.uninit_device(ctx, (batch, m, k)), ta.Tensor.uninit_device(ctx, (k, n))
+    bias, c = ta.Tensor.uninit_device(ctx, (batch, n)), ta.Tensor.uninit_device(ctx, (batch, m, n))
+    for t, h in ((a, ha), (b, hb), (bias, hbias), (c, hr)):
+        ex.upload(h, t)
+    # the residual is C itself (read by the epilogue, then overwritten)
+    ex.run_ops([ta.MatmulOp(ta.MatmulCall(a, b, c),
+                            ta.Epilogue(bias, A.GELU, ta.Binary.ADD_SCALED, c, 1.0))])
+    ref = orc.cpu_bmm(ha, hb, batch, m, n, k)
+    ref = orc.cpu_epilogue(ref, batch, m, n, bias=hbias, act="gelu", binary="add_scaled", d=hr, beta=1.0)
+    check(orc, ex.download(c), ref, epi_tol(orc, k), "batched few-tile op, in-place residual")
+
+
 def test_config2_shape_family_small(setup, orc):
     """Batched GEMM with shared B, per-batch bias, SiLU and residual at a size the
     oracle finishes in seconds (the full 32 x 2048^3 case is in test_full_size.py)."""
