@@ -234,6 +234,22 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   if (e_valid && (p.store_kind == 1 || p.store_kind == 3))
     pre_cs = *reinterpret_cast<const float2 *>(p.table + ((size_t)pos * (p.head_dim / 2) + (e_c % p.head_dim) / 2) * 2);
 
+  // ---- cluster hand-over: the partial tiles of ranks 1.. reach rank 0 as asynchronous
+  // shared-memory stores that count their bytes on a barrier in rank 0's shared memory (one hop, no
+  // fence, no cluster barrier on the way).  The barrier is armed here, before the dependency
+  // wait, and one cluster barrier makes it known to the other ranks while everybody idles.
+  const uint32_t cbar = (umma::smem_u32(scale + MROWS) + 7u) & ~7u;
+  __shared__ uint32_t cbar_abort;
+  if (S > 1 && g.handoff_async) {
+    if (rank == 0 && threadIdx.x == 0) {
+      cbar_abort = 0;
+      umma::mbar_init(cbar, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      umma::mbar_arrive_expect_tx(cbar, (S - 1u) * (uint32_t)((dual ? 2 : 1) * MROWS * TN * 4));
+    }
+    cluster.sync();
+  }
+
   // ---- everything below may depend on the previous kernel in the stream
   if (g.pdl) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -434,6 +450,26 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   }
   __syncthreads();
   const int nmat = dual ? 2 : 1;
+  if (S > 1 && g.handoff_async) {
+    uint32_t rdst = 0, rbar = 0;
+    if (rank != 0) {
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rdst) : "r"(umma::smem_u32(cpart + (size_t)rank * 2 * MROWS * TN)), "r"(0u));
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(cbar), "r"(0u));
+    }
+    for (int idx = threadIdx.x; idx < nmat * MROWS * TN; idx += GEMV_THREADS) {
+      const int mt = idx / (MROWS * TN), rem = idx % (MROWS * TN);
+      float s = 0.0f;
+      for (int w = 0; w < nw; ++w) s += wpart[((size_t)(mt * nw + w)) * MROWS * TN + rem];
+      if (rank == 0) cpart[idx] = s;
+      else
+        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(rdst + (uint32_t)idx * 4u),
+                     "r"(__float_as_uint(s)), "r"(rbar) : "memory");
+    }
+    if (rank != 0) return;
+    // every thread of rank 0 waits (bounded) for the other ranks' bytes
+    if (!umma::mbar_wait(cbar, 0, &cbar_abort) && threadIdx.x == 0 && g.status) atomicOr(g.status, 1u);
+    __syncthreads();
+  } else {
   float *cdst = S > 1 ? cluster.map_shared_rank(cpart, 0) : cpart;   // rank 0's buffer
   for (int idx = threadIdx.x; idx < nmat * MROWS * TN; idx += GEMV_THREADS) {
     const int mt = idx / (MROWS * TN), rem = idx % (MROWS * TN);
@@ -447,6 +483,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     cluster.barrier_wait();
   } else {
     __syncthreads();
+  }
   }
 
   // ---- rank 0: sum ranks in order, epilogue, store
@@ -629,6 +666,10 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
   uint64_t weight_bytes = 0;
   for (int i = 0; i < nseg; ++i) weight_bytes += (uint64_t)segs[i].k * segs[i].n * 2 * (segs[i].w2 ? 2 : 1);
   if (p0.m > 2) bulk = false;   // more rows: the staged x slice and the accumulators need the space
+  // The asynchronous hand-over arms its barrier behind one cluster barrier at CTA start: free while a
+  // resident CTA waits for the launch before it (the few-MB matrices of a decode step: 0.973 -> 0.937 ms
+  // per token), a cost per CTA when a long stream runs in several waves (4096 x 11008: 56.8 -> 58.7 us)
+  g.handoff_async = (tunables().gemv_handoff && weight_bytes < (64ull << 20)) ? 1u : 0u;
   // measured: the ring wins on long streams (4096 x 11008: 3.8 -> 4.8 TB/s) and is neutral to
   // slightly slower on the few-MB matrices of a decode step, which are latency-bound
   if (weight_bytes < (64ull << 20)) bulk = false;
