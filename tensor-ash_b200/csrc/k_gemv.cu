@@ -102,8 +102,54 @@ __device__ __forceinline__ float peer_pair_load(const uint2 *p, uint32_t flag, u
   return __uint_as_float(v.x);
 }
 
+// EB pushed elements at once: the pairs of up to four ranks per element are requested together and a
+// poll re-requests every pair that is still missing before it looks at any, so a pull costs one L2
+// round trip per poll, not one per (element, rank).  The sum runs in rank order.
+template <int EB>
+__device__ __forceinline__ void peer_pull_sum(const PeerLink &pl, uint32_t flag, const size_t (&off)[EB], const bool (&on)[EB],
+                                              float (&out)[EB], uint32_t *status, bool &dead) {
+#pragma unroll
+  for (int e = 0; e < EB; ++e) out[e] = 0.0f;
+  for (uint32_t r0 = 0; r0 < pl.world; r0 += 4) {
+    uint2 v[EB][4];
+    const uint2 *src[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) src[j] = peer_slot(pl, pl.rank, pl.pull_slot, min(r0 + j, pl.world - 1));
+#pragma unroll
+    for (int e = 0; e < EB; ++e)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[e][j] = make_uint2(0u, ~flag);
+    const uint64_t t0 = umma::global_timer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+#pragma unroll
+      for (int e = 0; e < EB; ++e)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (on[e] && r0 + j < pl.world && v[e][j].y != flag)
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[e][j].x), "=r"(v[e][j].y) : "l"(src[j] + off[e]) : "memory");
+      bool all = true;
+#pragma unroll
+      for (int e = 0; e < EB; ++e)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) all = all && (!on[e] || r0 + j >= pl.world || v[e][j].y == flag);
+      if (all || dead) break;
+      if ((++spins & 255u) == 0 && umma::global_timer_ns() - t0 > pl.limit_ns) {
+        if (status) atomicOr(status, 4u);     // reported by the host; the sums are then invalid
+        dead = true;
+        break;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < EB; ++e)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (r0 + j < pl.world) out[e] += __uint_as_float(v[e][j].x);
+  }
+}
+
 template <int MROWS, int TN, bool BULK, bool PEER = false>
-__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (BULK ? 3 : 4) : (MROWS == 4 ? 3 : 2))
+__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (PEER ? 2 : (BULK ? 3 : 4)) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   static_assert(!PEER || !BULK, "the exchange variant is built for the register-streamed path");
   constexpr int U = GemvCfg<MROWS>::U;
@@ -268,29 +314,58 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   auto xval = [&](uint32_t m, uint32_t k) -> float {
     if constexpr (PEER) {
       if (pull) {
-        float acc = 0.0f;
-        for (uint32_t r = 0; r < g.peer.world; ++r)
-          acc += peer_pair_load(peer_slot(g.peer, g.peer.rank, g.peer.pull_slot, r) + (size_t)m * p.k + k, pull_flag,
-                                g.peer.limit_ns, g.status, peer_dead);
-        return acc;
+        const size_t off[1] = {(size_t)m * p.k + k};
+        const bool on[1] = {true};
+        float out[1];
+        peer_pull_sum<1>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
+        return out[0];
       }
     }
     return p.x[(size_t)m * p.k + k];
   };
   const uint32_t stage_n = k_len * MROWS;
   float xv[XS_PRE];
+  bool xv_pulled = false;
+  if constexpr (PEER) {
+    if (pull) {   // two slice elements per poll
+      xv_pulled = true;
 #pragma unroll
-  for (int it = 0; it < XS_PRE; ++it) {
-    const uint32_t idx = threadIdx.x + it * GEMV_THREADS, kk = idx / MROWS, m = idx % MROWS;
-    xv[it] = (idx < stage_n && m < p.m) ? xval(m, k_lo + kk) : 0.0f;
+      for (int it = 0; it < XS_PRE; it += 2) {
+        size_t off[2];
+        bool on[2];
+        float out[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const uint32_t idx = threadIdx.x + (it + e) * GEMV_THREADS, kk = idx / MROWS, m = idx % MROWS;
+          on[e] = idx < stage_n && m < p.m;
+          off[e] = on[e] ? (size_t)m * p.k + k_lo + kk : 0;
+        }
+        if (on[0] || on[1]) peer_pull_sum<2>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
+        xv[it] = on[0] ? out[0] : 0.0f;
+        xv[it + 1] = on[1] ? out[1] : 0.0f;
+      }
+    }
+  }
+  if (!xv_pulled) {
+#pragma unroll
+    for (int it = 0; it < XS_PRE; ++it) {
+      const uint32_t idx = threadIdx.x + it * GEMV_THREADS, kk = idx / MROWS, m = idx % MROWS;
+      xv[it] = (idx < stage_n && m < p.m) ? xval(m, k_lo + kk) : 0.0f;
+    }
   }
   if constexpr (PEER) {
     // the first column tile leaves the summed activation where later launches expect x
-    if (pull && g.peer.x_out && tile_all == 0)
-      for (uint32_t idx = threadIdx.x; idx < stage_n; idx += GEMV_THREADS) {
+    if (pull && g.peer.x_out && tile_all == 0) {
+#pragma unroll
+      for (int it = 0; it < XS_PRE; ++it) {
+        const uint32_t idx = threadIdx.x + it * GEMV_THREADS, kk = idx / MROWS, m = idx % MROWS;
+        if (idx < stage_n && m < p.m) g.peer.x_out[(size_t)m * p.k + k_lo + kk] = xv[it];
+      }
+      for (uint32_t idx = threadIdx.x + XS_PRE * GEMV_THREADS; idx < stage_n; idx += GEMV_THREADS) {
         const uint32_t kk = idx / MROWS, m = idx % MROWS;
         if (m < p.m) g.peer.x_out[(size_t)m * p.k + k_lo + kk] = xval(m, k_lo + kk);
       }
+    }
   }
   if (e_valid && p.store_kind == 0) {
     if (p.d) pre_d = p.d[e_ci];
@@ -303,9 +378,22 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     for (int m = 0; m < MROWS; ++m) {
       ss[m] = 0.0f;
       if ((uint32_t)m < p.m && pull) {
-        for (uint32_t k = threadIdx.x; k < p.k; k += GEMV_THREADS) {
-          const float a = xval(m, k);
-          ss[m] = fmaf(a, a, ss[m]);
+        if constexpr (PEER) {   // four row elements per poll, squares added in k order
+          for (uint32_t k0 = threadIdx.x; k0 < p.k; k0 += 4 * GEMV_THREADS) {
+            size_t off[4];
+            bool on[4];
+            float out[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const uint32_t k = k0 + e * GEMV_THREADS;
+              on[e] = k < p.k;
+              off[e] = on[e] ? (size_t)m * p.k + k : 0;
+            }
+            peer_pull_sum<4>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (on[e]) ss[m] = fmaf(out[e], out[e], ss[m]);
+          }
         }
       } else if ((uint32_t)m < p.m) {
         const float *xr = p.x + (size_t)m * p.k;
