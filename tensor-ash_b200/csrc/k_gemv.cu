@@ -149,7 +149,11 @@ __device__ __forceinline__ void peer_pull_sum(const PeerLink &pl, uint32_t flag,
 }
 
 template <int MROWS, int TN, bool BULK, bool PEER = false>
-__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (PEER ? 2 : (BULK ? 3 : 4)) : (MROWS == 4 ? 3 : 2))
+// Three CTAs per SM for one and two rows (85 registers): at four (64 registers) the two prefetched
+// weight passes did not fit beside the staged activation, part of them went to local memory before
+// the dependency wait and came back from L2 after it, 1.3 us per launch of a decode step
+// (0.94 -> 0.83 ms per token).
+__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (PEER ? 2 : 3) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   static_assert(!PEER || !BULK, "the exchange variant is built for the register-streamed path");
   constexpr int U = GemvCfg<MROWS>::U;
@@ -746,7 +750,7 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
   const uint32_t rpl = 32 / (tn / 8);
   const uint32_t nw = p0.w2 ? GEMV_WARPS / 2 : GEMV_WARPS;
   const uint32_t rows_per_pass = nw * rpl * u;
-  // K split over a cluster: about one and a half CTAs per SM.  With four resident
+  // K split over a cluster: about one and a half CTAs per SM.  With three resident
   // per SM that is one wave for this launch and leaves room for the early CTAs of
   // the next launch, which prefetch their weights while this one finishes.  Never
   // split below one pass of rows.
@@ -780,9 +784,9 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
       // the staged x slice (k_cta x rows floats) must leave room for several CTAs per SM
       if (s < 8 && gemv_smem_bytes(k_cta, mrows, (int)tn, s) > 40 * 1024 && p0.k / (2 * s) >= rows_per_pass) continue;
       // small matrices: 1.5 CTAs per SM; from 16 MB up more CTAs keep more of the stream in flight
-      const uint64_t want2 = weight_bytes >= (16ull << 20) ? 7ull : 3ull;   // CTAs per SM, doubled
+      const uint64_t want2 = weight_bytes >= (16ull << 20) ? 6ull : 3ull;   // CTAs per SM, doubled
       if ((uint64_t)tiles * s * 2 >= want2 * (uint64_t)sm_count) break;
-      if (s < 8 && (uint64_t)tiles * s * 2 * 2 > 8ull * (uint64_t)sm_count) break;   // the next split would not fit one wave
+      if (s < 8 && (uint64_t)tiles * s * 2 * 2 > 6ull * (uint64_t)sm_count) break;   // the next split would not fit one wave (three CTAs per SM)
     }
   }
   {   // experiment switch: force the cluster split
