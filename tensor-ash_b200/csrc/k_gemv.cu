@@ -270,11 +270,12 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     if (g.peer.pull_point1) pull_flag = peer_flag_of(g.peer.expect_base[g.peer.pull_point1 - 1], g.peer.pull_point1);
   // also independent of earlier kernels: the norm weights of the first slice elements
   // and this thread's rope table entry; epilogue operands (D, bias, old C) follow the wait
-  float nwv[XS_PRE];
+  // (the norm weights wait in the thread's own xs slots, not in registers: the prefetched weight
+  // passes need those across the dependency wait)
 #pragma unroll
   for (int it = 0; it < XS_PRE; ++it) {
     const uint32_t idx = threadIdx.x + it * GEMV_THREADS, kk = idx / MROWS;
-    nwv[it] = (p.norm_w && kk < k_len) ? p.norm_w[k_lo + kk] : 1.0f;
+    if (idx < k_len * MROWS) xs[idx] = (p.norm_w && kk < k_len) ? p.norm_w[k_lo + kk] : 1.0f;
   }
   const uint32_t e_m = threadIdx.x / TN, e_c = col0 + threadIdx.x % TN;
   const bool e_valid = rank == 0 && threadIdx.x < MROWS * TN && e_m < p.m && e_c < p.n;
@@ -420,7 +421,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
 #pragma unroll
   for (int it = 0; it < XS_PRE; ++it) {
     const uint32_t idx = threadIdx.x + it * GEMV_THREADS;
-    if (idx < stage_n) xs[idx] = xv[it] * nwv[it];
+    if (idx < stage_n) xs[idx] = xv[it] * xs[idx];
   }
   if constexpr (MROWS >= 4) {
     // many rows: walk k within a row so that global reads are contiguous (the first
