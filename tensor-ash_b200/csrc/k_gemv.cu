@@ -102,37 +102,38 @@ __device__ __forceinline__ float peer_pair_load(const uint2 *p, uint32_t flag, u
   return __uint_as_float(v.x);
 }
 
-// EB pushed elements at once: the pairs of up to four ranks per element are requested together and a
-// poll re-requests every pair that is still missing before it looks at any, so a pull costs one L2
-// round trip per poll, not one per (element, rank).  The sum runs in rank order.
+// EB pushed elements at once: the pairs of two ranks per element are requested together and a poll
+// re-requests every pair that is still missing before it looks at any, so a pull costs one L2 round
+// trip per poll, not one per (element, rank).  The sum runs in rank order.
 template <int EB>
 __device__ __forceinline__ void peer_pull_sum(const PeerLink &pl, uint32_t flag, const size_t (&off)[EB], const bool (&on)[EB],
                                               float (&out)[EB], uint32_t *status, bool &dead) {
+  constexpr int RB = 2;
 #pragma unroll
   for (int e = 0; e < EB; ++e) out[e] = 0.0f;
-  for (uint32_t r0 = 0; r0 < pl.world; r0 += 4) {
-    uint2 v[EB][4];
-    const uint2 *src[4];
+  for (uint32_t r0 = 0; r0 < pl.world; r0 += RB) {
+    uint2 v[EB][RB];
+    const uint2 *src[RB];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) src[j] = peer_slot(pl, pl.rank, pl.pull_slot, min(r0 + j, pl.world - 1));
+    for (int j = 0; j < RB; ++j) src[j] = peer_slot(pl, pl.rank, pl.pull_slot, min(r0 + j, pl.world - 1));
 #pragma unroll
     for (int e = 0; e < EB; ++e)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[e][j] = make_uint2(0u, ~flag);
+      for (int j = 0; j < RB; ++j) v[e][j] = make_uint2(0u, ~flag);
     const uint64_t t0 = umma::global_timer_ns();
     uint32_t spins = 0;
     for (;;) {
 #pragma unroll
       for (int e = 0; e < EB; ++e)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < RB; ++j)
           if (on[e] && r0 + j < pl.world && v[e][j].y != flag)
             asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v[e][j].x), "=r"(v[e][j].y) : "l"(src[j] + off[e]) : "memory");
       bool all = true;
 #pragma unroll
       for (int e = 0; e < EB; ++e)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) all = all && (!on[e] || r0 + j >= pl.world || v[e][j].y == flag);
+        for (int j = 0; j < RB; ++j) all = all && (!on[e] || r0 + j >= pl.world || v[e][j].y == flag);
       if (all || dead) break;
       if ((++spins & 255u) == 0 && umma::global_timer_ns() - t0 > pl.limit_ns) {
         if (status) atomicOr(status, 4u);     // reported by the host; the sums are then invalid
@@ -143,7 +144,7 @@ __device__ __forceinline__ void peer_pull_sum(const PeerLink &pl, uint32_t flag,
 #pragma unroll
     for (int e = 0; e < EB; ++e)
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < RB; ++j)
         if (r0 + j < pl.world) out[e] += __uint_as_float(v[e][j].x);
   }
 }
@@ -153,7 +154,7 @@ template <int MROWS, int TN, bool BULK, bool PEER = false>
 // weight passes did not fit beside the staged activation, part of them went to local memory before
 // the dependency wait and came back from L2 after it, 1.3 us per launch of a decode step
 // (0.94 -> 0.83 ms per token).
-__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? (PEER ? 2 : 3) : (MROWS == 4 ? 3 : 2))
+__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? 3 : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   static_assert(!PEER || !BULK, "the exchange variant is built for the register-streamed path");
   constexpr int U = GemvCfg<MROWS>::U;
@@ -383,20 +384,20 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     for (int m = 0; m < MROWS; ++m) {
       ss[m] = 0.0f;
       if ((uint32_t)m < p.m && pull) {
-        if constexpr (PEER) {   // four row elements per poll, squares added in k order
-          for (uint32_t k0 = threadIdx.x; k0 < p.k; k0 += 4 * GEMV_THREADS) {
-            size_t off[4];
-            bool on[4];
-            float out[4];
+        if constexpr (PEER) {   // two row elements per poll (registers), squares added in k order
+          for (uint32_t k0 = threadIdx.x; k0 < p.k; k0 += 2 * GEMV_THREADS) {
+            size_t off[2];
+            bool on[2];
+            float out[2];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 2; ++e) {
               const uint32_t k = k0 + e * GEMV_THREADS;
               on[e] = k < p.k;
               off[e] = on[e] ? (size_t)m * p.k + k : 0;
             }
-            peer_pull_sum<4>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
+            peer_pull_sum<2>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
+            for (int e = 0; e < 2; ++e)
               if (on[e]) ss[m] = fmaf(out[e], out[e], ss[m]);
           }
         }
