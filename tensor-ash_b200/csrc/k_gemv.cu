@@ -102,13 +102,12 @@ __device__ __forceinline__ float peer_pair_load(const uint2 *p, uint32_t flag, u
   return __uint_as_float(v.x);
 }
 
-// EB pushed elements at once: the pairs of two ranks per element are requested together and a poll
+// EB pushed elements at once: the pairs of RB ranks per element are requested together and a poll
 // re-requests every pair that is still missing before it looks at any, so a pull costs one L2 round
 // trip per poll, not one per (element, rank).  The sum runs in rank order.
-template <int EB>
+template <int EB, int RB>
 __device__ __forceinline__ void peer_pull_sum(const PeerLink &pl, uint32_t flag, const size_t (&off)[EB], const bool (&on)[EB],
                                               float (&out)[EB], uint32_t *status, bool &dead) {
-  constexpr int RB = 2;
 #pragma unroll
   for (int e = 0; e < EB; ++e) out[e] = 0.0f;
   for (uint32_t r0 = 0; r0 < pl.world; r0 += RB) {
@@ -149,12 +148,15 @@ __device__ __forceinline__ void peer_pull_sum(const PeerLink &pl, uint32_t flag,
   }
 }
 
-template <int MROWS, int TN, bool BULK, bool PEER = false>
+template <int MROWS, int TN, bool BULK, bool PEER = false, bool WIDE = false>
 // Three CTAs per SM for one and two rows (85 registers): at four (64 registers) the two prefetched
 // weight passes did not fit beside the staged activation, part of them went to local memory before
 // the dependency wait and came back from L2 after it, 1.3 us per launch of a decode step
 // (0.94 -> 0.83 ms per token).
-__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? 3 : (MROWS == 4 ? 3 : 2))
+// WIDE (exchange variant only): two CTAs per SM (128 registers) for launches that fit one wave at
+// that residency; a pull then requests four elements x four ranks per poll instead of two x two
+// (4 GPUs: 0.733 against 0.786 ms per token; on 2 GPUs, whose launches need three per SM, 0.894 against 0.789).
+__global__ void __launch_bounds__(GEMV_THREADS, MROWS <= 2 ? ((PEER && WIDE) ? 2 : 3) : (MROWS == 4 ? 3 : 2))
 gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
   static_assert(!PEER || !BULK, "the exchange variant is built for the register-streamed path");
   constexpr int U = GemvCfg<MROWS>::U;
@@ -323,7 +325,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
         const size_t off[1] = {(size_t)m * p.k + k};
         const bool on[1] = {true};
         float out[1];
-        peer_pull_sum<1>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
+        peer_pull_sum<1, (WIDE ? 4 : 2)>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
         return out[0];
       }
     }
@@ -346,7 +348,7 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
           on[e] = idx < stage_n && m < p.m;
           off[e] = on[e] ? (size_t)m * p.k + k_lo + kk : 0;
         }
-        if (on[0] || on[1]) peer_pull_sum<2>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
+        if (on[0] || on[1]) peer_pull_sum<2, (WIDE ? 4 : 2)>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
         xv[it] = on[0] ? out[0] : 0.0f;
         xv[it + 1] = on[1] ? out[1] : 0.0f;
       }
@@ -384,20 +386,21 @@ gemv_f16w_kernel(const __grid_constant__ GemvGroup g) {
     for (int m = 0; m < MROWS; ++m) {
       ss[m] = 0.0f;
       if ((uint32_t)m < p.m && pull) {
-        if constexpr (PEER) {   // two row elements per poll (registers), squares added in k order
-          for (uint32_t k0 = threadIdx.x; k0 < p.k; k0 += 2 * GEMV_THREADS) {
-            size_t off[2];
-            bool on[2];
-            float out[2];
+        if constexpr (PEER) {   // NE row elements per poll (registers), squares added in k order
+          constexpr int NE = WIDE ? 4 : 2;
+          for (uint32_t k0 = threadIdx.x; k0 < p.k; k0 += NE * GEMV_THREADS) {
+            size_t off[NE];
+            bool on[NE];
+            float out[NE];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
+            for (int e = 0; e < NE; ++e) {
               const uint32_t k = k0 + e * GEMV_THREADS;
               on[e] = k < p.k;
               off[e] = on[e] ? (size_t)m * p.k + k : 0;
             }
-            peer_pull_sum<2>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
+            peer_pull_sum<NE, NE>(g.peer, pull_flag, off, on, out, g.status, peer_dead);
 #pragma unroll
-            for (int e = 0; e < 2; ++e)
+            for (int e = 0; e < NE; ++e)
               if (on[e]) ss[m] = fmaf(out[e], out[e], ss[m]);
           }
         }
@@ -654,14 +657,14 @@ size_t gemv_smem_bytes(uint32_t k_cta, int mrows, int tn, uint32_t s, bool bulk 
 
 bool pdl_enabled() { return tunables().pdl; }
 
-template <int MROWS, int TN, bool BULK, bool PEER = false>
+template <int MROWS, int TN, bool BULK, bool PEER = false, bool WIDE = false>
 void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   const size_t smem = gemv_smem_bytes(g.k_cta, MROWS, TN, g.ksplit, BULK);
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TA_CUDA(cudaFuncSetAttribute(gemv_f16w_kernel<MROWS, TN, BULK, PEER, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  200 * 1024));
     attr_done[dev & 63] = true;
   }
@@ -684,7 +687,7 @@ void launch_t(GemvGroup &g, uint32_t tiles, cudaStream_t stream) {
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK, PEER>, g));
+  TA_CUDA(cudaLaunchKernelEx(&cfg, gemv_f16w_kernel<MROWS, TN, BULK, PEER, WIDE>, g));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
@@ -811,8 +814,16 @@ void launch_gemv_f16w_group(const Context &ctx, const GemvParams *segs, int nseg
     return;                                                                       \
   }
   if (peer) {
-    if (tn == 64) launch_t<1, 64, false, true>(g, tiles, stream);
-    else launch_t<1, 32, false, true>(g, tiles, stream);
+    // four ranks and more, one wave at two CTAs per SM: the variant with the wider pulls (on 2 GPUs it
+    // measured 0.807 against 0.792 ms per token for the launches that fit, so two ranks never take it)
+    const bool wide = peer->world >= 4 && (uint64_t)tiles * best_s <= 2ull * (uint64_t)sm_count && tunables().gemv_peer_wide;
+    if (wide) {
+      if (tn == 64) launch_t<1, 64, false, true, true>(g, tiles, stream);
+      else launch_t<1, 32, false, true, true>(g, tiles, stream);
+    } else {
+      if (tn == 64) launch_t<1, 64, false, true, false>(g, tiles, stream);
+      else launch_t<1, 32, false, true, false>(g, tiles, stream);
+    }
     return;
   }
   TA_GEMV_CASE(1)

@@ -70,6 +70,7 @@ struct Tunables {
   bool f16w_dual = true;          // f16w tensor-core GEMM: up and gate of a SwiGLU pair as one dual-matrix launch
   uint32_t attn_chunks = 0;       // decode attention with a position cell: chunk grid (0 = one 64-position tile per chunk, 8..32)
   uint32_t flash_groups = 2;     // tensor-core prefill attention: warp groups per query block that split its K/V tiles (1 or 2)
+  bool gemv_peer_wide = true;     // exchange GEMV launches that fit one wave at two CTAs per SM take the 128-register variant
   bool gemv_handoff = true;       // row GEMV: cluster ranks reach rank 0 with st.async counted on an mbarrier (0: stores + cluster barrier)
   bool attn_pairs = true;         // decode attention hands its chunk partials over as flagged pairs (no fence, no ticket)
   bool pos_stage = true;          // position cells read by graph launches are staged to device memory per submission
