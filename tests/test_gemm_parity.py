@@ -370,6 +370,14 @@ def test_few_tile_ops_split_along_k(setup, orc):
     ref = orc.cpu_bmm(ha, hb, batch, m, n, k)
     ref = orc.cpu_epilogue(ref, batch, m, n, bias=hbias, act="gelu", binary="add_scaled", d=hr, beta=1.0)
     check(orc, ex.download(c), ref, epi_tol(orc, k), "batched few-tile op, in-place residual")
+    # planes are added in plane order: two runs on the same operands agree bit for bit
+    n2 = 1024
+    a2, _ = upload_det(ta, ctx, ex, orc, (n2, n2), 0)
+    b2, _ = upload_det(ta, ctx, ex, orc, (n2, n2), 1)
+    c2, c3 = ta.Tensor.uninit_device(ctx, (n2, n2)), ta.Tensor.uninit_device(ctx, (n2, n2))
+    ex.run_matmuls([ta.MatmulCall(a2, b2, c2)])
+    ex.run_matmuls([ta.MatmulCall(a2, b2, c3)])
+    assert (ex.download(c2) == ex.download(c3)).all()
 
 
 def test_config2_shape_family_small(setup, orc):
