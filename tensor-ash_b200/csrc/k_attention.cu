@@ -441,6 +441,99 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// The combine of the flagged hand-over, run by 128 threads (row = query row, lane = one of sixteen)
+// of the CTA of chunk 0: polls the pairs of every live chunk (bounded), weighs and sums them in
+// chunk order, writes the kv head's output rows and advances its launch count.
+__device__ __forceinline__ void attn_decode_combine_pairs(const AttnDecodeParams &p, uint4 *pair_rows, uint32_t kv_head, uint32_t row,
+                                                          uint32_t lane, uint32_t kv_len, uint32_t chunk_size, uint32_t pair_flag) {
+  if (row >= p.group) return;
+  constexpr uint32_t ROW_V4 = (DEC_DH + 2) / 2;
+  auto ld_pair = [](const uint4 *src) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+    return v;
+  };
+  const uint32_t live_chunks = chunk_size ? min(p.num_chunks, (kv_len + chunk_size - 1) / chunk_size) : 0u;
+  const uint32_t half_mask = 0xffffu << (16u * (row & 1u));   // the sixteen lanes of this row
+  const uint4 *rbase = pair_rows + (size_t)row * ROW_V4;
+  constexpr size_t CSTEP = 8u * ROW_V4;
+  const uint64_t t_begin = global_timer_ns();
+  bool gave_up = false;
+  // a pair is there when both of its flags are set.  A poll re-requests EVERY pair that is not
+  // there yet before it looks at any (one L2 round trip per poll, whatever the number missing),
+  // bounded at about a second.
+  auto there = [&](const uint4 &v) { return v.y == pair_flag && v.w == pair_flag; };
+  float num[4] = {0.f, 0.f, 0.f, 0.f}, l_total = 0.0f;
+  constexpr int MAXB = ATTN_DECODE_MAX_CHUNKS / 16;
+  uint4 ml[MAXB], pa[16], pb[16];   // this lane's (max, sum) pair per batch of sixteen chunks; a batch's sums
+#pragma unroll
+  for (int b = 0; b < MAXB; ++b) ml[b] = make_uint4(__float_as_uint(NEG_BIG), 0u, 0u, 0u);
+  auto poll_batch = [&](uint32_t c0, bool with_ml) {
+#pragma unroll
+    for (int u = 0; u < 16; ++u) pa[u] = pb[u] = make_uint4(0u, 0u, 0u, 0u);
+    uint32_t spins = 0;
+    for (;;) {
+      if (with_ml) {
+#pragma unroll
+        for (int b = 0; b < MAXB; ++b) {
+          const uint32_t c = 16u * b + lane;
+          if (c < live_chunks && !there(ml[b])) ml[b] = ld_pair(rbase + c * CSTEP + DEC_DH / 2);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const uint32_t c = c0 + u;
+        if (c < live_chunks) {
+          if (!there(pa[u])) pa[u] = ld_pair(rbase + c * CSTEP + lane * 2);
+          if (!there(pb[u])) pb[u] = ld_pair(rbase + c * CSTEP + lane * 2 + 1);
+        }
+      }
+      bool all = true;
+      if (with_ml) {
+#pragma unroll
+        for (int b = 0; b < MAXB; ++b) all = all && (16u * b + lane >= live_chunks || there(ml[b]));
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) all = all && (c0 + u >= live_chunks || (there(pa[u]) && there(pb[u])));
+      if (all) break;
+      if ((++spins & 63u) == 0 && global_timer_ns() - t_begin > 1000000000ull) {
+        gave_up = true;
+        break;
+      }
+    }
+  };
+  poll_batch(0, true);
+  float m_star = NEG_BIG, w_l[MAXB], l_l[MAXB];
+#pragma unroll
+  for (int b = 0; b < MAXB; ++b) m_star = fmaxf(m_star, 16u * b + lane < live_chunks ? __uint_as_float(ml[b].x) : NEG_BIG);
+#pragma unroll
+  for (int off = DEC_LANES / 2; off >= 1; off >>= 1) m_star = fmaxf(m_star, __shfl_xor_sync(half_mask, m_star, off, 16));
+#pragma unroll
+  for (int b = 0; b < MAXB; ++b) {
+    w_l[b] = 16u * b + lane < live_chunks ? expf(__uint_as_float(ml[b].x) - m_star) : 0.0f;
+    l_l[b] = __uint_as_float(ml[b].z);
+  }
+#pragma unroll
+  for (int b = 0; b < MAXB; ++b) {
+    if (16u * b < live_chunks) {   // the same for the sixteen lanes of the row
+      if (b > 0) poll_batch(16u * b, false);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        // past the live count: weight 0 (from the lane that holds no chunk) times the zeros of an unfetched pair
+        const float w = __shfl_sync(half_mask, w_l[b], u, 16), lc = __shfl_sync(half_mask, l_l[b], u, 16);
+        l_total = fmaf(lc, w, l_total);
+        num[0] = fmaf(__uint_as_float(pa[u].x), w, num[0]); num[1] = fmaf(__uint_as_float(pa[u].z), w, num[1]);
+        num[2] = fmaf(__uint_as_float(pb[u].x), w, num[2]); num[3] = fmaf(__uint_as_float(pb[u].z), w, num[3]);
+      }
+    }
+  }
+  if (gave_up && p.status) atomicOr(p.status, 1u);
+  const float inv = l_total > 0.0f ? 1.0f / l_total : 0.0f;
+  float *o = p.out + ((size_t)kv_head * p.group + row) * DEC_DH + lane * 4;
+  *reinterpret_cast<float4 *>(o) = make_float4(num[0] * inv, num[1] * inv, num[2] * inv, num[3] * inv);
+  if (row == 0 && lane == 0) p.pair_seq[kv_head] = pair_flag;   // the next launch on this slot tags with the next count
+}
+
 __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_kernel(const AttnDecodeParams p) {
   // f16 caches with 16-byte rows (the decode graph's case): a thread keeps ITS K values in registers
@@ -662,11 +755,6 @@ attn_decode_kernel(const AttnDecodeParams p) {
       asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(pair_flag),
                    "r"(__float_as_uint(b)), "r"(pair_flag) : "memory");
     };
-    auto ld_pair = [](const uint4 *src) {
-      uint4 v;
-      asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
-      return v;
-    };
     if (live && p0 < p1) {
       uint4 *dst = pair_rows + ((size_t)chunk * 8u + row) * ROW_V4;
       st_pair(dst + lane * 2, acc[0], acc[1]);
@@ -674,85 +762,7 @@ attn_decode_kernel(const AttnDecodeParams p) {
       if (lane == 0) st_pair(dst + DEC_DH / 2, m_run, l_run);
     }
     if (chunk != 0 || !live) return;
-    const uint32_t live_chunks = chunk_size ? min(p.num_chunks, (kv_len + chunk_size - 1) / chunk_size) : 0u;
-    const uint32_t half_mask = 0xffffu << (16u * (row & 1u));   // the sixteen lanes of this row
-    const uint4 *rbase = pair_rows + (size_t)row * ROW_V4;
-    constexpr size_t CSTEP = 8u * ROW_V4;
-    const uint64_t t_begin = global_timer_ns();
-    bool gave_up = false;
-    // a pair is there when both of its flags are set.  A poll re-requests EVERY pair that is not
-    // there yet before it looks at any (one L2 round trip per poll, whatever the number missing),
-    // bounded at about a second.
-    auto there = [&](const uint4 &v) { return v.y == pair_flag && v.w == pair_flag; };
-    float num[4] = {0.f, 0.f, 0.f, 0.f}, l_total = 0.0f;
-    constexpr int MAXB = ATTN_DECODE_MAX_CHUNKS / 16;
-    uint4 ml[MAXB], pa[16], pb[16];   // this lane's (max, sum) pair per batch of sixteen chunks; a batch's sums
-#pragma unroll
-    for (int b = 0; b < MAXB; ++b) ml[b] = make_uint4(__float_as_uint(NEG_BIG), 0u, 0u, 0u);
-    auto poll_batch = [&](uint32_t c0, bool with_ml) {
-#pragma unroll
-      for (int u = 0; u < 16; ++u) pa[u] = pb[u] = make_uint4(0u, 0u, 0u, 0u);
-      uint32_t spins = 0;
-      for (;;) {
-        if (with_ml) {
-#pragma unroll
-          for (int b = 0; b < MAXB; ++b) {
-            const uint32_t c = 16u * b + lane;
-            if (c < live_chunks && !there(ml[b])) ml[b] = ld_pair(rbase + c * CSTEP + DEC_DH / 2);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const uint32_t c = c0 + u;
-          if (c < live_chunks) {
-            if (!there(pa[u])) pa[u] = ld_pair(rbase + c * CSTEP + lane * 2);
-            if (!there(pb[u])) pb[u] = ld_pair(rbase + c * CSTEP + lane * 2 + 1);
-          }
-        }
-        bool all = true;
-        if (with_ml) {
-#pragma unroll
-          for (int b = 0; b < MAXB; ++b) all = all && (16u * b + lane >= live_chunks || there(ml[b]));
-        }
-#pragma unroll
-        for (int u = 0; u < 16; ++u) all = all && (c0 + u >= live_chunks || (there(pa[u]) && there(pb[u])));
-        if (all) break;
-        if ((++spins & 63u) == 0 && global_timer_ns() - t_begin > 1000000000ull) {
-          gave_up = true;
-          break;
-        }
-      }
-    };
-    poll_batch(0, true);
-    float m_star = NEG_BIG, w_l[MAXB], l_l[MAXB];
-#pragma unroll
-    for (int b = 0; b < MAXB; ++b) m_star = fmaxf(m_star, 16u * b + lane < live_chunks ? __uint_as_float(ml[b].x) : NEG_BIG);
-#pragma unroll
-    for (int off = DEC_LANES / 2; off >= 1; off >>= 1) m_star = fmaxf(m_star, __shfl_xor_sync(half_mask, m_star, off, 16));
-#pragma unroll
-    for (int b = 0; b < MAXB; ++b) {
-      w_l[b] = 16u * b + lane < live_chunks ? expf(__uint_as_float(ml[b].x) - m_star) : 0.0f;
-      l_l[b] = __uint_as_float(ml[b].z);
-    }
-#pragma unroll
-    for (int b = 0; b < MAXB; ++b) {
-      if (16u * b < live_chunks) {   // the same for the sixteen lanes of the row
-        if (b > 0) poll_batch(16u * b, false);
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          // past the live count: weight 0 (from the lane that holds no chunk) times the zeros of an unfetched pair
-          const float w = __shfl_sync(half_mask, w_l[b], u, 16), lc = __shfl_sync(half_mask, l_l[b], u, 16);
-          l_total = fmaf(lc, w, l_total);
-          num[0] = fmaf(__uint_as_float(pa[u].x), w, num[0]); num[1] = fmaf(__uint_as_float(pa[u].z), w, num[1]);
-          num[2] = fmaf(__uint_as_float(pb[u].x), w, num[2]); num[3] = fmaf(__uint_as_float(pb[u].z), w, num[3]);
-        }
-      }
-    }
-    if (gave_up && p.status) atomicOr(p.status, 1u);
-    const float inv = l_total > 0.0f ? 1.0f / l_total : 0.0f;
-    float *o = p.out + ((size_t)kv_head * p.group + row) * DEC_DH + lane * 4;
-    *reinterpret_cast<float4 *>(o) = make_float4(num[0] * inv, num[1] * inv, num[2] * inv, num[3] * inv);
-    if (tid == 0) p.pair_seq[kv_head] = pair_flag;   // the next launch on this slot tags with the next count
+    attn_decode_combine_pairs(p, pair_rows, kv_head, row, lane, kv_len, chunk_size, pair_flag);
     return;
   }
   if (live) {
@@ -822,6 +832,177 @@ attn_decode_kernel(const AttnDecodeParams p) {
 }
 
 
+// The decode graph's case as its own kernel: f16 caches with 16-byte rows and the flagged hand-over,
+// 256 threads = 8 query rows x 32 lanes (a warp per row).  A lane owns TWO positions of a tile (all
+// 64 head dims of K in 64 registers) and two output dims, half of what a lane of the 128-thread
+// kernel above carries, so the score loop and the P V loop are half as long.  Every sum runs in
+// the order of that kernel (scores over d, outputs over positions, the tile's weight sum as
+// ((p0 + p1) + p2) + p3 per group of four positions and then the same tree), so the two kernels
+// agree bit for bit; the combine is the same code on the first 128 threads.
+constexpr int DP_THREADS = 256;
+
+__global__ void __launch_bounds__(DP_THREADS)
+attn_decode_pairs_kernel(const AttnDecodeParams p) {
+  __shared__ __align__(16) __half Vh[DEC_BP * DEC_DH];   // [j][64 halves]
+  __shared__ __align__(16) float Qsh[DEC_DH * 8];        // [d][row]
+  __shared__ __align__(16) float Psh[DEC_BP * 8];        // [j][row]
+  const uint32_t chunk = blockIdx.x, kv_head = blockIdx.y, tid = threadIdx.x;
+  const uint32_t row = tid >> 5, l32 = tid & 31u, c = l32 >> 1, h = l32 & 1u;
+  const bool live = row < p.group;
+  const uint32_t pos_in = 4u * c + 2u * h;   // this lane's two positions inside a tile
+
+  uint32_t kv_len = p.kv_len + (p.pos_ptr ? *p.pos_ptr : 0u);
+  if (kv_len > p.t_max || kv_len < p.kv_len) {   // a position the cache does not hold: stay inside it and report
+    if (tid == 0 && chunk == 0 && kv_head == 0 && p.status) atomicOr(p.status, 8u);
+    kv_len = p.t_max;
+  }
+  const uint32_t chunk_size = (((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u;
+  const uint32_t p0 = min(kv_len, chunk * chunk_size), p1 = min(p0 + chunk_size, kv_len);
+  const size_t kt_base = (size_t)kv_head * DEC_DH * p.t_max, v_base = (size_t)kv_head * p.t_max * DEC_DH;
+
+  uint32_t kreg[DEC_DH];   // K[d][t0 + pos_in], K[d][t0 + pos_in + 1]
+  uint4 vraw[2];           // 64 position rows x 8 groups of 8 dims, two groups per thread
+  auto load_tile = [&](uint32_t t0, uint32_t n) {
+    const __half *kcol = static_cast<const __half *>(p.kt) + kt_base + t0 + pos_in;
+    const bool k_ok = pos_in < n;   // a pair may run past kv_len inside t_max (a multiple of 8): masked at the scores
+#pragma unroll
+    for (int d = 0; d < DEC_DH; ++d) kreg[d] = k_ok ? *reinterpret_cast<const uint32_t *>(kcol + (size_t)d * p.t_max) : 0u;
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const uint32_t i = tid + it * DP_THREADS, j = i >> 3, dg = (i & 7u) * 8u;
+      vraw[it] = make_uint4(0u, 0u, 0u, 0u);
+      if (j < n) vraw[it] = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)(t0 + j) * DEC_DH + dg);
+    }
+  };
+  const uint32_t n_first = min((uint32_t)DEC_BP, p1 - p0);
+  const bool newest_here = kv_len > 0 && kv_len - 1 >= p0 && kv_len - 1 < p0 + n_first;
+  const bool early = n_first > 0 && p.prefetch_kv;
+  if (early) load_tile(p0, n_first);
+  uint32_t pair_flag = __ldcg(p.pair_seq + kv_head) + 1u;
+  if (pair_flag == 0u) pair_flag = 1u;
+
+  if (p.pdl) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+  float4 qv = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool q_vec = (reinterpret_cast<uintptr_t>(p.q) & 15u) == 0;
+  if (q_vec) {
+    if (tid * 4 < p.group * DEC_DH) qv = *reinterpret_cast<const float4 *>(p.q + (size_t)kv_head * p.group * DEC_DH + tid * 4);
+  }
+  if (n_first > 0 && !early) load_tile(p0, n_first);
+  if (early && newest_here) {   // the appended position: its K pair column and its V row, past L1
+    const uint32_t jn = kv_len - 1u - p0;
+    if ((pos_in >> 1) == (jn >> 1)) {
+      const __half *kcol = static_cast<const __half *>(p.kt) + kt_base + p0 + pos_in;
+#pragma unroll
+      for (int d = 0; d < DEC_DH; ++d) kreg[d] = __ldcg(reinterpret_cast<const uint32_t *>(kcol + (size_t)d * p.t_max));
+    }
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const uint32_t i = tid + it * DP_THREADS, j = i >> 3, dg = (i & 7u) * 8u;
+      if (j == jn) vraw[it] = __ldcg(reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.v) + v_base + (size_t)(p0 + j) * DEC_DH + dg));
+    }
+  }
+  if (q_vec) {
+    if (tid * 4 < p.group * DEC_DH) {
+      const uint32_t qr = (tid * 4) / DEC_DH, qd = (tid * 4) % DEC_DH;
+      Qsh[(qd + 0) * 8 + qr] = qv.x; Qsh[(qd + 1) * 8 + qr] = qv.y;
+      Qsh[(qd + 2) * 8 + qr] = qv.z; Qsh[(qd + 3) * 8 + qr] = qv.w;
+    }
+  } else {
+    for (uint32_t i = tid; i < p.group * DEC_DH; i += DP_THREADS) Qsh[(i % DEC_DH) * 8 + i / DEC_DH] = p.q[(size_t)kv_head * p.group * DEC_DH + i];
+  }
+
+  float m_run = NEG_BIG, l_run = 0.0f, acc[2] = {0.f, 0.f};
+  for (uint32_t t0 = p0; t0 < p1; t0 += DEC_BP) {
+    const uint32_t n = min((uint32_t)DEC_BP, p1 - t0);
+    if (t0 != p0) load_tile(t0, n);
+#pragma unroll
+    for (int it = 0; it < 2; ++it) *reinterpret_cast<uint4 *>(Vh + (size_t)(tid + it * DP_THREADS) * 8) = vraw[it];
+    __syncthreads();
+
+    float s[2] = {0.f, 0.f};
+    {
+      float qn[8], qc[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) qn[u] = Qsh[u * 8 + row];
+#pragma unroll
+      for (int d0 = 0; d0 < DEC_DH; d0 += 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) qc[u] = qn[u];
+        if (d0 + 8 < DEC_DH) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) qn[u] = Qsh[(d0 + 8 + u) * 8 + row];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float2 k01 = __half22float2(*reinterpret_cast<const __half2 *>(&kreg[d0 + u]));
+          s[0] = fmaf(qc[u], k01.x, s[0]);
+          s[1] = fmaf(qc[u], k01.y, s[1]);
+        }
+      }
+    }
+    float tmax = NEG_BIG;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      s[q] = (pos_in + q) < n ? s[q] * p.scale : NEG_BIG;
+      tmax = fmaxf(tmax, s[q]);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+    const float m_new = fmaxf(m_run, tmax);
+    const float corr = expf(m_run - m_new);
+    float pe[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      pe[q] = (pos_in + q) < n ? expf(s[q] - m_new) : 0.0f;
+      Psh[(pos_in + q) * 8 + row] = pe[q];
+    }
+    // the weight sum of four positions as ((p0 + p1) + p2) + p3, then the tree over the groups of four
+    const float pair_sum = pe[0] + pe[1];
+    const float below = __shfl_xor_sync(0xffffffffu, pair_sum, 1);     // on the odd lane: p0 + p1 of its group
+    float lsum = (below + pe[0]) + pe[1];                              // valid on the odd lane
+    lsum = __shfl_sync(0xffffffffu, lsum, l32 | 1u);
+#pragma unroll
+    for (int off = 16; off >= 2; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+    l_run = l_run * corr + lsum;
+    m_run = m_new;
+    __syncthreads();
+    acc[0] *= corr;
+    acc[1] *= corr;
+    for (uint32_t j0 = 0; j0 < n; j0 += 8) {   // rows at or past n hold weight 0 and value 0
+      float pj[8];
+      float2 vv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        pj[u] = Psh[(j0 + u) * 8 + row];
+        vv[u] = __half22float2(*reinterpret_cast<const __half2 *>(Vh + (size_t)(j0 + u) * DEC_DH + pos_in));
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        acc[0] = fmaf(pj[u], vv[u].x, acc[0]);
+        acc[1] = fmaf(pj[u], vv[u].y, acc[1]);
+      }
+    }
+    __syncthreads();
+  }
+
+  constexpr uint32_t ROW_V4 = (DEC_DH + 2) / 2;
+  uint4 *pair_rows = reinterpret_cast<uint4 *>(p.pairs) + (size_t)kv_head * p.num_chunks * 8u * ROW_V4;
+  auto st_pair = [&](uint4 *dst, float a, float b) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(pair_flag),
+                 "r"(__float_as_uint(b)), "r"(pair_flag) : "memory");
+  };
+  if (live && p0 < p1) {
+    uint4 *dst = pair_rows + ((size_t)chunk * 8u + row) * ROW_V4;
+    st_pair(dst + l32, acc[0], acc[1]);          // dims 2 l32, 2 l32 + 1
+    if (l32 == 0) st_pair(dst + DEC_DH / 2, m_run, l_run);
+  }
+  if (chunk != 0 || tid >= 128u) return;
+  attn_decode_combine_pairs(p, pair_rows, kv_head, tid >> 4, tid & 15u, kv_len, chunk_size, pair_flag);
+}
+
 inline void launched() {
   TA_CUDA(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -880,7 +1061,14 @@ void launch_attn_decode(const AttnDecodeParams &p, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 1 : 0;
-  TA_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel, p));
+  const bool rows16 = p.kv_f16 && (p.t_max % 8u) == 0 && (reinterpret_cast<uintptr_t>(p.kt) & 15u) == 0 &&
+                      (reinterpret_cast<uintptr_t>(p.v) & 15u) == 0;
+  if (p.pairs && rows16 && tunables().attn_wide) {   // the decode graph's case: a warp per query row
+    cfg.blockDim = dim3(DP_THREADS, 1, 1);
+    TA_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_pairs_kernel, p));
+  } else {
+    TA_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel, p));
+  }
   launched();
 }
 

@@ -72,6 +72,7 @@ struct Tunables {
   uint32_t flash_groups = 2;     // tensor-core prefill attention: warp groups per query block that split its K/V tiles (1 or 2)
   bool gemv_peer_wide = true;     // exchange GEMV launches that fit one wave at two CTAs per SM take the 128-register variant
   bool gemv_handoff = true;       // row GEMV: cluster ranks reach rank 0 with st.async counted on an mbarrier (0: stores + cluster barrier)
+  bool attn_wide = true;          // decode attention on the flagged route runs the 256-thread kernel (a warp per query row)
   bool attn_pairs = true;         // decode attention hands its chunk partials over as flagged pairs (no fence, no ticket)
   bool pos_stage = true;          // position cells read by graph launches are staged to device memory per submission
 };

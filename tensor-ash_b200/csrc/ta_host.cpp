@@ -81,13 +81,14 @@ Tunables parse_tunables(const char *spec) {
     else if (name == "f16w_dual") t.f16w_dual = v != 0;
     else if (name == "pos_stage") t.pos_stage = v != 0;
     else if (name == "attn_pairs") t.attn_pairs = v != 0;
+    else if (name == "attn_wide") t.attn_wide = v != 0;
     else if (name == "gemv_handoff") t.gemv_handoff = v != 0;
     else if (name == "gemv_peer_wide") t.gemv_peer_wide = v != 0;
     else if (name == "flash_groups") t.flash_groups = v == 1 ? 1u : 2u;
     else if (name == "attn_chunks") t.attn_chunks = (uint32_t)std::max(0l, std::min(32l, v));
     else
       fail("TA_EXPERIMENT: unknown switch '%s' (known: tf32x3_chunk_kb, tf32x3_ksplit, gemv_ksplit, gemv_bulk, gemv_umma, "
-           "f16w_pre, f16w_apad, pdl, peer_allreduce, peer_allreduce_big, splitk2_tensor, f16w_splitk, f16w_bn, f16w_tma_store, f16w_dual, attn_chunks, pos_stage, flash_groups, attn_pairs, gemv_handoff, gemv_peer_wide)", name.c_str());
+           "f16w_pre, f16w_apad, pdl, peer_allreduce, peer_allreduce_big, splitk2_tensor, f16w_splitk, f16w_bn, f16w_tma_store, f16w_dual, attn_chunks, pos_stage, flash_groups, attn_pairs, attn_wide, gemv_handoff, gemv_peer_wide)", name.c_str());
   }
   return t;
 }

@@ -97,7 +97,7 @@ def test_experiment_switch_names(ta):
     ta.experiment_check("tf32x3_chunk_kb=32, peer_allreduce=0,gemv_ksplit=4")
     # every switch the integration notes list parses
     ta.experiment_check("tf32x3_ksplit=128,gemv_bulk=1,gemv_umma=0,gemv_handoff=0,gemv_peer_wide=0,f16w_pre=1,f16w_apad=0,"
-                        "f16w_splitk=2,f16w_bn=128,f16w_tma_store=0,f16w_dual=0,attn_chunks=16,attn_pairs=0,flash_groups=1,"
+                        "f16w_splitk=2,f16w_bn=128,f16w_tma_store=0,f16w_dual=0,attn_chunks=16,attn_pairs=0,attn_wide=0,flash_groups=1,"
                         "pos_stage=0,splitk2_tensor=0,pdl=0,peer_allreduce_big=1")
     ta.experiment_check("")
     with pytest.raises(ta.TensorAshError, match="unknown switch 'nope'"):
