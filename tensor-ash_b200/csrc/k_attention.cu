@@ -556,8 +556,11 @@ attn_decode_kernel(const AttnDecodeParams p) {
     if (tid == 0 && chunk == 0 && kv_head == 0 && p.status) atomicOr(p.status, 8u);
     kv_len = p.t_max;
   }
-  // positions per chunk, a multiple of 8 so that f16 K rows start on 16 bytes
-  const uint32_t chunk_size = (((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u;
+  // positions per chunk, a multiple of 8 so that f16 K rows start on 16 bytes: one whole tile when the
+  // grid can cover the current length that way (the fewest live chunks, each a single tile), else an
+  // even split
+  const uint32_t chunk_size = (uint64_t)p.num_chunks * DEC_BP >= kv_len ? (uint32_t)DEC_BP
+                                                                        : ((((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u);
   const uint32_t p0 = min(kv_len, chunk * chunk_size), p1 = min(p0 + chunk_size, kv_len);
   const size_t kt_base = (size_t)kv_head * DEC_DH * p.t_max, v_base = (size_t)kv_head * p.t_max * DEC_DH;
   const bool vec16 = p.kv_f16 && (p.t_max % 8u) == 0 &&
@@ -856,7 +859,8 @@ attn_decode_pairs_kernel(const AttnDecodeParams p) {
     if (tid == 0 && chunk == 0 && kv_head == 0 && p.status) atomicOr(p.status, 8u);
     kv_len = p.t_max;
   }
-  const uint32_t chunk_size = (((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u;
+  const uint32_t chunk_size = (uint64_t)p.num_chunks * DEC_BP >= kv_len ? (uint32_t)DEC_BP
+                                                                        : ((((kv_len + p.num_chunks - 1) / p.num_chunks) + 7u) & ~7u);
   const uint32_t p0 = min(kv_len, chunk * chunk_size), p1 = min(p0 + chunk_size, kv_len);
   const size_t kt_base = (size_t)kv_head * DEC_DH * p.t_max, v_base = (size_t)kv_head * p.t_max * DEC_DH;
 
