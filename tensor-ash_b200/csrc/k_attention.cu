@@ -433,6 +433,10 @@ flash_prefill_mma_kernel(const FlashParams p) {
 // (acc, m, l) go to caller scratch.  The last CTA of a kv head to finish (a
 // ticket counter, reset for the next launch) weighs every chunk by exp(m_i - max m)
 // and sums in chunk order, so the result does not depend on which CTA that is.
+// When the slot lends its pair region the partials travel as flagged (value, flag)
+// pairs instead and the CTA of chunk 0 combines (no fence, no ticket); with 16-byte
+// f16 cache rows that route runs attn_decode_pairs_kernel, a warp per query row.
+// All routes add in the same order and give the same bits.
 constexpr int DEC_DH = 64, DEC_LANES = 16, DEC_THREADS = 128, DEC_BP = 64;
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
